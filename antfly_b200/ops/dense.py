@@ -1,0 +1,189 @@
+"""Dense-layer ops backed by the sm_100a kernels: bf16 GEMM with fused epilogues, LayerNorm / RMSNorm with
+fused residual and partial-sum reduction, embedding lookups, pooling.
+
+Every function takes and returns ``torch`` CUDA tensors and launches on the current stream, so the calls can be
+captured in a CUDA graph.  There is no PyTorch fallback here: on a machine with a GPU a missing kernel library
+is an error.  The fp32 oracles used by the tests live in :mod:`antfly_b200.ops.reference`.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+ACT = {None: 0, "none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "gelu_new": 2, "relu": 3, "silu": 4}
+
+_c_int = ctypes.c_int
+_c_long = ctypes.c_long
+_c_float = ctypes.c_float
+
+
+def _bf16(t: torch.Tensor) -> torch.Tensor:
+    assert t.dtype == torch.bfloat16 and t.is_cuda, "expected a CUDA bf16 tensor"
+    return t
+
+
+def gemm_bf16(
+    a: torch.Tensor,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    act: Optional[str] = None,
+    residual: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    split_k: int = 1,
+    alpha: float = 1.0,
+    tile_n: int = 0,
+) -> torch.Tensor:
+    """``act(alpha * a @ w.T + bias) + residual`` on tcgen05 tensor cores.
+
+    ``a`` is [M, K] and ``w`` is [N, K] (an ``nn.Linear`` weight), both bf16 with unit inner stride.  With
+    ``split_k > 1`` the result is the fp32 partial stack ``[splits, M, N]`` (no bias / activation / residual),
+    to be summed by the consumer (e.g. :func:`norm` with ``partials=``).
+    """
+    _bf16(a), _bf16(w)
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    M, K = a.shape
+    Nn = w.shape[0]
+    lib = N.cuda()
+    splits = int(lib.afb_gemm_effective_splits(_c_int(K), _c_int(split_k))) if split_k > 1 else 1
+    if splits > 1:
+        assert bias is None and act in (None, "none") and residual is None
+        if out is None:
+            out = torch.empty((splits, M, Nn), dtype=torch.float32, device=a.device)
+        out_f32 = 1
+        ldc = Nn
+    else:
+        if out is None:
+            out = torch.empty((M, Nn), dtype=out_dtype, device=a.device)
+        out_f32 = 1 if out.dtype == torch.float32 else 0
+        ldc = out.stride(0) if out.dim() == 2 else Nn
+    ldr = residual.stride(0) if residual is not None else 0
+    rc = lib.afb_gemm_bf16(
+        N.ptr(a), N.ptr(w), N.ptr(out), N.ptr(bias), N.ptr(residual),
+        _c_int(M), _c_int(Nn), _c_int(K), _c_int(a.stride(0)), _c_int(w.stride(0)), _c_int(ldc), _c_int(ldr),
+        _c_int(ACT[act]), _c_int(out_f32), _c_int(splits), _c_float(alpha), _c_int(tile_n), N.stream_ptr(),
+    )
+    N.check(rc, "afb_gemm_bf16")
+    N.count_launch()
+    return out
+
+
+def norm(
+    x: Optional[torch.Tensor],
+    gamma: torch.Tensor,
+    beta: Optional[torch.Tensor] = None,
+    *,
+    eps: float = 1e-5,
+    rms: bool = False,
+    residual: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    partials: Optional[torch.Tensor] = None,
+    want_sum: bool = False,
+    want_norm: bool = True,
+    gamma_plus_one: bool = False,
+    out: Optional[torch.Tensor] = None,
+    sum_out: Optional[torch.Tensor] = None,
+):
+    """LayerNorm / RMSNorm of ``x + sum(partials) + bias + residual``.
+
+    Returns ``y`` or ``(sum, y)`` when ``want_sum``.  ``partials`` is an fp32 stack [S, rows, H] as produced
+    by a split-K GEMM.
+    """
+    src = x if x is not None else partials[0]
+    rows, H = src.shape[-2], src.shape[-1]
+    dev = src.device
+    if want_norm and out is None:
+        out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    if want_sum and sum_out is None:
+        sum_out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    nparts = 0 if partials is None else partials.shape[0]
+    pstride = 0 if partials is None else partials.stride(0)
+    rc = N.cuda().afb_norm(
+        N.ptr(x), N.ptr(partials), _c_int(nparts), _c_long(pstride), N.ptr(residual), N.ptr(bias), N.ptr(gamma),
+        N.ptr(beta), N.ptr(sum_out), N.ptr(out if want_norm else None), ctypes.c_void_p(0), _c_int(rows), _c_int(H),
+        _c_float(eps), _c_int(1 if rms else 0), _c_int(1 if gamma_plus_one else 0), N.stream_ptr(),
+    )
+    N.check(rc, "afb_norm")
+    N.count_launch()
+    if want_sum and want_norm:
+        return sum_out, out
+    return sum_out if want_sum else out
+
+
+def layer_norm(x, gamma, beta, eps: float = 1e-12, residual=None):
+    return norm(x, gamma, beta, eps=eps, rms=False, residual=residual)
+
+
+def rms_norm(x, gamma, eps: float = 1e-5, residual=None, want_sum: bool = False):
+    return norm(x, gamma, None, eps=eps, rms=True, residual=residual, want_sum=want_sum)
+
+
+def bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps: float = 1e-12) -> torch.Tensor:
+    """word[ids] + pos[positions] + typ[type_ids] followed by LayerNorm; ids are int32 [T]."""
+    T = ids.numel()
+    H = word.shape[1]
+    y = torch.empty((T, H), dtype=torch.bfloat16, device=word.device)
+    rc = N.cuda().afb_bert_embed_ln(
+        N.ptr(ids), N.ptr(positions), N.ptr(type_ids), N.ptr(word), N.ptr(pos), N.ptr(typ), N.ptr(gamma),
+        N.ptr(beta), N.ptr(y), _c_int(T), _c_int(H), _c_int(word.shape[0]), _c_int(pos.shape[0]),
+        _c_int(typ.shape[0]), _c_float(eps), N.stream_ptr(),
+    )
+    N.check(rc, "afb_bert_embed_ln")
+    N.count_launch()
+    return y
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, out=None) -> torch.Tensor:
+    T = ids.numel()
+    H = table.shape[1]
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=table.device)
+    rc = N.cuda().afb_embed_gather(N.ptr(ids), N.ptr(table), N.ptr(out), _c_int(T), _c_int(H),
+                                   _c_int(table.shape[0]), _c_float(scale), N.stream_ptr())
+    N.check(rc, "afb_embed_gather")
+    N.count_launch()
+    return out
+
+
+POOL_MODES = {"mean": 0, "cls": 1, "max": 2, "last": 3}
+
+
+def pool(h: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor, mode: str = "mean", normalize: bool = True,
+         mask: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pool token rows ``h`` [T, H] per document (rows starts[b] .. starts[b]+lens[b]) to fp32 [B, H]."""
+    B = starts.numel()
+    H = h.shape[-1]
+    if out is None:
+        out = torch.empty((B, H), dtype=torch.float32, device=h.device)
+    rc = N.cuda().afb_pool(N.ptr(h), N.ptr(starts), N.ptr(lens), N.ptr(mask), N.ptr(out), _c_int(B), _c_int(H),
+                           _c_int(POOL_MODES[mode]), _c_int(1 if normalize else 0), N.stream_ptr())
+    N.check(rc, "afb_pool")
+    N.count_launch()
+    return out
+
+
+def maxsim(q: torch.Tensor, d: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
+    """ColBERT MaxSim of one query [nq, D] against packed document token embeddings [T, D]."""
+    n_docs = starts.numel()
+    out = torch.empty((n_docs,), dtype=torch.float32, device=q.device)
+    rc = N.cuda().afb_maxsim(N.ptr(q), _c_int(q.shape[0]), N.ptr(d), N.ptr(starts), N.ptr(lens), N.ptr(out),
+                             _c_int(n_docs), _c_int(q.shape[1]), N.stream_ptr())
+    N.check(rc, "afb_maxsim")
+    N.count_launch()
+    return out
+
+
+def splade_pool(logits: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
+    B = starts.numel()
+    V = logits.shape[-1]
+    out = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    rc = N.cuda().afb_splade_pool(N.ptr(logits), N.ptr(starts), N.ptr(lens), N.ptr(out), _c_int(B), _c_int(V),
+                                  N.stream_ptr())
+    N.check(rc, "afb_splade_pool")
+    N.count_launch()
+    return out

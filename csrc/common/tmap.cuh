@@ -1,0 +1,34 @@
+// Host-side helpers that build TMA tensor maps without linking libcuda: the encoder is looked up through
+// the runtime's driver entry-point query, so the library loads on a machine that has no driver installed
+// (the build box) and only needs the driver once a kernel is launched.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace afb {
+
+// Returns 0 on success; a negative value if the encoder is unavailable or rejects the arguments.
+// 2-D row-major matrix [rows, cols] of `elem_bytes`-sized elements with row pitch `pitch_bytes`;
+// box = [box_rows, box_cols]; swizzle: 0 none, 1 32B, 2 64B, 3 128B.
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle);
+
+// 3-D [d2, d1, d0] with d0 innermost (contiguous); strides in bytes for d1 and d2.
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t d2,
+                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                 int swizzle);
+
+const char* last_error();
+void set_last_error(const char* fmt, ...);
+
+}  // namespace afb
+
+#define AFB_CHECK_CUDA(expr)                                                              \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess) {                                                              \
+      afb::set_last_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return -1;                                                                          \
+    }                                                                                     \
+  } while (0)

@@ -1,0 +1,303 @@
+// Row normalisations with everything around them fused: LayerNorm / RMSNorm over bf16 rows with fp32
+// statistics, optional residual add (and write-back of the sum), optional bias, and optional reduction of
+// fp32 split-K / cross-GPU partial sums produced by the GEMM kernels.  One CTA per row, 16-byte vector
+// accesses, the fp32 row staged in shared memory so the input is read from HBM exactly once.
+//
+// Replaces the reference's one-thread-per-row RMSNorm and 256-thread LayerNorm / add+LayerNorm
+// (zig/pkg/inference/src/ops/cuda/artifacts/inference_cuda_kernels.cu:390-499) and the Metal
+// rms-norm(+add, +scale) family (zig/pkg/inference/src/backends/metal_kernels.m:2477-2627).
+#include "../common/ptx.cuh"
+#include "../common/tmap.cuh"
+
+namespace afb {
+
+struct NormParams {
+  const __nv_bfloat16* x;         // [rows, H] or null
+  const float* partials;          // [num_partials, rows, H] or null
+  const __nv_bfloat16* residual;  // [rows, H] or null
+  const __nv_bfloat16* bias;      // [H] or null (added before the norm)
+  const __nv_bfloat16* gamma;     // [H]
+  const __nv_bfloat16* beta;      // [H] or null
+  __nv_bfloat16* sum_out;         // [rows, H] or null: x + partials + residual + bias
+  __nv_bfloat16* y;               // [rows, H] or null: normalised output
+  float* y_f32;                   // optional fp32 copy of the normalised output
+  int rows, H, num_partials;
+  long partial_stride;            // elements between partial slices
+  float eps;
+  int rms;                        // 1: RMSNorm, 0: LayerNorm
+  int gamma_plus_one;             // 1: scale by (1 + gamma) (Gemma convention)
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+
+__global__ void norm_kernel(NormParams p) {
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int H = p.H;
+  const size_t base = static_cast<size_t>(row) * H;
+  float lsum = 0.0f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+    if (p.x) {
+      uint4 u = *reinterpret_cast<const uint4*>(p.x + base + i);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+    }
+    for (int s = 0; s < p.num_partials; ++s) {
+      const float4* pp = reinterpret_cast<const float4*>(p.partials + s * p.partial_stride + base + i);
+      float4 a = pp[0], b = pp[1];
+      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    }
+    if (p.bias) {
+      uint4 u = *reinterpret_cast<const uint4*>(p.bias + i);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+    }
+    if (p.residual) {
+      uint4 u = *reinterpret_cast<const uint4*>(p.residual + base + i);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+    }
+    if (p.sum_out) {
+      uint4 u;
+      u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+      u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(p.sum_out + base + i) = u;
+      // The normalisation below sees exactly what was stored, so a later kernel that re-reads sum_out
+      // and one that consumed y agree bit for bit.
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      srow[i + j] = v[j];
+      lsum += p.rms ? v[j] * v[j] : v[j];
+    }
+  }
+  if (!p.y && !p.y_f32) return;
+  float mean = 0.0f, rstd;
+  if (p.rms) {
+    const float ss = block_sum(lsum, red);
+    rstd = rsqrtf(ss / H + p.eps);
+  } else {
+    mean = block_sum(lsum, red) / H;
+    float lv = 0.0f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = srow[i + j] - mean;
+        lv += d * d;
+      }
+    }
+    const float var = block_sum(lv, red) / H;
+    rstd = rsqrtf(var + p.eps);
+  }
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 g = *reinterpret_cast<const uint4*>(p.gamma + i);
+    float gv[8], bv[8];
+    {
+      float2 a = unpack_bf16x2(g.x), b = unpack_bf16x2(g.y), c = unpack_bf16x2(g.z), d = unpack_bf16x2(g.w);
+      gv[0] = a.x; gv[1] = a.y; gv[2] = b.x; gv[3] = b.y; gv[4] = c.x; gv[5] = c.y; gv[6] = d.x; gv[7] = d.y;
+    }
+    if (p.beta) {
+      uint4 u = *reinterpret_cast<const uint4*>(p.beta + i);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      bv[0] = a.x; bv[1] = a.y; bv[2] = b.x; bv[3] = b.y; bv[4] = c.x; bv[5] = c.y; bv[6] = d.x; bv[7] = d.y;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bv[j] = 0.0f;
+    }
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float g1 = p.gamma_plus_one ? gv[j] + 1.0f : gv[j];
+      o[j] = (srow[i + j] - mean) * rstd * g1 + bv[j];
+    }
+    if (p.y) {
+      uint4 u;
+      u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
+      u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
+      *reinterpret_cast<uint4*>(p.y + base + i) = u;
+    }
+    if (p.y_f32) {
+      float4* op = reinterpret_cast<float4*>(p.y_f32 + base + i);
+      op[0] = make_float4(o[0], o[1], o[2], o[3]);
+      op[1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+// BERT embeddings: word + position + token-type lookups, summed and LayerNormed in one pass.
+struct BertEmbedParams {
+  const int* ids;          // [T]
+  const int* positions;    // [T]
+  const int* type_ids;     // [T] or null (type 0)
+  const __nv_bfloat16 *word, *pos, *type;  // tables [*, H]
+  const __nv_bfloat16 *gamma, *beta;
+  __nv_bfloat16* y;        // [T, H]
+  int T, H, vocab, max_pos, n_types;
+  float eps;
+};
+
+__global__ void bert_embed_ln_kernel(BertEmbedParams p) {
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  int id = p.ids[t], pos = p.positions[t], ty = p.type_ids ? p.type_ids[t] : 0;
+  if (id < 0 || id >= p.vocab || pos < 0 || pos >= p.max_pos || ty < 0 || ty >= p.n_types) {
+    status_set(kStatusBadIndex);
+    id = min(max(id, 0), p.vocab - 1);
+    pos = min(max(pos, 0), p.max_pos - 1);
+    ty = min(max(ty, 0), p.n_types - 1);
+  }
+  const int H = p.H;
+  float lsum = 0.0f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 a = *reinterpret_cast<const uint4*>(p.word + static_cast<size_t>(id) * H + i);
+    uint4 b = *reinterpret_cast<const uint4*>(p.pos + static_cast<size_t>(pos) * H + i);
+    uint4 c = *reinterpret_cast<const uint4*>(p.type + static_cast<size_t>(ty) * H + i);
+    const uint32_t* au = &a.x; const uint32_t* bu = &b.x; const uint32_t* cu = &c.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = unpack_bf16x2(au[j]), y = unpack_bf16x2(bu[j]), z = unpack_bf16x2(cu[j]);
+      const float v0 = x.x + y.x + z.x, v1 = x.y + y.y + z.y;
+      srow[i + 2 * j] = v0; srow[i + 2 * j + 1] = v1;
+      lsum += v0 + v1;
+    }
+  }
+  const float mean = block_sum(lsum, red) / H;
+  float lv = 0.0f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float d = srow[i + j] - mean; lv += d * d; }
+  const float rstd = rsqrtf(block_sum(lv, red) / H + p.eps);
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 g = *reinterpret_cast<const uint4*>(p.gamma + i);
+    uint4 be = *reinterpret_cast<const uint4*>(p.beta + i);
+    const uint32_t* gu = &g.x; const uint32_t* bu = &be.x;
+    uint4 o; uint32_t* ou = &o.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 gg = unpack_bf16x2(gu[j]), bb = unpack_bf16x2(bu[j]);
+      ou[j] = pack_bf16x2((srow[i + 2 * j] - mean) * rstd * gg.x + bb.x,
+                          (srow[i + 2 * j + 1] - mean) * rstd * gg.y + bb.y);
+    }
+    *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(t) * H + i) = o;
+  }
+}
+
+// Plain embedding-row gather (decoder token embeddings), optional scale (Gemma multiplies by sqrt(H)).
+__global__ void embed_gather_kernel(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* y, int T, int H,
+                                    int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    status_set(kStatusBadIndex);
+    id = min(max(id, 0), vocab - 1);
+  }
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 a = *reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * H + i);
+    if (scale != 1.0f) {
+      uint32_t* au = &a.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 x = unpack_bf16x2(au[j]);
+        au[j] = pack_bf16x2(x.x * scale, x.y * scale);
+      }
+    }
+    *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + i) = a;
+  }
+}
+
+static int norm_threads(int H) {
+  int t = ((H / 8) + 31) / 32 * 32;
+  if (t < 32) t = 32;
+  if (t > 1024) t = 1024;
+  return t;
+}
+
+}  // namespace afb
+
+extern "C" {
+
+int afb_norm(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
+             const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
+             int H, float eps, int rms, int gamma_plus_one, cudaStream_t stream) {
+  using namespace afb;
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || H > 16384) {
+    set_last_error("afb_norm: hidden size must be a multiple of 8 and <= 16384 (got %d)", H);
+    return -1;
+  }
+  NormParams p;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.partials = partials; p.num_partials = partials ? num_partials : 0; p.partial_stride = partial_stride;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  p.beta = reinterpret_cast<const __nv_bfloat16*>(beta);
+  p.sum_out = reinterpret_cast<__nv_bfloat16*>(sum_out);
+  p.y = reinterpret_cast<__nv_bfloat16*>(y);
+  p.y_f32 = y_f32;
+  p.rows = rows; p.H = H; p.eps = eps; p.rms = rms; p.gamma_plus_one = gamma_plus_one;
+  const size_t smem = static_cast<size_t>(H) * 4;
+  static bool configured = false;
+  if (!configured) {
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
+    configured = true;
+  }
+  norm_kernel<<<rows, norm_threads(H), smem, stream>>>(p);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int afb_bert_embed_ln(const int* ids, const int* positions, const int* type_ids, const void* word, const void* pos,
+                      const void* type, const void* gamma, const void* beta, void* y, int T, int H, int vocab,
+                      int max_pos, int n_types, float eps, cudaStream_t stream) {
+  using namespace afb;
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || H > 12288) {
+    set_last_error("afb_bert_embed_ln: hidden size must be a multiple of 8 and <= 12288 (got %d)", H);
+    return -1;
+  }
+  BertEmbedParams p;
+  p.ids = ids; p.positions = positions; p.type_ids = type_ids;
+  p.word = reinterpret_cast<const __nv_bfloat16*>(word);
+  p.pos = reinterpret_cast<const __nv_bfloat16*>(pos);
+  p.type = reinterpret_cast<const __nv_bfloat16*>(type);
+  p.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  p.beta = reinterpret_cast<const __nv_bfloat16*>(beta);
+  p.y = reinterpret_cast<__nv_bfloat16*>(y);
+  p.T = T; p.H = H; p.vocab = vocab; p.max_pos = max_pos; p.n_types = n_types; p.eps = eps;
+  bert_embed_ln_kernel<<<T, norm_threads(H), static_cast<size_t>(H) * 4, stream>>>(p);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int afb_embed_gather(const int* ids, const void* table, void* y, int T, int H, int vocab, float scale,
+                     cudaStream_t stream) {
+  using namespace afb;
+  if (T <= 0) return 0;
+  if (H % 8 != 0) {
+    set_last_error("afb_embed_gather: hidden size must be a multiple of 8 (got %d)", H);
+    return -1;
+  }
+  embed_gather_kernel<<<T, norm_threads(H), 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
+                                                         reinterpret_cast<__nv_bfloat16*>(y), T, H, vocab, scale);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,144 @@
+// Library-wide host runtime: error string, status-word registry, TMA tensor-map encoder lookup.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <mutex>
+#include <vector>
+
+#include "../common/status.cuh"
+#include "../common/tmap.cuh"
+
+namespace afb {
+
+namespace {
+thread_local char g_err[512] = {0};
+
+std::vector<StatusReader>& readers() {
+  static std::vector<StatusReader> r;
+  return r;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+CUtensorMapDataType dtype_for(int elem_bytes) {
+  switch (elem_bytes) {
+    case 1: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    case 2: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case 4: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+CUtensorMapSwizzle swizzle_for(int s) {
+  switch (s) {
+    case 1: return CU_TENSOR_MAP_SWIZZLE_32B;
+    case 2: return CU_TENSOR_MAP_SWIZZLE_64B;
+    case 3: return CU_TENSOR_MAP_SWIZZLE_128B;
+    default: return CU_TENSOR_MAP_SWIZZLE_NONE;
+  }
+}
+}  // namespace
+
+void register_status_reader(StatusReader fn) { readers().push_back(fn); }
+
+const char* last_error() { return g_err; }
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle) {
+  EncodeTiledFn enc = get_encoder();
+  if (!enc) {
+    set_last_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15)) {
+    set_last_error("TMA operand must be 16-byte aligned with a 16-byte multiple pitch (base=%p pitch=%llu)", base,
+                   (unsigned long long)pitch_bytes);
+    return -2;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dtype_for(elem_bytes), 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(swizzle), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled(2d) failed with %d (rows=%llu cols=%llu pitch=%llu box=%ux%u)", (int)r,
+                   (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows,
+                   box_cols);
+    return -3;
+  }
+  return 0;
+}
+
+int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t d2,
+                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                 int swizzle) {
+  EncodeTiledFn enc = get_encoder();
+  if (!enc) {
+    set_last_error("cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (stride1_bytes & 15) || (stride2_bytes & 15)) {
+    set_last_error("TMA operand must be 16-byte aligned with 16-byte multiple strides");
+    return -2;
+  }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, dtype_for(elem_bytes), 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(swizzle), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled(3d) failed with %d", (int)r);
+    return -3;
+  }
+  return 0;
+}
+
+}  // namespace afb
+
+extern "C" {
+
+const char* afb_last_error() { return afb::last_error(); }
+
+// ORs the status words of every kernel file; clears them when `clear` is non-zero.  Call after a
+// synchronise.  Returns a negative value if a word could not be read.
+int afb_status_read(int clear) {
+  int v = 0;
+  for (auto fn : afb::readers()) {
+    int s = fn(clear);
+    if (s < 0) return -1;
+    v |= s;
+  }
+  return v;
+}
+
+int afb_num_status_words() { return static_cast<int>(afb::readers().size()); }
+
+}  // extern "C"
