@@ -1,0 +1,169 @@
+"""Attention and rotary ops: packed varlen encoder attention, paged-KV prefill/decode attention, fused
+QKV -> (head-norm, RoPE, KV-cache write).  CUDA tensors run the sm_100a kernels; CPU tensors run the fp32 oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+from . import reference as R
+
+_c_int = ctypes.c_int
+_c_long = ctypes.c_long
+_c_float = ctypes.c_float
+
+
+def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, scale: Optional[float] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, Hq, D], k/v [T, Hkv, D] (may be strided views of one fused QKV buffer); sequences are the packed
+    row ranges starts[b] .. starts[b]+lens[b]."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
+        return R.varlen_attention(q, k, v, cu, scale, causal).to(torch.bfloat16)
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
+    assert k.stride(0) == v.stride(0)
+    if out is None:
+        out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    B = starts.numel()
+    rc = N.cuda().afb_attention(
+        N.ptr(q), _c_long(q.stride(0)), N.ptr(k), N.ptr(v), _c_long(k.stride(0)), None, None, None, _c_int(0),
+        _c_int(16), N.ptr(starts), N.ptr(lens), N.ptr(lens), N.ptr(out), _c_long(out.stride(0)), None, None,
+        _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_len), _c_int(1 if causal else 0),
+        _c_int(0), _c_float(scale), _c_int(0), _c_int(0), _c_int(1), N.stream_ptr(),
+    )
+    N.check(rc, "afb_attention")
+    N.count_launch()
+    return out
+
+
+class PagedAttnScratch:
+    """Split-KV partial buffers, sized once for the largest decode batch (scratch memory reused every step)."""
+
+    def __init__(self, max_tokens: int, Hq: int, D: int, max_splits: int, device):
+        self.max_tokens, self.max_splits = max_tokens, max_splits
+        self.part_o = torch.empty((max_splits, max_tokens * Hq, D), dtype=torch.float32, device=device)
+        self.part_lse = torch.empty((max_splits, max_tokens * Hq), dtype=torch.float32, device=device)
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, max_q_len: int,
+                    scale: Optional[float] = None, window: int = 0, decode: Optional[bool] = None,
+                    num_splits: int = 1, scratch: Optional[PagedAttnScratch] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of packed query tokens q [T, Hq, D] against the paged cache
+    k_cache / v_cache [num_blocks, page, Hkv, D].  ``decode`` selects the split-keys organisation (<= 16
+    (position, head-in-group) rows per KV head); default: when max_q_len * group <= 16."""
+    T, Hq, D = q.shape
+    page, Hkv = k_cache.shape[1], k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        return R.paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale,
+                                 window).to(torch.bfloat16)
+    G = Hq // Hkv
+    if decode is None:
+        decode = max_q_len * G <= 16
+    if not decode:
+        num_splits = 1
+    if out is None:
+        out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    part_o = part_lse = None
+    if num_splits > 1:
+        if scratch is None:
+            scratch = PagedAttnScratch(T, Hq, D, num_splits, q.device)
+        assert scratch.max_splits >= num_splits and scratch.part_lse.shape[1] >= T * Hq
+        part_o, part_lse = scratch.part_o, scratch.part_lse
+    B = q_starts.numel()
+    rc = N.cuda().afb_attention(
+        N.ptr(q), _c_long(q.stride(0)), None, None, _c_long(0), N.ptr(k_cache), N.ptr(v_cache),
+        N.ptr(block_tables), _c_int(block_tables.shape[1]), _c_int(page), N.ptr(q_starts), N.ptr(q_lens),
+        N.ptr(kv_lens), N.ptr(out), _c_long(out.stride(0)), N.ptr(part_o), N.ptr(part_lse), _c_int(B), _c_int(T),
+        _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_q_len), _c_int(1), _c_int(window), _c_float(scale), _c_int(1),
+        _c_int(1 if decode else 0), _c_int(num_splits), N.stream_ptr(),
+    )
+    N.check(rc, "afb_attention")
+    N.count_launch(2 if num_splits > 1 else 1)
+    return out
+
+
+def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cache, Hq: int, Hkv: int, D: int,
+                  theta: float, *, partials: Optional[torch.Tensor] = None, bias=None, rope_dim: Optional[int] = None,
+                  half_split: bool = True, freq_scale: float = 1.0, q_norm_w=None, k_norm_w=None,
+                  norm_eps: float = 1e-6, norm_plus_one: bool = False, q_out: Optional[torch.Tensor] = None,
+                  kv_scale: float = 1.0) -> torch.Tensor:
+    """Takes fused QKV rows (bf16, or fp32 split-K partials), applies optional head RMS-norm and RoPE to Q and
+    K, writes K/V into the cache at ``slots`` and returns Q [T, Hq, D] bf16."""
+    src = qkv if qkv is not None else partials[0]
+    T = src.shape[0]
+    rd = rope_dim or D
+    if not src.is_cuda:
+        row = (qkv.float() if qkv is not None else 0) + (partials.float().sum(0) if partials is not None else 0)
+        if bias is not None:
+            row = row + bias.float()
+        row = row.reshape(T, Hq + 2 * Hkv, D)
+        qh, kh, vh = row[:, :Hq], row[:, Hq:Hq + Hkv], row[:, Hq + Hkv:]
+        if q_norm_w is not None:
+            qh = R.norm(qh, q_norm_w, eps=norm_eps, rms=True, gamma_plus_one=norm_plus_one, round_sum_bf16=False)[1]
+        if k_norm_w is not None:
+            kh = R.norm(kh, k_norm_w, eps=norm_eps, rms=True, gamma_plus_one=norm_plus_one, round_sum_bf16=False)[1]
+        qh = R.rope(qh, positions, theta, rd, half_split, freq_scale)
+        kh = R.rope(kh, positions, theta, rd, half_split, freq_scale)
+        kc = k_cache.view(-1, Hkv, D)
+        vc = v_cache.view(-1, Hkv, D)
+        ok = slots >= 0
+        kc[slots[ok].long()] = kh[ok].to(kc.dtype)
+        vc[slots[ok].long()] = vh[ok].to(vc.dtype)
+        return qh.to(torch.bfloat16)
+    if q_out is None:
+        q_out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=src.device)
+    nparts = 0 if partials is None else partials.shape[0]
+    pstride = 0 if partials is None else partials.stride(0)
+    kv_fp8 = 1 if k_cache.dtype in (torch.float8_e4m3fn, torch.uint8) else 0
+    num_slots = k_cache.shape[0] * k_cache.shape[1]
+    rc = N.cuda().afb_rope_kv_write(
+        N.ptr(qkv), N.ptr(partials), _c_int(nparts), _c_long(pstride), N.ptr(bias), N.ptr(positions), N.ptr(slots),
+        N.ptr(q_norm_w), N.ptr(k_norm_w), N.ptr(q_out), N.ptr(k_cache), N.ptr(v_cache), _c_int(T), _c_int(Hq),
+        _c_int(Hkv), _c_int(D), _c_int(rd), _c_int(1 if half_split else 0), _c_float(theta), _c_float(freq_scale),
+        _c_float(norm_eps), _c_int(1 if norm_plus_one else 0), _c_int(kv_fp8), _c_float(kv_scale),
+        _c_long(num_slots), N.stream_ptr(),
+    )
+    N.check(rc, "afb_rope_kv_write")
+    N.count_launch()
+    return q_out
+
+
+def rope_(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: Optional[int] = None,
+          half_split: bool = True, freq_scale: float = 1.0) -> torch.Tensor:
+    """In-place RoPE on x [T, heads, D] bf16."""
+    T, Hh, D = x.shape
+    rd = rope_dim or D
+    if not x.is_cuda:
+        x.copy_(R.rope(x, positions, theta, rd, half_split, freq_scale).to(x.dtype))
+        return x
+    rc = N.cuda().afb_rope_inplace(N.ptr(x), N.ptr(positions), _c_int(T), _c_int(Hh), _c_int(D), _c_int(rd),
+                                   _c_int(1 if half_split else 0), _c_float(theta), _c_float(freq_scale),
+                                   N.stream_ptr())
+    N.check(rc, "afb_rope_inplace")
+    N.count_launch()
+    return x
+
+
+def kv_copy_blocks(k_cache, v_cache, src: torch.Tensor, dst: torch.Tensor) -> None:
+    """Copy whole cache blocks src[i] -> dst[i] (copy-on-write of shared prefix blocks)."""
+    n = src.numel()
+    if n == 0:
+        return
+    if not k_cache.is_cuda:
+        k_cache[dst.long()] = k_cache[src.long()]
+        v_cache[dst.long()] = v_cache[src.long()]
+        return
+    block_bytes = k_cache[0].numel() * k_cache.element_size()
+    rc = N.cuda().afb_kv_copy_blocks(N.ptr(k_cache), N.ptr(v_cache), N.ptr(src), N.ptr(dst), _c_int(n),
+                                     _c_long(block_bytes), N.stream_ptr())
+    N.check(rc, "afb_kv_copy_blocks")
+    N.count_launch()

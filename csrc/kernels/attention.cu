@@ -1,0 +1,457 @@
+// Flash attention for every attention shape the models need, one templated kernel:
+//   * packed variable-length bidirectional attention (BERT-family encoders, cross-encoders),
+//   * causal prefill over a paged KV cache (chunked prefill, mixed prefill+decode batches, speculative verify),
+//   * paged-KV decode attention with the KV range split across the warps of a CTA and across CTAs, merged by
+//     log-sum-exp (a second tiny kernel when more than one CTA shares a sequence).
+// GQA is handled by packing the (query position, head-in-group) pairs of one KV head into the rows of a tile,
+// so K/V are read once per KV head.  Online softmax in the exp2 domain, fp32 accumulation, bf16 I/O.
+//
+// Mask semantics follow the reference's gqaPagedAttentionDirect
+// (zig/pkg/inference/src/ops/native_compute.zig:35093-35173): the query rows of a sequence are its LAST q_len
+// positions; a query at absolute position p sees keys at positions <= p (when causal) and > p - window (when
+// a sliding window is set).  Replaces the reference's thread-per-output encoder attention
+// (zig/pkg/inference/src/ops/cuda/artifacts/inference_cuda_kernels.cu:702-857), which has no paged or GQA
+// path on CUDA at all.
+//
+// Tensor-core path: mma.sync m16n8k16 (bf16) with ldmatrix from XOR-swizzled shared memory, K/V tiles staged
+// by cp.async (zero-filled past the end of the sequence) in a two-deep ring.
+#include "../common/ptx.cuh"
+#include "../common/tmap.cuh"
+
+namespace afb {
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  long q_stride;  // elements between consecutive tokens of q
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  long kv_stride;  // contiguous mode: elements between consecutive tokens of k / v
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;  // paged mode: [num_blocks, page, Hkv, D]
+  const int* block_tables;
+  int max_blocks;
+  int page;
+  const int* q_starts;  // [B] first token row of each sequence in q / out (and k / v in contiguous mode)
+  const int* q_lens;    // [B]
+  const int* kv_lens;   // [B] total keys visible to the sequence (contiguous mode: = q_lens)
+  __nv_bfloat16* out;
+  long out_stride;
+  float* part_o;    // [splits, T*Hq, D]
+  float* part_lse;  // [splits, T*Hq]
+  int T;            // total query tokens
+  int Hq, Hkv;
+  int causal, window;
+  float scale_log2;  // softmax scale * log2(e)
+  int num_splits;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kTileKeys = 64;
+
+template <int D, bool PAGED>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const AttnParams& p, int b,
+                                             int hk, int k0, int kv_len, int kv_row_start) {
+  constexpr int CH = D / 8;
+  for (int idx = threadIdx.x; idx < kTileKeys * CH; idx += blockDim.x) {
+    const int row = idx / CH, ch = idx % CH;
+    const int key = k0 + row;
+    const bool valid = key < kv_len;
+    const __nv_bfloat16 *srcK, *srcV;
+    if (PAGED) {
+      const int kk = valid ? key : 0;
+      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + kk / p.page];
+      const size_t off = ((static_cast<size_t>(blk) * p.page + kk % p.page) * p.Hkv + hk) * D + ch * 8;
+      srcK = p.k_cache + off;
+      srcV = p.v_cache + off;
+    } else {
+      const size_t off = static_cast<size_t>(kv_row_start + (valid ? key : 0)) * p.kv_stride + hk * D + ch * 8;
+      srcK = p.k + off;
+      srcV = p.v + off;
+    }
+    const int dst = row * D + ((ch ^ (row & 7)) * 8);
+    cp_async_16(sK + dst, srcK, valid ? 16 : 0);
+    cp_async_16(sV + dst, srcV, valid ? 16 : 0);
+  }
+}
+
+// SPLIT_KEYS = false: each of the 4 warps owns 16 query rows and all 64 keys of a tile (prefill / encoder).
+// SPLIT_KEYS = true : all warps share the same <= 16 query rows and each owns 16 keys of a tile (decode).
+template <int D, bool PAGED, bool SPLIT_KEYS>
+__global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
+  constexpr int NKB = SPLIT_KEYS ? 2 : 8;  // 8-key blocks per warp per tile
+  constexpr int ND = D / 8;                // 8-wide output blocks
+  constexpr int KSTEPS = D / 16;
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_attn);  // [2 stages][K tile, V tile]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z / p.num_splits;
+  const int split = blockIdx.z % p.num_splits;
+  const int hk = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const int q_start = p.q_starts[b], q_len = p.q_lens[b], kv_len = p.kv_lens[b];
+  const int rows_total = q_len * G;
+  const int tile_row0 = blockIdx.x * (SPLIT_KEYS ? 16 : 64);
+  if (tile_row0 >= rows_total) return;
+  const int pos_off = kv_len - q_len;  // absolute position of the first query row
+
+  // Rows this thread's fragments cover.
+  const int wrow0 = tile_row0 + (SPLIT_KEYS ? 0 : warp * 16);
+  int r_idx[2], r_pos[2], r_head[2];
+  bool r_ok[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = wrow0 + (lane >> 2) + 8 * h;
+    r_idx[h] = r;
+    r_ok[h] = r < rows_total;
+    r_pos[h] = r / G;
+    r_head[h] = hk * G + r % G;
+  }
+
+  // Q fragments straight from global memory (read once).
+  uint32_t qf[KSTEPS][4];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t lo = 0, hi = 0;
+      if (r_ok[h]) {
+        const __nv_bfloat16* qp = p.q + static_cast<size_t>(q_start + r_pos[h]) * p.q_stride + r_head[h] * D +
+                                  kk * 16 + 2 * (lane & 3);
+        lo = *reinterpret_cast<const uint32_t*>(qp);
+        hi = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+      qf[kk][h] = lo;
+      qf[kk][2 + h] = hi;
+    }
+  }
+
+  // KV tile range of this CTA.
+  int kv_hi = kv_len;
+  if (p.causal) {
+    const int last_row = min(rows_total, tile_row0 + (SPLIT_KEYS ? 16 : 64)) - 1;
+    kv_hi = min(kv_len, pos_off + last_row / G + 1);
+  }
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, pos_off + tile_row0 / G - p.window + 1);
+  const int tile_lo = kv_lo / kTileKeys;
+  const int tile_hi = (kv_hi + kTileKeys - 1) / kTileKeys;
+  const int ntiles_all = max(0, tile_hi - tile_lo);
+  const int per_split = (ntiles_all + p.num_splits - 1) / p.num_splits;
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_hi, t_begin + per_split);
+  const int ntiles = max(0, t_end - t_begin);
+
+  float o[ND][4];
+#pragma unroll
+  for (int i = 0; i < ND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+
+  constexpr int TILE_ELEMS = kTileKeys * D;
+  if (ntiles > 0) {
+    load_kv_tile<D, PAGED>(sKV, sKV + TILE_ELEMS, p, b, hk, t_begin * kTileKeys, kv_len, q_start);
+    cp_async_commit();
+  }
+  for (int it = 0; it < ntiles; ++it) {
+    const int stage = it & 1;
+    __nv_bfloat16* sK = sKV + stage * 2 * TILE_ELEMS;
+    __nv_bfloat16* sV = sK + TILE_ELEMS;
+    if (it + 1 < ntiles) {
+      __nv_bfloat16* nK = sKV + (stage ^ 1) * 2 * TILE_ELEMS;
+      load_kv_tile<D, PAGED>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + 1) * kTileKeys, kv_len, q_start);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    const int k0 = (t_begin + it) * kTileKeys;
+    const int wkey0 = SPLIT_KEYS ? warp * 16 : 0;  // first key of the tile this warp handles
+
+    // ---- S = Q K^T ----
+    float s[NKB][4];
+#pragma unroll
+    for (int nb = 0; nb < NKB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < NKB; nb += 2) {
+        const int mi = lane >> 3, rin = lane & 7;
+        const int key = wkey0 + nb * 8 + (mi >> 1) * 8 + rin;
+        const int chunk = kk * 2 + (mi & 1);
+        uint32_t kb[4];
+        ldmatrix_x4(kb, sK + key * D + ((chunk ^ (key & 7)) * 8));
+        mma_bf16_16816(s[nb], qf[kk], kb[0], kb[1]);
+        mma_bf16_16816(s[nb + 1], qf[kk], kb[2], kb[3]);
+      }
+    }
+
+    // ---- mask + online softmax ----
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NKB; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = k0 + wkey0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+        const int qpos = pos_off + r_pos[h];
+        bool ok = r_ok[h] && key < kv_len;
+        if (p.causal) ok = ok && key <= qpos;
+        if (p.window > 0) ok = ok && key > qpos - p.window;
+        const float val = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
+        s[nb][e] = val;
+        mx[h] = fmaxf(mx[h], val);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      alpha[h] = exp2f(m_run[h] - m_use);  // m_run = -inf -> 0
+      m_run[h] = m_new;
+      l_run[h] *= alpha[h];
+      mx[h] = m_use;
+    }
+    uint32_t pf[NKB / 2][4];
+#pragma unroll
+    for (int nb = 0; nb < NKB; ++nb) {
+      const float p0 = exp2f(s[nb][0] - mx[0]);
+      const float p1 = exp2f(s[nb][1] - mx[0]);
+      const float p2 = exp2f(s[nb][2] - mx[1]);
+      const float p3 = exp2f(s[nb][3] - mx[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      pf[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16x2(p0, p1);
+      pf[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+    }
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+
+    // ---- O += P V ----
+#pragma unroll
+    for (int ks = 0; ks < NKB / 2; ++ks) {
+#pragma unroll
+      for (int db = 0; db < ND / 2; ++db) {
+        const int mi = lane >> 3, rin = lane & 7;
+        const int key = wkey0 + ks * 16 + (mi & 1) * 8 + rin;
+        const int chunk = db * 2 + (mi >> 1);
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, sV + key * D + ((chunk ^ (key & 7)) * 8));
+        mma_bf16_16816(o[2 * db], pf[ks], vb[0], vb[1]);
+        mma_bf16_16816(o[2 * db + 1], pf[ks], vb[2], vb[3]);
+      }
+    }
+    __syncthreads();
+  }
+
+  // Row sums across the four threads that share a row.
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+
+  if constexpr (SPLIT_KEYS) {
+    // Merge the four warps (same rows, disjoint keys) through shared memory.
+    float* sO = reinterpret_cast<float*>(smem_attn);  // [4][16][D]
+    float* sM = sO + 4 * 16 * D;                      // [4][16]
+    float* sL = sM + 64;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = (lane >> 2) + 8 * (e >> 1);
+        const int col = i * 8 + 2 * (lane & 3) + (e & 1);
+        sO[(warp * 16 + row) * D + col] = o[i][e];
+      }
+    }
+    if ((lane & 3) == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sM[warp * 16 + (lane >> 2) + 8 * h] = m_run[h];
+        sL[warp * 16 + (lane >> 2) + 8 * h] = l_run[h];
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * D; idx += blockDim.x) {
+      const int row = idx / D, col = idx % D;
+      const int r = tile_row0 + row;
+      if (r >= rows_total) continue;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + row]);
+      float L = 0.0f, acc = 0.0f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float f = exp2f(sM[w * 16 + row] - M);
+          L += f * sL[w * 16 + row];
+          acc += f * sO[(w * 16 + row) * D + col];
+        }
+      }
+      const float val = L > 0.0f ? acc / L : 0.0f;
+      const int tok = q_start + r / G;
+      const int head = hk * G + r % G;
+      if (p.num_splits == 1) {
+        p.out[static_cast<size_t>(tok) * p.out_stride + head * D + col] = __float2bfloat16(val);
+      } else {
+        const size_t prow = static_cast<size_t>(split) * p.T * p.Hq + static_cast<size_t>(tok) * p.Hq + head;
+        p.part_o[prow * D + col] = val;
+        if (col == 0) p.part_lse[prow] = (L > 0.0f) ? M + log2f(L) : -INFINITY;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (!r_ok[h]) continue;
+      const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+      __nv_bfloat16* op = p.out + static_cast<size_t>(q_start + r_pos[h]) * p.out_stride + r_head[h] * D +
+                          2 * (lane & 3);
+#pragma unroll
+      for (int i = 0; i < ND; ++i) {
+        *reinterpret_cast<uint32_t*>(op + i * 8) = pack_bf16x2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      }
+    }
+  }
+}
+
+// Merge split-KV partials: out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max).
+__global__ void attn_merge_kernel(const float* part_o, const float* part_lse, __nv_bfloat16* out, long out_stride,
+                                  int rows /* T*Hq */, int Hq, int D, int splits) {
+  const int row = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_lse[static_cast<size_t>(s) * rows + row]);
+  const int tok = row / Hq, head = row % Hq;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.0f, den = 0.0f;
+    if (M != -INFINITY) {
+      for (int s = 0; s < splits; ++s) {
+        const float f = exp2f(part_lse[static_cast<size_t>(s) * rows + row] - M);
+        den += f;
+        acc += f * part_o[(static_cast<size_t>(s) * rows + row) * D + c];
+      }
+    }
+    out[static_cast<size_t>(tok) * out_stride + head * D + c] = __float2bfloat16(den > 0.0f ? acc / den : 0.0f);
+  }
+}
+
+template <int D, bool PAGED, bool SPLIT_KEYS>
+int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
+  const int smem_tiles = 2 * 2 * kTileKeys * D * 2;
+  const int smem_merge = SPLIT_KEYS ? (4 * 16 * D + 128) * 4 : 0;
+  const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
+  static bool configured = false;
+  if (!configured) {
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(flash_attn_kernel<D, PAGED, SPLIT_KEYS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int rows_per_cta = SPLIT_KEYS ? 16 : 64;
+  dim3 grid((max_rows + rows_per_cta - 1) / rows_per_cta, p.Hkv, B * p.num_splits);
+  flash_attn_kernel<D, PAGED, SPLIT_KEYS><<<grid, 128, smem, stream>>>(p);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace afb
+
+extern "C" {
+
+// mode 0: contiguous K/V (k, v given; kv rows of sequence b start at q_starts[b], kv_lens == q_lens)
+// mode 1: paged K/V (k_cache, v_cache, block_tables)
+// split_keys != 0 selects the decode organisation (<= 16 rows per (sequence, KV head) per CTA);
+// num_splits > 1 additionally splits the KV range across CTAs and needs part_o / part_lse scratch.
+// max_q_len: the largest q_lens[b] (host knowledge, sizes the grid).
+int afb_attention(const void* q, long q_stride, const void* k, const void* v, long kv_stride, const void* k_cache,
+                  const void* v_cache, const int* block_tables, int max_blocks, int page, const int* q_starts,
+                  const int* q_lens, const int* kv_lens, void* out, long out_stride, float* part_o, float* part_lse,
+                  int B, int T, int Hq, int Hkv, int D, int max_q_len, int causal, int window, float scale,
+                  int paged, int split_keys, int num_splits, cudaStream_t stream) {
+  using namespace afb;
+  if (B <= 0 || T <= 0) return 0;
+  if (Hq % Hkv != 0 || (D != 64 && D != 128)) {
+    set_last_error("afb_attention: head_dim must be 64 or 128 and Hq a multiple of Hkv (D=%d Hq=%d Hkv=%d)", D, Hq,
+                   Hkv);
+    return -1;
+  }
+  if ((q_stride & 7) || (kv_stride & 7) || (out_stride & 1)) {
+    set_last_error("afb_attention: q/kv strides must be multiples of 8 elements");
+    return -1;
+  }
+  if (num_splits < 1) num_splits = 1;
+  if (!split_keys) num_splits = 1;
+  if (num_splits > 1 && (!part_o || !part_lse)) {
+    set_last_error("afb_attention: num_splits > 1 needs partial buffers");
+    return -1;
+  }
+  AttnParams p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
+  p.k = reinterpret_cast<const __nv_bfloat16*>(k); p.v = reinterpret_cast<const __nv_bfloat16*>(v);
+  p.kv_stride = kv_stride;
+  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache);
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.page = page;
+  p.q_starts = q_starts; p.q_lens = q_lens; p.kv_lens = kv_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
+  p.part_o = part_o; p.part_lse = part_lse;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_splits = num_splits;
+  const int G = Hq / Hkv;
+  const int max_rows = max_q_len * G;
+  int rc;
+#define AFB_ATTN_DISPATCH(DD)                                                                      \
+  if (paged) {                                                                                     \
+    rc = split_keys ? launch_attn<DD, true, true>(p, B, max_rows, stream)                          \
+                    : launch_attn<DD, true, false>(p, B, max_rows, stream);                        \
+  } else {                                                                                         \
+    rc = split_keys ? launch_attn<DD, false, true>(p, B, max_rows, stream)                         \
+                    : launch_attn<DD, false, false>(p, B, max_rows, stream);                       \
+  }
+  if (D == 64) { AFB_ATTN_DISPATCH(64) } else { AFB_ATTN_DISPATCH(128) }
+#undef AFB_ATTN_DISPATCH
+  if (rc) return rc;
+  if (num_splits > 1) {
+    attn_merge_kernel<<<T * Hq, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_lse, p.out, out_stride, T * Hq, Hq, D,
+                                                                num_splits);
+    AFB_CHECK_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+}  // extern "C"
