@@ -1,0 +1,290 @@
+"""Llama-family decoder (Llama / Mistral / Qwen2 / Qwen3 style: RMSNorm, GQA, RoPE, SwiGLU) over a paged KV cache.
+
+What the layer computes follows the reference's decoderBlock (zig/pkg/inference/src/architectures/gpt.zig:3044:
+norm -> QKV -> RoPE -> paged attention -> o_proj -> +residual -> norm -> SwiGLU FFN -> +residual) and its
+Megatron sharding rules (zig/pkg/inference/src/graph/sharding.zig:74-82: q/k/v/gate/up split by output rows,
+o/down split by input columns).  How it is executed is B200-first:
+
+* weights are block-scaled fp8 (e4m3 + e8m0 per 32) streamed by the W8A16 tcgen05 GEMM; activations bf16;
+* a step is one packed batch of tokens (decode tokens and prefill chunks mixed), one launch per op;
+* skinny decode GEMMs run split-K and hand fp32 partial sums to the next kernel, which fuses the reduction with
+  what it had to do anyway: residual add + RMSNorm, or RoPE + KV-cache write;
+* SwiGLU is the epilogue of the fused gate/up GEMM (rows interleaved at load time);
+* a decode step with a fixed batch is captured once in a CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ops import attention as A
+from ..ops import dense as Dn
+from ..ops import quant as Q
+from ..ops import sampling as S
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 128256
+    hidden_size: int = 4096
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    intermediate_size: int = 14336
+    head_dim: int = 0
+    rope_theta: float = 500000.0
+    rope_dim: int = 0
+    rope_half_split: bool = True
+    rope_freq_scale: float = 1.0
+    rms_norm_eps: float = 1e-5
+    tie_word_embeddings: bool = False
+    qkv_bias: bool = False        # Qwen2
+    qk_norm: bool = False         # Qwen3 per-head RMS norm on Q and K
+    sliding_window: int = 0       # Mistral
+    max_position_embeddings: int = 131072
+
+    def __post_init__(self):
+        if not self.head_dim:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if not self.rope_dim:
+            self.rope_dim = self.head_dim
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "LlamaConfig":
+        keys = {f for f in cls.__dataclass_fields__}
+        cfg = cls(**{k: v for k, v in d.items() if k in keys and v is not None})
+        mt = d.get("model_type", "")
+        if mt == "qwen2":
+            cfg.qkv_bias = True
+        if mt == "qwen3":
+            cfg.qk_norm = True
+        return cfg
+
+    @classmethod
+    def llama3_8b(cls) -> "LlamaConfig":
+        return cls()
+
+    @classmethod
+    def llama3_70b(cls) -> "LlamaConfig":
+        return cls(hidden_size=8192, num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8,
+                   intermediate_size=28672)
+
+    @classmethod
+    def tiny(cls, **kw) -> "LlamaConfig":
+        base = dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, intermediate_size=512, head_dim=64, rope_theta=10000.0)
+        base.update(kw)
+        return cls(**base)
+
+
+@dataclass
+class StepBatch:
+    """One forward pass worth of packed tokens (all int32 tensors on the model's device)."""
+    ids: torch.Tensor           # [T]
+    positions: torch.Tensor     # [T]
+    slots: torch.Tensor         # [T] KV-cache slot of each token
+    q_starts: torch.Tensor      # [B]
+    q_lens: torch.Tensor        # [B]
+    kv_lens: torch.Tensor       # [B] sequence length including this step's tokens
+    block_tables: torch.Tensor  # [B, max_blocks]
+    logit_rows: torch.Tensor    # [R] token rows whose logits are wanted
+    max_q_len: int = 1
+    attn_splits: int = 1
+
+
+def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> int:
+    """Split K so a skinny GEMM still puts about one CTA on every SM."""
+    bt = 16 if m_tokens <= 16 else 32 if m_tokens <= 32 else 64 if m_tokens <= 64 else 128 if m_tokens <= 128 else 256
+    tiles = ((n_out + 127) // 128) * ((m_tokens + bt - 1) // bt)
+    if tiles >= sm_count * 3 // 4:
+        return 1
+    num_kb = (k_in + 63) // 64
+    s = max(1, min(sm_count // tiles, num_kb // 4))
+    return s
+
+
+class LlamaModel:
+    def __init__(self, cfg: LlamaConfig, weights: Dict[str, object], tp_rank: int = 0, tp_size: int = 1,
+                 comm=None):
+        self.cfg, self.w = cfg, weights
+        self.tp_rank, self.tp_size, self.comm = tp_rank, tp_size, comm
+        self.device = weights["embed"].device
+        self.Hq = cfg.num_attention_heads // tp_size
+        self.Hkv = max(cfg.num_key_value_heads // tp_size, 1)
+        self.D = cfg.head_dim
+        self.n_layers = cfg.num_hidden_layers
+        self.vocab_local = weights["lm_head"].out_features if isinstance(weights["lm_head"], Q.Fp8Weight) else \
+            weights["lm_head"].shape[0]
+        self.vocab_offset = tp_rank * self.vocab_local if tp_size > 1 else 0
+        self._scratch: Dict[tuple, torch.Tensor] = {}
+
+    # --------------------------------------------------------------------------------------------------
+    @classmethod
+    def random_init(cls, cfg: LlamaConfig, device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                    comm=None, fast_init: Optional[bool] = None, n_layers: Optional[int] = None) -> "LlamaModel":
+        """Random block-fp8 weights of this rank's shard.  ``fast_init`` draws directly in the quantised domain
+        (no fp32 master), which is what the full-size benchmark models use; small test models quantise real
+        Gaussian weights so the fp32 oracle has something to compare with."""
+        H, F, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+        Hq, Hkv = cfg.num_attention_heads // tp_size, max(cfg.num_key_value_heads // tp_size, 1)
+        if fast_init is None:
+            fast_init = H >= 2048
+        L = n_layers or cfg.num_hidden_layers
+        g = torch.Generator().manual_seed(seed)
+        dev = device
+
+        def dense(n, k, s):
+            return (torch.randn(n, k, generator=g) * (k ** -0.5)).to(torch.bfloat16)
+
+        def fp8(n, k, s, swiglu=False):
+            if fast_init:
+                return Q.random_fp8(n, k, dev, seed=s, interleaved_swiglu=swiglu)
+            w = dense(n, k, s).to(dev)
+            p = Q.pack_fp8(w)
+            p.interleaved_swiglu = swiglu
+            return p
+
+        w: Dict[str, object] = {}
+        V = cfg.vocab_size
+        if fast_init:
+            ge = torch.Generator(device=dev).manual_seed(seed + 1)
+            w["embed"] = (torch.randn(V, H, generator=ge, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        else:
+            w["embed"] = (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device=dev)
+        for l in range(L):
+            p = f"l{l}."
+            s0 = seed * 1000003 + l * 16 + tp_rank * 7919
+            w[p + "ln1"], w[p + "ln2"] = ones(H), ones(H)
+            w[p + "qkv"] = fp8((Hq + 2 * Hkv) * D, H, s0 + 1)
+            if cfg.qkv_bias:
+                w[p + "qkv.b"] = (torch.randn((Hq + 2 * Hkv) * D, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+            if cfg.qk_norm:
+                w[p + "qn"], w[p + "kn"] = ones(D), ones(D)
+            w[p + "o"] = fp8(H, Hq * D, s0 + 2)
+            w[p + "gu"] = fp8(2 * (F // tp_size), H, s0 + 3, swiglu=True)
+            w[p + "down"] = fp8(H, F // tp_size, s0 + 4)
+        w["norm"] = ones(H)
+        vl = V // tp_size if tp_size > 1 else V
+        if cfg.tie_word_embeddings and tp_size == 1:
+            w["lm_head"] = Q.pack_fp8(w["embed"]) if not fast_init else fp8(vl, H, seed + 99)
+        else:
+            w["lm_head"] = fp8(vl, H, seed + 99 + tp_rank)
+        m = cls(cfg, w, tp_rank, tp_size, comm)
+        m.n_layers = L
+        return m
+
+    @classmethod
+    def from_state_dict(cls, cfg: LlamaConfig, sd: Dict[str, torch.Tensor], device="cuda", tp_rank: int = 0,
+                        tp_size: int = 1, comm=None) -> "LlamaModel":
+        """HF names (model.layers.N.self_attn.{q,k,v,o}_proj, mlp.{gate,up,down}_proj, ...) -> fused, sharded,
+        block-fp8 packed layout."""
+        from ..parallel.sharding import shard_rows, shard_cols
+
+        D = cfg.head_dim
+        pre = "model." if any(k.startswith("model.") for k in sd) else ""
+        w: Dict[str, object] = {}
+        emb = sd[pre + "embed_tokens.weight"].to(torch.bfloat16)
+        w["embed"] = emb.to(device)
+        for l in range(cfg.num_hidden_layers):
+            s, p = f"{pre}layers.{l}.", f"l{l}."
+            w[p + "ln1"] = sd[s + "input_layernorm.weight"].to(torch.bfloat16).to(device)
+            w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
+            q = shard_rows(sd[s + "self_attn.q_proj.weight"], tp_rank, tp_size)
+            k = shard_rows(sd[s + "self_attn.k_proj.weight"], tp_rank, tp_size)
+            v = shard_rows(sd[s + "self_attn.v_proj.weight"], tp_rank, tp_size)
+            w[p + "qkv"] = Q.pack_fp8(torch.cat([q, k, v], 0).to(device))
+            if s + "self_attn.q_proj.bias" in sd:
+                w[p + "qkv.b"] = torch.cat([shard_rows(sd[s + f"self_attn.{n}_proj.bias"], tp_rank, tp_size)
+                                            for n in ("q", "k", "v")]).to(torch.bfloat16).to(device)
+            if s + "self_attn.q_norm.weight" in sd:
+                w[p + "qn"] = sd[s + "self_attn.q_norm.weight"].to(torch.bfloat16).to(device)
+                w[p + "kn"] = sd[s + "self_attn.k_norm.weight"].to(torch.bfloat16).to(device)
+            w[p + "o"] = Q.pack_fp8(shard_cols(sd[s + "self_attn.o_proj.weight"], tp_rank, tp_size).to(device))
+            gate = shard_rows(sd[s + "mlp.gate_proj.weight"], tp_rank, tp_size).to(device)
+            up = shard_rows(sd[s + "mlp.up_proj.weight"], tp_rank, tp_size).to(device)
+            w[p + "gu"] = Q.pack_fp8_swiglu(gate, up)
+            w[p + "down"] = Q.pack_fp8(shard_cols(sd[s + "mlp.down_proj.weight"], tp_rank, tp_size).to(device))
+        w["norm"] = sd[pre + "norm.weight"].to(torch.bfloat16).to(device)
+        head = sd.get("lm_head.weight", emb)
+        w["lm_head"] = Q.pack_fp8(shard_rows(head, tp_rank, tp_size).to(device) if tp_size > 1 else head.to(device))
+        return cls(cfg, w, tp_rank, tp_size, comm)
+
+    def draft_view(self, n_layers: int) -> "LlamaModel":
+        """A shallower model that shares this model's first ``n_layers`` layers, embedding, final norm and LM
+        head (self-speculative draft).  It needs its own KV cache of n_layers layers."""
+        m = LlamaModel(self.cfg, self.w, self.tp_rank, self.tp_size, self.comm)
+        m.n_layers = n_layers
+        return m
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for l in range(self.n_layers):
+            for nm in ("qkv", "o", "gu", "down"):
+                n += self.w[f"l{l}.{nm}"].nbytes()
+        n += self.w["lm_head"].nbytes() if isinstance(self.w["lm_head"], Q.Fp8Weight) else 0
+        return n
+
+    # --------------------------------------------------------------------------------------------------
+    def _reduce(self, parts: torch.Tensor) -> torch.Tensor:
+        """Tensor-parallel sum of row-parallel partial outputs (baseline path: NCCL all-reduce)."""
+        if self.tp_size == 1 or self.comm is None:
+            return parts
+        y = parts.sum(0, keepdim=True) if parts.shape[0] > 1 else parts
+        self.comm.all_reduce(y)
+        return y
+
+    def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
+        """Runs the stack on one step batch; K/V of the step's tokens are written into
+        k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
+        cfg, w = self.cfg, self.w
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        T = b.ids.numel()
+        x = Dn.embed_gather(b.ids, w["embed"])
+        h = Dn.norm(x, w["l0.ln1"], eps=cfg.rms_norm_eps, rms=True)
+        for l in range(self.n_layers):
+            p = f"l{l}."
+            qkv_w: Q.Fp8Weight = w[p + "qkv"]
+            parts = Q.gemm_w8a16(h, qkv_w, partials=True,
+                                 split_k=pick_split_k(qkv_w.out_features, qkv_w.in_features, T))
+            q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
+                                partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
+                                half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    scratch=attn_scratch)
+            o_w: Q.Fp8Weight = w[p + "o"]
+            parts = self._reduce(Q.gemm_w8a16(ctx.view(T, Hq * D), o_w, partials=True,
+                                              split_k=pick_split_k(o_w.out_features, o_w.in_features, T)))
+            x, h = Dn.norm(None, w[p + "ln2"], eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts,
+                           want_sum=True)
+            act = Q.gemm_w8a16(h, w[p + "gu"], swiglu=True)
+            d_w: Q.Fp8Weight = w[p + "down"]
+            parts = self._reduce(Q.gemm_w8a16(act, d_w, partials=True,
+                                              split_k=pick_split_k(d_w.out_features, d_w.in_features, T)))
+            last = l + 1 == self.n_layers
+            nw = w["norm"] if last else w[f"l{l + 1}.ln1"]
+            if last:
+                # Only the rows whose logits are wanted go through the final norm and the LM head.
+                x = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True,
+                            want_norm=False)
+            else:
+                x, h = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True)
+        rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
+        hl = Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True)
+        head = w["lm_head"]
+        if isinstance(head, Q.Fp8Weight):
+            return Q.gemm_w8a16(hl, head)
+        return Dn.gemm_bf16(hl, head)
+
+    def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        """Arg-max over the (possibly vocabulary-sharded) logits -> global token ids, int32 [R]."""
+        if self.tp_size == 1 or self.comm is None:
+            return S.argmax(logits)
+        idx, val = S.argmax(logits, vocab_offset=self.vocab_offset, want_val=True)
+        return self.comm.argmax_merge(idx, val)

@@ -1,9 +1,9 @@
 """Dense-layer ops backed by the sm_100a kernels: bf16 GEMM with fused epilogues, LayerNorm / RMSNorm with
 fused residual and partial-sum reduction, embedding lookups, pooling.
 
-Every function takes and returns ``torch`` CUDA tensors and launches on the current stream, so the calls can be
-captured in a CUDA graph.  There is no PyTorch fallback here: on a machine with a GPU a missing kernel library
-is an error.  The fp32 oracles used by the tests live in :mod:`antfly_b200.ops.reference`.
+CUDA tensors always run the kernels, launched on the current stream so the calls can be captured in a CUDA
+graph; a missing kernel library on a GPU machine is an error, never a silent fallback.  CPU tensors run the
+fp32 oracle of :mod:`antfly_b200.ops.reference` (the path the CPU-only tests and the CPU baseline use).
 """
 from __future__ import annotations
 
@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from .. import _native as N
+from . import reference as R
 
 ACT = {None: 0, "none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "gelu_new": 2, "relu": 3, "silu": 4}
 
@@ -44,6 +45,11 @@ def gemm_bf16(
     ``split_k > 1`` the result is the fp32 partial stack ``[splits, M, N]`` (no bias / activation / residual),
     to be summed by the consumer (e.g. :func:`norm` with ``partials=``).
     """
+    if not a.is_cuda:
+        y = R.linear(a, w, bias, act, residual, alpha)
+        if split_k > 1:
+            return y[None]
+        return y.to(out_dtype)
     _bf16(a), _bf16(w)
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
     assert a.stride(1) == 1 and w.stride(1) == 1
@@ -97,6 +103,13 @@ def norm(
     src = x if x is not None else partials[0]
     rows, H = src.shape[-2], src.shape[-1]
     dev = src.device
+    if not src.is_cuda:
+        s_, y_ = R.norm(x, gamma, beta, eps, rms, residual, bias, partials, gamma_plus_one,
+                        round_sum_bf16=want_sum)
+        s_, y_ = s_.to(torch.bfloat16), y_.to(torch.bfloat16)
+        if want_sum and want_norm:
+            return s_, y_
+        return s_ if want_sum else y_
     if want_norm and out is None:
         out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     if want_sum and sum_out is None:
@@ -127,6 +140,8 @@ def bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps: fl
     """word[ids] + pos[positions] + typ[type_ids] followed by LayerNorm; ids are int32 [T]."""
     T = ids.numel()
     H = word.shape[1]
+    if not word.is_cuda:
+        return R.bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps).to(torch.bfloat16)
     y = torch.empty((T, H), dtype=torch.bfloat16, device=word.device)
     rc = N.cuda().afb_bert_embed_ln(
         N.ptr(ids), N.ptr(positions), N.ptr(type_ids), N.ptr(word), N.ptr(pos), N.ptr(typ), N.ptr(gamma),
@@ -141,6 +156,8 @@ def bert_embed_ln(ids, positions, type_ids, word, pos, typ, gamma, beta, eps: fl
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, out=None) -> torch.Tensor:
     T = ids.numel()
     H = table.shape[1]
+    if not table.is_cuda:
+        return (table.float()[ids.long()] * scale).to(torch.bfloat16)
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=table.device)
     rc = N.cuda().afb_embed_gather(N.ptr(ids), N.ptr(table), N.ptr(out), _c_int(T), _c_int(H),
@@ -158,6 +175,8 @@ def pool(h: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor, mode: str = 
     """Pool token rows ``h`` [T, H] per document (rows starts[b] .. starts[b]+lens[b]) to fp32 [B, H]."""
     B = starts.numel()
     H = h.shape[-1]
+    if not h.is_cuda:
+        return R.pool(h, starts, lens, mode, normalize, mask)
     if out is None:
         out = torch.empty((B, H), dtype=torch.float32, device=h.device)
     rc = N.cuda().afb_pool(N.ptr(h), N.ptr(starts), N.ptr(lens), N.ptr(mask), N.ptr(out), _c_int(B), _c_int(H),
@@ -170,6 +189,8 @@ def pool(h: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor, mode: str = 
 def maxsim(q: torch.Tensor, d: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
     """ColBERT MaxSim of one query [nq, D] against packed document token embeddings [T, D]."""
     n_docs = starts.numel()
+    if not q.is_cuda:
+        return R.maxsim(q, d, starts, lens)
     out = torch.empty((n_docs,), dtype=torch.float32, device=q.device)
     rc = N.cuda().afb_maxsim(N.ptr(q), _c_int(q.shape[0]), N.ptr(d), N.ptr(starts), N.ptr(lens), N.ptr(out),
                              _c_int(n_docs), _c_int(q.shape[1]), N.stream_ptr())
@@ -181,6 +202,8 @@ def maxsim(q: torch.Tensor, d: torch.Tensor, starts: torch.Tensor, lens: torch.T
 def splade_pool(logits: torch.Tensor, starts: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
     B = starts.numel()
     V = logits.shape[-1]
+    if not logits.is_cuda:
+        return R.splade_pool(logits, starts, lens)
     out = torch.empty((B, V), dtype=torch.float32, device=logits.device)
     rc = N.cuda().afb_splade_pool(N.ptr(logits), N.ptr(starts), N.ptr(lens), N.ptr(out), _c_int(B), _c_int(V),
                                   N.stream_ptr())
