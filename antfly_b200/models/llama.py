@@ -101,8 +101,10 @@ def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> i
     tiles = ((n_out + 127) // 128) * ((m_tokens + bt - 1) // bt)
     if tiles >= sm_count * 3 // 4:
         return 1
-    num_kb = (k_in + 63) // 64
-    s = max(1, min(sm_count // tiles, num_kb // 4))
+    num_kb = (k_in + 127) // 128
+    # Two CTAs fit on an SM; aim for about 2 x 148 of them, but keep at least 4 K-chunks per CTA and at most 8
+    # partial slices for the consumer to sum.
+    s = max(1, min(2 * sm_count // tiles, num_kb // 4, 8))
     return s
 
 
@@ -229,6 +231,17 @@ class LlamaModel:
         return n
 
     # --------------------------------------------------------------------------------------------------
+    # Skinny batches (decode, speculative verify) take the native MX path: activations are quantised to MX fp8
+    # (two terms ~ bf16 accuracy) and the tensor core applies both block scales; large prefill batches keep
+    # bf16 activations and dequantise the weights in the GEMM (W8A16).
+    mx_max_tokens: int = 128
+    act_terms: int = 2
+
+    def _linear(self, h: torch.Tensor, w: "Q.Fp8Weight", T: int, **kw) -> torch.Tensor:
+        if T <= self.mx_max_tokens and w.in_features % 128 == 0 and self.act_terms > 0:
+            return Q.gemm_mxfp8(Q.quantize_mx(h, terms=self.act_terms), w, **kw)
+        return Q.gemm_w8a16(h, w, **kw)
+
     def _reduce(self, parts: torch.Tensor) -> torch.Tensor:
         """Tensor-parallel sum of row-parallel partial outputs (baseline path: NCCL all-reduce)."""
         if self.tp_size == 1 or self.comm is None:
@@ -249,7 +262,7 @@ class LlamaModel:
         for l in range(self.n_layers):
             p = f"l{l}."
             qkv_w: Q.Fp8Weight = w[p + "qkv"]
-            parts = Q.gemm_w8a16(h, qkv_w, partials=True,
+            parts = self._linear(h, qkv_w, T, partials=True,
                                  split_k=pick_split_k(qkv_w.out_features, qkv_w.in_features, T))
             q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
@@ -259,13 +272,13 @@ class LlamaModel:
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch)
             o_w: Q.Fp8Weight = w[p + "o"]
-            parts = self._reduce(Q.gemm_w8a16(ctx.view(T, Hq * D), o_w, partials=True,
+            parts = self._reduce(self._linear(ctx.view(T, Hq * D), o_w, T, partials=True,
                                               split_k=pick_split_k(o_w.out_features, o_w.in_features, T)))
             x, h = Dn.norm(None, w[p + "ln2"], eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts,
                            want_sum=True)
-            act = Q.gemm_w8a16(h, w[p + "gu"], swiglu=True)
+            act = self._linear(h, w[p + "gu"], T, swiglu=True)
             d_w: Q.Fp8Weight = w[p + "down"]
-            parts = self._reduce(Q.gemm_w8a16(act, d_w, partials=True,
+            parts = self._reduce(self._linear(act, d_w, T, partials=True,
                                               split_k=pick_split_k(d_w.out_features, d_w.in_features, T)))
             last = l + 1 == self.n_layers
             nw = w["norm"] if last else w[f"l{l + 1}.ln1"]
@@ -279,7 +292,7 @@ class LlamaModel:
         hl = Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True)
         head = w["lm_head"]
         if isinstance(head, Q.Fp8Weight):
-            return Q.gemm_w8a16(hl, head)
+            return self._linear(hl, head, hl.shape[0])
         return Dn.gemm_bf16(hl, head)
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:

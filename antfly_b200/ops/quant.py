@@ -121,3 +121,129 @@ def gemm_w8a16(
     N.check(rc, "afb_gemm_w8a16")
     N.count_launch()
     return out
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Native MX path: fp8 activations (one or two terms) x fp8 weights with tensor-core block scaling.
+# ----------------------------------------------------------------------------------------------------------
+_c_long = ctypes.c_long
+
+
+def sf_atoms_from_scales(scales: torch.Tensor) -> torch.Tensor:
+    """[K/32, N] e8m0 bytes -> [ceil(N/128), K/128, 512] scale-factor atoms
+    (byte (r % 32) * 16 + (r / 32) * 4 + kblock for row r of the 128-row tile)."""
+    kb, n = scales.shape
+    assert kb % 4 == 0, "K must be a multiple of 128 for the MX path"
+    n_pad = (n + 127) // 128 * 128
+    if n_pad != n:
+        pad = torch.full((kb, n_pad - n), 127, dtype=scales.dtype, device=scales.device)
+        scales = torch.cat([scales, pad], 1)
+    v = scales.view(kb // 4, 4, n_pad // 128, 4, 32)           # [chunk, j, tile, r/32, r%32]
+    return v.permute(2, 0, 4, 3, 1).contiguous().view(n_pad // 128, kb // 4, 512)
+
+
+def weight_sf_atoms(w: Fp8Weight) -> torch.Tensor:
+    a = getattr(w, "_sf_atoms", None)
+    if a is None:
+        a = sf_atoms_from_scales(w.scales)
+        w._sf_atoms = a
+    return a
+
+
+@dataclass
+class MxAct:
+    """MX-fp8 activations: e4m3 terms [T, K] and their scale-factor atoms [ceil(T/128), K/128, 512]."""
+    q0: torch.Tensor
+    sf0: torch.Tensor
+    q1: Optional[torch.Tensor] = None
+    sf1: Optional[torch.Tensor] = None
+
+    @property
+    def terms(self) -> int:
+        return 2 if self.q1 is not None else 1
+
+    def dequant(self) -> torch.Tensor:
+        def one(q, sf):
+            T, K = q.shape
+            tiles, chunks = sf.shape[0], sf.shape[1]
+            s = sf.view(tiles, chunks, 32, 4, 4).permute(1, 4, 0, 3, 2).reshape(chunks * 4, tiles * 128)[:, :T]
+            return R.dequantize_block_fp8(q.view(torch.float8_e4m3fn), s.contiguous())
+        y = one(self.q0, self.sf0)
+        if self.q1 is not None:
+            y = y + one(self.q1, self.sf1)
+        return y
+
+
+def quantize_mx(x: torch.Tensor, terms: int = 2, out: Optional[MxAct] = None) -> MxAct:
+    """bf16 [T, K] -> MX fp8 (``terms`` = 1: x ~ hi; 2: x ~ hi + lo with lo the quantised residual)."""
+    T, K = x.shape
+    assert K % 128 == 0
+    tiles = (T + 127) // 128
+    dev = x.device
+    if out is None:
+        mk = lambda: torch.empty((T, K), dtype=torch.uint8, device=dev)
+        # Scale bytes of rows past T are never used by a valid output, but keep them defined.
+        mks = lambda: torch.full((tiles, K // 128, 512), 127, dtype=torch.uint8, device=dev)
+        out = MxAct(mk(), mks(), mk() if terms == 2 else None, mks() if terms == 2 else None)
+    if not x.is_cuda:
+        def q_one(v):
+            q, e8 = R.quantize_block_fp8(v)
+            return q, e8
+        q0, e0 = q_one(x.float())
+        out.q0.copy_(q0.view(torch.uint8))
+        pad = tiles * 128 - T
+        def atoms(e8):  # e8: [K/32, T]
+            if pad:
+                e8 = torch.cat([e8, torch.full((e8.shape[0], pad), 127, dtype=e8.dtype)], 1)
+            return sf_atoms_from_scales(e8)
+        out.sf0.copy_(atoms(e0))
+        if terms == 2:
+            r = x.float() - R.dequantize_block_fp8(q0, e0)
+            q1, e1 = q_one(r)
+            out.q1.copy_(q1.view(torch.uint8))
+            out.sf1.copy_(atoms(e1))
+        return out
+    rc = N.cuda().afb_quantize_mx(N.ptr(x), _c_long(x.stride(0)), N.ptr(out.q0), N.ptr(out.q1), N.ptr(out.sf0),
+                                  N.ptr(out.sf1), _c_int(T), _c_int(K), N.stream_ptr())
+    N.check(rc, "afb_quantize_mx")
+    N.count_launch()
+    return out
+
+
+def gemm_mxfp8(x: MxAct, w: Fp8Weight, bias=None, act=None, residual=None, split_k: int = 1, swiglu: bool = False,
+               partials: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dequant(x) @ dequant(w).T`` through tcgen05 block-scaled MMA.  Same output modes as gemm_w8a16."""
+    M, K = x.q0.shape
+    Nn = w.out_features
+    assert K == w.in_features and K % 128 == 0
+    if not x.q0.is_cuda:
+        y = R.linear(x.dequant(), R.dequantize_block_fp8(w.q, w.scales), bias, None if swiglu else act,
+                     None if swiglu else residual)
+        if swiglu:
+            return R.swiglu_interleaved(y).to(torch.bfloat16)
+        return y[None] if (partials or split_k > 1) else y.to(torch.bfloat16)
+    lib = N.cuda()
+    if split_k > 1 or partials:
+        splits = int(lib.afb_mx_effective_splits(_c_int(K), _c_int(max(split_k, 1))))
+        mode = 1
+        if out is None:
+            out = torch.empty((splits, M, Nn), dtype=torch.float32, device=x.q0.device)
+        ldc = Nn
+    elif swiglu:
+        splits, mode = 1, 2
+        if out is None:
+            out = torch.empty((M, Nn // 2), dtype=torch.bfloat16, device=x.q0.device)
+        ldc = out.stride(0)
+    else:
+        splits, mode = 1, 0
+        if out is None:
+            out = torch.empty((M, Nn), dtype=torch.bfloat16, device=x.q0.device)
+        ldc = out.stride(0)
+    ldr = residual.stride(0) if residual is not None else 0
+    rc = lib.afb_gemm_mxfp8(N.ptr(x.q0), N.ptr(x.q1), N.ptr(x.sf0), N.ptr(x.sf1), N.ptr(w.q), N.ptr(weight_sf_atoms(w)),
+                            N.ptr(out), N.ptr(bias), N.ptr(residual), _c_int(M), _c_int(Nn), _c_int(K), _c_int(ldc),
+                            _c_int(ldr), _c_int(ACT[act]), _c_int(mode), _c_int(splits), _c_int(x.terms),
+                            N.stream_ptr())
+    N.check(rc, "afb_gemm_mxfp8")
+    N.count_launch()
+    return out

@@ -1,0 +1,417 @@
+// Block-scaled fp8 x fp8 GEMM on the native MX path of the 5th-generation tensor cores:
+//   out[t, n] = sum_k  (X8[t,k] * 2^(SX[t,k/32]-127))  *  (W8[n,k] * 2^(SW[n,k/32]-127))
+// issued as tcgen05.mma.kind::mxf8f6f4.block_scale (e4m3 operands, one e8m0 scale per 32 K elements, applied by
+// the tensor core itself from scale factors held in tensor memory).  Nothing but TMA and the tensor core touches
+// the weights, so a decode step streams them at memory speed with no CUDA-core work in the loop.
+//
+// Activations are bf16 in memory between layers; the producer kernel (RMSNorm / activation quantiser below)
+// emits them as MX fp8 in one or two terms: x ~= hi, or x ~= hi + lo where lo is the MX-fp8 quantisation of the
+// residual x - hi.  Two terms carry about 7 mantissa bits, i.e. bf16-class accuracy, at the cost of a second
+// (free at decode) MMA pass over the same weight tile.
+//
+// This kernel is the skinny-M (decode, speculative verify) linear layer of the decoder; large-M prefill uses
+// the W8A16 kernel.  Quantised-matmul counterpart of the reference's Metal mul_mv / mul_mm MXFP4 / NVFP4 kernels
+// (zig/pkg/inference/src/backends/metal_kernels.m:3491-3529) and its scalar CUDA Q8_0 / Q4_K linears
+// (zig/pkg/inference/src/ops/cuda/artifacts/inference_cuda_kernels.cu:873-1553).
+//
+// Tile: weights fill the 128 UMMA-M lanes, tokens are UMMA-N (BT = 16..128).  A stage is 128 K elements:
+// 128x128 B of weights + BT x 128 B of activations per term, 128-byte swizzle, plus 512-byte scale-factor atoms
+// that are copied shared -> tensor memory with tcgen05.cp (32x128b.warpx4) right before the four K=32 MMAs that
+// use them (scale-factor byte selected per MMA through the instruction descriptor).
+//   warp 0      TMA producer      warp 1   tcgen05.cp + tcgen05.mma issue      warps 2..5  epilogue
+//
+// Scale-factor atom (512 B, covers 128 rows x 4 K-blocks): byte (r % 32) * 16 + (r / 32) * 4 + kblock.
+#include "../common/ptx.cuh"
+#include "../common/tmap.cuh"
+
+namespace afb {
+
+struct MxParams {
+  void* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  const uint8_t* sfw;   // [n_tiles, k_chunks, 512]
+  const uint8_t* sfx0;  // [t_tiles, k_chunks, 512]
+  const uint8_t* sfx1;  // second term or null
+  int M, N, K;
+  int ldc, ldr;
+  int act;
+  int mode;  // 0 bf16 out, 1 fp32 partials, 2 swiglu
+  int chunks_per_split;
+  int k_chunks;
+};
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Shared-memory descriptor of a 32-row x 16-byte scale-factor atom for tcgen05.cp: no swizzle, 8-row groups
+// 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+// Instruction descriptor, kind::mxf8f6f4 block-scaled, e4m3 x e4m3, ue8m0 scales, K = 32.
+__device__ __forceinline__ uint32_t idesc_mx(int M, int N, int a_sf, int b_sf) {
+  return (static_cast<uint32_t>(b_sf) << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (1u << 23) | (static_cast<uint32_t>(M >> 4) << 24) | (static_cast<uint32_t>(a_sf) << 29);
+}
+
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
+template <int BT, int STAGES, int TERMS>
+struct MxSmem {
+  static constexpr int kWBytes = 128 * 128;
+  static constexpr int kXBytes = BT * 128;
+  static constexpr int kXStage = (kXBytes + 1023) / 1024 * 1024;
+  static constexpr int kSfBytes = 512;
+  static constexpr int kStage = kWBytes + TERMS * kXStage + 1024 + TERMS * 1024;  // SF atoms padded to 1 KiB each
+  static constexpr int kBarOff = STAGES * kStage;
+  static constexpr int kTotal = kBarOff + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static constexpr int kTxBytes = kWBytes + TERMS * kXBytes + (1 + TERMS) * kSfBytes;
+};
+
+template <int BT, int STAGES, int TERMS>
+__global__ void __launch_bounds__(192, (MxSmem<BT, STAGES, TERMS>::kTotal <= 110 * 1024 ? 2 : 1))
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x0,
+                  const __grid_constant__ CUtensorMap tma_x1, MxParams p) {
+  using L = MxSmem<BT, STAGES, TERMS>;
+  constexpr int D_COLS = BT < 32 ? 32 : BT;
+  constexpr int TMEM_COLS = D_COLS <= 32 ? 64 : (D_COLS <= 96 ? 128 : 256);  // D + 12 scale-factor columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, t_tile = blockIdx.y;
+  const int n0 = n_tile * 128, t0 = t_tile * BT;
+  const int c_begin = blockIdx.z * p.chunks_per_split;
+  const int c_end = min(p.k_chunks, c_begin + p.chunks_per_split);
+  const int num_c = c_end - c_begin;
+  // Scale-factor atoms of the token tile: the atom covers 128 rows, so BT < 128 tiles share an atom.
+  const int sfx_tile = t0 / 128;
+  const int sfx_row0 = t0 % 128;  // first row of this tile inside the atom
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_w);
+    tma_prefetch_desc(&tma_x0);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < num_c; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, kStatusEmptyWaitTimeout)) break;
+        uint8_t* st = smem + s * L::kStage;
+        const int c = c_begin + i;
+        mbar_expect_tx(&full[s], L::kTxBytes);
+        tma_load_2d(st, &tma_w, &full[s], c * 128, n0);
+        tma_load_2d(st + L::kWBytes, &tma_x0, &full[s], c * 128, t0);
+        if (TERMS == 2) tma_load_2d(st + L::kWBytes + L::kXStage, &tma_x1, &full[s], c * 128, t0);
+        uint8_t* sf = st + L::kWBytes + TERMS * L::kXStage;
+        bulk_load(sf, p.sfw + (static_cast<size_t>(n_tile) * p.k_chunks + c) * 512, 512, &full[s]);
+        bulk_load(sf + 1024, p.sfx0 + (static_cast<size_t>(sfx_tile) * p.k_chunks + c) * 512, 512, &full[s]);
+        if (TERMS == 2)
+          bulk_load(sf + 2048, p.sfx1 + (static_cast<size_t>(sfx_tile) * p.k_chunks + c) * 512, 512, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t t_sfa = tmem_base + D_COLS;
+      const uint32_t t_sfb0 = t_sfa + 4;
+      const uint32_t t_sfb1 = t_sfa + 8;
+      // Token rows sfx_row0 .. +BT of the atom: row r lives in column r / 32 of the 4-column scale block, so a
+      // tile that starts at row 32, 64 or 96 starts that many columns in.  (BT < 32 tiles start on a multiple
+      // of BT inside a 32-row group; those use the lane offset implicitly because the MMA reads scale lanes
+      // 0..N-1 -- such tiles are only launched with sfx_row0 % 32 == 0.)
+      const uint32_t sfb_col = static_cast<uint32_t>(sfx_row0 / 32);
+      for (int i = 0; i < num_c; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, kStatusTmaWaitTimeout)) break;
+        tcgen05_fence_after();
+        uint8_t* st = smem + s * L::kStage;
+        uint8_t* sf = st + L::kWBytes + TERMS * L::kXStage;
+        tmem_cp_32x128b_warpx4(t_sfa, sf_desc(smem_u32(sf)));
+        tmem_cp_32x128b_warpx4(t_sfb0, sf_desc(smem_u32(sf + 1024)));
+        if (TERMS == 2) tmem_cp_32x128b_warpx4(t_sfb1, sf_desc(smem_u32(sf + 2048)));
+        const uint64_t adesc = umma_desc_k_sw128(smem_u32(st));
+        const uint64_t b0desc = umma_desc_k_sw128(smem_u32(st + L::kWBytes));
+        const uint64_t b1desc = umma_desc_k_sw128(smem_u32(st + L::kWBytes + L::kXStage));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t id = idesc_mx(128, BT < 16 ? 16 : BT, k, k);
+          umma_mx(tmem_base, adesc + 2 * k, b0desc + 2 * k, id, t_sfa, t_sfb0 + sfb_col, (i | k) != 0);
+          if (TERMS == 2) umma_mx(tmem_base, adesc + 2 * k, b1desc + 2 * k, id, t_sfa, t_sfb1 + sfb_col, 1);
+        }
+        umma_commit(&empty[s]);
+      }
+      umma_commit(tmem_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int n = n0 + q * 32 + lane;
+    const bool ok = mbar_wait(tmem_full, 0, kStatusMmaWaitTimeout);
+    tcgen05_fence_after();
+    if (ok && num_c > 0) {
+      const float bias = (p.bias && p.mode != 1 && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+      constexpr int CH = BT < 32 ? 16 : 32;
+#pragma unroll 1
+      for (int c = 0; c < BT; c += CH) {
+        float v[CH];
+        if constexpr (CH == 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        } else {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        if (p.mode == 1) {
+          float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(blockIdx.z) * p.M * p.ldc;
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.M) op[static_cast<size_t>(t) * p.ldc + n] = v[j];
+            }
+          }
+        } else if (p.mode == 2) {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const float mine = v[j] + bias;
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            const int t = t0 + c + j;
+            if (((lane ^ j) & 1) == 0 && t < p.M && n < p.N) {
+              const float g = (lane & 1) ? other : mine;
+              const float u = (lane & 1) ? mine : other;
+              op[static_cast<size_t>(t) * p.ldc + (n >> 1)] = __float2bfloat16(silu(g) * u);
+            }
+          }
+        } else {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out);
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.M) {
+                float x = v[j] + bias;
+                switch (p.act) {
+                  case 1: x = gelu_erf(x); break;
+                  case 2: x = gelu_tanh(x); break;
+                  case 3: x = fmaxf(x, 0.0f); break;
+                  case 4: x = silu(x); break;
+                  default: break;
+                }
+                if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
+                op[static_cast<size_t>(t) * p.ldc + n] = __float2bfloat16(x);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <int BT, int STAGES, int TERMS>
+int launch_mx(const void* W, const void* X0, const void* X1, MxParams p, int splits, cudaStream_t stream) {
+  using L = MxSmem<BT, STAGES, TERMS>;
+  CUtensorMap tw, tx0, tx1;
+  if (make_tmap_2d(&tw, W, 1, p.N, p.K, static_cast<uint64_t>(p.K), 128, 128, 3)) return -1;
+  if (make_tmap_2d(&tx0, X0, 1, p.M, p.K, static_cast<uint64_t>(p.K), BT, 128, 3)) return -1;
+  if (make_tmap_2d(&tx1, TERMS == 2 ? X1 : X0, 1, p.M, p.K, static_cast<uint64_t>(p.K), BT, 128, 3)) return -1;
+  static bool configured = false;
+  if (!configured) {
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_mxfp8_kernel<BT, STAGES, TERMS>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
+  gemm_mxfp8_kernel<BT, STAGES, TERMS><<<grid, 192, L::kTotal, stream>>>(tw, tx0, tx1, p);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Activation quantiser: bf16 [T, K] -> MX fp8 terms (e4m3 bytes [T, K]) + scale-factor atoms.
+// One warp per (token, 128-wide K chunk ... ) : each lane owns 4 consecutive elements, 8 lanes share a 32-block.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e8m0_for_amax(float amax) {
+  // Smallest power of two s with amax / s <= 448; e4m3 max is 448 = 1.75 * 2^8.
+  if (!(amax > 0.0f)) return 127u - 8u;
+  int e;
+  const float m = frexpf(amax, &e);  // amax = m * 2^e, m in [0.5, 1)
+  // amax / 2^s <= 448  <=>  s >= log2(amax) - log2(448); ceil() of that:
+  int s = e - 9 + ((m > 0.875f) ? 1 : 0);  // 448 = 0.875 * 2^9
+  s = max(-127, min(127, s));
+  return static_cast<uint32_t>(s + 127);
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+__device__ __forceinline__ void unpack_e4m3x4(uint32_t v, float (&o)[4]) {
+  const float2 a = e4m3x2_to_float2(static_cast<uint16_t>(v & 0xFFFF));
+  const float2 b = e4m3x2_to_float2(static_cast<uint16_t>(v >> 16));
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
+__global__ void quantize_mx_kernel(const __nv_bfloat16* x, long ldx, uint8_t* q0, uint8_t* q1, uint8_t* sf0,
+                                   uint8_t* sf1, int T, int K) {
+  const int t = blockIdx.x;
+  const int k_chunks = K / 128;
+  for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * ldx + i);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    float v[4] = {a.x, a.y, b.x, b.y};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const uint32_t e0 = e8m0_for_amax(amax);
+    const float inv0 = __uint_as_float((254u - e0) << 23);  // 2^-(e0-127)
+    const uint32_t p0 = pack_e4m3x4(v[0] * inv0, v[1] * inv0, v[2] * inv0, v[3] * inv0);
+    *reinterpret_cast<uint32_t*>(q0 + static_cast<size_t>(t) * K + i) = p0;
+    const int kb = i / 32, chunk = kb / 4, j = kb % 4;
+    const size_t sf_off = (static_cast<size_t>(t / 128) * k_chunks + chunk) * 512 + ((t % 128) % 32) * 16 +
+                          ((t % 128) / 32) * 4 + j;
+    if ((threadIdx.x & 7) == 0) sf0[sf_off] = static_cast<uint8_t>(e0);
+    if (q1) {
+      float d[4];
+      unpack_e4m3x4(p0, d);
+      const float s0 = __uint_as_float(e0 << 23);
+      float r[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) r[c] = v[c] - d[c] * s0;
+      float rmax = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+      const uint32_t e1 = e8m0_for_amax(rmax);
+      const float inv1 = __uint_as_float((254u - e1) << 23);
+      *reinterpret_cast<uint32_t*>(q1 + static_cast<size_t>(t) * K + i) =
+          pack_e4m3x4(r[0] * inv1, r[1] * inv1, r[2] * inv1, r[3] * inv1);
+      if ((threadIdx.x & 7) == 0) sf1[sf_off] = static_cast<uint8_t>(e1);
+    }
+  }
+}
+
+}  // namespace afb
+
+extern "C" {
+
+// X8 terms [M, K] e4m3 with scale atoms sfx*; W8 [N, K] e4m3 with scale atoms sfw.  terms = 1 or 2.
+// Modes as afb_gemm_w8a16.  K must be a multiple of 128.
+int afb_gemm_mxfp8(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8, const void* sfw,
+                   void* out, const void* bias, const void* residual, int M, int N, int K, int ldc, int ldr, int act,
+                   int mode, int split_k, int terms, cudaStream_t stream) {
+  using namespace afb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 128 || (N & 15) || M > 128 * 1024) {
+    set_last_error("afb_gemm_mxfp8: K must be a multiple of 128 and N of 16 (K=%d N=%d)", K, N);
+    return -1;
+  }
+  const int k_chunks = K / 128;
+  if (split_k < 1) split_k = 1;
+  if (split_k > k_chunks) split_k = k_chunks;
+  int per = (k_chunks + split_k - 1) / split_k;
+  split_k = (k_chunks + per - 1) / per;
+  if (mode != 1 && split_k != 1) {
+    set_last_error("afb_gemm_mxfp8: split_k > 1 needs mode 1 (fp32 partials)");
+    return -1;
+  }
+  MxParams p;
+  p.out = out;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.sfw = reinterpret_cast<const uint8_t*>(sfw);
+  p.sfx0 = reinterpret_cast<const uint8_t*>(sfx0);
+  p.sfx1 = reinterpret_cast<const uint8_t*>(sfx1);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr; p.act = act; p.mode = mode;
+  p.chunks_per_split = per; p.k_chunks = k_chunks;
+  if (terms == 2) {
+    if (M <= 32) return launch_mx<32, 4, 2>(W8, X0, X1, p, split_k, stream);
+    if (M <= 64) return launch_mx<64, 3, 2>(W8, X0, X1, p, split_k, stream);
+    return launch_mx<128, 4, 2>(W8, X0, X1, p, split_k, stream);
+  }
+  if (M <= 32) return launch_mx<32, 5, 1>(W8, X0, X1, p, split_k, stream);
+  if (M <= 64) return launch_mx<64, 4, 1>(W8, X0, X1, p, split_k, stream);
+  return launch_mx<128, 5, 1>(W8, X0, X1, p, split_k, stream);
+}
+
+int afb_mx_effective_splits(int K, int split_k) {
+  const int k_chunks = K / 128;
+  if (split_k < 1) split_k = 1;
+  if (split_k > k_chunks) split_k = k_chunks;
+  int per = (k_chunks + split_k - 1) / split_k;
+  return (k_chunks + per - 1) / per;
+}
+
+// bf16 [T, K] (row pitch ldx) -> e4m3 terms + scale atoms ([ceil(T/128), K/128, 512] bytes each).
+int afb_quantize_mx(const void* x, long ldx, void* q0, void* q1, void* sf0, void* sf1, int T, int K,
+                    cudaStream_t stream) {
+  using namespace afb;
+  if (T <= 0) return 0;
+  if (K % 128 || (ldx & 3)) {
+    set_last_error("afb_quantize_mx: K must be a multiple of 128 (got %d)", K);
+    return -1;
+  }
+  int threads = K / 4;
+  if (threads > 1024) threads = 1024;
+  quantize_mx_kernel<<<T, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                               reinterpret_cast<uint8_t*>(q0), reinterpret_cast<uint8_t*>(q1),
+                                               reinterpret_cast<uint8_t*>(sf0), reinterpret_cast<uint8_t*>(sf1), T, K);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

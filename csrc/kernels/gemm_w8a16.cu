@@ -8,12 +8,13 @@
 //
 // The tile is "swapped": the weight rows (output features) occupy the 128 lanes of the UMMA M dimension and
 // the tokens are the UMMA N dimension (BT = 16..256), so a decode batch of 64 tokens wastes no tensor-core
-// rows and no tensor memory.  Seven warps:
+// rows and no tensor memory.  Eleven warps:
 //   warp 0      TMA producer for raw fp8 weight tiles (128 x 64 bytes) + their 2 x 128 scale bytes, RAW-deep ring
 //   warp 1      tensor-memory owner and tcgen05.mma issuer
-//   warps 2..5  dequantise raw fp8 -> bf16 into a 128-byte-swizzled UMMA operand tile (the XOR pattern TMA would
-//               have produced), publish it to the async proxy, later run the epilogue
-//   warp 6      TMA producer for the activation tiles (BT x 64 bf16, 128-byte swizzle)
+//   warps 2..9  dequantise raw fp8 -> bf16 into a 128-byte-swizzled UMMA operand tile (the XOR pattern TMA would
+//               have produced), publish it to the async proxy; warps 2..5 later run the epilogue
+//   warp 10     TMA producer for the activation tiles (BT x 64 bf16, 128-byte swizzle), its own XST-deep ring so
+//               the L2 latency of an activation tile never sits on the MMA critical path
 // Epilogue modes: bf16 out (+bias, activation, residual), fp32 split-K partials, or SwiGLU over interleaved
 // gate/up rows (row 2i = gate_i, row 2i+1 = up_i -> out[t, i] = silu(gate) * up).
 #include "../common/ptx.cuh"
@@ -32,7 +33,13 @@ struct W8Params {
   int kb_per_split;
 };
 
-template <int BT, int RAW, int ST>
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+template <int BT, int RAW, int ST, int XST>
 struct W8Smem {
   static constexpr int kRawBytes = 128 * 64;       // fp8 tile
   static constexpr int kScaleBytes = 2 * 128;      // two 32-wide K blocks x 128 rows
@@ -43,16 +50,16 @@ struct W8Smem {
   static constexpr int kRawOff = 0;
   static constexpr int kWOff = kRawOff + RAW * kRawStage;
   static constexpr int kXOff = kWOff + ST * kWBytes;
-  static constexpr int kBarOff = kXOff + ST * kXStage;
-  static constexpr int kNumBars = 2 * RAW + 3 * ST + 1;
+  static constexpr int kBarOff = kXOff + XST * kXStage;
+  static constexpr int kNumBars = 2 * RAW + 2 * ST + 2 * XST + 1;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16 + 1024;
 };
 
-template <int BT, int RAW, int ST>
-__global__ void __launch_bounds__(224, 1)
+template <int BT, int RAW, int ST, int XST>
+__global__ void __launch_bounds__(352, (BT <= 64 ? 2 : 1))
 gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_s,
                   const __grid_constant__ CUtensorMap tma_x, W8Params p) {
-  using L = W8Smem<BT, RAW, ST>;
+  using L = W8Smem<BT, RAW, ST, XST>;
   constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -60,7 +67,8 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   uint64_t* raw_full = bars;
   uint64_t* raw_empty = raw_full + RAW;
   uint64_t* x_full = raw_empty + RAW;
-  uint64_t* w_ready = x_full + ST;
+  uint64_t* x_empty = x_full + XST;
+  uint64_t* w_ready = x_empty + XST;
   uint64_t* mma_done = w_ready + ST;
   uint64_t* tmem_full = mma_done + ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
@@ -77,11 +85,14 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 128);
+      mbar_init(&raw_empty[s], 256);
+    }
+    for (int s = 0; s < XST; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], 1);
     }
     for (int s = 0; s < ST; ++s) {
-      mbar_init(&x_full[s], 1);
-      mbar_init(&w_ready[s], 128);
+      mbar_init(&w_ready[s], 256);
       mbar_init(&mma_done[s], 1);
     }
     mbar_init(tmem_full, 1);
@@ -111,12 +122,12 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         tma_load_2d(dst + L::kRawBytes, &tma_s, &raw_full[r], n0, (kb_begin + i) * 2);
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     if (lane == 0) {
       for (int i = 0; i < num_kb; ++i) {
-        const int s = i % ST;
-        const uint32_t ph = (i / ST) & 1;
-        if (!mbar_wait(&mma_done[s], ph ^ 1, kStatusEmptyWaitTimeout)) break;
+        const int s = i % XST;
+        const uint32_t ph = (i / XST) & 1;
+        if (!mbar_wait(&x_empty[s], ph ^ 1, kStatusEmptyWaitTimeout)) break;
         mbar_expect_tx(&x_full[s], L::kXBytes);
         tma_load_2d(smem + L::kXOff + s * L::kXStage, &tma_x, &x_full[s], (kb_begin + i) * 64, t0);
       }
@@ -127,19 +138,22 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       for (int i = 0; i < num_kb; ++i) {
         const int s = i % ST;
         const uint32_t ph = (i / ST) & 1;
+        const int xs = i % XST;
+        const uint32_t xph = (i / XST) & 1;
+        if (!mbar_wait(&x_full[xs], xph, kStatusTmaWaitTimeout)) break;
         if (!mbar_wait(&w_ready[s], ph, kStatusDequantWaitTimeout)) break;
-        if (!mbar_wait(&x_full[s], ph, kStatusTmaWaitTimeout)) break;
         tcgen05_fence_after();
         const uint64_t adesc = umma_desc_k_sw128(smem_u32(smem + L::kWOff + s * L::kWBytes));
-        const uint64_t bdesc = umma_desc_k_sw128(smem_u32(smem + L::kXOff + s * L::kXStage));
+        const uint64_t bdesc = umma_desc_k_sw128(smem_u32(smem + L::kXOff + xs * L::kXStage));
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i | k) != 0);
         umma_commit(&mma_done[s]);
+        umma_commit(&x_empty[xs]);
       }
       umma_commit(tmem_full);
     }
   } else {
-    // ---- dequantise: 128 threads, thread handles 16-byte chunk (tid & 3) of rows (tid >> 2) + 32*j ----
+    // ---- dequantise: 256 threads, thread handles 16-byte chunk (tid & 3) of rows (tid >> 2) + 64*j ----
     const int tid = threadIdx.x - 64;
     const int chunk = tid & 3;
     const int rbase = tid >> 2;
@@ -156,18 +170,25 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       const uint8_t* sc = raw + L::kRawBytes;
       uint8_t* wdst = smem + L::kWOff + s * L::kWBytes;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int row = rbase + 32 * j;
+      for (int j = 0; j < 2; ++j) {
+        const int row = rbase + 64 * j;
         const uint4 v = *reinterpret_cast<const uint4*>(raw + row * 64 + chunk * 16);
-        const float scale = e8m0_to_float(sc[(chunk >> 1) * 128 + row]);
+        // e4m3 -> bf16 without conversion instructions: the 7 exponent+mantissa bits dropped into bf16 bit
+        // positions 10..4 read as the same value times 2^-120 (subnormals included), so one packed bf16
+        // multiply by 2^120 * block_scale finishes the job exactly.
+        const uint32_t e8 = sc[(chunk >> 1) * 128 + row];
+        const uint32_t sb = min(e8 + 120u, 254u) << 7;
+        const uint32_t scale2 = sb | (sb << 16);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t o[8];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float2 lo = e4m3x2_to_float2(static_cast<uint16_t>(w[q] & 0xFFFF));
-          const float2 hi = e4m3x2_to_float2(static_cast<uint16_t>(w[q] >> 16));
-          o[2 * q] = pack_bf16x2(lo.x * scale, lo.y * scale);
-          o[2 * q + 1] = pack_bf16x2(hi.x * scale, hi.y * scale);
+          const uint32_t lo = __byte_perm(w[q], 0u, 0x1404);  // bytes 0,1 -> high byte of each 16-bit lane
+          const uint32_t hi = __byte_perm(w[q], 0u, 0x3424);  // bytes 2,3
+          const uint32_t blo = ((lo >> 4) & 0x07F007F0u) | (lo & 0x80008000u);
+          const uint32_t bhi = ((hi >> 4) & 0x07F007F0u) | (hi & 0x80008000u);
+          o[2 * q] = bf16x2_mul(blo, scale2);
+          o[2 * q + 1] = bf16x2_mul(bhi, scale2);
         }
         // bf16 row is 128 bytes = 8 chunks of 16 bytes; this thread produced chunks 2*chunk and 2*chunk+1.
         const int c0 = (2 * chunk) ^ (row & 7);
@@ -180,7 +201,8 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       mbar_arrive(&raw_empty[r]);
     }
 
-    // ---- epilogue: lane = output feature, registers = tokens ----
+    // ---- epilogue (first four dequant warps): lane = output feature, registers = tokens ----
+    if (warp < 6) {
     const int q = warp & 3;
     const int n = n0 + q * 32 + lane;
     const bool ok = mbar_wait(tmem_full, 0, kStatusMmaWaitTimeout);
@@ -251,27 +273,28 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         }
       }
     }
+    }  // epilogue warps
   }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int BT, int RAW, int ST>
+template <int BT, int RAW, int ST, int XST>
 int launch_w8(const void* W, const void* S, const void* X, W8Params p, int ldx, int splits, cudaStream_t stream) {
-  using L = W8Smem<BT, RAW, ST>;
+  using L = W8Smem<BT, RAW, ST, XST>;
   CUtensorMap tw, ts, tx;
   if (make_tmap_2d(&tw, W, 1, p.N, p.K, static_cast<uint64_t>(p.K), 128, 64, 0)) return -1;
   if (make_tmap_2d(&ts, S, 1, p.K / 32, p.N, static_cast<uint64_t>(p.N), 2, 128, 0)) return -1;
   if (make_tmap_2d(&tx, X, 2, p.M, p.K, static_cast<uint64_t>(ldx) * 2, BT, 64, 3)) return -1;
   static bool configured = false;
   if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_w8a16_kernel<BT, RAW, ST>,
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_w8a16_kernel<BT, RAW, ST, XST>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
   dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
-  gemm_w8a16_kernel<BT, RAW, ST><<<grid, 224, L::kTotal, stream>>>(tw, ts, tx, p);
+  gemm_w8a16_kernel<BT, RAW, ST, XST><<<grid, 352, L::kTotal, stream>>>(tw, ts, tx, p);
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -308,11 +331,12 @@ int afb_gemm_w8a16(const void* X, const void* W8, const void* S, void* out, cons
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr; p.act = act; p.mode = mode; p.kb_per_split = kb_per;
-  if (M <= 16) return launch_w8<16, 10, 3>(W8, S, X, p, ldx, split_k, stream);
-  if (M <= 32) return launch_w8<32, 10, 3>(W8, S, X, p, ldx, split_k, stream);
-  if (M <= 64) return launch_w8<64, 8, 3>(W8, S, X, p, ldx, split_k, stream);
-  if (M <= 128) return launch_w8<128, 6, 3>(W8, S, X, p, ldx, split_k, stream);
-  return launch_w8<256, 4, 3>(W8, S, X, p, ldx, split_k, stream);
+  // Small token tiles keep the footprint under half an SM's shared memory so two CTAs are co-resident.
+  if (M <= 16) return launch_w8<16, 5, 2, 6>(W8, S, X, p, ldx, split_k, stream);
+  if (M <= 32) return launch_w8<32, 5, 2, 6>(W8, S, X, p, ldx, split_k, stream);
+  if (M <= 64) return launch_w8<64, 4, 3, 3>(W8, S, X, p, ldx, split_k, stream);
+  if (M <= 128) return launch_w8<128, 4, 2, 4>(W8, S, X, p, ldx, split_k, stream);
+  return launch_w8<256, 3, 2, 4>(W8, S, X, p, ldx, split_k, stream);
 }
 
 }  // extern "C"
