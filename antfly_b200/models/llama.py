@@ -102,9 +102,9 @@ def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> i
     if tiles >= sm_count * 3 // 4:
         return 1
     num_kb = (k_in + 127) // 128
-    # Two CTAs fit on an SM; aim for about 2 x 148 of them, but keep at least 4 K-chunks per CTA and at most 8
-    # partial slices for the consumer to sum.
-    s = max(1, min(2 * sm_count // tiles, num_kb // 4, 8))
+    # Aim for about one CTA per SM, keep at least 4 K-chunks per CTA and at most 8 partial slices for the
+    # consumer to sum (every slice is read back by the kernel that follows).
+    s = max(1, min((sm_count + tiles - 1) // tiles, num_kb // 4, 8))
     return s
 
 
@@ -237,8 +237,16 @@ class LlamaModel:
     mx_max_tokens: int = 128
     act_terms: int = 2
 
-    def _linear(self, h: torch.Tensor, w: "Q.Fp8Weight", T: int, **kw) -> torch.Tensor:
-        if T <= self.mx_max_tokens and w.in_features % 128 == 0 and self.act_terms > 0:
+    def _use_mx(self, T: int) -> bool:
+        c = self.cfg
+        return (T <= self.mx_max_tokens and self.act_terms > 0 and c.hidden_size % 128 == 0
+                and (c.intermediate_size // self.tp_size) % 128 == 0 and (self.Hq * self.D) % 128 == 0)
+
+    def _linear(self, h, w: "Q.Fp8Weight", T: int, **kw) -> torch.Tensor:
+        """h is bf16 [T, K] or already-quantised MX activations."""
+        if isinstance(h, Q.MxAct):
+            return Q.gemm_mxfp8(h, w, **kw)
+        if self._use_mx(T):
             return Q.gemm_mxfp8(Q.quantize_mx(h, terms=self.act_terms), w, **kw)
         return Q.gemm_w8a16(h, w, **kw)
 
@@ -257,8 +265,9 @@ class LlamaModel:
         cfg, w = self.cfg, self.w
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = b.ids.numel()
+        mxt = self.act_terms if self._use_mx(T) else 0
         x = Dn.embed_gather(b.ids, w["embed"])
-        h = Dn.norm(x, w["l0.ln1"], eps=cfg.rms_norm_eps, rms=True)
+        h = Dn.norm(x, w["l0.ln1"], eps=cfg.rms_norm_eps, rms=True, mx_terms=mxt)
         for l in range(self.n_layers):
             p = f"l{l}."
             qkv_w: Q.Fp8Weight = w[p + "qkv"]
@@ -275,7 +284,7 @@ class LlamaModel:
             parts = self._reduce(self._linear(ctx.view(T, Hq * D), o_w, T, partials=True,
                                               split_k=pick_split_k(o_w.out_features, o_w.in_features, T)))
             x, h = Dn.norm(None, w[p + "ln2"], eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts,
-                           want_sum=True)
+                           want_sum=True, mx_terms=mxt)
             act = self._linear(h, w[p + "gu"], T, swiglu=True)
             d_w: Q.Fp8Weight = w[p + "down"]
             parts = self._reduce(self._linear(act, d_w, T, partials=True,
@@ -287,12 +296,14 @@ class LlamaModel:
                 x = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True,
                             want_norm=False)
             else:
-                x, h = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True)
+                x, h = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True,
+                               mx_terms=mxt)
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
-        hl = Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True)
+        hl = Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True,
+                     mx_terms=self.act_terms if self._use_mx(rows.shape[0]) else 0)
         head = w["lm_head"]
         if isinstance(head, Q.Fp8Weight):
-            return self._linear(hl, head, hl.shape[0])
+            return self._linear(hl, head, rows.shape[0])
         return Dn.gemm_bf16(hl, head)
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:

@@ -94,11 +94,13 @@ def norm(
     gamma_plus_one: bool = False,
     out: Optional[torch.Tensor] = None,
     sum_out: Optional[torch.Tensor] = None,
+    mx_terms: int = 0,
 ):
     """LayerNorm / RMSNorm of ``x + sum(partials) + bias + residual``.
 
     Returns ``y`` or ``(sum, y)`` when ``want_sum``.  ``partials`` is an fp32 stack [S, rows, H] as produced
-    by a split-K GEMM.
+    by a split-K GEMM.  With ``mx_terms`` 1 or 2 the normalised output is returned as MX-fp8 activations
+    (:class:`antfly_b200.ops.quant.MxAct`) for the block-scaled GEMM instead of bf16.
     """
     src = x if x is not None else partials[0]
     rows, H = src.shape[-2], src.shape[-1]
@@ -107,10 +109,22 @@ def norm(
         s_, y_ = R.norm(x, gamma, beta, eps, rms, residual, bias, partials, gamma_plus_one,
                         round_sum_bf16=want_sum)
         s_, y_ = s_.to(torch.bfloat16), y_.to(torch.bfloat16)
+        if mx_terms:
+            from . import quant as Q
+
+            y_ = Q.quantize_mx(y_, terms=mx_terms)
         if want_sum and want_norm:
             return s_, y_
         return s_ if want_sum else y_
-    if want_norm and out is None:
+    mx = None
+    if mx_terms and want_norm:
+        from . import quant as Q
+
+        tiles = (rows + 127) // 128
+        mk = lambda: torch.empty((rows, H), dtype=torch.uint8, device=dev)
+        mks = lambda: torch.full((tiles, H // 128, 512), 127, dtype=torch.uint8, device=dev)
+        mx = Q.MxAct(mk(), mks(), mk() if mx_terms == 2 else None, mks() if mx_terms == 2 else None)
+    elif want_norm and out is None:
         out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     if want_sum and sum_out is None:
         sum_out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
@@ -118,14 +132,17 @@ def norm(
     pstride = 0 if partials is None else partials.stride(0)
     rc = N.cuda().afb_norm(
         N.ptr(x), N.ptr(partials), _c_int(nparts), _c_long(pstride), N.ptr(residual), N.ptr(bias), N.ptr(gamma),
-        N.ptr(beta), N.ptr(sum_out), N.ptr(out if want_norm else None), ctypes.c_void_p(0), _c_int(rows), _c_int(H),
-        _c_float(eps), _c_int(1 if rms else 0), _c_int(1 if gamma_plus_one else 0), N.stream_ptr(),
+        N.ptr(beta), N.ptr(sum_out), N.ptr(out if (want_norm and mx is None) else None), ctypes.c_void_p(0),
+        _c_int(rows), _c_int(H), _c_float(eps), _c_int(1 if rms else 0), _c_int(1 if gamma_plus_one else 0),
+        N.ptr(mx.q0 if mx else None), N.ptr(mx.q1 if mx else None), N.ptr(mx.sf0 if mx else None),
+        N.ptr(mx.sf1 if mx else None), N.stream_ptr(),
     )
     N.check(rc, "afb_norm")
     N.count_launch()
+    y = mx if mx is not None else out
     if want_sum and want_norm:
-        return sum_out, out
-    return sum_out if want_sum else out
+        return sum_out, y
+    return sum_out if want_sum else y
 
 
 def layer_norm(x, gamma, beta, eps: float = 1e-12, residual=None):

@@ -161,9 +161,12 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------------
     def _attn_splits(self, B: int, max_kv: int) -> int:
         ctas = B * self.model.Hkv
-        if ctas >= 256 or max_kv < 1024:
+        if max_kv < 1024:
             return 1
-        return int(min(8, max(1, 296 // max(ctas, 1)), max(1, max_kv // 512)))
+        if ctas >= 256:
+            # Enough CTAs already; a 2-way split evens out the last wave (3 CTAs fit per SM).
+            return 2 if ctas < 1500 else 1
+        return int(min(8, max(1, 444 // max(ctas, 1)), max(1, max_kv // 512)))
 
     def _scratch_for(self, T: int, splits: int) -> Optional[A.PagedAttnScratch]:
         if splits <= 1:

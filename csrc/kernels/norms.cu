@@ -26,7 +26,60 @@ struct NormParams {
   float eps;
   int rms;                        // 1: RMSNorm, 0: LayerNorm
   int gamma_plus_one;             // 1: scale by (1 + gamma) (Gemma convention)
+  // Optional MX-fp8 copy of the normalised output for the block-scaled GEMM: e4m3 terms [rows, H] and their
+  // scale-factor atoms [ceil(rows/128), H/128, 512] (byte (r%32)*16 + (r/32)*4 + kblock).  q1/sf1 null: one term.
+  uint8_t* q0;
+  uint8_t* q1;
+  uint8_t* sf0;
+  uint8_t* sf1;
 };
+
+__device__ __forceinline__ uint32_t mx_e8m0_for_amax(float amax) {
+  if (!(amax > 0.0f)) return 127u - 8u;
+  int e;
+  const float m = frexpf(amax, &e);
+  int s = e - 9 + ((m > 0.875f) ? 1 : 0);  // smallest power of two with amax / 2^s <= 448
+  s = max(-127, min(127, s));
+  return static_cast<uint32_t>(s + 127);
+}
+
+__device__ __forceinline__ uint32_t mx_pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// Quantises 8 consecutive values held by this thread; the 4 threads that share a 32-element block agree on the
+// scale through two shuffles.  Must be called by all 4 threads of the group.
+__device__ __forceinline__ void mx_quantize8(const float (&v)[8], uint8_t* q, uint8_t* sf_byte, bool write_sf,
+                                             float (&resid)[8]) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  // Groups of 4 lanes are active or inactive together (H is a multiple of 32), so the partners exist.
+  const unsigned mask = __activemask();
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(mask, amax, 2));
+  const uint32_t e = mx_e8m0_for_amax(amax);
+  const float inv = __uint_as_float((254u - e) << 23);
+  const float sc = __uint_as_float(e << 23);
+  uint2 p;
+  p.x = mx_pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+  p.y = mx_pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+  *reinterpret_cast<uint2*>(q) = p;
+  if (write_sf) *sf_byte = static_cast<uint8_t>(e);
+  const uint32_t w[2] = {p.x, p.y};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float2 a = e4m3x2_to_float2(static_cast<uint16_t>(w[h] & 0xFFFF));
+    const float2 b = e4m3x2_to_float2(static_cast<uint16_t>(w[h] >> 16));
+    resid[4 * h + 0] = v[4 * h + 0] - a.x * sc;
+    resid[4 * h + 1] = v[4 * h + 1] - a.y * sc;
+    resid[4 * h + 2] = v[4 * h + 2] - b.x * sc;
+    resid[4 * h + 3] = v[4 * h + 3] - b.y * sc;
+  }
+}
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
@@ -86,7 +139,7 @@ __global__ void norm_kernel(NormParams p) {
       lsum += p.rms ? v[j] * v[j] : v[j];
     }
   }
-  if (!p.y && !p.y_f32) return;
+  if (!p.y && !p.y_f32 && !p.q0) return;
   float mean = 0.0f, rstd;
   if (p.rms) {
     const float ss = block_sum(lsum, red);
@@ -135,6 +188,18 @@ __global__ void norm_kernel(NormParams p) {
       float4* op = reinterpret_cast<float4*>(p.y_f32 + base + i);
       op[0] = make_float4(o[0], o[1], o[2], o[3]);
       op[1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    if (p.q0) {
+      // Quantise what a bf16 consumer would have seen, so both paths agree.
+      float ob[8], r1[8], r2[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ob[j] = __bfloat162float(__float2bfloat16(o[j]));
+      const int kb = i / 32;
+      const size_t sf_off = (static_cast<size_t>(row / 128) * (H / 128) + kb / 4) * 512 + ((row % 128) % 32) * 16 +
+                            ((row % 128) / 32) * 4 + (kb % 4);
+      const bool lead = (threadIdx.x & 3) == 0;
+      mx_quantize8(ob, p.q0 + base + i, p.sf0 + sf_off, lead, r1);
+      if (p.q1) mx_quantize8(r1, p.q1 + base + i, p.sf1 + sf_off, lead, r2);
     }
   }
 }
@@ -234,7 +299,8 @@ extern "C" {
 
 int afb_norm(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
              const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
-             int H, float eps, int rms, int gamma_plus_one, cudaStream_t stream) {
+             int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
+             cudaStream_t stream) {
   using namespace afb;
   if (rows <= 0) return 0;
   if (H % 8 != 0 || H > 16384) {
@@ -252,6 +318,12 @@ int afb_norm(const void* x, const float* partials, int num_partials, long partia
   p.y = reinterpret_cast<__nv_bfloat16*>(y);
   p.y_f32 = y_f32;
   p.rows = rows; p.H = H; p.eps = eps; p.rms = rms; p.gamma_plus_one = gamma_plus_one;
+  p.q0 = reinterpret_cast<uint8_t*>(q0); p.q1 = reinterpret_cast<uint8_t*>(q1);
+  p.sf0 = reinterpret_cast<uint8_t*>(sf0); p.sf1 = reinterpret_cast<uint8_t*>(sf1);
+  if (q0 && (H % 128)) {
+    set_last_error("afb_norm: MX output needs a hidden size that is a multiple of 128 (got %d)", H);
+    return -1;
+  }
   const size_t smem = static_cast<size_t>(H) * 4;
   static bool configured = false;
   if (!configured) {

@@ -54,10 +54,11 @@ __device__ __forceinline__ void store_kv(const RopeKvParams& p, void* cache, siz
   }
 }
 
-// One CTA per token; each warp takes heads round-robin (Hq query heads, Hkv key heads, Hkv value heads).
+// gridDim.x = tokens, gridDim.y = groups of heads; each warp takes one head of the group at a time (Hq query
+// heads, then Hkv key heads, then Hkv value heads).
 __global__ void rope_kv_kernel(RopeKvParams p) {
   const int t = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x >> 5) * gridDim.y;
   const int D = p.D, half = D / 2;
   const int row_width = (p.Hq + 2 * p.Hkv) * D;
   const float pos = static_cast<float>(p.positions[t]);
@@ -68,7 +69,7 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
   const int rd = p.rope_dim, rh = rd / 2;
   const int total_heads = p.Hq + 2 * p.Hkv;
-  for (int hd = warp; hd < total_heads; hd += nw) {
+  for (int hd = blockIdx.y * (blockDim.x >> 5) + warp; hd < total_heads; hd += nw) {
     const int kind = hd < p.Hq ? 0 : (hd < p.Hq + p.Hkv ? 1 : 2);
     const int col0 = hd * D;
     const int hl = kind == 0 ? hd : (kind == 1 ? hd - p.Hq : hd - p.Hq - p.Hkv);
@@ -189,7 +190,12 @@ int afb_rope_kv_write(const void* qkv, const float* partials, int num_partials, 
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rope_dim = rope_dim; p.half_split = half_split;
   p.log2_theta = log2f(theta); p.freq_scale = freq_scale; p.norm_eps = norm_eps; p.norm_plus_one = norm_plus_one;
   p.kv_fp8 = kv_fp8; p.kv_scale_inv = kv_scale > 0.0f ? 1.0f / kv_scale : 1.0f; p.num_slots = num_slots;
-  rope_kv_kernel<<<T, 256, 0, stream>>>(p);
+  const int total_heads = Hq + 2 * Hkv;
+  // Few tokens (decode): spread the heads of a token over several CTAs; many tokens: one CTA per token.
+  int groups = T >= 1024 ? 1 : (total_heads + 7) / 8;
+  if (groups < 1) groups = 1;
+  dim3 grid(T, groups);
+  rope_kv_kernel<<<grid, 256, 0, stream>>>(p);
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
