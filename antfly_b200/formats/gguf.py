@@ -1,0 +1,199 @@
+"""GGUF v3 reader: magic ``GGUF``, typed metadata key/values (13 value types), tensor directory, 32-byte aligned
+data section (zig/pkg/inference/src/gguf/format.zig:18-60).  Tensor payloads are dequantised by the C++ codecs
+(``csrc/host/codecs.cpp``) for F32 / F16 / BF16 / Q8_0 / Q4_0 / Q4_K / MXFP4; other encodings are listed in the
+directory and reported as unsupported when asked for.  A small writer exists for tests and for exporting."""
+from __future__ import annotations
+
+import ctypes
+import mmap
+import struct
+from dataclasses import dataclass
+from typing import Any, Dict, List, Tuple
+
+import numpy as np
+import torch
+
+from .. import _native as N
+
+GGUF_MAGIC = b"GGUF"
+TYPE_NAMES = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
+              11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K", 16: "IQ2_XXS", 17: "IQ2_XS", 18: "IQ3_XXS",
+              19: "IQ1_S", 20: "IQ4_NL", 21: "IQ3_S", 22: "IQ2_S", 23: "IQ4_XS", 24: "I8", 25: "I16", 26: "I32",
+              27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16", 34: "TQ1_0", 35: "TQ2_0", 39: "MXFP4"}
+SUPPORTED = {0, 1, 2, 8, 12, 30, 39}
+_SCALARS = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
+
+
+@dataclass
+class GGUFTensorInfo:
+    name: str
+    shape: Tuple[int, ...]  # row-major (outermost first)
+    type: int
+    offset: int
+
+    @property
+    def type_name(self) -> str:
+        return TYPE_NAMES.get(self.type, f"type{self.type}")
+
+
+class GGUFFile:
+    def __init__(self, path: str):
+        self._f = open(path, "rb")
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        mm = self._mm
+        if mm[:4] != GGUF_MAGIC:
+            raise ValueError(f"{path}: not a GGUF file")
+        self.version, n_tensors, n_kv = struct.unpack_from("<IQQ", mm, 4)
+        self._pos = 24
+        self.metadata: Dict[str, Any] = {}
+        for _ in range(n_kv):
+            key = self._string()
+            (vt,) = struct.unpack_from("<I", mm, self._pos)
+            self._pos += 4
+            self.metadata[key] = self._value(vt)
+        self.tensors: Dict[str, GGUFTensorInfo] = {}
+        for _ in range(n_tensors):
+            name = self._string()
+            (nd,) = struct.unpack_from("<I", mm, self._pos)
+            self._pos += 4
+            dims = struct.unpack_from(f"<{nd}Q", mm, self._pos)
+            self._pos += 8 * nd
+            ty, off = struct.unpack_from("<IQ", mm, self._pos)
+            self._pos += 12
+            self.tensors[name] = GGUFTensorInfo(name, tuple(reversed(dims)), ty, off)
+        align = int(self.metadata.get("general.alignment", 32))
+        self.data_start = (self._pos + align - 1) // align * align
+
+    def _string(self) -> str:
+        (n,) = struct.unpack_from("<Q", self._mm, self._pos)
+        s = self._mm[self._pos + 8:self._pos + 8 + n].decode("utf-8", errors="replace")
+        self._pos += 8 + n
+        return s
+
+    def _value(self, vt: int):
+        if vt in _SCALARS:
+            fmt = _SCALARS[vt]
+            (v,) = struct.unpack_from(fmt, self._mm, self._pos)
+            self._pos += struct.calcsize(fmt)
+            return v
+        if vt == 8:
+            return self._string()
+        if vt == 9:
+            et, n = struct.unpack_from("<IQ", self._mm, self._pos)
+            self._pos += 12
+            return [self._value(et) for _ in range(n)]
+        raise ValueError(f"unknown GGUF metadata value type {vt}")
+
+    def tensor(self, name: str) -> torch.Tensor:
+        """Dequantised fp32 tensor."""
+        info = self.tensors[name]
+        if info.type not in SUPPORTED:
+            raise NotImplementedError(f"GGUF tensor type {info.type_name} is not supported")
+        lib = N.host()
+        lib.afb_gguf_block_bytes.restype = ctypes.c_long
+        lib.afb_gguf_block_values.restype = ctypes.c_long
+        n = int(np.prod(info.shape)) if info.shape else 1
+        bv, bb = lib.afb_gguf_block_values(info.type), lib.afb_gguf_block_bytes(info.type)
+        nbytes = n // bv * bb
+        start = self.data_start + info.offset
+        src = np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=start)
+        out = np.empty(n, dtype=np.float32)
+        rc = lib.afb_gguf_dequantize(ctypes.c_int(info.type), src.ctypes.data_as(ctypes.c_void_p),
+                                     out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(n))
+        if rc != 0:
+            raise NotImplementedError(f"GGUF tensor type {info.type_name} is not supported")
+        return torch.from_numpy(out).view(info.shape)
+
+    def raw(self, name: str) -> np.ndarray:
+        info = self.tensors[name]
+        lib = N.host()
+        lib.afb_gguf_block_bytes.restype = ctypes.c_long
+        lib.afb_gguf_block_values.restype = ctypes.c_long
+        n = int(np.prod(info.shape))
+        nbytes = n // lib.afb_gguf_block_values(info.type) * lib.afb_gguf_block_bytes(info.type)
+        return np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=self.data_start + info.offset)
+
+
+# HF <- GGUF tensor names for llama-family checkpoints (the loader-side normalisation the reference performs).
+_GGUF_TO_HF = {
+    "token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
+    "output.weight": "lm_head.weight",
+}
+_LAYER = {"attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
+          "attn_output": "self_attn.o_proj", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj",
+          "ffn_down": "mlp.down_proj", "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm"}
+
+
+def hf_name(gguf_name: str) -> str:
+    if gguf_name in _GGUF_TO_HF:
+        return _GGUF_TO_HF[gguf_name]
+    parts = gguf_name.split(".")
+    if parts[0] == "blk" and len(parts) >= 4 and parts[2] in _LAYER:
+        return f"model.layers.{parts[1]}.{_LAYER[parts[2]]}.{parts[3]}"
+    return gguf_name
+
+
+def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
+    arch = md.get("general.architecture", "llama")
+    g = lambda k, d=None: md.get(f"{arch}.{k}", d)
+    return {"model_type": arch, "hidden_size": g("embedding_length"), "num_hidden_layers": g("block_count"),
+            "num_attention_heads": g("attention.head_count"),
+            "num_key_value_heads": g("attention.head_count_kv", g("attention.head_count")),
+            "intermediate_size": g("feed_forward_length"), "rope_theta": g("rope.freq_base", 10000.0),
+            "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
+            "vocab_size": g("vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or None)}
+
+
+def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[int, torch.Tensor]]) -> None:
+    """tensors: name -> (type id, fp32 tensor); quantises with the C++ codecs (F32, F16, Q8_0, Q4_0)."""
+    lib = N.host()
+
+    def s(x: str) -> bytes:
+        b = x.encode("utf-8")
+        return struct.pack("<Q", len(b)) + b
+
+    def val(v) -> bytes:
+        if isinstance(v, bool):
+            return struct.pack("<I?", 7, v)
+        if isinstance(v, int):
+            return struct.pack("<Iq", 11, v) if v < 0 else struct.pack("<II", 4, v) if v < 2 ** 32 else struct.pack("<IQ", 10, v)
+        if isinstance(v, float):
+            return struct.pack("<If", 6, v)
+        if isinstance(v, str):
+            return struct.pack("<I", 8) + s(v)
+        if isinstance(v, (list, tuple)):
+            if all(isinstance(e, str) for e in v):
+                return struct.pack("<IIQ", 9, 8, len(v)) + b"".join(s(e) for e in v)
+            return struct.pack("<IIQ", 9, 6, len(v)) + b"".join(struct.pack("<f", float(e)) for e in v)
+        raise TypeError(type(v))
+
+    blobs, infos, off = [], [], 0
+    for name, (ty, t) in tensors.items():
+        a = t.detach().float().cpu().contiguous().numpy().reshape(-1)
+        if ty == 0:
+            raw = a.tobytes()
+        elif ty == 1:
+            raw = a.astype(np.float16).tobytes()
+        elif ty in (8, 2):
+            bb = 34 if ty == 8 else 18
+            out = np.empty(a.size // 32 * bb, dtype=np.uint8)
+            fn = lib.afb_gguf_quantize_q8_0 if ty == 8 else lib.afb_gguf_quantize_q4_0
+            fn(a.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(a.size))
+            raw = out.tobytes()
+        else:
+            raise NotImplementedError(ty)
+        pad = (32 - len(raw) % 32) % 32
+        infos.append((name, tuple(t.shape), ty, off))
+        blobs.append(raw + b"\0" * pad)
+        off += len(raw) + pad
+    head = GGUF_MAGIC + struct.pack("<IQQ", 3, len(infos), len(metadata))
+    for k, v in metadata.items():
+        head += s(k) + val(v)
+    for name, shape, ty, o in infos:
+        dims = tuple(reversed(shape))
+        head += s(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims) + struct.pack("<IQ", ty, o)
+    head += b"\0" * ((32 - len(head) % 32) % 32)
+    with open(path, "wb") as f:
+        f.write(head)
+        for b in blobs:
+            f.write(b)

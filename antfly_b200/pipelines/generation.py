@@ -1,0 +1,99 @@
+"""Generation pipeline: chat template -> tokenize -> engine -> detokenize, with streaming deltas.
+
+Mirrors the reference's generateWithCallback (zig/pkg/inference/src/pipelines/generation.zig:1288): apply the
+model's Jinja chat template (``chat_template.jinja`` or the ``chat_template`` field of tokenizer_config.json, a
+plain role-tagged fallback otherwise), add BOS, run prefill + decode through the scheduler, emit decoded text
+deltas, and report usage and timing (``generate_timing_ms: prompt_format tokenize prefill decode total``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+from ..runtime.engine import LLMEngine
+from ..runtime.sampling_params import SamplingParams
+
+DEFAULT_TEMPLATE = (
+    "{% for m in messages %}<|{{ m['role'] }}|>\n{{ m['content'] }}\n{% endfor %}"
+    "{% if add_generation_prompt %}<|assistant|>\n{% endif %}"
+)
+
+
+@dataclass
+class GenerationOutput:
+    text: str
+    token_ids: List[int]
+    finish_reason: str
+    prompt_tokens: int
+    completion_tokens: int
+    timing_ms: Dict[str, float] = field(default_factory=dict)
+
+    def timing_line(self) -> str:
+        t = self.timing_ms
+        return ("generate_timing_ms: prompt_format=%.1f tokenize=%.1f prefill=%.1f decode=%.1f total=%.1f" %
+                (t.get("prompt_format", 0), t.get("tokenize", 0), t.get("prefill", 0), t.get("decode", 0),
+                 t.get("total", 0)))
+
+
+class ChatTemplate:
+    def __init__(self, source: Optional[str] = None):
+        import jinja2
+
+        env = jinja2.Environment(trim_blocks=True, lstrip_blocks=True)
+        env.globals["raise_exception"] = lambda m: (_ for _ in ()).throw(ValueError(m))
+        self.template = env.from_string(source or DEFAULT_TEMPLATE)
+
+    def apply(self, messages: Sequence[dict], add_generation_prompt: bool = True, **extra) -> str:
+        msgs = []
+        for m in messages:
+            c = m.get("content", "")
+            if isinstance(c, list):  # OpenAI content parts: keep the text parts
+                c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") == "text")
+            msgs.append({**m, "content": c})
+        return self.template.render(messages=msgs, add_generation_prompt=add_generation_prompt, **extra)
+
+
+class Generator:
+    def __init__(self, engine: LLMEngine, tokenizer, chat_template: Optional[str] = None, add_bos: bool = True):
+        self.engine, self.tokenizer, self.add_bos = engine, tokenizer, add_bos
+        self.template = ChatTemplate(chat_template)
+        if engine.eos is None and tokenizer.special.eos_id is not None:
+            engine.eos = tokenizer.special.eos_id
+
+    def generate(self, messages_or_prompt, params: SamplingParams, raw_prompt: bool = False,
+                 on_delta: Optional[Callable[[str], None]] = None) -> GenerationOutput:
+        t0 = time.perf_counter()
+        if isinstance(messages_or_prompt, str):
+            prompt = messages_or_prompt if raw_prompt else self.template.apply(
+                [{"role": "user", "content": messages_or_prompt}])
+        else:
+            prompt = self.template.apply(messages_or_prompt)
+        t1 = time.perf_counter()
+        ids = self.tokenizer.encode_prompt(prompt, add_bos=self.add_bos)
+        t2 = time.perf_counter()
+        emitted = {"n": 0, "text": ""}
+        collected: List[int] = []
+
+        def on_token(_rid, tok):
+            collected.append(tok)
+            if on_delta is not None:
+                full = self.tokenizer.decode(collected)
+                # Hold back while the tail is an incomplete UTF-8 sequence.
+                if not full.endswith("�"):
+                    delta = full[len(emitted["text"]):]
+                    if delta:
+                        emitted["text"] = full
+                        on_delta(delta)
+
+        p0, d0 = self.engine.timing["prefill_s"], self.engine.timing["decode_s"]
+        res = self.engine.generate([ids], params, on_token=on_token)[0]
+        t3 = time.perf_counter()
+        toks = res.token_ids
+        eos = self.engine.eos
+        text_ids = [t for t in toks if t != eos]
+        out = GenerationOutput(self.tokenizer.decode(text_ids), toks, res.finish_reason, len(ids), len(toks), {
+            "prompt_format": (t1 - t0) * 1e3, "tokenize": (t2 - t1) * 1e3,
+            "prefill": (self.engine.timing["prefill_s"] - p0) * 1e3,
+            "decode": (self.engine.timing["decode_s"] - d0) * 1e3, "total": (t3 - t0) * 1e3})
+        return out

@@ -1,0 +1,199 @@
+from __future__ import annotations
+
+import json
+import os
+import unicodedata
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+
+@dataclass
+class SpecialTokens:
+    cls_id: int = 101
+    sep_id: int = 102
+    pad_id: int = 0
+    unk_id: int = 100
+    bos_id: Optional[int] = None
+    eos_id: Optional[int] = None
+
+
+class Tokenizer:
+    """Common surface: ``encode`` (no special tokens), ``decode``, special ids, and the model-facing helpers."""
+
+    special = SpecialTokens()
+    vocab_size = 0
+
+    def encode(self, text: str) -> List[int]:
+        raise NotImplementedError
+
+    def decode(self, ids: Sequence[int]) -> str:
+        raise NotImplementedError
+
+    # zig/lib/tokenizer/src/tokenizer.zig:120-160: [CLS] tokens [SEP], truncated to max_length.
+    def encode_for_model(self, text: str, max_length: int = 512) -> List[int]:
+        ids = self.encode(text)[: max(max_length - 2, 0)]
+        return [self.special.cls_id] + ids + [self.special.sep_id]
+
+    # zig/lib/tokenizer/src/tokenizer.zig:163-215: [CLS] a [SEP] b [SEP]; budget max_length - 3; text a (the
+    # query) keeps priority and b gets what is left.  Token types: 0 through the first [SEP], then 1
+    # (zig/pkg/inference/src/pipelines/reranking.zig:335-352).
+    def encode_pair(self, a: str, b: str, max_length: int = 512) -> Tuple[List[int], List[int]]:
+        ia, ib = self.encode(a), self.encode(b)
+        budget = max(max_length - 3, 0)
+        na = min(len(ia), budget)
+        nb = min(len(ib), budget - na)
+        ids = [self.special.cls_id] + ia[:na] + [self.special.sep_id] + ib[:nb] + [self.special.sep_id]
+        types = [0] * (na + 2) + [1] * (nb + 1)
+        return ids, types
+
+    def encode_prompt(self, text: str, add_bos: bool = True) -> List[int]:
+        ids = self.encode(text)
+        if add_bos and self.special.bos_id is not None:
+            ids = [self.special.bos_id] + ids
+        return ids
+
+
+class HFTokenizer(Tokenizer):
+    """``tokenizer.json`` through the ``tokenizers`` library."""
+
+    def __init__(self, path: str, config: Optional[dict] = None):
+        from tokenizers import Tokenizer as _T
+
+        self.tk = _T.from_file(path)
+        self.vocab_size = self.tk.get_vocab_size()
+        cfg = config or {}
+
+        def tid(name, default):
+            tok = cfg.get(name)
+            if isinstance(tok, dict):
+                tok = tok.get("content")
+            if tok is not None and self.tk.token_to_id(tok) is not None:
+                return self.tk.token_to_id(tok)
+            for cand in default:
+                i = self.tk.token_to_id(cand)
+                if i is not None:
+                    return i
+            return None
+
+        self.special = SpecialTokens(
+            cls_id=tid("cls_token", ["[CLS]", "<s>"]) or 0, sep_id=tid("sep_token", ["[SEP]", "</s>"]) or 0,
+            pad_id=tid("pad_token", ["[PAD]", "<pad>"]) or 0, unk_id=tid("unk_token", ["[UNK]", "<unk>"]) or 0,
+            bos_id=tid("bos_token", ["<|begin_of_text|>", "<s>", "<bos>"]),
+            eos_id=tid("eos_token", ["<|end_of_text|>", "<|eot_id|>", "</s>", "<eos>"]))
+
+    def encode(self, text: str) -> List[int]:
+        return self.tk.encode(text, add_special_tokens=False).ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return self.tk.decode(list(ids), skip_special_tokens=True)
+
+
+class WordPieceTokenizer(Tokenizer):
+    """BERT WordPiece (basic tokenisation: lower-case, strip accents, split punctuation; greedy longest-match with
+    the ``##`` continuation prefix).  Used when only ``vocab.txt`` exists or the ``tokenizers`` wheel is missing."""
+
+    def __init__(self, vocab: Dict[str, int], lower: bool = True, max_chars: int = 100):
+        self.vocab, self.lower, self.max_chars = vocab, lower, max_chars
+        self.inv = {i: t for t, i in vocab.items()}
+        self.vocab_size = len(vocab)
+        g = lambda t, d: vocab.get(t, d)
+        self.special = SpecialTokens(g("[CLS]", 101), g("[SEP]", 102), g("[PAD]", 0), g("[UNK]", 100))
+
+    @classmethod
+    def from_vocab_file(cls, path: str, lower: bool = True) -> "WordPieceTokenizer":
+        with open(path, encoding="utf-8") as f:
+            return cls({line.rstrip("\n"): i for i, line in enumerate(f)}, lower)
+
+    @staticmethod
+    def _is_punct(ch: str) -> bool:
+        cp = ord(ch)
+        if 33 <= cp <= 47 or 58 <= cp <= 64 or 91 <= cp <= 96 or 123 <= cp <= 126:
+            return True
+        return unicodedata.category(ch).startswith("P")
+
+    def _basic(self, text: str) -> List[str]:
+        if self.lower:
+            text = unicodedata.normalize("NFD", text.lower())
+            text = "".join(c for c in text if unicodedata.category(c) != "Mn")
+        out, cur = [], []
+        for ch in text:
+            if ch.isspace():
+                if cur:
+                    out.append("".join(cur)); cur = []
+            elif self._is_punct(ch):
+                if cur:
+                    out.append("".join(cur)); cur = []
+                out.append(ch)
+            else:
+                cur.append(ch)
+        if cur:
+            out.append("".join(cur))
+        return out
+
+    def encode(self, text: str) -> List[int]:
+        ids: List[int] = []
+        for word in self._basic(text):
+            if len(word) > self.max_chars:
+                ids.append(self.special.unk_id)
+                continue
+            start, sub = 0, []
+            while start < len(word):
+                end, cur = len(word), None
+                while start < end:
+                    piece = word[start:end] if start == 0 else "##" + word[start:end]
+                    if piece in self.vocab:
+                        cur = self.vocab[piece]
+                        break
+                    end -= 1
+                if cur is None:
+                    sub = [self.special.unk_id]
+                    break
+                sub.append(cur)
+                start = end
+            ids.extend(sub)
+        return ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        toks = [self.inv.get(int(i), "[UNK]") for i in ids]
+        out = ""
+        for t in toks:
+            if t in ("[CLS]", "[SEP]", "[PAD]"):
+                continue
+            out += t[2:] if t.startswith("##") else (" " + t if out else t)
+        return out
+
+
+class ByteTokenizer(Tokenizer):
+    """UTF-8 bytes + offset: a dependency-free tokenizer for random-init models, smoke tests and benchmarks."""
+
+    def __init__(self, vocab_size: int = 512, offset: int = 3, bos_id: int = 1, eos_id: int = 2):
+        self.vocab_size, self.offset = vocab_size, offset
+        self.special = SpecialTokens(cls_id=bos_id, sep_id=eos_id, pad_id=0, unk_id=0, bos_id=bos_id, eos_id=eos_id)
+
+    def encode(self, text: str) -> List[int]:
+        return [min(b + self.offset, self.vocab_size - 1) for b in text.encode("utf-8")]
+
+    def decode(self, ids: Sequence[int]) -> str:
+        bs = bytes(max(0, min(255, int(i) - self.offset)) for i in ids if int(i) >= self.offset)
+        return bs.decode("utf-8", errors="replace")
+
+
+def load_tokenizer(model_dir: str, vocab_size: int = 0) -> Tokenizer:
+    """tokenizer.json -> HFTokenizer; vocab.txt -> WordPiece; otherwise the byte tokenizer
+    (selection order of zig/pkg/inference/src/server/model_manager.zig:383-520)."""
+    cfg = {}
+    for name in ("tokenizer_config.json", "special_tokens_map.json"):
+        p = os.path.join(model_dir, name)
+        if os.path.exists(p):
+            with open(p, encoding="utf-8") as f:
+                cfg.update(json.load(f))
+    tj = os.path.join(model_dir, "tokenizer.json")
+    if os.path.exists(tj):
+        try:
+            return HFTokenizer(tj, cfg)
+        except ImportError:
+            pass
+    vt = os.path.join(model_dir, "vocab.txt")
+    if os.path.exists(vt):
+        return WordPieceTokenizer.from_vocab_file(vt, lower=cfg.get("do_lower_case", True))
+    return ByteTokenizer(vocab_size or 512)
