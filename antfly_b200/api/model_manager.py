@@ -1,0 +1,145 @@
+"""Model manager: resolves model names to directories, loads and caches models with their tokenizer and
+pipelines (the reference's ModelManager.loadFromDir / LoadedModel, zig/pkg/inference/src/server/
+model_manager.zig:641-1100), bounded by ``max_loaded_models`` with least-recently-used eviction.  Models can also be
+registered in memory (random-init models for tests and benchmarks)."""
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Dict, Optional
+
+import torch
+
+from ..formats import manifest as MF
+from ..formats import safetensors_io as ST
+from ..models.bert import BertConfig, BertModel
+from ..models.llama import LlamaConfig, LlamaModel
+from ..pipelines.embedding import Embedder
+from ..pipelines.generation import Generator
+from ..pipelines.reranking import CrossEncoderReranker
+from ..runtime.engine import LLMEngine
+from ..tokenizer import ByteTokenizer, load_tokenizer
+
+
+class ModelNotFound(KeyError):
+    pass
+
+
+@dataclass
+class LoadedModel:
+    name: str
+    task: str  # embedder | reranker | generator
+    pipeline: object
+    tokenizer: object
+    path: Optional[str] = None
+    loaded_at: float = field(default_factory=time.time)
+    info: Dict = field(default_factory=dict)
+
+
+class ModelManager:
+    def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
+                 kv_blocks: int = 4096, max_batch: int = 64):
+        self.models_dir = models_dir or MF.default_models_dir()
+        self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.max_loaded = max_loaded_models
+        self.kv_blocks, self.max_batch = kv_blocks, max_batch
+        self._models: "OrderedDict[str, LoadedModel]" = OrderedDict()
+        self._lock = threading.Lock()
+
+    # -- registration of in-memory models ------------------------------------------------------------------
+    def register(self, name: str, task: str, pipeline, tokenizer, info: Optional[dict] = None) -> LoadedModel:
+        lm = LoadedModel(name, task, pipeline, tokenizer, info=info or {})
+        with self._lock:
+            self._models[f"{task}:{name}"] = lm
+        return lm
+
+    def register_random(self, name: str, task: str, size: str = "tiny", seed: int = 0) -> LoadedModel:
+        """Random-init model of a named size, with the byte tokenizer (no artifacts needed)."""
+        dev = self.device
+        if task in ("embedder", "reranker"):
+            cfgs = {"tiny": BertConfig(hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                       intermediate_size=256, vocab_size=512),
+                    "base": BertConfig.base()}
+            cfg = cfgs[size]
+            if task == "reranker":
+                cfg.num_labels = 1
+            model = BertModel.random_init(cfg, device=dev, seed=seed)
+            tok = ByteTokenizer(cfg.vocab_size)
+            pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
+            return self.register(name, task, pipe, tok, {"hidden_size": cfg.hidden_size, "random_init": True})
+        cfgs = {"tiny": LlamaConfig.tiny(), "8b": LlamaConfig.llama3_8b(), "70b": LlamaConfig.llama3_70b()}
+        cfg = cfgs[size]
+        model = LlamaModel.random_init(cfg, device=dev, seed=seed, fast_init=(size != "tiny"))
+        tok = ByteTokenizer(cfg.vocab_size)
+        eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
+                        use_cuda_graph=dev.type == "cuda", eos_token_id=tok.special.eos_id)
+        return self.register(name, "generator", Generator(eng, tok), tok, {"random_init": True})
+
+    # -- directory-backed models ---------------------------------------------------------------------------
+    def _load_dir(self, name: str, task: str, path: str) -> LoadedModel:
+        mf = MF.read_manifest(path)
+        tok = load_tokenizer(path, mf.config.get("vocab_size", 0))
+        if mf.weights == "gguf":
+            from ..formats import gguf as GG
+
+            f = GG.GGUFFile(os.path.join(path, mf.weight_files[0]))
+            sd = {GG.hf_name(n): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
+            cfg_d = {k: v for k, v in GG.llama_config_from_gguf(f.metadata).items() if v is not None}
+        elif mf.weights == "safetensors":
+            sd, cfg_d = ST.load_model_dir(path), mf.config
+        else:
+            raise ModelNotFound(f"{name}: no loadable weights (found {mf.weights})")
+        if task in ("embedder", "reranker"):
+            cfg = BertConfig.from_hf(cfg_d)
+            model = BertModel.from_state_dict(cfg, sd, device=self.device)
+            pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
+        else:
+            cfg = LlamaConfig.from_hf(cfg_d)
+            model = LlamaModel.from_state_dict(cfg, sd, device=self.device)
+            eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
+                            use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id)
+            pipe = Generator(eng, tok, mf.chat_template)
+        return LoadedModel(name, task, pipe, tok, path, info={"weights": mf.weights, "capabilities": mf.capabilities})
+
+    def get(self, name: str, task: str) -> LoadedModel:
+        key = f"{task}:{name}"
+        with self._lock:
+            if key in self._models:
+                self._models.move_to_end(key)
+                return self._models[key]
+        path = MF.resolve_model_path(name, self.models_dir, task + "s")
+        if path is None:
+            raise ModelNotFound(f"model {name!r} not found under {self.models_dir} ({task}s/)")
+        lm = self._load_dir(name, task, path)
+        with self._lock:
+            self._models[key] = lm
+            while len(self._models) > self.max_loaded:
+                self._models.popitem(last=False)
+        return lm
+
+    def list_models(self) -> Dict[str, Dict[str, dict]]:
+        out: Dict[str, Dict[str, dict]] = {t: {} for t in MF.TASK_DIRS}
+        out["extractors"] = {}
+        with self._lock:
+            for lm in self._models.values():
+                out[lm.task + "s"][lm.name] = {"name": lm.name, "loaded": True, **lm.info}
+        if os.path.isdir(self.models_dir):
+            for t in MF.TASK_DIRS:
+                root = os.path.join(self.models_dir, t)
+                if not os.path.isdir(root):
+                    continue
+                for dirpath, dirs, files in os.walk(root):
+                    if "config.json" in files or any(f.endswith((".safetensors", ".gguf")) for f in files):
+                        nm = os.path.relpath(dirpath, root)
+                        out[t].setdefault(nm, {"name": nm, "loaded": False})
+                        dirs[:] = []
+        out["chunkers"].setdefault("fixed", {"name": "fixed", "loaded": True})
+        return out
+
+    def loaded_count(self) -> int:
+        with self._lock:
+            return len(self._models)

@@ -1,0 +1,160 @@
+"""Request / response models of the inference API (specs/openapi/inference/api.yaml: EmbedRequest :740,
+EmbedResponse :800, RerankRequest :999, RerankResponse :1054, GenerateRequest :2299, GenerateResponse :2472,
+GenerateChunk, ModelsResponse :2099, Error :722) and the vector-search subset of the DB QueryRequest
+(specs/openapi/antfly/metadata.yaml:4077-4420)."""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Literal, Optional, Union
+
+from pydantic import BaseModel, ConfigDict, Field
+
+
+class ContentPart(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    type: str
+    text: Optional[str] = None
+
+
+class EmbedRequest(BaseModel):
+    model: str
+    input: Union[str, List[str], List[ContentPart]]
+    encoding_format: Literal["float"] = "float"
+    dimensions: Optional[int] = Field(default=None, gt=0)
+    task_type: Optional[str] = None
+    input_type: Optional[str] = None
+
+
+class SparseVector(BaseModel):
+    indices: List[int]
+    values: List[float]
+
+
+class EmbeddingObject(BaseModel):
+    object: Literal["embedding"] = "embedding"
+    embedding: Union[List[float], SparseVector]
+    index: int
+
+
+class EmbeddingUsage(BaseModel):
+    prompt_tokens: int
+    total_tokens: int
+
+
+class EmbedResponse(BaseModel):
+    object: Literal["list"] = "list"
+    data: List[EmbeddingObject]
+    model: str
+    usage: EmbeddingUsage
+
+
+class RerankRequest(BaseModel):
+    model: str
+    query: str
+    prompts: List[str]
+
+
+class RerankObject(BaseModel):
+    object: Literal["rerank.score"] = "rerank.score"
+    index: int
+    score: float
+
+
+class GenerateUsage(BaseModel):
+    prompt_tokens: int
+    completion_tokens: int
+    total_tokens: int
+
+
+class RerankResponse(BaseModel):
+    object: Literal["list"] = "list"
+    data: List[RerankObject]
+    model: str
+    usage: GenerateUsage
+
+
+class ChatMessage(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    role: str
+    content: Union[str, List[ContentPart], None] = None
+
+
+class GenerateRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    messages: List[ChatMessage]
+    max_tokens: int = 256
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    stop: Union[str, List[str], None] = None
+    seed: Optional[int] = None
+    stream: bool = False
+    draft_model: Optional[str] = None
+    speculative_k: Optional[int] = Field(default=None, ge=1, le=16)
+    cache_dtype: Optional[Literal["f16", "f32", "int8", "fp8", "int4", "bf16"]] = None
+    cache_compaction_ratio: Optional[float] = None
+    backend: Optional[str] = None
+    mode: Optional[str] = None
+    grammar: Optional[str] = None
+    response_format: Optional[Dict[str, Any]] = None
+
+
+class GenerateMessage(BaseModel):
+    role: str = "assistant"
+    content: Optional[str] = None
+
+
+class GenerateChoice(BaseModel):
+    index: int = 0
+    message: GenerateMessage
+    finish_reason: str
+
+
+class GenerateResponse(BaseModel):
+    id: str
+    object: Literal["chat.completion"] = "chat.completion"
+    created: int
+    model: str
+    choices: List[GenerateChoice]
+    usage: GenerateUsage
+
+
+class ChunkRequest(BaseModel):
+    text: str
+    model: str = "fixed"
+    target_tokens: int = 500
+    overlap_tokens: int = 50
+    max_chunks: int = 0
+
+
+class ErrorBody(BaseModel):
+    error: str
+    message: str
+
+
+class SearchRequest(BaseModel):
+    """Vector-search subset of QueryRequest: one dense query per index name, or packed base64 little-endian f32."""
+    model_config = ConfigDict(extra="allow")
+    index: str
+    embeddings: Union[List[List[float]], List[float], str, None] = None
+    semantic_search: Optional[str] = None
+    embedder: Optional[str] = None
+    limit: int = Field(default=10, gt=0)
+    search_effort: float = 0.5
+    distance_under: Optional[float] = None
+    distance_over: Optional[float] = None
+
+
+class SearchHit(BaseModel):
+    id: int
+    distance: float
+
+
+class SearchResponse(BaseModel):
+    hits: List[List[SearchHit]]
+    took_ms: float
+    index: str

@@ -1,0 +1,321 @@
+"""FastAPI application exposing the reference's inference API.
+
+Routes (specs/openapi/inference/api.yaml:57-688, zig/pkg/inference/src/server/server.zig:4651-4700):
+``POST /ai/v1/embed`` = ``/ai/v1/embeddings``, ``POST /ai/v1/rerank``, ``POST /ai/v1/generate`` =
+``/ai/v1/chat/completions`` (SSE when ``stream``; terminator ``data: [DONE]``), ``POST /ai/v1/chunk``,
+``GET /ai/v1/models``, ``GET /ai/v1/metrics`` and ``/metrics``, ``GET /healthz``, ``GET /readyz``, plus
+``POST /ai/v1/search`` for the vector indexes.  Errors are ``{"error", "message"}`` with 400 / 404 / 500 / 503;
+a bounded, weighted request queue answers 503 when full (server/request_queue.zig:22-40).
+"""
+from __future__ import annotations
+
+import asyncio
+import base64
+import json
+import struct
+import threading
+import time
+import uuid
+from typing import Dict, List, Optional
+
+import torch
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, Response, StreamingResponse
+
+from .. import _native as N
+from ..index.codec import decode_vectors
+from ..pipelines.chunking import chunk_text
+from ..pipelines.embedding import INPUT_TYPE_ALIASES
+from ..runtime.sampling_params import SamplingParams
+from ..runtime.scheduler import QueueFull
+from . import schemas as S
+from .metrics import Metrics
+from .model_manager import ModelManager, ModelNotFound
+
+
+class RequestQueue:
+    """Weighted admission: ``max_units`` of work in flight, ``max_waiting`` callers queued behind it."""
+
+    def __init__(self, max_units: int = 64, max_waiting: int = 256):
+        self.max_units, self.max_waiting = max_units, max_waiting
+        self.units, self.waiting = 0, 0
+        self._cv = threading.Condition()
+
+    def acquire(self, units: int = 1, timeout: float = 300.0) -> None:
+        units = min(units, self.max_units)
+        with self._cv:
+            if self.units + units > self.max_units and self.waiting >= self.max_waiting:
+                raise QueueFull("request queue is full")
+            self.waiting += 1
+            try:
+                ok = self._cv.wait_for(lambda: self.units + units <= self.max_units, timeout)
+                if not ok:
+                    raise QueueFull("timed out waiting for a slot")
+                self.units += units
+            finally:
+                self.waiting -= 1
+
+    def release(self, units: int = 1) -> None:
+        with self._cv:
+            self.units -= min(units, self.max_units)
+            self._cv.notify_all()
+
+
+def _err(status: int, code: str, message: str) -> JSONResponse:
+    return JSONResponse(status_code=status, content={"error": code, "message": message})
+
+
+def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
+               max_concurrent_requests: int = 64, max_queue_size: int = 256) -> FastAPI:
+    app = FastAPI(title="antfly-b200 inference", version="0.1")
+    mgr = manager or ModelManager()
+    metrics = Metrics()
+    queue = RequestQueue(max_concurrent_requests, max_queue_size)
+    gpu_lock = threading.Lock()  # one request drives the device at a time; batching happens inside pipelines
+    app.state.manager, app.state.metrics, app.state.queue = mgr, metrics, queue
+    app.state.indexes = indexes if indexes is not None else {}
+
+    def run_guarded(endpoint: str, units: int, fn):
+        t0 = time.perf_counter()
+        try:
+            queue.acquire(units)
+        except QueueFull as e:
+            metrics.queue_rejected.inc()
+            metrics.requests.labels(endpoint, "503").inc()
+            return _err(503, "queue_full", str(e))
+        metrics.queue_depth.set(queue.waiting)
+        try:
+            with gpu_lock:
+                out = fn()
+            metrics.requests.labels(endpoint, "200").inc()
+            return out
+        except ModelNotFound as e:
+            metrics.requests.labels(endpoint, "404").inc()
+            return _err(404, "model_not_found", str(e.args[0]) if e.args else str(e))
+        except (ValueError, AssertionError) as e:
+            metrics.requests.labels(endpoint, "400").inc()
+            return _err(400, "invalid_request", str(e))
+        except Exception as e:  # pragma: no cover - defensive
+            metrics.requests.labels(endpoint, "500").inc()
+            return _err(500, "internal_error", f"{type(e).__name__}: {e}")
+        finally:
+            queue.release(units)
+            metrics.latency.labels(endpoint).observe(time.perf_counter() - t0)
+            metrics.loaded_models.set(mgr.loaded_count())
+            metrics.kernel_launches.set(N.launches())
+
+    async def parse(request: Request, model):
+        try:
+            return model.model_validate(await request.json()), None
+        except Exception as e:
+            return None, _err(400, "invalid_request", str(e))
+
+    # ---- embeddings -----------------------------------------------------------------------------------
+    async def embed(request: Request):
+        req, bad = await parse(request, S.EmbedRequest)
+        if bad:
+            return bad
+        if isinstance(req.input, str):
+            texts = [req.input]
+        else:
+            texts = [p if isinstance(p, str) else (p.text or "") for p in req.input]
+            if any(not isinstance(p, str) and p.type != "text" for p in req.input):
+                return _err(400, "invalid_request", "only text content parts are supported by this build")
+        if not texts:
+            return _err(400, "invalid_request", "input must not be empty")
+        task_type = req.task_type or INPUT_TYPE_ALIASES.get(req.input_type or "")
+
+        def work():
+            lm = mgr.get(req.model, "embedder")
+            emb, ntok = lm.pipeline.embed(texts, task_type, req.dimensions)
+            metrics.tokens.labels("embed", "prompt").inc(ntok)
+            data = [S.EmbeddingObject(embedding=row.tolist(), index=i) for i, row in enumerate(emb)]
+            return S.EmbedResponse(data=data, model=req.model,
+                                   usage=S.EmbeddingUsage(prompt_tokens=ntok, total_tokens=ntok)).model_dump()
+
+        return await asyncio.to_thread(run_guarded, "embed", len(texts), work)
+
+    # ---- rerank ---------------------------------------------------------------------------------------
+    async def rerank(request: Request):
+        req, bad = await parse(request, S.RerankRequest)
+        if bad:
+            return bad
+        if not req.prompts:
+            return _err(400, "invalid_request", "prompts must not be empty")
+
+        def work():
+            lm = mgr.get(req.model, "reranker")
+            scores, ntok = lm.pipeline.rerank(req.query, req.prompts)
+            metrics.tokens.labels("rerank", "prompt").inc(ntok)
+            return S.RerankResponse(
+                data=[S.RerankObject(index=i, score=float(s)) for i, s in enumerate(scores)], model=req.model,
+                usage=S.GenerateUsage(prompt_tokens=ntok, completion_tokens=0, total_tokens=ntok)).model_dump()
+
+        return await asyncio.to_thread(run_guarded, "rerank", len(req.prompts), work)
+
+    # ---- generate / chat completions --------------------------------------------------------------------
+    def sampling_from(req: S.GenerateRequest, tok) -> SamplingParams:
+        stops: List[int] = []
+        if req.stop:
+            for s in ([req.stop] if isinstance(req.stop, str) else req.stop):
+                ids = tok.encode(s)
+                if len(ids) == 1:
+                    stops.append(ids[0])
+        return SamplingParams(max_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k, top_p=req.top_p,
+                              min_p=req.min_p, repetition_penalty=req.repetition_penalty,
+                              frequency_penalty=req.frequency_penalty, presence_penalty=req.presence_penalty,
+                              stop_token_ids=stops, seed=req.seed)
+
+    async def generate(request: Request):
+        req, bad = await parse(request, S.GenerateRequest)
+        if bad:
+            return bad
+        if not req.messages:
+            return _err(400, "invalid_request", "messages must not be empty")
+        if req.max_tokens <= 0:
+            return _err(400, "invalid_request", "max_tokens must be positive")
+        msgs = [m.model_dump() for m in req.messages]
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+        if not req.stream:
+            def work():
+                lm = mgr.get(req.model, "generator")
+                out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer))
+                metrics.tokens.labels("generate", "prompt").inc(out.prompt_tokens)
+                metrics.tokens.labels("generate", "completion").inc(out.completion_tokens)
+                return S.GenerateResponse(
+                    id=rid, created=created, model=req.model,
+                    choices=[S.GenerateChoice(message=S.GenerateMessage(content=out.text),
+                                              finish_reason=out.finish_reason)],
+                    usage=S.GenerateUsage(prompt_tokens=out.prompt_tokens, completion_tokens=out.completion_tokens,
+                                          total_tokens=out.prompt_tokens + out.completion_tokens)).model_dump()
+
+            return await asyncio.to_thread(run_guarded, "generate", 1, work)
+
+        # Streaming: the generation runs in a worker thread and feeds an asyncio queue.
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+
+        def chunk(delta: dict, finish: Optional[str] = None) -> str:
+            body = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": req.model,
+                    "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+            return "data: " + json.dumps(body) + "\n\n"
+
+        def worker():
+            def work():
+                lm = mgr.get(req.model, "generator")
+                loop.call_soon_threadsafe(q.put_nowait, chunk({"role": "assistant"}))
+                out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer),
+                                           on_delta=lambda d: loop.call_soon_threadsafe(q.put_nowait,
+                                                                                        chunk({"content": d})))
+                loop.call_soon_threadsafe(q.put_nowait, chunk({}, out.finish_reason))
+                return None
+
+            res = run_guarded("generate", 1, work)
+            if isinstance(res, JSONResponse):
+                loop.call_soon_threadsafe(q.put_nowait, "data: " + res.body.decode() + "\n\n")
+            loop.call_soon_threadsafe(q.put_nowait, None)
+
+        threading.Thread(target=worker, daemon=True).start()
+
+        async def gen():
+            while True:
+                item = await q.get()
+                if item is None:
+                    break
+                yield item
+            yield "data: [DONE]\n\n"
+
+        return StreamingResponse(gen(), media_type="text/event-stream")
+
+    # ---- chunk ----------------------------------------------------------------------------------------
+    async def chunk_ep(request: Request):
+        req, bad = await parse(request, S.ChunkRequest)
+        if bad:
+            return bad
+        chunks = chunk_text(req.text, req.target_tokens, req.overlap_tokens, req.max_chunks)
+        metrics.requests.labels("chunk", "200").inc()
+        return {"chunks": chunks, "model": req.model}
+
+    # ---- vector search --------------------------------------------------------------------------------
+    async def search(request: Request):
+        req, bad = await parse(request, S.SearchRequest)
+        if bad:
+            return bad
+        idx = app.state.indexes.get(req.index)
+        if idx is None:
+            return _err(404, "index_not_found", f"index {req.index!r} is not loaded")
+
+        def work():
+            t0 = time.perf_counter()
+            if req.embeddings is not None:
+                qv = decode_vectors(req.embeddings)
+            elif req.semantic_search is not None:
+                if not req.embedder:
+                    raise ValueError("semantic_search needs an embedder model name")
+                qv, _ = mgr.get(req.embedder, "embedder").pipeline.embed([req.semantic_search])
+            else:
+                raise ValueError("one of embeddings / semantic_search is required")
+            res = idx.search(qv.to(idx.device), req.limit, effort=req.search_effort) if hasattr(idx, "search_effort") \
+                else idx.search(qv.to(idx.device), req.limit)
+            d, ids = res.distances.cpu(), res.ids.cpu()
+            hits = []
+            for qi in range(d.shape[0]):
+                row = []
+                for dist, i in zip(d[qi].tolist(), ids[qi].tolist()):
+                    if i < 0 or (req.distance_under is not None and dist >= req.distance_under) or \
+                            (req.distance_over is not None and dist <= req.distance_over):
+                        continue
+                    row.append(S.SearchHit(id=int(i), distance=float(dist)))
+                hits.append(row)
+            return S.SearchResponse(hits=hits, took_ms=(time.perf_counter() - t0) * 1e3, index=req.index).model_dump()
+
+        return await asyncio.to_thread(run_guarded, "search", 1, work)
+
+    # ---- models / health / metrics ------------------------------------------------------------------------
+    async def models():
+        per_task = mgr.list_models()
+        data = [{"id": n, "object": "model", "owned_by": "antfly-b200", "task": t[:-1]}
+                for t in ("generators", "embedders", "rerankers") for n in per_task.get(t, {})]
+        body = {"object": "list", "data": data, "allow_downloads": False,
+                "backends": {"default": "b200", "available": ["b200" if torch.cuda.is_available() else "cpu-oracle"]}}
+        body.update(per_task)
+        return body
+
+    async def metrics_ep():
+        for name, sched_owner in list(mgr._models.items()):
+            eng = getattr(getattr(sched_owner.pipeline, "engine", None), "sched", None)
+            if eng is not None:
+                for k, v in eng.stats().items():
+                    metrics.sched.labels(k).set(v)
+                e = sched_owner.pipeline.engine
+                metrics.kv_free_blocks.labels(sched_owner.name).set(e.cache.alloc.free_blocks)
+                for k in ("rounds", "drafted", "matched", "rejected", "accepted", "corrections", "bonus"):
+                    metrics.spec.labels(k).set(getattr(e.spec, k))
+        return Response(metrics.render(), media_type="text/plain; version=0.0.4")
+
+    async def healthz():
+        return {"status": "ok"}
+
+    async def readyz():
+        return {"status": "ready", "device": str(mgr.device), "loaded_models": mgr.loaded_count()}
+
+    for path in ("/ai/v1/embed", "/ai/v1/embeddings"):
+        app.add_api_route(path, embed, methods=["POST"])
+    app.add_api_route("/ai/v1/rerank", rerank, methods=["POST"])
+    for path in ("/ai/v1/generate", "/ai/v1/chat/completions"):
+        app.add_api_route(path, generate, methods=["POST"])
+    app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
+    app.add_api_route("/ai/v1/search", search, methods=["POST"])
+    app.add_api_route("/ai/v1/models", models, methods=["GET"])
+    app.add_api_route("/ai/v1/metrics", metrics_ep, methods=["GET"])
+    app.add_api_route("/metrics", metrics_ep, methods=["GET"])
+    app.add_api_route("/healthz", healthz, methods=["GET"])
+    app.add_api_route("/readyz", readyz, methods=["GET"])
+    return app
+
+
+def serve(host: str = "127.0.0.1", port: int = 11433, **kw) -> None:
+    import uvicorn
+
+    uvicorn.run(create_app(**kw), host=host, port=port, timeout_keep_alive=300)

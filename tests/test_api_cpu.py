@@ -1,0 +1,105 @@
+"""HTTP contract on the CPU path, modelled on the reference's product-level pytest suites
+(zig/e2e/inference/test_embed.py:37-85, test_rerank.py:27-50, test_generate.py, test_openai_compat.py)."""
+import json
+import math
+
+import pytest
+from fastapi.testclient import TestClient
+
+from antfly_b200.api.model_manager import ModelManager
+from antfly_b200.api.server import RequestQueue, create_app
+from antfly_b200.runtime.scheduler import QueueFull
+
+
+@pytest.fixture(scope="module")
+def client():
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu", kv_blocks=128, max_batch=4)
+    mgr.register_random("tiny-embed", "embedder")
+    mgr.register_random("tiny-rerank", "reranker")
+    mgr.register_random("tiny-gen", "generator")
+    return TestClient(create_app(mgr))
+
+
+def test_health_ready_models(client):
+    assert client.get("/healthz").json()["status"] == "ok"
+    assert client.get("/readyz").status_code == 200
+    m = client.get("/ai/v1/models").json()
+    assert m["object"] == "list" and "tiny-embed" in m["embedders"] and "tiny-gen" in m["generators"]
+    assert "fixed" in m["chunkers"] and {"rerankers", "backends", "allow_downloads"} <= set(m)
+
+
+@pytest.mark.parametrize("path", ["/ai/v1/embed", "/ai/v1/embeddings"])
+def test_embed_shape_norm_and_dimensions(client, path):
+    r = client.post(path, json={"model": "tiny-embed", "input": ["hello world", "second text"]})
+    assert r.status_code == 200
+    body = r.json()
+    assert body["object"] == "list" and body["model"] == "tiny-embed" and len(body["data"]) == 2
+    for i, d in enumerate(body["data"]):
+        assert d["object"] == "embedding" and d["index"] == i and len(d["embedding"]) == 128
+        assert abs(math.sqrt(sum(x * x for x in d["embedding"])) - 1.0) < 1e-2
+    assert body["usage"]["prompt_tokens"] == body["usage"]["total_tokens"] > 0
+    r = client.post(path, json={"model": "tiny-embed", "input": "one", "dimensions": 16})
+    assert len(r.json()["data"][0]["embedding"]) == 16
+    assert client.post(path, json={"model": "tiny-embed", "input": "x", "dimensions": 4096}).status_code == 400
+
+
+def test_embed_errors(client):
+    assert client.post("/ai/v1/embed", json={"model": "missing", "input": "x"}).status_code == 404
+    r = client.post("/ai/v1/embed", json={"input": "x"})
+    assert r.status_code == 400 and set(r.json()) == {"error", "message"}
+    assert client.post("/ai/v1/embed", json={"model": "tiny-embed", "input": "x", "encoding_format": "base64"}).status_code == 400
+
+
+def test_rerank_contract(client):
+    r = client.post("/ai/v1/rerank", json={"model": "tiny-rerank", "query": "q", "prompts": ["doc a", "doc b", "c"]})
+    assert r.status_code == 200
+    body = r.json()
+    assert body["object"] == "list" and [d["index"] for d in body["data"]] == [0, 1, 2]
+    assert all(d["object"] == "rerank.score" and 0.0 <= d["score"] <= 1.0 for d in body["data"])
+    assert body["usage"]["completion_tokens"] == 0
+    assert client.post("/ai/v1/rerank", json={"model": "tiny-rerank", "query": "q", "prompts": []}).status_code == 400
+
+
+@pytest.mark.parametrize("path", ["/ai/v1/generate", "/ai/v1/chat/completions"])
+def test_generate_contract(client, path):
+    r = client.post(path, json={"model": "tiny-gen", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 5,
+                                "temperature": 0})
+    assert r.status_code == 200
+    b = r.json()
+    assert b["object"] == "chat.completion" and b["choices"][0]["message"]["role"] == "assistant"
+    assert b["choices"][0]["finish_reason"] in ("length", "stop")
+    u = b["usage"]
+    assert u["completion_tokens"] <= 5 and u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"]
+    r2 = client.post(path, json={"model": "tiny-gen", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 5,
+                                 "temperature": 0})
+    assert r2.json()["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+
+
+def test_generate_streaming_sse(client):
+    with client.stream("POST", "/ai/v1/chat/completions",
+                       json={"model": "tiny-gen", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                             "temperature": 0, "stream": True}) as r:
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        lines = [l for l in r.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    assert all(c["object"] == "chat.completion.chunk" for c in chunks)
+    assert chunks[0]["choices"][0]["delta"].get("role") == "assistant"
+    assert chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop")
+
+
+def test_chunk_and_metrics(client):
+    r = client.post("/ai/v1/chunk", json={"text": "a b c d e f g h i j", "target_tokens": 4, "overlap_tokens": 1})
+    ch = r.json()["chunks"]
+    assert ch[0]["text"] == "a b c d" and ch[1]["text"].startswith("d e") and ch[-1]["text"].endswith("j")
+    text = client.get("/ai/v1/metrics").text
+    assert "antfly_inference_requests_total" in text and 'endpoint="embed"' in text
+
+
+def test_request_queue_backpressure():
+    q = RequestQueue(max_units=1, max_waiting=0)
+    q.acquire(1)
+    with pytest.raises(QueueFull):
+        q.acquire(1, timeout=0.05)
+    q.release(1)
+    q.acquire(1)
