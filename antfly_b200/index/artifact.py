@@ -1,0 +1,155 @@
+"""Index artifacts on disk.
+
+(1) HBC records in the reference's key/value layout (zig/lib/vectorindex/src/hbc.zig:20-198,
+store.zig:23-28): four ordered namespaces ``nodes, meta, quant, vecs``; metadata key ``hbc:meta`` holding a 50-byte
+little-endian record {version u32 = 1, dims u32, branching_factor u32, leaf_size u32, root_node u64,
+active_count u64, node_count u64, use_quantization u8, quantizer_seed u64, metric u8}; node keys
+``n:<u64 BE id>:<suffix>`` with the packed node value ``HBN1`` + header {is_leaf u8, level u16, parent u64} +
+centroid_len u32 + ids_len u32 + centroid f32s + ids u64s; ``v:<id>`` raw f32 vector; ``l:<id>`` vector -> leaf.
+The namespaces are persisted here as one sorted key/value file each (the reference stores them in LMDB / LSM).
+(2) GPU index shards (flat / IVF) as safetensors bundles: centroids, posting offsets, sorted vectors, ids.
+"""
+from __future__ import annotations
+
+import json
+import os
+import struct
+from typing import Dict, Tuple
+
+import torch
+
+from ..formats import safetensors_io as ST
+from .hbc import HBCConfig, HBCIndex, Node
+
+META_KEY = b"hbc:meta"
+_METRICS = {"l2_squared": 0, "inner_product": 1, "cosine": 2}
+_METRIC_NAMES = {v: k for k, v in _METRICS.items()}
+_META = struct.Struct("<IIIIQQQBQB")
+assert _META.size == 50
+
+
+def pack_metadata(cfg: HBCConfig, root: int, active: int, nodes: int) -> bytes:
+    return _META.pack(1, cfg.dims, cfg.branching_factor, cfg.leaf_size, root, active, nodes,
+                      1 if cfg.use_quantization else 0, cfg.quantizer_seed, _METRICS[cfg.metric])
+
+
+def unpack_metadata(b: bytes) -> dict:
+    v, dims, bf, ls, root, active, nodes, uq, seed, metric = _META.unpack(b)
+    if v != 1:
+        raise ValueError(f"unsupported HBC metadata version {v}")
+    return {"dims": dims, "branching_factor": bf, "leaf_size": ls, "root_node": root, "active_count": active,
+            "node_count": nodes, "use_quantization": bool(uq), "quantizer_seed": seed, "metric": _METRIC_NAMES[metric]}
+
+
+def node_key(node_id: int, suffix: str) -> bytes:
+    return b"n:" + struct.pack(">Q", node_id) + b":" + suffix.encode()
+
+
+def pack_node(nd: Node) -> bytes:
+    c = nd.centroid.detach().float().cpu()
+    ids = [int(i) for i in nd.children]
+    return (b"HBN1" + struct.pack("<BHQ", 1 if nd.is_leaf else 0, nd.level, nd.parent) +
+            struct.pack("<II", c.numel(), len(ids)) + c.numpy().astype("<f4").tobytes() +
+            struct.pack(f"<{len(ids)}Q", *ids))
+
+
+def unpack_node(node_id: int, b: bytes) -> Node:
+    if b[:4] != b"HBN1":
+        raise ValueError("bad packed node magic")
+    is_leaf, level, parent = struct.unpack_from("<BHQ", b, 4)
+    cl, il = struct.unpack_from("<II", b, 15)
+    off = 23
+    cent = torch.frombuffer(bytearray(b[off:off + 4 * cl]), dtype=torch.float32).clone()
+    off += 4 * cl
+    ids = list(struct.unpack_from(f"<{il}Q", b, off))
+    return Node(node_id, bool(is_leaf), level, parent, cent, ids)
+
+
+def _write_ns(path: str, kv: Dict[bytes, bytes]) -> None:
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(kv)))
+        for k in sorted(kv):
+            f.write(struct.pack("<II", len(k), len(kv[k])) + k + kv[k])
+
+
+def _read_ns(path: str) -> Dict[bytes, bytes]:
+    out = {}
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        for _ in range(n):
+            kl, vl = struct.unpack("<II", f.read(8))
+            k = f.read(kl)
+            out[k] = f.read(vl)
+    return out
+
+
+def save_hbc(index: HBCIndex, directory: str) -> None:
+    os.makedirs(directory, exist_ok=True)
+    nodes = {node_key(nd.id, "p"): pack_node(nd) for nd in index.nodes.values()}
+    meta = {META_KEY: pack_metadata(index.cfg, index.root, int(index.vectors.shape[0]), len(index.nodes))}
+    vecs: Dict[bytes, bytes] = {}
+    x = index.vectors.detach().float().cpu()
+    for i in range(x.shape[0]):
+        vid = int(index.ids[i])
+        vecs[b"v:" + struct.pack(">Q", vid)] = x[i].numpy().astype("<f4").tobytes()
+        vecs[b"l:" + struct.pack(">Q", vid)] = struct.pack("<Q", index.leaf_of.get(i, 0))
+    _write_ns(os.path.join(directory, "nodes.kv"), nodes)
+    _write_ns(os.path.join(directory, "meta.kv"), meta)
+    _write_ns(os.path.join(directory, "vecs.kv"), vecs)
+    _write_ns(os.path.join(directory, "quant.kv"), {})  # quantised payloads are rebuilt from vectors on load
+
+
+def load_hbc(directory: str) -> HBCIndex:
+    md = unpack_metadata(_read_ns(os.path.join(directory, "meta.kv"))[META_KEY])
+    cfg = HBCConfig(md["dims"], md["metric"], md["branching_factor"], md["leaf_size"],
+                    use_quantization=md["use_quantization"], quantizer_seed=md["quantizer_seed"])
+    idx = HBCIndex(cfg)
+    for k, v in _read_ns(os.path.join(directory, "nodes.kv")).items():
+        nid = struct.unpack(">Q", k[2:10])[0]
+        idx.nodes[nid] = unpack_node(nid, v)
+    idx.root = md["root_node"]
+    vecs = _read_ns(os.path.join(directory, "vecs.kv"))
+    vids = sorted(struct.unpack(">Q", k[2:])[0] for k in vecs if k.startswith(b"v:"))
+    rows = [torch.frombuffer(bytearray(vecs[b"v:" + struct.pack(">Q", v)]), dtype=torch.float32) for v in vids]
+    idx.vectors = torch.stack(rows) if rows else torch.zeros(0, cfg.dims)
+    idx.ids = torch.tensor(vids)
+    pos = {v: i for i, v in enumerate(vids)}
+    for nd in idx.nodes.values():
+        if nd.is_leaf:
+            # leaf members are stored as positions at build time; ids == positions for bulk builds without ids
+            for m in nd.children:
+                idx.leaf_of[m] = nd.id
+    if cfg.use_quantization:
+        for nd in idx.nodes.values():
+            pts = idx.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+                [idx.nodes[c].centroid for c in nd.children])
+            nd.quant = idx.quantizer.quantize(nd.centroid, pts)
+    return idx
+
+
+def save_ivf(index, path: str) -> None:
+    ST.save_file({"centroids": index.centroids, "offsets": index.offsets, "order": index.order, "vectors": index.x},
+                 path, {"metric": index.metric, "n_lists": index.n_lists, "kind": "ivf", "id_offset": index.id_offset})
+
+
+def load_ivf(path: str, device="cuda"):
+    from .distance import score_form
+    from .flat import FlatIndex
+    from .ivf import IVFIndex
+    from ..ops import index_ops as IX
+
+    f = ST.SafetensorsFile(path)
+    md = f.metadata
+    idx = IVFIndex.__new__(IVFIndex)
+    idx.metric, idx.form = md["metric"], score_form(md["metric"])
+    idx.id_offset = int(md.get("id_offset", 0))
+    idx.centroids = f.tensor("centroids").to(device)
+    idx.offsets = f.tensor("offsets").to(device)
+    idx.order = f.tensor("order").to(device)
+    idx.x = f.tensor("vectors").to(device)
+    idx.n_lists, idx.n, idx.dim = int(md["n_lists"]), idx.x.shape[0], idx.x.shape[1]
+    idx.col_norm = IX.row_sqnorm(idx.x) if idx.form.use_col_norm else None
+    idx.centroid_index = FlatIndex(idx.centroids, metric=idx.metric)
+    idx.list_sizes = idx.offsets[1:] - idx.offsets[:-1]
+    idx.kmeans_iterations = 0
+    return idx

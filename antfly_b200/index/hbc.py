@@ -1,0 +1,182 @@
+"""HBC: hierarchical balanced clustering tree with RaBitQ-quantised nodes and exact re-ranking.
+
+A compact restatement of the reference's main vector index (zig/lib/vectorindex/src/hbc_index.zig, hbc.zig,
+search.zig; defaults zig/lib/vectorindex/src/types.zig:44-77): leaves hold up to ``leaf_size`` vectors, internal
+nodes up to ``branching_factor`` children, the tree is bulk-built bottom-up with k-means (K ~ N / leaf_size per
+level, parents clustered by branching factor), every node's members are RaBitQ-quantised once against the node
+centroid, search is a best-first beam over a priority queue of (estimated distance - error bound) that stops after
+``search_width`` leaves, skips subtrees whose lower bound exceeds ``d_min * (1 + epsilon)`` once the result set is
+full (not for inner-product), and re-ranks ``k * ceil(1 + epsilon)`` candidates with exact distances.  On-disk
+layout (four key namespaces, 50-byte metadata record, ``HBN1`` packed nodes) is implemented in
+:mod:`antfly_b200.index.artifact`.
+"""
+from __future__ import annotations
+
+import heapq
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import reference as R
+from .kmeans import kmeans
+from .rabitq import RaBitQSet, RaBitQuantizer
+
+
+@dataclass
+class HBCConfig:
+    dims: int
+    metric: str = "l2_squared"
+    branching_factor: int = 16
+    leaf_size: int = 100
+    search_width: int = 32
+    epsilon: float = 0.1
+    kmeans_max_iter: int = 16
+    use_quantization: bool = True
+    quantizer_seed: int = 42
+
+
+@dataclass
+class Node:
+    id: int
+    is_leaf: bool
+    level: int
+    parent: int
+    centroid: torch.Tensor
+    children: List[int] = field(default_factory=list)  # child node ids (internal) or vector ids (leaf)
+    quant: Optional[RaBitQSet] = None
+
+
+class HBCIndex:
+    def __init__(self, cfg: HBCConfig):
+        self.cfg = cfg
+        self.nodes: Dict[int, Node] = {}
+        self.root = 0
+        self.vectors: Optional[torch.Tensor] = None  # [N, D] fp32 (exact re-rank store)
+        self.ids: Optional[torch.Tensor] = None
+        self.quantizer = RaBitQuantizer(cfg.dims, cfg.metric, cfg.quantizer_seed)
+        self.leaf_of: Dict[int, int] = {}
+
+    # -- build --------------------------------------------------------------------------------------------
+    @classmethod
+    def bulk_build(cls, vectors: torch.Tensor, cfg: HBCConfig, ids: Optional[torch.Tensor] = None) -> "HBCIndex":
+        self = cls(cfg)
+        x = vectors.float()
+        if cfg.metric == "cosine":
+            x = torch.nn.functional.normalize(x, dim=-1)
+        self.vectors = x
+        n = x.shape[0]
+        self.ids = ids if ids is not None else torch.arange(n)
+        next_id = [1]
+
+        def new_node(is_leaf, level, centroid, children) -> Node:
+            nd = Node(next_id[0], is_leaf, level, 0, centroid, children)
+            next_id[0] += 1
+            self.nodes[nd.id] = nd
+            return nd
+
+        # level 0: leaves
+        k = max(1, math.ceil(n / cfg.leaf_size))
+        members: List[torch.Tensor]
+        if k == 1:
+            cents = x.mean(0, keepdim=True)
+            members = [torch.arange(n)]
+        else:
+            km = kmeans(x.to(torch.bfloat16), k, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
+            cents = km.centroids.float().cpu() if not x.is_cuda else km.centroids.float()
+            a = km.assignments.long()
+            members = [torch.nonzero(a == c).flatten() for c in range(k)]
+        level_nodes: List[Node] = []
+        for c, mem in enumerate(members):
+            if mem.numel() == 0:
+                continue
+            nd = new_node(True, 0, cents[c].to(x.device), mem.tolist())
+            for v in nd.children:
+                self.leaf_of[v] = nd.id
+            level_nodes.append(nd)
+        level = 0
+        while len(level_nodes) > 1:
+            level += 1
+            cm = torch.stack([nd.centroid for nd in level_nodes])
+            kk = max(1, math.ceil(len(level_nodes) / cfg.branching_factor))
+            if kk == 1:
+                groups = [list(range(len(level_nodes)))]
+                pc = cm.mean(0, keepdim=True)
+            else:
+                km = kmeans(cm.to(torch.bfloat16), kk, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
+                a = km.assignments.long()
+                groups = [torch.nonzero(a == c).flatten().tolist() for c in range(kk)]
+                pc = km.centroids.float()
+            parents = []
+            for c, grp in enumerate(groups):
+                if not grp:
+                    continue
+                p = new_node(False, level, pc[c].to(x.device), [level_nodes[i].id for i in grp])
+                for i in grp:
+                    level_nodes[i].parent = p.id
+                parents.append(p)
+            level_nodes = parents
+        self.root = level_nodes[0].id
+        if cfg.use_quantization:
+            for nd in self.nodes.values():
+                pts = x[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+                    [self.nodes[c].centroid for c in nd.children])
+                nd.quant = self.quantizer.quantize(nd.centroid, pts)
+        return self
+
+    # -- search -------------------------------------------------------------------------------------------
+    def _score(self, nd: Node, q: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        if nd.quant is not None:
+            return self.quantizer.estimate(nd.quant, q)
+        pts = self.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+            [self.nodes[c].centroid for c in nd.children])
+        d = R.distances(q[None], pts, self.cfg.metric)[0]
+        return d, torch.zeros_like(d)
+
+    def search(self, query: torch.Tensor, k: int, search_width: Optional[int] = None,
+               epsilon: Optional[float] = None) -> Tuple[List[int], List[float]]:
+        cfg = self.cfg
+        width = search_width or cfg.search_width
+        eps = cfg.epsilon if epsilon is None else epsilon
+        q = query.float().to(self.vectors.device)
+        if cfg.metric == "cosine":
+            q = torch.nn.functional.normalize(q, dim=-1)
+        rerank_n = k * math.ceil(1 + eps)
+        cap = min(max(4 * width, 2 * cfg.branching_factor, 1), 1024) * max(cfg.leaf_size, 1)
+        pq: List[Tuple[float, int, int]] = [(0.0, 0, self.root)]
+        cands: List[Tuple[float, int]] = []
+        leaves, counter = 0, 1
+        dmin = float("inf")
+        while pq and leaves < width:
+            bound, _, nid = heapq.heappop(pq)
+            nd = self.nodes[nid]
+            if cfg.metric != "inner_product" and len(cands) >= rerank_n and bound > dmin * (1 + eps):
+                continue
+            d, e = self._score(nd, q)
+            d, e = d.tolist(), e.tolist()
+            if nd.is_leaf:
+                leaves += 1
+                for vid, dist in zip(nd.children, d):
+                    cands.append((dist, vid))
+                if len(cands) > cap:
+                    cands = heapq.nsmallest(cap, cands)
+                if len(cands) >= rerank_n:
+                    dmin = heapq.nsmallest(rerank_n, cands)[-1][0]
+            else:
+                for cid, dist, err in zip(nd.children, d, e):
+                    heapq.heappush(pq, (dist - err, counter, cid))
+                    counter += 1
+        # Exact re-rank of the best estimated candidates, up to the reference's candidate capacity.
+        capacity = min(max(4 * width, 2 * cfg.branching_factor, 1), 1024)
+        short = [vid for _, vid in heapq.nsmallest(max(rerank_n, k, capacity), cands)]
+        if not short:
+            return [], []
+        exact = R.distances(q[None], self.vectors[torch.tensor(short)], cfg.metric)[0]
+        order = torch.argsort(exact)[:k]
+        return [int(self.ids[short[i]]) for i in order.tolist()], exact[order].tolist()
+
+    def stats(self) -> dict:
+        leaves = sum(1 for n in self.nodes.values() if n.is_leaf)
+        return {"nodes": len(self.nodes), "leaves": leaves, "levels": self.nodes[self.root].level + 1,
+                "vectors": 0 if self.vectors is None else int(self.vectors.shape[0])}

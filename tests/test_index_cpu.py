@@ -1,0 +1,117 @@
+"""Index logic on the CPU: fusion / pruner, search-effort mapping, wire codecs, RaBitQ, HBC tree and artifacts."""
+import math
+
+import pytest
+import torch
+
+from antfly_b200.index import artifact, codec, fusion
+from antfly_b200.index.distance import resolve_search_effort
+from antfly_b200.index.flat import FlatIndex, exact_search_fp32, recall_at_k
+from antfly_b200.index.hbc import HBCConfig, HBCIndex
+from antfly_b200.index.rabitq import RaBitQuantizer, bit_product
+
+
+def test_rrf_rsf_failover_and_pruner():
+    res = {"dense": [("a", 0.9), ("b", 0.8), ("c", 0.1)], "text": [("b", 12.0), ("d", 3.0)]}
+    rrf = fusion.fuse(res, fusion.MergeConfig("rrf"))
+    assert [h.doc_id for h in rrf] == ["b", "a", "d", "c"]
+    assert rrf[0].score == pytest.approx(1 / 62 + 1 / 61) and rrf[0].index_count == 2
+    w = fusion.fuse(res, fusion.MergeConfig("rrf", weights={"text": 0.0}))
+    assert [h.doc_id for h in w][:3] == ["a", "b", "c"]
+    rsf = fusion.fuse(res, fusion.MergeConfig("rsf"))
+    assert rsf[0].doc_id == "b" and rsf[0].score == pytest.approx((0.8 - 0.1) / 0.8 + 1.0)
+    assert fusion.fuse({"x": [], "y": [("q", 1.0)]}, fusion.MergeConfig("failover"))[0].doc_id == "q"
+    pr = fusion.prune(rrf, fusion.Pruner(require_multi_index=True))
+    assert [h.doc_id for h in pr] == ["b"]
+    pr = fusion.prune(rrf, fusion.Pruner(min_score_ratio=0.6))
+    assert [h.doc_id for h in pr] == ["b"]
+    hits = [fusion.FusedHit(i, s) for i, s in enumerate([1.0, 0.95, 0.9, 0.3, 0.25])]
+    assert len(fusion.prune(hits, fusion.Pruner(max_score_gap_percent=50.0))) == 3
+    assert len(fusion.prune(hits, fusion.Pruner(min_absolute_score=0.28))) == 4
+    assert len(fusion.prune(hits, fusion.Pruner(std_dev_threshold=0.5))) == 3
+
+
+def test_search_effort_mapping():
+    w0, e0 = resolve_search_effort(10, 0.0)
+    wh, eh = resolve_search_effort(10, 0.5)
+    w1, e1 = resolve_search_effort(10, 1.0)
+    assert w0 == 64 and e0 == 1.0
+    assert wh == round(64 + 0.5 * (4096 - 64)) and eh == 7.0
+    assert w1 == 4096 and e1 == 100.0
+    assert resolve_search_effort(500, 0.0)[0] == 500
+
+
+def test_vector_wire_codecs():
+    v = torch.randn(3, 8)
+    assert torch.equal(codec.decode_packed(codec.encode_packed(v), 8), v)
+    assert codec.decode_vectors([1.0, 2.0]).shape == (1, 2) and codec.decode_vectors([[1, 2], [3, 4]]).shape == (2, 2)
+    sp = codec.encode_sparse_packed([7, 2], [0.5, 1.5])
+    assert codec.decode_sparse(sp) == {"indices": [2, 7], "values": [1.5, 0.5]}
+    with pytest.raises(ValueError):
+        codec.decode_packed("AAAA", 3)
+
+
+@pytest.mark.parametrize("metric", ["l2_squared", "inner_product", "cosine"])
+def test_rabitq_estimates_track_exact_distances(metric):
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(0)
+    D, n = 256, 400
+    c = torch.randn(D, generator=g) * 0.1
+    x = c + torch.randn(n, D, generator=g)
+    q = c + torch.randn(D, generator=g)
+    rq = RaBitQuantizer(D, metric)
+    qs = rq.quantize(c, x)
+    assert qs.codes.shape == (n, 4) and int(qs.code_counts[0]) == int((x[0] - c >= 0).sum())
+    d, e = rq.estimate(qs, q)
+    exact = R.distances(q[None], x, metric)[0]
+    # within a few error bounds for almost every vector, and the ranking is strongly correlated
+    within = ((d - exact).abs() <= 4 * e + 1e-3).float().mean()
+    assert float(within) > 0.9
+    rk = torch.corrcoef(torch.stack([d, exact]))[0, 1]
+    assert float(rk) > 0.7
+    # the weighted popcount agrees with a per-bit restatement
+    planes = rq._query_planes(qs, q)[0]
+    bp = bit_product(qs.codes[:5], planes)
+    for i in range(5):
+        bits = lambda w: [(int(w[j]) >> (63 - b)) & 1 for j in range(4) for b in range(64)]
+        cb = bits(qs.codes[i])
+        ref = sum((1 << p) * sum(a & b for a, b in zip(cb, bits(planes[p]))) for p in range(4))
+        assert int(bp[i]) == ref
+
+
+def test_hbc_build_search_recall_and_artifact_roundtrip(tmp_path):
+    g = torch.Generator().manual_seed(1)
+    centers = torch.randn(20, 32, generator=g)
+    x = centers[torch.randint(0, 20, (3000,), generator=g)] + 0.3 * torch.randn(3000, 32, generator=g)
+    q = centers[torch.randint(0, 20, (40,), generator=g)] + 0.3 * torch.randn(40, 32, generator=g)
+    cfg = HBCConfig(32, "l2_squared", branching_factor=8, leaf_size=60, search_width=16)
+    idx = HBCIndex.bulk_build(x, cfg)
+    st = idx.stats()
+    assert st["vectors"] == 3000 and st["leaves"] >= 3000 // 60 * 0.5 and st["levels"] >= 2
+    truth = exact_search_fp32(q, x, 10, "l2_squared")
+    found = torch.tensor([idx.search(q[i], 10)[0] + [-1] * 10 for i in range(40)])[:, :10]
+    r = recall_at_k(found, truth.ids, 10)
+    assert r > 0.8, r
+    wide = torch.tensor([idx.search(q[i], 10, search_width=64)[0] for i in range(40)])
+    assert recall_at_k(wide, truth.ids, 10) >= r
+    artifact.save_hbc(idx, str(tmp_path / "hbc"))
+    md = artifact.unpack_metadata(artifact.pack_metadata(cfg, idx.root, 3000, len(idx.nodes)))
+    assert md["dims"] == 32 and md["leaf_size"] == 60 and md["metric"] == "l2_squared" and md["root_node"] == idx.root
+    back = artifact.load_hbc(str(tmp_path / "hbc"))
+    assert back.stats() == st
+    assert back.search(q[0], 10)[0] == idx.search(q[0], 10)[0]
+    nd = idx.nodes[idx.root]
+    rt = artifact.unpack_node(nd.id, artifact.pack_node(nd))
+    assert rt.children == nd.children and rt.level == nd.level and torch.equal(rt.centroid, nd.centroid.cpu())
+
+
+def test_flat_index_cpu_path_is_exact():
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(5000, 32, generator=g)
+    q = torch.randn(16, 32, generator=g)
+    idx = FlatIndex(x.to(torch.bfloat16).float(), metric="l2_squared")
+    idx.seed_cols, idx.cand_cap = 256, 512
+    res = idx.search(q.to(torch.bfloat16).float(), 10)
+    truth = exact_search_fp32(q.to(torch.bfloat16).float(), x.to(torch.bfloat16).float(), 10, "l2_squared")
+    assert recall_at_k(res.ids, truth.ids, 10) == 1.0
