@@ -17,6 +17,11 @@
 // by cp.async (zero-filled past the end of the sequence) in a two-deep ring.
 #include "../common/ptx.cuh"
 #include "../common/tmap.cuh"
+#include "../include/antfly_b200_noalloc.h"
+
+// Scratch of the allocation-free entry point (see antfly_b200_noalloc.h): split-KV partial outputs followed by
+// their log-sum-exps.  In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_afb_noalloc_scratch[AFB_NOALLOC_SCRATCH_BYTES];
 
 namespace afb {
 
@@ -452,6 +457,54 @@ int afb_attention(const void* q, long q_stride, const void* k, const void* v, lo
     AFB_CHECK_CUDA(cudaGetLastError());
   }
   return 0;
+}
+
+}  // extern "C"
+
+extern "C" {
+
+// Allocation-free variant of the split-KV paged decode attention; contract in antfly_b200_noalloc.h.
+int afb_paged_decode_attention_noalloc(const void* q, long q_stride, const void* k_cache, const void* v_cache,
+                                       const int* block_tables, int max_blocks, int page, const int* q_starts,
+                                       const int* q_lens, const int* kv_lens, void* out, long out_stride, int B,
+                                       int T, int Hq, int Hkv, int D, int max_q_len, int window, float scale,
+                                       int num_splits, cudaStream_t stream) {
+  using namespace afb;
+  if (B <= 0 || T <= 0) return 0;
+  if (num_splits < 1) num_splits = 1;
+  if (Hkv <= 0 || Hq % Hkv != 0 || max_q_len * (Hq / Hkv) > 16) {
+    set_last_error("afb_paged_decode_attention_noalloc: needs q_len * (Hq / Hkv) <= 16 (decode shapes only)");
+    return -1;
+  }
+  const size_t rows = static_cast<size_t>(num_splits) * T * Hq;
+  const size_t o_bytes = (rows * D * sizeof(float) + 255) / 256 * 256;
+  const size_t need = o_bytes + rows * sizeof(float);
+  if (need > AFB_NOALLOC_SCRATCH_BYTES) {
+    set_last_error(
+        "afb_paged_decode_attention_noalloc: num_splits * T * Hq = %zu rows of D = %d need %zu bytes of scratch; "
+        "the built-in array holds %d",
+        rows, D, need, AFB_NOALLOC_SCRATCH_BYTES);
+    return -1;
+  }
+  // One-time, per-device lookup of the array's device address (the symbol itself is not a device pointer).
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  AFB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_last_error("afb_paged_decode_attention_noalloc: device ordinal %d out of range", dev);
+    return -1;
+  }
+  if (!scratch_of_device[dev]) {
+    void* ptr = nullptr;
+    AFB_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_afb_noalloc_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  unsigned char* base = static_cast<unsigned char*>(scratch_of_device[dev]);
+  float* part_o = reinterpret_cast<float*>(base);
+  float* part_lse = reinterpret_cast<float*>(base + o_bytes);
+  return afb_attention(q, q_stride, nullptr, nullptr, 0, k_cache, v_cache, block_tables, max_blocks, page, q_starts,
+                       q_lens, kv_lens, out, out_stride, part_o, part_lse, B, T, Hq, Hkv, D, max_q_len, 1, window,
+                       scale, 1, 1, num_splits, stream);
 }
 
 }  // extern "C"
