@@ -1,0 +1,152 @@
+"""Multi-rank host logic on CPU (gloo, world size 2): sharding rules, the baseline TP communicator, a
+tensor-parallel decoder that reproduces the single-rank logits, rank-failure detection by timeout."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from antfly_b200.parallel import sharding
+
+
+def _free_port() -> int:
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _hf_llama_state(cfg, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    H, F, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    r = lambda n, k: (torch.randn(n, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    sd = {"model.embed_tokens.weight": (torch.randn(cfg.vocab_size, H, generator=g) * 0.02).to(torch.bfloat16),
+          "model.norm.weight": torch.ones(H, dtype=torch.bfloat16), "lm_head.weight": r(cfg.vocab_size, H)}
+    for l in range(cfg.num_hidden_layers):
+        p = f"model.layers.{l}."
+        sd[p + "input_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(H, dtype=torch.bfloat16)
+        sd[p + "self_attn.q_proj.weight"] = r(cfg.num_attention_heads * D, H)
+        sd[p + "self_attn.k_proj.weight"] = r(cfg.num_key_value_heads * D, H)
+        sd[p + "self_attn.v_proj.weight"] = r(cfg.num_key_value_heads * D, H)
+        sd[p + "self_attn.o_proj.weight"] = r(H, cfg.num_attention_heads * D)
+        sd[p + "mlp.gate_proj.weight"] = r(F, H)
+        sd[p + "mlp.up_proj.weight"] = r(F, H)
+        sd[p + "mlp.down_proj.weight"] = r(H, F)
+    return sd
+
+
+def _forward_logits(model, cfg, device="cpu"):
+    from antfly_b200.models.llama import StepBatch
+
+    lens = [9, 4]
+    T = sum(lens)
+    ids = (torch.arange(T, dtype=torch.int32) * 7 + 3) % cfg.vocab_size
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+    ql = torch.tensor(lens, dtype=torch.int32)
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    tables = torch.tensor([[0, 0], [1, 0]], dtype=torch.int32)
+    slots = torch.tensor(list(range(9)) + list(range(16, 20)), dtype=torch.int32)
+    b = StepBatch(ids, pos, slots, qs, ql, ql.clone(), tables, (qs + ql - 1).int(), max(lens), 1)
+    kc = torch.zeros((cfg.num_hidden_layers, 2, 16, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    return model.forward(b, kc, torch.zeros_like(kc)).float()
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.parallel.comm import DistributedConfig, TpComm, init_process_group
+
+    cfg_d = init_process_group(backend="gloo", timeout_s=60)
+    assert cfg_d.mode == "tensor_parallel" and cfg_d.world_size == world
+    comm = TpComm(rank, world, torch.device("cpu"))
+    t = torch.full((3,), float(rank + 1))
+    comm.all_reduce(t)
+    assert t.tolist() == [3.0, 3.0, 3.0]
+    # vocabulary-sharded arg-max merge: rank 1 holds the winner of row 0, a tie in row 1 resolves to the lower index
+    idx = torch.tensor([5 + 100 * rank, 7 + 100 * rank], dtype=torch.int32)
+    val = torch.tensor([1.0 + rank, 2.0])
+    assert comm.argmax_merge(idx, val).tolist() == [105, 7]
+    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    sd = _hf_llama_state(cfg)
+    model = LlamaModel.from_state_dict(cfg, sd, device="cpu", tp_rank=rank, tp_size=world, comm=comm)
+    logits = _forward_logits(model, cfg)                    # [2, V / world]
+    full = comm.all_gather(logits).permute(1, 0, 2).reshape(2, -1)
+    tok = model.greedy_tokens(logits.to(torch.bfloat16))
+    if rank == 0:
+        q.put((full, tok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_decoder_matches_single_rank():
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    full, tok = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    single = LlamaModel.from_state_dict(cfg, _hf_llama_state(cfg), device="cpu")
+    ref = _forward_logits(single, cfg)
+    torch.testing.assert_close(full, ref, atol=6e-2, rtol=5e-2)
+    assert tok.tolist() == ref.argmax(-1).tolist()
+
+
+def test_sharding_rules():
+    assert sharding.shard_dim("model.layers.0.self_attn.q_proj.weight") == 0
+    assert sharding.shard_dim("model.layers.0.mlp.down_proj.weight") == 1
+    assert sharding.shard_dim("encoder.layer.0.attention.output.dense.weight") == 1
+    assert sharding.shard_dim("encoder.layer.0.intermediate.dense.bias") == 0
+    assert sharding.shard_dim("model.norm.weight") == -1
+    w = torch.arange(64 * 128).view(64, 128).float()
+    assert torch.equal(torch.cat([sharding.shard_rows(w, r, 4) for r in range(4)], 0), w)
+    assert torch.equal(torch.cat([sharding.shard_cols(w, r, 4) for r in range(4)], 1), w)
+    with pytest.raises(AssertionError):
+        sharding.shard_cols(w, 0, 8)  # 16 columns per rank is not a whole 32-element quantisation block
+
+
+def _silent_peer_worker(rank, world, port, q):
+    """Rank 1 never joins the collective; rank 0 must get an error after the short timeout, not hang."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from antfly_b200.parallel.comm import init_process_group
+    from antfly_b200.parallel.health import HeartbeatMonitor
+
+    init_process_group(backend="gloo", timeout_s=5)
+    store = dist.distributed_c10d._get_default_store()
+    mon = HeartbeatMonitor(store, rank, world, interval_s=0.2, dead_after_s=1.5)
+    mon.beat()
+    if rank == 1:
+        # leaves between steps, with nothing in flight
+        q.put(("left", rank))
+        return
+    import time
+
+    time.sleep(2.5)
+    mon.beat()
+    dead = mon.dead_ranks()
+    q.put(("dead", dead))
+
+
+def test_rank_failure_is_detected_on_the_host():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_silent_peer_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert got["left"] == 1 and got["dead"] == [1]
