@@ -1,0 +1,203 @@
+"""Command line: ``python -m antfly_b200 <command>`` (the reference's ``antfly inference {run, embed, generate,
+...}``, zig/pkg/inference/src/main.zig:92-157; generate / embed flags follow native_generate.zig / native_embed.zig).
+
+  run       start the HTTP server            --host --port --models-dir --preload task:name[:size]
+  embed     embed texts                      --model --text ... [--dimensions N] [--print-timing]
+  rerank    score documents against a query  --model --query Q --doc ... 
+  generate  generate text                    --model --prompt P [--max-tokens --temperature --top-k --top-p --min-p
+                                             --repetition-penalty --speculative-k --draft-layers --cache-dtype
+                                             --prefill-chunk-size --kv-budget-mb --no-bos --no-chat-template
+                                             --print-timing --print-token-ids --print-finish-reason]
+  search    query a saved index              --index PATH --vector "0.1,0.2,..." | --packed B64 [--k --nprobe]
+  quantize  pack a safetensors checkpoint to block-scaled fp8   --in DIR --out FILE
+  list      list models                      --models-dir
+  smoke     tiny end-to-end run on the GPU
+  bench     forwards to bench.py workloads   --workload decode|embed|knn ...
+
+Model names resolve like the server's; ``random:<size>`` builds a random-init model (tiny | base | 8b | 70b).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from typing import List, Optional
+
+
+def _manager(args):
+    from .api.model_manager import ModelManager
+
+    return ModelManager(models_dir=getattr(args, "models_dir", None), device=getattr(args, "device", None),
+                        kv_blocks=getattr(args, "kv_blocks", 4096))
+
+
+def _get(mgr, name: str, task: str):
+    if name.startswith("random:"):
+        size = name.split(":", 1)[1] or "tiny"
+        return mgr.register_random(name, task, size)
+    return mgr.get(name, task)
+
+
+def cmd_run(args) -> int:
+    from .api.server import serve
+
+    mgr = _manager(args)
+    for spec in args.preload or []:
+        task, name = spec.split(":", 1)
+        _get(mgr, name, task)
+    serve(args.host, args.port, manager=mgr, max_concurrent_requests=args.max_concurrent_requests,
+          max_queue_size=args.max_queue_size)
+    return 0
+
+
+def cmd_embed(args) -> int:
+    mgr = _manager(args)
+    lm = _get(mgr, args.model, "embedder")
+    t0 = time.perf_counter()
+    emb, ntok = lm.pipeline.embed(args.text, dimensions=args.dimensions)
+    dt = time.perf_counter() - t0
+    for i, row in enumerate(emb):
+        print(json.dumps({"index": i, "embedding": [round(x, 6) for x in row.tolist()]}))
+    if args.print_timing:
+        print(f"embed_timing_ms: total={dt * 1e3:.1f} texts={len(args.text)} tokens={ntok}", file=sys.stderr)
+    return 0
+
+
+def cmd_rerank(args) -> int:
+    mgr = _manager(args)
+    lm = _get(mgr, args.model, "reranker")
+    scores, _ = lm.pipeline.rerank(args.query, args.doc)
+    for i in sorted(range(len(scores)), key=lambda j: -scores[j]):
+        print(json.dumps({"index": i, "score": scores[i], "text": args.doc[i]}))
+    return 0
+
+
+def cmd_generate(args) -> int:
+    from .runtime.sampling_params import SamplingParams
+
+    mgr = _manager(args)
+    lm = _get(mgr, args.model, "generator")
+    gen = lm.pipeline
+    eng = gen.engine
+    if args.draft_layers:
+        eng.draft = eng.model.draft_view(args.draft_layers)
+        eng.spec_k = args.speculative_k
+    if args.no_bos:
+        gen.add_bos = False
+    sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
+                        min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed)
+    out = gen.generate(args.prompt, sp, raw_prompt=args.no_chat_template or args.raw_prompt,
+                       on_delta=(lambda d: (sys.stdout.write(d), sys.stdout.flush())) if args.stream else None)
+    if not args.stream:
+        print(out.text)
+    else:
+        print()
+    if args.print_token_ids:
+        print("token_ids:", out.token_ids, file=sys.stderr)
+    if args.print_finish_reason:
+        print("finish_reason:", out.finish_reason, file=sys.stderr)
+    if args.print_timing:
+        print(out.timing_line(), file=sys.stderr)
+        if eng.draft is not None:
+            print(eng.spec.line(), file=sys.stderr)
+    return 0
+
+
+def cmd_search(args) -> int:
+    import torch
+
+    from .index import artifact, codec
+
+    idx = artifact.load_ivf(args.index, device="cuda" if torch.cuda.is_available() else "cpu")
+    q = codec.decode_packed(args.packed, idx.dim) if args.packed else codec.decode_vectors(
+        [float(x) for x in args.vector.split(",")])
+    res = idx.search(q.to(idx.x.device), args.k, nprobe=args.nprobe)
+    for d, i in zip(res.distances[0].tolist(), res.ids[0].tolist()):
+        print(json.dumps({"id": i, "distance": d}))
+    return 0
+
+
+def cmd_quantize(args) -> int:
+    """Pack every 2-D weight of a safetensors checkpoint to block-scaled fp8 (e4m3 + e8m0 per 32 along K)."""
+    from .formats import safetensors_io as ST
+    from .ops import quant as Q
+
+    sd = ST.load_model_dir(args.inp)
+    out = {}
+    for name, t in sd.items():
+        if t.dim() == 2 and t.shape[1] % 32 == 0 and not name.endswith("embed_tokens.weight"):
+            p = Q.pack_fp8(t.float())
+            out[name + ".q"], out[name + ".scales"] = p.q.view(t.shape).view(dtype=p.q.dtype), p.scales
+        else:
+            out[name] = t
+    ST.save_file(out, args.out, {"format": "antfly_b200.block_fp8", "block": "32", "scale": "e8m0"})
+    print(f"wrote {args.out}: {len(out)} tensors")
+    return 0
+
+
+def cmd_list(args) -> int:
+    print(json.dumps(_manager(args).list_models(), indent=2))
+    return 0
+
+
+def cmd_smoke(args) -> int:
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("graft_entry", os.path.join(root, "__graft_entry__.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+    mod.smoke()
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="antfly_b200", description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p):
+        p.add_argument("--models-dir")
+        p.add_argument("--device")
+        p.add_argument("--kv-blocks", type=int, default=4096)
+
+    p = sub.add_parser("run"); common(p)
+    p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=11433)
+    p.add_argument("--preload", nargs="*"); p.add_argument("--max-concurrent-requests", type=int, default=64)
+    p.add_argument("--max-queue-size", type=int, default=256); p.set_defaults(fn=cmd_run)
+    p = sub.add_parser("embed"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--dimensions", type=int); p.add_argument("--print-timing", action="store_true")
+    p.set_defaults(fn=cmd_embed)
+    p = sub.add_parser("rerank"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--query", required=True)
+    p.add_argument("--doc", nargs="+", required=True); p.set_defaults(fn=cmd_rerank)
+    p = sub.add_parser("generate"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--prompt", required=True)
+    p.add_argument("--max-tokens", type=int, default=256); p.add_argument("--temperature", type=float, default=0.0)
+    p.add_argument("--top-k", type=int, default=0); p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--min-p", type=float, default=0.0); p.add_argument("--repetition-penalty", type=float, default=1.0)
+    p.add_argument("--seed", type=int); p.add_argument("--speculative-k", type=int, default=4)
+    p.add_argument("--draft-layers", type=int, default=0); p.add_argument("--cache-dtype", default="bf16")
+    p.add_argument("--prefill-chunk-size", type=int, default=2048); p.add_argument("--kv-budget-mb", type=int, default=0)
+    p.add_argument("--no-bos", action="store_true"); p.add_argument("--no-chat-template", action="store_true")
+    p.add_argument("--raw-prompt", action="store_true"); p.add_argument("--stream", action="store_true")
+    p.add_argument("--print-timing", action="store_true"); p.add_argument("--print-token-ids", action="store_true")
+    p.add_argument("--print-finish-reason", action="store_true"); p.set_defaults(fn=cmd_generate)
+    p = sub.add_parser("search")
+    p.add_argument("--index", required=True); p.add_argument("--vector"); p.add_argument("--packed")
+    p.add_argument("--k", type=int, default=10); p.add_argument("--nprobe", type=int, default=64)
+    p.set_defaults(fn=cmd_search)
+    p = sub.add_parser("quantize")
+    p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
+    p.set_defaults(fn=cmd_quantize)
+    p = sub.add_parser("list"); common(p); p.set_defaults(fn=cmd_list)
+    p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

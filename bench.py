@@ -64,9 +64,23 @@ def _clock_summary(proc):
             "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _log(msg):
+    if os.environ.get("ANTFLY_B200_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} t={time.perf_counter():.1f}] {msg}", file=sys.stderr,
+              flush=True)
+
+
 def _dist_setup(n_gpus):
+    import faulthandler
+
     import torch
     import torch.distributed as dist
+
+    # A multi-rank run that stops making progress dumps every thread's Python stack and exits instead of
+    # sitting in a collective until the launcher's limit.
+    limit = int(os.environ.get("ANTFLY_B200_BENCH_WATCHDOG_S", "0"))
+    if limit > 0:
+        faulthandler.dump_traceback_later(limit, exit=True)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -122,7 +136,8 @@ def bench_decode(args):
     total = prompt_len + gen + 16
     blocks = B * ((total + 15) // 16) + 8
     eng = LLMEngine(model, num_blocks=blocks, page=16, max_batch=B, max_step_tokens=8192, prefill_chunk=2048,
-                    max_seq_len=total)
+                    max_seq_len=total, use_cuda_graph=not os.environ.get("ANTFLY_B200_NO_GRAPH"))
+    _log("model and engine ready")
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab_size, (B, prompt_len), generator=g).tolist()
     sp = SamplingParams(max_tokens=gen, ignore_eos=True)
@@ -132,14 +147,17 @@ def bench_decode(args):
         eng.add_request(p, sp)
     while eng.sched.snapshot()["waiting"] + eng.sched.snapshot()["prefill"] > 0:
         eng.step()
+        _log(f"prefill step done, {eng.sched.snapshot()}")
     _barrier(world)
     prefill_s = time.perf_counter() - t0
+    _log(f"prefill done in {prefill_s:.2f}s")
 
     W, K = args.warmup, args.steps
     assert W >= 3, "at least 3 warm-up steps"
     assert W + 2 * K + 1 <= gen, "warm-up + timed steps exceed the generation length"
     for _ in range(W):
         eng.step()
+    _log("warm-up done")
     # ---- end-to-end: K engine steps, each with its H2D of inputs and D2H of tokens ----
     h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
     _barrier(world)
@@ -150,6 +168,7 @@ def bench_decode(args):
     e2e_s = _max_over_ranks(time.perf_counter() - t1, world)
     h2d_step = (eng.h2d_bytes - h2d0) / K
     d2h_step = (eng.d2h_bytes - d2h0) / K
+    _log("e2e steps done")
     # ---- device-timed burst ----
     _barrier(world)
     clocks = _clock_sampler()
