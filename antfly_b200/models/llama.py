@@ -220,6 +220,7 @@ class LlamaModel:
         head (self-speculative draft).  It needs its own KV cache of n_layers layers."""
         m = LlamaModel(self.cfg, self.w, self.tp_rank, self.tp_size, self.comm)
         m.n_layers = n_layers
+        m.fused = self.fused
         return m
 
     def weight_bytes(self) -> int:
@@ -258,11 +259,53 @@ class LlamaModel:
         self.comm.all_reduce(y)
         return y
 
+    fused = None  # antfly_b200.parallel.fused.FusedTp when the peer-memory path is enabled
+
+    def _forward_fused(self, b: StepBatch, k_cache, v_cache, attn_scratch) -> torch.Tensor:
+        """Tensor-parallel step with the collectives fused into the GEMM and norm kernels (skinny batches)."""
+        cfg, w, fz = self.cfg, self.w, self.fused
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        T = b.ids.numel()
+        tl = fz.tokens_per_rank(T)
+        x_full = Dn.embed_gather(b.ids, w["embed"])
+        h = Dn.norm(x_full, w["l0.ln1"], eps=cfg.rms_norm_eps, rms=True, mx_terms=self.act_terms)
+        x = x_full[self.tp_rank * tl:(self.tp_rank + 1) * tl].contiguous()
+        for l in range(self.n_layers):
+            p = f"l{l}."
+            qkv_w: Q.Fp8Weight = w[p + "qkv"]
+            sk = pick_split_k(qkv_w.out_features, qkv_w.in_features, T)
+            if l == 0:
+                parts = Q.gemm_mxfp8(h, qkv_w, partials=True, split_k=sk)
+            else:
+                parts = fz.gemm_gathered(qkv_w, T, split_k=sk, partials=True)
+            q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
+                                partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
+                                half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    scratch=attn_scratch)
+            o_w: Q.Fp8Weight = w[p + "o"]
+            S = fz.gemm_push(Q.quantize_mx(ctx.view(T, Hq * D), terms=self.act_terms), o_w, T,
+                             pick_split_k(o_w.out_features, o_w.in_features, T))
+            x = fz.norm_reduce_gather(w[p + "ln2"], x, T, S, o_w.out_features, cfg.rms_norm_eps)
+            act = fz.gemm_gathered(w[p + "gu"], T, swiglu=True)
+            d_w: Q.Fp8Weight = w[p + "down"]
+            S = fz.gemm_push(Q.quantize_mx(act, terms=self.act_terms), d_w, T,
+                             pick_split_k(d_w.out_features, d_w.in_features, T))
+            nw = w["norm"] if l + 1 == self.n_layers else w[f"l{l + 1}.ln1"]
+            x = fz.norm_reduce_gather(nw, x, T, S, d_w.out_features, cfg.rms_norm_eps)
+        return fz.gemm_gathered(w["lm_head"], T)
+
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
         """Runs the stack on one step batch; K/V of the step's tokens are written into
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
+        if (self.fused is not None and self.tp_size > 1 and self._use_mx(b.ids.numel())
+                and b.ids.numel() % self.tp_size == 0 and b.logit_rows.numel() == b.ids.numel()
+                and isinstance(w["lm_head"], Q.Fp8Weight)):
+            return self._forward_fused(b, k_cache, v_cache, attn_scratch)
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = b.ids.numel()
         mxt = self.act_terms if self._use_mx(T) else 0

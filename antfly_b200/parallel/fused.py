@@ -1,0 +1,188 @@
+"""Fused compute + collective path for tensor-parallel decode (peer memory over NVLink / NVSwitch).
+
+One symmetric workspace per rank (``torch.distributed._symmetric_memory``; every rank maps every other rank's copy)
+holds (a) the partial-sum slices pushed by the row-parallel GEMMs' epilogues, (b) the MX-fp8 activation rows pushed
+by the norm kernels, (c) arrival counters.  The collectives disappear into the kernels around them:
+
+  GEMM -> reduce-scatter   o_proj / down epilogues store each fp32 partial tile into the buffer of the rank that
+                           owns the token (mode 3 of ``afb_gemm_mxfp8_tp``) and bump a counter there; the residual +
+                           RMSNorm kernel of the owner waits for the counters and sums the slices it already has
+                           to read.
+  all-gather -> GEMM       that same norm kernel quantises its rows and stores them into every rank's activation
+                           buffers; the next column-parallel GEMM (QKV, gate/up, LM head) streams its weight tiles
+                           immediately and only waits for the row counter before its first activation load.
+
+Counters are re-armed by the last CTA of the consuming kernel, so a CUDA graph of the step replays without host
+involvement.  All waits are bounded; an expired wait sets the kernel status word (``_native.status()``).
+Transfers are plain peer loads / stores -- no TMA multicast, no multimem.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as N
+from ..ops import quant as Q
+from ..ops.dense import ACT
+
+_c_int = ctypes.c_int
+_c_long = ctypes.c_long
+_c_float = ctypes.c_float
+
+
+def _ptr_array(ptrs: List[int]):
+    return (ctypes.c_void_p * 8)(*(list(ptrs) + [0] * (8 - len(ptrs))))
+
+
+class SymmetricWorkspace:
+    """Peer-mapped scratch of a tensor-parallel group, carved into named regions with identical offsets on all
+    ranks."""
+
+    def __init__(self, rank: int, world: int, device, hidden: int, max_tokens: int = 128, max_slices: int = 8,
+                 group=None):
+        import torch.distributed._symmetric_memory as symm
+
+        assert max_tokens % world == 0
+        self.rank, self.world, self.device = rank, world, device
+        self.hidden, self.max_tokens, self.max_slices = hidden, max_tokens, max_slices
+        self.tl_max = max_tokens // world
+        off = 0
+
+        def region(nbytes):
+            nonlocal off
+            o = off
+            off = (off + nbytes + 1023) // 1024 * 1024
+            return o
+
+        self.off_flags = region(4096)
+        self.off_parts = region(world * max_slices * self.tl_max * hidden * 4)
+        self.off_q0 = region(max_tokens * hidden)
+        self.off_q1 = region(max_tokens * hidden)
+        tiles = (max_tokens + 127) // 128
+        self.sf_bytes = tiles * (hidden // 128) * 512
+        self.off_sf0 = region(self.sf_bytes)
+        self.off_sf1 = region(self.sf_bytes)
+        self.nbytes = off
+        group = group or dist.group.WORLD
+        self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.hdl = symm.rendezvous(self.buf, group)
+        self.buf.zero_()
+        # scale bytes of rows that are never written must still be a valid exponent
+        self.local(self.off_sf0, self.sf_bytes).fill_(127)
+        self.local(self.off_sf1, self.sf_bytes).fill_(127)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.base_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        assert self.base_ptrs[rank] == self.buf.data_ptr()
+
+    def local(self, off: int, nbytes: int) -> torch.Tensor:
+        return self.buf[off:off + nbytes]
+
+    def peers(self, off: int):
+        return _ptr_array([b + off for b in self.base_ptrs])
+
+    # flag slots (int32 indices inside the flag region)
+    PART_FLAGS, PART_ARRIVED, X_READY, X_CONSUMED = 0, 8, 9, 10
+
+    def flag_ptr(self, slot: int) -> ctypes.c_void_p:
+        return ctypes.c_void_p(self.buf.data_ptr() + self.off_flags + 4 * slot)
+
+    def peer_flag_ptrs(self, slot: int):
+        return _ptr_array([b + self.off_flags + 4 * slot for b in self.base_ptrs])
+
+
+class FusedTp:
+    """The three fused operations of a tensor-parallel decode step."""
+
+    def __init__(self, ws: SymmetricWorkspace, terms: int = 2):
+        self.ws, self.terms = ws, terms
+        self.rank, self.world = ws.rank, ws.world
+
+    def tokens_per_rank(self, T: int) -> int:
+        assert T % self.world == 0 and T <= self.ws.max_tokens
+        return T // self.world
+
+    # -- GEMM -> reduce-scatter -----------------------------------------------------------------------------
+    def gemm_push(self, x: Q.MxAct, w: Q.Fp8Weight, T: int, split_k: int) -> int:
+        """Row-parallel GEMM whose epilogue pushes the partial tiles to the owners.  Returns the slice count."""
+        ws = self.ws
+        M, K = x.q0.shape
+        Nn = w.out_features
+        assert Nn == ws.hidden, "row-parallel outputs are hidden-sized"
+        lib = N.cuda()
+        S = int(lib.afb_mx_effective_splits(_c_int(K), _c_int(max(split_k, 1))))
+        assert S <= ws.max_slices
+        rc = lib.afb_gemm_mxfp8_tp(
+            N.ptr(x.q0), N.ptr(x.q1), N.ptr(x.sf0), N.ptr(x.sf1), N.ptr(w.q), N.ptr(Q.weight_sf_atoms(w)), None, None,
+            None, _c_int(M), _c_int(Nn), _c_int(K), _c_int(Nn), _c_int(0), _c_int(0), _c_int(3), _c_int(S),
+            _c_int(x.terms), ws.peers(ws.off_parts), ws.peer_flag_ptrs(ws.PART_FLAGS), _c_int(self.world),
+            _c_int(self.rank), _c_int(self.tokens_per_rank(T)), _c_int(S), None, _c_int(0), None, N.stream_ptr())
+        N.check(rc, "afb_gemm_mxfp8_tp(push)")
+        N.count_launch()
+        return S
+
+    # -- reduce (own rows) + residual + RMSNorm + all-gather push ---------------------------------------------
+    def norm_reduce_gather(self, gamma: torch.Tensor, residual: torch.Tensor, T: int, slices: int, n_out: int,
+                           eps: float, gather: bool = True):
+        """Waits for every rank's partial slices of this rank's rows, returns the new residual rows [T/world, H]
+        and (when ``gather``) leaves the normalised MX rows of all ranks in the gathered activation buffers."""
+        ws = self.ws
+        tl = self.tokens_per_rank(T)
+        H = ws.hidden
+        parts = ws.local(ws.off_parts, self.world * slices * tl * H * 4).view(torch.float32)
+        sum_out = torch.empty((tl, H), dtype=torch.bfloat16, device=ws.device)
+        expected = ((n_out + 127) // 128) * slices
+        two = self.terms == 2
+        rc = N.cuda().afb_norm_tp(
+            None, N.ptr(parts), _c_int(self.world * slices), _c_long(tl * H), N.ptr(residual), None, N.ptr(gamma), None,
+            N.ptr(sum_out), None, None, _c_int(tl), _c_int(H), _c_float(eps), _c_int(1), _c_int(0), None, None, None,
+            None, ws.flag_ptr(ws.PART_FLAGS), _c_int(self.world), _c_int(expected), ws.flag_ptr(ws.PART_ARRIVED),
+            ws.peers(ws.off_q0), ws.peers(ws.off_q1) if two else None, ws.peers(ws.off_sf0),
+            ws.peers(ws.off_sf1) if two else None, ws.peer_flag_ptrs(ws.X_READY), _c_int(self.world if gather else 0),
+            _c_int(self.rank * tl), N.stream_ptr())
+        N.check(rc, "afb_norm_tp")
+        N.count_launch()
+        return sum_out
+
+    def gathered(self, T: int) -> Q.MxAct:
+        ws = self.ws
+        H = ws.hidden
+        q0 = ws.local(ws.off_q0, T * H).view(T, H)
+        sf0 = ws.local(ws.off_sf0, ws.sf_bytes).view(-1, H // 128, 512)
+        if self.terms == 2:
+            return Q.MxAct(q0, sf0, ws.local(ws.off_q1, T * H).view(T, H), ws.local(ws.off_sf1, ws.sf_bytes).view(
+                -1, H // 128, 512))
+        return Q.MxAct(q0, sf0)
+
+    # -- all-gather -> GEMM ---------------------------------------------------------------------------------
+    def gemm_gathered(self, w: Q.Fp8Weight, T: int, split_k: int = 1, swiglu: bool = False, partials: bool = False,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Column-parallel GEMM on the gathered activations; waits for all T rows to arrive."""
+        ws = self.ws
+        x = self.gathered(T)
+        K, Nn = ws.hidden, w.out_features
+        lib = N.cuda()
+        dev = ws.device
+        if split_k > 1 or partials:
+            S = int(lib.afb_mx_effective_splits(_c_int(K), _c_int(max(split_k, 1))))
+            mode, ldc = 1, Nn
+            out = torch.empty((S, T, Nn), dtype=torch.float32, device=dev) if out is None else out
+        elif swiglu:
+            S, mode = 1, 2
+            out = torch.empty((T, Nn // 2), dtype=torch.bfloat16, device=dev) if out is None else out
+            ldc = out.stride(0)
+        else:
+            S, mode = 1, 0
+            out = torch.empty((T, Nn), dtype=torch.bfloat16, device=dev) if out is None else out
+            ldc = out.stride(0)
+        rc = lib.afb_gemm_mxfp8_tp(
+            N.ptr(x.q0), N.ptr(x.q1), N.ptr(x.sf0), N.ptr(x.sf1), N.ptr(w.q), N.ptr(Q.weight_sf_atoms(w)), N.ptr(out),
+            None, None, _c_int(T), _c_int(Nn), _c_int(K), _c_int(ldc), _c_int(0), _c_int(0), _c_int(mode), _c_int(S),
+            _c_int(x.terms), None, None, _c_int(0), _c_int(0), _c_int(0), _c_int(0), ws.flag_ptr(ws.X_READY), _c_int(T),
+            ws.flag_ptr(ws.X_CONSUMED), N.stream_ptr())
+        N.check(rc, "afb_gemm_mxfp8_tp(gathered)")
+        N.count_launch()
+        return out

@@ -103,6 +103,21 @@ def _max_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
+def _finish(world):
+    """Multi-rank exit: process-group teardown can block while captured graphs still hold NCCL work, so ranks
+    meet at a barrier, flush and leave without running destructors."""
+    if world <= 1:
+        return
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def _barrier(world):
     import torch
 
@@ -132,6 +147,11 @@ def bench_decode(args):
         comm = TpComm(rank, world, torch.device("cuda", local), hidden=cfg.hidden_size, max_tokens=8192)
     model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=rank, tp_size=world,
                                    comm=comm)
+    if world > 1 and args.tp_path == "fused":
+        from antfly_b200.parallel.fused import FusedTp, SymmetricWorkspace
+
+        model.fused = FusedTp(SymmetricWorkspace(rank, world, torch.device("cuda", local), cfg.hidden_size,
+                                                 max_tokens=128))
     B, prompt_len, gen = args.batch, args.prompt_len, args.gen_len
     total = prompt_len + gen + 16
     blocks = B * ((total + 15) // 16) + 8
@@ -186,7 +206,7 @@ def bench_decode(args):
             "vs_baseline": None, "dtype": "bf16 activations, block-scaled fp8 (e4m3 + e8m0/32) weights",
             "data": "synthetic: uniform-random token ids, random-init weights",
             "config": {"model": "Llama-3-8B architecture" + (f" ({cfg.num_hidden_layers} layers)" if args.layers else ""),
-                       "global_batch": B, "seq_len": prompt_len, "gen_len": gen, "parallelism": f"tp{world}",
+                       "global_batch": B, "seq_len": prompt_len, "gen_len": gen, "parallelism": f"tp{world}" + (f" ({args.tp_path})" if world > 1 else ""),
                        "kv": "paged bf16, block 16", "l2": "inputs (weights + KV read per step) far exceed L2",
                        "prefill_s": round(prefill_s, 3), "kernel_status": st},
             "clocks": clk,
@@ -195,10 +215,7 @@ def bench_decode(args):
             "gpu_launches": int(launches),
         }
         print(json.dumps(out))
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.destroy_process_group()
+    _finish(world)
 
 
 def bench_embed(args):
@@ -254,10 +271,7 @@ def bench_embed(args):
             "e2e": {"value": round(docs / e2e_s, 1), "unit": "docs/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h / K)},
             "gpu_launches": int(launches)}))
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.destroy_process_group()
+    _finish(world)
 
 
 def main():
@@ -270,6 +284,8 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--gen-len", type=int, default=256)
+    ap.add_argument("--tp-path", default="fused", choices=["fused", "nccl"],
+                    help="tensor-parallel collectives: fused into the kernels over peer memory, or the NCCL baseline")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline config)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -39,7 +39,36 @@ struct MxParams {
   int mode;  // 0 bf16 out, 1 fp32 partials, 2 swiglu
   int chunks_per_split;
   int k_chunks;
+  // ---- tensor-parallel fused collectives (unused when world == 0) ----
+  // mode 3 (GEMM -> reduce-scatter): the epilogue pushes its fp32 partial tile straight into the symmetric
+  // buffer of the rank that owns each token (plain peer stores over NVLink), laid out on the owner as
+  // [world * slices][tokens_per_rank][ldc], then bumps this rank's arrival counter on every owner.
+  float* peer_parts[8];
+  int* peer_part_flags[8];
+  int world, my_rank, tokens_per_rank, slices;
+  // all-gather -> GEMM: the activation rows are pushed into this rank's X buffers by every rank's producer
+  // kernel; the TMA producer streams weight tiles at once and only waits for `x_expected` arrivals before its
+  // first activation load.
+  int* x_ready;
+  int x_expected;
+  int* x_consumed;
 };
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait on a counter that other GPUs increment.  Returns false (status recorded) on expiry.
+__device__ __forceinline__ bool wait_counter_sys(const int* p, int expected) {
+  for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
+    if (ld_acquire_sys(p) >= expected) return true;
+    __nanosleep(20);
+  }
+  status_set(kStatusPeerFlagTimeout);
+  return false;
+}
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -135,21 +164,48 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < num_c; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, kStatusEmptyWaitTimeout)) break;
+      auto load_w = [&](int i, int s) {
         uint8_t* st = smem + s * L::kStage;
         const int c = c_begin + i;
         mbar_expect_tx(&full[s], L::kTxBytes);
         tma_load_2d(st, &tma_w, &full[s], c * 128, n0);
+        bulk_load(st + L::kWBytes + TERMS * L::kXStage, p.sfw + (static_cast<size_t>(n_tile) * p.k_chunks + c) * 512,
+                  512, &full[s]);
+      };
+      auto load_x = [&](int i, int s) {
+        uint8_t* st = smem + s * L::kStage;
+        const int c = c_begin + i;
         tma_load_2d(st + L::kWBytes, &tma_x0, &full[s], c * 128, t0);
         if (TERMS == 2) tma_load_2d(st + L::kWBytes + L::kXStage, &tma_x1, &full[s], c * 128, t0);
         uint8_t* sf = st + L::kWBytes + TERMS * L::kXStage;
-        bulk_load(sf, p.sfw + (static_cast<size_t>(n_tile) * p.k_chunks + c) * 512, 512, &full[s]);
         bulk_load(sf + 1024, p.sfx0 + (static_cast<size_t>(sfx_tile) * p.k_chunks + c) * 512, 512, &full[s]);
         if (TERMS == 2)
           bulk_load(sf + 2048, p.sfx1 + (static_cast<size_t>(sfx_tile) * p.k_chunks + c) * 512, 512, &full[s]);
+      };
+      int first = 0;
+      bool alive = true;
+      if (p.x_ready) {
+        // Weight tiles do not depend on the other ranks: fill the ring with them, then wait for the gathered
+        // activations, then complete those stages.
+        const int pre = min(num_c, STAGES);
+        for (int i = 0; i < pre; ++i) load_w(i, i);
+        alive = wait_counter_sys(p.x_ready, p.x_expected);
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        const int ctas = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(p.x_consumed, 1) == ctas - 1) {
+          // Every CTA of this GEMM is past its wait: re-arm the counters for the next use.
+          *p.x_consumed = 0;
+          atomicExch(p.x_ready, 0);
+        }
+        for (int i = 0; i < pre; ++i) load_x(i, i);
+        first = pre;
+      }
+      for (int i = first; i < num_c && alive; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, kStatusEmptyWaitTimeout)) break;
+        load_w(i, s);
+        load_x(i, s);
       }
     }
   } else if (warp == 1) {
@@ -209,7 +265,20 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
         }
-        if (p.mode == 1) {
+        if (p.mode == 3) {
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.M) {
+                const int owner = t / p.tokens_per_rank, row = t - owner * p.tokens_per_rank;
+                float* op = p.peer_parts[owner] +
+                            (static_cast<size_t>(p.my_rank * p.slices + blockIdx.z) * p.tokens_per_rank + row) * p.ldc;
+                op[n] = v[j];
+              }
+            }
+          }
+        } else if (p.mode == 1) {
           float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(blockIdx.z) * p.M * p.ldc;
           if (n < p.N) {
 #pragma unroll
@@ -252,6 +321,16 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
             }
           }
         }
+      }
+    }
+    if (p.mode == 3) {
+      // Publish: every writer fences its peer stores, the four epilogue warps meet, one thread bumps this
+      // rank's arrival counter on every owner rank.
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        __threadfence_system();
+        for (int o = 0; o < p.world; ++o) atomicAdd_system(p.peer_part_flags[o] + p.my_rank, 1);
       }
     }
   }
@@ -351,9 +430,27 @@ extern "C" {
 
 // X8 terms [M, K] e4m3 with scale atoms sfx*; W8 [N, K] e4m3 with scale atoms sfw.  terms = 1 or 2.
 // Modes as afb_gemm_w8a16.  K must be a multiple of 128.
+int afb_gemm_mxfp8_tp(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8,
+                      const void* sfw, void* out, const void* bias, const void* residual, int M, int N, int K, int ldc,
+                      int ldr, int act, int mode, int split_k, int terms, void* const* peer_parts,
+                      void* const* peer_part_flags, int world, int my_rank, int tokens_per_rank, int slices,
+                      int* x_ready, int x_expected, int* x_consumed, cudaStream_t stream);
+
 int afb_gemm_mxfp8(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8, const void* sfw,
                    void* out, const void* bias, const void* residual, int M, int N, int K, int ldc, int ldr, int act,
                    int mode, int split_k, int terms, cudaStream_t stream) {
+  return afb_gemm_mxfp8_tp(X0, X1, sfx0, sfx1, W8, sfw, out, bias, residual, M, N, K, ldc, ldr, act, mode, split_k,
+                           terms, nullptr, nullptr, 0, 0, 0, 0, nullptr, 0, nullptr, stream);
+}
+
+// Tensor-parallel form.  mode 3 pushes fp32 partial tiles to the owners' symmetric buffers (peer_parts[o],
+// laid out [world * slices][tokens_per_rank][ldc]) and signals peer_part_flags[o][my_rank]; x_ready != null makes
+// the producer wait for x_expected arrivals before touching the activation buffers.
+int afb_gemm_mxfp8_tp(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8,
+                      const void* sfw, void* out, const void* bias, const void* residual, int M, int N, int K, int ldc,
+                      int ldr, int act, int mode, int split_k, int terms, void* const* peer_parts,
+                      void* const* peer_part_flags, int world, int my_rank, int tokens_per_rank, int slices,
+                      int* x_ready, int x_expected, int* x_consumed, cudaStream_t stream) {
   using namespace afb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % 128 || (N & 15) || M > 128 * 1024) {
@@ -365,11 +462,15 @@ int afb_gemm_mxfp8(const void* X0, const void* X1, const void* sfx0, const void*
   if (split_k > k_chunks) split_k = k_chunks;
   int per = (k_chunks + split_k - 1) / split_k;
   split_k = (k_chunks + per - 1) / per;
-  if (mode != 1 && split_k != 1) {
-    set_last_error("afb_gemm_mxfp8: split_k > 1 needs mode 1 (fp32 partials)");
+  if (mode != 1 && mode != 3 && split_k != 1) {
+    set_last_error("afb_gemm_mxfp8: split_k > 1 needs mode 1 or 3 (fp32 partials)");
     return -1;
   }
-  MxParams p;
+  if (mode == 3 && (world < 1 || world > 8 || split_k > slices || tokens_per_rank < 1)) {
+    set_last_error("afb_gemm_mxfp8: mode 3 needs 1..8 ranks and split_k <= slices");
+    return -1;
+  }
+  MxParams p = {};
   p.out = out;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -378,6 +479,12 @@ int afb_gemm_mxfp8(const void* X0, const void* X1, const void* sfx0, const void*
   p.sfx1 = reinterpret_cast<const uint8_t*>(sfx1);
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr; p.act = act; p.mode = mode;
   p.chunks_per_split = per; p.k_chunks = k_chunks;
+  p.world = mode == 3 ? world : 0; p.my_rank = my_rank; p.tokens_per_rank = tokens_per_rank; p.slices = slices;
+  for (int o = 0; o < 8; ++o) {
+    p.peer_parts[o] = (mode == 3 && o < world) ? reinterpret_cast<float*>(peer_parts[o]) : nullptr;
+    p.peer_part_flags[o] = (mode == 3 && o < world) ? reinterpret_cast<int*>(peer_part_flags[o]) : nullptr;
+  }
+  p.x_ready = x_ready; p.x_expected = x_expected; p.x_consumed = x_consumed;
   if (terms == 2) {
     if (M <= 32) return launch_mx<32, 4, 2>(W8, X0, X1, p, split_k, stream);
     if (M <= 64) return launch_mx<64, 3, 2>(W8, X0, X1, p, split_k, stream);

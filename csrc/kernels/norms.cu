@@ -32,7 +32,28 @@ struct NormParams {
   uint8_t* q1;
   uint8_t* sf0;
   uint8_t* sf1;
+  // ---- tensor-parallel fused collectives (all zero when unused) ----
+  // Reduce-scatter side: the partial slices of this rank's rows are pushed into `partials` by every rank's GEMM
+  // epilogue; wait until each of the `wait_n` source counters reached `wait_expected`, then reduce.  The last CTA
+  // past the wait re-arms the counters.
+  int* wait_flags;
+  int wait_n, wait_expected;
+  int* wait_arrived;
+  // All-gather side: the MX output row is written into every rank's activation buffers at row `row_offset + row`
+  // (peer stores), then each rank's arrival counter is bumped.
+  uint8_t* peer_q0[8];
+  uint8_t* peer_q1[8];
+  uint8_t* peer_sf0[8];
+  uint8_t* peer_sf1[8];
+  int* peer_x_ready[8];
+  int ag_world, row_offset;
 };
+
+__device__ __forceinline__ int norm_ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint32_t mx_e8m0_for_amax(float amax) {
   if (!(amax > 0.0f)) return 127u - 8u;
@@ -53,7 +74,8 @@ __device__ __forceinline__ uint32_t mx_pack_e4m3x4(float a, float b, float c, fl
 // Quantises 8 consecutive values held by this thread; the 4 threads that share a 32-element block agree on the
 // scale through two shuffles.  Must be called by all 4 threads of the group.
 __device__ __forceinline__ void mx_quantize8(const float (&v)[8], uint8_t* q, uint8_t* sf_byte, bool write_sf,
-                                             float (&resid)[8]) {
+                                             float (&resid)[8], uint2* packed_out = nullptr,
+                                             uint32_t* scale_out = nullptr) {
   float amax = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
@@ -67,8 +89,10 @@ __device__ __forceinline__ void mx_quantize8(const float (&v)[8], uint8_t* q, ui
   uint2 p;
   p.x = mx_pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
   p.y = mx_pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-  *reinterpret_cast<uint2*>(q) = p;
-  if (write_sf) *sf_byte = static_cast<uint8_t>(e);
+  if (q) *reinterpret_cast<uint2*>(q) = p;
+  if (write_sf && sf_byte) *sf_byte = static_cast<uint8_t>(e);
+  if (packed_out) *packed_out = p;
+  if (scale_out) *scale_out = e;
   const uint32_t w[2] = {p.x, p.y};
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -98,6 +122,23 @@ __global__ void norm_kernel(NormParams p) {
   const int row = blockIdx.x;
   const int H = p.H;
   const size_t base = static_cast<size_t>(row) * H;
+  if (p.wait_flags) {
+    if (threadIdx.x < p.wait_n) {
+      bool ok = false;
+      for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
+        if (norm_ld_acquire_sys(p.wait_flags + threadIdx.x) >= p.wait_expected) { ok = true; break; }
+        __nanosleep(20);
+      }
+      if (!ok) status_set(kStatusPeerFlagTimeout);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(p.wait_arrived, 1) == static_cast<int>(gridDim.x) - 1) {
+      // Every CTA of this kernel is past its wait and no rank can push again before it has seen this kernel's
+      // output, so the counters can be re-armed here.
+      *p.wait_arrived = 0;
+      for (int s = 0; s < p.wait_n; ++s) atomicExch(p.wait_flags + s, 0);
+    }
+  }
   float lsum = 0.0f;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     float v[8];
@@ -139,7 +180,7 @@ __global__ void norm_kernel(NormParams p) {
       lsum += p.rms ? v[j] * v[j] : v[j];
     }
   }
-  if (!p.y && !p.y_f32 && !p.q0) return;
+  if (!p.y && !p.y_f32 && !p.q0 && !p.ag_world) return;
   float mean = 0.0f, rstd;
   if (p.rms) {
     const float ss = block_sum(lsum, red);
@@ -200,6 +241,39 @@ __global__ void norm_kernel(NormParams p) {
       const bool lead = (threadIdx.x & 3) == 0;
       mx_quantize8(ob, p.q0 + base + i, p.sf0 + sf_off, lead, r1);
       if (p.q1) mx_quantize8(r1, p.q1 + base + i, p.sf1 + sf_off, lead, r2);
+    }
+    if (p.ag_world) {
+      // All-gather by pushing: quantise once, store the row into every rank's buffers.
+      float ob[8], r1[8], r2[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ob[j] = __bfloat162float(__float2bfloat16(o[j]));
+      const int grow = p.row_offset + row;
+      const int kb = i / 32;
+      const size_t sf_off = (static_cast<size_t>(grow / 128) * (H / 128) + kb / 4) * 512 + ((grow % 128) % 32) * 16 +
+                            ((grow % 128) / 32) * 4 + (kb % 4);
+      const size_t q_off = static_cast<size_t>(grow) * H + i;
+      const bool lead = (threadIdx.x & 3) == 0;
+      uint2 pk0, pk1 = make_uint2(0, 0);
+      uint32_t e0, e1 = 0;
+      mx_quantize8(ob, nullptr, nullptr, false, r1, &pk0, &e0);
+      const bool two = p.peer_q1[0] != nullptr;
+      if (two) mx_quantize8(r1, nullptr, nullptr, false, r2, &pk1, &e1);
+      for (int o_ = 0; o_ < p.ag_world; ++o_) {
+        *reinterpret_cast<uint2*>(p.peer_q0[o_] + q_off) = pk0;
+        if (lead) p.peer_sf0[o_][sf_off] = static_cast<uint8_t>(e0);
+        if (two) {
+          *reinterpret_cast<uint2*>(p.peer_q1[o_] + q_off) = pk1;
+          if (lead) p.peer_sf1[o_][sf_off] = static_cast<uint8_t>(e1);
+        }
+      }
+    }
+  }
+  if (p.ag_world) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      for (int o_ = 0; o_ < p.ag_world; ++o_) atomicAdd_system(p.peer_x_ready[o_], 1);
     }
   }
 }
@@ -297,17 +371,50 @@ static int norm_threads(int H) {
 
 extern "C" {
 
+int afb_norm_tp(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
+                const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
+                int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
+                int* wait_flags, int wait_n, int wait_expected, int* wait_arrived, void* const* peer_q0,
+                void* const* peer_q1, void* const* peer_sf0, void* const* peer_sf1, void* const* peer_x_ready,
+                int ag_world, int row_offset, cudaStream_t stream);
+
 int afb_norm(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
              const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
              int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
              cudaStream_t stream) {
+  return afb_norm_tp(x, partials, num_partials, partial_stride, residual, bias, gamma, beta, sum_out, y, y_f32, rows,
+                     H, eps, rms, gamma_plus_one, q0, q1, sf0, sf1, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr,
+                     nullptr, nullptr, 0, 0, stream);
+}
+
+// Tensor-parallel form: optional wait on per-source arrival counters before reducing `partials` (the
+// reduce-scatter half), optional push of the MX output row to every rank (the all-gather half).
+int afb_norm_tp(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
+                const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
+                int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
+                int* wait_flags, int wait_n, int wait_expected, int* wait_arrived, void* const* peer_q0,
+                void* const* peer_q1, void* const* peer_sf0, void* const* peer_sf1, void* const* peer_x_ready,
+                int ag_world, int row_offset, cudaStream_t stream) {
   using namespace afb;
   if (rows <= 0) return 0;
   if (H % 8 != 0 || H > 16384) {
     set_last_error("afb_norm: hidden size must be a multiple of 8 and <= 16384 (got %d)", H);
     return -1;
   }
-  NormParams p;
+  NormParams p = {};
+  if (ag_world < 0 || ag_world > 8 || wait_n > 32) {
+    set_last_error("afb_norm_tp: at most 8 ranks and 32 source counters");
+    return -1;
+  }
+  p.wait_flags = wait_flags; p.wait_n = wait_n; p.wait_expected = wait_expected; p.wait_arrived = wait_arrived;
+  p.ag_world = ag_world; p.row_offset = row_offset;
+  for (int o = 0; o < ag_world; ++o) {
+    p.peer_q0[o] = reinterpret_cast<uint8_t*>(peer_q0[o]);
+    p.peer_q1[o] = peer_q1 ? reinterpret_cast<uint8_t*>(peer_q1[o]) : nullptr;
+    p.peer_sf0[o] = reinterpret_cast<uint8_t*>(peer_sf0[o]);
+    p.peer_sf1[o] = peer_sf1 ? reinterpret_cast<uint8_t*>(peer_sf1[o]) : nullptr;
+    p.peer_x_ready[o] = reinterpret_cast<int*>(peer_x_ready[o]);
+  }
   p.x = reinterpret_cast<const __nv_bfloat16*>(x);
   p.partials = partials; p.num_partials = partials ? num_partials : 0; p.partial_stride = partial_stride;
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -320,7 +427,7 @@ int afb_norm(const void* x, const float* partials, int num_partials, long partia
   p.rows = rows; p.H = H; p.eps = eps; p.rms = rms; p.gamma_plus_one = gamma_plus_one;
   p.q0 = reinterpret_cast<uint8_t*>(q0); p.q1 = reinterpret_cast<uint8_t*>(q1);
   p.sf0 = reinterpret_cast<uint8_t*>(sf0); p.sf1 = reinterpret_cast<uint8_t*>(sf1);
-  if (q0 && (H % 128)) {
+  if ((q0 || ag_world) && (H % 128)) {
     set_last_error("afb_norm: MX output needs a hidden size that is a multiple of 128 (got %d)", H);
     return -1;
   }
