@@ -55,6 +55,13 @@ def gemm_bf16(
     assert a.stride(1) == 1 and w.stride(1) == 1
     M, K = a.shape
     Nn = w.shape[0]
+    if (split_k <= 1 and tile_n == 0 and K <= 1536 and ((M + 127) // 128) * ((Nn + 255) // 256) >= 296
+            and (out is None or out.dim() == 2)):
+        # Many tiles with a short K loop: the persistent kernel overlaps each tile's epilogue with the next
+        # tile's MMAs (measured 15-25 % faster on the encoder shapes).
+        from .index_ops import gemm_persistent
+
+        return gemm_persistent(a, w, bias, act, residual, out, out_dtype, alpha)
     lib = N.cuda()
     splits = int(lib.afb_gemm_effective_splits(_c_int(K), _c_int(split_k))) if split_k > 1 else 1
     if splits > 1:

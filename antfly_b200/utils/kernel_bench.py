@@ -36,7 +36,7 @@ def _graph_time(fns, reps: int = 10) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["w8a16", "mxfp8", "gemm", "attn", "norm", "encattn"])
+    ap.add_argument("kernel", choices=["w8a16", "mxfp8", "gemm", "pgemm", "attn", "norm", "encattn"])
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -81,13 +81,18 @@ def main() -> None:
         else:
             fns = [(lambda w=w: Q.gemm_mxfp8(x, w, split_k=args.split, partials=True)) for w in ws]
         nbytes, flops = Nn * K + Nn * K // 32, 2.0 * M * Nn * K
-    elif args.kernel == "gemm":
+    elif args.kernel in ("gemm", "pgemm"):
         M, Nn, K = args.m, args.n, args.k
         copies = args.copies or max(2, min(8, (300 << 20) // (2 * (M * K + Nn * K)) + 1))
         a = [torch.randn(M, K, device=dev).to(torch.bfloat16) for _ in range(copies)]
         w = [torch.randn(Nn, K, device=dev).to(torch.bfloat16) for _ in range(copies)]
         out = torch.empty(M, Nn, device=dev, dtype=torch.bfloat16)
-        fns = [(lambda i=i: Dn.gemm_bf16(a[i], w[i], out=out, tile_n=args.tile_n)) for i in range(copies)]
+        if args.kernel == "pgemm":
+            from ..ops import index_ops as IX
+
+            fns = [(lambda i=i: IX.gemm_persistent(a[i], w[i], out=out)) for i in range(copies)]
+        else:
+            fns = [(lambda i=i: Dn.gemm_bf16(a[i], w[i], out=out, tile_n=args.tile_n)) for i in range(copies)]
         nbytes, flops = 2 * (M * K + Nn * K + M * Nn), 2.0 * M * Nn * K
     elif args.kernel == "attn":
         B, ctx, Hq, Hkv, D, page = args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, 16

@@ -150,9 +150,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 32; ++j)
                 if (full_chunk || nbase + j < p.N) v[j] += __bfloat162float(p.bias[nbase + j]);
             }
-            if (p.act) {
+            // Chosen once per chunk, outside the element loop (a per-element switch is if-converted into
+            // evaluating every activation for every element).
+            if (p.act == 1) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+              for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+            } else if (p.act == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+            } else if (p.act == 3) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+            } else if (p.act == 4) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
             }
             if (p.residual) {
               const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + nbase;

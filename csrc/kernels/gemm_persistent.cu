@@ -12,8 +12,8 @@
 // the throughput version of gemm_bf16.cu.
 //
 // Warp roles: 0 TMA producer (ring of STAGES 128x64 + 256x64 tiles, 128-byte swizzle), 1 tcgen05.mma issuer
-// (owns all 512 tensor-memory columns: two 256-column accumulators), 2..5 epilogue (warp w reads TMEM lanes
-// 32*(w%4)..+31; a lane is one row of the tile).
+// (owns all 512 tensor-memory columns: two 256-column accumulators), 2..9 epilogue: two warpgroups that split
+// the tile's 256 columns (warp w reads TMEM lanes 32*(w%4)..+31; a lane is one row of the tile).
 #include "../common/ptx.cuh"
 #include "../common/tmap.cuh"
 
@@ -84,7 +84,7 @@ __device__ __forceinline__ bool tile_at(const PersistParams& p, long it, int& m_
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        PersistParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -107,7 +107,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     mbar_fence_init();
     tma_prefetch_desc(&tma_a);
@@ -168,6 +168,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     }
   } else {
     const int q = warp & 3;
+    const int col_lo = ((warp - 2) >> 2) * (kPBN / 2);  // two epilogue warpgroups split the tile's columns
     float run_best = INFINITY;  // kArgmin running state
     int run_idx = 0;
     for (long it = 0;; ++it) {
@@ -187,12 +188,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         if (MODE == kArgmin && nt == 0) { run_best = INFINITY; run_idx = 0; }
       }
 #pragma unroll 1
-      for (int c = 0; c < kPBN; c += 32) {
+      for (int c = col_lo; c < col_lo + kPBN / 2; c += 32) {
         uint32_t r[32];
+        __syncwarp();
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
         const int nbase = nt * kPBN + c;
-        if (c + 32 == kPBN) {
+        if (c + 32 == col_lo + kPBN / 2) {
           // Everything of this accumulator is in registers (or consumed): hand it back to the MMA warp.
           tcgen05_fence_before();
           __syncwarp();
@@ -210,9 +212,20 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             for (int j = 0; j < 32; ++j)
               if (full_chunk || nbase + j < p.N) v[j] += __bfloat162float(p.bias[nbase + j]);
           }
-          if (p.act) {
+          // The activation is chosen once per chunk, outside the element loop: a per-element switch gets
+          // if-converted into evaluating every activation for every element.
+          if (p.act == 1) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = persist_act(v[j], p.act);
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+          } else if (p.act == 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+          } else if (p.act == 3) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+          } else if (p.act == 4) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
           }
           if (p.residual) {
             const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + nbase;
@@ -287,9 +300,22 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           }
         }
       }
-      if (MODE == kArgmin && nt == p.n_tiles - 1 && row_ok) {
-        p.assign[row] = run_idx;
-        if (p.best) p.best[row] = run_best + rterm;
+      if (MODE == kArgmin && nt == p.n_tiles - 1) {
+        // The two warpgroups each hold the arg-min of their half of the columns: combine through shared memory
+        // (lower index wins ties, matching a left-to-right scan).
+        __shared__ float s_best[128];
+        __shared__ int s_idx[128];
+        const int r = q * 32 + lane;
+        if (col_lo != 0) { s_best[r] = run_best; s_idx[r] = run_idx; }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (col_lo == 0 && row_ok) {
+          const float ob = s_best[r];
+          const int oi = s_idx[r];
+          if (ob < run_best || (ob == run_best && oi < run_idx)) { run_best = ob; run_idx = oi; }
+          p.assign[row] = run_idx;
+          if (p.best) p.best[row] = run_best + rterm;
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
       }
     }
   }
@@ -320,7 +346,7 @@ int launch_persistent(const void* A, const void* B, PersistParams p, int lda, in
   int ctas = static_cast<int>(work < sm_count ? work : sm_count);
   if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
   if (ctas < 1) ctas = 1;
-  gemm_persistent_kernel<MODE><<<ctas, 192, kPSmem, stream>>>(ta, tb, p);
+  gemm_persistent_kernel<MODE><<<ctas, 320, kPSmem, stream>>>(ta, tb, p);
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -22,6 +22,17 @@
 
 namespace afb {
 
+// Kept out of line so the unrolled epilogue does not evaluate every activation for every element.
+__device__ __noinline__ float act_one_w8(float x, int act) {
+  switch (act) {
+    case 1: return gelu_erf(x);
+    case 2: return gelu_tanh(x);
+    case 3: return fmaxf(x, 0.0f);
+    case 4: return silu(x);
+    default: return x;
+  }
+}
+
 struct W8Params {
   void* out;
   const __nv_bfloat16* bias;      // [N] or null
@@ -258,13 +269,7 @@ gemm_w8a16_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
               const int t = t0 + c + j;
               if (t < p.M) {
                 float x = v[j] + bias;
-                switch (p.act) {
-                  case 1: x = gelu_erf(x); break;
-                  case 2: x = gelu_tanh(x); break;
-                  case 3: x = fmaxf(x, 0.0f); break;
-                  case 4: x = silu(x); break;
-                  default: break;
-                }
+                if (p.act) x = act_one_w8(x, p.act);
                 if (p.residual) x += __bfloat162float(p.residual[static_cast<size_t>(t) * p.ldr + n]);
                 op[static_cast<size_t>(t) * p.ldc + n] = __float2bfloat16(x);
               }

@@ -132,3 +132,19 @@ def test_maxsim_and_splade():
     logits = _rand(int(lens.sum()), 1000, seed=32)
     sp = dense.splade_pool(logits, starts.cuda(), lens.cuda())
     torch.testing.assert_close(sp, R.splade_pool(logits, starts, lens), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("H", [256, 768, 1024])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_warp_per_row_path(H, rms):
+    """Many short rows take the warp-per-row kernel."""
+    from antfly_b200.ops import dense
+
+    rows = 4099
+    x, r, g = _rand(rows, H, seed=41), _rand(rows, H, seed=42), _rand(H, seed=43)
+    b = None if rms else _rand(H, seed=44)
+    bias = _rand(H, seed=45)
+    s, y = dense.norm(x, g, b, eps=1e-6, rms=rms, residual=r, bias=bias, want_sum=True)
+    rs, ry = R.norm(x, g, b, eps=1e-6, rms=rms, residual=r, bias=bias)
+    torch.testing.assert_close(s.float(), rs, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(y.float(), ry, atol=4e-2, rtol=3e-2)
