@@ -1,0 +1,22 @@
+"""Fused tensor-parallel path on real GPUs (needs at least two): child ranks under torchrun compare the peer-memory
+fused step with the NCCL baseline.  Skipped on a single-GPU machine."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_fused_tp_matches_nccl_baseline():
+    n = 2
+    script = os.path.join(os.path.dirname(__file__), "helpers", "tp_fused_check.py")
+    env = dict(os.environ, NCCL_DEBUG="WARN")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29577", script], capture_output=True,
+                       text=True, timeout=300, env=env)
+    out = r.stdout + r.stderr
+    assert out.count("TP_FUSED_CHECK OK") == n, out[-3000:]
