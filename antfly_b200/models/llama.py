@@ -302,7 +302,7 @@ class LlamaModel:
         """Runs the stack on one step batch; K/V of the step's tokens are written into
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
-        if (self.fused is not None and self.tp_size > 1 and self._use_mx(b.ids.numel())
+        if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.ids.numel() % self.tp_size == 0 and b.logit_rows.numel() == b.ids.numel()
                 and isinstance(w["lm_head"], Q.Fp8Weight)):
             return self._forward_fused(b, k_cache, v_cache, attn_scratch)

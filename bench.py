@@ -147,7 +147,13 @@ def bench_decode(args):
         comm = TpComm(rank, world, torch.device("cuda", local), hidden=cfg.hidden_size, max_tokens=8192)
     model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=rank, tp_size=world,
                                    comm=comm)
-    if world > 1 and args.tp_path == "fused":
+    if args.force_fused and world == 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29588")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    if (world > 1 or args.force_fused) and args.tp_path == "fused":
         from antfly_b200.parallel.fused import FusedTp, SymmetricWorkspace
 
         model.fused = FusedTp(SymmetricWorkspace(rank, world, torch.device("cuda", local), cfg.hidden_size,
@@ -286,6 +292,8 @@ def main():
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--tp-path", default="fused", choices=["fused", "nccl"],
                     help="tensor-parallel collectives: fused into the kernels over peer memory, or the NCCL baseline")
+    ap.add_argument("--force-fused", action="store_true",
+                    help="debug: run the peer-memory fused path with a single rank (pushes to itself)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline config)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -278,11 +278,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         }
         if (p.mode == 3) {
           if (n < p.N) {
+            const float inv_tpr = 1.0f / static_cast<float>(p.tokens_per_rank);
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
               const int t = t0 + c + j;
               if (t < p.M) {
-                const int owner = t / p.tokens_per_rank, row = t - owner * p.tokens_per_rank;
+                const int owner = static_cast<int>((static_cast<float>(t) + 0.5f) * inv_tpr);
+                const int row = t - owner * p.tokens_per_rank;
                 float* op = p.peer_parts[owner] +
                             (static_cast<size_t>(p.my_rank * p.slices + blockIdx.z) * p.tokens_per_rank + row) * p.ldc;
                 op[n] = v[j];
@@ -329,13 +331,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
       }
     }
     if (p.mode == 3) {
-      // Publish: every writer fences its peer stores, the four epilogue warps meet, one thread bumps this
-      // rank's arrival counter on every owner rank.
-      __threadfence_system();
+      // Publish: the four epilogue warps meet, one thread bumps this rank's arrival counter on every owner.
+      // The barrier orders every epilogue thread's peer stores before thread 64's release at system scope
+      // (release is cumulative over what the thread has observed), so one releasing atomic per owner suffices.
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) {
-        __threadfence_system();
-        for (int o = 0; o < p.world; ++o) atomicAdd_system(p.peer_part_flags[o] + p.my_rank, 1);
+        for (int o = 0; o < p.world; ++o)
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.peer_part_flags[o] + p.my_rank) : "memory");
       }
     }
   }

@@ -269,11 +269,11 @@ __global__ void norm_kernel(NormParams p) {
     }
   }
   if (p.ag_world) {
-    __threadfence_system();
+    // Block barrier, then one system-scope releasing atomic per rank (cumulative over the block's peer stores).
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();
-      for (int o_ = 0; o_ < p.ag_world; ++o_) atomicAdd_system(p.peer_x_ready[o_], 1);
+      for (int o_ = 0; o_ < p.ag_world; ++o_)
+        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.peer_x_ready[o_]) : "memory");
     }
   }
 }
