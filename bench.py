@@ -292,6 +292,7 @@ def main():
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--tp-path", default="fused", choices=["fused", "nccl"],
                     help="tensor-parallel collectives: fused into the kernels over peer memory, or the NCCL baseline")
+    ap.add_argument("--knn-rows", type=int, default=2_000_000, help="database rows per GPU for --workload knn")
     ap.add_argument("--force-fused", action="store_true",
                     help="debug: run the peer-memory fused path with a single rank (pushes to itself)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline config)")
