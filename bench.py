@@ -145,8 +145,14 @@ def bench_decode(args):
         from antfly_b200.parallel.comm import TpComm
 
         comm = TpComm(rank, world, torch.device("cuda", local), hidden=cfg.hidden_size, max_tokens=8192)
-    model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=rank, tp_size=world,
-                                   comm=comm)
+    if args.emulate_tp > 1 and world == 1:
+        # Debug: run rank 0's shard of a tp-way split alone, without any communication (results are not a model
+        # output; the point is the per-GPU compute time of the sharded shapes).
+        model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=0,
+                                       tp_size=args.emulate_tp, comm=None)
+    else:
+        model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=rank, tp_size=world,
+                                       comm=comm)
     if args.force_fused and world == 1:
         import torch.distributed as dist
 
@@ -212,7 +218,8 @@ def bench_decode(args):
             "vs_baseline": None, "dtype": "bf16 activations, block-scaled fp8 (e4m3 + e8m0/32) weights",
             "data": "synthetic: uniform-random token ids, random-init weights",
             "config": {"model": "Llama-3-8B architecture" + (f" ({cfg.num_hidden_layers} layers)" if args.layers else ""),
-                       "global_batch": B, "seq_len": prompt_len, "gen_len": gen, "parallelism": f"tp{world}" + (f" ({args.tp_path})" if world > 1 else ""),
+                       "global_batch": B, "seq_len": prompt_len, "gen_len": gen, "parallelism": f"tp{world}" + (f" ({args.tp_path})" if world > 1 else "") +
+                       (f" EMULATED shard of tp{args.emulate_tp}, no comm: not a headline number" if args.emulate_tp > 1 else ""),
                        "kv": "paged bf16, block 16", "l2": "inputs (weights + KV read per step) far exceed L2",
                        "prefill_s": round(prefill_s, 3), "kernel_status": st},
             "clocks": clk,
@@ -235,6 +242,13 @@ def bench_embed(args):
     dev = torch.device("cuda", local)
     model = BertModel.random_init(BertConfig.base(), device=dev, seed=0)
     emb = Embedder(model)
+    if world > 1:
+        # Data parallel: every rank embeds its own 256 documents; the pooling kernel pushes the finished rows
+        # into every rank's gathered buffer, so each step ends with all world * 256 embeddings on every rank.
+        from antfly_b200.parallel.dp_embed import DpEmbedder
+
+        dp = DpEmbedder(model, rank, world, max_local_batch=256)
+        emb.embed_packed = lambda b: dp.embed(b, emb.pooling, emb.normalize)
     W, K = args.warmup, args.steps
     batches = synthetic_batches(W + 2 * K, batch=256, lo=32, hi=512, vocab=(1000, 30000), seed=rank)
     pinned = [b.pin() for b in batches]
@@ -293,6 +307,8 @@ def main():
     ap.add_argument("--tp-path", default="fused", choices=["fused", "nccl"],
                     help="tensor-parallel collectives: fused into the kernels over peer memory, or the NCCL baseline")
     ap.add_argument("--knn-rows", type=int, default=2_000_000, help="database rows per GPU for --workload knn")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="debug: time one rank's shard of a tp-way split on a single GPU with no communication")
     ap.add_argument("--force-fused", action="store_true",
                     help="debug: run the peer-memory fused path with a single rank (pushes to itself)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline config)")

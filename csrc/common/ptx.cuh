@@ -69,6 +69,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
 }
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may start
+// while its predecessor in the stream is still running: everything before griddep_wait() (barrier init, tensor
+// memory allocation, descriptor prefetch, loads of data the predecessor does not produce, e.g. weights)
+// overlaps the predecessor's tail; griddep_wait() returns once the predecessor has completed and its writes are
+// visible.  griddep_launch() lets this kernel's own successor begin launching.  Both are no-ops for a kernel
+// launched without the attribute.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------------------------
 // Proxy fences
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem_attn[];
   __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_attn);  // [2 stages][K tile, V tile]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  griddep_launch();
+  griddep_wait();
   const int b = blockIdx.z / p.num_splits;
   const int split = blockIdx.z % p.num_splits;
   const int hk = blockIdx.y;
@@ -359,6 +361,8 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
 __global__ void attn_merge_kernel(const float* part_o, const float* part_lse, __nv_bfloat16* out, long out_stride,
                                   int rows /* T*Hq */, int Hq, int D, int splits) {
   const int row = blockIdx.x;
+  griddep_launch();
+  griddep_wait();
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_lse[static_cast<size_t>(s) * rows + row]);
   const int tok = row / Hq, head = row % Hq;
@@ -388,8 +392,7 @@ int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
   }
   const int rows_per_cta = SPLIT_KEYS ? 16 : 64;
   dim3 grid((max_rows + rows_per_cta - 1) / rows_per_cta, p.Hkv, B * p.num_splits);
-  flash_attn_kernel<D, PAGED, SPLIT_KEYS><<<grid, 128, smem, stream>>>(p);
-  AFB_CHECK_CUDA(cudaGetLastError());
+  AFB_CHECK_CUDA(launch_pdl(flash_attn_kernel<D, PAGED, SPLIT_KEYS>, grid, dim3(128), smem, stream, p));
   return 0;
 }
 
@@ -452,9 +455,9 @@ int afb_attention(const void* q, long q_stride, const void* k, const void* v, lo
 #undef AFB_ATTN_DISPATCH
   if (rc) return rc;
   if (num_splits > 1) {
-    attn_merge_kernel<<<T * Hq, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_lse, p.out, out_stride, T * Hq, Hq, D,
-                                                                num_splits);
-    AFB_CHECK_CUDA(cudaGetLastError());
+    AFB_CHECK_CUDA(launch_pdl(attn_merge_kernel, dim3(T * Hq), dim3(D <= 64 ? 64 : 128), 0, stream,
+                              static_cast<const float*>(part_o), static_cast<const float*>(part_lse), p.out, out_stride,
+                              T * Hq, Hq, D, num_splits));
   }
   return 0;
 }

@@ -154,6 +154,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   const int sfx_tile = t0 / 128;
   const int sfx_row0 = t0 % 128;  // first row of this tile inside the atom
 
+  griddep_launch();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -193,13 +194,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
         if (TERMS == 2)
           bulk_load(sf + 2048, p.sfx1 + (static_cast<size_t>(sfx_tile) * p.k_chunks + c) * 512, 512, &full[s]);
       };
-      int first = 0;
       bool alive = true;
+      // Weight tiles depend neither on the previous kernel nor on the other ranks: fill the ring with them
+      // first, then wait for the predecessor grid (and, tensor-parallel, for the gathered activation rows), then
+      // complete those stages with the activation tiles.
+      const int pre = min(num_c, STAGES);
+      for (int i = 0; i < pre; ++i) load_w(i, i);
+      griddep_wait();
       if (p.x_ready) {
-        // Weight tiles do not depend on the other ranks: fill the ring with them, then wait for the gathered
-        // activations, then complete those stages.
-        const int pre = min(num_c, STAGES);
-        for (int i = 0; i < pre; ++i) load_w(i, i);
         alive = wait_counter_sys(p.x_ready, p.x_expected);
         asm volatile("fence.proxy.async.global;" ::: "memory");
         const int ctas = gridDim.x * gridDim.y * gridDim.z;
@@ -208,9 +210,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
           *p.x_consumed = 0;
           atomicExch(p.x_ready, 0);
         }
-        for (int i = 0; i < pre; ++i) load_x(i, i);
-        first = pre;
       }
+      for (int i = 0; i < pre; ++i) load_x(i, i);
+      const int first = pre;
       for (int i = first; i < num_c && alive; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (i / STAGES) & 1;
@@ -255,6 +257,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   } else {
     const int q = warp & 3;
     const int n = n0 + q * 32 + lane;
+    griddep_wait();
     const bool ok = mbar_wait(tmem_full, 0, kStatusMmaWaitTimeout);
     tcgen05_fence_after();
     if (ok && num_c > 0) {
@@ -360,8 +363,7 @@ int launch_mx(const void* W, const void* X0, const void* X1, MxParams p, int spl
     configured = true;
   }
   dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
-  gemm_mxfp8_kernel<BT, STAGES, TERMS><<<grid, 192, L::kTotal, stream>>>(tw, tx0, tx1, p);
-  AFB_CHECK_CUDA(cudaGetLastError());
+  AFB_CHECK_CUDA(launch_pdl(gemm_mxfp8_kernel<BT, STAGES, TERMS>, grid, dim3(192), L::kTotal, stream, tw, tx0, tx1, p));
   return 0;
 }
 
@@ -397,6 +399,8 @@ __global__ void quantize_mx_kernel(const __nv_bfloat16* x, long ldx, uint8_t* q0
                                    uint8_t* sf1, int T, int K) {
   const int t = blockIdx.x;
   const int k_chunks = K / 128;
+  griddep_launch();
+  griddep_wait();
   for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
     const uint2 u = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * ldx + i);
     const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
@@ -521,10 +525,10 @@ int afb_quantize_mx(const void* x, long ldx, void* q0, void* q1, void* sf0, void
   }
   int threads = K / 4;
   if (threads > 1024) threads = 1024;
-  quantize_mx_kernel<<<T, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
-                                               reinterpret_cast<uint8_t*>(q0), reinterpret_cast<uint8_t*>(q1),
-                                               reinterpret_cast<uint8_t*>(sf0), reinterpret_cast<uint8_t*>(sf1), T, K);
-  AFB_CHECK_CUDA(cudaGetLastError());
+  AFB_CHECK_CUDA(launch_pdl(quantize_mx_kernel, dim3(T), dim3(threads), 0, stream,
+                            reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<uint8_t*>(q0),
+                            reinterpret_cast<uint8_t*>(q1), reinterpret_cast<uint8_t*>(sf0),
+                            reinterpret_cast<uint8_t*>(sf1), T, K));
   return 0;
 }
 

@@ -122,6 +122,8 @@ __global__ void norm_kernel(NormParams p) {
   const int row = blockIdx.x;
   const int H = p.H;
   const size_t base = static_cast<size_t>(row) * H;
+  griddep_launch();
+  griddep_wait();
   if (p.wait_flags) {
     if (threadIdx.x < p.wait_n) {
       bool ok = false;
@@ -421,6 +423,8 @@ __global__ void bert_embed_ln_kernel(BertEmbedParams p) {
 __global__ void embed_gather_kernel(const int* ids, const __nv_bfloat16* table, __nv_bfloat16* y, int T, int H,
                                     int vocab, float scale) {
   const int t = blockIdx.x;
+  griddep_launch();
+  griddep_wait();
   int id = ids[t];
   if (id < 0 || id >= vocab) {
     status_set(kStatusBadIndex);
@@ -529,7 +533,7 @@ int afb_norm_tp(const void* x, const float* partials, int num_partials, long par
     AFB_CHECK_CUDA(cudaGetLastError());
     return 0;
   }
-  norm_kernel<<<rows, norm_threads(H), smem, stream>>>(p);
+  AFB_CHECK_CUDA(launch_pdl(norm_kernel, dim3(rows), dim3(norm_threads(H)), smem, stream, p));
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -565,9 +569,9 @@ int afb_embed_gather(const int* ids, const void* table, void* y, int T, int H, i
     set_last_error("afb_embed_gather: hidden size must be a multiple of 8 (got %d)", H);
     return -1;
   }
-  embed_gather_kernel<<<T, norm_threads(H), 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
-                                                         reinterpret_cast<__nv_bfloat16*>(y), T, H, vocab, scale);
-  AFB_CHECK_CUDA(cudaGetLastError());
+  AFB_CHECK_CUDA(launch_pdl(embed_gather_kernel, dim3(T), dim3(norm_threads(H)), 0, stream, ids,
+                            reinterpret_cast<const __nv_bfloat16*>(table), reinterpret_cast<__nv_bfloat16*>(y), T, H,
+                            vocab, scale));
   return 0;
 }
 

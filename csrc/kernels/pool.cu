@@ -20,6 +20,12 @@ struct PoolParams {
   int B, H;
   int mode;                // 0 mean, 1 cls, 2 max, 3 last
   int normalize;
+  // Data-parallel gather fused into the producer: the finished row is also stored into every rank's gathered
+  // buffer (peer stores over NVLink) at row `row_offset + b`, and each rank's arrival counter is bumped once per
+  // CTA, so the all-gather of per-GPU embedding outputs needs no separate collective.
+  float* peer_out[8];
+  int* peer_ready[8];
+  int n_peers, row_offset;
 };
 
 __global__ void pool_kernel(PoolParams p) {
@@ -67,9 +73,21 @@ __global__ void pool_kernel(PoolParams p) {
     }
     p.out[static_cast<size_t>(b) * H + c] = a0;
     p.out[static_cast<size_t>(b) * H + c + 1] = a1;
+    if (!p.normalize) {
+      for (int o = 0; o < p.n_peers; ++o)
+        *reinterpret_cast<float2*>(p.peer_out[o] + static_cast<size_t>(p.row_offset + b) * H + c) = make_float2(a0, a1);
+    }
     ss += a0 * a0 + a1 * a1;
   }
-  if (!p.normalize) return;
+  if (!p.normalize) {
+    if (p.n_peers) {
+      __syncthreads();
+      if (threadIdx.x == 0)
+        for (int o = 0; o < p.n_peers; ++o)
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.peer_ready[o]) : "memory");
+    }
+    return;
+  }
   ss = warp_sum(ss);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
   if (lane == 0) red[warp] = ss;
@@ -78,8 +96,17 @@ __global__ void pool_kernel(PoolParams p) {
   t = warp_sum(t);
   const float inv = t > 0.0f ? rsqrtf(t) : 0.0f;
   for (int c = threadIdx.x * 2; c < H; c += blockDim.x * 2) {
-    p.out[static_cast<size_t>(b) * H + c] *= inv;
-    p.out[static_cast<size_t>(b) * H + c + 1] *= inv;
+    const float a0 = p.out[static_cast<size_t>(b) * H + c] * inv, a1 = p.out[static_cast<size_t>(b) * H + c + 1] * inv;
+    p.out[static_cast<size_t>(b) * H + c] = a0;
+    p.out[static_cast<size_t>(b) * H + c + 1] = a1;
+    for (int o = 0; o < p.n_peers; ++o)
+      *reinterpret_cast<float2*>(p.peer_out[o] + static_cast<size_t>(p.row_offset + b) * H + c) = make_float2(a0, a1);
+  }
+  if (p.n_peers) {
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int o = 0; o < p.n_peers; ++o)
+        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.peer_ready[o]) : "memory");
   }
 }
 
@@ -151,15 +178,35 @@ __global__ void splade_pool_kernel(const __nv_bfloat16* logits, const int* start
 
 extern "C" {
 
+int afb_pool_gather(const void* h, const int* starts, const int* lens, const int* mask, float* out, int B, int H,
+                    int mode, int normalize, void* const* peer_out, void* const* peer_ready, int n_peers,
+                    int row_offset, cudaStream_t stream);
+
 int afb_pool(const void* h, const int* starts, const int* lens, const int* mask, float* out, int B, int H, int mode,
              int normalize, cudaStream_t stream) {
+  return afb_pool_gather(h, starts, lens, mask, out, B, H, mode, normalize, nullptr, nullptr, 0, 0, stream);
+}
+
+// Pooling whose output rows are also pushed into every rank's gathered buffer (data-parallel embedding gather).
+int afb_pool_gather(const void* h, const int* starts, const int* lens, const int* mask, float* out, int B, int H,
+                    int mode, int normalize, void* const* peer_out, void* const* peer_ready, int n_peers,
+                    int row_offset, cudaStream_t stream) {
   using namespace afb;
   if (B <= 0) return 0;
   if (H % 2 != 0) {
     set_last_error("afb_pool: hidden size must be even (got %d)", H);
     return -1;
   }
-  PoolParams p;
+  PoolParams p = {};
+  if (n_peers < 0 || n_peers > 8) {
+    set_last_error("afb_pool_gather: at most 8 ranks");
+    return -1;
+  }
+  p.n_peers = n_peers; p.row_offset = row_offset;
+  for (int o = 0; o < n_peers; ++o) {
+    p.peer_out[o] = reinterpret_cast<float*>(peer_out[o]);
+    p.peer_ready[o] = reinterpret_cast<int*>(peer_ready[o]);
+  }
   p.h = reinterpret_cast<const __nv_bfloat16*>(h);
   p.starts = starts; p.lens = lens; p.mask = mask; p.out = out; p.B = B; p.H = H; p.mode = mode;
   p.normalize = normalize;

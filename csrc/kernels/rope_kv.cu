@@ -58,6 +58,8 @@ __device__ __forceinline__ void store_kv(const RopeKvParams& p, void* cache, siz
 // heads, then Hkv key heads, then Hkv value heads).
 __global__ void rope_kv_kernel(RopeKvParams p) {
   const int t = blockIdx.x;
+  griddep_launch();
+  griddep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x >> 5) * gridDim.y;
   const int D = p.D, half = D / 2;
   const int row_width = (p.Hq + 2 * p.Hkv) * D;
@@ -195,7 +197,7 @@ int afb_rope_kv_write(const void* qkv, const float* partials, int num_partials, 
   int groups = T >= 1024 ? 1 : (total_heads + 7) / 8;
   if (groups < 1) groups = 1;
   dim3 grid(T, groups);
-  rope_kv_kernel<<<grid, 256, 0, stream>>>(p);
+  AFB_CHECK_CUDA(launch_pdl(rope_kv_kernel, grid, dim3(256), 0, stream, p));
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,6 +1,7 @@
 // Library-wide host runtime: error string, status-word registry, TMA tensor-map encoder lookup.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <vector>
@@ -57,6 +58,15 @@ CUtensorMapSwizzle swizzle_for(int s) {
 }  // namespace
 
 void register_status_reader(StatusReader fn) { readers().push_back(fn); }
+
+int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("ANTFLY_B200_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
 
 const char* last_error() { return g_err; }
 
@@ -138,6 +148,11 @@ int afb_status_read(int clear) {
   }
   return v;
 }
+
+// Programmatic dependent launch on (1) / off (0) for the kernels that support it; default on, or
+// ANTFLY_B200_PDL=0 in the environment.
+void afb_set_pdl(int on) { afb::g_pdl = on ? 1 : 0; }
+int afb_get_pdl() { return afb::pdl_enabled() ? 1 : 0; }
 
 int afb_num_status_words() { return static_cast<int>(afb::readers().size()); }
 

@@ -40,6 +40,8 @@ __global__ void argmax_kernel(const T* logits, long row_stride, int V, int* out_
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const int row = blockIdx.x;
+  griddep_launch();
+  griddep_wait();
   const T* lp = logits + static_cast<size_t>(row) * row_stride;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -321,12 +323,12 @@ int afb_argmax(const void* logits, int is_f32, long row_stride, int rows, int V,
   using namespace afb;
   if (rows <= 0) return 0;
   if (is_f32)
-    argmax_kernel<float><<<rows, 1024, 0, stream>>>(reinterpret_cast<const float*>(logits), row_stride, V, out_idx,
-                                                    out_val, vocab_offset);
+    AFB_CHECK_CUDA(launch_pdl(argmax_kernel<float>, dim3(rows), dim3(1024), 0, stream,
+                              reinterpret_cast<const float*>(logits), row_stride, V, out_idx, out_val, vocab_offset));
   else
-    argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
-                                                            row_stride, V, out_idx, out_val, vocab_offset);
-  AFB_CHECK_CUDA(cudaGetLastError());
+    AFB_CHECK_CUDA(launch_pdl(argmax_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, stream,
+                              reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, out_idx, out_val,
+                              vocab_offset));
   return 0;
 }
 

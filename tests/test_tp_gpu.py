@@ -20,3 +20,14 @@ def test_fused_tp_matches_nccl_baseline():
                        text=True, timeout=300, env=env)
     out = r.stdout + r.stderr
     assert out.count("TP_FUSED_CHECK OK") == n, out[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_dp_embedding_gather_and_sharded_search_merge():
+    n = 2
+    script = os.path.join(os.path.dirname(__file__), "helpers", "dp_sharded_check.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29578", script], capture_output=True,
+                       text=True, timeout=300, env=dict(os.environ, NCCL_DEBUG="WARN"))
+    out = r.stdout + r.stderr
+    assert out.count("DP_SHARDED_CHECK OK") == n, out[-3000:]
