@@ -99,7 +99,7 @@ def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> i
     """Split K so a skinny GEMM still puts about one CTA on every SM."""
     bt = 16 if m_tokens <= 16 else 32 if m_tokens <= 32 else 64 if m_tokens <= 64 else 128 if m_tokens <= 128 else 256
     tiles = ((n_out + 127) // 128) * ((m_tokens + bt - 1) // bt)
-    if tiles >= sm_count * 3 // 4:
+    if tiles >= sm_count:
         return 1
     num_kb = (k_in + 127) // 128
     # Aim for about one CTA per SM, keep at least 4 K-chunks per CTA and at most 8 partial slices for the
@@ -284,18 +284,58 @@ class LlamaModel:
                                 q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
-                                    scratch=attn_scratch)
+                                    scratch=attn_scratch, mx_terms=self.act_terms)
             o_w: Q.Fp8Weight = w[p + "o"]
-            S = fz.gemm_push(Q.quantize_mx(ctx.view(T, Hq * D), terms=self.act_terms), o_w, T,
-                             pick_split_k(o_w.out_features, o_w.in_features, T))
+            S = fz.gemm_push(ctx, o_w, T, pick_split_k(o_w.out_features, o_w.in_features, T))
             x = fz.norm_reduce_gather(w[p + "ln2"], x, T, S, o_w.out_features, cfg.rms_norm_eps)
-            act = fz.gemm_gathered(w[p + "gu"], T, swiglu=True)
+            gu_w: Q.Fp8Weight = w[p + "gu"]
+            sk = pick_split_k(gu_w.out_features, gu_w.in_features, T)
+            if sk > 1:
+                act = Q.swiglu_quantize_mx(fz.gemm_gathered(gu_w, T, split_k=sk, partials=True),
+                                           terms=self.act_terms)
+            else:
+                act = Q.quantize_mx(fz.gemm_gathered(gu_w, T, swiglu=True), terms=self.act_terms)
             d_w: Q.Fp8Weight = w[p + "down"]
-            S = fz.gemm_push(Q.quantize_mx(act, terms=self.act_terms), d_w, T,
-                             pick_split_k(d_w.out_features, d_w.in_features, T))
+            S = fz.gemm_push(act, d_w, T, pick_split_k(d_w.out_features, d_w.in_features, T))
             nw = w["norm"] if l + 1 == self.n_layers else w[f"l{l + 1}.ln1"]
             x = fz.norm_reduce_gather(nw, x, T, S, d_w.out_features, cfg.rms_norm_eps)
         return fz.gemm_gathered(w["lm_head"], T)
+
+    def _forward_one_shot(self, b: StepBatch, k_cache, v_cache, attn_scratch) -> torch.Tensor:
+        """Tensor-parallel step whose two collectives per layer are one-shot all-reduces fused into the
+        row-parallel GEMMs (push) and the norms (wait + sum): one NVLink hop each, replicated residual stream."""
+        cfg, w, fz = self.cfg, self.w, self.fused
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        T = b.ids.numel()
+        mxt = self.act_terms
+        x = Dn.embed_gather(b.ids, w["embed"])
+        h = Dn.norm(x, w["l0.ln1"], eps=cfg.rms_norm_eps, rms=True, mx_terms=mxt)
+        for l in range(self.n_layers):
+            p = f"l{l}."
+            qkv_w: Q.Fp8Weight = w[p + "qkv"]
+            parts = Q.gemm_mxfp8(h, qkv_w, partials=True,
+                                 split_k=pick_split_k(qkv_w.out_features, qkv_w.in_features, T))
+            q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
+                                partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
+                                half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    scratch=attn_scratch, mx_terms=mxt)
+            o_w: Q.Fp8Weight = w[p + "o"]
+            fz.gemm_bcast(ctx, o_w, T, pick_split_k(o_w.out_features, o_w.in_features, T), 0)
+            x, h = fz.norm_bcast(w[p + "ln2"], x, T, cfg.rms_norm_eps, 0)
+            gu_w: Q.Fp8Weight = w[p + "gu"]
+            sk = pick_split_k(gu_w.out_features, gu_w.in_features, T)
+            if sk > 1:
+                act = Q.swiglu_quantize_mx(Q.gemm_mxfp8(h, gu_w, partials=True, split_k=sk), terms=mxt)
+            else:
+                act = Q.quantize_mx(Q.gemm_mxfp8(h, gu_w, swiglu=True), terms=mxt)
+            d_w: Q.Fp8Weight = w[p + "down"]
+            fz.gemm_bcast(act, d_w, T, pick_split_k(d_w.out_features, d_w.in_features, T), 1)
+            nw = w["norm"] if l + 1 == self.n_layers else w[f"l{l + 1}.ln1"]
+            x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
+        return Q.gemm_mxfp8(h, w["lm_head"])
 
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
@@ -303,9 +343,12 @@ class LlamaModel:
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
         if (self.fused is not None and self._use_mx(b.ids.numel())
-                and b.ids.numel() % self.tp_size == 0 and b.logit_rows.numel() == b.ids.numel()
-                and isinstance(w["lm_head"], Q.Fp8Weight)):
-            return self._forward_fused(b, k_cache, v_cache, attn_scratch)
+                and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)
+                and b.ids.numel() <= self.fused.ws.max_tokens):
+            if self.fused.one_shot:
+                return self._forward_one_shot(b, k_cache, v_cache, attn_scratch)
+            if b.ids.numel() % self.tp_size == 0:
+                return self._forward_fused(b, k_cache, v_cache, attn_scratch)
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = b.ids.numel()
         mxt = self.act_terms if self._use_mx(T) else 0
@@ -322,13 +365,19 @@ class LlamaModel:
                                 q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
-                                    scratch=attn_scratch)
+                                    scratch=attn_scratch, mx_terms=mxt)
             o_w: Q.Fp8Weight = w[p + "o"]
-            parts = self._reduce(self._linear(ctx.view(T, Hq * D), o_w, T, partials=True,
+            parts = self._reduce(self._linear(ctx if mxt else ctx.view(T, Hq * D), o_w, T, partials=True,
                                               split_k=pick_split_k(o_w.out_features, o_w.in_features, T)))
             x, h = Dn.norm(None, w[p + "ln2"], eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts,
                            want_sum=True, mx_terms=mxt)
-            act = self._linear(h, w[p + "gu"], T, swiglu=True)
+            gu_w: Q.Fp8Weight = w[p + "gu"]
+            sk = pick_split_k(gu_w.out_features, gu_w.in_features, T) if mxt else 1
+            if sk > 1:
+                # Too few weight tiles to fill the SMs: split K and let the quantiser apply SwiGLU to the summed slices.
+                act = Q.swiglu_quantize_mx(self._linear(h, gu_w, T, partials=True, split_k=sk), terms=mxt)
+            else:
+                act = self._linear(h, gu_w, T, swiglu=True)
             d_w: Q.Fp8Weight = w[p + "down"]
             parts = self._reduce(self._linear(act, d_w, T, partials=True,
                                               split_k=pick_split_k(d_w.out_features, d_w.in_features, T)))

@@ -55,22 +55,35 @@ class PagedAttnScratch:
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, max_q_len: int,
                     scale: Optional[float] = None, window: int = 0, decode: Optional[bool] = None,
                     num_splits: int = 1, scratch: Optional[PagedAttnScratch] = None,
-                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, mx_terms: int = 0):
     """Causal attention of packed query tokens q [T, Hq, D] against the paged cache
     k_cache / v_cache [num_blocks, page, Hkv, D].  ``decode`` selects the split-keys organisation (<= 16
-    (position, head-in-group) rows per KV head); default: when max_q_len * group <= 16."""
+    (position, head-in-group) rows per KV head); default: when max_q_len * group <= 16.
+    ``mx_terms`` 1 or 2 returns the context rows [T, Hq * D] as MX-fp8 activations
+    (:class:`antfly_b200.ops.quant.MxAct`) for the output projection: emitted by the split merge kernel when the
+    KV range is split, by a quantisation pass otherwise."""
     T, Hq, D = q.shape
     page, Hkv = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
-        return R.paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale,
-                                 window).to(torch.bfloat16)
+        y = R.paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale,
+                              window).to(torch.bfloat16)
+        if mx_terms:
+            from . import quant as Q
+
+            return Q.quantize_mx(y.reshape(T, Hq * D), terms=mx_terms)
+        return y
     G = Hq // Hkv
     if decode is None:
         decode = max_q_len * G <= 16
     if not decode:
         num_splits = 1
-    if out is None:
+    mx = None
+    if mx_terms and num_splits > 1 and (Hq * D) % 128 == 0:
+        from . import quant as Q
+
+        mx = Q.new_mx(T, Hq * D, mx_terms, q.device)
+    elif out is None:
         out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     part_o = part_lse = None
     if num_splits > 1:
@@ -79,15 +92,23 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
         assert scratch.max_splits >= num_splits and scratch.part_lse.shape[1] >= T * Hq
         part_o, part_lse = scratch.part_o, scratch.part_lse
     B = q_starts.numel()
-    rc = N.cuda().afb_attention(
+    rc = N.cuda().afb_attention_mx(
         N.ptr(q), _c_long(q.stride(0)), None, None, _c_long(0), N.ptr(k_cache), N.ptr(v_cache),
         N.ptr(block_tables), _c_int(block_tables.shape[1]), _c_int(page), N.ptr(q_starts), N.ptr(q_lens),
-        N.ptr(kv_lens), N.ptr(out), _c_long(out.stride(0)), N.ptr(part_o), N.ptr(part_lse), _c_int(B), _c_int(T),
-        _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_q_len), _c_int(1), _c_int(window), _c_float(scale), _c_int(1),
-        _c_int(1 if decode else 0), _c_int(num_splits), N.stream_ptr(),
+        N.ptr(kv_lens), N.ptr(out), _c_long(out.stride(0) if out is not None else Hq * D), N.ptr(part_o),
+        N.ptr(part_lse), _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_q_len), _c_int(1),
+        _c_int(window), _c_float(scale), _c_int(1), _c_int(1 if decode else 0), _c_int(num_splits),
+        N.ptr(mx.q0 if mx else None), N.ptr(mx.q1 if mx else None), N.ptr(mx.sf0 if mx else None),
+        N.ptr(mx.sf1 if mx else None), N.stream_ptr(),
     )
     N.check(rc, "afb_attention")
     N.count_launch(2 if num_splits > 1 else 1)
+    if mx is not None:
+        return mx
+    if mx_terms:
+        from . import quant as Q
+
+        return Q.quantize_mx(out.view(T, Hq * D), terms=mx_terms)
     return out
 
 

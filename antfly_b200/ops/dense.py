@@ -127,10 +127,7 @@ def norm(
     if mx_terms and want_norm:
         from . import quant as Q
 
-        tiles = (rows + 127) // 128
-        mk = lambda: torch.empty((rows, H), dtype=torch.uint8, device=dev)
-        mks = lambda: torch.full((tiles, H // 128, 512), 127, dtype=torch.uint8, device=dev)
-        mx = Q.MxAct(mk(), mks(), mk() if mx_terms == 2 else None, mks() if mx_terms == 2 else None)
+        mx = Q.new_mx(rows, H, mx_terms, dev)
     elif want_norm and out is None:
         out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     if want_sum and sum_out is None:

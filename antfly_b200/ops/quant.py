@@ -174,6 +174,43 @@ class MxAct:
         return y
 
 
+def new_mx(T: int, K: int, terms: int, device) -> MxAct:
+    """Uninitialised MX activation buffers.  The scale bytes of the padding rows of the last 128-row atom stay
+    undefined on the GPU: a row's scale only ever multiplies that row's own output column, and columns past T
+    are not stored, so no fill kernel is spent on them."""
+    tiles = (T + 127) // 128
+    mk = lambda: torch.empty((T, K), dtype=torch.uint8, device=device)
+    if torch.device(device).type == "cuda":
+        mks = lambda: torch.empty((tiles, K // 128, 512), dtype=torch.uint8, device=device)
+    else:
+        mks = lambda: torch.full((tiles, K // 128, 512), 127, dtype=torch.uint8, device=device)
+    return MxAct(mk(), mks(), mk() if terms == 2 else None, mks() if terms == 2 else None)
+
+
+def swiglu_quantize_mx(parts: torch.Tensor, terms: int = 2, bias: Optional[torch.Tensor] = None,
+                       want_bf16: bool = False):
+    """fp32 split-K partial slices [S, T, 2F] of an interleaved gate/up GEMM -> silu(gate) * up -> MX activations
+    [T, F] (and the bf16 rows too when ``want_bf16``): the consumer side of a split gate/up GEMM."""
+    S, T, N2 = parts.shape
+    F = N2 // 2
+    assert F % 128 == 0
+    if not parts.is_cuda:
+        y = parts.sum(0)
+        if bias is not None:
+            y = y + bias.float()
+        y = R.swiglu_interleaved(y).to(torch.bfloat16)
+        mx = quantize_mx(y, terms=terms)
+        return (mx, y) if want_bf16 else mx
+    mx = new_mx(T, F, terms, parts.device)
+    y = torch.empty((T, F), dtype=torch.bfloat16, device=parts.device) if want_bf16 else None
+    rc = N.cuda().afb_swiglu_quantize_mx(
+        N.ptr(parts), _c_int(S), _c_long(parts.stride(0)), _c_long(parts.stride(1)), N.ptr(bias), N.ptr(mx.q0),
+        N.ptr(mx.q1), N.ptr(mx.sf0), N.ptr(mx.sf1), N.ptr(y), _c_long(F), _c_int(T), _c_int(F), N.stream_ptr())
+    N.check(rc, "afb_swiglu_quantize_mx")
+    N.count_launch()
+    return (mx, y) if want_bf16 else mx
+
+
 def quantize_mx(x: torch.Tensor, terms: int = 2, out: Optional[MxAct] = None) -> MxAct:
     """bf16 [T, K] -> MX fp8 (``terms`` = 1: x ~ hi; 2: x ~ hi + lo with lo the quantised residual)."""
     T, K = x.shape
@@ -181,10 +218,7 @@ def quantize_mx(x: torch.Tensor, terms: int = 2, out: Optional[MxAct] = None) ->
     tiles = (T + 127) // 128
     dev = x.device
     if out is None:
-        mk = lambda: torch.empty((T, K), dtype=torch.uint8, device=dev)
-        # Scale bytes of rows past T are never used by a valid output, but keep them defined.
-        mks = lambda: torch.full((tiles, K // 128, 512), 127, dtype=torch.uint8, device=dev)
-        out = MxAct(mk(), mks(), mk() if terms == 2 else None, mks() if terms == 2 else None)
+        out = new_mx(T, K, terms, dev)
     if not x.is_cuda:
         def q_one(v):
             q, e8 = R.quantize_block_fp8(v)

@@ -12,6 +12,17 @@ by the norm kernels, (c) arrival counters.  The collectives disappear into the k
                            buffers; the next column-parallel GEMM (QKV, gate/up, LM head) streams its weight tiles
                            immediately and only waits for the row counter before its first activation load.
 
+For the skinniest batches a one-shot variant halves the number of NVLink hops per collective:
+
+  GEMM -> all-reduce       o_proj / down reduce their split-K slices inside a thread-block cluster (distributed
+                           shared memory), round to bf16 and store the tile into slot `rank` of EVERY rank's buffer
+                           (``afb_gemm_mxfp8_bcast``);
+                           each rank's residual + RMSNorm kernel polls the slots themselves (they hold a sentinel
+                           until data lands -- no flags, no fences), sums them in rank order, so the replicated
+                           residual stream stays bit-identical on all ranks, and puts the sentinel back; the next
+                           column-parallel GEMM reads local activations with no second hop.  Two buffers alternate
+                           between the two collectives of a layer.
+
 Counters are re-armed by the last CTA of the consuming kernel, so a CUDA graph of the step replays without host
 involvement.  All waits are bounded; an expired wait sets the kernel status word (``_native.status()``).
 Transfers are plain peer loads / stores -- no TMA multicast, no multimem.
@@ -65,6 +76,8 @@ class SymmetricWorkspace:
         self.sf_bytes = tiles * (hidden // 128) * 512
         self.off_sf0 = region(self.sf_bytes)
         self.off_sf1 = region(self.sf_bytes)
+        # one-shot all-reduce: two alternating [world][max_tokens][hidden] bf16 slot buffers
+        self.off_bcast = [region(world * max_tokens * hidden * 2) for _ in range(2)]
         self.nbytes = off
         group = group or dist.group.WORLD
         self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
@@ -73,10 +86,17 @@ class SymmetricWorkspace:
         # scale bytes of rows that are never written must still be a valid exponent
         self.local(self.off_sf0, self.sf_bytes).fill_(127)
         self.local(self.off_sf1, self.sf_bytes).fill_(127)
+        self.clear_one_shot_slots()
         torch.cuda.synchronize(device)
         dist.barrier(group)
         self.base_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
         assert self.base_ptrs[rank] == self.buf.data_ptr()
+
+    def clear_one_shot_slots(self) -> None:
+        """Puts the 'nothing here yet' sentinel (bf16 -0.0) into every one-shot slot.  Done at construction; the
+        consumer kernels restore it after every read, so this is only needed again after a failed step."""
+        for off in self.off_bcast:
+            self.local(off, self.world * self.max_tokens * self.hidden * 2).view(torch.int16).fill_(-32768)
 
     def local(self, off: int, nbytes: int) -> torch.Tensor:
         return self.buf[off:off + nbytes]
@@ -97,8 +117,8 @@ class SymmetricWorkspace:
 class FusedTp:
     """The three fused operations of a tensor-parallel decode step."""
 
-    def __init__(self, ws: SymmetricWorkspace, terms: int = 2):
-        self.ws, self.terms = ws, terms
+    def __init__(self, ws: SymmetricWorkspace, terms: int = 2, one_shot: bool = True):
+        self.ws, self.terms, self.one_shot = ws, terms, one_shot
         self.rank, self.world = ws.rank, ws.world
 
     def tokens_per_rank(self, T: int) -> int:
@@ -137,7 +157,8 @@ class FusedTp:
         expected = ((n_out + 127) // 128) * slices
         two = self.terms == 2
         rc = N.cuda().afb_norm_tp(
-            None, N.ptr(parts), _c_int(self.world * slices), _c_long(tl * H), N.ptr(residual), None, N.ptr(gamma), None,
+            None, N.ptr(parts), _c_int(self.world * slices), _c_long(tl * H), _c_int(0), N.ptr(residual), None,
+            N.ptr(gamma), None,
             N.ptr(sum_out), None, None, _c_int(tl), _c_int(H), _c_float(eps), _c_int(1), _c_int(0), None, None, None,
             None, ws.flag_ptr(ws.PART_FLAGS), _c_int(self.world), _c_int(expected), ws.flag_ptr(ws.PART_ARRIVED),
             ws.peers(ws.off_q0), ws.peers(ws.off_q1) if two else None, ws.peers(ws.off_sf0),
@@ -186,3 +207,40 @@ class FusedTp:
         N.check(rc, "afb_gemm_mxfp8_tp(gathered)")
         N.count_launch()
         return out
+
+    # -- one-shot: GEMM -> all-reduce (broadcast of the reduced bf16 tile) ------------------------------------
+    def gemm_bcast(self, x: Q.MxAct, w: Q.Fp8Weight, T: int, split_k: int, buf: int) -> None:
+        """Row-parallel GEMM whose reduced bf16 tiles land in slot ``rank`` of every rank's buffer ``buf``.
+        No flag accompanies the data: the consumer polls the slots themselves."""
+        ws = self.ws
+        M, K = x.q0.shape
+        Nn = w.out_features
+        assert Nn == ws.hidden and M == T and T <= ws.max_tokens
+        lib = N.cuda()
+        S = int(lib.afb_mx_effective_splits(_c_int(K), _c_int(max(split_k, 1))))
+        assert S <= 8
+        rc = lib.afb_gemm_mxfp8_bcast(
+            N.ptr(x.q0), N.ptr(x.q1), N.ptr(x.sf0), N.ptr(x.sf1), N.ptr(w.q), N.ptr(Q.weight_sf_atoms(w)),
+            _c_int(M), _c_int(Nn), _c_int(K), _c_int(Nn), _c_int(S), _c_int(x.terms), ws.peers(ws.off_bcast[buf]),
+            _c_int(self.world), _c_int(self.rank), N.stream_ptr())
+        N.check(rc, "afb_gemm_mxfp8_bcast")
+        N.count_launch()
+
+    def norm_bcast(self, gamma: torch.Tensor, residual: torch.Tensor, T: int, eps: float, buf: int,
+                   want_norm: bool = True):
+        """Polls the world's slots of buffer ``buf`` until every element has landed, sums them in rank order with
+        the (replicated) residual, restores the slots' sentinel, and returns (new residual [T, H] bf16, normalised rows as MX activations or None)."""
+        ws = self.ws
+        H = ws.hidden
+        parts = ws.local(ws.off_bcast[buf], self.world * T * H * 2).view(torch.bfloat16)
+        sum_out = torch.empty((T, H), dtype=torch.bfloat16, device=ws.device)
+        mx = Q.new_mx(T, H, self.terms, ws.device) if want_norm else None
+        rc = N.cuda().afb_norm_tp(
+            None, N.ptr(parts), _c_int(self.world), _c_long(T * H), _c_int(2), N.ptr(residual), None, N.ptr(gamma),
+            None, N.ptr(sum_out), None, None, _c_int(T), _c_int(H), _c_float(eps), _c_int(1), _c_int(0),
+            N.ptr(mx.q0 if mx else None), N.ptr(mx.q1 if mx else None), N.ptr(mx.sf0 if mx else None),
+            N.ptr(mx.sf1 if mx else None), None, _c_int(0), _c_int(0), None, None, None, None, None, None, _c_int(0),
+            _c_int(0), N.stream_ptr())
+        N.check(rc, "afb_norm_tp(bcast)")
+        N.count_launch()
+        return sum_out, mx

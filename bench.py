@@ -159,11 +159,11 @@ def bench_decode(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29588")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
-    if (world > 1 or args.force_fused) and args.tp_path == "fused":
+    if (world > 1 or args.force_fused) and args.tp_path in ("fused", "fused2"):
         from antfly_b200.parallel.fused import FusedTp, SymmetricWorkspace
 
         model.fused = FusedTp(SymmetricWorkspace(rank, world, torch.device("cuda", local), cfg.hidden_size,
-                                                 max_tokens=128))
+                                                 max_tokens=128), one_shot=args.tp_path == "fused")
     B, prompt_len, gen = args.batch, args.prompt_len, args.gen_len
     total = prompt_len + gen + 16
     blocks = B * ((total + 15) // 16) + 8
@@ -304,8 +304,9 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--gen-len", type=int, default=256)
-    ap.add_argument("--tp-path", default="fused", choices=["fused", "nccl"],
-                    help="tensor-parallel collectives: fused into the kernels over peer memory, or the NCCL baseline")
+    ap.add_argument("--tp-path", default="fused", choices=["fused", "fused2", "nccl"],
+                    help="tensor-parallel collectives: fused into the kernels over peer memory as one-shot "
+                         "all-reduces (fused) or as reduce-scatter + all-gather (fused2), or the NCCL baseline")
     ap.add_argument("--knn-rows", type=int, default=2_000_000, help="database rows per GPU for --workload knn")
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="debug: time one rank's shard of a tp-way split on a single GPU with no communication")

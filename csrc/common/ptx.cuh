@@ -80,6 +80,74 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------------------------
+// Thread-block clusters: distributed shared memory and the cluster barrier.  A kernel launched without a
+// cluster dimension is a cluster of one, for which these degenerate to CTA-local operations.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_num_ctas() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// Shared-window address of `local_addr` (a shared::cta address of this CTA) inside CTA `cta_rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+// Every thread of every CTA of the cluster must execute both halves (warp-converged).
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
+// Flag-free cross-GPU hand-off of bf16 rows (Lamport-style): a slot holds the sentinel 0x8000 (bf16 -0.0) in
+// every element until data lands; producers never send the sentinel, consumers poll the data and put the
+// sentinel back.  Works at any store-tearing granularity of two bytes or more because every element is checked.
+// ----------------------------------------------------------------------------------------------
+constexpr uint32_t kLamportSentinelX2 = 0x80008000u;
+__device__ __forceinline__ uint32_t lamport_clean_bf16x2(uint32_t w) {
+  if ((w & 0xFFFFu) == 0x8000u) w &= 0xFFFF0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000FFFFu;
+  return w;
+}
+// True if any 16-bit lane of w equals 0x8000 (zero-halfword test on w ^ 0x80008000).
+__device__ __forceinline__ bool lamport_pending_x2(uint32_t w) {
+  const uint32_t x = w ^ kLamportSentinelX2;
+  return ((x - 0x00010001u) & ~x & 0x80008000u) != 0u;
+}
+__device__ __forceinline__ bool lamport_pending(const uint4& u) {
+  return lamport_pending_x2(u.x) || lamport_pending_x2(u.y) || lamport_pending_x2(u.z) || lamport_pending_x2(u.w);
+}
+__device__ __forceinline__ void st_relaxed_sys_v4(void* p, const uint4& u) {
+  asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 u;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+               : "l"(p)
+               : "memory");
+  return u;
+}
+
+// ----------------------------------------------------------------------------------------------
 // Proxy fences
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -14,7 +14,8 @@
 // path on CUDA at all.
 //
 // Tensor-core path: mma.sync m16n8k16 (bf16) with ldmatrix from XOR-swizzled shared memory, K/V tiles staged
-// by cp.async (zero-filled past the end of the sequence) in a two-deep ring.
+// by cp.async (zero-filled past the end of the sequence) in a two- or three-deep ring.
+#include "../common/mxquant.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tmap.cuh"
 #include "../include/antfly_b200_noalloc.h"
@@ -36,6 +37,7 @@ struct AttnParams {
   const int* block_tables;
   int max_blocks;
   int page;
+  int page_shift;  // log2(page) when page is a power of two, else -1
   const int* q_starts;  // [B] first token row of each sequence in q / out (and k / v in contiguous mode)
   const int* q_lens;    // [B]
   const int* kv_lens;   // [B] total keys visible to the sequence (contiguous mode: = q_lens)
@@ -83,32 +85,47 @@ constexpr int kTileKeys = 64;
 template <int D, bool PAGED>
 __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* sV, const AttnParams& p, int b,
                                              int hk, int k0, int kv_len, int kv_row_start) {
+  // Each thread owns one 16-byte column chunk and every (128 / CH)-th row of the tile, so the swizzle term and
+  // the column offset are loop invariants and the per-row work is one block-table read plus a few integer ops.
   constexpr int CH = D / 8;
-  for (int idx = threadIdx.x; idx < kTileKeys * CH; idx += blockDim.x) {
-    const int row = idx / CH, ch = idx % CH;
+  constexpr int ROWS_PER_PASS = 128 / CH;
+  const int ch = threadIdx.x % CH, r0 = threadIdx.x / CH;
+  const int dst0 = r0 * D + ((ch ^ (r0 & 7)) * 8);  // ROWS_PER_PASS is a multiple of 8: row & 7 == r0 & 7
+  const int* table = PAGED ? p.block_tables + static_cast<size_t>(b) * p.max_blocks : nullptr;
+  const size_t row_elems = PAGED ? static_cast<size_t>(p.Hkv) * D : static_cast<size_t>(p.kv_stride);
+  const size_t col_off = static_cast<size_t>(hk) * D + ch * 8;
+#pragma unroll
+  for (int i = 0; i < kTileKeys / ROWS_PER_PASS; ++i) {
+    const int row = r0 + i * ROWS_PER_PASS;
     const int key = k0 + row;
     const bool valid = key < kv_len;
-    const __nv_bfloat16 *srcK, *srcV;
+    const int kk = valid ? key : 0;
+    size_t off;
     if (PAGED) {
-      const int kk = valid ? key : 0;
-      const int blk = p.block_tables[static_cast<size_t>(b) * p.max_blocks + kk / p.page];
-      const size_t off = ((static_cast<size_t>(blk) * p.page + kk % p.page) * p.Hkv + hk) * D + ch * 8;
-      srcK = p.k_cache + off;
-      srcV = p.v_cache + off;
+      int blk, in_page;
+      if (p.page_shift >= 0) {
+        blk = table[kk >> p.page_shift];
+        in_page = kk & (p.page - 1);
+        off = ((static_cast<size_t>(blk) << p.page_shift) + in_page) * row_elems + col_off;
+      } else {
+        blk = table[kk / p.page];
+        in_page = kk % p.page;
+        off = (static_cast<size_t>(blk) * p.page + in_page) * row_elems + col_off;
+      }
     } else {
-      const size_t off = static_cast<size_t>(kv_row_start + (valid ? key : 0)) * p.kv_stride + hk * D + ch * 8;
-      srcK = p.k + off;
-      srcV = p.v + off;
+      off = static_cast<size_t>(kv_row_start + kk) * row_elems + col_off;
     }
-    const int dst = row * D + ((ch ^ (row & 7)) * 8);
-    cp_async_16(sK + dst, srcK, valid ? 16 : 0);
-    cp_async_16(sV + dst, srcV, valid ? 16 : 0);
+    const int dst = dst0 + i * ROWS_PER_PASS * D;
+    cp_async_16(sK + dst, (PAGED ? p.k_cache : p.k) + off, valid ? 16 : 0);
+    cp_async_16(sV + dst, (PAGED ? p.v_cache : p.v) + off, valid ? 16 : 0);
   }
 }
 
 // SPLIT_KEYS = false: each of the 4 warps owns 16 query rows and all 64 keys of a tile (prefill / encoder).
 // SPLIT_KEYS = true : all warps share the same <= 16 query rows and each owns 16 keys of a tile (decode).
-template <int D, bool PAGED, bool SPLIT_KEYS>
+// STAGES: depth of the K/V tile ring (2, or 3 for small grids where one or two CTAs per SM must cover the DRAM
+// latency by themselves).
+template <int D, bool PAGED, bool SPLIT_KEYS, int STAGES>
 __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   constexpr int NKB = SPLIT_KEYS ? 2 : 8;  // 8-key blocks per warp per tile
   constexpr int ND = D / 8;                // 8-wide output blocks
@@ -182,22 +199,26 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   float l_run[2] = {0.0f, 0.0f};
 
   constexpr int TILE_ELEMS = kTileKeys * D;
-  if (ntiles > 0) {
-    load_kv_tile<D, PAGED>(sKV, sKV + TILE_ELEMS, p, b, hk, t_begin * kTileKeys, kv_len, q_start);
+  // One commit group per tile slot (empty past the end) keeps the group count uniform for wait_group.
+#pragma unroll
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+    if (s0 < ntiles) {
+      __nv_bfloat16* nK = sKV + s0 * 2 * TILE_ELEMS;
+      load_kv_tile<D, PAGED>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + s0) * kTileKeys, kv_len, q_start);
+    }
     cp_async_commit();
   }
   for (int it = 0; it < ntiles; ++it) {
-    const int stage = it & 1;
+    const int stage = it % STAGES;
     __nv_bfloat16* sK = sKV + stage * 2 * TILE_ELEMS;
     __nv_bfloat16* sV = sK + TILE_ELEMS;
-    if (it + 1 < ntiles) {
-      __nv_bfloat16* nK = sKV + (stage ^ 1) * 2 * TILE_ELEMS;
-      load_kv_tile<D, PAGED>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + 1) * kTileKeys, kv_len, q_start);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    if (it + STAGES - 1 < ntiles) {
+      __nv_bfloat16* nK = sKV + ((it + STAGES - 1) % STAGES) * 2 * TILE_ELEMS;
+      load_kv_tile<D, PAGED>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + STAGES - 1) * kTileKeys, kv_len,
+                             q_start);
     }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
 
     const int k0 = (t_begin + it) * kTileKeys;
@@ -222,50 +243,66 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
     }
 
     // ---- mask + online softmax ----
+    // Tiles that lie wholly inside every row's visible range (the common case in decode) skip the mask; rows past
+    // rows_total then hold finite garbage that is never stored.
+    const int row_lo = tile_row0 + (SPLIT_KEYS ? 0 : warp * 16);
+    const int min_qpos = pos_off + row_lo / G;
+    const int max_qpos = pos_off + (min(rows_total, row_lo + 16) - 1) / G;
+    const bool full_tile = (k0 + kTileKeys <= kv_len) && (!p.causal || k0 + kTileKeys - 1 <= min_qpos) &&
+                           (p.window <= 0 || k0 > max_qpos - p.window);
     float mx[2] = {-INFINITY, -INFINITY};
+    if (!full_tile) {
+#pragma unroll
+      for (int nb = 0; nb < NKB; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = e >> 1;
+          const int key = k0 + wkey0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+          const int qpos = pos_off + r_pos[h];
+          bool ok = r_ok[h] && key < kv_len;
+          if (p.causal) ok = ok && key <= qpos;
+          if (p.window > 0) ok = ok && key > qpos - p.window;
+          if (!ok) s[nb][e] = -INFINITY;
+        }
+      }
+    }
 #pragma unroll
     for (int nb = 0; nb < NKB; ++nb) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h = e >> 1;
-        const int key = k0 + wkey0 + nb * 8 + 2 * (lane & 3) + (e & 1);
-        const int qpos = pos_off + r_pos[h];
-        bool ok = r_ok[h] && key < kv_len;
-        if (p.causal) ok = ok && key <= qpos;
-        if (p.window > 0) ok = ok && key > qpos - p.window;
-        const float val = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
-        s[nb][e] = val;
-        mx[h] = fmaxf(mx[h], val);
-      }
+      mx[0] = fmaxf(mx[0], fmaxf(s[nb][0], s[nb][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[nb][2], s[nb][3]));
     }
     float alpha[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      mx[h] *= p.scale_log2;  // the softmax scale is positive: max and scaling commute; -inf stays -inf
       const float m_new = fmaxf(m_run[h], mx[h]);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
       alpha[h] = exp2f(m_run[h] - m_use);  // m_run = -inf -> 0
       m_run[h] = m_new;
       l_run[h] *= alpha[h];
-      mx[h] = m_use;
+      mx[h] = -m_use;
     }
     uint32_t pf[NKB / 2][4];
 #pragma unroll
     for (int nb = 0; nb < NKB; ++nb) {
-      const float p0 = exp2f(s[nb][0] - mx[0]);
-      const float p1 = exp2f(s[nb][1] - mx[0]);
-      const float p2 = exp2f(s[nb][2] - mx[1]);
-      const float p3 = exp2f(s[nb][3] - mx[1]);
+      const float p0 = exp2f(fmaf(s[nb][0], p.scale_log2, mx[0]));
+      const float p1 = exp2f(fmaf(s[nb][1], p.scale_log2, mx[0]));
+      const float p2 = exp2f(fmaf(s[nb][2], p.scale_log2, mx[1]));
+      const float p3 = exp2f(fmaf(s[nb][3], p.scale_log2, mx[1]));
       l_run[0] += p0 + p1;
       l_run[1] += p2 + p3;
       pf[nb >> 1][(nb & 1) * 2 + 0] = pack_bf16x2(p0, p1);
       pf[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16x2(p2, p3);
     }
+    // The running maximum settles after the first tiles; skip the accumulator rescale when no row of the warp moved.
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-    for (int i = 0; i < ND; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      for (int i = 0; i < ND; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
     }
 
     // ---- O += P V ----
@@ -357,43 +394,82 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   }
 }
 
-// Merge split-KV partials: out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max).
-__global__ void attn_merge_kernel(const float* part_o, const float* part_lse, __nv_bfloat16* out, long out_stride,
-                                  int rows /* T*Hq */, int Hq, int D, int splits) {
-  const int row = blockIdx.x;
+// Merge split-KV partials: out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max).  Each thread owns 4 adjacent
+// columns of one (token, head) row; 128-thread CTAs cover 512 / D rows.  When q0 is given the merged row is also
+// written as MX fp8 activations of the [T, Hq * D] matrix the output projection consumes, so no separate
+// quantisation pass runs between attention and that GEMM; `out` may then be null.
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float* part_o, const float* part_lse,
+                                                         __nv_bfloat16* out, long out_stride, int rows /* T*Hq */,
+                                                         int Hq, int D, int splits, uint8_t* q0, uint8_t* q1,
+                                                         uint8_t* sf0, uint8_t* sf1) {
   griddep_launch();
   griddep_wait();
+  const int tpr = D >> 2;  // threads per row
+  const int row_raw = blockIdx.x * (128 / tpr) + threadIdx.x / tpr;
+  const bool live = row_raw < rows;
+  const int row = live ? row_raw : rows - 1;
+  const int c = (threadIdx.x % tpr) * 4;
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_lse[static_cast<size_t>(s) * rows + row]);
-  const int tok = row / Hq, head = row % Hq;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    float acc = 0.0f, den = 0.0f;
-    if (M != -INFINITY) {
-      for (int s = 0; s < splits; ++s) {
-        const float f = exp2f(part_lse[static_cast<size_t>(s) * rows + row] - M);
-        den += f;
-        acc += f * part_o[(static_cast<size_t>(s) * rows + row) * D + c];
-      }
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, den = 0.0f;
+  if (M != -INFINITY) {
+    for (int s = 0; s < splits; ++s) {
+      const float f = exp2f(part_lse[static_cast<size_t>(s) * rows + row] - M);
+      const float4 o = *reinterpret_cast<const float4*>(part_o + (static_cast<size_t>(s) * rows + row) * D + c);
+      den += f;
+      acc[0] += f * o.x; acc[1] += f * o.y; acc[2] += f * o.z; acc[3] += f * o.w;
     }
-    out[static_cast<size_t>(tok) * out_stride + head * D + c] = __float2bfloat16(den > 0.0f ? acc / den : 0.0f);
+  }
+  const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = acc[j] * inv;
+  const int tok = row / Hq, head = row % Hq;
+  if (out && live) {
+    uint2 o;
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(tok) * out_stride + head * D + c) = o;
+  }
+  if (q0) {
+    // Quantise what the bf16 path would have produced, so both routes feed the GEMM the same values.
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(__float2bfloat16(v[j]));
+    mx_quantize4_store(v, tok, head * D + c, Hq * D, q0, q1, sf0, sf1, live);
   }
 }
 
-template <int D, bool PAGED, bool SPLIT_KEYS>
-int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
-  const int smem_tiles = 2 * 2 * kTileKeys * D * 2;
+template <int D, bool PAGED, bool SPLIT_KEYS, int STAGES>
+int launch_attn_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  const int smem_tiles = STAGES * 2 * kTileKeys * D * 2;
   const int smem_merge = SPLIT_KEYS ? (4 * 16 * D + 128) * 4 : 0;
   const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
   static bool configured = false;
   if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(flash_attn_kernel<D, PAGED, SPLIT_KEYS>,
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(flash_attn_kernel<D, PAGED, SPLIT_KEYS, STAGES>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
+  AFB_CHECK_CUDA(launch_pdl(flash_attn_kernel<D, PAGED, SPLIT_KEYS, STAGES>, grid, dim3(128), smem, stream, p));
+  return 0;
+}
+
+template <int D, bool PAGED, bool SPLIT_KEYS>
+int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
   const int rows_per_cta = SPLIT_KEYS ? 16 : 64;
   dim3 grid((max_rows + rows_per_cta - 1) / rows_per_cta, p.Hkv, B * p.num_splits);
-  AFB_CHECK_CUDA(launch_pdl(flash_attn_kernel<D, PAGED, SPLIT_KEYS>, grid, dim3(128), smem, stream, p));
-  return 0;
+  if constexpr (SPLIT_KEYS && PAGED) {
+    // A decode grid that leaves at most two CTAs per SM gets a deeper ring.
+    static int sms = 0;
+    if (!sms) {
+      int dev = 0;
+      AFB_CHECK_CUDA(cudaGetDevice(&dev));
+      AFB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const long ctas = static_cast<long>(grid.x) * grid.y * grid.z;
+    if (ctas <= 2L * sms) return launch_attn_s<D, PAGED, SPLIT_KEYS, 3>(p, grid, stream);
+  }
+  return launch_attn_s<D, PAGED, SPLIT_KEYS, 2>(p, grid, stream);
 }
 
 }  // namespace afb
@@ -405,11 +481,31 @@ extern "C" {
 // split_keys != 0 selects the decode organisation (<= 16 rows per (sequence, KV head) per CTA);
 // num_splits > 1 additionally splits the KV range across CTAs and needs part_o / part_lse scratch.
 // max_q_len: the largest q_lens[b] (host knowledge, sizes the grid).
+int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v, long kv_stride,
+                     const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks, int page,
+                     const int* q_starts, const int* q_lens, const int* kv_lens, void* out, long out_stride,
+                     float* part_o, float* part_lse, int B, int T, int Hq, int Hkv, int D, int max_q_len, int causal,
+                     int window, float scale, int paged, int split_keys, int num_splits, void* mx_q0, void* mx_q1,
+                     void* mx_sf0, void* mx_sf1, cudaStream_t stream);
+
 int afb_attention(const void* q, long q_stride, const void* k, const void* v, long kv_stride, const void* k_cache,
                   const void* v_cache, const int* block_tables, int max_blocks, int page, const int* q_starts,
                   const int* q_lens, const int* kv_lens, void* out, long out_stride, float* part_o, float* part_lse,
                   int B, int T, int Hq, int Hkv, int D, int max_q_len, int causal, int window, float scale,
                   int paged, int split_keys, int num_splits, cudaStream_t stream) {
+  return afb_attention_mx(q, q_stride, k, v, kv_stride, k_cache, v_cache, block_tables, max_blocks, page, q_starts,
+                          q_lens, kv_lens, out, out_stride, part_o, part_lse, B, T, Hq, Hkv, D, max_q_len, causal,
+                          window, scale, paged, split_keys, num_splits, nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+// As afb_attention; with num_splits > 1 and mx_q0 given, the merge kernel also emits the context rows as MX fp8
+// activations [T, Hq * D] (mx_q1 / mx_sf1 null: one term) and `out` may be null.
+int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v, long kv_stride,
+                     const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks, int page,
+                     const int* q_starts, const int* q_lens, const int* kv_lens, void* out, long out_stride,
+                     float* part_o, float* part_lse, int B, int T, int Hq, int Hkv, int D, int max_q_len, int causal,
+                     int window, float scale, int paged, int split_keys, int num_splits, void* mx_q0, void* mx_q1,
+                     void* mx_sf0, void* mx_sf1, cudaStream_t stream) {
   using namespace afb;
   if (B <= 0 || T <= 0) return 0;
   if (Hq % Hkv != 0 || (D != 64 && D != 128)) {
@@ -417,14 +513,26 @@ int afb_attention(const void* q, long q_stride, const void* k, const void* v, lo
                    Hkv);
     return -1;
   }
-  if ((q_stride & 7) || (kv_stride & 7) || (out_stride & 1)) {
+  if ((q_stride & 7) || (kv_stride & 7) || (out_stride & 3)) {
     set_last_error("afb_attention: q/kv strides must be multiples of 8 elements");
+    return -1;
+  }
+  if (!(scale > 0.0f)) {
+    set_last_error("afb_attention: the softmax scale must be positive");
     return -1;
   }
   if (num_splits < 1) num_splits = 1;
   if (!split_keys) num_splits = 1;
   if (num_splits > 1 && (!part_o || !part_lse)) {
     set_last_error("afb_attention: num_splits > 1 needs partial buffers");
+    return -1;
+  }
+  if (mx_q0 && (num_splits < 2 || (Hq * D) % 128 != 0 || !mx_sf0)) {
+    set_last_error("afb_attention: MX output needs num_splits > 1 and Hq * D a multiple of 128");
+    return -1;
+  }
+  if (!out && !mx_q0) {
+    set_last_error("afb_attention: no output buffer");
     return -1;
   }
   AttnParams p;
@@ -434,6 +542,11 @@ int afb_attention(const void* q, long q_stride, const void* k, const void* v, lo
   p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache);
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.page = page;
+  p.page_shift = -1;
+  if (page > 0 && (page & (page - 1)) == 0) {
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page) ++p.page_shift;
+  }
   p.q_starts = q_starts; p.q_lens = q_lens; p.kv_lens = kv_lens;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
   p.part_o = part_o; p.part_lse = part_lse;
@@ -455,9 +568,12 @@ int afb_attention(const void* q, long q_stride, const void* k, const void* v, lo
 #undef AFB_ATTN_DISPATCH
   if (rc) return rc;
   if (num_splits > 1) {
-    AFB_CHECK_CUDA(launch_pdl(attn_merge_kernel, dim3(T * Hq), dim3(D <= 64 ? 64 : 128), 0, stream,
+    const int rows_per_cta = 128 / (D / 4);
+    AFB_CHECK_CUDA(launch_pdl(attn_merge_kernel, dim3((T * Hq + rows_per_cta - 1) / rows_per_cta), dim3(128), 0, stream,
                               static_cast<const float*>(part_o), static_cast<const float*>(part_lse), p.out, out_stride,
-                              T * Hq, Hq, D, num_splits));
+                              T * Hq, Hq, D, num_splits, reinterpret_cast<uint8_t*>(mx_q0),
+                              reinterpret_cast<uint8_t*>(mx_q1), reinterpret_cast<uint8_t*>(mx_sf0),
+                              reinterpret_cast<uint8_t*>(mx_sf1)));
   }
   return 0;
 }

@@ -21,6 +21,7 @@
 //   warp 0      TMA producer      warp 1   tcgen05.cp + tcgen05.mma issue      warps 2..5  epilogue
 //
 // Scale-factor atom (512 B, covers 128 rows x 4 K-blocks): byte (r % 32) * 16 + (r / 32) * 4 + kblock.
+#include "../common/mxquant.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tmap.cuh"
 
@@ -47,7 +48,7 @@ struct MxParams {
   int M, N, K;
   int ldc, ldr;
   int act;
-  int mode;  // 0 bf16 out, 1 fp32 partials, 2 swiglu
+  int mode;  // 0 bf16 out, 1 fp32 partials, 2 swiglu, 3 push partial tiles to owner ranks, 4 reduce + broadcast
   int chunks_per_split;
   int k_chunks;
   // ---- tensor-parallel fused collectives (unused when world == 0) ----
@@ -63,6 +64,13 @@ struct MxParams {
   int* x_ready;
   int x_expected;
   int* x_consumed;
+  // mode 4 (GEMM -> one-shot all-reduce): the split-K CTAs of a tile form a thread-block cluster (1, 1, splits).
+  // Each stages its fp32 slice in its own shared memory; after a cluster barrier every CTA sums one share of the
+  // tile's rows over all slices (distributed shared memory, slice order), rounds to bf16 and stores the rows into
+  // slot `my_rank` of every rank's [world][M][ldc] bf16 buffer (peer_parts reinterpreted).  There is no flag and no
+  // fence: the slots hold a sentinel (bf16 -0.0, which the producer never sends: a computed -0.0 goes out as +0.0)
+  // until the data lands, and the consumer polls the data itself and restores the sentinel after reading
+  // (Lamport-style).  The consumer sums the world slots in rank order, so every rank computes bit-identical sums.
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -294,6 +302,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
               }
             }
           }
+        } else if (p.mode == 4) {
+          // Stage the fp32 slice [BT][128] in the (now idle) pipeline stages for the cluster-wide reduction.
+          float* stile = reinterpret_cast<float*>(smem);
+#pragma unroll
+          for (int j = 0; j < CH; ++j) stile[(c + j) * 128 + q * 32 + lane] = v[j];
         } else if (p.mode == 1) {
           float* op = reinterpret_cast<float*>(p.out) + static_cast<size_t>(blockIdx.z) * p.M * p.ldc;
           if (n < p.N) {
@@ -346,6 +359,53 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (p.mode == 4) {
+    // All slices of the tile are staged: cluster barrier, then this CTA reduces and publishes its share of rows.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp >= 2) {
+      const int S = static_cast<int>(gridDim.z);  // == cluster size; cluster rank == blockIdx.z
+      const int et = threadIdx.x - 64;
+      const int cg = et & 15, tr = et >> 4;  // 16 column groups of 8, 8 token rows per pass
+      const int nn = n0 + cg * 8;
+      const int valid = min(BT, p.M - t0);
+      const int rows_per = (valid + S - 1) / S;
+      const int r_lo = static_cast<int>(blockIdx.z) * rows_per;
+      const int r_hi = min(valid, r_lo + rows_per);
+      const uint32_t stile = smem_u32(smem);
+      if (nn < p.N && num_c > 0) {
+        for (int r = r_lo + tr; r < r_hi; r += 8) {
+          const uint32_t off = static_cast<uint32_t>(r * 128 + cg * 8) * 4;
+          float4 lo[8], hi[8];
+#pragma unroll
+          for (int z = 0; z < 8; ++z) {
+            if (z < S) {
+              const uint32_t ra = cluster_map_shared(stile + off, static_cast<uint32_t>(z));
+              lo[z] = ld_shared_cluster_f4(ra);
+              hi[z] = ld_shared_cluster_f4(ra + 16);
+            }
+          }
+          float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+          for (int z = 0; z < 8; ++z) {
+            if (z < S) {
+              a[0] += lo[z].x; a[1] += lo[z].y; a[2] += lo[z].z; a[3] += lo[z].w;
+              a[4] += hi[z].x; a[5] += hi[z].y; a[6] += hi[z].z; a[7] += hi[z].w;
+            }
+          }
+          uint4 u;
+          u.x = lamport_clean_bf16x2(pack_bf16x2(a[0], a[1])); u.y = lamport_clean_bf16x2(pack_bf16x2(a[2], a[3]));
+          u.z = lamport_clean_bf16x2(pack_bf16x2(a[4], a[5])); u.w = lamport_clean_bf16x2(pack_bf16x2(a[6], a[7]));
+          const size_t goff = (static_cast<size_t>(p.my_rank) * p.M + t0 + r) * p.ldc + nn;
+          for (int o = 0; o < p.world; ++o)
+            st_relaxed_sys_v4(reinterpret_cast<__nv_bfloat16*>(p.peer_parts[o]) + goff, u);
+        }
+      }
+    }
+    // No CTA may exit (and give up its shared memory) while a peer still reads its slice.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -363,6 +423,11 @@ int launch_mx(const void* W, const void* X0, const void* X1, MxParams p, int spl
     configured = true;
   }
   dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
+  if (p.mode == 4 && splits > 1) {
+    AFB_CHECK_CUDA(launch_pdl_cluster(gemm_mxfp8_kernel<BT, STAGES, TERMS>, grid, dim3(192), dim3(1, 1, splits),
+                                      L::kTotal, stream, tw, tx0, tx1, p));
+    return 0;
+  }
   AFB_CHECK_CUDA(launch_pdl(gemm_mxfp8_kernel<BT, STAGES, TERMS>, grid, dim3(192), L::kTotal, stream, tw, tx0, tx1, p));
   return 0;
 }
@@ -371,67 +436,53 @@ int launch_mx(const void* W, const void* X0, const void* X1, MxParams p, int spl
 // Activation quantiser: bf16 [T, K] -> MX fp8 terms (e4m3 bytes [T, K]) + scale-factor atoms.
 // One warp per (token, 128-wide K chunk ... ) : each lane owns 4 consecutive elements, 8 lanes share a 32-block.
 // ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t e8m0_for_amax(float amax) {
-  // Smallest power of two s with amax / s <= 448; e4m3 max is 448 = 1.75 * 2^8.
-  if (!(amax > 0.0f)) return 127u - 8u;
-  int e;
-  const float m = frexpf(amax, &e);  // amax = m * 2^e, m in [0.5, 1)
-  // amax / 2^s <= 448  <=>  s >= log2(amax) - log2(448); ceil() of that:
-  int s = e - 9 + ((m > 0.875f) ? 1 : 0);  // 448 = 0.875 * 2^9
-  s = max(-127, min(127, s));
-  return static_cast<uint32_t>(s + 127);
-}
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
-  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-}
-
-__device__ __forceinline__ void unpack_e4m3x4(uint32_t v, float (&o)[4]) {
-  const float2 a = e4m3x2_to_float2(static_cast<uint16_t>(v & 0xFFFF));
-  const float2 b = e4m3x2_to_float2(static_cast<uint16_t>(v >> 16));
-  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
-}
-
+// Threads past K / 4 do not exist: the block has exactly K / 4 threads (K a multiple of 128, so whole warps) or
+// 1024, and the loop bound is uniform per lane octet.
 __global__ void quantize_mx_kernel(const __nv_bfloat16* x, long ldx, uint8_t* q0, uint8_t* q1, uint8_t* sf0,
                                    uint8_t* sf1, int T, int K) {
   const int t = blockIdx.x;
-  const int k_chunks = K / 128;
   griddep_launch();
   griddep_wait();
   for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
     const uint2 u = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * ldx + i);
     const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-    float v[4] = {a.x, a.y, b.x, b.y};
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const uint32_t e0 = e8m0_for_amax(amax);
-    const float inv0 = __uint_as_float((254u - e0) << 23);  // 2^-(e0-127)
-    const uint32_t p0 = pack_e4m3x4(v[0] * inv0, v[1] * inv0, v[2] * inv0, v[3] * inv0);
-    *reinterpret_cast<uint32_t*>(q0 + static_cast<size_t>(t) * K + i) = p0;
-    const int kb = i / 32, chunk = kb / 4, j = kb % 4;
-    const size_t sf_off = (static_cast<size_t>(t / 128) * k_chunks + chunk) * 512 + ((t % 128) % 32) * 16 +
-                          ((t % 128) / 32) * 4 + j;
-    if ((threadIdx.x & 7) == 0) sf0[sf_off] = static_cast<uint8_t>(e0);
-    if (q1) {
-      float d[4];
-      unpack_e4m3x4(p0, d);
-      const float s0 = __uint_as_float(e0 << 23);
-      float r[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) r[c] = v[c] - d[c] * s0;
-      float rmax = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
-      const uint32_t e1 = e8m0_for_amax(rmax);
-      const float inv1 = __uint_as_float((254u - e1) << 23);
-      *reinterpret_cast<uint32_t*>(q1 + static_cast<size_t>(t) * K + i) =
-          pack_e4m3x4(r[0] * inv1, r[1] * inv1, r[2] * inv1, r[3] * inv1);
-      if ((threadIdx.x & 7) == 0) sf1[sf_off] = static_cast<uint8_t>(e1);
+    const float v[4] = {a.x, a.y, b.x, b.y};
+    mx_quantize4_store(v, t, i, K, q0, q1, sf0, sf1, true);
+  }
+}
+
+// SwiGLU over the fp32 split-K partial slices of an interleaved gate/up GEMM (column 2c = gate, 2c + 1 = up of
+// output c), then MX quantisation: the consumer of a split gate/up GEMM and the producer of the down GEMM's
+// activations in one pass.  parts: [S][T][ldp] fp32; bias (optional) bf16 [2F] in the same interleaved order.
+__global__ void swiglu_quantize_mx_kernel(const float* parts, int S, long slice_stride, long ldp,
+                                          const __nv_bfloat16* bias, uint8_t* q0, uint8_t* q1, uint8_t* sf0,
+                                          uint8_t* sf1, __nv_bfloat16* y, long ldy, int T, int F) {
+  const int t = blockIdx.x;
+  griddep_launch();
+  griddep_wait();
+  for (int i = threadIdx.x * 4; i < F; i += blockDim.x * 4) {
+    float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const float* src = parts + static_cast<size_t>(t) * ldp + 2 * i;
+    for (int s = 0; s < S; ++s) {
+      const float4 lo = *reinterpret_cast<const float4*>(src + s * slice_stride);
+      const float4 hi = *reinterpret_cast<const float4*>(src + s * slice_stride + 4);
+      a[0] += lo.x; a[1] += lo.y; a[2] += lo.z; a[3] += lo.w;
+      a[4] += hi.x; a[5] += hi.y; a[6] += hi.z; a[7] += hi.w;
     }
+    if (bias) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) a[c] += __bfloat162float(bias[2 * i + c]);
+    }
+    float v[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) v[c] = silu(a[2 * c]) * a[2 * c + 1];
+    if (y) {
+      uint2 o;
+      o.x = pack_bf16x2(v[0], v[1]);
+      o.y = pack_bf16x2(v[2], v[3]);
+      *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * ldy + i) = o;
+    }
+    if (q0) mx_quantize4_store(v, t, i, F, q0, q1, sf0, sf1, true);
   }
 }
 
@@ -446,6 +497,9 @@ int afb_gemm_mxfp8_tp(const void* X0, const void* X1, const void* sfx0, const vo
                       int ldr, int act, int mode, int split_k, int terms, void* const* peer_parts,
                       void* const* peer_part_flags, int world, int my_rank, int tokens_per_rank, int slices,
                       int* x_ready, int x_expected, int* x_consumed, cudaStream_t stream);
+int afb_gemm_mxfp8_bcast(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8,
+                         const void* sfw, int M, int N, int K, int ldc, int split_k, int terms,
+                         void* const* peer_bufs, int world, int my_rank, cudaStream_t stream);
 
 int afb_gemm_mxfp8(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8, const void* sfw,
                    void* out, const void* bias, const void* residual, int M, int N, int K, int ldc, int ldr, int act,
@@ -506,6 +560,45 @@ int afb_gemm_mxfp8_tp(const void* X0, const void* X1, const void* sfx0, const vo
   return launch_mx<128, 5, 1>(W8, X0, X1, p, split_k, stream);
 }
 
+// Row-parallel GEMM whose reduced bf16 tile is broadcast to every rank (one-shot all-reduce; mode 4 above).
+// peer_bufs[o]: rank o's bf16 [world][M][ldc] slot buffer, holding the sentinel 0x8000 wherever no data is
+// pending (the consuming norm kernel restores it).  split_k <= 8 (the portable cluster size).
+int afb_gemm_mxfp8_bcast(const void* X0, const void* X1, const void* sfx0, const void* sfx1, const void* W8,
+                         const void* sfw, int M, int N, int K, int ldc, int split_k, int terms,
+                         void* const* peer_bufs, int world, int my_rank, cudaStream_t stream) {
+  using namespace afb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 128 || (N & 15) || (ldc & 7) || M > 128 || world < 1 || world > 8) {
+    set_last_error("afb_gemm_mxfp8_bcast: needs K %% 128 == 0, N %% 16 == 0, ldc %% 8 == 0, M <= 128, 1..8 ranks");
+    return -1;
+  }
+  const int k_chunks = K / 128;
+  if (split_k < 1) split_k = 1;
+  if (split_k > k_chunks) split_k = k_chunks;
+  const int per = (k_chunks + split_k - 1) / split_k;
+  split_k = (k_chunks + per - 1) / per;
+  if (split_k > 8) {
+    set_last_error("afb_gemm_mxfp8_bcast: at most 8 K splits (one thread-block cluster per tile)");
+    return -1;
+  }
+  MxParams p = {};
+  p.sfw = reinterpret_cast<const uint8_t*>(sfw);
+  p.sfx0 = reinterpret_cast<const uint8_t*>(sfx0);
+  p.sfx1 = reinterpret_cast<const uint8_t*>(sfx1);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.mode = 4;
+  p.chunks_per_split = per; p.k_chunks = k_chunks;
+  p.world = world; p.my_rank = my_rank;
+  for (int o = 0; o < world; ++o) p.peer_parts[o] = reinterpret_cast<float*>(peer_bufs[o]);
+  if (terms == 2) {
+    if (M <= 32) return launch_mx<32, 4, 2>(W8, X0, X1, p, split_k, stream);
+    if (M <= 64) return launch_mx<64, 3, 2>(W8, X0, X1, p, split_k, stream);
+    return launch_mx<128, 4, 2>(W8, X0, X1, p, split_k, stream);
+  }
+  if (M <= 32) return launch_mx<32, 5, 1>(W8, X0, X1, p, split_k, stream);
+  if (M <= 64) return launch_mx<64, 4, 1>(W8, X0, X1, p, split_k, stream);
+  return launch_mx<128, 5, 1>(W8, X0, X1, p, split_k, stream);
+}
+
 int afb_mx_effective_splits(int K, int split_k) {
   const int k_chunks = K / 128;
   if (split_k < 1) split_k = 1;
@@ -529,6 +622,25 @@ int afb_quantize_mx(const void* x, long ldx, void* q0, void* q1, void* sf0, void
                             reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<uint8_t*>(q0),
                             reinterpret_cast<uint8_t*>(q1), reinterpret_cast<uint8_t*>(sf0),
                             reinterpret_cast<uint8_t*>(sf1), T, K));
+  return 0;
+}
+
+// fp32 partial slices [S, T, 2F] of an interleaved gate/up GEMM -> SwiGLU -> MX fp8 terms [T, F] (+ scale atoms)
+// and / or bf16 y [T, F].  F must be a multiple of 128; ldp a multiple of 4.
+int afb_swiglu_quantize_mx(const float* parts, int S, long slice_stride, long ldp, const void* bias, void* q0,
+                           void* q1, void* sf0, void* sf1, void* y, long ldy, int T, int F, cudaStream_t stream) {
+  using namespace afb;
+  if (T <= 0) return 0;
+  if (F % 128 || (ldp & 3) || (slice_stride & 3) || (ldy & 3) || S < 1) {
+    set_last_error("afb_swiglu_quantize_mx: F must be a multiple of 128 and pitches of 4 (F=%d)", F);
+    return -1;
+  }
+  int threads = F / 4;
+  if (threads > 1024) threads = 1024;
+  AFB_CHECK_CUDA(launch_pdl(swiglu_quantize_mx_kernel, dim3(T), dim3(threads), 0, stream, parts, S, slice_stride, ldp,
+                            reinterpret_cast<const __nv_bfloat16*>(bias), reinterpret_cast<uint8_t*>(q0),
+                            reinterpret_cast<uint8_t*>(q1), reinterpret_cast<uint8_t*>(sf0),
+                            reinterpret_cast<uint8_t*>(sf1), reinterpret_cast<__nv_bfloat16*>(y), ldy, T, F));
   return 0;
 }
 

@@ -23,6 +23,8 @@ struct NormParams {
   float* y_f32;                   // optional fp32 copy of the normalised output
   int rows, H, num_partials;
   long partial_stride;            // elements between partial slices
+  int partials_bf16;              // 0: fp32 slices; 1: bf16 slices; 2: bf16 cross-GPU slots handed off Lamport-style
+                                  // (poll each element against the sentinel, restore the sentinel after reading)
   float eps;
   int rms;                        // 1: RMSNorm, 0: LayerNorm
   int gamma_plus_one;             // 1: scale by (1 + gamma) (Gemma convention)
@@ -151,10 +153,44 @@ __global__ void norm_kernel(NormParams p) {
       float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
       v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
     }
-    for (int s = 0; s < p.num_partials; ++s) {
-      const float4* pp = reinterpret_cast<const float4*>(p.partials + s * p.partial_stride + base + i);
-      float4 a = pp[0], b = pp[1];
-      v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+    if (p.partials_bf16 == 2) {
+      // One-shot all-reduce, consumer side: the slots of all source ranks are polled together (one round trip
+      // when the data is already there), each bounded; then summed in rank order.
+      __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(const_cast<float*>(p.partials));
+      uint4 u[8];
+      unsigned pending = (1u << p.num_partials) - 1u;
+      for (uint32_t it = 0; it < AFB_SPIN_LIMIT && pending; ++it) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (pending & (1u << s)) u[s] = ld_relaxed_sys_v4(pb + s * p.partial_stride + base + i);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if ((pending & (1u << s)) && !lamport_pending(u[s])) pending &= ~(1u << s);
+        if (pending && it > 16) __nanosleep(20);
+      }
+      if (pending) status_set(kStatusPeerFlagTimeout);
+      const uint4 sentinel = make_uint4(kLamportSentinelX2, kLamportSentinelX2, kLamportSentinelX2, kLamportSentinelX2);
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < p.num_partials) {
+          *reinterpret_cast<uint4*>(pb + s * p.partial_stride + base + i) = sentinel;
+          float2 a = unpack_bf16x2(u[s].x), b = unpack_bf16x2(u[s].y), c = unpack_bf16x2(u[s].z), d = unpack_bf16x2(u[s].w);
+          v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+        }
+      }
+    } else if (p.partials_bf16) {
+      const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(p.partials);
+      for (int s = 0; s < p.num_partials; ++s) {
+        const uint4 u = *reinterpret_cast<const uint4*>(pb + s * p.partial_stride + base + i);
+        float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        v[0] += a.x; v[1] += a.y; v[2] += b.x; v[3] += b.y; v[4] += c.x; v[5] += c.y; v[6] += d.x; v[7] += d.y;
+      }
+    } else {
+      for (int s = 0; s < p.num_partials; ++s) {
+        const float4* pp = reinterpret_cast<const float4*>(p.partials + s * p.partial_stride + base + i);
+        float4 a = pp[0], b = pp[1];
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
     }
     if (p.bias) {
       uint4 u = *reinterpret_cast<const uint4*>(p.bias + i);
@@ -455,7 +491,8 @@ static int norm_threads(int H) {
 
 extern "C" {
 
-int afb_norm_tp(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
+int afb_norm_tp(const void* x, const void* partials, int num_partials, long partial_stride, int partials_bf16,
+                const void* residual,
                 const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
                 int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
                 int* wait_flags, int wait_n, int wait_expected, int* wait_arrived, void* const* peer_q0,
@@ -466,14 +503,16 @@ int afb_norm(const void* x, const float* partials, int num_partials, long partia
              const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
              int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
              cudaStream_t stream) {
-  return afb_norm_tp(x, partials, num_partials, partial_stride, residual, bias, gamma, beta, sum_out, y, y_f32, rows,
+  return afb_norm_tp(x, partials, num_partials, partial_stride, 0, residual, bias, gamma, beta, sum_out, y, y_f32, rows,
                      H, eps, rms, gamma_plus_one, q0, q1, sf0, sf1, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr,
                      nullptr, nullptr, 0, 0, stream);
 }
 
 // Tensor-parallel form: optional wait on per-source arrival counters before reducing `partials` (the
-// reduce-scatter half), optional push of the MX output row to every rank (the all-gather half).
-int afb_norm_tp(const void* x, const float* partials, int num_partials, long partial_stride, const void* residual,
+// reduce-scatter half), optional push of the MX output row to every rank (the all-gather half).  partials_bf16 = 2:
+// `partials` are the per-rank bf16 slots of a one-shot all-reduce, polled and cleared element-wise (no counters).
+int afb_norm_tp(const void* x, const void* partials, int num_partials, long partial_stride, int partials_bf16,
+                const void* residual,
                 const void* bias, const void* gamma, const void* beta, void* sum_out, void* y, float* y_f32, int rows,
                 int H, float eps, int rms, int gamma_plus_one, void* q0, void* q1, void* sf0, void* sf1,
                 int* wait_flags, int wait_n, int wait_expected, int* wait_arrived, void* const* peer_q0,
@@ -500,7 +539,8 @@ int afb_norm_tp(const void* x, const float* partials, int num_partials, long par
     p.peer_x_ready[o] = reinterpret_cast<int*>(peer_x_ready[o]);
   }
   p.x = reinterpret_cast<const __nv_bfloat16*>(x);
-  p.partials = partials; p.num_partials = partials ? num_partials : 0; p.partial_stride = partial_stride;
+  p.partials = reinterpret_cast<const float*>(partials); p.num_partials = partials ? num_partials : 0;
+  p.partial_stride = partial_stride; p.partials_bf16 = partials_bf16;
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);

@@ -117,3 +117,31 @@ def test_rope_kv_write(half_split, rope_dim, norm):
     xr = R.rope(x, pos, 10000.0, rope_dim, half_split)
     A.rope_(x, pos, 10000.0, rope_dim, half_split)
     torch.testing.assert_close(x.float(), xr, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,ctx", [(64, 32, 8, 130), (6, 4, 1, 700)])
+@pytest.mark.parametrize("terms", [1, 2])
+def test_paged_decode_emits_mx_activations(B, Hq, Hkv, ctx, terms):
+    """Split-KV decode whose merge kernel writes MX-fp8 context rows: same values as quantising the bf16 output.
+    The two shapes cover the two- and three-deep tile rings (large and small grids)."""
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import quant
+
+    D = 128
+    kv_lens = [ctx - (i % 7) for i in range(B)]
+    kc, vc, bt = _build_paged(B, kv_lens, Hkv, D, 16, seed=11)
+    q = _rand(B, Hq, D, seed=12)
+    q_starts = torch.arange(B, dtype=torch.int32, device="cuda")
+    q_lens = torch.ones(B, dtype=torch.int32, device="cuda")
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    ref = R.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl)
+    out = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=2)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    mx = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=2, mx_terms=terms)
+    assert isinstance(mx, quant.MxAct) and mx.terms == terms
+    want = quant.quantize_mx(out.view(B, Hq * D), terms=terms)
+    assert torch.equal(mx.q0, want.q0)
+    torch.testing.assert_close(mx.dequant(), want.dequant(), atol=0, rtol=0)
+    # unsplit: falls back to a quantisation pass, same contract
+    mx1 = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=1, mx_terms=terms)
+    torch.testing.assert_close(mx1.dequant().view(B, Hq, D), ref, atol=3e-2 if terms == 2 else 1e-1, rtol=5e-2)

@@ -19,7 +19,11 @@ def test_quantize_mx_matches_oracle_and_is_accurate(T, K):
     x = _rand(T, K, seed=1) * torch.exp(_rand(T, 1, seed=2).float()).to(torch.bfloat16)
     g = quant.quantize_mx(x, terms=2)
     c = quant.quantize_mx(x.cpu(), terms=2)
-    assert torch.equal(g.q0.cpu(), c.q0) and torch.equal(g.sf0.cpu()[: c.sf0.shape[0]], c.sf0)
+    def rows(sf):  # scale bytes of the T real rows; the padding rows of the last atom are left undefined on the GPU
+        tiles, chunks = sf.shape[0], sf.shape[1]
+        return sf.cpu().view(tiles, chunks, 32, 4, 4).permute(1, 4, 0, 3, 2).reshape(chunks * 4, tiles * 128)[:, :T]
+
+    assert torch.equal(g.q0.cpu(), c.q0) and torch.equal(rows(g.sf0), rows(c.sf0))
     d1 = quant.MxAct(g.q0, g.sf0).dequant()
     d2 = g.dequant()
     xf = x.float()
@@ -67,3 +71,21 @@ def test_gemm_mxfp8_modes():
     y = quant.gemm_mxfp8(xq, w, bias=b, act="silu", residual=r)
     torch.testing.assert_close(y.float(), R.linear(xq.dequant(), R.dequantize_block_fp8(w.q, w.scales), b, "silu", r),
                                atol=4e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T,F,S", [(64, 1792, 3), (5, 128, 1), (130, 1024, 8)])
+@pytest.mark.parametrize("terms", [1, 2])
+def test_swiglu_quantize_from_partials(T, F, S, terms):
+    """SwiGLU + MX quantisation over split-K slices of an interleaved gate/up GEMM vs the fp32 reference."""
+    from antfly_b200.ops import quant
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    parts = torch.randn(S, T, 2 * F, generator=g, device="cuda") * 0.7
+    ref = R.swiglu_interleaved(parts.sum(0))
+    mx, y = quant.swiglu_quantize_mx(parts, terms=terms, want_bf16=True)
+    torch.testing.assert_close(y.float(), ref, atol=2e-2, rtol=1e-2)
+    tol = 1e-2 if terms == 2 else 8e-2
+    torch.testing.assert_close(mx.dequant(), ref, atol=tol, rtol=tol)
+    # the CPU route of the same op agrees with the kernel's bf16 rows
+    mx_cpu, y_cpu = quant.swiglu_quantize_mx(parts.cpu(), terms=terms, want_bf16=True)
+    torch.testing.assert_close(y_cpu.float(), y.float().cpu(), atol=2e-2, rtol=1e-2)
