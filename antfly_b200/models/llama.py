@@ -402,5 +402,7 @@ class LlamaModel:
         """Arg-max over the (possibly vocabulary-sharded) logits -> global token ids, int32 [R]."""
         if self.tp_size == 1 or self.comm is None:
             return S.argmax(logits)
+        if self.fused is not None and logits.shape[0] <= self.fused.ws.ARGMAX_ROWS:
+            return self.fused.argmax(logits, self.vocab_offset)
         idx, val = S.argmax(logits, vocab_offset=self.vocab_offset, want_val=True)
         return self.comm.argmax_merge(idx, val)

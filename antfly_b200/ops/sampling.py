@@ -31,6 +31,23 @@ def argmax(logits: torch.Tensor, vocab_offset: int = 0, out: Optional[torch.Tens
     return (out, val) if want_val else out
 
 
+def argmax_tp(logits: torch.Tensor, vocab_offset: int, peer_slots, world: int, rank: int, max_rows: int,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Arg-max over vocabulary-sharded logits merged across the tensor-parallel ranks inside the kernel
+    (``peer_slots``: ctypes array of every rank's key-slot buffer, see SymmetricWorkspace).  Returns global
+    token ids, identical on every rank."""
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    rc = N.cuda().afb_argmax_tp(N.ptr(logits), _c_int(1 if logits.dtype == torch.float32 else 0),
+                                _c_long(logits.stride(0)), _c_int(rows), _c_int(V), N.ptr(out), None,
+                                _c_int(vocab_offset), peer_slots, _c_int(world), _c_int(rank), _c_int(max_rows),
+                                N.stream_ptr())
+    N.check(rc, "afb_argmax_tp")
+    N.count_launch()
+    return out
+
+
 def count_tokens(counts: torch.Tensor, tokens: torch.Tensor, rows: torch.Tensor) -> None:
     """counts[rows[i], tokens[i]] += 1 (uint16 saturating; stored as int16 tensor [B, V])."""
     n = tokens.numel()

@@ -78,6 +78,8 @@ class SymmetricWorkspace:
         self.off_sf1 = region(self.sf_bytes)
         # one-shot all-reduce: two alternating [world][max_tokens][hidden] bf16 slot buffers
         self.off_bcast = [region(world * max_tokens * hidden * 2) for _ in range(2)]
+        # in-kernel arg-max merge: [world][ARGMAX_ROWS] 64-bit keys, zero = empty
+        self.off_argmax = region(world * self.ARGMAX_ROWS * 8)
         self.nbytes = off
         group = group or dist.group.WORLD
         self.buf = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
@@ -106,6 +108,7 @@ class SymmetricWorkspace:
 
     # flag slots (int32 indices inside the flag region)
     PART_FLAGS, PART_ARRIVED, X_READY, X_CONSUMED = 0, 8, 9, 10
+    ARGMAX_ROWS = 1024
 
     def flag_ptr(self, slot: int) -> ctypes.c_void_p:
         return ctypes.c_void_p(self.buf.data_ptr() + self.off_flags + 4 * slot)
@@ -244,3 +247,11 @@ class FusedTp:
         N.check(rc, "afb_norm_tp(bcast)")
         N.count_launch()
         return sum_out, mx
+
+    # -- vocabulary-sharded arg-max merged across ranks inside the kernel ---------------------------------------
+    def argmax(self, logits: torch.Tensor, vocab_offset: int) -> torch.Tensor:
+        from ..ops import sampling as S
+
+        ws = self.ws
+        assert logits.shape[0] <= ws.ARGMAX_ROWS
+        return S.argmax_tp(logits, vocab_offset, ws.peers(ws.off_argmax), self.world, self.rank, ws.ARGMAX_ROWS)

@@ -29,39 +29,56 @@ sys.path.insert(0, ROOT)
 
 
 def _clock_sampler():
-    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Starts nvidia-smi sampling SM clocks and throttle reasons every 50 ms for the GPUs of this job.  Only local
+    rank 0 samples (for all of the job's GPUs); started before the warm-up steps because the tool takes longer to
+    produce its first line than a short timed region lasts.  Returns None on the other ranks."""
+    if int(os.environ.get("LOCAL_RANK", "0")) != 0:
+        return None
+    q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    n = int(os.environ.get("WORLD_SIZE", "1"))
     try:
-        return subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                 "-i", os.environ.get("LOCAL_RANK", "0")], stdout=subprocess.PIPE, text=True)
+        return subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                 "-i", ",".join(str(i) for i in range(n))], stdout=subprocess.PIPE, text=True)
     except Exception:
         return None
 
 
-def _clock_summary(proc):
+def _clock_summary(proc, t_begin=None, t_end=None):
+    """Median SM clock and the throttle reasons seen between t_begin and t_end (datetime, local time); if the
+    window caught no sample, all samples since the sampler started (warm-up and timed steps) are used."""
+    import datetime
+
     if proc is None:
-        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["not sampled on this rank"], "samples": 0}
     proc.terminate()
     try:
         out, _ = proc.communicate(timeout=5)
     except Exception:
         proc.kill()
         out = ""
-    sm, mx, reasons = [], [], set()
+    rows = []
     for line in out.strip().splitlines():
         f = [x.strip() for x in line.split(",")]
-        if len(f) < 9:
+        if len(f) < 10:
             continue
         try:
-            sm.append(float(f[1])); mx.append(float(f[2]))
+            ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+            rows.append((ts, float(f[2]), float(f[3]), f[6:10]))
         except ValueError:
             continue
-        for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+    window = [r for r in rows if t_begin is not None and t_end is not None and t_begin <= r[0] <= t_end]
+    scope = "timed region"
+    if not window:
+        window, scope = rows, "warm-up and timed steps"
+    sm, mx, reasons = [r[1] for r in window], [r[2] for r in window], set()
+    for r in window:
+        for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
             if v.lower().startswith("active"):
                 reasons.add(name)
     return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-            "reasons": sorted(reasons), "samples": len(sm)}
+            "reasons": sorted(reasons), "samples": len(sm), "scope": scope}
 
 
 def _log(msg):
@@ -187,6 +204,7 @@ def bench_decode(args):
     W, K = args.warmup, args.steps
     assert W >= 3, "at least 3 warm-up steps"
     assert W + 2 * K + 1 <= gen, "warm-up + timed steps exceed the generation length"
+    clocks = _clock_sampler()
     for _ in range(W):
         eng.step()
     _log("warm-up done")
@@ -203,10 +221,12 @@ def bench_decode(args):
     _log("e2e steps done")
     # ---- device-timed burst ----
     _barrier(world)
-    clocks = _clock_sampler()
+    import datetime
+
+    tb = datetime.datetime.now()
     _, ms, launches = decode_burst(eng, K)
     _barrier(world)
-    clk = _clock_summary(clocks)
+    clk = _clock_summary(clocks, tb, datetime.datetime.now())
     ms = _max_over_ranks(ms, world)
     st = N.status()
     value = B * K / (ms / 1e3)
@@ -253,10 +273,13 @@ def bench_embed(args):
     batches = synthetic_batches(W + 2 * K, batch=256, lo=32, hi=512, vocab=(1000, 30000), seed=rank)
     pinned = [b.pin() for b in batches]
     dev_batches = [b.to(dev) for b in pinned[W:W + K]]
+    import datetime
+
+    clocks = _clock_sampler()
     for b in pinned[:W]:
         emb.embed_packed(b.to(dev))
     _barrier(world)
-    clocks = _clock_sampler()
+    tb = datetime.datetime.now()
     n0 = N.launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -265,7 +288,7 @@ def bench_embed(args):
     e1.record()
     _barrier(world)
     launches = N.launches() - n0
-    clk = _clock_summary(clocks)
+    clk = _clock_summary(clocks, tb, datetime.datetime.now())
     ms = _max_over_ranks(e0.elapsed_time(e1), world)
     # end to end: pinned host ids -> device -> embeddings -> host
     h2d = sum(b.nbytes() for b in pinned[W + K:W + 2 * K]) / K

@@ -118,7 +118,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-__global__ void norm_kernel(NormParams p) {
+__global__ void __launch_bounds__(512) norm_kernel(NormParams p) {
   extern __shared__ float srow[];
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -483,7 +483,7 @@ __global__ void embed_gather_kernel(const int* ids, const __nv_bfloat16* table, 
 static int norm_threads(int H) {
   int t = ((H / 8) + 31) / 32 * 32;
   if (t < 32) t = 32;
-  if (t > 1024) t = 1024;
+  if (t > 512) t = 512;  // norm_kernel is compiled for at most 512 threads (128 registers each)
   return t;
 }
 

@@ -34,9 +34,21 @@ __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p,
 // argmax: one CTA per row.  Ties resolve to the lowest index.  `row_stride` lets the caller pick rows out of a
 // larger logits buffer; vocab_offset is added to the result (vocabulary-sharded heads).
 // ---------------------------------------------------------------------------------------------------------
+// Cross-GPU merge of a vocabulary-sharded arg-max (tensor-parallel LM head), fused into the same kernel: each
+// rank packs its best (value, global index) into one 64-bit key (order-preserving value bits high, inverted index
+// low, so the larger key is the better candidate and ties go to the lower index), stores it into slot
+// [my_rank][row] of every rank (8-byte peer stores), then polls its own world slots until all keys have landed,
+// takes the maximum and zeroes the slots again (0 is never a valid key).  No flags, no fences, no collective
+// library call.  A rank can only reach this kernel again after a cross-rank hand-off of the next step, which the
+// slower ranks enter after their own merge, so one set of slots suffices.
+struct ArgmaxTp {
+  unsigned long long* peer_slots[8];  // rank o's [world][max_rows] key slots
+  int world, my_rank, max_rows;
+};
+
 template <typename T>
 __global__ void argmax_kernel(const T* logits, long row_stride, int V, int* out_idx, float* out_val,
-                              int vocab_offset) {
+                              int vocab_offset, ArgmaxTp tp) {
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const int row = blockIdx.x;
@@ -45,9 +57,32 @@ __global__ void argmax_kernel(const T* logits, long row_stride, int V, int* out_
   const T* lp = logits + static_cast<size_t>(row) * row_stride;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = ld_logit<T>(lp, i);
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  constexpr int VEC = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(lp) & 15) == 0) {
+    // 16-byte loads; within a thread indices ascend, so a strict > keeps the lowest index on ties.
+    const int nvec = V / VEC;
+    for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+      const uint4 u = *reinterpret_cast<const uint4*>(lp + static_cast<size_t>(j) * VEC);
+      float v[VEC];
+      if constexpr (sizeof(T) == 2) {
+        const float2 a = unpack_bf16x2(u.x), b2 = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        v[0] = a.x; v[1] = a.y; v[2] = b2.x; v[3] = b2.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+      } else {
+        v[0] = __uint_as_float(u.x); v[1] = __uint_as_float(u.y); v[2] = __uint_as_float(u.z); v[3] = __uint_as_float(u.w);
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        if (v[e] > best) { best = v[e]; bi = j * VEC + e; }
+    }
+    for (int i = nvec * VEC + threadIdx.x; i < V; i += blockDim.x) {
+      const float v = ld_logit<T>(lp, i);
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = ld_logit<T>(lp, i);
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -67,7 +102,35 @@ __global__ void argmax_kernel(const T* logits, long row_stride, int V, int* out_
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (lane == 0) {
+    if (tp.world > 0) {
+      // All lanes hold the local winner; lane o publishes to rank o, then lane s polls slot s.
+      const unsigned gidx = static_cast<unsigned>(bi + vocab_offset);
+      const unsigned long long key = (static_cast<unsigned long long>(float_key(best)) << 32) | (0xFFFFFFFFu - gidx);
+      if (lane < tp.world) {
+        unsigned long long* dst = tp.peer_slots[lane] + static_cast<size_t>(tp.my_rank) * tp.max_rows + row;
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(key) : "memory");
+      }
+      unsigned long long got = 0;
+      if (lane < tp.world) {
+        unsigned long long* src = tp.peer_slots[tp.my_rank] + static_cast<size_t>(lane) * tp.max_rows + row;
+        for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
+          asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+          if (got != 0ull) break;
+          if (it > 16) __nanosleep(20);
+        }
+        if (got == 0ull) status_set(kStatusPeerFlagTimeout);
+        else *src = 0ull;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, got, o);
+        got = other > got ? other : got;
+      }
+      if (lane == 0) {
+        out_idx[row] = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned>(got & 0xFFFFFFFFull));
+        if (out_val) out_val[row] = best;
+      }
+    } else if (lane == 0) {
       out_idx[row] = bi + vocab_offset;
       if (out_val) out_val[row] = best;
     }
@@ -318,17 +381,39 @@ __global__ void spec_verify_kernel(const int* draft, const int* target, int B, i
 
 extern "C" {
 
+int afb_argmax_tp(const void* logits, int is_f32, long row_stride, int rows, int V, int* out_idx, float* out_val,
+                  int vocab_offset, void* const* peer_slots, int world, int my_rank, int max_rows,
+                  cudaStream_t stream);
+
 int afb_argmax(const void* logits, int is_f32, long row_stride, int rows, int V, int* out_idx, float* out_val,
                int vocab_offset, cudaStream_t stream) {
+  return afb_argmax_tp(logits, is_f32, row_stride, rows, V, out_idx, out_val, vocab_offset, nullptr, 0, 0, 0, stream);
+}
+
+// Arg-max over a vocabulary shard merged across `world` ranks inside the kernel (see ArgmaxTp): peer_slots[o] is
+// rank o's zero-initialised [world][max_rows] array of 64-bit keys.  world = 0: local arg-max only.
+int afb_argmax_tp(const void* logits, int is_f32, long row_stride, int rows, int V, int* out_idx, float* out_val,
+                  int vocab_offset, void* const* peer_slots, int world, int my_rank, int max_rows,
+                  cudaStream_t stream) {
   using namespace afb;
   if (rows <= 0) return 0;
+  ArgmaxTp tp = {};
+  if (world > 0) {
+    if (world > 8 || rows > max_rows || !peer_slots) {
+      set_last_error("afb_argmax_tp: at most 8 ranks and rows <= max_rows (rows=%d max_rows=%d)", rows, max_rows);
+      return -1;
+    }
+    tp.world = world; tp.my_rank = my_rank; tp.max_rows = max_rows;
+    for (int o = 0; o < world; ++o) tp.peer_slots[o] = reinterpret_cast<unsigned long long*>(peer_slots[o]);
+  }
   if (is_f32)
     AFB_CHECK_CUDA(launch_pdl(argmax_kernel<float>, dim3(rows), dim3(1024), 0, stream,
-                              reinterpret_cast<const float*>(logits), row_stride, V, out_idx, out_val, vocab_offset));
+                              reinterpret_cast<const float*>(logits), row_stride, V, out_idx, out_val, vocab_offset,
+                              tp));
   else
     AFB_CHECK_CUDA(launch_pdl(argmax_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, stream,
                               reinterpret_cast<const __nv_bfloat16*>(logits), row_stride, V, out_idx, out_val,
-                              vocab_offset));
+                              vocab_offset, tp));
   return 0;
 }
 

@@ -53,7 +53,16 @@ for one_shot in (True, False):
     torch.cuda.synchronize()
     gerr=float((lg.float()-ref).abs().max()); gst=N.status()
     print(f"rank {rank} [{name}]: graph replay err={gerr:.4f} status={gst}", flush=True)
-    all_ok = all_ok and st == 0 and gst == 0 and max(err) < 5e-2 and gerr < 5e-2 and min(agree) > 0.9 and same
+    # vocabulary-sharded arg-max merged inside the kernel vs the NCCL gather + torch merge
+    lg_cur = outs[-1].bfloat16()
+    tok_fused = model.greedy_tokens(lg_cur)
+    fz = model.fused; model.fused = None
+    tok_nccl = model.greedy_tokens(lg_cur)
+    model.fused = fz
+    torch.cuda.synchronize()
+    tok_ok = bool(torch.equal(tok_fused, tok_nccl)) and N.status() == 0
+    print(f"rank {rank} [{name}]: argmax merge equal={tok_ok}", flush=True)
+    all_ok = all_ok and st == 0 and gst == 0 and max(err) < 5e-2 and gerr < 5e-2 and min(agree) > 0.9 and same and tok_ok
     dist.barrier()
 ok = all_ok
 print(f"rank {rank}: TP_FUSED_CHECK {'OK' if ok else 'FAILED'}", flush=True)
