@@ -15,6 +15,8 @@
 //
 // Tensor-core path: mma.sync m16n8k16 (bf16) with ldmatrix from XOR-swizzled shared memory, K/V tiles staged
 // by cp.async (zero-filled past the end of the sequence) in a two- or three-deep ring.
+#include <stdlib.h>
+
 #include "../common/mxquant.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tmap.cuh"
@@ -394,6 +396,232 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Decode attention for at most 8 (position, head-in-group) rows per KV head, i.e. one new token with a GQA
+// group of up to 8: the transposed formulation.  Keys sit on the MMA's M axis and the query rows on its N = 8
+// axis, S^T = K Q^T and O^T = V^T P^T, so a warp spends one m16n8k16 per 16 keys x 16 dims instead of two with
+// three quarters of the rows padding, and the output accumulator is D x 8 (32 registers at D = 128) instead of
+// 16 x D (64).  Each of the four warps owns 16 keys of a 64-key tile; P^T goes from accumulator layout to the
+// B-operand layout with two movmatrix transposes; warps and KV splits are merged by log-sum-exp as before.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+  return r;
+}
+
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128) decode_attn_t_kernel(AttnParams p) {
+  constexpr int KSTEPS = D / 16;  // 16-wide steps over the head dimension
+  constexpr int NDB = D / 16;     // 16-row blocks of O^T
+  extern __shared__ __align__(128) uint8_t smem_attn[];
+  __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_attn);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  griddep_launch();
+  griddep_wait();
+  const int b = blockIdx.z / p.num_splits;
+  const int split = blockIdx.z % p.num_splits;
+  const int hk = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const int q_start = p.q_starts[b], q_len = p.q_lens[b], kv_len = p.kv_lens[b];
+  const int rows_total = q_len * G;  // <= 8
+  if (rows_total <= 0) return;
+  const int pos_off = kv_len - q_len;
+
+  // Q^T as the B operand: lane (g, t) holds Q[row g][16 kk + 2t, +1] and [.. + 8, + 9]; rows >= rows_total are 0.
+  uint32_t qf[KSTEPS][2];
+  {
+    const bool ok = g < rows_total;
+    const __nv_bfloat16* qp = p.q + static_cast<size_t>(q_start + (ok ? g / G : 0)) * p.q_stride +
+                              (hk * G + (ok ? g % G : 0)) * D + 2 * t;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      qf[kk][0] = ok ? *reinterpret_cast<const uint32_t*>(qp + kk * 16) : 0u;
+      qf[kk][1] = ok ? *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8) : 0u;
+    }
+  }
+  // This thread's two query columns (2t, 2t + 1) and their absolute positions.
+  int qpos[2];
+  bool qok[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int r = 2 * t + e;
+    qok[e] = r < rows_total;
+    qpos[e] = pos_off + r / G;
+  }
+
+  int kv_hi = kv_len;
+  if (p.causal) kv_hi = min(kv_len, pos_off + (rows_total - 1) / G + 1);
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, pos_off - p.window + 1);
+  const int tile_lo = kv_lo / kTileKeys;
+  const int tile_hi = (kv_hi + kTileKeys - 1) / kTileKeys;
+  const int ntiles_all = max(0, tile_hi - tile_lo);
+  const int per_split = (ntiles_all + p.num_splits - 1) / p.num_splits;
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_hi, t_begin + per_split);
+  const int ntiles = max(0, t_end - t_begin);
+
+  float o[NDB][4];
+#pragma unroll
+  for (int i = 0; i < NDB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+
+  constexpr int TILE_ELEMS = kTileKeys * D;
+#pragma unroll
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+    if (s0 < ntiles) {
+      __nv_bfloat16* nK = sKV + s0 * 2 * TILE_ELEMS;
+      load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + s0) * kTileKeys, kv_len, q_start);
+    }
+    cp_async_commit();
+  }
+  const int mi = lane >> 3, rin = lane & 7;
+  for (int it = 0; it < ntiles; ++it) {
+    const int stage = it % STAGES;
+    const __nv_bfloat16* sK = sKV + stage * 2 * TILE_ELEMS;
+    const __nv_bfloat16* sV = sK + TILE_ELEMS;
+    if (it + STAGES - 1 < ntiles) {
+      __nv_bfloat16* nK = sKV + ((it + STAGES - 1) % STAGES) * 2 * TILE_ELEMS;
+      load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + STAGES - 1) * kTileKeys, kv_len, q_start);
+    }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncthreads();
+
+    const int k0 = (t_begin + it) * kTileKeys + warp * 16;  // first key of this warp's slab
+    // ---- S^T = K Q^T : two independent accumulators (even / odd k-steps) shorten the dependency chain ----
+    float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    {
+      const int key = warp * 16 + (mi & 1) * 8 + rin;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int chunk = kk * 2 + (mi >> 1);
+        uint32_t ka[4];
+        ldmatrix_x4(ka, sK + key * D + ((chunk ^ (key & 7)) * 8));
+        if (kk & 1) mma_bf16_16816(s1, ka, qf[kk][0], qf[kk][1]);
+        else mma_bf16_16816(s0, ka, qf[kk][0], qf[kk][1]);
+      }
+    }
+    float s[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] = s0[e] + s1[e];
+    // s[0], s[1]: key k0 + g, queries 2t, 2t + 1;  s[2], s[3]: key k0 + g + 8, same queries.
+    const bool full = (k0 + 16 <= kv_len) && (!p.causal || k0 + 15 <= pos_off) && (p.window <= 0 || k0 > pos_off + (rows_total - 1) / G - p.window);
+    if (!full) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = k0 + g + 8 * (e >> 1);
+        const int c = e & 1;
+        bool ok = qok[c] && key < kv_len;
+        if (p.causal) ok = ok && key <= qpos[c];
+        if (p.window > 0) ok = ok && key > qpos[c] - p.window;
+        if (!ok) s[e] = -INFINITY;
+      }
+    }
+    float mx[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+    float alpha[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
+      mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
+      mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
+      mx[c] *= p.scale_log2;
+      const float m_new = fmaxf(m_run[c], mx[c]);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      alpha[c] = exp2f(m_run[c] - m_use);
+      m_run[c] = m_new;
+      l_run[c] *= alpha[c];
+      mx[c] = -m_use;
+    }
+    const float p0 = exp2f(fmaf(s[0], p.scale_log2, mx[0]));
+    const float p1 = exp2f(fmaf(s[1], p.scale_log2, mx[1]));
+    const float p2 = exp2f(fmaf(s[2], p.scale_log2, mx[0]));
+    const float p3 = exp2f(fmaf(s[3], p.scale_log2, mx[1]));
+    l_run[0] += p0 + p2;
+    l_run[1] += p1 + p3;
+    // Accumulator layout (key row, query column pair) -> B-operand layout (key pair, query column).
+    const uint32_t pb0 = movmatrix_trans(pack_bf16x2(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16x2(p2, p3));
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+      for (int i = 0; i < NDB; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[1];
+        o[i][2] *= alpha[0]; o[i][3] *= alpha[1];
+      }
+    }
+    // ---- O^T += V^T P^T ----
+    {
+      const int key = warp * 16 + (mi >> 1) * 8 + rin;
+#pragma unroll
+      for (int db = 0; db < NDB; ++db) {
+        const int chunk = db * 2 + (mi & 1);
+        uint32_t va[4];
+        ldmatrix_x4_trans(va, sV + key * D + ((chunk ^ (key & 7)) * 8));
+        mma_bf16_16816(o[db], va, pb0, pb1);
+      }
+    }
+    __syncthreads();
+  }
+
+  // Per-query sums across the eight lane groups that hold different keys.
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 4);
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 8);
+    l_run[c] += __shfl_xor_sync(0xffffffffu, l_run[c], 16);
+  }
+  // Merge the four warps (same queries, disjoint keys) through shared memory: sO[warp][query][d].
+  float* sO = reinterpret_cast<float*>(smem_attn);
+  float* sM = sO + 4 * 8 * D;
+  float* sL = sM + 32;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < NDB; ++i) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = i * 16 + g + 8 * (e >> 1);
+      const int q = 2 * t + (e & 1);
+      sO[(warp * 8 + q) * D + d] = o[i][e];
+    }
+  }
+  if (g == 0) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      sM[warp * 8 + 2 * t + c] = m_run[c];
+      sL[warp * 8 + 2 * t + c] = l_run[c];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows_total * D; idx += blockDim.x) {
+    const int r = idx / D, col = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 8 + r]);
+    float L = 0.0f, acc = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(sM[w * 8 + r] - M);
+        L += f * sL[w * 8 + r];
+        acc += f * sO[(w * 8 + r) * D + col];
+      }
+    }
+    const float val = L > 0.0f ? acc / L : 0.0f;
+    const int tok = q_start + r / G;
+    const int head = hk * G + r % G;
+    if (p.num_splits == 1) {
+      p.out[static_cast<size_t>(tok) * p.out_stride + head * D + col] = __float2bfloat16(val);
+    } else {
+      const size_t prow = static_cast<size_t>(split) * p.T * p.Hq + static_cast<size_t>(tok) * p.Hq + head;
+      p.part_o[prow * D + col] = val;
+      if (col == 0) p.part_lse[prow] = (L > 0.0f) ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+
 // Merge split-KV partials: out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max).  Each thread owns 4 adjacent
 // columns of one (token, head) row; 128-thread CTAs cover 512 / D rows.  When q0 is given the merged row is also
 // written as MX fp8 activations of the [T, Hq * D] matrix the output projection consumes, so no separate
@@ -454,11 +682,54 @@ int launch_attn_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   return 0;
 }
 
+inline bool transposed_decode_disabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ANTFLY_B200_ATTN_LEGACY_DECODE");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+template <int D, int STAGES>
+int launch_decode_t_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  const int smem_tiles = STAGES * 2 * kTileKeys * D * 2;
+  const int smem_merge = (4 * 8 * D + 64) * 4;
+  const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
+  static bool configured = false;
+  if (!configured) {
+    AFB_CHECK_CUDA(cudaFuncSetAttribute(decode_attn_t_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        smem));
+    configured = true;
+  }
+  AFB_CHECK_CUDA(launch_pdl(decode_attn_t_kernel<D, STAGES>, grid, dim3(128), smem, stream, p));
+  return 0;
+}
+
+template <int D>
+int launch_decode_t(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    AFB_CHECK_CUDA(cudaGetDevice(&dev));
+    AFB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const long ctas = static_cast<long>(grid.x) * grid.y * grid.z;
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("ANTFLY_B200_ATTN_STAGES");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 3 || (forced == 0 && ctas <= 2L * sms)) return launch_decode_t_s<D, 3>(p, grid, stream);
+  return launch_decode_t_s<D, 2>(p, grid, stream);
+}
+
 template <int D, bool PAGED, bool SPLIT_KEYS>
 int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
   const int rows_per_cta = SPLIT_KEYS ? 16 : 64;
   dim3 grid((max_rows + rows_per_cta - 1) / rows_per_cta, p.Hkv, B * p.num_splits);
   if constexpr (SPLIT_KEYS && PAGED) {
+    if (max_rows <= 8 && !transposed_decode_disabled()) return launch_decode_t<D>(p, grid, stream);
     // A decode grid that leaves at most two CTAs per SM gets a deeper ring.
     static int sms = 0;
     if (!sms) {

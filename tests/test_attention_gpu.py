@@ -145,3 +145,23 @@ def test_paged_decode_emits_mx_activations(B, Hq, Hkv, ctx, terms):
     # unsplit: falls back to a quantisation pass, same contract
     mx1 = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=1, mx_terms=terms)
     torch.testing.assert_close(mx1.dequant().view(B, Hq, D), ref, atol=3e-2 if terms == 2 else 1e-1, rtol=5e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 1), (16, 1)])
+def test_paged_decode_sliding_window_and_legacy_agree(Hq, Hkv):
+    """Decode with a sliding window (masked first and last tiles) on both decode organisations: groups of up to 8
+    rows take the transposed-MMA kernel, a group of 16 the 16-row one."""
+    from antfly_b200.ops import attention as A
+
+    D, window = 128, 100
+    kv_lens = [1, 99, 100, 101, 333, 1500]
+    B = len(kv_lens)
+    kc, vc, bt = _build_paged(B, kv_lens, Hkv, D, 16, seed=21)
+    q = _rand(B, Hq, D, seed=22)
+    q_starts = torch.arange(B, dtype=torch.int32, device="cuda")
+    q_lens = torch.ones(B, dtype=torch.int32, device="cuda")
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    ref = R.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, None, window)
+    for splits in (1, 3):
+        out = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, window=window, num_splits=splits)
+        torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
