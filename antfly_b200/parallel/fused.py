@@ -255,3 +255,57 @@ class FusedTp:
         ws = self.ws
         assert logits.shape[0] <= ws.ARGMAX_ROWS
         return S.argmax_tp(logits, vocab_offset, ws.peers(ws.off_argmax), self.world, self.rank, ws.ARGMAX_ROWS)
+
+    # -- pre-flight -------------------------------------------------------------------------------------------------
+    def self_check(self, group=None) -> bool:
+        """Runs each fused hand-off once on small random data with a host synchronise in between and compares it
+        with the same arithmetic done through NCCL: row-parallel GEMM -> all-reduce -> residual + RMSNorm, and the
+        sharded arg-max merge.  Returns True only if every rank saw matching results and no wait expired.  Meant
+        to be called once before a serving loop or a benchmark commits to the fused path; a missing or misbehaving
+        rank costs one wait limit here instead of wedging a queue of graphs."""
+        ws = self.ws
+        dev, H = ws.device, ws.hidden
+        T, K = 16, 256
+        ok = True
+        try:
+            g = torch.Generator(device=dev).manual_seed(1000 + self.rank)
+            x = (torch.randn(T, K, generator=g, device=dev) * 0.5).to(torch.bfloat16)
+            w = Q.random_fp8(H, K, dev, seed=77 + self.rank)
+            gamma = torch.ones(H, dtype=torch.bfloat16, device=dev)
+            residual = torch.zeros((T, H), dtype=torch.bfloat16, device=dev)
+            xq = Q.quantize_mx(x, terms=self.terms)
+            local = Q.gemm_mxfp8(xq, w).float()                       # this rank's partial product, bf16-rounded
+            want = local.clone()
+            dist.all_reduce(want, group=group)
+            for buf in (0, 1):
+                self.gemm_bcast(xq, w, T, 1, buf)
+                got, _ = self.norm_bcast(gamma, residual, T, 1e-5, buf)
+                torch.cuda.synchronize(dev)
+                err = float((got.float() - want).abs().max())
+                ok = ok and err <= 0.05 * max(1.0, float(want.abs().max()))
+            V = 4096
+            logits = torch.randn(T, V, generator=g, device=dev)  # fp32: ties between ranks are negligible
+            tok = self.argmax(logits, self.rank * V)
+            vals = logits.float().max(-1)
+            all_v = [torch.empty_like(vals.values) for _ in range(self.world)]
+            all_i = [torch.empty_like(vals.indices) for _ in range(self.world)]
+            dist.all_gather(all_v, vals.values.contiguous(), group=group)
+            dist.all_gather(all_i, (vals.indices + self.rank * V).contiguous(), group=group)
+            av, ai = torch.stack(all_v), torch.stack(all_i)
+            best = av.max(0).values
+            want_tok = torch.where(av == best[None], ai, torch.full_like(ai, 2 ** 40)).min(0).values
+            torch.cuda.synchronize(dev)
+            ok = ok and bool(torch.equal(tok.long(), want_tok.long()))
+            ok = ok and N.status() == 0
+        except Exception:
+            ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            N.status()  # clear whatever the failed attempt recorded
+            ws.clear_one_shot_slots()
+            ws.local(ws.off_argmax, self.world * ws.ARGMAX_ROWS * 8).zero_()
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=group)
+            return False
+        return True

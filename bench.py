@@ -181,6 +181,16 @@ def bench_decode(args):
 
         model.fused = FusedTp(SymmetricWorkspace(rank, world, torch.device("cuda", local), cfg.hidden_size,
                                                  max_tokens=128), one_shot=args.tp_path == "fused")
+        # Pre-flight: every fused hand-off once, checked against NCCL.  If it does not hold on this machine the run
+        # continues on the NCCL path and says so in its output line.
+        try:
+            fused_ok = model.fused.self_check()
+        except Exception:
+            fused_ok = False
+        if not fused_ok:
+            model.fused = None
+            args.tp_path = "nccl (fused path failed its pre-flight check)"
+        _log(f"fused pre-flight: {fused_ok}")
     B, prompt_len, gen = args.batch, args.prompt_len, args.gen_len
     total = prompt_len + gen + 16
     blocks = B * ((total + 15) // 16) + 8
@@ -208,6 +218,15 @@ def bench_decode(args):
     for _ in range(W):
         eng.step()
     _log("warm-up done")
+    # A bounded wait that expired during warm-up (a rank missing, a hand-off that never arrived) means the numbers
+    # would be garbage and every further step would cost a wait limit: stop here instead of queueing more work.
+    st0 = int(_max_over_ranks(float(N.status()), world))
+    if st0 != 0:
+        if rank == 0:
+            print(json.dumps({"metric": "decode tok/s @8B TP", "error": "a kernel wait expired during warm-up",
+                              "kernel_status": st0, "n_gpus": world}))
+        _finish(world)
+        return
     # ---- end-to-end: K engine steps, each with its H2D of inputs and D2H of tokens ----
     h2d0, d2h0 = eng.h2d_bytes, eng.d2h_bytes
     _barrier(world)

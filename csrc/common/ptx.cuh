@@ -19,6 +19,37 @@ namespace afb {
 #ifndef AFB_SPIN_LIMIT
 #define AFB_SPIN_LIMIT (1u << 24)
 #endif
+// Wall-clock limit of one wait on data or a flag that ANOTHER GPU writes.  Long enough for the skew between
+// ranks at start-up (graph capture, first-use module loads), short enough that a missing rank costs seconds.
+#ifndef AFB_PEER_WAIT_NS
+#define AFB_PEER_WAIT_NS 2000000000ull
+#endif
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Deadline of a cross-GPU wait.  expired() is cheap on most polls (the clock and the status word are looked at
+// every 32nd call).  Once any cross-GPU wait of this library file has expired, every later one gives up on its
+// first poll: the kernels still queued behind a failure (a whole CUDA graph of them) then drain in microseconds
+// instead of serving one limit each, and the host finds the status word set.
+struct PeerDeadline {
+  uint64_t t0;
+  uint32_t polls;
+  __device__ __forceinline__ PeerDeadline() : t0(0), polls(0) {}
+  __device__ __forceinline__ bool expired() {
+    if ((polls++ & 31u) != 0u) return false;
+    if (status_peek() & kStatusPeerFlagTimeout) return true;
+    const uint64_t now = globaltimer_ns();
+    if (t0 == 0) {
+      t0 = now | 1ull;
+      return false;
+    }
+    return now - t0 > AFB_PEER_WAIT_NS;
+  }
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -59,10 +90,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false (and records `code`) when the limit is hit.
+// Bounded wait.  Returns false (and records `code`) when the limit is hit: an iteration cap, a wall-clock limit
+// (AFB_LOCAL_WAIT_NS, looked at every 64th poll), or -- so that whatever is queued behind a failure drains at
+// once -- a wait-timeout code already recorded by this library file.
+#ifndef AFB_LOCAL_WAIT_NS
+#define AFB_LOCAL_WAIT_NS 2000000000ull
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+  uint64_t t0 = 0;
   for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (status_peek() & kStatusAnyWaitTimeout) break;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now | 1ull;
+      else if (now - t0 > AFB_LOCAL_WAIT_NS) break;
+    }
   }
   status_set(code);
   return false;

@@ -20,6 +20,10 @@ enum StatusCode : int {
   kStatusGridFlagTimeout = 1 << 7,     // wait on a flag another CTA of the same grid writes ran out
 };
 
+// Codes that mean "a wait gave up": once one is recorded, later waits of the same library file give up at once.
+constexpr int kStatusAnyWaitTimeout = kStatusTmaWaitTimeout | kStatusEmptyWaitTimeout | kStatusMmaWaitTimeout |
+                                      kStatusDequantWaitTimeout | kStatusPeerFlagTimeout | kStatusGridFlagTimeout;
+
 typedef int (*StatusReader)(int clear);
 // Defined in runtime.cu.
 void register_status_reader(StatusReader fn);
@@ -30,6 +34,8 @@ static __device__ int g_afb_status = 0;
 
 namespace afb {
 __device__ __forceinline__ void status_set(int code) { atomicOr(&g_afb_status, code); }
+// Current value of this file's status word (uncached read).
+__device__ __forceinline__ int status_peek() { return *reinterpret_cast<volatile int*>(&g_afb_status); }
 }  // namespace afb
 
 namespace {

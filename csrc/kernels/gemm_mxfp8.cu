@@ -81,8 +81,10 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 
 // Bounded wait on a counter that other GPUs increment.  Returns false (status recorded) on expiry.
 __device__ __forceinline__ bool wait_counter_sys(const int* p, int expected) {
+  PeerDeadline dl;
   for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
     if (ld_acquire_sys(p) >= expected) return true;
+    if (dl.expired()) break;
     __nanosleep(20);
   }
   status_set(kStatusPeerFlagTimeout);

@@ -129,8 +129,10 @@ __global__ void __launch_bounds__(512) norm_kernel(NormParams p) {
   if (p.wait_flags) {
     if (threadIdx.x < p.wait_n) {
       bool ok = false;
+      PeerDeadline dl;
       for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
         if (norm_ld_acquire_sys(p.wait_flags + threadIdx.x) >= p.wait_expected) { ok = true; break; }
+        if (dl.expired()) break;
         __nanosleep(20);
       }
       if (!ok) status_set(kStatusPeerFlagTimeout);
@@ -159,6 +161,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormParams p) {
       __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(const_cast<float*>(p.partials));
       uint4 u[8];
       unsigned pending = (1u << p.num_partials) - 1u;
+      PeerDeadline dl;
       for (uint32_t it = 0; it < AFB_SPIN_LIMIT && pending; ++it) {
 #pragma unroll
         for (int s = 0; s < 8; ++s)
@@ -166,6 +169,7 @@ __global__ void __launch_bounds__(512) norm_kernel(NormParams p) {
 #pragma unroll
         for (int s = 0; s < 8; ++s)
           if ((pending & (1u << s)) && !lamport_pending(u[s])) pending &= ~(1u << s);
+        if (pending && dl.expired()) break;
         if (pending && it > 16) __nanosleep(20);
       }
       if (pending) status_set(kStatusPeerFlagTimeout);

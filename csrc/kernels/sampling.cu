@@ -113,9 +113,10 @@ __global__ void argmax_kernel(const T* logits, long row_stride, int V, int* out_
       unsigned long long got = 0;
       if (lane < tp.world) {
         unsigned long long* src = tp.peer_slots[tp.my_rank] + static_cast<size_t>(lane) * tp.max_rows + row;
+        PeerDeadline dl;
         for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
           asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
-          if (got != 0ull) break;
+          if (got != 0ull || dl.expired()) break;
           if (it > 16) __nanosleep(20);
         }
         if (got == 0ull) status_set(kStatusPeerFlagTimeout);

@@ -29,7 +29,9 @@ ids=(ar*37+5)%cfg.vocab_size
 b=StepBatch(ids.int(),kvl-1,slots,ar,torch.ones_like(ar),kvl,tables,ar,1,1)
 k1,v1=cache(); ref=model.forward(b,k1,v1).float()
 ws=SymmetricWorkspace(rank,world,dev,cfg.hidden_size,max_tokens=128)
-all_ok=True
+pre=FusedTp(ws).self_check()
+print(f"rank {rank}: pre-flight self-check {pre}", flush=True)
+all_ok=bool(pre)
 for one_shot in (True, False):
     if not one_shot and B % world: continue
     name='one-shot' if one_shot else 'two-shot'
