@@ -159,6 +159,14 @@ class LLMEngine:
         return any(not r.finished for r in self.reqs.values())
 
     # ------------------------------------------------------------------------------------------------
+    def _after_capture(self) -> None:
+        """Tensor-parallel ranks meet on the host after capturing a graph: capture allocates and takes tens of
+        milliseconds, and a rank that is already replaying would otherwise sit in its kernels' cross-GPU waits for
+        as long as the slowest rank still captures."""
+        if self.model.tp_size > 1 and getattr(self.model, "comm", None) is not None:
+            torch.cuda.synchronize()
+            self.model.comm.barrier()
+
     def _attn_splits(self, B: int, max_kv: int) -> int:
         ctas = B * self.model.Hkv
         if max_kv < 1024:
@@ -298,6 +306,7 @@ class LLMEngine:
                     run()
                 st.launches = N.launches() - n0
                 st.graph = g
+                self._after_capture()
                 # The warm-up and capture passes rewrote the same KV slots with the same values; replay for real.
             st.graph.replay()
             from .. import _native as N
@@ -522,6 +531,7 @@ def decode_burst(engine: "LLMEngine", n_steps: int):
             run()
         st.launches = N.launches() - n0
         st.graph = g
+        engine._after_capture()
     out = torch.empty((n_steps, B), dtype=torch.int32, device=engine.device)
     assert st.pos.data_ptr() + 4 * B == st.slots.data_ptr()
     ps_view = st.dev[B:3 * B]
