@@ -41,7 +41,7 @@ class BertConfig:
         cfg = cls(**{k: v for k, v in d.items() if k in keys})
         if d.get("model_type") in ("roberta", "xlm-roberta"):
             cfg.position_offset = int(d.get("pad_token_id", 1)) + 1
-        if "id2label" in d and cfg.num_labels == 0 and d.get("architectures", [""])[0].endswith(
+        if "id2label" in d and cfg.num_labels == 0 and (d.get("architectures") or [""])[0].endswith(
                 "ForSequenceClassification"):
             cfg.num_labels = len(d["id2label"])
         return cfg

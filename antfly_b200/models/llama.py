@@ -56,6 +56,19 @@ class LlamaConfig:
     def from_hf(cls, d: dict) -> "LlamaConfig":
         keys = {f for f in cls.__dataclass_fields__}
         cfg = cls(**{k: v for k, v in d.items() if k in keys and v is not None})
+        # RoPE settings: top-level ``rope_theta`` (older config.json files) or the ``rope_parameters`` /
+        # ``rope_scaling`` dictionary (newer ones); linear position scaling and partial rotary factors are honoured,
+        # frequency-dependent schemes (llama3, yarn) fall back to the unscaled frequencies.
+        rp = d.get("rope_parameters") or d.get("rope_scaling") or {}
+        if d.get("rope_theta") is None and rp.get("rope_theta") is not None:
+            cfg.rope_theta = float(rp["rope_theta"])
+        if rp.get("rope_type", rp.get("type")) == "linear" and rp.get("factor"):
+            cfg.rope_freq_scale = 1.0 / float(rp["factor"])
+        prf = d.get("partial_rotary_factor") or rp.get("partial_rotary_factor")
+        if prf:
+            cfg.rope_dim = int(cfg.head_dim * float(prf))
+        if d.get("use_sliding_window") is False:
+            cfg.sliding_window = 0
         mt = d.get("model_type", "")
         if mt == "qwen2":
             cfg.qkv_bias = True

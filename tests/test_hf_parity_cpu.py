@@ -1,0 +1,129 @@
+"""Architecture parity on CPU against Hugging Face `transformers` reference implementations with random weights:
+decoder families (Llama GQA, Qwen2 with QKV bias, Qwen3 with per-head Q/K RMS norm and an explicit head size,
+Mistral with a sliding window) through prefill + decode over the paged KV cache, and the BERT encoder with mean
+pooling and a classification head.  The decoder's linear weights are block-fp8 in this engine, so the HF model
+gets the same weights rounded to that grid first; what is compared is the wiring (RoPE convention, GQA, norms,
+biases, masks, weight tying), not the quantiser."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from antfly_b200.models.bert import BertConfig, BertModel, pack_sequences
+from antfly_b200.models.llama import LlamaConfig, LlamaModel, StepBatch
+from antfly_b200.ops import reference as R
+
+
+def _round_linears_to_fp8_grid(model):
+    with torch.no_grad():
+        for name, mod in model.named_modules():
+            if isinstance(mod, torch.nn.Linear):
+                q, e8 = R.quantize_block_fp8(mod.weight.data)
+                mod.weight.data.copy_(R.dequantize_block_fp8(q, e8))
+
+
+def _hf_decoder(kind: str):
+    common = dict(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5,
+                  rope_theta=10000.0, tie_word_embeddings=False, attention_dropout=0.0)
+    if kind == "llama":
+        cfg = transformers.LlamaConfig(**common)
+        m = transformers.LlamaForCausalLM(cfg)
+    elif kind == "qwen2":
+        cfg = transformers.Qwen2Config(**common)
+        m = transformers.Qwen2ForCausalLM(cfg)
+    elif kind == "qwen3":
+        cfg = transformers.Qwen3Config(**common, head_dim=64)
+        m = transformers.Qwen3ForCausalLM(cfg)
+    elif kind == "mistral":
+        cfg = transformers.MistralConfig(**common, sliding_window=8)
+        m = transformers.MistralForCausalLM(cfg)
+    elif kind == "llama_tied":
+        common["tie_word_embeddings"] = True
+        cfg = transformers.LlamaConfig(**common)
+        m = transformers.LlamaForCausalLM(cfg)
+    else:
+        raise ValueError(kind)
+    return cfg, m.eval().float()
+
+
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied"])
+def test_decoder_matches_transformers(kind):
+    torch.manual_seed(0)
+    hf_cfg, hf = _hf_decoder(kind)
+    with torch.no_grad():  # make biases and norm gains non-trivial
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+            elif "norm" in n:
+                p.uniform_(0.5, 1.5)
+    _round_linears_to_fp8_grid(hf)
+    cfg = LlamaConfig.from_hf(hf_cfg.to_dict())
+    if kind == "llama_tied":
+        assert cfg.tie_word_embeddings
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    if kind == "llama_tied":
+        sd.pop("lm_head.weight", None)
+    model = LlamaModel.from_state_dict(cfg, sd, device="cpu")
+
+    S, page = 24, 16
+    ids = torch.randint(0, hf_cfg.vocab_size, (S + 1,))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0].float()  # [S + 1, V]
+
+    nblk = 3
+    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    table = torch.arange(nblk, dtype=torch.int32)[None]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    pos = torch.arange(S, dtype=torch.int32)
+    prefill = StepBatch(ids[:S].int(), pos, pos.clone(), i32([0]), i32([S]), i32([S]), table, pos.clone(), S, 1)
+    got_prefill = model.forward(prefill, k_cache, v_cache).float()
+    decode = StepBatch(ids[S:].int(), i32([S]), i32([S]), i32([0]), i32([1]), i32([S + 1]), table, i32([0]), 1, 1)
+    got_decode = model.forward(decode, k_cache, v_cache).float()
+    got = torch.cat([got_prefill, got_decode], 0)
+
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.99, (kind, cos)
+    agree = (got.argmax(-1) == want.argmax(-1)).float().mean()
+    assert float(agree) >= 0.8, (kind, float(agree))
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) < 0.08 * max(scale, 1.0), (kind, float((got - want).abs().max()), scale)
+
+
+@pytest.mark.parametrize("head", [False, True])
+def test_bert_matches_transformers(head):
+    torch.manual_seed(1)
+    hf_cfg = transformers.BertConfig(vocab_size=400, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                     intermediate_size=128, max_position_embeddings=64, num_labels=3,
+                                     hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    hf = (transformers.BertForSequenceClassification(hf_cfg) if head else transformers.BertModel(hf_cfg)).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+    cfg = BertConfig.from_hf(hf_cfg.to_dict())
+    model = BertModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    seqs = [[101] + torch.randint(103, 400, (n,)).tolist() + [102] for n in (5, 17, 30)]
+    types = [[0] * (len(s) // 2) + [1] * (len(s) - len(s) // 2) for s in seqs]
+    batch = pack_sequences(seqs, types)
+    L = max(len(s) for s in seqs)
+    ids = torch.zeros((len(seqs), L), dtype=torch.long)
+    tt = torch.zeros_like(ids)
+    mask = torch.zeros_like(ids)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.tensor(s)
+        tt[i, : len(s)] = torch.tensor(types[i])
+        mask[i, : len(s)] = 1
+    with torch.no_grad():
+        out = hf(input_ids=ids, token_type_ids=tt, attention_mask=mask)
+    if head:
+        got = model.classify(batch).float()
+        torch.testing.assert_close(got, out.logits.float(), atol=3e-2, rtol=3e-2)
+    else:
+        hidden = out.last_hidden_state
+        want = (hidden * mask[..., None]).sum(1) / mask.sum(1, keepdim=True)
+        want = torch.nn.functional.normalize(want, dim=-1)
+        got = model.embed(batch, pooling="mean", normalize=True).float()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        assert float(cos.min()) > 0.999, cos
