@@ -98,8 +98,13 @@ class ModelManager:
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         else:
-            cfg = LlamaConfig.from_hf(cfg_d)
-            model = LlamaModel.from_state_dict(cfg, sd, device=self.device)
+            if cfg_d.get("model_type") in ("gpt2", "gpt_neox", "opt"):
+                from ..models.gpt import GptConfig, GptModel
+
+                model = GptModel.from_state_dict(GptConfig.from_hf(cfg_d), sd, device=self.device)
+            else:
+                cfg = LlamaConfig.from_hf(cfg_d)
+                model = LlamaModel.from_state_dict(cfg, sd, device=self.device)
             eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
                             use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id)
             pipe = Generator(eng, tok, mf.chat_template)

@@ -51,10 +51,11 @@ class Manifest:
         for t in self.tasks:
             if t in ("embedder", "reranker", "generator", "chunker"):
                 return t
-        arch = " ".join(self.config.get("architectures", []))
+        arch = " ".join(self.config.get("architectures") or [])
         if "ForSequenceClassification" in arch:
             return "reranker"
-        if "CausalLM" in arch or self.config.get("model_type") in ("llama", "mistral", "qwen2", "qwen3", "gemma"):
+        if "CausalLM" in arch or self.config.get("model_type") in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gpt2",
+                                                                     "gpt_neox", "opt"):
             return "generator"
         return "embedder"
 

@@ -1,0 +1,240 @@
+"""LayerNorm-based decoder family: GPT-2, GPT-NeoX / Pythia and OPT, on the same paged-KV engine interface as
+:class:`antfly_b200.models.llama.LlamaModel`.
+
+What differs from the Llama family and how it maps onto the existing kernels (the reference covers these under one
+``ModelFamily`` switch, zig/pkg/inference/src/models/gpt.zig:28-233, zig/pkg/inference/src/architectures/gpt.zig):
+
+* LayerNorm with bias instead of RMSNorm: the same norm kernel (``rms=False``, beta), fused with the residual add.
+* biased linears with a GELU (erf or tanh form) / ReLU MLP: the bf16 tcgen05 GEMM with its bias + activation +
+  residual epilogues; weights stay bf16 (these are small models).
+* learned absolute positions (GPT-2, OPT with its offset of 2): added to the token embedding; the RoPE + KV-write
+  kernel is then run with all positions zero, which rotates by the identity and only writes K / V into the cache.
+* partial rotary embedding and the parallel residual of GPT-NeoX (``x + attn(ln1 x) + mlp(ln2 x)``).
+* fused QKV layouts: GPT-2's ``c_attn`` is a transposed ``Conv1D`` [in, 3 * out]; GPT-NeoX interleaves q, k, v per
+  head; both are re-packed at load time into the [q heads | k heads | v heads] rows the kernels expect.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import attention as A
+from ..ops import dense as Dn
+from ..ops import sampling as S
+from .llama import StepBatch
+
+
+@dataclass
+class GptConfig:
+    family: str = "gpt2"              # gpt2 | gpt_neox | opt
+    vocab_size: int = 50257
+    hidden_size: int = 768
+    num_hidden_layers: int = 12
+    num_attention_heads: int = 12
+    intermediate_size: int = 3072
+    max_position_embeddings: int = 1024
+    layer_norm_eps: float = 1e-5
+    activation: str = "gelu_tanh"     # gelu | gelu_tanh | relu
+    rope_theta: float = 10000.0
+    rotary_pct: float = 0.0           # 0: learned absolute positions
+    parallel_residual: bool = False
+    position_offset: int = 0          # OPT: 2
+    tie_word_embeddings: bool = True
+    sliding_window: int = 0
+
+    # Names the engine reads from every decoder config.
+    @property
+    def num_key_value_heads(self) -> int:
+        return self.num_attention_heads
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_hf(cls, d: dict) -> "GptConfig":
+        mt = d.get("model_type", "gpt2")
+        act = {"gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_fast": "gelu_tanh", "gelu": "gelu",
+               "relu": "relu"}
+        if mt == "gpt2":
+            H = d.get("n_embd", d.get("hidden_size", 768))
+            return cls("gpt2", d["vocab_size"], H, d.get("n_layer", d.get("num_hidden_layers", 12)),
+                       d.get("n_head", d.get("num_attention_heads", 12)), d.get("n_inner") or 4 * H,
+                       d.get("n_positions", d.get("max_position_embeddings", 1024)),
+                       d.get("layer_norm_epsilon", 1e-5), act[d.get("activation_function", "gelu_new")],
+                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if mt == "gpt_neox":
+            rp = d.get("rope_parameters") or d.get("rope_scaling") or {}
+            theta = d.get("rope_theta") or d.get("rotary_emb_base") or rp.get("rope_theta") or 10000.0
+            pct = d.get("rotary_pct") or rp.get("partial_rotary_factor") or d.get("partial_rotary_factor") or 1.0
+            return cls("gpt_neox", d["vocab_size"], d["hidden_size"], d["num_hidden_layers"],
+                       d["num_attention_heads"], d["intermediate_size"], d.get("max_position_embeddings", 2048),
+                       d.get("layer_norm_eps", 1e-5), act[d.get("hidden_act", "gelu")], float(theta), float(pct),
+                       bool(d.get("use_parallel_residual", True)),
+                       tie_word_embeddings=d.get("tie_word_embeddings", False))
+        if mt == "opt":
+            assert d.get("do_layer_norm_before", True), "post-LayerNorm OPT variants (350m) are not supported"
+            assert d.get("word_embed_proj_dim", d["hidden_size"]) == d["hidden_size"]
+            return cls("opt", d["vocab_size"], d["hidden_size"], d["num_hidden_layers"], d["num_attention_heads"],
+                       d["ffn_dim"], d.get("max_position_embeddings", 2048), 1e-5,
+                       act[d.get("activation_function", "relu")], position_offset=2,
+                       tie_word_embeddings=d.get("tie_word_embeddings", True))
+        raise ValueError(f"unsupported model_type {mt!r}")
+
+
+_ACT = {"gelu": "gelu", "gelu_tanh": "gelu_tanh", "relu": "relu"}
+
+
+class GptModel:
+    """Same call surface as LlamaModel (``forward(StepBatch, k_cache, v_cache)``, ``greedy_tokens``, ``Hq``,
+    ``Hkv``, ``D``, ``n_layers``) so the engine, the scheduler and speculative decoding work unchanged."""
+
+    tp_rank, tp_size, comm, fused = 0, 1, None, None
+
+    def __init__(self, cfg: GptConfig, weights: Dict[str, torch.Tensor]):
+        self.cfg, self.w = cfg, weights
+        self.device = weights["embed"].device
+        self.Hq = self.Hkv = cfg.num_attention_heads
+        self.D = cfg.head_dim
+        self.n_layers = cfg.num_hidden_layers
+        self.rope_dim = int(round(self.D * cfg.rotary_pct)) if cfg.rotary_pct > 0 else 0
+        self.vocab_local, self.vocab_offset = weights["lm_head"].shape[0], 0
+        self._zero_pos: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------------------------------------------
+    @classmethod
+    def from_state_dict(cls, cfg: GptConfig, sd: Dict[str, torch.Tensor], device="cuda",
+                        dtype=torch.bfloat16) -> "GptModel":
+        H, nh, D = cfg.hidden_size, cfg.num_attention_heads, cfg.head_dim
+        t = lambda x: x.to(dtype).to(device).contiguous()
+        w: Dict[str, torch.Tensor] = {}
+        if cfg.family == "gpt2":
+            pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
+            w["embed"], w["pos"] = t(sd[pre + "wte.weight"]), t(sd[pre + "wpe.weight"])
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}h.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "ln_1.weight"]), t(sd[s + "ln_1.bias"])
+                w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "ln_2.weight"]), t(sd[s + "ln_2.bias"])
+                # Conv1D stores [in, out]; the kernels want nn.Linear's [out, in]
+                w[p + "qkv.w"], w[p + "qkv.b"] = t(sd[s + "attn.c_attn.weight"].t()), t(sd[s + "attn.c_attn.bias"])
+                w[p + "o.w"], w[p + "o.b"] = t(sd[s + "attn.c_proj.weight"].t()), t(sd[s + "attn.c_proj.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.c_fc.weight"].t()), t(sd[s + "mlp.c_fc.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.c_proj.weight"].t()), t(sd[s + "mlp.c_proj.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "ln_f.weight"]), t(sd[pre + "ln_f.bias"])
+            w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
+                w["embed"]
+        elif cfg.family == "gpt_neox":
+            pre = "gpt_neox." if any(k.startswith("gpt_neox.") for k in sd) else ""
+            w["embed"] = t(sd[pre + "embed_in.weight"])
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}layers.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "input_layernorm.weight"]), t(sd[s + "input_layernorm.bias"])
+                w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "post_attention_layernorm.weight"]), t(
+                    sd[s + "post_attention_layernorm.bias"])
+                # rows are [head][q | k | v][D]; regroup to [q heads | k heads | v heads]
+                qkv_w = sd[s + "attention.query_key_value.weight"].view(nh, 3, D, H).permute(1, 0, 2, 3).reshape(
+                    3 * H, H)
+                qkv_b = sd[s + "attention.query_key_value.bias"].view(nh, 3, D).permute(1, 0, 2).reshape(3 * H)
+                w[p + "qkv.w"], w[p + "qkv.b"] = t(qkv_w), t(qkv_b)
+                w[p + "o.w"], w[p + "o.b"] = t(sd[s + "attention.dense.weight"]), t(sd[s + "attention.dense.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.dense_h_to_4h.weight"]), t(sd[s + "mlp.dense_h_to_4h.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.dense_4h_to_h.weight"]), t(
+                    sd[s + "mlp.dense_4h_to_h.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layer_norm.weight"]), t(sd[pre + "final_layer_norm.bias"])
+            w["lm_head"] = t(sd["embed_out.weight"]) if "embed_out.weight" in sd else w["embed"]
+        elif cfg.family == "opt":
+            pre = "model.decoder." if any(k.startswith("model.decoder.") for k in sd) else "decoder."
+            w["embed"], w["pos"] = t(sd[pre + "embed_tokens.weight"]), t(sd[pre + "embed_positions.weight"])
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}layers.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "self_attn_layer_norm.weight"]), t(
+                    sd[s + "self_attn_layer_norm.bias"])
+                w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "final_layer_norm.weight"]), t(sd[s + "final_layer_norm.bias"])
+                w[p + "qkv.w"] = t(torch.cat([sd[s + f"self_attn.{n}_proj.weight"] for n in ("q", "k", "v")], 0))
+                w[p + "qkv.b"] = t(torch.cat([sd[s + f"self_attn.{n}_proj.bias"] for n in ("q", "k", "v")], 0))
+                w[p + "o.w"], w[p + "o.b"] = t(sd[s + "self_attn.out_proj.weight"]), t(sd[s + "self_attn.out_proj.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "fc1.weight"]), t(sd[s + "fc1.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "fc2.weight"]), t(sd[s + "fc2.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layer_norm.weight"]), t(sd[pre + "final_layer_norm.bias"])
+            w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
+                w["embed"]
+        else:
+            raise ValueError(cfg.family)
+        return cls(cfg, w)
+
+    @classmethod
+    def random_init(cls, cfg: GptConfig, device="cuda", seed: int = 0, dtype=torch.bfloat16) -> "GptModel":
+        g = torch.Generator().manual_seed(seed)
+        H, F = cfg.hidden_size, cfg.intermediate_size
+        rnd = lambda *s, std=0.02: (torch.randn(*s, generator=g) * std).to(dtype).to(device)
+        w: Dict[str, torch.Tensor] = {"embed": rnd(cfg.vocab_size, H)}
+        if cfg.rotary_pct <= 0:
+            w["pos"] = rnd(cfg.max_position_embeddings + cfg.position_offset, H)
+        for l in range(cfg.num_hidden_layers):
+            p = f"l{l}."
+            for n in ("ln1", "ln2"):
+                w[p + n + ".g"], w[p + n + ".b"] = torch.ones(H, dtype=dtype, device=device), rnd(H)
+            w[p + "qkv.w"], w[p + "qkv.b"] = rnd(3 * H, H), rnd(3 * H)
+            w[p + "o.w"], w[p + "o.b"] = rnd(H, H), rnd(H)
+            w[p + "fc.w"], w[p + "fc.b"] = rnd(F, H), rnd(F)
+            w[p + "proj.w"], w[p + "proj.b"] = rnd(H, F), rnd(H)
+        w["lnf.g"], w["lnf.b"] = torch.ones(H, dtype=dtype, device=device), rnd(H)
+        w["lm_head"] = w["embed"] if cfg.tie_word_embeddings else rnd(cfg.vocab_size, H)
+        return cls(cfg, w)
+
+    # ------------------------------------------------------------------------------------------------------
+    def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        Hq, D, eps = self.Hq, self.D, cfg.layer_norm_eps
+        T = b.ids.numel()
+        act = _ACT[cfg.activation]
+        x = Dn.embed_gather(b.ids, w["embed"])
+        if "pos" in w:
+            x = x + w["pos"].index_select(0, (b.positions + cfg.position_offset).long())
+            if self._zero_pos is None or self._zero_pos.numel() < T:
+                self._zero_pos = torch.zeros(max(T, 1024), dtype=torch.int32, device=x.device)
+            rope_pos, rope_dim = self._zero_pos[:T], D  # identity rotation: the kernel only writes K / V
+        else:
+            rope_pos, rope_dim = b.positions, self.rope_dim
+        for l in range(self.n_layers):
+            p = f"l{l}."
+            h = Dn.norm(x, w[p + "ln1.g"], w[p + "ln1.b"], eps=eps, rms=False)
+            qkv = Dn.gemm_bf16(h, w[p + "qkv.w"], bias=w[p + "qkv.b"])
+            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache[l], v_cache[l], Hq, Hq, D, cfg.rope_theta,
+                                rope_dim=rope_dim, half_split=True)
+            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    scratch=attn_scratch)
+            if cfg.parallel_residual:
+                # x + attn(ln1 x) + mlp(ln2 x): both branches read the same x
+                a_out = Dn.gemm_bf16(ctx.view(T, Hq * D), w[p + "o.w"], bias=w[p + "o.b"], residual=x)
+                h2 = Dn.norm(x, w[p + "ln2.g"], w[p + "ln2.b"], eps=eps, rms=False)
+                m = Dn.gemm_bf16(h2, w[p + "fc.w"], bias=w[p + "fc.b"], act=act)
+                x = Dn.gemm_bf16(m, w[p + "proj.w"], bias=w[p + "proj.b"], residual=a_out)
+            else:
+                x = Dn.gemm_bf16(ctx.view(T, Hq * D), w[p + "o.w"], bias=w[p + "o.b"], residual=x)
+                h2 = Dn.norm(x, w[p + "ln2.g"], w[p + "ln2.b"], eps=eps, rms=False)
+                m = Dn.gemm_bf16(h2, w[p + "fc.w"], bias=w[p + "fc.b"], act=act)
+                x = Dn.gemm_bf16(m, w[p + "proj.w"], bias=w[p + "proj.b"], residual=x)
+        rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
+        hl = Dn.norm(rows, w["lnf.g"], w["lnf.b"], eps=eps, rms=False)
+        return Dn.gemm_bf16(hl, w["lm_head"])
+
+    def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        return S.argmax(logits)
+
+    def draft_view(self, n_layers: int) -> "GptModel":
+        m = GptModel(self.cfg, self.w)
+        m.n_layers = n_layers
+        return m
+
+    def weight_bytes(self) -> int:
+        seen, n = set(), 0
+        for v in self.w.values():
+            if v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                n += v.numel() * v.element_size()
+        return n

@@ -50,3 +50,37 @@ def test_sampling_with_penalties_runs_and_respects_limits():
     out = eng.generate([[1, 2, 3], [4, 5, 6, 7]], sp)
     assert all(len(r.token_ids) == 5 for r in out)
     assert all(0 <= t < 512 for r in out for t in r.token_ids)
+
+
+def test_engine_generates_with_layernorm_decoder_family():
+    """The paged-KV engine drives a GPT-2-style model (learned positions, LayerNorm, GELU MLP) exactly like a
+    Llama-style one: greedy continuation equals a step-by-step full-recompute of the same model."""
+    import torch
+
+    from antfly_b200.models.gpt import GptConfig, GptModel
+    from antfly_b200.models.llama import StepBatch
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    cfg = GptConfig("gpt2", vocab_size=200, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                    intermediate_size=128, max_position_embeddings=64)
+    model = GptModel.random_init(cfg, device="cpu", seed=3, dtype=torch.float32)
+    eng = LLMEngine(model, num_blocks=16, page=16, max_batch=2, max_step_tokens=64, prefill_chunk=8,
+                    max_seq_len=48, use_cuda_graph=False)
+    prompt = [5, 17, 99, 3, 42, 7, 150, 21, 8, 64, 11]
+    rid = eng.add_request(prompt, SamplingParams(max_tokens=6, ignore_eos=True))
+    while eng.has_work():
+        eng.step()
+    got = list(eng.reqs[rid].out)
+
+    seq = list(prompt)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    for _ in range(6):
+        n = len(seq)
+        kc = torch.zeros((2, 4, 16, 4, 16), dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        pos = torch.arange(n, dtype=torch.int32)
+        b = StepBatch(i32(seq), pos, pos.clone(), i32([0]), i32([n]), i32([n]), torch.arange(4, dtype=torch.int32)[None],
+                      i32([n - 1]), n, 1)
+        seq.append(int(model.forward(b, kc, vc).float().argmax(-1)))
+    assert got == seq[len(prompt):], (got, seq[len(prompt):])

@@ -127,3 +127,52 @@ def test_bert_matches_transformers(head):
         got = model.embed(batch, pooling="mean", normalize=True).float()
         cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
         assert float(cos.min()) > 0.999, cos
+
+
+def _hf_gpt(kind: str):
+    if kind == "gpt2":
+        cfg = transformers.GPT2Config(vocab_size=300, n_positions=64, n_embd=64, n_layer=2, n_head=4,
+                                      resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        return cfg, transformers.GPT2LMHeadModel(cfg)
+    if kind.startswith("neox"):
+        cfg = transformers.GPTNeoXConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                         intermediate_size=128, max_position_embeddings=64, rotary_pct=0.25,
+                                         use_parallel_residual=kind == "neox_parallel", hidden_dropout=0.0,
+                                         attention_dropout=0.0, tie_word_embeddings=False)
+        return cfg, transformers.GPTNeoXForCausalLM(cfg)
+    cfg = transformers.OPTConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                 ffn_dim=128, max_position_embeddings=64, word_embed_proj_dim=64, dropout=0.0,
+                                 attention_dropout=0.0)
+    return cfg, transformers.OPTForCausalLM(cfg)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt"])
+def test_layernorm_decoders_match_transformers(kind):
+    from antfly_b200.models.gpt import GptConfig, GptModel
+
+    torch.manual_seed(2)
+    hf_cfg, hf = _hf_gpt(kind)
+    hf = hf.eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+    cfg = GptConfig.from_hf(hf_cfg.to_dict())
+    model = GptModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    S, page, nblk = 20, 16, 2
+    ids = torch.randint(0, hf_cfg.vocab_size, (S + 1,))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0].float()
+    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, model.D), dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    table = torch.arange(nblk, dtype=torch.int32)[None]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    pos = torch.arange(S, dtype=torch.int32)
+    got = torch.cat([
+        model.forward(StepBatch(ids[:S].int(), pos, pos.clone(), i32([0]), i32([S]), i32([S]), table, pos.clone(),
+                                S, 1), k_cache, v_cache).float(),
+        model.forward(StepBatch(ids[S:].int(), i32([S]), i32([S]), i32([0]), i32([1]), i32([S + 1]), table,
+                                i32([0]), 1, 1), k_cache, v_cache).float()], 0)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.995, (kind, cos)
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.85
