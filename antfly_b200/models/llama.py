@@ -45,6 +45,9 @@ class LlamaConfig:
     qk_norm: bool = False         # Qwen3 per-head RMS norm on Q and K
     sliding_window: int = 0       # Mistral
     max_position_embeddings: int = 131072
+    norm_plus_one: bool = False   # Gemma: RMSNorm scales by (1 + gamma)
+    embed_scale: float = 1.0      # Gemma: token embeddings multiplied by sqrt(hidden)
+    gate_act: str = "silu"        # gated-MLP activation: silu (SwiGLU) or gelu_tanh (GeGLU, Gemma)
 
     def __post_init__(self):
         if not self.head_dim:
@@ -74,6 +77,11 @@ class LlamaConfig:
             cfg.qkv_bias = True
         if mt == "qwen3":
             cfg.qk_norm = True
+        if mt == "gemma":
+            cfg.norm_plus_one = True
+            cfg.embed_scale = float(cfg.hidden_size) ** 0.5
+            cfg.gate_act = "gelu_tanh"
+            cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
         return cfg
 
     @classmethod
@@ -208,6 +216,15 @@ class LlamaModel:
             s, p = f"{pre}layers.{l}.", f"l{l}."
             w[p + "ln1"] = sd[s + "input_layernorm.weight"].to(torch.bfloat16).to(device)
             w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
+            if s + "self_attn.qkv_proj.weight" in sd:  # Phi-3: fused [q | k | v] rows
+                nq, nk = cfg.num_attention_heads * D, cfg.num_key_value_heads * D
+                fused = sd[s + "self_attn.qkv_proj.weight"]
+                sd[s + "self_attn.q_proj.weight"], sd[s + "self_attn.k_proj.weight"] = fused[:nq], fused[nq:nq + nk]
+                sd[s + "self_attn.v_proj.weight"] = fused[nq + nk:]
+            if s + "mlp.gate_up_proj.weight" in sd:    # Phi-3: fused [gate ; up] rows
+                gu_f = sd[s + "mlp.gate_up_proj.weight"]
+                sd[s + "mlp.gate_proj.weight"], sd[s + "mlp.up_proj.weight"] = gu_f[: gu_f.shape[0] // 2], gu_f[
+                    gu_f.shape[0] // 2:]
             q = shard_rows(sd[s + "self_attn.q_proj.weight"], tp_rank, tp_size)
             k = shard_rows(sd[s + "self_attn.k_proj.weight"], tp_rank, tp_size)
             v = shard_rows(sd[s + "self_attn.v_proj.weight"], tp_rank, tp_size)
@@ -224,7 +241,7 @@ class LlamaModel:
             w[p + "gu"] = Q.pack_fp8_swiglu(gate, up)
             w[p + "down"] = Q.pack_fp8(shard_cols(sd[s + "mlp.down_proj.weight"], tp_rank, tp_size).to(device))
         w["norm"] = sd[pre + "norm.weight"].to(torch.bfloat16).to(device)
-        head = sd.get("lm_head.weight", emb)
+        head = emb if cfg.tie_word_embeddings else sd.get("lm_head.weight", emb)
         w["lm_head"] = Q.pack_fp8(shard_rows(head, tp_rank, tp_size).to(device) if tp_size > 1 else head.to(device))
         return cls(cfg, w, tp_rank, tp_size, comm)
 
@@ -350,11 +367,55 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    def _forward_general(self, b: StepBatch, k_cache, v_cache, attn_scratch) -> torch.Tensor:
+        """Variants the fused decode path does not special-case (Gemma: (1 + gamma) norms, scaled embeddings,
+        GeGLU): same kernels, with the gated activation applied between the gate/up and down GEMMs instead of in
+        an epilogue.  Single GPU."""
+        assert self.tp_size == 1, "this model variant runs on one GPU"
+        cfg, w = self.cfg, self.w
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        T = b.ids.numel()
+        gp1, eps = cfg.norm_plus_one, cfg.rms_norm_eps
+        x = Dn.embed_gather(b.ids, w["embed"], scale=cfg.embed_scale)
+        h = Dn.norm(x, w["l0.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
+        for l in range(self.n_layers):
+            p = f"l{l}."
+            qkv = self._linear(h, w[p + "qkv"], T)
+            q = A.rope_kv_write(qkv, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
+                                bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
+                                freq_scale=cfg.rope_freq_scale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
+                                norm_eps=eps, norm_plus_one=gp1)
+            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    scratch=attn_scratch)
+            x = self._linear(ctx.view(T, Hq * D), w[p + "o"], T, residual=x)
+            h = Dn.norm(x, w[p + "ln2"], eps=eps, rms=True, gamma_plus_one=gp1)
+            gu = self._linear(h, w[p + "gu"], T).float()  # columns alternate gate_i, up_i
+            gate, up = gu[:, 0::2], gu[:, 1::2]
+            if cfg.gate_act == "gelu_tanh":
+                gate = torch.nn.functional.gelu(gate, approximate="tanh")
+            elif cfg.gate_act == "gelu":
+                gate = torch.nn.functional.gelu(gate)
+            else:
+                gate = torch.nn.functional.silu(gate)
+            x = self._linear((gate * up).to(torch.bfloat16), w[p + "down"], T, residual=x)
+            nw = w["norm"] if l + 1 == self.n_layers else w[f"l{l + 1}.ln1"]
+            if l + 1 < self.n_layers:
+                h = Dn.norm(x, nw, eps=eps, rms=True, gamma_plus_one=gp1)
+        rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
+        hl = Dn.norm(rows, w["norm"], eps=eps, rms=True, gamma_plus_one=gp1)
+        head = w["lm_head"]
+        if isinstance(head, Q.Fp8Weight):
+            return self._linear(hl, head, rows.shape[0])
+        return Dn.gemm_bf16(hl, head)
+
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
         """Runs the stack on one step batch; K/V of the step's tokens are written into
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
+        if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu":
+            return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)
                 and b.ids.numel() <= self.fused.ws.max_tokens):

@@ -38,6 +38,12 @@ def _hf_decoder(kind: str):
     elif kind == "mistral":
         cfg = transformers.MistralConfig(**common, sliding_window=8)
         m = transformers.MistralForCausalLM(cfg)
+    elif kind == "gemma":
+        cfg = transformers.GemmaConfig(**{**common, "head_dim": 64, "hidden_activation": "gelu_pytorch_tanh"})
+        m = transformers.GemmaForCausalLM(cfg)
+    elif kind == "phi3":
+        cfg = transformers.Phi3Config(**{**common, "pad_token_id": 0})
+        m = transformers.Phi3ForCausalLM(cfg)
     elif kind == "llama_tied":
         common["tie_word_embeddings"] = True
         cfg = transformers.LlamaConfig(**common)
@@ -47,7 +53,7 @@ def _hf_decoder(kind: str):
     return cfg, m.eval().float()
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "phi3"])
 def test_decoder_matches_transformers(kind):
     torch.manual_seed(0)
     hf_cfg, hf = _hf_decoder(kind)
@@ -56,7 +62,7 @@ def test_decoder_matches_transformers(kind):
             if n.endswith("bias"):
                 p.normal_(0, 0.05)
             elif "norm" in n:
-                p.uniform_(0.5, 1.5)
+                p.uniform_(-0.3, 0.3) if kind == "gemma" else p.uniform_(0.5, 1.5)
     _round_linears_to_fp8_grid(hf)
     cfg = LlamaConfig.from_hf(hf_cfg.to_dict())
     if kind == "llama_tied":
