@@ -1,5 +1,6 @@
 // CPU codecs for quantised artifact formats (the numerical authority the GPU paths are tested against):
-// GGUF Q8_0 / Q4_0 / Q4_K / MXFP4 block dequantisation, fp16 / bf16 widening, fp8 E4M3 encode / decode and the
+// GGUF block dequantisation (legacy Q4/Q5/Q8, the K-quants Q2_K..Q6_K and Q8_K, IQ4_NL / IQ4_XS, ternary TQ1_0 /
+// TQ2_0, MXFP4, NVFP4), fp16 / bf16 widening, fp8 E4M3 encode / decode and the
 // int8 / int4 KV-cache encodings.
 //
 // Block geometry and decode rules follow the reference's gguf/tensor_types.zig:160-214 and gguf/quant_codec.zig
@@ -75,25 +76,46 @@ inline void q4k_scale_min(int j, const uint8_t* q, uint8_t* d, uint8_t* m) {
   }
 }
 
+inline float load_half(const uint8_t* p) {
+  uint16_t h;
+  memcpy(&h, p, 2);
+  return half_to_float(h);
+}
+
+// Unsigned e4m3 (4 exponent bits, bias 7, 3 mantissa bits, no sign): the NVFP4 sub-block scale.
+inline float ue4m3_to_float(uint8_t v) {
+  const int exp = (v >> 3) & 0xF, man = v & 7;
+  if (exp == 0) return man / 8.0f * 0.015625f;
+  if (exp == 15 && man == 7) return 0.0f;
+  return (1.0f + man / 8.0f) * ldexpf(1.0f, exp - 7);
+}
+
+const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
 const float kMxfp4Values[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
 
 }  // namespace
 
 extern "C" {
 
-// type ids: 0 F32, 1 F16, 2 Q4_0, 8 Q8_0, 12 Q4_K, 30 BF16, 39 MXFP4 (ggml numbering).
+// type ids (ggml numbering): 0 F32, 1 F16, 2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K,
+// 13 Q5_K, 14 Q6_K, 15 Q8_K, 20 IQ4_NL, 23 IQ4_XS, 30 BF16, 34 TQ1_0, 35 TQ2_0, 39 MXFP4, 40 NVFP4.
 long afb_gguf_block_bytes(int type) {
   switch (type) {
     case 0: return 4; case 1: return 2; case 30: return 2;
-    case 2: return 18; case 8: return 34; case 12: return 144; case 39: return 17;
+    case 2: return 18; case 3: return 20; case 6: return 22; case 7: return 24; case 8: return 34;
+    case 10: return 84; case 11: return 110; case 12: return 144; case 13: return 176; case 14: return 210;
+    case 15: return 292; case 20: return 18; case 23: return 136; case 34: return 54; case 35: return 66;
+    case 39: return 17; case 40: return 36;
     default: return -1;
   }
 }
 long afb_gguf_block_values(int type) {
   switch (type) {
     case 0: case 1: case 30: return 1;
-    case 2: case 8: case 39: return 32;
-    case 12: return 256;
+    case 2: case 3: case 6: case 7: case 8: case 20: case 39: return 32;
+    case 40: return 64;
+    case 10: case 11: case 12: case 13: case 14: case 15: case 23: case 34: case 35: return 256;
     default: return -1;
   }
 }
@@ -159,6 +181,227 @@ int afb_gguf_dequantize(int type, const uint8_t* src, float* dst, long n_values)
         for (int j = 0; j < 16; ++j) {
           dst[b * 32 + j] = kMxfp4Values[p[1 + j] & 0xF] * d;
           dst[b * 32 + j + 16] = kMxfp4Values[p[1 + j] >> 4] * d;
+        }
+      }
+      return 0;
+    }
+    case 3: {  // Q4_1: fp16 d, fp16 m, 16 nibble bytes; x = d * q + m
+      for (long b = 0; b < n_values / 32; ++b) {
+        const uint8_t* p = src + b * 20;
+        const float d = load_half(p), m = load_half(p + 2);
+        const uint8_t* q = p + 4;
+        for (int j = 0; j < 16; ++j) {
+          dst[b * 32 + j] = d * (q[j] & 0xF) + m;
+          dst[b * 32 + j + 16] = d * (q[j] >> 4) + m;
+        }
+      }
+      return 0;
+    }
+    case 6: case 7: {  // Q5_0 (fp16 d, offset 16) / Q5_1 (fp16 d, fp16 m): 32 fifth bits, then 16 nibble bytes
+      const bool has_min = type == 7;
+      const int bytes = has_min ? 24 : 22;
+      for (long b = 0; b < n_values / 32; ++b) {
+        const uint8_t* p = src + b * bytes;
+        const float d = load_half(p), m = has_min ? load_half(p + 2) : 0.0f;
+        uint32_t qh; memcpy(&qh, p + (has_min ? 4 : 2), 4);
+        const uint8_t* q = p + (has_min ? 8 : 6);
+        for (int j = 0; j < 16; ++j) {
+          const int lo = (q[j] & 0xF) | (((qh >> j) & 1u) << 4);
+          const int hi = (q[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4);
+          dst[b * 32 + j] = has_min ? d * lo + m : d * (lo - 16);
+          dst[b * 32 + j + 16] = has_min ? d * hi + m : d * (hi - 16);
+        }
+      }
+      return 0;
+    }
+    case 10: {  // Q2_K: 16 x (4-bit scale | 4-bit min), 64 bytes of 2-bit values, fp16 d, fp16 dmin
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 84;
+        const uint8_t* scales = p;
+        const uint8_t* q = p + 16;
+        const float d = load_half(p + 80), dmin = load_half(p + 82);
+        float* y = dst + b * 256;
+        int is = 0;
+        for (int n = 0; n < 256; n += 128) {
+          for (int shift = 0; shift < 8; shift += 2) {
+            for (int half = 0; half < 2; ++half) {
+              const uint8_t sc = scales[is++];
+              const float dl = d * (sc & 0xF), ml = dmin * (sc >> 4);
+              for (int l = 0; l < 16; ++l) *y++ = dl * ((q[l + 16 * half] >> shift) & 3) - ml;
+            }
+          }
+          q += 32;
+        }
+      }
+      return 0;
+    }
+    case 11: {  // Q3_K: 32 bytes of high bits, 64 bytes of low 2-bit values, 16 six-bit scales in 12 bytes, fp16 d
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 110;
+        const uint8_t* hm = p;
+        const uint8_t* q = p + 32;
+        const float d_all = load_half(p + 108);
+        uint32_t aux[4] = {0, 0, 0, 0};
+        memcpy(aux, p + 96, 12);
+        const uint32_t k1 = 0x03030303u, k2 = 0x0f0f0f0fu, tmp = aux[2];
+        aux[2] = ((aux[0] >> 4) & k2) | (((tmp >> 4) & k1) << 4);
+        aux[3] = ((aux[1] >> 4) & k2) | (((tmp >> 6) & k1) << 4);
+        aux[0] = (aux[0] & k2) | (((tmp >> 0) & k1) << 4);
+        aux[1] = (aux[1] & k2) | (((tmp >> 2) & k1) << 4);
+        int8_t scales[16];
+        memcpy(scales, aux, 16);
+        float* y = dst + b * 256;
+        int is = 0;
+        uint8_t m = 1;
+        for (int n = 0; n < 256; n += 128) {
+          for (int shift = 0; shift < 8; shift += 2) {
+            for (int half = 0; half < 2; ++half) {
+              const float dl = d_all * (scales[is++] - 32);
+              for (int l = 0; l < 16; ++l) {
+                const int lo = (q[l + 16 * half] >> shift) & 3;
+                *y++ = dl * (lo - ((hm[l + 16 * half] & m) ? 0 : 4));
+              }
+            }
+            m <<= 1;
+          }
+          q += 32;
+        }
+      }
+      return 0;
+    }
+    case 13: {  // Q5_K: fp16 d, fp16 dmin, 12 scale bytes (as Q4_K), 32 bytes of fifth bits, 128 nibble bytes
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 176;
+        const float d = load_half(p), dmin = load_half(p + 2);
+        const uint8_t* sc = p + 4;
+        const uint8_t* qh = p + 16;
+        const uint8_t* ql = p + 48;
+        float* y = dst + b * 256;
+        int is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (int j = 0; j < 256; j += 64) {
+          uint8_t s1, m1, s2, m2;
+          q4k_scale_min(is, sc, &s1, &m1);
+          q4k_scale_min(is + 1, sc, &s2, &m2);
+          const float d1 = d * s1, mm1 = dmin * m1, d2 = d * s2, mm2 = dmin * m2;
+          for (int l = 0; l < 32; ++l) *y++ = d1 * ((ql[l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - mm1;
+          for (int l = 0; l < 32; ++l) *y++ = d2 * ((ql[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - mm2;
+          ql += 32;
+          is += 2;
+          u1 <<= 2;
+          u2 <<= 2;
+        }
+      }
+      return 0;
+    }
+    case 14: {  // Q6_K: 128 bytes of low nibbles, 64 bytes of high 2-bit pairs, 16 int8 scales, fp16 d
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 210;
+        const uint8_t* ql = p;
+        const uint8_t* qh = p + 128;
+        const int8_t* sc = reinterpret_cast<const int8_t*>(p + 192);
+        const float d = load_half(p + 208);
+        float* y = dst + b * 256;
+        for (int n = 0; n < 256; n += 128) {
+          for (int l = 0; l < 32; ++l) {
+            const int is = l / 16;
+            const int q1 = static_cast<int>((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+            const int q2 = static_cast<int>((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+            const int q3 = static_cast<int>((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+            const int q4 = static_cast<int>((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+            y[l] = d * sc[is] * q1;
+            y[l + 32] = d * sc[is + 2] * q2;
+            y[l + 64] = d * sc[is + 4] * q3;
+            y[l + 96] = d * sc[is + 6] * q4;
+          }
+          y += 128; ql += 64; qh += 32; sc += 8;
+        }
+      }
+      return 0;
+    }
+    case 15: {  // Q8_K: fp32 d, 256 int8 values, 16 int16 block sums (unused when decoding)
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 292;
+        float d; memcpy(&d, p, 4);
+        const int8_t* q = reinterpret_cast<const int8_t*>(p + 4);
+        for (int j = 0; j < 256; ++j) dst[b * 256 + j] = d * q[j];
+      }
+      return 0;
+    }
+    case 20: {  // IQ4_NL: fp16 d, 16 nibble bytes indexing a fixed non-linear 16-entry table
+      for (long b = 0; b < n_values / 32; ++b) {
+        const uint8_t* p = src + b * 18;
+        const float d = load_half(p);
+        for (int j = 0; j < 16; ++j) {
+          dst[b * 32 + j] = d * kIq4nlValues[p[2 + j] & 0xF];
+          dst[b * 32 + j + 16] = d * kIq4nlValues[p[2 + j] >> 4];
+        }
+      }
+      return 0;
+    }
+    case 23: {  // IQ4_XS: fp16 d, 8 six-bit sub-block scales (2 high bits in a u16, 4 low bits in nibbles), 128 nibble bytes
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 136;
+        const float d = load_half(p);
+        uint16_t sh; memcpy(&sh, p + 2, 2);
+        const uint8_t* sl = p + 4;
+        const uint8_t* q = p + 8;
+        float* y = dst + b * 256;
+        for (int ib = 0; ib < 8; ++ib) {
+          const int ls = ((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4);
+          const float dl = d * (ls - 32);
+          for (int j = 0; j < 16; ++j) {
+            y[j] = dl * kIq4nlValues[q[j] & 0xF];
+            y[j + 16] = dl * kIq4nlValues[q[j] >> 4];
+          }
+          y += 32; q += 16;
+        }
+      }
+      return 0;
+    }
+    case 34: {  // TQ1_0: ternary digits packed five per byte (base 3, fixed-point), 48 + 4 bytes, fp16 d
+      static const uint8_t pow3[6] = {1, 3, 9, 27, 81, 243};
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 54;
+        const uint8_t* qs = p;
+        const uint8_t* qh = p + 48;
+        const float d = load_half(p + 52);
+        float* y = dst + b * 256;
+        auto digit = [](uint8_t byte, uint8_t mul) -> int {
+          const uint8_t q = static_cast<uint8_t>(byte * mul);
+          return static_cast<int>((static_cast<uint16_t>(q) * 3) >> 8);
+        };
+        for (int n = 0; n < 5; ++n)
+          for (int m = 0; m < 32; ++m) *y++ = (digit(qs[m], pow3[n]) - 1) * d;
+        for (int n = 0; n < 5; ++n)
+          for (int m = 0; m < 16; ++m) *y++ = (digit(qs[32 + m], pow3[n]) - 1) * d;
+        for (int n = 0; n < 4; ++n)
+          for (int j = 0; j < 4; ++j) *y++ = (digit(qh[j], pow3[n]) - 1) * d;
+      }
+      return 0;
+    }
+    case 35: {  // TQ2_0: ternary values in 2 bits, 64 bytes, fp16 d
+      for (long b = 0; b < n_values / 256; ++b) {
+        const uint8_t* p = src + b * 66;
+        const float d = load_half(p + 64);
+        float* y = dst + b * 256;
+        for (int j = 0; j < 64; j += 32)
+          for (int l = 0; l < 4; ++l)
+            for (int m = 0; m < 32; ++m) *y++ = (static_cast<int>((p[j + m] >> (l * 2)) & 3) - 1) * d;
+      }
+      return 0;
+    }
+    case 40: {  // NVFP4: four unsigned-e4m3 scales, then four 16-value sub-blocks of e2m1 nibbles (8 bytes each)
+      for (long b = 0; b < n_values / 64; ++b) {
+        const uint8_t* p = src + b * 36;
+        for (int sub = 0; sub < 4; ++sub) {
+          const float d = ue4m3_to_float(p[sub]);
+          const uint8_t* q = p + 4 + sub * 8;
+          float* y = dst + b * 64 + sub * 16;
+          for (int j = 0; j < 8; ++j) {
+            y[j] = kMxfp4Values[q[j] & 0xF] * d;
+            y[j + 8] = kMxfp4Values[q[j] >> 4] * d;
+          }
         }
       }
       return 0;

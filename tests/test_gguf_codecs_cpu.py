@@ -1,0 +1,81 @@
+"""GGUF block codecs against the `gguf` Python package's reference (numpy) dequantisers: random block bytes with
+finite scale fields are decoded by both and must agree exactly (same arithmetic in fp32), for every block format
+the C++ decoder knows; plus the NVFP4 golden vector from the reference's own unit test
+(zig/pkg/inference/src/gguf/quant_codec.zig:4327-4340)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+gguf = pytest.importorskip("gguf")
+
+from antfly_b200 import _native as N
+
+TYPES = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS",
+         "TQ1_0", "TQ2_0", "MXFP4", "NVFP4"]
+
+# byte offsets of the fp16 scale fields inside a block (random bytes there could be inf / NaN)
+HALF_FIELDS = {"Q4_0": [0], "Q4_1": [0, 2], "Q5_0": [0], "Q5_1": [0, 2], "Q8_0": [0], "Q2_K": [80, 82], "Q3_K": [108],
+               "Q4_K": [0, 2], "Q5_K": [0, 2], "Q6_K": [208], "IQ4_NL": [0], "IQ4_XS": [0], "TQ1_0": [52],
+               "TQ2_0": [64], "MXFP4": [], "NVFP4": []}
+
+
+def _ours(type_id: int, raw: np.ndarray, n: int) -> np.ndarray:
+    lib = N.host()
+    out = np.empty(n, dtype=np.float32)
+    rc = lib.afb_gguf_dequantize(ctypes.c_int(type_id), raw.ctypes.data_as(ctypes.c_void_p),
+                                 out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(n))
+    assert rc == 0
+    return out
+
+
+@pytest.mark.parametrize("name", TYPES)
+def test_dequantize_matches_gguf_package(name):
+    qt = getattr(gguf.GGMLQuantizationType, name, None)
+    if qt is None:
+        pytest.skip(f"this gguf package has no {name}")
+    values, nbytes = gguf.GGML_QUANT_SIZES[qt]
+    lib = N.host()
+    lib.afb_gguf_block_bytes.restype = ctypes.c_long
+    lib.afb_gguf_block_values.restype = ctypes.c_long
+    assert lib.afb_gguf_block_bytes(int(qt)) == nbytes and lib.afb_gguf_block_values(int(qt)) == values
+    rng = np.random.default_rng(int(qt))
+    blocks = 24
+    raw = rng.integers(0, 256, size=(blocks, nbytes), dtype=np.uint8)
+    for off in HALF_FIELDS[name]:
+        scale = rng.uniform(-2.0, 2.0, size=blocks).astype(np.float16)
+        raw[:, off:off + 2] = scale.view(np.uint8).reshape(blocks, 2)
+    if name == "MXFP4":
+        raw[:, 0] = rng.integers(110, 140, size=blocks)  # e8m0 scale near 1
+    if name == "NVFP4":
+        raw[:, :4] = rng.integers(0x18, 0x60, size=(blocks, 4))
+    if name == "TQ1_0":
+        raw[:, :52] = rng.integers(0, 243, size=(blocks, 52))  # five base-3 digits per byte
+    try:
+        want = gguf.quants.dequantize(raw.reshape(-1), qt).astype(np.float32).reshape(-1)
+    except NotImplementedError:
+        pytest.skip(f"the gguf package cannot dequantize {name}")
+    got = _ours(int(qt), np.ascontiguousarray(raw.reshape(-1)), blocks * values)
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_nvfp4_golden_vector():
+    raw = np.zeros(36, dtype=np.uint8)
+    raw[0] = 0x40  # sub-block scale
+    raw[4] = 0x5A  # low nibble -> first value, high nibble -> ninth value of the first sub-block
+    out = _ours(40, raw, 64)
+    assert abs(out[0] - (-2.0)) < 1e-3 and abs(out[8] - 6.0) < 1e-3 and abs(out[16]) < 1e-3
+
+
+def test_quantize_roundtrip_through_gguf_package():
+    """Our Q8_0 / Q4_0 quantisers produce blocks the reference decoder reads back close to the input."""
+    lib = N.host()
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal(32 * 40).astype(np.float32)
+    for name, fn, tol in (("Q8_0", lib.afb_gguf_quantize_q8_0, 0.02), ("Q4_0", lib.afb_gguf_quantize_q4_0, 0.3)):
+        qt = getattr(gguf.GGMLQuantizationType, name)
+        values, nbytes = gguf.GGML_QUANT_SIZES[qt]
+        raw = np.empty(x.size // values * nbytes, dtype=np.uint8)
+        fn(x.ctypes.data_as(ctypes.c_void_p), raw.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(x.size))
+        back = gguf.quants.dequantize(raw, qt).astype(np.float32).reshape(-1)
+        assert float(np.abs(back - x).max()) < tol * float(np.abs(x).max())
