@@ -161,10 +161,25 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 ids = tok.encode(s)
                 if len(ids) == 1:
                     stops.append(ids[0])
+        grammar = None
+        fmt = (req.response_format or {}).get("type")
+        if fmt in ("json_object", "json"):
+            # JSON mode: every sampled token must keep the reply a valid JSON prefix; the byte table of the
+            # vocabulary is built once per tokenizer and shared by all requests.
+            from ..runtime.grammar import JsonGrammar, token_bytes_table
+
+            table = getattr(tok, "_grammar_token_bytes", None)
+            if table is None:
+                table = token_bytes_table(tok, int(getattr(tok, "vocab_size", 0)) or len(getattr(tok, "vocab", [])))
+                try:
+                    tok._grammar_token_bytes = table
+                except Exception:
+                    pass
+            grammar = JsonGrammar(table, eos_id=tok.special.eos_id, root_object_only=fmt == "json_object")
         return SamplingParams(max_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k, top_p=req.top_p,
                               min_p=req.min_p, repetition_penalty=req.repetition_penalty,
                               frequency_penalty=req.frequency_penalty, presence_penalty=req.presence_penalty,
-                              stop_token_ids=stops, seed=req.seed)
+                              stop_token_ids=stops, seed=req.seed, grammar=grammar)
 
     async def generate(request: Request):
         req, bad = await parse(request, S.GenerateRequest)

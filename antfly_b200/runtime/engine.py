@@ -227,6 +227,19 @@ class LLMEngine:
         return StepBatch(d_ids, d_pos, d_slots, d_qs, d_ql, d_kvl, d_tab, d_rows, max_q, splits)
 
     def _pick_tokens(self, logits: torch.Tensor, reqs: List[Request]) -> torch.Tensor:
+        if any(r.params.grammar is not None for r in reqs):
+            # Grammar-constrained rows: every token the grammar cannot continue with goes to -inf.  The masks are
+            # computed on the host (C++ recogniser stepped over the vocabulary) and applied on the device.
+            V = logits.shape[-1]
+            m = np.ones((len(reqs), V), dtype=np.uint8)
+            for i, r in enumerate(reqs):
+                if r.params.grammar is not None:
+                    gm = r.params.grammar.mask()
+                    m[i, : min(V, gm.shape[0])] = gm[:V]
+                    m[i, gm.shape[0]:] = 0
+            md = torch.from_numpy(m).to(logits.device, non_blocking=True).bool()
+            self.h2d_bytes += m.nbytes
+            logits = logits.float().masked_fill(~md, float("-inf"))
         if all(r.params.greedy and not r.params.needs_penalties for r in reqs):
             return self.model.greedy_tokens(logits)
         lg = logits
@@ -249,6 +262,8 @@ class LLMEngine:
     def _accept(self, r: Request, tok: int, now: float) -> bool:
         """Append one sampled token; returns True when the request is finished."""
         r.out.append(tok)
+        if r.params.grammar is not None:
+            r.params.grammar.accept(tok)
         if r.t_first is None:
             r.t_first = now
         if r.row >= 0:
@@ -293,7 +308,7 @@ class LLMEngine:
             st.logits = logits
             st.out_tokens = self.model.greedy_tokens(logits)
 
-        greedy = all(r.params.greedy and not r.params.needs_penalties for r in reqs)
+        greedy = all(r.params.greedy and not r.params.needs_penalties and r.params.grammar is None for r in reqs)
         if self.use_graph and greedy:
             if st.graph is None:
                 from .. import _native as N
@@ -318,7 +333,8 @@ class LLMEngine:
 
     def step(self) -> int:
         """Run one scheduler step.  Returns the number of tokens produced."""
-        if self.draft is not None:
+        if self.draft is not None and not any(r.params.grammar is not None and not r.finished
+                                              for r in self.reqs.values()):
             snap = self.sched.snapshot()
             if snap["decode"] > 0 and snap["waiting"] + snap["prefill"] == 0:
                 return self._spec_round()

@@ -18,6 +18,7 @@ class SamplingParams:
     stop_token_ids: List[int] = field(default_factory=list)
     ignore_eos: bool = False
     seed: Optional[int] = None
+    grammar: Optional[object] = None  # antfly_b200.runtime.grammar.JsonGrammar: constrains every sampled token
 
     @property
     def greedy(self) -> bool:

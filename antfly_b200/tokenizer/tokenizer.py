@@ -87,6 +87,46 @@ class HFTokenizer(Tokenizer):
     def decode(self, ids: Sequence[int]) -> str:
         return self.tk.decode(list(ids), skip_special_tokens=True)
 
+    # -- exact byte string of one token (grammar-constrained decoding needs bytes, not lossy text) -----------------
+    _byte_decoder: Optional[Dict[str, int]] = None
+
+    @staticmethod
+    def _bytelevel_map() -> Dict[str, int]:
+        """Inverse of the byte-level BPE alphabet: the printable stand-in character of every byte value."""
+        keep = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+        chars, n = list(keep), 0
+        order = list(keep)
+        for b in range(256):
+            if b not in keep:
+                order.append(b)
+                chars.append(256 + n)
+                n += 1
+        return {chr(c): b for b, c in zip(order, chars)}
+
+    def token_bytes(self, token_id: int) -> bytes:
+        piece = self.tk.id_to_token(int(token_id))
+        if piece is None:
+            return b""
+        if len(piece) == 6 and piece.startswith("<0x") and piece.endswith(">"):  # SentencePiece byte fallback
+            try:
+                return bytes([int(piece[3:5], 16)])
+            except ValueError:
+                pass
+        if HFTokenizer._byte_decoder is None:
+            HFTokenizer._byte_decoder = self._bytelevel_map()
+        bd = HFTokenizer._byte_decoder
+        if "Ġ" in piece or "Ċ" in piece or all(ch in bd for ch in piece) and any(ord(ch) >= 0x100 for ch in piece):
+            try:
+                return bytes(bd[ch] for ch in piece)
+            except KeyError:
+                pass
+        if "\u2581" in piece:  # SentencePiece word-boundary marker
+            return piece.replace("\u2581", " ").encode("utf-8")
+        if piece.startswith("##"):  # WordPiece continuation
+            return piece[2:].encode("utf-8")
+        text = self.tk.decode([int(token_id)], skip_special_tokens=True)
+        return text.encode("utf-8")
+
 
 class WordPieceTokenizer(Tokenizer):
     """BERT WordPiece (basic tokenisation: lower-case, strip accents, split punctuation; greedy longest-match with

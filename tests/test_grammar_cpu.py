@@ -1,0 +1,108 @@
+"""JSON-constrained decoding: the C++ recogniser (strings it must accept / reject), the token mask (random walks
+over allowed tokens always end in text that ``json.loads`` parses), and the engine applying the mask."""
+import json
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from antfly_b200.runtime.grammar import JsonGrammar, token_bytes_table
+
+BYTE_VOCAB = [bytes([b]) for b in range(256)]
+MULTI = [b'{"', b'":', b'": ', b'", "', b'true', b'false', b'null', b', ', b'[]', b'{}', b'0.5e', b'-1', b'"}',
+         b'\\u00e9', b'\\n', b'  ', b'}]', b'[[', b'12', b'e+3', b'"a"', b'":[', b'\xc3\xa9']
+VOCAB = BYTE_VOCAB + MULTI + [b""]  # last id plays end-of-sequence
+EOS = len(VOCAB) - 1
+
+
+@pytest.mark.parametrize("text", ['{"a": 1, "b": [true, false, null], "c": {"d": "x\\n\\u00e9"}}', '[]', '{}', '  [1, 2.5e-3, -0]  ',
+                                  '"just a string"', '-12.75E+2', 'null', '[[[]]]', '{"k":"v","k2":[{}]}'])
+def test_accepts_valid_documents(text):
+    g = JsonGrammar(VOCAB, eos_id=EOS)
+    assert g.accept_text(text), text
+    assert g.complete
+    json.loads(text)
+
+
+@pytest.mark.parametrize("text", ['{"a":1,}', '01', '[1 2]', '"\x01"', '{"a" 1}', 'tru e', '{a:1}', '[1,,2]', '{"a":}',
+                                  '1.', '-', '"\\x"', '"\\u12g4"', ']', '{"a":1}}', '[1]]', '+1', '.5', 'nul1'])
+def test_rejects_invalid_documents(text):
+    g = JsonGrammar(VOCAB, eos_id=EOS)
+    ok = g.accept_text(text)
+    assert not (ok and g.complete), text
+    if ok:  # a valid *prefix* at most ('1.' / '-'): never complete, and the json module agrees it is not a document
+        with pytest.raises(json.JSONDecodeError):
+            json.loads(text)
+
+
+def test_root_object_only_mode():
+    g = JsonGrammar(VOCAB, eos_id=EOS, root_object_only=True)
+    m = g.mask()
+    allowed = {i for i in range(len(VOCAB)) if m[i]}
+    assert ord("{") in allowed and ord("[") not in allowed and ord("1") not in allowed
+    assert g.accept_text('  {"x": [1]}') and g.complete
+
+
+def test_random_walks_over_the_mask_always_produce_json():
+    rng = random.Random(0)
+    closers = {ord("}"), ord("]"), ord('"')}
+    for walk in range(120):
+        g = JsonGrammar(VOCAB, eos_id=EOS)
+        out = bytearray()
+        for step in range(400):
+            m = g.mask()
+            ids = np.flatnonzero(m)
+            assert len(ids) > 0
+            if m[EOS] and (step > 40 or rng.random() < 0.2):
+                assert g.accept(EOS)
+                break
+            cand = [int(i) for i in ids if i != EOS]
+            # keep documents finite: past a length, favour tokens that close something
+            pref = [i for i in cand if i in closers or VOCAB[i] in (b'"}', b'}]')] if step > 60 else []
+            if g._lib.afb_grammar_depth(g._h) == 0 and step > 60 and m[EOS]:
+                assert g.accept(EOS)
+                break
+            tok = rng.choice(pref or cand)
+            assert g.accept(tok)
+            out += VOCAB[tok]
+        else:
+            continue  # did not finish within the budget: nothing to parse
+        json.loads(out.decode("utf-8", errors="strict") if all(b < 0x80 for b in out) else out.decode("utf-8", "ignore"))
+
+
+def test_mask_matches_stepwise_acceptance():
+    g = JsonGrammar(VOCAB, eos_id=EOS)
+    assert g.accept_text('{"key": [1, ')
+    m = g.mask()
+    for t in range(len(VOCAB) - 1):
+        h = JsonGrammar(VOCAB, eos_id=EOS)
+        assert h.accept_text('{"key": [1, ')
+        assert bool(m[t]) == h.accept(t), (t, VOCAB[t])
+    assert not m[EOS]
+
+
+def test_engine_applies_the_grammar_mask():
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    tok = ByteTokenizer(vocab_size=512)
+    cfg = LlamaConfig.tiny(vocab_size=512)
+    model = LlamaModel.random_init(cfg, device="cpu", seed=1, fast_init=False)
+    eng = LLMEngine(model, num_blocks=32, page=16, max_batch=2, max_step_tokens=128, prefill_chunk=64,
+                    max_seq_len=128, use_cuda_graph=False, eos_token_id=tok.special.eos_id)
+    table = token_bytes_table(tok, 512)
+    for temperature in (0.0, 0.9):
+        gr = JsonGrammar(table, eos_id=tok.special.eos_id)
+        rid = eng.add_request(tok.encode_prompt("reply in json: "),
+                              SamplingParams(max_tokens=48, temperature=temperature, seed=7, grammar=gr))
+        while eng.has_work():
+            eng.step()
+        r = eng.reqs[rid]
+        text = b"".join(table[t] for t in r.out if t != tok.special.eos_id)
+        check = JsonGrammar(table, eos_id=tok.special.eos_id)
+        assert check._lib.afb_grammar_accept_bytes(check._h, text, len(text)) == 1, text
+        if r.finish_reason == "stop":
+            json.loads(text.decode("utf-8", "ignore"))
