@@ -55,7 +55,7 @@ class Manifest:
         if "ForSequenceClassification" in arch:
             return "reranker"
         if "CausalLM" in arch or self.config.get("model_type") in ("llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "gpt2",
-                                                                     "gpt_neox", "opt"):
+                                                                     "gpt_neox", "opt", "gptj", "phi"):
             return "generator"
         return "embedder"
 

@@ -1,5 +1,5 @@
-"""LayerNorm-based decoder family: GPT-2, GPT-NeoX / Pythia and OPT, on the same paged-KV engine interface as
-:class:`antfly_b200.models.llama.LlamaModel`.
+"""LayerNorm-based decoder family: GPT-2, GPT-NeoX / Pythia, OPT, GPT-J and Phi (1 / 1.5 / 2), on the same
+paged-KV engine interface as :class:`antfly_b200.models.llama.LlamaModel`.
 
 What differs from the Llama family and how it maps onto the existing kernels (the reference covers these under one
 ``ModelFamily`` switch, zig/pkg/inference/src/models/gpt.zig:28-233, zig/pkg/inference/src/architectures/gpt.zig):
@@ -10,6 +10,8 @@ What differs from the Llama family and how it maps onto the existing kernels (th
 * learned absolute positions (GPT-2, OPT with its offset of 2): added to the token embedding; the RoPE + KV-write
   kernel is then run with all positions zero, which rotates by the identity and only writes K / V into the cache.
 * partial rotary embedding and the parallel residual of GPT-NeoX (``x + attn(ln1 x) + mlp(ln2 x)``).
+* the single-norm parallel block of GPT-J and Phi (``x + attn(ln x) + mlp(ln x)``), GPT-J's interleaved
+  ("consecutive pairs") rotary embedding, and the biased LM head both of them carry.
 * fused QKV layouts: GPT-2's ``c_attn`` is a transposed ``Conv1D`` [in, 3 * out]; GPT-NeoX interleaves q, k, v per
   head; both are re-packed at load time into the [q heads | k heads | v heads] rows the kernels expect.
 """
@@ -28,7 +30,7 @@ from .llama import StepBatch
 
 @dataclass
 class GptConfig:
-    family: str = "gpt2"              # gpt2 | gpt_neox | opt
+    family: str = "gpt2"              # gpt2 | gpt_neox | opt | gptj | phi
     vocab_size: int = 50257
     hidden_size: int = 768
     num_hidden_layers: int = 12
@@ -43,6 +45,8 @@ class GptConfig:
     position_offset: int = 0          # OPT: 2
     tie_word_embeddings: bool = True
     sliding_window: int = 0
+    shared_norm: bool = False         # GPT-J / Phi: one LayerNorm feeds both the attention and the MLP branch
+    rope_half_split: bool = True      # False: GPT-J pairs (2i, 2i + 1) instead of (i, i + rot/2)
 
     # Names the engine reads from every decoder config.
     @property
@@ -81,6 +85,21 @@ class GptConfig:
                        d["ffn_dim"], d.get("max_position_embeddings", 2048), 1e-5,
                        act[d.get("activation_function", "relu")], position_offset=2,
                        tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if mt == "gptj":
+            H, nh = d["n_embd"], d["n_head"]
+            rot = d.get("rotary_dim") or (H // nh)
+            return cls("gptj", d["vocab_size"], H, d["n_layer"], nh, d.get("n_inner") or 4 * H,
+                       d.get("n_positions", 2048), d.get("layer_norm_epsilon", 1e-5),
+                       act[d.get("activation_function", "gelu_new")], 10000.0, rot / (H // nh), True,
+                       tie_word_embeddings=False, shared_norm=True, rope_half_split=False)
+        if mt == "phi":
+            rp = d.get("rope_parameters") or d.get("rope_scaling") or {}
+            theta = d.get("rope_theta") or rp.get("rope_theta") or 10000.0
+            pct = d.get("partial_rotary_factor") or rp.get("partial_rotary_factor") or 0.5
+            return cls("phi", d["vocab_size"], d["hidden_size"], d["num_hidden_layers"], d["num_attention_heads"],
+                       d["intermediate_size"], d.get("max_position_embeddings", 2048), d.get("layer_norm_eps", 1e-5),
+                       act[d.get("hidden_act", "gelu_new")], float(theta), float(pct), True,
+                       tie_word_embeddings=False, shared_norm=True)
         raise ValueError(f"unsupported model_type {mt!r}")
 
 
@@ -160,6 +179,33 @@ class GptModel:
             w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layer_norm.weight"]), t(sd[pre + "final_layer_norm.bias"])
             w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
                 w["embed"]
+        elif cfg.family == "gptj":
+            pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
+            w["embed"] = t(sd[pre + "wte.weight"])
+            zeros = lambda n: torch.zeros(n, dtype=dtype, device=device)
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}h.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "ln_1.weight"]), t(sd[s + "ln_1.bias"])
+                w[p + "qkv.w"] = t(torch.cat([sd[s + f"attn.{n}_proj.weight"] for n in ("q", "k", "v")], 0))
+                w[p + "qkv.b"] = zeros(3 * H)
+                w[p + "o.w"], w[p + "o.b"] = t(sd[s + "attn.out_proj.weight"]), zeros(H)
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.fc_in.weight"]), t(sd[s + "mlp.fc_in.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.fc_out.weight"]), t(sd[s + "mlp.fc_out.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "ln_f.weight"]), t(sd[pre + "ln_f.bias"])
+            w["lm_head"], w["lm_head.b"] = t(sd["lm_head.weight"]), t(sd["lm_head.bias"])
+        elif cfg.family == "phi":
+            pre = "model." if any(k.startswith("model.") for k in sd) else ""
+            w["embed"] = t(sd[pre + "embed_tokens.weight"])
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}layers.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "input_layernorm.weight"]), t(sd[s + "input_layernorm.bias"])
+                w[p + "qkv.w"] = t(torch.cat([sd[s + f"self_attn.{n}_proj.weight"] for n in ("q", "k", "v")], 0))
+                w[p + "qkv.b"] = t(torch.cat([sd[s + f"self_attn.{n}_proj.bias"] for n in ("q", "k", "v")], 0))
+                w[p + "o.w"], w[p + "o.b"] = t(sd[s + "self_attn.dense.weight"]), t(sd[s + "self_attn.dense.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.fc1.weight"]), t(sd[s + "mlp.fc1.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.fc2.weight"]), t(sd[s + "mlp.fc2.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layernorm.weight"]), t(sd[pre + "final_layernorm.bias"])
+            w["lm_head"], w["lm_head.b"] = t(sd["lm_head.weight"]), t(sd["lm_head.bias"])
         else:
             raise ValueError(cfg.family)
         return cls(cfg, w)
@@ -204,14 +250,14 @@ class GptModel:
             h = Dn.norm(x, w[p + "ln1.g"], w[p + "ln1.b"], eps=eps, rms=False)
             qkv = Dn.gemm_bf16(h, w[p + "qkv.w"], bias=w[p + "qkv.b"])
             q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache[l], v_cache[l], Hq, Hq, D, cfg.rope_theta,
-                                rope_dim=rope_dim, half_split=True)
+                                rope_dim=rope_dim, half_split=cfg.rope_half_split)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch)
             if cfg.parallel_residual:
                 # x + attn(ln1 x) + mlp(ln2 x): both branches read the same x
                 a_out = Dn.gemm_bf16(ctx.view(T, Hq * D), w[p + "o.w"], bias=w[p + "o.b"], residual=x)
-                h2 = Dn.norm(x, w[p + "ln2.g"], w[p + "ln2.b"], eps=eps, rms=False)
+                h2 = h if cfg.shared_norm else Dn.norm(x, w[p + "ln2.g"], w[p + "ln2.b"], eps=eps, rms=False)
                 m = Dn.gemm_bf16(h2, w[p + "fc.w"], bias=w[p + "fc.b"], act=act)
                 x = Dn.gemm_bf16(m, w[p + "proj.w"], bias=w[p + "proj.b"], residual=a_out)
             else:
@@ -221,7 +267,7 @@ class GptModel:
                 x = Dn.gemm_bf16(m, w[p + "proj.w"], bias=w[p + "proj.b"], residual=x)
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
         hl = Dn.norm(rows, w["lnf.g"], w["lnf.b"], eps=eps, rms=False)
-        return Dn.gemm_bf16(hl, w["lm_head"])
+        return Dn.gemm_bf16(hl, w["lm_head"], bias=w.get("lm_head.b"))
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
         return S.argmax(logits)

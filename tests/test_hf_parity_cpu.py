@@ -146,13 +146,22 @@ def _hf_gpt(kind: str):
                                          use_parallel_residual=kind == "neox_parallel", hidden_dropout=0.0,
                                          attention_dropout=0.0, tie_word_embeddings=False)
         return cfg, transformers.GPTNeoXForCausalLM(cfg)
+    if kind == "gptj":
+        cfg = transformers.GPTJConfig(vocab_size=300, n_positions=64, n_embd=64, n_layer=2, n_head=4, rotary_dim=8,
+                                      resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        return cfg, transformers.GPTJForCausalLM(cfg)
+    if kind == "phi":
+        cfg = transformers.PhiConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                     num_attention_heads=4, max_position_embeddings=64, partial_rotary_factor=0.5,
+                                     resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0)
+        return cfg, transformers.PhiForCausalLM(cfg)
     cfg = transformers.OPTConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
                                  ffn_dim=128, max_position_embeddings=64, word_embed_proj_dim=64, dropout=0.0,
                                  attention_dropout=0.0)
     return cfg, transformers.OPTForCausalLM(cfg)
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt"])
+@pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt", "gptj", "phi"])
 def test_layernorm_decoders_match_transformers(kind):
     from antfly_b200.models.gpt import GptConfig, GptModel
 
