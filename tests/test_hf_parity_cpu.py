@@ -191,3 +191,32 @@ def test_layernorm_decoders_match_transformers(kind):
     cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
     assert float(cos.min()) > 0.995, (kind, cos)
     assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.85
+
+
+@pytest.mark.parametrize("kind", ["roberta", "xlm-roberta"])
+def test_roberta_family_matches_transformers(kind):
+    """Position ids start after the padding index, one token type, same encoder otherwise."""
+    torch.manual_seed(3)
+    C, M = ((transformers.RobertaConfig, transformers.RobertaModel) if kind == "roberta"
+            else (transformers.XLMRobertaConfig, transformers.XLMRobertaModel))
+    hf_cfg = C(vocab_size=400, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+               max_position_embeddings=70, type_vocab_size=1, pad_token_id=1, hidden_dropout_prob=0.0,
+               attention_probs_dropout_prob=0.0)
+    hf = M(hf_cfg, add_pooling_layer=False).eval()
+    cfg = BertConfig.from_hf(hf_cfg.to_dict())
+    assert cfg.position_offset == 2
+    model = BertModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    seqs = [[0] + torch.randint(3, 400, (n,)).tolist() + [2] for n in (4, 19, 33)]
+    batch = pack_sequences(seqs, None, position_offset=cfg.position_offset)
+    L = max(len(s) for s in seqs)
+    ids = torch.full((len(seqs), L), 1, dtype=torch.long)
+    mask = torch.zeros_like(ids)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.tensor(s)
+        mask[i, : len(s)] = 1
+    with torch.no_grad():
+        hidden = hf(input_ids=ids, attention_mask=mask).last_hidden_state
+    want = torch.nn.functional.normalize((hidden * mask[..., None]).sum(1) / mask.sum(1, keepdim=True), dim=-1)
+    got = model.embed(batch, pooling="mean", normalize=True).float()
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.999, cos
