@@ -249,6 +249,13 @@ class BertModel:
                                           out_dtype=torch.float32)).to(h.dtype)
         return Dn.gemm_bf16(cls, self.w["cls.w"], bias=self.w["cls.b"], out_dtype=torch.float32)
 
+    def token_logits(self, b: PackedBatch) -> torch.Tensor:
+        """Token-classification logits, fp32 [T, num_labels] (the classifier applied to every token's hidden
+        state, no pooler): NER / chunk-boundary heads."""
+        assert "cls.w" in self.w, "model has no classification head"
+        h = self.encode(b)
+        return Dn.gemm_bf16(h, self.w["cls.w"], bias=self.w["cls.b"], out_dtype=torch.float32)
+
     def param_count(self) -> int:
         return sum(t.numel() for t in self.w.values())
 

@@ -1,0 +1,87 @@
+"""Classification / NER pipelines, the HBM planner and the parallel-strategy planner (all host-side logic)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from antfly_b200.models.bert import BertConfig, BertModel, pack_sequences
+from antfly_b200.models.llama import LlamaConfig
+from antfly_b200.parallel.strategy import plan_parallel
+from antfly_b200.pipelines.classification import Entity, TextClassifier, TokenClassifier, aggregate_bio
+from antfly_b200.runtime.memory import estimate_generation, plan_kv_blocks
+
+
+def test_bio_aggregation_rules():
+    tags = ["O", "B-PER", "I-PER", "O", "I-LOC", "I-LOC", "B-LOC", "I-ORG", "O"]
+    ents = aggregate_bio(tags, [0.9] * len(tags))
+    assert [(e.label, e.start_token, e.end_token) for e in ents] == [("PER", 1, 3), ("LOC", 4, 6), ("LOC", 6, 7),
+                                                                      ("ORG", 7, 8)]
+    # special tokens split entities; continuation pieces extend the open one regardless of their own tag
+    ents = aggregate_bio(["B-PER", "O", "I-PER", "B-LOC"], [1.0, 0.2, 0.8, 0.6], is_special=[False, False, True, False],
+                         is_continuation=[False, True, False, False])
+    assert [(e.label, e.start_token, e.end_token) for e in ents] == [("PER", 0, 2), ("LOC", 3, 4)]
+    assert abs(ents[0].score - 0.6) < 1e-6
+
+
+def test_token_classifier_matches_transformers():
+    torch.manual_seed(0)
+    labels = ["O", "B-PER", "I-PER", "B-LOC", "I-LOC"]
+    hf_cfg = transformers.BertConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                     intermediate_size=128, max_position_embeddings=64, num_labels=len(labels),
+                                     hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    hf = transformers.BertForTokenClassification(hf_cfg).eval()
+    cfg = BertConfig.from_hf(hf_cfg.to_dict())
+    cfg.num_labels = len(labels)
+    model = BertModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    seqs = [[101] + torch.randint(103, 300, (n,)).tolist() + [102] for n in (6, 13)]
+    got = model.token_logits(pack_sequences(seqs, None)).float()
+    o = 0
+    for s in seqs:
+        with torch.no_grad():
+            want = hf(input_ids=torch.tensor([s])).logits[0]
+        torch.testing.assert_close(got[o:o + len(s)], want, atol=2e-2, rtol=2e-2)
+        o += len(s)
+    tagger = TokenClassifier(model, dict(enumerate(labels)))
+    ents = tagger.entities_ids(seqs, special_ids=[101, 102])
+    assert len(ents) == 2 and all(isinstance(e, Entity) for row in ents for e in row)
+    assert all(0 < e.start_token < e.end_token < len(s) for s, row in zip(seqs, ents) for e in row)
+
+
+def test_text_classifier_probabilities():
+    cfg = BertConfig(vocab_size=200, hidden_size=64, num_hidden_layers=1, num_attention_heads=4,
+                     intermediate_size=128, max_position_embeddings=64, num_labels=3)
+    model = BertModel.random_init(cfg, device="cpu", seed=0, dtype=torch.float32)
+    clf = TextClassifier(model, id2label={0: "neg", 1: "neu", 2: "pos"})
+    out = clf.classify_ids([[101, 5, 6, 102], [101, 9, 102]], top_k=3)
+    assert len(out) == 2 and abs(sum(d["score"] for d in out[0]) - 1.0) < 1e-5
+    assert {d["label"] for d in out[0]} == {"neg", "neu", "pos"}
+
+
+def test_memory_planner():
+    cfg = LlamaConfig.llama3_8b()
+    est = estimate_generation(cfg)
+    assert 8.0e9 < est.weight_bytes < 10.5e9              # ~8 B fp8 parameters + bf16 embedding table
+    assert est.kv_bytes_per_token == 2 * 32 * 8 * 128 * 2  # K and V, 32 layers, 8 KV heads, bf16
+    blocks = plan_kv_blocks(cfg, max_seq_len=8192)
+    assert blocks * 16 * est.kv_bytes_per_token < 180e9 and blocks * 16 > 64 * 2304  # the headline workload fits
+    est8 = estimate_generation(LlamaConfig.llama3_70b(), tp_size=8)
+    assert est8.kv_bytes_per_token == 2 * 80 * 1 * 128 * 2 and est8.weight_bytes < 15e9
+    with pytest.raises(MemoryError):
+        plan_kv_blocks(LlamaConfig.llama3_70b(), hbm_bytes=40 * 10 ** 9, tp_size=1)
+
+
+def test_parallel_strategy_planner():
+    cfg = LlamaConfig.llama3_8b()
+    assert plan_parallel(cfg, 1).strategy == "single"
+    p = plan_parallel(cfg, 8)
+    assert p.strategy == "tensor" and [r.tp_rank for r in p.ranks] == list(range(8)) and all(
+        r.layers == (0, 32) for r in p.ranks)
+    pp = plan_parallel(cfg, 3, "pipeline")
+    assert [r.layers for r in pp.ranks] == [(0, 11), (11, 22), (22, 32)]
+    assert pp.ranks[0].holds_embedding and not pp.ranks[0].holds_lm_head and pp.ranks[2].holds_lm_head
+    with pytest.raises(ValueError):
+        plan_parallel(cfg, 3, "tensor")
+    assert plan_parallel(cfg, 3).strategy == "pipeline"
+    assert plan_parallel(LlamaConfig.llama3_70b(), 8).notes == []      # 8 KV heads over 8 ranks: nothing replicated
+    small_kv = LlamaConfig(num_attention_heads=32, num_key_value_heads=4, intermediate_size=14336)
+    assert any("replicated" in n for n in plan_parallel(small_kv, 8).notes)
