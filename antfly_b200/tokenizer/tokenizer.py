@@ -128,6 +128,35 @@ class HFTokenizer(Tokenizer):
         return text.encode("utf-8")
 
 
+class SentencePieceTokenizer(Tokenizer):
+    """``tokenizer.model`` / ``spiece.model`` / ``sentencepiece.bpe.model`` through the ``sentencepiece`` library
+    (the reference parses the same protobuf itself, zig/lib/tokenizer/src/sentencepiece.zig)."""
+
+    def __init__(self, path: str, config: Optional[dict] = None):
+        import sentencepiece as spm
+
+        self.sp = spm.SentencePieceProcessor(model_file=path)
+        self.vocab_size = self.sp.get_piece_size()
+        pick = lambda i: i if i is not None and i >= 0 else None
+        self.special = SpecialTokens(cls_id=pick(self.sp.bos_id()) or 0, sep_id=pick(self.sp.eos_id()) or 0,
+                                     pad_id=pick(self.sp.pad_id()) or 0, unk_id=pick(self.sp.unk_id()) or 0,
+                                     bos_id=pick(self.sp.bos_id()), eos_id=pick(self.sp.eos_id()))
+
+    def encode(self, text: str) -> List[int]:
+        return list(self.sp.encode(text))
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return self.sp.decode([int(i) for i in ids])
+
+    def token_bytes(self, token_id: int) -> bytes:
+        t = int(token_id)
+        if self.sp.is_control(t) or self.sp.is_unknown(t):
+            return b""
+        if self.sp.is_byte(t):
+            return bytes([int(self.sp.id_to_piece(t)[3:5], 16)])
+        return self.sp.id_to_piece(t).replace("\u2581", " ").encode("utf-8")
+
+
 class WordPieceTokenizer(Tokenizer):
     """BERT WordPiece (basic tokenisation: lower-case, strip accents, split punctuation; greedy longest-match with
     the ``##`` continuation prefix).  Used when only ``vocab.txt`` exists or the ``tokenizers`` wheel is missing."""
@@ -233,6 +262,13 @@ def load_tokenizer(model_dir: str, vocab_size: int = 0) -> Tokenizer:
             return HFTokenizer(tj, cfg)
         except ImportError:
             pass
+    for name in ("tokenizer.model", "spiece.model", "sentencepiece.bpe.model"):
+        sm = os.path.join(model_dir, name)
+        if os.path.exists(sm):
+            try:
+                return SentencePieceTokenizer(sm, cfg)
+            except ImportError:
+                pass
     vt = os.path.join(model_dir, "vocab.txt")
     if os.path.exists(vt):
         return WordPieceTokenizer.from_vocab_file(vt, lower=cfg.get("do_lower_case", True))

@@ -85,3 +85,24 @@ def test_parallel_strategy_planner():
     assert plan_parallel(LlamaConfig.llama3_70b(), 8).notes == []      # 8 KV heads over 8 ranks: nothing replicated
     small_kv = LlamaConfig(num_attention_heads=32, num_key_value_heads=4, intermediate_size=14336)
     assert any("replicated" in n for n in plan_parallel(small_kv, 8).notes)
+
+
+def test_sentencepiece_tokenizer_roundtrip_and_token_bytes(tmp_path):
+    spm = pytest.importorskip("sentencepiece")
+    from antfly_b200.tokenizer.tokenizer import SentencePieceTokenizer, load_tokenizer
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(["the quick brown fox jumps over the lazy dog", "json {\"key\": [1, 2, 3]}",
+                                 "vector search with paged attention", "hello world, hello tokens"] * 30))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(tmp_path / "tokenizer"), vocab_size=340,
+                                   model_type="bpe", byte_fallback=True, character_coverage=1.0,
+                                   minloglevel=2)
+    tok = load_tokenizer(str(tmp_path))
+    assert isinstance(tok, SentencePieceTokenizer) and tok.vocab_size == 340
+    text = "hello brown json {\"key\": 7} é"
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+    # the per-token byte strings concatenate to the text (with SentencePiece's leading word-boundary space)
+    joined = b"".join(tok.token_bytes(i) for i in ids).decode("utf-8")
+    assert joined.lstrip(" ") == text
+    assert tok.token_bytes(tok.special.eos_id) == b""
