@@ -1,6 +1,6 @@
-"""Grammar-constrained decoding: JSON mode.
+"""Grammar-constrained decoding: JSON mode and GBNF grammars.
 
-``JsonGrammar`` wraps the C++ recogniser (``csrc/host/grammar.cpp``).  The engine asks it for the set of tokens
+``JsonGrammar`` and ``GbnfGrammar`` wrap the C++ matchers (``csrc/host/grammar.cpp``).  The engine asks it for the set of tokens
 that keep the output a valid JSON prefix, masks every other logit to -inf before arg-max / sampling, and feeds
 the chosen token back.  The end-of-sequence token becomes available once the document is complete, and is forced
 when nothing else can follow.  Mirrors the reference's JSON grammar masking in the generation pipeline
@@ -40,12 +40,15 @@ def token_bytes_table(tokenizer, vocab_size: int) -> List[bytes]:
 
 
 class JsonGrammar:
-    """One request's JSON recogniser state plus the (shared) vocabulary byte table."""
+    """One request's matcher state plus the (shared) vocabulary byte table."""
 
     def __init__(self, token_bytes: Sequence[bytes], eos_id: Optional[int] = None, root_object_only: bool = False):
         self._lib = N.host()
         self._lib.afb_grammar_json_new.restype = ctypes.c_void_p
         self._h = ctypes.c_void_p(self._lib.afb_grammar_json_new(ctypes.c_int(1 if root_object_only else 0)))
+        self._set_vocab(token_bytes, eos_id)
+
+    def _set_vocab(self, token_bytes: Sequence[bytes], eos_id: Optional[int]) -> None:
         self.n = len(token_bytes)
         self.eos_id = eos_id
         offsets = np.zeros(self.n + 1, dtype=np.int64)
@@ -85,3 +88,20 @@ class JsonGrammar:
     def accept_text(self, text: str) -> bool:
         b = text.encode("utf-8")
         return bool(self._lib.afb_grammar_accept_bytes(self._h, b, ctypes.c_int(len(b))))
+
+
+class GbnfGrammar(JsonGrammar):
+    """A context-free grammar in GBNF notation (rules ``name ::= ...``, literals, character classes, groups and
+    the ``* + ? {m,n}`` operators), matched byte-wise.  Same interface as :class:`JsonGrammar`.  Raises
+    ``ValueError`` with the parser's message for a malformed, incomplete or left-recursive grammar."""
+
+    def __init__(self, token_bytes: Sequence[bytes], grammar: str, eos_id: Optional[int] = None, root: str = "root"):
+        self._lib = N.host()
+        self._lib.afb_grammar_gbnf_new.restype = ctypes.c_void_p
+        self._lib.afb_grammar_last_error.restype = ctypes.c_char_p
+        h = self._lib.afb_grammar_gbnf_new(grammar.encode("utf-8"), root.encode("utf-8"))
+        if not h:
+            self._h = None
+            raise ValueError("GBNF: " + self._lib.afb_grammar_last_error().decode("utf-8", "replace"))
+        self._h = ctypes.c_void_p(h)
+        self._set_vocab(token_bytes, eos_id)

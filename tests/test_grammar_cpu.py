@@ -106,3 +106,84 @@ def test_engine_applies_the_grammar_mask():
         assert check._lib.afb_grammar_accept_bytes(check._h, text, len(text)) == 1, text
         if r.finish_reason == "stop":
             json.loads(text.decode("utf-8", "ignore"))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GBNF
+# ---------------------------------------------------------------------------------------------------------------
+from antfly_b200.runtime.grammar import GbnfGrammar
+
+ARITH = r"""
+# arithmetic with parentheses
+root  ::= expr
+expr  ::= term (("+" | "-") term)*
+term  ::= factor (("*" | "/") factor)*
+factor ::= number | "(" expr ")"
+number ::= [0-9]+ ("." [0-9]{1,3})?
+"""
+
+ISO_DATE = 'root ::= [0-9]{4} "-" ("0" [1-9] | "1" [0-2]) "-" [0-3] [0-9]'
+
+CHOICE = 'root ::= ("yes" | "no" | "maybe") "\\n"?'
+
+
+def _gb(text, **kw):
+    return GbnfGrammar(VOCAB, text, eos_id=EOS, **kw)
+
+
+@pytest.mark.parametrize("grammar,good,bad", [
+    (ARITH, ["1", "12+3", "(1+2)*3.25", "((7))", "4/2-1"], ["", "+", "1+", "(1", "1.2345", "1 + 2", "a"]),
+    (ISO_DATE, ["2026-11-25", "1999-01-01"], ["2026-13-01", "26-11-25", "2026-1-1", "2026-00-10"]),
+    (CHOICE, ["yes", "no\n", "maybe"], ["ye", "nope", "yes\n\n", "YES"]),
+    ('root ::= [^"\\\\\\x00-\\x1f]* "!"', ["abc!", "!", "café!"], ['a"b!', "a\\b!", "abc"]),
+])
+def test_gbnf_accepts_and_rejects(grammar, good, bad):
+    for text in good:
+        g = _gb(grammar)
+        assert g.accept_text(text) and g.complete, text
+    for text in bad:
+        g = _gb(grammar)
+        assert not (g.accept_text(text) and g.complete), text
+
+
+def test_gbnf_mask_and_random_walks():
+    rng = random.Random(1)
+    g0 = _gb(ARITH)
+    m = g0.mask()
+    allowed = {VOCAB[i] for i in np.flatnonzero(m)}
+    assert b"(" in allowed and b"7" in allowed and b"12" in allowed and b"[[" not in allowed
+    assert b"+" not in allowed and not m[EOS]
+    for walk in range(60):
+        g = _gb(ARITH)
+        out = bytearray()
+        for step in range(200):
+            m = g.mask()
+            ids = [int(i) for i in np.flatnonzero(m)]
+            assert ids
+            if m[EOS] and (step > 20 or rng.random() < 0.15):
+                assert g.accept(EOS)
+                break
+            cand = [i for i in ids if i != EOS]
+            closing = [i for i in cand if VOCAB[i] in (b")", b"1", b"12")] if step > 30 else []
+            tok = rng.choice(closing or cand)
+            assert g.accept(tok)
+            out += VOCAB[tok]
+        else:
+            continue
+        text = out.decode()
+        assert set(text) <= set("0123456789.+-*/()") and text.count("(") == text.count(")")
+        check = _gb(ARITH)  # the emitted text, re-read in one piece, is a complete sentence of the grammar
+        assert check.accept_text(text) and check.complete, text
+        assert text[-1] in "0123456789)" and text[0] in "0123456789("
+
+
+def test_gbnf_errors():
+    with pytest.raises(ValueError, match="never defined"):
+        _gb('root ::= missing "x"')
+    with pytest.raises(ValueError, match="no rule named"):
+        _gb('start ::= "x"')
+    with pytest.raises(ValueError, match="left recursion|terminate"):
+        _gb('root ::= root "a" | "a"')
+    with pytest.raises(ValueError):
+        _gb('root ::= "unterminated')
+    assert _gb('start ::= "x"', root="start").accept_text("x")
