@@ -406,8 +406,9 @@ bool match_terminal(const Rule& r, uint32_t idx, uint8_t c, uint32_t* next) {
 }
 
 // Expands rule references at the top of `stack` until every resulting stack is empty or topped by a terminal.
-bool advance_stack(const Gbnf& g, const Stack& stack, std::vector<Stack>& out, int* budget) {
-  if (--*budget < 0) return false;
+bool advance_stack(const Gbnf& g, const Stack& stack, std::vector<Stack>& out, int* budget, int depth = 0) {
+  // total expansions and nesting are both capped: a left-recursive rule would otherwise expand forever
+  if (--*budget < 0 || depth > 512 || stack.size() > 4096) return false;
   if (stack.empty()) { out.push_back(stack); return true; }
   const Pos top = stack.back();
   const Rule& r = g.rules[top.rule];
@@ -421,7 +422,7 @@ bool advance_stack(const Gbnf& g, const Stack& stack, std::vector<Stack>& out, i
       const uint32_t after = top.idx + 1;
       if (r[after].type != kAlt && r[after].type != kEnd) ns.push_back({top.rule, after});
       if (sub[alt].type != kAlt && sub[alt].type != kEnd) ns.push_back({e.value, alt});
-      if (!advance_stack(g, ns, out, budget)) return false;
+      if (!advance_stack(g, ns, out, budget, depth + 1)) return false;
       while (sub[alt].type != kAlt && sub[alt].type != kEnd) ++alt;
       if (sub[alt].type == kEnd) break;
       ++alt;
