@@ -101,11 +101,14 @@ class GenerateRequest(BaseModel):
     mode: Optional[str] = None
     grammar: Optional[str] = None
     response_format: Optional[Dict[str, Any]] = None
+    tools: Optional[List[Dict[str, Any]]] = None
+    tool_choice: Optional[Union[str, Dict[str, Any]]] = None
 
 
 class GenerateMessage(BaseModel):
     role: str = "assistant"
     content: Optional[str] = None
+    tool_calls: Optional[List[Dict[str, Any]]] = None
 
 
 class GenerateChoice(BaseModel):

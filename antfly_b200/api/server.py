@@ -163,7 +163,19 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     stops.append(ids[0])
         grammar = None
         fmt = (req.response_format or {}).get("type")
-        if fmt in ("json_object", "json"):
+        if req.grammar:
+            # a GBNF grammar supplied with the request constrains the whole reply
+            from ..runtime.grammar import GbnfGrammar, token_bytes_table
+
+            table = getattr(tok, "_grammar_token_bytes", None)
+            if table is None:
+                table = token_bytes_table(tok, int(getattr(tok, "vocab_size", 0)) or len(getattr(tok, "vocab", [])))
+                try:
+                    tok._grammar_token_bytes = table
+                except Exception:
+                    pass
+            grammar = GbnfGrammar(table, req.grammar, eos_id=tok.special.eos_id)
+        elif fmt in ("json_object", "json"):
             # JSON mode: every sampled token must keep the reply a valid JSON prefix; the byte table of the
             # vocabulary is built once per tokenizer and shared by all requests.
             from ..runtime.grammar import JsonGrammar, token_bytes_table
@@ -192,16 +204,49 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         msgs = [m.model_dump() for m in req.messages]
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
+        # Tool calling: declare the tools in a system message and parse calls out of the reply.
+        tool_fmt = None
+        if req.tools:
+            from ..pipelines import tool_calls as TC
+
+            try:
+                choice = TC.parse_tool_choice(req.tool_choice)
+            except ValueError as e:
+                return _err(400, "invalid_request", str(e))
+            if choice.enabled:
+                try:
+                    lm0 = mgr.get(req.model, "generator")
+                    tool_fmt = TC.detect_format(getattr(lm0.pipeline.template, "source", None))
+                except Exception:
+                    tool_fmt = "hermes"
+                decl = TC.format_tools_prompt(req.tools, tool_fmt, choice)
+                if msgs and msgs[0].get("role") == "system":
+                    msgs[0] = dict(msgs[0], content=(msgs[0].get("content") or "") + "\n\n" + decl)
+                else:
+                    msgs.insert(0, {"role": "system", "content": decl})
+        if req.grammar:
+            try:  # reject a malformed grammar before any work is queued
+                from ..runtime.grammar import GbnfGrammar
+
+                GbnfGrammar([b"a"], req.grammar)
+            except ValueError as e:
+                return _err(400, "invalid_request", str(e))
         if not req.stream:
             def work():
                 lm = mgr.get(req.model, "generator")
                 out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer))
                 metrics.tokens.labels("generate", "prompt").inc(out.prompt_tokens)
                 metrics.tokens.labels("generate", "completion").inc(out.completion_tokens)
+                message, finish = S.GenerateMessage(content=out.text), out.finish_reason
+                if tool_fmt is not None:
+                    from ..pipelines import tool_calls as TC
+
+                    content, calls = TC.parse_tool_calls(out.text, tool_fmt)
+                    if calls:
+                        message, finish = S.GenerateMessage(content=content or None, tool_calls=calls), "tool_calls"
                 return S.GenerateResponse(
                     id=rid, created=created, model=req.model,
-                    choices=[S.GenerateChoice(message=S.GenerateMessage(content=out.text),
-                                              finish_reason=out.finish_reason)],
+                    choices=[S.GenerateChoice(message=message, finish_reason=finish)],
                     usage=S.GenerateUsage(prompt_tokens=out.prompt_tokens, completion_tokens=out.completion_tokens,
                                           total_tokens=out.prompt_tokens + out.completion_tokens)).model_dump()
 
@@ -220,10 +265,26 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             def work():
                 lm = mgr.get(req.model, "generator")
                 loop.call_soon_threadsafe(q.put_nowait, chunk({"role": "assistant"}))
-                out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer),
-                                           on_delta=lambda d: loop.call_soon_threadsafe(q.put_nowait,
-                                                                                        chunk({"content": d})))
-                loop.call_soon_threadsafe(q.put_nowait, chunk({}, out.finish_reason))
+                parser = None
+                if tool_fmt is not None:
+                    from ..pipelines import tool_calls as TC
+
+                    parser = TC.ToolCallParser(tool_fmt)
+
+                def on_delta(d: str):
+                    shown = parser.feed(d) if parser is not None else d
+                    if shown:
+                        loop.call_soon_threadsafe(q.put_nowait, chunk({"content": shown}))
+
+                out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer), on_delta=on_delta)
+                finish = out.finish_reason
+                if parser is not None:
+                    _, calls = parser.finish()
+                    if calls:
+                        deltas = [dict(c, index=i) for i, c in enumerate(calls)]
+                        loop.call_soon_threadsafe(q.put_nowait, chunk({"tool_calls": deltas}))
+                        finish = "tool_calls"
+                loop.call_soon_threadsafe(q.put_nowait, chunk({}, finish))
                 return None
 
             res = run_guarded("generate", 1, work)

@@ -42,7 +42,8 @@ class ChatTemplate:
 
         env = jinja2.Environment(trim_blocks=True, lstrip_blocks=True)
         env.globals["raise_exception"] = lambda m: (_ for _ in ()).throw(ValueError(m))
-        self.template = env.from_string(source or DEFAULT_TEMPLATE)
+        self.source = source or DEFAULT_TEMPLATE
+        self.template = env.from_string(self.source)
 
     def apply(self, messages: Sequence[dict], add_generation_prompt: bool = True, **extra) -> str:
         msgs = []

@@ -88,6 +88,34 @@ def test_generate_streaming_sse(client):
     assert chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop")
 
 
+def test_generate_json_mode_gbnf_and_tools(client):
+    """Constrained decoding and tool plumbing through the HTTP API (random weights: only the constraints are
+    checked, not what the model says)."""
+    base = {"model": "tiny-gen", "messages": [{"role": "user", "content": "give me json"}], "max_tokens": 24,
+            "temperature": 0}
+    r = client.post("/ai/v1/chat/completions", json=dict(base, response_format={"type": "json_object"}))
+    assert r.status_code == 200
+    text = r.json()["choices"][0]["message"]["content"] or ""
+    assert text.lstrip().startswith("{")      # root must be an object; every prefix stays valid JSON
+    if r.json()["choices"][0]["finish_reason"] == "stop":
+        json.loads(text)
+    r = client.post("/ai/v1/chat/completions", json=dict(base, grammar='root ::= ("yes" | "no") "!"'))
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"] in ("yes!", "no!")
+    assert r.json()["choices"][0]["finish_reason"] == "stop"
+    r = client.post("/ai/v1/chat/completions", json=dict(base, grammar='root ::= undefined-rule'))
+    assert r.status_code == 400 and "never defined" in r.json()["message"]
+    tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object"}}}]
+    r = client.post("/ai/v1/chat/completions", json=dict(base, tools=tools, tool_choice="sometimes"))
+    assert r.status_code == 400
+    # force a syntactically valid tool call with a grammar and check it comes back parsed
+    call_grammar = 'root ::= "<tool_call>{\\"name\\": \\"lookup\\", \\"arguments\\": {\\"id\\": " [1-9] "}}</tool_call>"'
+    r = client.post("/ai/v1/chat/completions", json=dict(base, max_tokens=80, tools=tools, grammar=call_grammar))
+    assert r.status_code == 200, r.text
+    choice = r.json()["choices"][0]
+    assert choice["finish_reason"] == "tool_calls" and choice["message"]["tool_calls"][0]["function"]["name"] == "lookup"
+    assert 1 <= json.loads(choice["message"]["tool_calls"][0]["function"]["arguments"])["id"] <= 9
+
+
 def test_chunk_and_metrics(client):
     r = client.post("/ai/v1/chunk", json={"text": "a b c d e f g h i j", "target_tokens": 4, "overlap_tokens": 1})
     ch = r.json()["chunks"]
