@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: greedy decode throughput of a Llama-3-8B-architecture generator.
 
-Config (BASELINE.json #4): 32 layers, hidden 4096, 32 heads / 8 KV heads, FFN 14336 SwiGLU, vocab 128256,
+Config: 32 layers, hidden 4096, 32 heads / 8 KV heads, FFN 14336 SwiGLU, vocab 128256,
 RoPE theta 500000, random-init block-scaled fp8 weights, bf16 activations, 64 concurrent prompts of 2048
 uniform-random token ids, paged KV (block 16), greedy decoding, tensor parallel over --gpus ranks.
 
@@ -12,7 +12,7 @@ engine before the timed region (prefill is not part of the decode metric; its ti
 `value`   : tokens/s over K decode steps timed with CUDA events around a host-sync-free burst (graph replays).
 `e2e`     : tokens/s over K steps of LLMEngine.step(), each with its pinned-memory H2D of the step's inputs and
             a D2H read of the sampled tokens (wall clock between synchronisations).
-Other workloads of the metric string: --workload embed | knn.
+Other workloads: --workload embed | knn | rerank | cpu.
 """
 from __future__ import annotations
 
