@@ -83,6 +83,15 @@ def status(clear: bool = True) -> int:
     return int(cuda().afb_status_read(1 if clear else 0))
 
 
+def poison_waits() -> int:
+    """Make every bounded kernel wait (running, queued or future) give up at once; see ``afb_poison_waits``.
+    For watchdogs and signal handlers: the GPU drains before the process goes away.  ``status()`` clears it."""
+    try:
+        return int(cuda().afb_poison_waits())
+    except Exception:
+        return -1
+
+
 _launch_counter = 0
 
 

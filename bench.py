@@ -96,8 +96,32 @@ def _dist_setup(n_gpus):
     # A multi-rank run that stops making progress dumps every thread's Python stack and exits instead of
     # sitting in a collective until the launcher's limit.
     limit = int(os.environ.get("ANTFLY_B200_BENCH_WATCHDOG_S", "0"))
+
+    def _drain_and_exit(code):
+        # Never leave the process while kernels sit in cross-GPU waits: poison the waits so everything queued
+        # drains in microseconds, give the GPU a moment, then go.
+        try:
+            from antfly_b200 import _native as N
+
+            N.poison_waits()
+            time.sleep(1.0)
+        finally:
+            os._exit(code)
+
     if limit > 0:
-        faulthandler.dump_traceback_later(limit, exit=True)
+        import threading
+
+        def _watchdog():
+            faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+            _drain_and_exit(3)
+
+        t = threading.Timer(limit, _watchdog)
+        t.daemon = True
+        t.start()
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import signal
+
+        signal.signal(signal.SIGTERM, lambda *_: _drain_and_exit(4))
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -25,8 +25,11 @@ constexpr int kStatusAnyWaitTimeout = kStatusTmaWaitTimeout | kStatusEmptyWaitTi
                                       kStatusDequantWaitTimeout | kStatusPeerFlagTimeout | kStatusGridFlagTimeout;
 
 typedef int (*StatusReader)(int clear);
+// ORs `code` into the file's status word from the host, on `stream`, while kernels may be running.
+typedef int (*StatusPoisoner)(int code, cudaStream_t stream);
 // Defined in runtime.cu.
 void register_status_reader(StatusReader fn);
+void register_status_poisoner(StatusPoisoner fn);
 
 }  // namespace afb
 
@@ -49,6 +52,17 @@ struct AfbStatusRegistration {
         cudaMemcpyToSymbol(g_afb_status, &z, sizeof(int));
       }
       return v;
+    });
+    // Host-side poison: kernels spinning in a bounded wait re-read the word (uncached) and give up at once.
+    // The value is written, not OR-ed: the host cannot read-modify-write under a running kernel, and a set
+    // timeout code is all the waits look for.
+    afb::register_status_poisoner(+[](int code, cudaStream_t stream) -> int {
+      static int staged;
+      staged = code;
+      return cudaMemcpyToSymbolAsync(g_afb_status, &staged, sizeof(int), 0, cudaMemcpyHostToDevice, stream) ==
+                     cudaSuccess
+                 ? 0
+                 : -1;
     });
   }
 };

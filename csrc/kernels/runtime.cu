@@ -59,6 +59,24 @@ CUtensorMapSwizzle swizzle_for(int s) {
 
 void register_status_reader(StatusReader fn) { readers().push_back(fn); }
 
+namespace {
+std::vector<StatusPoisoner>& poisoners() {
+  static std::vector<StatusPoisoner> p;
+  return p;
+}
+}  // namespace
+void register_status_poisoner(StatusPoisoner fn) { poisoners().push_back(fn); }
+int poison_all(int code) {
+  // A stream of its own, non-blocking with respect to the default stream, so the writes overtake whatever
+  // kernels are queued or spinning on the compute streams.
+  static cudaStream_t s = nullptr;
+  if (!s && cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return -1;
+  int rc = 0;
+  for (auto fn : poisoners()) rc |= fn(code, s);
+  if (cudaStreamSynchronize(s) != cudaSuccess) rc = -1;
+  return rc;
+}
+
 int g_pdl = -1;
 bool pdl_enabled() {
   if (g_pdl < 0) {
@@ -148,6 +166,12 @@ int afb_status_read(int clear) {
   }
   return v;
 }
+
+// Makes every bounded wait of every kernel file give up at once, including waits of kernels that are running or
+// queued right now (a CUDA graph full of cross-GPU hand-offs whose peer will never answer): the timeout code is
+// written into each status word from a side stream.  Call before tearing a process down on a watchdog or signal,
+// so the GPU drains in microseconds and is idle when the process exits.  afb_status_read(1) clears it again.
+int afb_poison_waits() { return afb::poison_all(afb::kStatusPeerFlagTimeout); }
 
 // Programmatic dependent launch on (1) / off (0) for the kernels that support it; default on, or
 // ANTFLY_B200_PDL=0 in the environment.

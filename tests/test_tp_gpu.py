@@ -91,3 +91,10 @@ def test_cross_gpu_wait_expires_with_status_and_later_waits_give_up_at_once():
     assert 1.0 < first < 10.0, first     # the wait ran to its limit (about two seconds), not forever
     assert second < 0.5, second          # poisoned: the next wait gave up at once
     assert N.status() == 0               # reading cleared it
+    # the host can poison the waits too (what a watchdog or a SIGTERM handler does before the process leaves)
+    assert N.poison_waits() == 0
+    t0 = time.perf_counter()
+    run()
+    assert time.perf_counter() - t0 < 0.5
+    assert N.status() & 16
+    assert N.status() == 0
