@@ -56,6 +56,15 @@ def _forward_logits(model, cfg, device="cpu"):
     return model.forward(b, kc, torch.zeros_like(kc)).float()
 
 
+def _tp_cfg(world):
+    from antfly_b200.models.llama import LlamaConfig
+
+    if world <= 2:
+        return LlamaConfig.tiny(num_hidden_layers=2)
+    return LlamaConfig.tiny(num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=4, hidden_size=512,
+                            intermediate_size=1024)
+
+
 def _tp_worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -67,12 +76,13 @@ def _tp_worker(rank, world, port, q):
     comm = TpComm(rank, world, torch.device("cpu"))
     t = torch.full((3,), float(rank + 1))
     comm.all_reduce(t)
-    assert t.tolist() == [3.0, 3.0, 3.0]
-    # vocabulary-sharded arg-max merge: rank 1 holds the winner of row 0, a tie in row 1 resolves to the lower index
+    assert t.tolist() == [world * (world + 1) / 2.0] * 3
+    # vocabulary-sharded arg-max merge: the last rank holds the winner of row 0, a tie in row 1 resolves to the
+    # lower index
     idx = torch.tensor([5 + 100 * rank, 7 + 100 * rank], dtype=torch.int32)
     val = torch.tensor([1.0 + rank, 2.0])
-    assert comm.argmax_merge(idx, val).tolist() == [105, 7]
-    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    assert comm.argmax_merge(idx, val).tolist() == [5 + 100 * (world - 1), 7]
+    cfg = _tp_cfg(world)
     sd = _hf_llama_state(cfg)
     model = LlamaModel.from_state_dict(cfg, sd, device="cpu", tp_rank=rank, tp_size=world, comm=comm)
     logits = _forward_logits(model, cfg)                    # [2, V / world]
@@ -84,20 +94,21 @@ def _tp_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-def test_tensor_parallel_decoder_matches_single_rank():
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_decoder_matches_single_rank(world):
     from antfly_b200.models.llama import LlamaConfig, LlamaModel
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     full, tok = q.get(timeout=240)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    cfg = _tp_cfg(world)
     single = LlamaModel.from_state_dict(cfg, _hf_llama_state(cfg), device="cpu")
     ref = _forward_logits(single, cfg)
     torch.testing.assert_close(full, ref, atol=6e-2, rtol=5e-2)
