@@ -20,6 +20,7 @@ from ..models.llama import LlamaModel, StepBatch
 from ..ops import attention as A
 from ..ops import sampling as S
 from .kv_cache import KvOutOfBlocks, PagedKvCache
+from .prefix_cache import PrefixCache
 from .sampling_params import SamplingParams
 from .scheduler import SchedulerPolicy, StepItem, StepScheduler
 
@@ -103,7 +104,8 @@ class LLMEngine:
     def __init__(self, model: LlamaModel, num_blocks: int, page: int = 16, max_batch: int = 64,
                  max_step_tokens: int = 8192, prefill_chunk: int = 2048, kv_dtype: str = "bf16",
                  use_cuda_graph: bool = True, draft_layers: int = 0, spec_k: int = 4, eos_token_id: Optional[int] = None,
-                 max_seq_len: int = 8192 + 1024, max_queue: int = 0):
+                 max_seq_len: int = 8192 + 1024, max_queue: int = 0, prefix_cache: bool = False,
+                 prefix_cache_entries: int = 256):
         self.model = model
         self.device = model.device
         self.page = page
@@ -120,6 +122,11 @@ class LLMEngine:
         self._static: Dict[tuple, _StaticStep] = {}
         self._attn_scratch: Optional[A.PagedAttnScratch] = None
         self.draft = model.draft_view(draft_layers) if draft_layers > 0 else None
+        # Prompts that begin with already-prefilled tokens reuse those KV blocks (not with a sliding window, whose
+        # trimming releases the very blocks a later prompt would share).
+        self.prefix: Optional[PrefixCache] = None
+        if prefix_cache and not getattr(model.cfg, "sliding_window", 0):
+            self.prefix = PrefixCache(self.cache.alloc, page, prefix_cache_entries)
         self.spec_k = spec_k
         self.spec = SpecStats()
         self.counts: Optional[torch.Tensor] = None  # [max_batch, V] int16 penalty table, allocated lazily
@@ -134,8 +141,22 @@ class LLMEngine:
     def add_request(self, prompt: Sequence[int], params: SamplingParams) -> int:
         rid = self._next_id
         self._next_id += 1
-        self.sched.admit(rid, len(prompt), params.max_tokens)
-        self.cache.alloc.attach(rid)
+        shared = 0
+        if self.prefix is not None:
+            eid, n = self.prefix.lookup(prompt)
+            if eid is not None:
+                try:
+                    self.cache.alloc.attach_shared(rid, eid, n)
+                    shared = n
+                except (KvOutOfBlocks, KeyError):
+                    shared = 0
+        if not shared:
+            self.cache.alloc.attach(rid)
+        try:
+            self.sched.admit(rid, len(prompt), params.max_tokens, prompt_done=shared)
+        except Exception:
+            self.cache.alloc.detach(rid)
+            raise
         r = Request(rid, list(prompt), params, t_admit=time.perf_counter())
         if params.needs_penalties:
             r.row = self._rows_free.pop()
@@ -369,7 +390,18 @@ class LLMEngine:
                     toks_dev = None
         except KvOutOfBlocks:
             self.sched.fail_step()
+            # Slots reserved for the items packed before the one that failed go back to the pool.
+            for it in items:
+                if self.cache.alloc.length(it.request_id) > it.kv_before:
+                    self.cache.alloc.truncate(it.request_id, it.kv_before)
+            # Cached prefixes are the first thing to give up under memory pressure: drop one and retry the step.
+            if self.prefix is not None and self.prefix.evict_one():
+                return 0
             raise
+        if self.prefix is not None:
+            for it, r in zip(items, reqs):
+                if it.mode != "decode" and it.kv_before + it.q_len >= len(r.prompt):
+                    self.prefix.insert(it.request_id, r.prompt)
         toks = toks_dev.cpu().tolist() if toks_dev is not None else []
         self.d2h_bytes += 4 * len(toks)
         now = time.perf_counter()

@@ -80,8 +80,12 @@ class StepScheduler:
         except Exception:
             pass
 
-    def admit(self, request_id: int, prompt_len: int, max_new_tokens: int) -> None:
-        rc = self.lib.afb_sched_admit(self.h, request_id, prompt_len, max_new_tokens)
+    def admit(self, request_id: int, prompt_len: int, max_new_tokens: int, prompt_done: int = 0) -> None:
+        """``prompt_done`` > 0: that many leading prompt tokens are already in the KV cache (shared prefix)."""
+        if prompt_done > 0:
+            rc = self.lib.afb_sched_admit_prefilled(self.h, request_id, prompt_len, max_new_tokens, prompt_done)
+        else:
+            rc = self.lib.afb_sched_admit(self.h, request_id, prompt_len, max_new_tokens)
         if rc == -2:
             raise QueueFull("generation queue is full")
         if rc != 0:

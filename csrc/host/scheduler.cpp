@@ -94,6 +94,18 @@ int afb_sched_admit(void* h, int64_t id, int prompt_len, int max_new_tokens) {
   return 0;
 }
 
+// As afb_sched_admit for a request whose first `prompt_done` prompt tokens are already in the KV cache (a shared
+// prefix): prefill starts after them.  At least one prompt token must remain so the first output token has logits.
+int afb_sched_admit_prefilled(void* h, int64_t id, int prompt_len, int max_new_tokens, int prompt_done) {
+  if (prompt_done < 0 || prompt_done >= prompt_len) return -1;
+  const int rc = afb_sched_admit(h, id, prompt_len, max_new_tokens);
+  if (rc != 0) return rc;
+  Sched* s = static_cast<Sched*>(h);
+  std::lock_guard<std::mutex> g(s->mu);
+  s->reqs[id].prompt_done = prompt_done;
+  return 0;
+}
+
 int afb_sched_set_decode_width(void* h, int64_t id, int width) {
   Sched* s = static_cast<Sched*>(h);
   std::lock_guard<std::mutex> g(s->mu);

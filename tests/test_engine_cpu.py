@@ -84,3 +84,47 @@ def test_engine_generates_with_layernorm_decoder_family():
                       i32([n - 1]), n, 1)
         seq.append(int(model.forward(b, kc, vc).float().argmax(-1)))
     assert got == seq[len(prompt):], (got, seq[len(prompt):])
+
+
+def test_prefix_cache_reuses_blocks_and_keeps_outputs():
+    """Requests whose prompts share a block-aligned prefix skip prefilling it; generated tokens are the same as
+    without the cache; entries are evicted when the pool runs short."""
+    import torch
+
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    cfg = LlamaConfig.tiny(vocab_size=256)
+    model = LlamaModel.random_init(cfg, device="cpu", seed=5, fast_init=False)
+    g = torch.Generator().manual_seed(0)
+    system = torch.randint(0, 256, (70,), generator=g).tolist()           # 4 whole blocks + 6 tokens
+    prompts = [system + torch.randint(0, 256, (n,), generator=g).tolist() for n in (5, 9, 3)]
+
+    def run(prefix_cache, num_blocks=64):
+        eng = LLMEngine(model, num_blocks=num_blocks, page=16, max_batch=4, max_step_tokens=128, prefill_chunk=32,
+                        max_seq_len=128, use_cuda_graph=False, prefix_cache=prefix_cache)
+        outs = []
+        for p in prompts:   # one after the other so the later ones can hit
+            rid = eng.add_request(p, SamplingParams(max_tokens=6, ignore_eos=True))
+            while eng.has_work():
+                eng.step()
+            outs.append(list(eng.reqs[rid].out))
+        return eng, outs
+
+    base_eng, base = run(False)
+    eng, got = run(True)
+    assert got == base
+    st = eng.prefix.stats()
+    assert st["hits"] == 2 and st["misses"] == 1 and st["tokens_reused"] == 2 * 64
+    # the shared prompt blocks are held once by the cache entries, not once per request
+    assert eng.sched.stats()["step_query_tokens_total"] < base_eng.sched.stats()["step_query_tokens_total"] - 100
+    free_with_entries = eng.cache.alloc.free_blocks
+    eng.prefix.clear()
+    assert eng.cache.alloc.free_blocks > free_with_entries and eng.cache.alloc.free_blocks == 64
+
+    # a pool too small to keep every cached prefix: entries are dropped on demand and generation still completes
+    prompts = [torch.randint(0, 256, (70 + i,), generator=g).tolist() for i in range(3)]   # unrelated prompts
+    _, want = run(False, num_blocks=64)
+    small, got_small = run(True, num_blocks=10)
+    assert got_small == want and small.prefix.stats()["evictions"] >= 1 and small.prefix.stats()["hits"] == 0
