@@ -42,11 +42,11 @@ class LoadedModel:
 
 class ModelManager:
     def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
-                 kv_blocks: int = 4096, max_batch: int = 64):
+                 kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True):
         self.models_dir = models_dir or MF.default_models_dir()
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         self.max_loaded = max_loaded_models
-        self.kv_blocks, self.max_batch = kv_blocks, max_batch
+        self.kv_blocks, self.max_batch, self.prefix_cache = kv_blocks, max_batch, prefix_cache
         self._models: "OrderedDict[str, LoadedModel]" = OrderedDict()
         self._lock = threading.Lock()
 
@@ -76,7 +76,8 @@ class ModelManager:
         model = LlamaModel.random_init(cfg, device=dev, seed=seed, fast_init=(size != "tiny"))
         tok = ByteTokenizer(cfg.vocab_size)
         eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
-                        use_cuda_graph=dev.type == "cuda", eos_token_id=tok.special.eos_id)
+                        use_cuda_graph=dev.type == "cuda", eos_token_id=tok.special.eos_id,
+                        prefix_cache=self.prefix_cache)
         return self.register(name, "generator", Generator(eng, tok), tok, {"random_init": True})
 
     # -- directory-backed models ---------------------------------------------------------------------------
@@ -106,7 +107,8 @@ class ModelManager:
                 cfg = LlamaConfig.from_hf(cfg_d)
                 model = LlamaModel.from_state_dict(cfg, sd, device=self.device)
             eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
-                            use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id)
+                            use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id,
+                            prefix_cache=self.prefix_cache)
             pipe = Generator(eng, tok, mf.chat_template)
         return LoadedModel(name, task, pipe, tok, path, info={"weights": mf.weights, "capabilities": mf.capabilities})
 

@@ -29,7 +29,8 @@ def _manager(args):
     from .api.model_manager import ModelManager
 
     return ModelManager(models_dir=getattr(args, "models_dir", None), device=getattr(args, "device", None),
-                        kv_blocks=getattr(args, "kv_blocks", 4096))
+                        kv_blocks=getattr(args, "kv_blocks", 4096),
+                        prefix_cache=not getattr(args, "no_prefix_cache", False))
 
 
 def _get(mgr, name: str, task: str):
@@ -162,6 +163,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         p.add_argument("--models-dir")
         p.add_argument("--device")
         p.add_argument("--kv-blocks", type=int, default=4096)
+        p.add_argument("--no-prefix-cache", action="store_true",
+                       help="do not reuse the KV blocks of prompt prefixes that were prefilled before")
 
     p = sub.add_parser("run"); common(p)
     p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=11433)
