@@ -12,6 +12,8 @@
 #include <stdint.h>
 #include <string.h>
 
+#include "../common/gguf_elem.h"
+
 namespace {
 
 inline float half_to_float(uint16_t h) {
@@ -409,6 +411,10 @@ int afb_gguf_dequantize(int type, const uint8_t* src, float* dst, long n_values)
     default: return -1;
   }
 }
+
+// Value j of one block through the host/device per-element decoder (the code the GPU kernel runs).
+float afb_gguf_element(int type, const uint8_t* block, int j) { return afb::gguf::element(type, block, j); }
+long afb_gguf_element_block_values(int type) { return afb::gguf::block_values(type); }
 
 // Quantisers (used by tests and the export tool).
 int afb_gguf_quantize_q8_0(const float* src, uint8_t* dst, long n_values) {

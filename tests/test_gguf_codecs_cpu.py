@@ -79,3 +79,28 @@ def test_quantize_roundtrip_through_gguf_package():
         fn(x.ctypes.data_as(ctypes.c_void_p), raw.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(x.size))
         back = gguf.quants.dequantize(raw, qt).astype(np.float32).reshape(-1)
         assert float(np.abs(back - x).max()) < tol * float(np.abs(x).max())
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "MXFP4"])
+def test_per_element_decoder_matches_block_decoder(name):
+    """The host/device per-element decoder (what the GPU expansion kernel runs per thread) against the
+    block-at-a-time decoder, element by element."""
+    qt = getattr(gguf.GGMLQuantizationType, name)
+    values, nbytes = gguf.GGML_QUANT_SIZES[qt]
+    lib = N.host()
+    lib.afb_gguf_element.restype = ctypes.c_float
+    lib.afb_gguf_element_block_values.restype = ctypes.c_long
+    assert lib.afb_gguf_element_block_values(int(qt)) == values
+    rng = np.random.default_rng(100 + int(qt))
+    blocks = 6
+    raw = rng.integers(0, 256, size=(blocks, nbytes), dtype=np.uint8)
+    for off in HALF_FIELDS[name]:
+        raw[:, off:off + 2] = rng.uniform(-2.0, 2.0, size=blocks).astype(np.float16).view(np.uint8).reshape(blocks, 2)
+    if name == "MXFP4":
+        raw[:, 0] = rng.integers(110, 140, size=blocks)
+    want = _ours(int(qt), np.ascontiguousarray(raw.reshape(-1)), blocks * values).reshape(blocks, values)
+    for b in range(blocks):
+        blk = np.ascontiguousarray(raw[b])
+        got = np.array([lib.afb_gguf_element(ctypes.c_int(int(qt)), blk.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(j))
+                        for j in range(values)], dtype=np.float32)
+        np.testing.assert_allclose(got, want[b], rtol=1e-6, atol=1e-6)
