@@ -224,6 +224,10 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     msgs[0] = dict(msgs[0], content=(msgs[0].get("content") or "") + "\n\n" + decl)
                 else:
                     msgs.insert(0, {"role": "system", "content": decl})
+        if req.cache_dtype not in (None, "bf16", "f16"):
+            # engines are built with a bf16 cache; a per-request dtype cannot be honoured after the fact
+            return _err(400, "invalid_request", f"cache_dtype {req.cache_dtype!r} is not supported by this server "
+                                                "(KV cache is bf16)")
         if req.grammar:
             try:  # reject a malformed grammar before any work is queued
                 from ..runtime.grammar import GbnfGrammar

@@ -73,6 +73,9 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
 
             return Q.quantize_mx(y.reshape(T, Hq * D), terms=mx_terms)
         return y
+    if k_cache.dtype != torch.bfloat16:
+        raise NotImplementedError("the GPU attention kernels read a bf16 KV cache; an fp8 cache is supported on the "
+                                  "write side and on the CPU path only")
     G = Hq // Hkv
     if decode is None:
         decode = max_q_len * G <= 16

@@ -109,6 +109,9 @@ class LLMEngine:
         self.model = model
         self.device = model.device
         self.page = page
+        if self.device.type == "cuda" and kv_dtype not in ("bf16", "bfloat16", "f16"):
+            raise ValueError(f"KV cache dtype {kv_dtype!r} is not available on the GPU path (bf16 only); "
+                             "the CPU path also accepts fp8")
         self.cache = PagedKvCache(model.n_layers, num_blocks, model.Hkv, model.D, page, kv_dtype, self.device)
         self.max_batch = max_batch
         self.max_blocks = (max_seq_len + page - 1) // page
