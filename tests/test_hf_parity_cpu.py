@@ -220,3 +220,55 @@ def test_roberta_family_matches_transformers(kind):
     got = model.embed(batch, pooling="mean", normalize=True).float()
     cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
     assert float(cos.min()) > 0.999, cos
+
+
+def test_clip_text_and_vision_towers_match_transformers():
+    from antfly_b200.models.clip import ClipConfig, ClipModel
+    from antfly_b200.ops import image_ops as I
+
+    torch.manual_seed(4)
+    hf_cfg = transformers.CLIPConfig(
+        text_config=dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, max_position_embeddings=24, eos_token_id=2, bos_token_id=0,
+                         pad_token_id=1, attention_dropout=0.0),
+        vision_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           image_size=32, patch_size=8, attention_dropout=0.0),
+        projection_dim=48)
+    hf = transformers.CLIPModel(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+    cfg = ClipConfig.from_hf(hf_cfg.to_dict())
+    assert cfg.text.hidden_act == "quick_gelu" and cfg.vision.patch_size == 8 and cfg.projection_dim == 48
+    model = ClipModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+
+    # text: sequences of different lengths, the end-of-text token has the highest id (original tokenizer layout)
+    seqs = [[298] + torch.randint(3, 290, (n,)).tolist() + [299] for n in (3, 9, 15)]
+    L = max(len(s) for s in seqs)
+    ids = torch.full((len(seqs), L), 1, dtype=torch.long)
+    mask = torch.zeros_like(ids)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.tensor(s)
+        mask[i, : len(s)] = 1
+    with torch.no_grad():
+        want_t = hf.get_text_features(input_ids=ids, attention_mask=mask)
+    want_t = getattr(want_t, "pooler_output", want_t)
+    got_t = model.embed_text(seqs, normalize=False)
+    # (the CPU path rounds every GEMM output to bf16 like the kernels do: compare directions and magnitudes)
+    assert float(torch.nn.functional.cosine_similarity(got_t, want_t.float(), dim=-1).min()) > 0.9995
+    torch.testing.assert_close(got_t, want_t.float(), atol=3e-2, rtol=3e-2)
+
+    # vision: uint8 images through our preprocessing, the same pixels into the reference
+    g = torch.Generator().manual_seed(0)
+    imgs = torch.randint(0, 256, (2, 40, 52, 3), generator=g, dtype=torch.uint8)
+    pixels = I.clip_preprocess(imgs, size=32, mode="bicubic")
+    with torch.no_grad():
+        want_v = hf.get_image_features(pixel_values=pixels)
+    want_v = getattr(want_v, "pooler_output", want_v)
+    got_v = model.embed_images(pixels, normalize=False)
+    assert float(torch.nn.functional.cosine_similarity(got_v, want_v.float(), dim=-1).min()) > 0.9995
+    torch.testing.assert_close(got_v, want_v.float(), atol=3e-2, rtol=3e-2)
+    # normalised embeddings give the usual similarity matrix
+    sim = model.embed_text(seqs) @ model.embed_images(pixels).T
+    assert sim.shape == (3, 2) and float(sim.abs().max()) <= 1.0 + 1e-5

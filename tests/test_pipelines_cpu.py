@@ -106,3 +106,34 @@ def test_sentencepiece_tokenizer_roundtrip_and_token_bytes(tmp_path):
     joined = b"".join(tok.token_bytes(i) for i in ids).decode("utf-8")
     assert joined.lstrip(" ") == text
     assert tok.token_bytes(tok.special.eos_id) == b""
+
+
+def test_clip_embedder_pipeline(tmp_path):
+    import numpy as np
+
+    from antfly_b200.models.clip import ClipConfig, ClipModel
+    from antfly_b200.pipelines.multimodal import ClipEmbedder, load_image
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.CLIPConfig(
+        text_config=dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                         num_attention_heads=4, max_position_embeddings=16),
+        vision_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                           image_size=32, patch_size=16), projection_dim=32)
+    hf = transformers.CLIPModel(hf_cfg).eval()
+    model = ClipModel.from_state_dict(ClipConfig.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                      dtype=torch.float32)
+    emb = ClipEmbedder(model)
+    rng = np.random.default_rng(0)
+    arr = rng.integers(0, 256, size=(50, 70, 3), dtype=np.uint8)
+    imgs = [arr, torch.from_numpy(rng.integers(0, 256, size=(33, 33, 4), dtype=np.uint8)), arr[:, :, 0]]
+    pil = pytest.importorskip("PIL.Image")
+    path = tmp_path / "img.png"
+    pil.fromarray(arr).save(path)
+    imgs.append(str(path))
+    e = emb.embed_images(imgs)
+    assert e.shape == (4, 32) and torch.allclose(e.norm(dim=-1), torch.ones(4), atol=1e-4)
+    torch.testing.assert_close(e[0], e[3], atol=1e-5, rtol=1e-5)     # the PNG round trip is lossless
+    assert load_image(arr[:, :, 0]).shape == (50, 70, 3)
+    t = emb.embed_token_ids([[298, 5, 6, 299], [298, 7, 299]])
+    assert t.shape == (2, 32) and (t @ e.T).shape == (2, 4)
