@@ -94,7 +94,13 @@ class ModelManager:
             sd, cfg_d = ST.load_model_dir(path), mf.config
         else:
             raise ModelNotFound(f"{name}: no loadable weights (found {mf.weights})")
-        if task in ("embedder", "reranker"):
+        if task == "embedder" and cfg_d.get("model_type") == "clip":
+            from ..models.clip import ClipConfig, ClipModel
+            from ..pipelines.multimodal import ClipEmbedder
+
+            model = ClipModel.from_state_dict(ClipConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = ClipEmbedder(model, tok)
+        elif task in ("embedder", "reranker"):
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)

@@ -115,19 +115,55 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         req, bad = await parse(request, S.EmbedRequest)
         if bad:
             return bad
+        images = {}  # position in the input -> decoded image (content parts of type image_url / image)
         if isinstance(req.input, str):
             texts = [req.input]
         else:
-            texts = [p if isinstance(p, str) else (p.text or "") for p in req.input]
-            if any(not isinstance(p, str) and p.type != "text" for p in req.input):
-                return _err(400, "invalid_request", "only text content parts are supported by this build")
+            texts = []
+            for i, p in enumerate(req.input):
+                if isinstance(p, str):
+                    texts.append(p)
+                elif p.type == "text":
+                    texts.append(p.text or "")
+                elif p.type in ("image_url", "image"):
+                    extra = p.model_extra or {}
+                    url = extra.get("image_url") or extra.get("url") or extra.get("image")
+                    if isinstance(url, dict):
+                        url = url.get("url")
+                    try:
+                        from ..pipelines.multimodal import decode_data_url
+
+                        images[i] = decode_data_url(url or "")
+                    except Exception as e:
+                        return _err(400, "invalid_request", f"content part {i}: {e}")
+                    texts.append(None)
+                else:
+                    return _err(400, "invalid_request", f"content part type {p.type!r} is not supported")
         if not texts:
             return _err(400, "invalid_request", "input must not be empty")
         task_type = req.task_type or INPUT_TYPE_ALIASES.get(req.input_type or "")
 
         def work():
             lm = mgr.get(req.model, "embedder")
-            emb, ntok = lm.pipeline.embed(texts, task_type, req.dimensions)
+            if images:
+                if not hasattr(lm.pipeline, "embed_images"):
+                    raise ValueError(f"model {req.model!r} does not embed images")
+                import torch as _torch
+
+                only_text = [t for t in texts if t is not None]
+                temb, ntok = lm.pipeline.embed(only_text, task_type, req.dimensions) if only_text else (None, 0)
+                iemb = lm.pipeline.embed_images([images[i] for i in sorted(images)]).cpu()
+                if req.dimensions:
+                    iemb = _torch.nn.functional.normalize(iemb[:, : req.dimensions], dim=-1)
+                rows, ti, ii = [], 0, 0
+                for i, t in enumerate(texts):
+                    if t is None:
+                        rows.append(iemb[ii]); ii += 1
+                    else:
+                        rows.append(temb[ti]); ti += 1
+                emb = _torch.stack(rows)
+            else:
+                emb, ntok = lm.pipeline.embed(texts, task_type, req.dimensions)
             metrics.tokens.labels("embed", "prompt").inc(ntok)
             data = [S.EmbeddingObject(embedding=row.tolist(), index=i) for i, row in enumerate(emb)]
             return S.EmbedResponse(data=data, model=req.model,

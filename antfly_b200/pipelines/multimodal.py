@@ -20,6 +20,27 @@ from ..ops import image_ops as I
 ImageLike = Union[str, np.ndarray, torch.Tensor]
 
 
+def decode_image_bytes(data: bytes) -> torch.Tensor:
+    """Encoded image bytes (PNG / JPEG / ...) -> uint8 [H, W, 3] tensor (needs Pillow)."""
+    import io
+
+    from PIL import Image
+
+    with Image.open(io.BytesIO(data)) as im:
+        return torch.from_numpy(np.asarray(im.convert("RGB")).copy())
+
+
+def decode_data_url(url: str) -> torch.Tensor:
+    """``data:image/png;base64,...`` -> uint8 [H, W, 3]."""
+    import base64
+
+    if not url.startswith("data:") or "," not in url:
+        raise ValueError("only data: URLs are accepted (this server does not fetch remote images)")
+    head, payload = url.split(",", 1)
+    raw = base64.b64decode(payload) if head.endswith(";base64") else payload.encode("latin-1")
+    return decode_image_bytes(raw)
+
+
 def load_image(src: ImageLike) -> torch.Tensor:
     """-> uint8 [H, W, 3 or 4] tensor on the host."""
     if isinstance(src, torch.Tensor):
@@ -61,6 +82,16 @@ class ClipEmbedder:
             pix.append(I.clip_preprocess(img.to(dev) if dev.type == "cuda" else img, size=size, mode=self.resample)[0])
         out = [self.model.embed_images(torch.stack(pix[i:i + batch_size])) for i in range(0, len(pix), batch_size)]
         return torch.cat(out, 0) if out else torch.zeros((0, self.dim))
+
+    def embed(self, texts: Sequence[str], task_type: Optional[str] = None, dimensions: Optional[int] = None):
+        """The text-embedding contract of the HTTP endpoint: (fp32 [N, dims] on the host, prompt tokens)."""
+        e = self.embed_texts(texts).cpu()
+        if dimensions:
+            if dimensions > e.shape[1]:
+                raise ValueError(f"dimensions {dimensions} exceeds the model's {e.shape[1]}")
+            e = torch.nn.functional.normalize(e[:, :dimensions], dim=-1)
+        limit = self.model.cfg.text.max_position_embeddings
+        return e, sum(min(len(self.tokenizer.encode(t)) + 2, limit) for t in texts)
 
     def embed_token_ids(self, seqs: Sequence[Sequence[int]]) -> torch.Tensor:
         return self.model.embed_text(seqs)

@@ -116,6 +116,48 @@ def test_generate_json_mode_gbnf_and_tools(client):
     assert 1 <= json.loads(choice["message"]["tool_calls"][0]["function"]["arguments"])["id"] <= 9
 
 
+def test_embed_images_and_text_with_a_clip_model():
+    """Content parts of type image_url (data: URLs) and text through one CLIP-style embedder."""
+    import base64
+    import io
+
+    import numpy as np
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    pil = pytest.importorskip("PIL.Image")
+    from antfly_b200.models.clip import ClipConfig, ClipModel
+    from antfly_b200.pipelines.multimodal import ClipEmbedder
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.CLIPConfig(
+        text_config=dict(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                         num_attention_heads=4, max_position_embeddings=32, eos_token_id=2),
+        vision_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                           image_size=32, patch_size=16), projection_dim=32)
+    model = ClipModel.from_state_dict(ClipConfig.from_hf(hf_cfg.to_dict()), transformers.CLIPModel(hf_cfg).state_dict(),
+                                      device="cpu", dtype=torch.float32)
+    tok = ByteTokenizer(512)
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register("tiny-clip", "embedder", ClipEmbedder(model, tok), tok)
+    c = TestClient(create_app(mgr))
+    buf = io.BytesIO()
+    pil.fromarray(np.random.default_rng(0).integers(0, 256, size=(40, 60, 3), dtype=np.uint8)).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    r = c.post("/ai/v1/embed", json={"model": "tiny-clip", "input": [
+        {"type": "text", "text": "a photo"}, {"type": "image_url", "image_url": {"url": url}},
+        {"type": "text", "text": "another"}]})
+    assert r.status_code == 200, r.text
+    data = r.json()["data"]
+    assert [d["index"] for d in data] == [0, 1, 2] and all(len(d["embedding"]) == 32 for d in data)
+    assert all(abs(sum(v * v for v in d["embedding"]) - 1.0) < 1e-3 for d in data)
+    r = c.post("/ai/v1/embed", json={"model": "tiny-clip", "input": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]})
+    assert r.status_code == 400 and "data:" in r.json()["message"]
+    r = c.post("/ai/v1/embed", json={"model": "tiny-clip", "input": [{"type": "audio", "text": "x"}]})
+    assert r.status_code == 400
+
+
 def test_chunk_and_metrics(client):
     r = client.post("/ai/v1/chunk", json={"text": "a b c d e f g h i j", "target_tokens": 4, "overlap_tokens": 1})
     ch = r.json()["chunks"]
