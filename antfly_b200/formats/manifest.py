@@ -54,7 +54,7 @@ class Manifest:
         arch = " ".join(self.config.get("architectures") or [])
         if "ForSequenceClassification" in arch:
             return "reranker"
-        if "CausalLM" in arch or self.config.get("model_type") in ("llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "gpt2",
+        if "CausalLM" in arch or self.config.get("model_type") in ("llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "mixtral", "qwen2_moe", "qwen3_moe", "gpt2",
                                                                      "gpt_neox", "opt", "gptj", "phi"):
             return "generator"
         return "embedder"

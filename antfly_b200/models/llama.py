@@ -48,6 +48,12 @@ class LlamaConfig:
     norm_plus_one: bool = False   # Gemma: RMSNorm scales by (1 + gamma)
     embed_scale: float = 1.0      # Gemma: token embeddings multiplied by sqrt(hidden)
     gate_act: str = "silu"        # gated-MLP activation: silu (SwiGLU) or gelu_tanh (GeGLU, Gemma)
+    # Mixture of experts (Mixtral, Qwen2-MoE, Qwen3-MoE): 0 experts = dense MLP
+    num_experts: int = 0
+    num_experts_per_tok: int = 2
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True   # renormalise the selected experts' weights to sum to one
+    shared_expert_intermediate_size: int = 0
 
     def __post_init__(self):
         if not self.head_dim:
@@ -77,6 +83,17 @@ class LlamaConfig:
             cfg.qkv_bias = True
         if mt == "qwen3":
             cfg.qk_norm = True
+        if mt in ("mixtral", "qwen2_moe", "qwen3_moe"):
+            cfg.num_experts = int(d.get("num_local_experts") or d.get("num_experts") or 0)
+            cfg.num_experts_per_tok = int(d.get("num_experts_per_tok", 2))
+            cfg.moe_intermediate_size = int(d.get("moe_intermediate_size") or d.get("intermediate_size"))
+            cfg.norm_topk_prob = True if mt == "mixtral" else bool(d.get("norm_topk_prob", False))
+            cfg.shared_expert_intermediate_size = int(d.get("shared_expert_intermediate_size") or 0) \
+                if mt == "qwen2_moe" else 0
+            if d.get("mlp_only_layers") or int(d.get("decoder_sparse_step", 1) or 1) != 1:
+                raise ValueError("models that mix dense and sparse MLP layers are not supported")
+            cfg.qkv_bias = mt == "qwen2_moe"
+            cfg.qk_norm = mt == "qwen3_moe"
         if mt == "gemma":
             cfg.norm_plus_one = True
             cfg.embed_scale = float(cfg.hidden_size) ** 0.5
@@ -236,6 +253,29 @@ class LlamaModel:
                 w[p + "qn"] = sd[s + "self_attn.q_norm.weight"].to(torch.bfloat16).to(device)
                 w[p + "kn"] = sd[s + "self_attn.k_norm.weight"].to(torch.bfloat16).to(device)
             w[p + "o"] = Q.pack_fp8(shard_cols(sd[s + "self_attn.o_proj.weight"], tp_rank, tp_size).to(device))
+            if cfg.num_experts > 0:
+                assert tp_size == 1, "mixture-of-experts models run on one GPU"
+                moe = s + ("block_sparse_moe." if s + "block_sparse_moe.gate.weight" in sd else "mlp.")
+                w[p + "router"] = sd[moe + "gate.weight"].to(torch.bfloat16).to(device)
+                Fm = cfg.moe_intermediate_size
+                for e in range(cfg.num_experts):
+                    if moe + "experts.gate_up_proj" in sd:      # fused [E, 2F, H] (gate rows, then up rows) / [E, H, F]
+                        gu = sd[moe + "experts.gate_up_proj"][e]
+                        g_e, u_e, d_e = gu[:Fm], gu[Fm:], sd[moe + "experts.down_proj"][e]
+                    elif moe + f"experts.{e}.w1.weight" in sd:  # Mixtral checkpoints: w1 gate, w3 up, w2 down
+                        g_e, u_e = sd[moe + f"experts.{e}.w1.weight"], sd[moe + f"experts.{e}.w3.weight"]
+                        d_e = sd[moe + f"experts.{e}.w2.weight"]
+                    else:
+                        g_e, u_e = sd[moe + f"experts.{e}.gate_proj.weight"], sd[moe + f"experts.{e}.up_proj.weight"]
+                        d_e = sd[moe + f"experts.{e}.down_proj.weight"]
+                    w[p + f"e{e}.gu"] = Q.pack_fp8_swiglu(g_e.to(device), u_e.to(device))
+                    w[p + f"e{e}.down"] = Q.pack_fp8(d_e.to(device))
+                if cfg.shared_expert_intermediate_size:
+                    w[p + "shared.gu"] = Q.pack_fp8_swiglu(sd[moe + "shared_expert.gate_proj.weight"].to(device),
+                                                           sd[moe + "shared_expert.up_proj.weight"].to(device))
+                    w[p + "shared.down"] = Q.pack_fp8(sd[moe + "shared_expert.down_proj.weight"].to(device))
+                    w[p + "shared.gate"] = sd[moe + "shared_expert_gate.weight"].to(torch.bfloat16).to(device)
+                continue
             gate = shard_rows(sd[s + "mlp.gate_proj.weight"], tp_rank, tp_size).to(device)
             up = shard_rows(sd[s + "mlp.up_proj.weight"], tp_rank, tp_size).to(device)
             w[p + "gu"] = Q.pack_fp8_swiglu(gate, up)
@@ -277,7 +317,7 @@ class LlamaModel:
         """h is bf16 [T, K] or already-quantised MX activations."""
         if isinstance(h, Q.MxAct):
             return Q.gemm_mxfp8(h, w, **kw)
-        if self._use_mx(T):
+        if self._use_mx(T) and h.shape[1] % 128 == 0:
             return Q.gemm_mxfp8(Q.quantize_mx(h, terms=self.act_terms), w, **kw)
         return Q.gemm_w8a16(h, w, **kw)
 
@@ -290,6 +330,11 @@ class LlamaModel:
         return y
 
     fused = None  # antfly_b200.parallel.fused.FusedTp when the peer-memory path is enabled
+
+    @property
+    def graph_safe(self) -> bool:
+        """False when a step's launch sequence depends on the data (expert routing): no CUDA-graph capture."""
+        return self.cfg.num_experts == 0
 
     def _forward_fused(self, b: StepBatch, k_cache, v_cache, attn_scratch) -> torch.Tensor:
         """Tensor-parallel step with the collectives fused into the GEMM and norm kernels (skinny batches)."""
@@ -367,6 +412,31 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    def _moe_mlp(self, h: torch.Tensor, l: int, T: int) -> torch.Tensor:
+        """Sparse mixture-of-experts MLP: soft-max router, top-k experts per token (weights optionally renormalised),
+        each expert a SwiGLU MLP on the block-fp8 GEMMs, outputs combined with the routing weights in fp32; plus the
+        sigmoid-gated shared expert of Qwen2-MoE.  Tokens are gathered per expert, so every expert's weights are
+        read once per step whatever the batch.  Returns fp32 [T, H]."""
+        cfg, w, p = self.cfg, self.w, f"l{l}."
+        logits = Dn.gemm_bf16(h, w[p + "router"], out_dtype=torch.float32).float()
+        probs = torch.softmax(logits, -1)
+        topv, topi = probs.topk(cfg.num_experts_per_tok, -1)
+        if cfg.norm_topk_prob:
+            topv = topv / topv.sum(-1, keepdim=True)
+        out = torch.zeros((T, h.shape[1]), dtype=torch.float32, device=h.device)
+        for e in torch.unique(topi).tolist():
+            rows, slot = (topi == e).nonzero(as_tuple=True)
+            xe = h.index_select(0, rows)
+            act = self._linear(xe, w[p + f"e{e}.gu"], rows.numel(), swiglu=True)
+            ye = self._linear(act, w[p + f"e{e}.down"], rows.numel()).float()
+            out.index_add_(0, rows, ye * topv[rows, slot][:, None])
+        if p + "shared.gu" in w:
+            act = self._linear(h, w[p + "shared.gu"], T, swiglu=True)
+            ys = self._linear(act, w[p + "shared.down"], T).float()
+            gate = torch.sigmoid(Dn.gemm_bf16(h, w[p + "shared.gate"], out_dtype=torch.float32).float())
+            out = out + gate * ys
+        return out
+
     def _forward_general(self, b: StepBatch, k_cache, v_cache, attn_scratch) -> torch.Tensor:
         """Variants the fused decode path does not special-case (Gemma: (1 + gamma) norms, scaled embeddings,
         GeGLU): same kernels, with the gated activation applied between the gate/up and down GEMMs instead of in
@@ -390,6 +460,11 @@ class LlamaModel:
                                     scratch=attn_scratch)
             x = self._linear(ctx.view(T, Hq * D), w[p + "o"], T, residual=x)
             h = Dn.norm(x, w[p + "ln2"], eps=eps, rms=True, gamma_plus_one=gp1)
+            if cfg.num_experts > 0:
+                x = (x.float() + self._moe_mlp(h, l, T)).to(torch.bfloat16)
+                if l + 1 < self.n_layers:
+                    h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
+                continue
             gu = self._linear(h, w[p + "gu"], T).float()  # columns alternate gate_i, up_i
             gate, up = gu[:, 0::2], gu[:, 1::2]
             if cfg.gate_act == "gelu_tanh":
@@ -414,7 +489,7 @@ class LlamaModel:
         """Runs the stack on one step batch; K/V of the step's tokens are written into
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
-        if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu":
+        if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

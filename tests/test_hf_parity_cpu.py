@@ -20,6 +20,13 @@ def _round_linears_to_fp8_grid(model):
             if isinstance(mod, torch.nn.Linear):
                 q, e8 = R.quantize_block_fp8(mod.weight.data)
                 mod.weight.data.copy_(R.dequantize_block_fp8(q, e8))
+        for name, p in model.named_parameters():
+            if p.dim() == 3 and "experts" in name:      # fused expert weights [E, out, in]
+                for e in range(p.shape[0]):
+                    q, e8 = R.quantize_block_fp8(p.data[e])
+                    p.data[e].copy_(R.dequantize_block_fp8(q, e8))
+            elif name.endswith("mlp.gate.weight") or name.endswith("shared_expert_gate.weight"):
+                p.data.copy_(p.data.to(torch.bfloat16).float())   # router weights are kept in bf16
 
 
 def _hf_decoder(kind: str):
@@ -44,6 +51,19 @@ def _hf_decoder(kind: str):
     elif kind == "phi3":
         cfg = transformers.Phi3Config(**{**common, "pad_token_id": 0})
         m = transformers.Phi3ForCausalLM(cfg)
+    elif kind == "mixtral":
+        cfg = transformers.MixtralConfig(**common, num_local_experts=4, num_experts_per_tok=2)
+        m = transformers.MixtralForCausalLM(cfg)
+    elif kind == "qwen2_moe":
+        cfg = transformers.Qwen2MoeConfig(**common, moe_intermediate_size=96, shared_expert_intermediate_size=160,
+                                          num_experts=4, num_experts_per_tok=2, decoder_sparse_step=1,
+                                          mlp_only_layers=[])
+        m = transformers.Qwen2MoeForCausalLM(cfg)
+    elif kind == "qwen3_moe":
+        cfg = transformers.Qwen3MoeConfig(**common, head_dim=64, moe_intermediate_size=96, num_experts=4,
+                                          num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[],
+                                          norm_topk_prob=True)
+        m = transformers.Qwen3MoeForCausalLM(cfg)
     elif kind == "llama_tied":
         common["tie_word_embeddings"] = True
         cfg = transformers.LlamaConfig(**common)
@@ -53,7 +73,8 @@ def _hf_decoder(kind: str):
     return cfg, m.eval().float()
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "phi3"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "phi3", "mixtral",
+                                  "qwen2_moe", "qwen3_moe"])
 def test_decoder_matches_transformers(kind):
     torch.manual_seed(0)
     hf_cfg, hf = _hf_decoder(kind)
