@@ -227,7 +227,8 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         return SamplingParams(max_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k, top_p=req.top_p,
                               min_p=req.min_p, repetition_penalty=req.repetition_penalty,
                               frequency_penalty=req.frequency_penalty, presence_penalty=req.presence_penalty,
-                              stop_token_ids=stops, seed=req.seed, grammar=grammar)
+                              stop_token_ids=stops, seed=req.seed, grammar=grammar,
+                              cache_compaction_ratio=req.cache_compaction_ratio)
 
     async def generate(request: Request):
         req, bad = await parse(request, S.GenerateRequest)

@@ -87,7 +87,8 @@ def cmd_generate(args) -> int:
     if args.no_bos:
         gen.add_bos = False
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
-                        min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed)
+                        min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
+                        cache_compaction_ratio=args.cache_compaction_ratio)
     out = gen.generate(args.prompt, sp, raw_prompt=args.no_chat_template or args.raw_prompt,
                        on_delta=(lambda d: (sys.stdout.write(d), sys.stdout.flush())) if args.stream else None)
     if not args.stream:
@@ -185,6 +186,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--seed", type=int); p.add_argument("--speculative-k", type=int, default=4)
     p.add_argument("--draft-layers", type=int, default=0); p.add_argument("--cache-dtype", default="bf16")
     p.add_argument("--prefill-chunk-size", type=int, default=2048); p.add_argument("--kv-budget-mb", type=int, default=0)
+    p.add_argument("--cache-compaction-ratio", type=float,
+                   help="after prefill keep this fraction of the KV cache (attention-matching compaction)")
     p.add_argument("--no-bos", action="store_true"); p.add_argument("--no-chat-template", action="store_true")
     p.add_argument("--raw-prompt", action="store_true"); p.add_argument("--stream", action="store_true")
     p.add_argument("--print-timing", action="store_true"); p.add_argument("--print-token-ids", action="store_true")

@@ -56,6 +56,7 @@ class Request:
     t_admit: float = 0.0
     t_first: Optional[float] = None
     row: int = -1  # row in the penalty-count table
+    kv_removed: int = 0  # tokens dropped from the physical KV cache by compaction (logical positions keep counting)
 
     @property
     def tokens(self) -> List[int]:
@@ -223,7 +224,7 @@ class LLMEngine:
             ids.extend(toks)
             pos.extend(range(it.kv_before, it.kv_before + n))
             slots.extend(sl.tolist())
-            qs.append(t0); ql.append(n); kvl.append(it.kv_before + n)
+            qs.append(t0); ql.append(n); kvl.append(it.kv_before + n - self.reqs[it.request_id].kv_removed)
             bt = alloc.block_table(it.request_id)
             tables[i, : len(bt)] = bt
             rows.append(t0 + n - 1)
@@ -320,7 +321,7 @@ class LLMEngine:
         slots, lens = self.cache.alloc.append_batch(seqs, ones, self.max_blocks, tab_np)
         st.h_slots.numpy()[:] = slots
         st.h_kvl.numpy()[:] = lens
-        st.h_pos.numpy()[:] = lens - 1
+        st.h_pos.numpy()[:] = lens - 1 + np.array([r.kv_removed for r in reqs], dtype=np.int32)
         st.h_ids.numpy()[:] = [r.out[-1] if r.out else r.prompt[-1] for r in reqs]
         st.dev.copy_(st.host, non_blocking=True)
         self.h2d_bytes += st.h2d_bytes()
@@ -401,9 +402,12 @@ class LLMEngine:
             if self.prefix is not None and self.prefix.evict_one():
                 return 0
             raise
-        if self.prefix is not None:
-            for it, r in zip(items, reqs):
-                if it.mode != "decode" and it.kv_before + it.q_len >= len(r.prompt):
+        for it, r in zip(items, reqs):
+            if it.mode != "decode" and it.kv_before + it.q_len >= len(r.prompt):
+                ratio = r.params.cache_compaction_ratio
+                if ratio is not None and 0.0 < ratio < 1.0:
+                    self.compact_request(it.request_id, ratio)
+                elif self.prefix is not None:
                     self.prefix.insert(it.request_id, r.prompt)
         toks = toks_dev.cpu().tolist() if toks_dev is not None else []
         self.d2h_bytes += 4 * len(toks)
@@ -418,6 +422,42 @@ class LLMEngine:
         dt = time.perf_counter() - t_start
         self.timing["decode_s" if all(it.mode == "decode" for it in items) else "prefill_s"] += dt
         return len(producing)
+
+    # ------------------------------------------------------------------------------------------------
+    def compact_request(self, rid: int, ratio: float, n_ref: int = 64, keep_recent: int = 16) -> int:
+        """Attention-matching compaction of one sequence's KV cache (all layers, every KV head) to about ``ratio``
+        of its tokens; the sequence moves to fresh blocks (its old ones may be shared with cached prefixes) and
+        the freed blocks return to the pool.  Returns the number of tokens removed.  Not combined with
+        speculative decoding."""
+        from .kv_compaction import compact_layer
+
+        if self.draft is not None:
+            raise ValueError("KV compaction cannot be combined with speculative decoding")
+        r = self.reqs[rid]
+        alloc, page = self.cache.alloc, self.page
+        N = alloc.length(rid)
+        if N < 4 * page:
+            return 0
+        table = torch.from_numpy(alloc.block_table(rid).astype(np.int64)).to(self.device)
+        slots = (table[:, None] * page + torch.arange(page, device=self.device)[None]).reshape(-1)[:N]
+        L = self.cache.k.shape[0]
+        Hkv, D = self.cache.k.shape[3], self.cache.k.shape[4]
+        new_k, new_v = [], []
+        for l in range(L):
+            K = self.cache.k[l].view(-1, Hkv, D).index_select(0, slots)
+            V = self.cache.v[l].view(-1, Hkv, D).index_select(0, slots)
+            kh, vh = compact_layer(K, V, ratio, n_ref, keep_recent)
+            new_k.append(kh)
+            new_v.append(vh)
+        M = new_k[0].shape[0]
+        alloc.detach(rid)
+        alloc.attach(rid)
+        dst = torch.from_numpy(alloc.append(rid, M).astype(np.int64)).to(self.device)
+        for l in range(L):
+            self.cache.k[l].view(-1, Hkv, D)[dst] = new_k[l].to(self.cache.k.dtype)
+            self.cache.v[l].view(-1, Hkv, D)[dst] = new_v[l].to(self.cache.v.dtype)
+        r.kv_removed += N - M
+        return N - M
 
     # ------------------------------------------------------------------------------------------------
     def _spec_round(self) -> int:
@@ -558,12 +598,13 @@ def decode_burst(engine: "LLMEngine", n_steps: int):
     st.h_ids.numpy()[:] = [r.out[-1] if r.out else r.prompt[-1] for r in reqs]
     st.h_slots.numpy()[:] = slots[0]
     st.h_pos.numpy()[:] = base
-    st.h_kvl.numpy()[:] = base + 1
+    removed = np.array([r.kv_removed for r in reqs], dtype=np.int32)
+    st.h_kvl.numpy()[:] = base + 1 - removed
     st.dev.copy_(st.host, non_blocking=True)
     steps = np.arange(n_steps, dtype=np.int32)[:, None]
     per_step = np.stack([base[None] + steps, slots, ], 1)  # [n_steps, 2, B]: positions, slots
     per_step_dev = torch.from_numpy(per_step.astype(np.int32)).pin_memory().to(engine.device, non_blocking=True)
-    kvl_dev = torch.from_numpy((base[None] + steps + 1).astype(np.int32)).pin_memory().to(engine.device,
+    kvl_dev = torch.from_numpy((base[None] + steps + 1 - removed[None]).astype(np.int32)).pin_memory().to(engine.device,
                                                                                          non_blocking=True)
     engine.h2d_bytes += st.h2d_bytes() + per_step.nbytes + kvl_dev.numel() * 4
     scratch = engine._scratch_for(B, splits)

@@ -18,6 +18,7 @@ class SamplingParams:
     stop_token_ids: List[int] = field(default_factory=list)
     ignore_eos: bool = False
     seed: Optional[int] = None
+    cache_compaction_ratio: Optional[float] = None  # in (0, 1): compact the KV cache to this fraction after prefill
     grammar: Optional[object] = None  # antfly_b200.runtime.grammar.JsonGrammar: constrains every sampled token
 
     @property
