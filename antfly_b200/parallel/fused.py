@@ -92,6 +92,8 @@ class SymmetricWorkspace:
         torch.cuda.synchronize(device)
         dist.barrier(group)
         self.base_ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        # 0 when the buffer is not bound to an NVLink multicast object (what this package asks for)
+        self.multicast_ptr = int(getattr(self.hdl, "multicast_ptr", 0) or 0)
         assert self.base_ptrs[rank] == self.buf.data_ptr()
 
     def clear_one_shot_slots(self) -> None:
