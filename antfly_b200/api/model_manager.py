@@ -100,6 +100,12 @@ class ModelManager:
 
             model = ClipModel.from_state_dict(ClipConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = ClipEmbedder(model, tok)
+        elif task == "embedder" and cfg_d.get("model_type") in ("qwen2", "qwen3", "llama", "mistral", "gemma", "phi3"):
+            # decoder-based embedding models (Qwen3-Embedding, E5-Mistral, ...): last-token pooling
+            from ..pipelines.embedding import DecoderEmbedder
+
+            model = LlamaModel.from_state_dict(LlamaConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = DecoderEmbedder(model, tok)
         elif task in ("embedder", "reranker"):
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)

@@ -330,6 +330,7 @@ class LlamaModel:
         return y
 
     fused = None  # antfly_b200.parallel.fused.FusedTp when the peer-memory path is enabled
+    return_hidden = False  # True: forward returns the final-norm hidden states of the wanted rows, not logits
 
     @property
     def graph_safe(self) -> bool:
@@ -479,6 +480,8 @@ class LlamaModel:
                 h = Dn.norm(x, nw, eps=eps, rms=True, gamma_plus_one=gp1)
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
         hl = Dn.norm(rows, w["norm"], eps=eps, rms=True, gamma_plus_one=gp1)
+        if self.return_hidden:
+            return hl
         head = w["lm_head"]
         if isinstance(head, Q.Fp8Weight):
             return self._linear(hl, head, rows.shape[0])
@@ -540,6 +543,8 @@ class LlamaModel:
                 x, h = Dn.norm(None, nw, eps=cfg.rms_norm_eps, rms=True, residual=x, partials=parts, want_sum=True,
                                mx_terms=mxt)
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
+        if self.return_hidden:
+            return Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True)
         hl = Dn.norm(rows, w["norm"], eps=cfg.rms_norm_eps, rms=True,
                      mx_terms=self.act_terms if self._use_mx(rows.shape[0]) else 0)
         head = w["lm_head"]

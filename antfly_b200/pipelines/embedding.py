@@ -127,3 +127,80 @@ class SparseEmbedder:
                 nz, vals = nz[keep], vals[keep]
             out.append({"indices": nz.tolist(), "values": vals.tolist()})
         return out
+
+
+class DecoderEmbedder:
+    """Text embeddings from a decoder-only model (Qwen3-Embedding, E5-Mistral and the like): the prompt is run
+    causally through the stack, the final-norm hidden state of the LAST token is the embedding, L2-normalised;
+    ``dimensions`` truncates and re-normalises (Matryoshka).  The reference's resident Qwen3 embedding path does
+    the same (zig/pkg/inference/src/pipelines/embedding.zig:893 ``tryEmbedTextResidentQwen3``).  Prompts are
+    packed into one causal prefill pass over a scratch paged KV cache."""
+
+    def __init__(self, model, tokenizer=None, max_length: int = 8192, append_eos: bool = True,
+                 instruction: Optional[str] = None, page: int = 16):
+        self.model, self.tokenizer, self.max_length = model, tokenizer, max_length
+        self.append_eos, self.instruction, self.page = append_eos, instruction, page
+
+    @property
+    def dim(self) -> int:
+        return self.model.cfg.hidden_size
+
+    def tokenize(self, texts: Sequence[str], task_type: Optional[str] = None) -> List[List[int]]:
+        if self.tokenizer is None:
+            raise RuntimeError("this embedder has no tokenizer")
+        out = []
+        for t in texts:
+            if self.instruction and task_type in (None, "query", "search_query"):
+                t = f"Instruct: {self.instruction}\nQuery:{t}"
+            ids = self.tokenizer.encode(t)[: self.max_length - 1]
+            eos = self.tokenizer.special.eos_id
+            out.append(ids + ([eos] if self.append_eos and eos is not None else []))
+        return out
+
+    def embed_ids(self, seqs: Sequence[Sequence[int]], dimensions: Optional[int] = None,
+                  max_batch_tokens: int = 16384) -> torch.Tensor:
+        from ..models.llama import StepBatch
+
+        m, dev, page = self.model, self.model.device, self.page
+        outs = []
+        i = 0
+        while i < len(seqs):
+            j, tok = i, 0
+            while j < len(seqs) and (j == i or tok + len(seqs[j]) <= max_batch_tokens):
+                tok += len(seqs[j])
+                j += 1
+            group = seqs[i:j]
+            lens = [len(s) for s in group]
+            blocks = [(n + page - 1) // page for n in lens]
+            nblk, maxb = sum(blocks), max(blocks)
+            kc = torch.zeros((m.n_layers, nblk, page, m.Hkv, m.D), dtype=torch.bfloat16, device=dev)
+            vc = torch.zeros_like(kc)
+            tables = torch.zeros((len(group), maxb), dtype=torch.int32)
+            slots, pos, b0 = [], [], 0
+            for r, (n, nb) in enumerate(zip(lens, blocks)):
+                tables[r, :nb] = torch.arange(b0, b0 + nb, dtype=torch.int32)
+                slots.extend(range(b0 * page, b0 * page + n))
+                pos.extend(range(n))
+                b0 += nb
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+            ql = i32(lens)
+            qs = (torch.cumsum(ql, 0) - ql).to(torch.int32)
+            batch = StepBatch(i32([t for s in group for t in s]), i32(pos), i32(slots), qs, ql, ql.clone(),
+                              tables.to(dev), (qs + ql - 1).to(torch.int32), max(lens), 1)
+            prev, m.return_hidden = m.return_hidden, True
+            try:
+                h = m.forward(batch, kc, vc).float()
+            finally:
+                m.return_hidden = prev
+            outs.append(h)
+            i = j
+        e = torch.cat(outs, 0) if outs else torch.zeros((0, self.dim))
+        if dimensions:
+            if dimensions > e.shape[1]:
+                raise ValueError(f"dimensions {dimensions} exceeds the model's {e.shape[1]}")
+            e = e[:, :dimensions]
+        return torch.nn.functional.normalize(e, dim=-1).cpu()
+
+    def embed(self, texts: Sequence[str], task_type: Optional[str] = None, dimensions: Optional[int] = None):
+        seqs = self.tokenize(texts, task_type)
+        return self.embed_ids(seqs, dimensions), sum(len(s) for s in seqs)

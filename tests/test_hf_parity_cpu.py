@@ -293,3 +293,27 @@ def test_clip_text_and_vision_towers_match_transformers():
     # normalised embeddings give the usual similarity matrix
     sim = model.embed_text(seqs) @ model.embed_images(pixels).T
     assert sim.shape == (3, 2) and float(sim.abs().max()) <= 1.0 + 1e-5
+
+
+def test_decoder_embedder_last_token_pooling_matches_transformers():
+    """Qwen3-Embedding style: last-token hidden state after the final norm, L2-normalised."""
+    from antfly_b200.pipelines.embedding import DecoderEmbedder
+
+    torch.manual_seed(5)
+    hf_cfg, hf = _hf_decoder("qwen3")
+    _round_linears_to_fp8_grid(hf)
+    model = LlamaModel.from_state_dict(LlamaConfig.from_hf(hf_cfg.to_dict()),
+                                       {k: v.detach().clone() for k, v in hf.state_dict().items()}, device="cpu")
+    seqs = [torch.randint(0, 320, (n,)).tolist() for n in (7, 21, 12)]
+    emb = DecoderEmbedder(model)
+    got = emb.embed_ids(seqs)
+    want = []
+    for s in seqs:
+        with torch.no_grad():
+            h = hf.model(torch.tensor([s])).last_hidden_state[0, -1]
+        want.append(torch.nn.functional.normalize(h.float(), dim=-1))
+    want = torch.stack(want)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.995, cos
+    assert emb.embed_ids(seqs, dimensions=32).shape == (3, 32)
+    assert model.return_hidden is False
