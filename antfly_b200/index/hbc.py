@@ -35,6 +35,9 @@ class HBCConfig:
     kmeans_max_iter: int = 16
     use_quantization: bool = True
     quantizer_seed: int = 42
+    # kmeans: cluster every level (farthest-first seeding); hilbert_seeded: k-means seeded with the means of
+    # Hilbert-curve runs (the reference's default bulk build); hilbert: cut the curve order into runs, no clustering
+    bulk_build: str = "kmeans"
 
 
 @dataclass
@@ -82,6 +85,24 @@ class HBCIndex:
         if k == 1:
             cents = x.mean(0, keepdim=True)
             members = [torch.arange(n)]
+        elif cfg.bulk_build in ("hilbert", "hilbert_seeded"):
+            # Sort along the Hilbert curve and cut into leaf-sized runs (the reference's hilbert bulk builds,
+            # zig/HBC.md).  "hilbert" keeps the runs as leaves: no clustering pass over the data, but a space-filling
+            # curve preserves little locality in many dimensions, so leaves are loose.  "hilbert_seeded" uses the
+            # runs' means as the starting centroids of the usual Lloyd iterations.
+            from .hilbert import hilbert_order
+
+            order = hilbert_order(x).to(x.device)
+            members = [order[i:i + cfg.leaf_size] for i in range(0, n, cfg.leaf_size)]
+            cents = torch.stack([x[m].mean(0) for m in members])
+            if cfg.metric == "cosine":
+                cents = torch.nn.functional.normalize(cents, dim=-1)
+            if cfg.bulk_build == "hilbert_seeded":
+                km = kmeans(x.to(torch.bfloat16), len(members), metric=cfg.metric, max_iter=cfg.kmeans_max_iter,
+                            init=cents)
+                cents = km.centroids.float().cpu() if not x.is_cuda else km.centroids.float()
+                a = km.assignments.long()
+                members = [torch.nonzero(a == c).flatten() for c in range(cents.shape[0])]
         else:
             km = kmeans(x.to(torch.bfloat16), k, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
             cents = km.centroids.float().cpu() if not x.is_cuda else km.centroids.float()
@@ -103,6 +124,13 @@ class HBCIndex:
             if kk == 1:
                 groups = [list(range(len(level_nodes)))]
                 pc = cm.mean(0, keepdim=True)
+            elif cfg.bulk_build == "hilbert":
+                # leaves were created in curve order, so consecutive nodes are neighbours: group them in runs
+                bf = cfg.branching_factor
+                groups = [list(range(i, min(i + bf, len(level_nodes)))) for i in range(0, len(level_nodes), bf)]
+                pc = torch.stack([cm[g].mean(0) for g in groups])
+                if cfg.metric == "cosine":
+                    pc = torch.nn.functional.normalize(pc, dim=-1)
             else:
                 km = kmeans(cm.to(torch.bfloat16), kk, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
                 a = km.assignments.long()

@@ -115,3 +115,74 @@ def test_flat_index_cpu_path_is_exact():
     res = idx.search(q.to(torch.bfloat16).float(), 10)
     truth = exact_search_fp32(q.to(torch.bfloat16).float(), x.to(torch.bfloat16).float(), 10, "l2_squared")
     assert recall_at_k(res.ids, truth.ids, 10) == 1.0
+
+
+def test_hilbert_keys_match_an_independent_restatement_and_order_is_local():
+    import numpy as np
+
+    from antfly_b200.index.hilbert import hilbert_keys, hilbert_order, random_orthogonal
+
+    def py_key(vec):
+        # Skilling's transform written independently (lists of Python ints), then MSB-first bit interleave
+        x = [int(np.float32(v).view(np.uint32)) for v in vec]
+        n, m = len(x), 1 << 31
+        q = m
+        while q > 1:
+            p = q - 1
+            for i in range(n):
+                if x[i] & q:
+                    x[0] ^= p
+                else:
+                    t = (x[0] ^ x[i]) & p
+                    x[0] ^= t
+                    x[i] ^= t
+            q >>= 1
+        for i in range(1, n):
+            x[i] ^= x[i - 1]
+        t, q = 0, m
+        while q > 1:
+            if x[n - 1] & q:
+                t ^= q - 1
+            q >>= 1
+        x = [v ^ t for v in x]
+        bits = [(x[i] >> b) & 1 for b in range(31, -1, -1) for i in range(n)]
+        return bytes(int("".join(map(str, bits[k:k + 8])), 2) for k in range(0, len(bits), 8))
+
+    g = torch.Generator().manual_seed(0)
+    v = torch.rand(40, 3, generator=g)
+    keys = hilbert_keys(v)
+    assert keys.shape == (40, 12)
+    for r in range(40):
+        assert bytes(keys[r]) == py_key(v[r].tolist())
+    # locality: neighbours along the curve are much closer than neighbours in random order (positive coordinates,
+    # where float bit patterns are monotonic in value)
+    pts = torch.rand(4000, 2, generator=g) + 1.0
+    order = hilbert_order(pts)
+    assert sorted(order.tolist()) == list(range(4000))
+    along = (pts[order][1:] - pts[order][:-1]).norm(dim=-1).mean()
+    rand = (pts[1:] - pts[:-1]).norm(dim=-1).mean()
+    assert float(along) < 0.1 * float(rand)
+    q = random_orthogonal(48, seed=7)
+    torch.testing.assert_close(q @ q.T, torch.eye(48), atol=1e-5, rtol=1e-5)
+    assert torch.equal(q, random_orthogonal(48, seed=7)) and not torch.equal(q, random_orthogonal(48, seed=8))
+
+
+def test_hbc_hilbert_bulk_builds():
+    g = torch.Generator().manual_seed(2)
+    centers = torch.rand(20, 16, generator=g) * 4 + 1.0
+    x = centers[torch.randint(0, 20, (3000,), generator=g)] + 0.1 * torch.randn(3000, 16, generator=g)
+    q = centers[torch.randint(0, 20, (40,), generator=g)] + 0.1 * torch.randn(40, 16, generator=g)
+    truth = exact_search_fp32(q, x, 10, "l2_squared")
+
+    def recall(mode, width):
+        idx = HBCIndex.bulk_build(x, HBCConfig(16, "l2_squared", branching_factor=8, leaf_size=60, search_width=width,
+                                               bulk_build=mode))
+        assert idx.stats()["vectors"] == 3000 and idx.stats()["levels"] >= 2
+        found = torch.tensor([idx.search(q[i], 10)[0] + [-1] * 10 for i in range(40)])[:, :10]
+        return recall_at_k(found, truth.ids, 10), idx
+
+    r_seeded, idx = recall("hilbert_seeded", 16)
+    assert r_seeded > 0.8, r_seeded                       # clustered leaves: as good as the k-means build
+    r_pure, idx_pure = recall("hilbert", 16)
+    assert idx_pure.stats()["leaves"] == 50 and r_pure > 0.3   # loose leaves: usable, clearly worse
+    assert r_seeded > r_pure
