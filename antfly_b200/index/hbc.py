@@ -204,6 +204,123 @@ class HBCIndex:
         order = torch.argsort(exact)[:k]
         return [int(self.ids[short[i]]) for i in order.tolist()], exact[order].tolist()
 
+    # -- online maintenance -------------------------------------------------------------------------------
+    def _requantize(self, nd: Node) -> None:
+        if not self.cfg.use_quantization:
+            return
+        pts = self.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+            [self.nodes[c].centroid for c in nd.children])
+        nd.quant = self.quantizer.quantize(nd.centroid, pts)
+
+    def _recentre(self, nd: Node) -> None:
+        pts = self.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+            [self.nodes[c].centroid for c in nd.children])
+        c = pts.mean(0)
+        nd.centroid = torch.nn.functional.normalize(c, dim=-1) if self.cfg.metric == "cosine" else c
+
+    def _new_node(self, is_leaf: bool, level: int, parent: int, children: List[int]) -> Node:
+        nid = max(self.nodes) + 1
+        nd = Node(nid, is_leaf, level, parent, torch.zeros(self.cfg.dims), children)
+        self.nodes[nid] = nd
+        return nd
+
+    def _split(self, nd: Node) -> None:
+        """Split an over-full node in two with 2-means over its members (SPFresh-style posting split); the new
+        sibling joins the parent, which may split in turn; a split root grows the tree by one level."""
+        pts = self.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+            [self.nodes[c].centroid for c in nd.children])
+        km = kmeans(pts.to(torch.bfloat16), 2, metric=self.cfg.metric, max_iter=self.cfg.kmeans_max_iter)
+        a = km.assignments.long().tolist()
+        left = [c for c, g in zip(nd.children, a) if g == 0]
+        right = [c for c, g in zip(nd.children, a) if g == 1]
+        if not left or not right:  # degenerate (identical points): cut in the middle
+            half = len(nd.children) // 2
+            left, right = nd.children[:half], nd.children[half:]
+        sib = self._new_node(nd.is_leaf, nd.level, nd.parent, right)
+        nd.children = left
+        for node in (nd, sib):
+            if node.is_leaf:
+                for v in node.children:
+                    self.leaf_of[v] = node.id
+            else:
+                for c in node.children:
+                    self.nodes[c].parent = node.id
+            self._recentre(node)
+            self._requantize(node)
+        limit = 2 * (self.cfg.leaf_size if nd.is_leaf else self.cfg.branching_factor)
+        self._attach_sibling(nd, sib)
+        for node in (nd, sib):  # a large batch can leave a half that is still over-full
+            if len(node.children) > limit:
+                self._split(node)
+
+    def _attach_sibling(self, nd: Node, sib: Node) -> None:
+        if nd.id == self.root:
+            root = self._new_node(False, nd.level + 1, 0, [nd.id, sib.id])
+            nd.parent = sib.parent = root.id
+            self.root = root.id
+            self._recentre(root)
+            self._requantize(root)
+            return
+        parent = self.nodes[nd.parent]
+        parent.children.append(sib.id)
+        self._recentre(parent)
+        self._requantize(parent)
+        if len(parent.children) > 2 * self.cfg.branching_factor:
+            self._split(parent)
+
+    def insert(self, vectors: torch.Tensor, ids: Optional[torch.Tensor] = None) -> None:
+        """Online batch insert: every vector descends greedily to its nearest leaf (exact centroid distances),
+        leaves that grow past twice the leaf size are split, splits propagate upwards.  Mirrors the reference's
+        online insert path (zig/lib/vectorindex/src/hbc_index.zig, spfresh_index.zig)."""
+        x = vectors.float().to(self.vectors.device)
+        if self.cfg.metric == "cosine":
+            x = torch.nn.functional.normalize(x, dim=-1)
+        base = self.vectors.shape[0]
+        self.vectors = torch.cat([self.vectors, x], 0)
+        new_ids = ids if ids is not None else torch.arange(int(self.ids.max()) + 1, int(self.ids.max()) + 1 + x.shape[0])
+        self.ids = torch.cat([self.ids, new_ids.to(self.ids.dtype)])
+        touched = set()
+        for i in range(x.shape[0]):
+            nd = self.nodes[self.root]
+            while not nd.is_leaf:
+                cents = torch.stack([self.nodes[c].centroid for c in nd.children])
+                nd = self.nodes[nd.children[int(torch.argmin(R.distances(x[i][None], cents, self.cfg.metric)[0]))]]
+            nd.children.append(base + i)
+            self.leaf_of[base + i] = nd.id
+            touched.add(nd.id)
+        for nid in sorted(touched):
+            nd = self.nodes[nid]
+            self._recentre(nd)
+            if len(nd.children) > 2 * self.cfg.leaf_size:
+                self._split(nd)
+            else:
+                self._requantize(nd)
+                p = nd.parent
+                if p in self.nodes:
+                    self._requantize(self.nodes[p])  # the parent's payload encodes its children's centroids
+
+    def delete(self, vector_ids: List[int]) -> int:
+        """Remove vectors by external id from their leaves (leaves may become small; they are not merged).
+        Returns how many were found."""
+        pos = {int(v): i for i, v in enumerate(self.ids.tolist())}
+        n, touched = 0, set()
+        for vid in vector_ids:
+            i = pos.get(int(vid))
+            if i is None or i not in self.leaf_of:
+                continue
+            leaf = self.nodes[self.leaf_of.pop(i)]
+            leaf.children.remove(i)
+            touched.add(leaf.id)
+            n += 1
+        for nid in touched:
+            nd = self.nodes[nid]
+            if nd.children:
+                self._recentre(nd)
+                self._requantize(nd)
+            else:
+                nd.quant = None
+        return n
+
     def stats(self) -> dict:
         leaves = sum(1 for n in self.nodes.values() if n.is_leaf)
         return {"nodes": len(self.nodes), "leaves": leaves, "levels": self.nodes[self.root].level + 1,

@@ -186,3 +186,35 @@ def test_hbc_hilbert_bulk_builds():
     r_pure, idx_pure = recall("hilbert", 16)
     assert idx_pure.stats()["leaves"] == 50 and r_pure > 0.3   # loose leaves: usable, clearly worse
     assert r_seeded > r_pure
+
+
+def test_hbc_online_insert_split_and_delete():
+    g = torch.Generator().manual_seed(3)
+    centers = torch.randn(12, 24, generator=g)
+    def draw(n):
+        return centers[torch.randint(0, 12, (n,), generator=g)] + 0.25 * torch.randn(n, 24, generator=g)
+    x0, x1 = draw(600), draw(2400)
+    cfg = HBCConfig(24, "l2_squared", branching_factor=6, leaf_size=40, search_width=24)
+    idx = HBCIndex.bulk_build(x0, cfg)
+    before = idx.stats()
+    for lo in range(0, 2400, 800):                      # three online batches
+        idx.insert(x1[lo:lo + 800])
+    st = idx.stats()
+    assert st["vectors"] == 3000 and st["leaves"] > before["leaves"] and st["levels"] >= before["levels"]
+    assert max(len(n.children) for n in idx.nodes.values() if n.is_leaf) <= 2 * cfg.leaf_size
+    assert max(len(n.children) for n in idx.nodes.values() if not n.is_leaf) <= 2 * cfg.branching_factor
+    # every vector sits in exactly one leaf and parents / children agree
+    seen = sorted(v for n in idx.nodes.values() if n.is_leaf for v in n.children)
+    assert seen == list(range(3000))
+    for n in idx.nodes.values():
+        if not n.is_leaf:
+            assert all(idx.nodes[c].parent == n.id for c in n.children)
+    allx = torch.cat([x0, x1])
+    q = draw(40)
+    truth = exact_search_fp32(q, allx, 10, "l2_squared")
+    found = torch.tensor([idx.search(q[i], 10)[0] + [-1] * 10 for i in range(40)])[:, :10]
+    assert recall_at_k(found, truth.ids, 10) > 0.8
+    # deletion: the deleted ids never come back
+    gone = truth.ids[0, :5].tolist()
+    assert idx.delete(gone) == 5 and idx.delete(gone) == 0
+    assert not set(idx.search(q[0], 10)[0]) & set(gone)
