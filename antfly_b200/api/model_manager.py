@@ -106,6 +106,11 @@ class ModelManager:
 
             model = LlamaModel.from_state_dict(LlamaConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = DecoderEmbedder(model, tok)
+        elif task in ("embedder", "reranker") and cfg_d.get("model_type") == "modernbert":
+            from ..models.modernbert import ModernBertConfig, ModernBertModel
+
+            model = ModernBertModel.from_state_dict(ModernBertConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         elif task in ("embedder", "reranker"):
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)

@@ -18,15 +18,16 @@ _c_float = ctypes.c_float
 
 
 def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, scale: Optional[float] = None,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
     """q [T, Hq, D], k/v [T, Hkv, D] (may be strided views of one fused QKV buffer); sequences are the packed
-    row ranges starts[b] .. starts[b]+lens[b]."""
+    row ranges starts[b] .. starts[b]+lens[b].  ``window`` > 0: keys with key > query - window, and for
+    bidirectional attention also key < query + window."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
         cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
-        return R.varlen_attention(q, k, v, cu, scale, causal).to(torch.bfloat16)
+        return R.varlen_attention(q, k, v, cu, scale, causal, window).to(torch.bfloat16)
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert k.stride(0) == v.stride(0)
     if out is None:
@@ -36,7 +37,7 @@ def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, 
         N.ptr(q), _c_long(q.stride(0)), N.ptr(k), N.ptr(v), _c_long(k.stride(0)), None, None, None, _c_int(0),
         _c_int(16), N.ptr(starts), N.ptr(lens), N.ptr(lens), N.ptr(out), _c_long(out.stride(0)), None, None,
         _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_len), _c_int(1 if causal else 0),
-        _c_int(0), _c_float(scale), _c_int(0), _c_int(0), _c_int(1), N.stream_ptr(),
+        _c_int(window), _c_float(scale), _c_int(0), _c_int(0), _c_int(1), N.stream_ptr(),
     )
     N.check(rc, "afb_attention")
     N.count_launch()
@@ -163,15 +164,17 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
 
 def rope_(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: Optional[int] = None,
           half_split: bool = True, freq_scale: float = 1.0) -> torch.Tensor:
-    """In-place RoPE on x [T, heads, D] bf16."""
+    """In-place RoPE on x [T, heads, D] bf16; x may be a view whose token rows are further apart than heads * D
+    (the Q and K heads inside a fused QKV buffer)."""
     T, Hh, D = x.shape
     rd = rope_dim or D
     if not x.is_cuda:
         x.copy_(R.rope(x, positions, theta, rd, half_split, freq_scale).to(x.dtype))
         return x
-    rc = N.cuda().afb_rope_inplace(N.ptr(x), N.ptr(positions), _c_int(T), _c_int(Hh), _c_int(D), _c_int(rd),
-                                   _c_int(1 if half_split else 0), _c_float(theta), _c_float(freq_scale),
-                                   N.stream_ptr())
+    assert x.stride(2) == 1 and x.stride(1) == D
+    rc = N.cuda().afb_rope_inplace_strided(N.ptr(x), N.ptr(positions), _c_int(T), _c_int(Hh), _c_int(D), _c_int(rd),
+                                           _c_int(1 if half_split else 0), _c_float(theta), _c_float(freq_scale),
+                                           _c_long(x.stride(0)), N.stream_ptr())
     N.check(rc, "afb_rope_inplace")
     N.count_launch()
     return x

@@ -147,8 +147,9 @@ def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: Optio
 # ----------------------------------------------------------------------------------------------------------
 # Attention
 # ----------------------------------------------------------------------------------------------------------
-def varlen_attention(q, k, v, cu_seqlens, scale=None, causal=False):
-    """Packed bidirectional (or causal) attention.  q: [T, Hq, D], k/v: [T, Hkv, D]."""
+def varlen_attention(q, k, v, cu_seqlens, scale=None, causal=False, window=0):
+    """Packed bidirectional (or causal) attention.  q: [T, Hq, D], k/v: [T, Hkv, D].  ``window`` > 0 keeps keys
+    with key > query - window, and without the causal mask also key < query + window."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     g = Hq // Hkv
@@ -166,6 +167,11 @@ def varlen_attention(q, k, v, cu_seqlens, scale=None, causal=False):
         if causal:
             L = e - s
             m = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            sc = sc.masked_fill(~m, float("-inf"))
+        if window > 0:
+            i = torch.arange(e - s, device=q.device)
+            d = i[None, :] - i[:, None]  # key - query
+            m = (d > -window) & ((d < window) if not causal else torch.ones_like(d, dtype=torch.bool))
             sc = sc.masked_fill(~m, float("-inf"))
         out[s:e] = (sc.softmax(-1) @ vv).transpose(0, 1)
     return out

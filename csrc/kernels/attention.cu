@@ -9,7 +9,8 @@
 // Mask semantics follow the reference's gqaPagedAttentionDirect
 // (zig/pkg/inference/src/ops/native_compute.zig:35093-35173): the query rows of a sequence are its LAST q_len
 // positions; a query at absolute position p sees keys at positions <= p (when causal) and > p - window (when
-// a sliding window is set).  Replaces the reference's thread-per-output encoder attention
+// a sliding window is set); without the causal mask a window is two-sided, |key - p| < window (the local layers of
+// ModernBERT-style encoders).  Replaces the reference's thread-per-output encoder attention
 // (zig/pkg/inference/src/ops/cuda/artifacts/inference_cuda_kernels.cu:702-857), which has no paged or GQA
 // path on CUDA at all.
 //
@@ -183,6 +184,9 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
   if (p.causal) {
     const int last_row = min(rows_total, tile_row0 + (SPLIT_KEYS ? 16 : 64)) - 1;
     kv_hi = min(kv_len, pos_off + last_row / G + 1);
+  } else if (p.window > 0) {  // bidirectional local attention: |key - qpos| < window
+    const int last_row = min(rows_total, tile_row0 + (SPLIT_KEYS ? 16 : 64)) - 1;
+    kv_hi = min(kv_len, pos_off + last_row / G + p.window);
   }
   int kv_lo = 0;
   if (p.window > 0) kv_lo = max(0, pos_off + tile_row0 / G - p.window + 1);
@@ -251,7 +255,8 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
     const int min_qpos = pos_off + row_lo / G;
     const int max_qpos = pos_off + (min(rows_total, row_lo + 16) - 1) / G;
     const bool full_tile = (k0 + kTileKeys <= kv_len) && (!p.causal || k0 + kTileKeys - 1 <= min_qpos) &&
-                           (p.window <= 0 || k0 > max_qpos - p.window);
+                           (p.window <= 0 || (k0 > max_qpos - p.window &&
+                                              (p.causal || k0 + kTileKeys - 1 < min_qpos + p.window)));
     float mx[2] = {-INFINITY, -INFINITY};
     if (!full_tile) {
 #pragma unroll
@@ -263,7 +268,7 @@ __global__ void __launch_bounds__(128) flash_attn_kernel(AttnParams p) {
           const int qpos = pos_off + r_pos[h];
           bool ok = r_ok[h] && key < kv_len;
           if (p.causal) ok = ok && key <= qpos;
-          if (p.window > 0) ok = ok && key > qpos - p.window;
+          if (p.window > 0) ok = ok && key > qpos - p.window && (p.causal || key < qpos + p.window);
           if (!ok) s[nb][e] = -INFINITY;
         }
       }

@@ -135,16 +135,17 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   }
 }
 
-// Standalone RoPE on a [T, heads, D] bf16 tensor, in place (encoders with rotary positions, tests).
+// Standalone RoPE on a [T, heads, D] bf16 tensor, in place (encoders with rotary positions, tests).  Token rows are
+// row_stride elements apart, so the Q and K heads of a fused QKV buffer can be rotated where they lie.
 __global__ void rope_inplace_kernel(__nv_bfloat16* x, const int* positions, int heads, int D, int rope_dim,
-                                    int half_split, float log2_theta, float freq_scale) {
+                                    int half_split, float log2_theta, float freq_scale, long row_stride) {
   const int t = blockIdx.x;
   const float pos = static_cast<float>(positions[t]);
   const int rh = rope_dim / 2;
   for (int idx = threadIdx.x; idx < heads * rh; idx += blockDim.x) {
     const int h = idx / rh, j = idx % rh;
     const int i0 = half_split ? j : 2 * j, i1 = half_split ? j + rh : 2 * j + 1;
-    __nv_bfloat16* row = x + (static_cast<size_t>(t) * heads + h) * D;
+    __nv_bfloat16* row = x + static_cast<size_t>(t) * row_stride + static_cast<size_t>(h) * D;
     const float a = __bfloat162float(row[i0]), b = __bfloat162float(row[i1]);
     const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(rope_dim) * log2_theta);
     float sn, cs;
@@ -202,14 +203,24 @@ int afb_rope_kv_write(const void* qkv, const float* partials, int num_partials, 
   return 0;
 }
 
-int afb_rope_inplace(void* x, const int* positions, int T, int heads, int D, int rope_dim, int half_split, float theta,
-                     float freq_scale, cudaStream_t stream) {
+int afb_rope_inplace_strided(void* x, const int* positions, int T, int heads, int D, int rope_dim, int half_split,
+                             float theta, float freq_scale, long row_stride, cudaStream_t stream) {
   using namespace afb;
   if (T <= 0) return 0;
+  if (row_stride < static_cast<long>(heads) * D || rope_dim > D || rope_dim % 2) {
+    set_last_error("afb_rope_inplace: row stride shorter than heads * D, or bad rope_dim");
+    return -1;
+  }
   rope_inplace_kernel<<<T, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(x), positions, heads, D, rope_dim,
-                                             half_split, log2f(theta), freq_scale);
+                                             half_split, log2f(theta), freq_scale, row_stride);
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+int afb_rope_inplace(void* x, const int* positions, int T, int heads, int D, int rope_dim, int half_split, float theta,
+                     float freq_scale, cudaStream_t stream) {
+  return afb_rope_inplace_strided(x, positions, T, heads, D, rope_dim, half_split, theta, freq_scale,
+                                  static_cast<long>(heads) * D, stream);
 }
 
 int afb_kv_copy_blocks(void* k_cache, void* v_cache, const int* src, const int* dst, int n_pairs, long block_bytes,

@@ -32,6 +32,30 @@ def test_varlen_attention(D, Hq, Hkv, causal):
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("window", [9, 65, 300])
+def test_varlen_attention_two_sided_window(window):
+    """Bidirectional local attention (|key - query| < window), fused-QKV views with RoPE applied in place on the
+    strided Q / K heads: the local layers of ModernBERT-style encoders."""
+    from antfly_b200.ops import attention as A
+
+    D, Hh = 64, 6
+    lens = torch.tensor([1, 17, 64, 130, 257, 512, 33], dtype=torch.int32)
+    starts = (torch.cumsum(lens, 0) - lens).int()
+    T = int(lens.sum())
+    qkv = _rand(T, 3 * Hh * D, seed=5)
+    pos = torch.cat([torch.arange(int(n), dtype=torch.int32) for n in lens]).cuda()
+    ref_qk = R.rope(qkv[:, : 2 * Hh * D].reshape(T, 2 * Hh, D).cpu(), pos.cpu(), 10000.0)
+    A.rope_(qkv[:, : 2 * Hh * D].view(T, 2 * Hh, D), pos, 10000.0)
+    torch.testing.assert_close(qkv[:, : 2 * Hh * D].float().cpu().view(T, 2 * Hh, D), ref_qk, atol=3e-2, rtol=2e-2)
+    q = qkv[:, : Hh * D].view(T, Hh, D)
+    k = qkv[:, Hh * D: 2 * Hh * D].view(T, Hh, D)
+    v = qkv[:, 2 * Hh * D:].view(T, Hh, D)
+    out = A.varlen_attention(q, k, v, starts.cuda(), lens.cuda(), int(lens.max()), causal=False, window=window)
+    cu = torch.cat([starts, torch.tensor([T], dtype=torch.int32)])
+    ref = R.varlen_attention(q, k, v, cu, causal=False, window=window)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+
+
 def _build_paged(B, kv_lens, Hkv, D, page, seed):
     nblk_per = [(l + page - 1) // page for l in kv_lens]
     total = sum(nblk_per) + 3

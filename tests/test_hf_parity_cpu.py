@@ -317,3 +317,47 @@ def test_decoder_embedder_last_token_pooling_matches_transformers():
     assert float(cos.min()) > 0.995, cos
     assert emb.embed_ids(seqs, dimensions=32).shape == (3, 32)
     assert model.return_hidden is False
+
+
+@pytest.mark.parametrize("head", ["embed", "sequence", "token"])
+def test_modernbert_matches_transformers(head):
+    """Alternating global / local (two-sided window) attention with two rotary bases, pre-norm blocks, gated-GELU
+    MLP, prediction head; sequences longer than the local window so the window mask matters."""
+    from antfly_b200.models.modernbert import ModernBertConfig, ModernBertModel
+
+    torch.manual_seed(2)
+    hf_cfg = transformers.ModernBertConfig(vocab_size=400, hidden_size=64, num_hidden_layers=4,
+                                           num_attention_heads=4, intermediate_size=96,
+                                           max_position_embeddings=128, local_attention=16,
+                                           global_attn_every_n_layers=3, num_labels=3, pad_token_id=0,
+                                           bos_token_id=1, eos_token_id=2, cls_token_id=1, sep_token_id=2,
+                                           attention_dropout=0.0, mlp_dropout=0.0, embedding_dropout=0.0,
+                                           classifier_dropout=0.0, classifier_pooling="mean",
+                                           attn_implementation="eager")
+    cls = {"embed": transformers.ModernBertModel, "sequence": transformers.ModernBertForSequenceClassification,
+           "token": transformers.ModernBertForTokenClassification}[head]
+    hf = cls(hf_cfg).eval()
+    cfg = ModernBertConfig.from_hf(hf_cfg.to_dict())
+    assert [cfg.is_global(l) for l in range(4)] == [True, False, False, True]
+    model = ModernBertModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    seqs = [[1] + torch.randint(3, 400, (n,)).tolist() + [2] for n in (5, 40, 61)]
+    batch = pack_sequences(seqs)
+    L = max(len(s) for s in seqs)
+    ids = torch.zeros((len(seqs), L), dtype=torch.long)
+    mask = torch.zeros_like(ids)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.tensor(s)
+        mask[i, : len(s)] = 1
+    with torch.no_grad():
+        out = hf(input_ids=ids, attention_mask=mask)
+    if head == "sequence":
+        torch.testing.assert_close(model.classify(batch).float(), out.logits.float(), atol=3e-2, rtol=3e-2)
+    elif head == "token":
+        want = torch.cat([out.logits[i, : len(s)] for i, s in enumerate(seqs)])
+        torch.testing.assert_close(model.token_logits(batch).float(), want.float(), atol=3e-2, rtol=3e-2)
+    else:
+        hidden = out.last_hidden_state
+        want = torch.nn.functional.normalize((hidden * mask[..., None]).sum(1) / mask.sum(1, keepdim=True), dim=-1)
+        got = model.embed(batch, pooling="mean", normalize=True).float()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        assert float(cos.min()) > 0.999, cos
