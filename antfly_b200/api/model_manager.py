@@ -111,6 +111,11 @@ class ModelManager:
 
             model = ModernBertModel.from_state_dict(ModernBertConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
+        elif task in ("embedder", "reranker") and cfg_d.get("model_type") == "deberta-v2":
+            from ..models.deberta import DebertaConfig, DebertaModel
+
+            model = DebertaModel.from_state_dict(DebertaConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         elif task in ("embedder", "reranker"):
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)

@@ -361,3 +361,54 @@ def test_modernbert_matches_transformers(head):
         got = model.embed(batch, pooling="mean", normalize=True).float()
         cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
         assert float(cos.min()) > 0.999, cos
+
+
+@pytest.mark.parametrize("variant", ["v3_embed", "v3_sequence", "v2_token"])
+def test_deberta_matches_transformers(variant):
+    """Disentangled attention (content-to-position and position-to-content terms over log-bucketed relative
+    distances), shared or separate position projections, with / without absolute positions and token types."""
+    from antfly_b200.models.deberta import DebertaConfig, DebertaModel
+
+    torch.manual_seed(3)
+    v3 = variant.startswith("v3")
+    hf_cfg = transformers.DebertaV2Config(
+        vocab_size=400, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+        max_position_embeddings=64, type_vocab_size=0 if v3 else 2, relative_attention=True,
+        position_buckets=16 if v3 else -1, max_relative_positions=-1 if v3 else 24, pos_att_type=["p2c", "c2p"],
+        share_att_key=v3, norm_rel_ebd="layer_norm" if v3 else "none", position_biased_input=not v3,
+        hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, pooler_dropout=0.0, num_labels=3,
+        pooler_hidden_size=64, layer_norm_eps=1e-7)
+    cls = {"v3_embed": transformers.DebertaV2Model, "v3_sequence": transformers.DebertaV2ForSequenceClassification,
+           "v2_token": transformers.DebertaV2ForTokenClassification}[variant]
+    hf = cls(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+    cfg = DebertaConfig.from_hf(hf_cfg.to_dict())
+    model = DebertaModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    seqs = [[1] + torch.randint(3, 400, (n,)).tolist() + [2] for n in (5, 28, 45)]
+    types = None if v3 else [[0] * (len(s) // 2) + [1] * (len(s) - len(s) // 2) for s in seqs]
+    batch = pack_sequences(seqs, types)
+    L = max(len(s) for s in seqs)
+    ids = torch.zeros((len(seqs), L), dtype=torch.long)
+    mask = torch.zeros_like(ids)
+    tt = torch.zeros_like(ids)
+    for i, s in enumerate(seqs):
+        ids[i, : len(s)] = torch.tensor(s)
+        mask[i, : len(s)] = 1
+        if types:
+            tt[i, : len(s)] = torch.tensor(types[i])
+    with torch.no_grad():
+        out = hf(input_ids=ids, attention_mask=mask, token_type_ids=None if v3 else tt)
+    if variant == "v3_sequence":
+        torch.testing.assert_close(model.classify(batch).float(), out.logits.float(), atol=3e-2, rtol=3e-2)
+    elif variant == "v2_token":
+        want = torch.cat([out.logits[i, : len(s)] for i, s in enumerate(seqs)])
+        torch.testing.assert_close(model.token_logits(batch).float(), want.float(), atol=3e-2, rtol=3e-2)
+    else:
+        hidden = out.last_hidden_state
+        want = torch.nn.functional.normalize((hidden * mask[..., None]).sum(1) / mask.sum(1, keepdim=True), dim=-1)
+        got = model.embed(batch, pooling="mean", normalize=True).float()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        assert float(cos.min()) > 0.999, cos
