@@ -120,6 +120,12 @@ class ModelManager:
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
+        elif cfg_d.get("model_type") in ("t5", "mt5"):
+            from ..models.t5 import T5Config, T5Model
+            from ..pipelines.seq2seq import Seq2SeqGenerator
+
+            model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
+            pipe = Seq2SeqGenerator(model, tok)
         else:
             if cfg_d.get("model_type") in ("gpt2", "gpt_neox", "opt", "gptj", "phi"):
                 from ..models.gpt import GptConfig, GptModel

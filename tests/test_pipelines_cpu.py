@@ -137,3 +137,45 @@ def test_clip_embedder_pipeline(tmp_path):
     assert load_image(arr[:, :, 0]).shape == (50, 70, 3)
     t = emb.embed_token_ids([[298, 5, 6, 299], [298, 7, 299]])
     assert t.shape == (2, 32) and (t @ e.T).shape == (2, 4)
+
+
+def test_seq2seq_pipeline_t5_greedy_and_streaming():
+    """Encoder-decoder text-to-text pipeline: same output as the model's own greedy loop, streamed deltas
+    concatenate to the final text, chat messages are flattened."""
+    import torch
+
+    from antfly_b200.models.t5 import T5Config, T5Model
+    from antfly_b200.pipelines.seq2seq import Seq2SeqGenerator
+    from antfly_b200.runtime.sampling_params import SamplingParams
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    cfg = T5Config(vocab_size=300, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4,
+                   relative_attention_num_buckets=8, relative_attention_max_distance=20, eos_token_id=2)
+    g = torch.Generator().manual_seed(0)
+    sd = {"shared.weight": torch.randn(300, 64, generator=g)}
+    for stack, ff in (("encoder", 1), ("decoder", 2)):
+        for l in range(2):
+            s = f"{stack}.block.{l}.layer."
+            for n in "qkvo":
+                sd[s + f"0.SelfAttention.{n}.weight"] = torch.randn(64, 64, generator=g) * 0.2
+                if stack == "decoder":
+                    sd[s + f"1.EncDecAttention.{n}.weight"] = torch.randn(64, 64, generator=g) * 0.2
+            sd[s + "0.layer_norm.weight"] = torch.ones(64)
+            if stack == "decoder":
+                sd[s + "1.layer_norm.weight"] = torch.ones(64)
+            sd[s + f"{ff}.DenseReluDense.wi.weight"] = torch.randn(128, 64, generator=g) * 0.2
+            sd[s + f"{ff}.DenseReluDense.wo.weight"] = torch.randn(64, 128, generator=g) * 0.2
+            sd[s + f"{ff}.layer_norm.weight"] = torch.ones(64)
+        sd[f"{stack}.block.0.layer.0.SelfAttention.relative_attention_bias.weight"] = torch.randn(8, 4, generator=g)
+        sd[f"{stack}.final_layer_norm.weight"] = torch.ones(64)
+    model = T5Model.from_state_dict(cfg, sd, device="cpu", dtype=torch.float32)
+    tok = ByteTokenizer(vocab_size=300)
+    pipe = Seq2SeqGenerator(model, tok)
+    deltas = []
+    out = pipe.generate("rewrite: where is the cat", SamplingParams(max_tokens=12), on_delta=deltas.append)
+    ids = pipe._encode("rewrite: where is the cat")
+    assert ids[-1] == 2 and out.token_ids == model.generate(ids, max_new_tokens=12)
+    assert out.completion_tokens == len(out.token_ids) <= 12 and out.prompt_tokens == len(ids)
+    assert "".join(deltas) == out.text or out.text.endswith("�")
+    out2 = pipe.generate([{"role": "user", "content": "rewrite: where is the cat"}], SamplingParams(max_tokens=12))
+    assert out2.token_ids == out.token_ids
