@@ -38,21 +38,44 @@ class LoadedModel:
     path: Optional[str] = None
     loaded_at: float = field(default_factory=time.time)
     info: Dict = field(default_factory=dict)
+    last_used: float = field(default_factory=time.time)
+    pinned: bool = False      # eager strategy / registered in memory: never unloaded for idleness or room
+    bytes: int = 0            # parameter bytes (advisory memory accounting)
+
+
+def _param_bytes(pipeline) -> int:
+    model = getattr(pipeline, "model", None) or getattr(getattr(pipeline, "engine", None), "model", None)
+    total = 0
+    for v in getattr(model, "w", {}).values():
+        if isinstance(v, torch.Tensor):
+            total += v.numel() * v.element_size()
+        else:  # block-fp8 weight: codes + scales
+            total += sum(t.numel() * t.element_size() for t in (getattr(v, "q", None), getattr(v, "scales", None))
+                         if isinstance(t, torch.Tensor))
+    return total
 
 
 class ModelManager:
     def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
-                 kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True):
+                 kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True, keep_alive_s: float = 0.0,
+                 max_memory_mb: int = 0, strategies: Optional[Dict[str, str]] = None, clock=time.time):
+        """``max_loaded_models`` 0 = unlimited; ``keep_alive_s`` > 0 unloads directory-backed models idle for that
+        long (checked on every access and by :meth:`evict_idle`); ``max_memory_mb`` > 0 is an advisory budget on
+        parameter bytes, enforced by unloading least-recently-used models; ``strategies`` maps model names to
+        eager (never unloaded) / lazy / bounded."""
         self.models_dir = models_dir or MF.default_models_dir()
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         self.max_loaded = max_loaded_models
+        self.keep_alive_s, self.max_memory_mb = keep_alive_s, max_memory_mb
+        self.strategies, self._clock = dict(strategies or {}), clock
+        self.evictions = 0
         self.kv_blocks, self.max_batch, self.prefix_cache = kv_blocks, max_batch, prefix_cache
         self._models: "OrderedDict[str, LoadedModel]" = OrderedDict()
         self._lock = threading.Lock()
 
     # -- registration of in-memory models ------------------------------------------------------------------
     def register(self, name: str, task: str, pipeline, tokenizer, info: Optional[dict] = None) -> LoadedModel:
-        lm = LoadedModel(name, task, pipeline, tokenizer, info=info or {})
+        lm = LoadedModel(name, task, pipeline, tokenizer, info=info or {}, pinned=True)
         with self._lock:
             self._models[f"{task}:{name}"] = lm
         return lm
@@ -142,19 +165,62 @@ class ModelManager:
 
     def get(self, name: str, task: str) -> LoadedModel:
         key = f"{task}:{name}"
+        now = self._clock()
         with self._lock:
+            self._evict_idle_locked(now, keep=key)
             if key in self._models:
                 self._models.move_to_end(key)
+                self._models[key].last_used = now
                 return self._models[key]
         path = MF.resolve_model_path(name, self.models_dir, task + "s")
         if path is None:
             raise ModelNotFound(f"model {name!r} not found under {self.models_dir} ({task}s/)")
         lm = self._load_dir(name, task, path)
+        lm.last_used = now
+        lm.pinned = self.strategies.get(name) == "eager"
+        lm.bytes = _param_bytes(lm.pipeline)
         with self._lock:
             self._models[key] = lm
-            while len(self._models) > self.max_loaded:
-                self._models.popitem(last=False)
+            self._make_room_locked(keep=key)
         return lm
+
+    # -- eviction ------------------------------------------------------------------------------------------
+    def _drop_locked(self, key: str) -> None:
+        self._models.pop(key, None)
+        self.evictions += 1
+
+    def _evict_idle_locked(self, now: float, keep: Optional[str] = None) -> int:
+        if self.keep_alive_s <= 0:
+            return 0
+        idle = [k for k, m in self._models.items()
+                if k != keep and not m.pinned and now - m.last_used > self.keep_alive_s]
+        for k in idle:
+            self._drop_locked(k)
+        return len(idle)
+
+    def _make_room_locked(self, keep: str) -> None:
+        def over() -> bool:
+            if self.max_loaded and len(self._models) > self.max_loaded:
+                return True
+            return bool(self.max_memory_mb) and sum(m.bytes for m in self._models.values()) > self.max_memory_mb << 20
+
+        while over():
+            victim = next((k for k, m in self._models.items() if k != keep and not m.pinned), None)
+            if victim is None:
+                break                      # only pinned models and the new one are left: the limits are advisory
+            self._drop_locked(victim)
+
+    def evict_idle(self) -> int:
+        """Unload models idle for longer than keep_alive; returns how many were unloaded."""
+        with self._lock:
+            return self._evict_idle_locked(self._clock())
+
+    def unload(self, name: str, task: str) -> bool:
+        with self._lock:
+            found = f"{task}:{name}" in self._models
+            if found:
+                self._drop_locked(f"{task}:{name}")
+            return found
 
     def list_models(self) -> Dict[str, Dict[str, dict]]:
         out: Dict[str, Dict[str, dict]] = {t: {} for t in MF.TASK_DIRS}

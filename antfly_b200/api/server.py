@@ -33,11 +33,17 @@ from .metrics import Metrics
 from .model_manager import ModelManager, ModelNotFound
 
 
+class QueueTimeout(QueueFull):
+    """The request waited longer than request_timeout for admission (answered 504, not 503)."""
+
+
 class RequestQueue:
     """Weighted admission: ``max_units`` of work in flight, ``max_waiting`` callers queued behind it."""
 
     def __init__(self, max_units: int = 64, max_waiting: int = 256):
-        self.max_units, self.max_waiting = max_units, max_waiting
+        # 0 means unlimited for either bound (the configuration file's convention)
+        self.max_units = max_units if max_units > 0 else 1 << 30
+        self.max_waiting = max_waiting if max_waiting > 0 else 1 << 30
         self.units, self.waiting = 0, 0
         self._cv = threading.Condition()
 
@@ -50,7 +56,7 @@ class RequestQueue:
             try:
                 ok = self._cv.wait_for(lambda: self.units + units <= self.max_units, timeout)
                 if not ok:
-                    raise QueueFull("timed out waiting for a slot")
+                    raise QueueTimeout("timed out waiting for a slot")
                 self.units += units
             finally:
                 self.waiting -= 1
@@ -66,7 +72,8 @@ def _err(status: int, code: str, message: str) -> JSONResponse:
 
 
 def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
-               max_concurrent_requests: int = 64, max_queue_size: int = 256) -> FastAPI:
+               max_concurrent_requests: int = 64, max_queue_size: int = 256,
+               request_timeout_s: float = 0.0) -> FastAPI:
     app = FastAPI(title="antfly-b200 inference", version="0.1")
     mgr = manager or ModelManager()
     metrics = Metrics()
@@ -78,11 +85,17 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     def run_guarded(endpoint: str, units: int, fn):
         t0 = time.perf_counter()
         try:
-            queue.acquire(units)
+            queue.acquire(units, timeout=request_timeout_s if request_timeout_s > 0 else 300.0)
+        except QueueTimeout as e:
+            metrics.queue_rejected.inc()
+            metrics.requests.labels(endpoint, "504").inc()
+            return _err(504, "timeout", str(e))
         except QueueFull as e:
             metrics.queue_rejected.inc()
             metrics.requests.labels(endpoint, "503").inc()
-            return _err(503, "queue_full", str(e))
+            r = _err(503, "queue_full", str(e))
+            r.headers["Retry-After"] = "1"
+            return r
         metrics.queue_depth.set(queue.waiting)
         try:
             with gpu_lock:

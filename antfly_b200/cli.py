@@ -43,13 +43,42 @@ def _get(mgr, name: str, task: str):
 def cmd_run(args) -> int:
     from .api.server import serve
 
-    mgr = _manager(args)
-    for spec in args.preload or []:
-        task, name = spec.split(":", 1)
-        _get(mgr, name, task)
-    serve(args.host, args.port, manager=mgr, max_concurrent_requests=args.max_concurrent_requests,
-          max_queue_size=args.max_queue_size)
+    from .api.model_manager import ModelManager
+    from .config import load_config
+
+    # file < environment < flags that were given on the command line
+    over = {k: v for k, v in (("models_dir", args.models_dir), ("preload", args.preload),
+                              ("max_concurrent_requests", args.max_concurrent_requests),
+                              ("max_queue_size", args.max_queue_size)) if v is not None}
+    if args.host is not None or args.port is not None:
+        over["api_url"] = f"http://{args.host or '127.0.0.1'}:{args.port or 11433}"
+    elif not args.config:
+        over["api_url"] = "http://127.0.0.1:11433"
+    cfg = load_config(args.config, **over)
+    host, port = cfg.host_port
+    mgr = ModelManager(models_dir=cfg.models_dir, device=args.device or cfg.device(), kv_blocks=args.kv_blocks,
+                       prefix_cache=not args.no_prefix_cache, max_loaded_models=cfg.max_loaded_models,
+                       keep_alive_s=cfg.keep_alive_s, max_memory_mb=cfg.max_memory_mb,
+                       strategies=cfg.model_strategies)
+    eager = [f"{t}:{n}" for n, s in cfg.model_strategies.items() if s == "eager"
+             for t in ("embedder", "reranker", "generator") if _resolvable(mgr, n, t)]
+    for spec in list(cfg.preload) + eager:
+        task, _, name = spec.partition(":")
+        if not name:                       # a bare model name: look it up under every task directory
+            name, tasks = task, [t for t in ("embedder", "reranker", "generator") if _resolvable(mgr, task, t)]
+        else:
+            tasks = [task]
+        for t in tasks:
+            _get(mgr, name, t)
+    serve(host, port, manager=mgr, max_concurrent_requests=cfg.max_concurrent_requests or 64,
+          max_queue_size=cfg.max_queue_size or 256, request_timeout_s=cfg.request_timeout_s)
     return 0
+
+
+def _resolvable(mgr, name: str, task: str) -> bool:
+    from .formats import manifest as MF
+
+    return name.startswith("random:") or MF.resolve_model_path(name, mgr.models_dir, task + "s") is not None
 
 
 def cmd_embed(args) -> int:
@@ -168,9 +197,11 @@ def main(argv: Optional[List[str]] = None) -> int:
                        help="do not reuse the KV blocks of prompt prefixes that were prefilled before")
 
     p = sub.add_parser("run"); common(p)
-    p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=11433)
-    p.add_argument("--preload", nargs="*"); p.add_argument("--max-concurrent-requests", type=int, default=64)
-    p.add_argument("--max-queue-size", type=int, default=256); p.set_defaults(fn=cmd_run)
+    p.add_argument("--config", help="YAML / JSON configuration file (api_url, models_dir, keep_alive, "
+                                    "max_loaded_models, max_memory_mb, preload, model_strategies, ...)")
+    p.add_argument("--host"); p.add_argument("--port", type=int)
+    p.add_argument("--preload", nargs="*"); p.add_argument("--max-concurrent-requests", type=int)
+    p.add_argument("--max-queue-size", type=int); p.set_defaults(fn=cmd_run)
     p = sub.add_parser("embed"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
     p.add_argument("--dimensions", type=int); p.add_argument("--print-timing", action="store_true")
