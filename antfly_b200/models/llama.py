@@ -24,6 +24,7 @@ from ..ops import attention as A
 from ..ops import dense as Dn
 from ..ops import quant as Q
 from ..ops import sampling as S
+from ..runtime.moe import CoactivationPredictor, ExpertResidency, HostExpertStore, route_batches
 
 
 @dataclass
@@ -146,6 +147,14 @@ def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> i
     return s
 
 
+@dataclass
+class MoeRuntimeState:
+    store: HostExpertStore
+    residency: ExpertResidency
+    predictor: CoactivationPredictor
+    max_predicted: int = 2
+
+
 class LlamaModel:
     def __init__(self, cfg: LlamaConfig, weights: Dict[str, object], tp_rank: int = 0, tp_size: int = 1,
                  comm=None):
@@ -160,6 +169,7 @@ class LlamaModel:
             weights["lm_head"].shape[0]
         self.vocab_offset = tp_rank * self.vocab_local if tp_size > 1 else 0
         self._scratch: Dict[tuple, torch.Tensor] = {}
+        self.moe_runtime = None   # set by offload_experts(): expert weights live in host memory
 
     # --------------------------------------------------------------------------------------------------
     @classmethod
@@ -413,6 +423,21 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    def offload_experts(self, max_resident_per_layer: int, max_predicted: int = 2) -> "MoeRuntimeState":
+        """Move the routed experts' weights to (pinned) host memory and keep at most ``max_resident_per_layer`` of
+        each layer's experts on the device; absent experts are copied in when a step routes to them and the experts
+        predicted for the next step are prefetched on a side stream.  For checkpoints whose experts exceed HBM."""
+        store = HostExpertStore(self.device)
+        for l in range(self.n_layers):
+            for e in range(self.cfg.num_experts):
+                gu, down = self.w.pop(f"l{l}.e{e}.gu", None), self.w.pop(f"l{l}.e{e}.down", None)
+                if gu is not None:
+                    store.put(l, e, {"gu": gu, "down": down})
+        stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        self.moe_runtime = MoeRuntimeState(store, ExpertResidency(store.load, max_resident_per_layer, stream),
+                                           CoactivationPredictor(), max_predicted)
+        return self.moe_runtime
+
     def _moe_mlp(self, h: torch.Tensor, l: int, T: int) -> torch.Tensor:
         """Sparse mixture-of-experts MLP: soft-max router, top-k experts per token (weights optionally renormalised),
         each expert a SwiGLU MLP on the block-fp8 GEMMs, outputs combined with the routing weights in fp32; plus the
@@ -425,12 +450,19 @@ class LlamaModel:
         if cfg.norm_topk_prob:
             topv = topv / topv.sum(-1, keepdim=True)
         out = torch.zeros((T, h.shape[1]), dtype=torch.float32, device=h.device)
-        for e in torch.unique(topi).tolist():
-            rows, slot = (topi == e).nonzero(as_tuple=True)
+        batches = route_batches(topi, topv, cfg.num_experts)
+        rt = self.moe_runtime
+        if rt is not None:  # offloaded experts: load what this step needs, prefetch what the next is likely to
+            ws = rt.residency.ensure(l, batches.active)
+            rt.predictor.note(l, cfg.num_experts, batches.active)
+            rt.residency.prefetch(l, rt.predictor.predict(l, batches.active, rt.max_predicted)[0],
+                                  protect=batches.active)
+        for e, rows, wts in batches:
+            gu, down = (ws[e]["gu"], ws[e]["down"]) if rt is not None else (w[p + f"e{e}.gu"], w[p + f"e{e}.down"])
             xe = h.index_select(0, rows)
-            act = self._linear(xe, w[p + f"e{e}.gu"], rows.numel(), swiglu=True)
-            ye = self._linear(act, w[p + f"e{e}.down"], rows.numel()).float()
-            out.index_add_(0, rows, ye * topv[rows, slot][:, None])
+            act = self._linear(xe, gu, rows.numel(), swiglu=True)
+            ye = self._linear(act, down, rows.numel()).float()
+            out.index_add_(0, rows, ye * wts[:, None])
         if p + "shared.gu" in w:
             act = self._linear(h, w[p + "shared.gu"], T, swiglu=True)
             ys = self._linear(act, w[p + "shared.down"], T).float()
