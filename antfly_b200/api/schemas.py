@@ -161,3 +161,39 @@ class SearchResponse(BaseModel):
     hits: List[List[SearchHit]]
     took_ms: float
     index: str
+
+
+class TableCreateRequest(BaseModel):
+    """Subset of the table-creation body: one dense embedding index (dimension, metric, embedder model, exact or
+    HBC) and an optional sparse index."""
+    model_config = ConfigDict(extra="allow")
+    dimension: Optional[int] = None
+    metric: str = "cosine"
+    embedder: Optional[str] = None
+    index_type: str = "flat"            # flat | hbc
+    reranker: Optional[str] = None
+    text_field: str = "text"
+
+
+class BatchRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    inserts: Dict[str, Dict[str, Any]] = Field(default_factory=dict)
+    deletes: List[str] = Field(default_factory=list)
+    embeddings: Optional[Dict[str, List[float]]] = None     # precomputed dense vectors per inserted key
+
+
+class TableQueryRequest(BaseModel):
+    """Hybrid-search subset of QueryRequest (metadata.yaml:4077-4400)."""
+    model_config = ConfigDict(extra="allow")
+    semantic_search: Optional[str] = None
+    full_text_search: Union[str, Dict[str, Any], None] = None
+    embeddings: Union[Dict[str, Any], List[float], str, None] = None
+    limit: int = Field(default=10, gt=0)
+    offset: int = Field(default=0, ge=0)
+    search_effort: float = 0.5
+    distance_under: Optional[float] = None
+    distance_over: Optional[float] = None
+    merge_config: Optional[Dict[str, Any]] = None
+    pruner: Optional[Dict[str, Any]] = None
+    reranker: Optional[Dict[str, Any]] = None
+    fields: Optional[List[str]] = None

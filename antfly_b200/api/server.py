@@ -67,6 +67,37 @@ class RequestQueue:
             self._cv.notify_all()
 
 
+class _HbcAdapter:
+    """HBC tree behind the table's ``add`` / ``search`` calls: the first batch bulk-builds the tree, later ones are
+    online inserts."""
+
+    def __init__(self, dim: int, metric: str):
+        from ..index.hbc import HBCConfig
+
+        self.cfg = HBCConfig(dim, "l2_squared" if metric in ("l2", "l2_squared", "euclidean") else metric)
+        self.idx = None
+
+    def add(self, vectors, ids):
+        from ..index.hbc import HBCIndex
+
+        if self.idx is None:
+            self.idx = HBCIndex.bulk_build(vectors, self.cfg, ids=ids)
+        else:
+            self.idx.insert(vectors, ids)
+
+    def search(self, queries, k, effort: float = 0.5):
+        from ..index.distance import resolve_search_effort
+        from ..index.flat import SearchResult
+
+        if self.idx is None:
+            return SearchResult(torch.full((1, k), float("inf")), torch.full((1, k), -1, dtype=torch.int64))
+        width, eps = resolve_search_effort(k, effort, self.idx.vectors.shape[0])
+        ids, dists = self.idx.search(queries[0], k, search_width=width, epsilon=eps)
+        pad = k - len(ids)
+        return SearchResult(torch.tensor([list(dists) + [float("inf")] * pad]),
+                            torch.tensor([list(ids) + [-1] * pad], dtype=torch.int64))
+
+
 def _err(status: int, code: str, message: str) -> JSONResponse:
     return JSONResponse(status_code=status, content={"error": code, "message": message})
 
@@ -402,6 +433,113 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "search", 1, work)
 
+    # ---- tables: documents + dense / sparse / full-text indexes, hybrid query ---------------------------------
+    app.state.tables = {}
+
+    async def table_create(table: str, request: Request):
+        req, bad = await parse(request, S.TableCreateRequest)
+        if bad:
+            return bad
+        if table in app.state.tables:
+            return _err(409, "table_exists", f"table {table!r} already exists")
+
+        def work():
+            from ..index.flat import GrowableFlatIndex
+            from ..index.table import Table
+
+            embed = rerank = None
+            dim = req.dimension
+            if req.embedder:
+                pipe = mgr.get(req.embedder, "embedder").pipeline
+                embed = lambda texts: pipe.embed(list(texts))[0]
+                dim = dim or pipe.dim
+            if req.reranker:
+                rpipe = mgr.get(req.reranker, "reranker").pipeline
+                rerank = lambda q, docs: rpipe.rerank(q, list(docs))[0]
+            dense = None
+            if dim:
+                if req.index_type == "hbc":
+                    dense = _HbcAdapter(dim, req.metric)
+                elif req.index_type == "flat":
+                    dense = GrowableFlatIndex(dim, req.metric, device=str(mgr.device))
+                else:
+                    raise ValueError(f"unknown index_type {req.index_type!r}")
+            app.state.tables[table] = Table(table, dense_index=dense, embed=embed, rerank=rerank,
+                                            text_field=req.text_field)
+            return {"table": table, "dimension": dim, "metric": req.metric, "index_type": req.index_type}
+
+        return await asyncio.to_thread(run_guarded, "table_create", 1, work)
+
+    async def table_batch(table: str, request: Request):
+        req, bad = await parse(request, S.BatchRequest)
+        if bad:
+            return bad
+        tbl = app.state.tables.get(table)
+        if tbl is None:
+            return _err(404, "table_not_found", f"table {table!r} does not exist")
+
+        def work():
+            emb = None
+            if req.embeddings is not None and req.inserts:
+                emb = torch.tensor([req.embeddings[k] for k in req.inserts], dtype=torch.float32)
+            if req.inserts:
+                tbl.upsert(req.inserts, emb)
+            deleted = sum(1 for k in req.deletes if tbl.delete(k))
+            return {"inserted": len(req.inserts), "deleted": deleted, "count": len(tbl)}
+
+        return await asyncio.to_thread(run_guarded, "table_batch", max(1, len(req.inserts)), work)
+
+    async def table_query(table: str, request: Request):
+        req, bad = await parse(request, S.TableQueryRequest)
+        if bad:
+            return bad
+        tbl = app.state.tables.get(table)
+        if tbl is None:
+            return _err(404, "table_not_found", f"table {table!r} does not exist")
+
+        def work():
+            from ..index.fusion import MergeConfig, Pruner
+            from ..index.table import TableQuery
+
+            t0 = time.perf_counter()
+            ft = req.full_text_search
+            if isinstance(ft, dict):
+                ft = ft.get("query") or ft.get("match") or ""
+            emb = None
+            if req.embeddings is not None:
+                e = req.embeddings
+                if isinstance(e, dict):          # {index name: vector}: the table has one dense index
+                    e = next(iter(e.values()))
+                emb = decode_vectors(e)[0]
+            mc = req.merge_config or {}
+            merge = MergeConfig(mc.get("strategy", "rrf"), dict(mc.get("weights") or {}),
+                                int(mc.get("window_size", 0) or 0), float(mc.get("rank_constant", 60.0) or 60.0))
+            pr = Pruner(**{k: v for k, v in (req.pruner or {}).items() if k in Pruner.__dataclass_fields__}) \
+                if req.pruner else None
+            rq = None
+            if req.reranker is not None:
+                rq = req.reranker.get("query") or req.semantic_search or (ft if isinstance(ft, str) else None)
+            q = TableQuery(embedding=emb, semantic_search=req.semantic_search, full_text_search=ft or None,
+                           limit=req.limit + req.offset, search_effort=req.search_effort,
+                           distance_under=req.distance_under, distance_over=req.distance_over, merge=merge,
+                           pruner=pr, rerank_query=rq,
+                           rerank_field=(req.reranker or {}).get("field", tbl.text_field))
+            hits = tbl.query(q)[req.offset:]
+            out = []
+            for h in hits:
+                src = h.document or {}
+                if req.fields is not None:
+                    src = {k: v for k, v in src.items() if k in req.fields}
+                out.append({"_id": h.id, "_score": h.score, "_index_scores": h.index_scores, "_source": src})
+            return {"responses": [{"hits": {"total": len(out), "hits": out,
+                                            "max_score": max((x["_score"] for x in out), default=0.0)},
+                                   "took": int((time.perf_counter() - t0) * 1e3), "status": 200, "table": table}]}
+
+        return await asyncio.to_thread(run_guarded, "table_query", 1, work)
+
+    async def table_list():
+        return {"tables": [{"name": n, "count": len(t)} for n, t in app.state.tables.items()]}
+
     # ---- models / health / metrics ------------------------------------------------------------------------
     async def models():
         per_task = mgr.list_models()
@@ -437,6 +575,10 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         app.add_api_route(path, generate, methods=["POST"])
     app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
+    app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
+    app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])
+    app.add_api_route("/db/v1/tables/{table}/batch", table_batch, methods=["POST"])
+    app.add_api_route("/db/v1/tables/{table}/query", table_query, methods=["POST"])
     app.add_api_route("/ai/v1/models", models, methods=["GET"])
     app.add_api_route("/ai/v1/metrics", metrics_ep, methods=["GET"])
     app.add_api_route("/metrics", metrics_ep, methods=["GET"])

@@ -13,7 +13,7 @@ zig/lib/vectorindex/src/search_results.zig).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -181,3 +181,39 @@ def recall_at_k(found: torch.Tensor, truth: torch.Tensor, k: int) -> float:
     f, t = found[:, :k].cpu().tolist(), truth[:, :k].cpu().tolist()
     hit = sum(len(set(a) & set(b)) for a, b in zip(f, t))
     return hit / (len(t) * k)
+
+
+class GrowableFlatIndex:
+    """Exact index that accepts new vectors: rows are appended to a staging list and the searchable
+    :class:`FlatIndex` is rebuilt on the first search after a change (a re-upload of the bf16 matrix; exact search
+    has no structure to maintain).  Re-adding an id replaces its vector."""
+
+    def __init__(self, dim: int, metric: str = "cosine", device=None, storage: str = "bf16"):
+        self.dim, self.metric, self.device, self.storage = dim, metric, device, storage
+        self._rows: List[torch.Tensor] = []
+        self._ids: List[int] = []
+        self._pos: dict = {}
+        self._index: Optional[FlatIndex] = None
+
+    def __len__(self) -> int:
+        return len(self._ids)
+
+    def add(self, vectors: torch.Tensor, ids: torch.Tensor) -> None:
+        assert vectors.shape[1] == self.dim
+        for v, i in zip(vectors.float().cpu(), ids.tolist()):
+            if i in self._pos:
+                self._rows[self._pos[i]] = v
+            else:
+                self._pos[i] = len(self._ids)
+                self._ids.append(int(i))
+                self._rows.append(v)
+        self._index = None
+
+    def search(self, queries: torch.Tensor, k: int, **_kw) -> SearchResult:
+        if not self._ids:
+            q = queries.shape[0]
+            return SearchResult(torch.full((q, k), float("inf")), torch.full((q, k), -1, dtype=torch.int64))
+        if self._index is None:
+            self._index = FlatIndex(torch.stack(self._rows), self.metric, ids=torch.tensor(self._ids),
+                                    storage=self.storage, device=self.device)
+        return self._index.search(queries, min(k, len(self._ids)))

@@ -173,3 +173,47 @@ def test_request_queue_backpressure():
         q.acquire(1, timeout=0.05)
     q.release(1)
     q.acquire(1)
+
+
+@pytest.mark.parametrize("index_type", ["flat", "hbc"])
+def test_table_create_batch_and_hybrid_query(client, index_type):
+    t = f"docs_{index_type}"
+    r = client.post(f"/db/v1/tables/{t}", json={"embedder": "tiny-embed", "reranker": "tiny-rerank",
+                                                 "index_type": index_type})
+    assert r.status_code == 200 and r.json()["dimension"] == 128
+    assert client.post(f"/db/v1/tables/{t}", json={}).status_code == 409
+    texts = ["red apples and green apples", "how to bake an apple pie", "history of the roman empire",
+             "roman roads and aqueducts", "a new phone was released", "height of the empire state building"]
+    texts += [f"filler document number {i} about topic {i % 7}" for i in range(60)]
+    r = client.post(f"/db/v1/tables/{t}/batch", json={"inserts": {f"k{i}": {"text": x, "n": i}
+                                                                    for i, x in enumerate(texts)}})
+    assert r.status_code == 200 and r.json() == {"inserted": 66, "deleted": 0, "count": 66}
+    assert {"name": t, "count": 66} in client.get("/db/v1/tables").json()["tables"]
+    # full text + semantic, fused with RRF; documents and per-index scores come back
+    r = client.post(f"/db/v1/tables/{t}/query", json={"semantic_search": "roman empire",
+                                                       "full_text_search": {"query": "roman empire"}, "limit": 5})
+    body = r.json()["responses"][0]
+    assert r.status_code == 200 and body["status"] == 200 and body["hits"]["total"] == 5
+    top = body["hits"]["hits"][0]
+    assert top["_id"] == "k2" and top["_source"]["text"] == texts[2] and "full_text" in top["_index_scores"]
+    assert body["hits"]["max_score"] == top["_score"]
+    # the document's own embedding finds it first; fields filter the source
+    e = client.post("/ai/v1/embed", json={"model": "tiny-embed", "input": texts[1]}).json()["data"][0]["embedding"]
+    r = client.post(f"/db/v1/tables/{t}/query", json={"embeddings": {"dense": e}, "limit": 3, "fields": ["n"]})
+    h = r.json()["responses"][0]["hits"]["hits"]
+    assert h[0]["_id"] == "k1" and h[0]["_source"] == {"n": 1} and set(h[0]["_index_scores"]) == {"dense"}
+    # rerank stage, offset paging, deletes
+    r = client.post(f"/db/v1/tables/{t}/query", json={"full_text_search": "apple", "limit": 2,
+                                                       "reranker": {"query": "apple pie recipe"}})
+    assert all("reranker" in x["_index_scores"] for x in r.json()["responses"][0]["hits"]["hits"])
+    a = client.post(f"/db/v1/tables/{t}/query", json={"full_text_search": "roman", "limit": 2}).json()
+    b = client.post(f"/db/v1/tables/{t}/query", json={"full_text_search": "roman", "limit": 1, "offset": 1}).json()
+    assert b["responses"][0]["hits"]["hits"][0]["_id"] == a["responses"][0]["hits"]["hits"][1]["_id"]
+    r = client.post(f"/db/v1/tables/{t}/batch", json={"deletes": ["k2", "nope"]})
+    assert r.json()["deleted"] == 1 and r.json()["count"] == 65
+    ids = [x["_id"] for x in client.post(f"/db/v1/tables/{t}/query", json={
+        "semantic_search": "roman empire", "full_text_search": "roman empire", "limit": 10}).json()[
+        "responses"][0]["hits"]["hits"]]
+    assert "k2" not in ids
+    assert client.post("/db/v1/tables/missing/query", json={"full_text_search": "x"}).status_code == 404
+    assert client.post(f"/db/v1/tables/{t}/query", json={"limit": 0}).status_code == 400
