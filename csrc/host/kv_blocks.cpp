@@ -149,7 +149,8 @@ int afb_kv_append(void* h, int64_t seq, int n_tokens, int* out_slots) {
   const int need = (new_len + p->page - 1) / p->page;
   const int have = static_cast<int>(s.blocks.size());
   // A shared tail block must not be appended into: copy it first.
-  const bool tail_shared = have > 0 && (s.len % p->page) != 0 && p->refcount[s.blocks[have - 1]] > 1 && n_tokens > 0;
+  const bool tail_shared = have > 0 && (s.len % p->page) != 0 && s.blocks[have - 1] >= 0 &&
+                           p->refcount[s.blocks[have - 1]] > 1 && n_tokens > 0;
   const int extra = (need > have ? need - have : 0) + (tail_shared ? 1 : 0);
   if (extra > static_cast<int>(p->free_list.size())) {
     ++p->oom_total;
@@ -179,6 +180,9 @@ int afb_kv_truncate(void* h, int64_t seq, int new_len) {
   if (it == p->seqs.end()) return -1;
   Sequence& s = it->second;
   if (new_len < 0 || new_len > s.len) return -1;
+  // Tokens whose blocks the sliding window already released cannot become the tail again (their block is gone):
+  // only a full reset may cut below the trimmed boundary.
+  if (new_len != 0 && new_len < s.first_live_block * p->page) return -1;
   const int keep = (new_len + p->page - 1) / p->page;
   while (static_cast<int>(s.blocks.size()) > keep) {
     p->release(s.blocks.back());

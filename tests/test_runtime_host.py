@@ -68,6 +68,23 @@ def test_sliding_window_trim_releases_only_whole_old_tiles():
     assert a.trim_window(1, 100) == 4
 
 
+def test_truncate_cannot_cut_into_blocks_the_window_released():
+    """After the sliding window released old blocks, a rollback may only go back to a token whose block still
+    exists (anything else would append into a block that is gone); a full reset is allowed."""
+    a = BlockAllocator(num_blocks=64, page=16)
+    a.attach(1)
+    a.append(1, 300)
+    assert a.trim_window(1, 100) == 12                   # blocks of tokens 0..191 released
+    with pytest.raises(KeyError):
+        a.truncate(1, 150)
+    a.truncate(1, 250)                                   # speculative-decoding style rollback: fine
+    slots = a.append(1, 5)
+    assert a.length(1) == 255 and (slots >= 0).all()
+    a.truncate(1, 0)
+    slots = a.append(1, 20)
+    assert a.length(1) == 20 and (slots >= 0).all() and a.free_blocks == 62
+
+
 def test_append_batch_matches_single_appends():
     a = BlockAllocator(num_blocks=32, page=16)
     for s in (1, 2, 3):
