@@ -53,6 +53,14 @@ int afb_kvq_decode_rows(int codec, int is_value, const uint8_t* src, float* dst,
 int afb_kvq_attention_host(int codec, const float* q, const uint8_t* k_rows, const uint8_t* v_rows, long n_tokens,
                            int Hq, int Hkv, int D, float scale, float k_scale, float v_scale, int window, float* out);
 
+long afb_gguf_block_bytes(int type);
+long afb_gguf_block_values(int type);
+int afb_gguf_dequantize(int type, const uint8_t* src, float* dst, long n_values);
+float afb_gguf_element(int type, const uint8_t* block, int j);
+long afb_gguf_element_block_values(int type);
+int afb_image_preprocess_host(const uint8_t* img, int src_w, int src_h, int channels, float crop_x, float crop_y,
+                              float crop_w, float crop_h, int out_w, int out_h, int mode, float rescale,
+                              const float* mean3, const float* std3, float* out_chw);
 int afb_hilbert_keys(const float* vectors, long n, int dims, uint8_t* keys);
 void afb_cpu_set_threads(int n);
 int afb_cpu_topk(const float* q, const float* x, int Q, long N, int D, int k, int metric, int* out_idx,
@@ -217,6 +225,52 @@ static void kv_codec_workload(unsigned seed) {
   CHECK(afb_kvq_row_bytes(4, 2, 96, 0) == 0);
 }
 
+static void gguf_and_image_workload(unsigned seed) {
+  std::mt19937 rng(seed);
+  // every block decoder over random bytes in buffers of exactly the block size (an overrun is an ASan report)
+  for (int type = 0; type < 64; ++type) {
+    const long bb = afb_gguf_block_bytes(type), bv = afb_gguf_block_values(type);
+    if (bb <= 0 || bv <= 0) continue;
+    const long blocks = 7;
+    std::vector<uint8_t> src(blocks * bb);
+    for (auto& b : src) b = static_cast<uint8_t>(rng());
+    std::vector<float> dst(blocks * bv);
+    CHECK(afb_gguf_dequantize(type, src.data(), dst.data(), blocks * bv) == 0);
+    const long ev = afb_gguf_element_block_values(type);
+    if (ev > 0) {
+      for (long b = 0; b < blocks; ++b)
+        for (long j = 0; j < ev; ++j) {
+          const float e = afb_gguf_element(type, src.data() + b * bb, static_cast<int>(j));
+          const float d = dst[b * bv + j];
+          CHECK(e == d || (e != e && d != d));     // the per-element decoder and the block decoder agree
+        }
+    }
+  }
+  // image preprocessing at awkward geometries: 1-pixel sources, crops at the border, up- and down-scaling
+  const float mean[3] = {0.48f, 0.45f, 0.40f}, sd[3] = {0.26f, 0.26f, 0.27f};
+  const int geo[][4] = {{1, 1, 8, 8}, {2, 3, 5, 7}, {37, 19, 16, 16}, {64, 64, 3, 1}, {5, 200, 9, 2}};
+  for (auto& g : geo) {
+    for (int ch : {3, 4}) {
+      for (int mode = 0; mode < 3; ++mode) {
+        std::vector<uint8_t> img(static_cast<size_t>(g[0]) * g[1] * ch);
+        for (auto& b : img) b = static_cast<uint8_t>(rng());
+        std::vector<float> out(3u * g[2] * g[3]);
+        CHECK(afb_image_preprocess_host(img.data(), g[0], g[1], ch, 0.0f, 0.0f, static_cast<float>(g[0]),
+                                        static_cast<float>(g[1]), g[2], g[3], mode, 1.0f / 255, mean, sd,
+                                        out.data()) == 0);
+        // a crop hanging off the bottom-right corner
+        CHECK(afb_image_preprocess_host(img.data(), g[0], g[1], ch, g[0] * 0.5f, g[1] * 0.5f, g[0] * 0.5f + 0.49f,
+                                        g[1] * 0.5f + 0.49f, g[2], g[3], mode, 1.0f / 255, mean, sd, out.data()) == 0);
+        for (float v : out) CHECK(v == v);
+      }
+    }
+  }
+  std::vector<float> pts(257 * 24);
+  for (auto& v : pts) v = static_cast<float>(rng() % 2000) / 1000.0f - 1.0f;
+  std::vector<uint8_t> keys(257 * 4 * 24, 0);   // exactly 4 bytes per dimension
+  afb_hilbert_keys(pts.data(), 257, 24, keys.data());
+}
+
 static void threaded_workload(unsigned seed) {
   std::mt19937 rng(seed);
   std::normal_distribution<float> nd;
@@ -265,6 +319,7 @@ int main(int argc, char** argv) {
     scheduler_workload(seed + 1, 4000);
     grammar_workload(seed + 2);
     kv_codec_workload(seed + 3);
+    gguf_and_image_workload(seed + 5);
     threaded_workload(seed + 4);
   }
   std::printf("sanitize_main %s seed=%u failures=%d\n", mode.c_str(), seed, g_fail);
