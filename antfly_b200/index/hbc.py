@@ -163,7 +163,16 @@ class HBCIndex:
         return d, torch.zeros_like(d)
 
     def search(self, query: torch.Tensor, k: int, search_width: Optional[int] = None,
-               epsilon: Optional[float] = None) -> Tuple[List[int], List[float]]:
+               epsilon: Optional[float] = None, profile: Optional[dict] = None) -> Tuple[List[int], List[float]]:
+        """Beam search.  When ``profile`` is a dict it is filled with the per-query breakdown the reference's
+        SearchProfile reports (zig/lib/vectorindex/src/hbc_index.zig:1652 searchProfiledRequest): nodes expanded,
+        leaves scored, candidates kept, vectors re-ranked exactly, pruned queue pops, and nanoseconds spent scoring
+        internal nodes, scoring leaves and re-ranking."""
+        import time as _time
+
+        t_start = _time.perf_counter_ns()
+        prof = {"internal_nodes": 0, "leaves": 0, "pruned": 0, "candidates": 0, "reranked": 0,
+                "internal_ns": 0, "leaf_ns": 0, "rerank_ns": 0, "total_ns": 0}
         cfg = self.cfg
         width = search_width or cfg.search_width
         eps = cfg.epsilon if epsilon is None else epsilon
@@ -180,9 +189,13 @@ class HBCIndex:
             bound, _, nid = heapq.heappop(pq)
             nd = self.nodes[nid]
             if cfg.metric != "inner_product" and len(cands) >= rerank_n and bound > dmin * (1 + eps):
+                prof["pruned"] += 1
                 continue
+            t0 = _time.perf_counter_ns()
             d, e = self._score(nd, q)
             d, e = d.tolist(), e.tolist()
+            prof["leaf_ns" if nd.is_leaf else "internal_ns"] += _time.perf_counter_ns() - t0
+            prof["leaves" if nd.is_leaf else "internal_nodes"] += 1
             if nd.is_leaf:
                 leaves += 1
                 for vid, dist in zip(nd.children, d):
@@ -198,11 +211,21 @@ class HBCIndex:
         # Exact re-rank of the best estimated candidates, up to the reference's candidate capacity.
         capacity = min(max(4 * width, 2 * cfg.branching_factor, 1), 1024)
         short = [vid for _, vid in heapq.nsmallest(max(rerank_n, k, capacity), cands)]
+        prof["candidates"], prof["reranked"] = len(cands), len(short)
         if not short:
+            if profile is not None:
+                prof["total_ns"] = _time.perf_counter_ns() - t_start
+                profile.update(prof)
             return [], []
+        t0 = _time.perf_counter_ns()
         exact = R.distances(q[None], self.vectors[torch.tensor(short)], cfg.metric)[0]
         order = torch.argsort(exact)[:k]
-        return [int(self.ids[short[i]]) for i in order.tolist()], exact[order].tolist()
+        out = [int(self.ids[short[i]]) for i in order.tolist()], exact[order].tolist()
+        if profile is not None:
+            prof["rerank_ns"] = _time.perf_counter_ns() - t0
+            prof["total_ns"] = _time.perf_counter_ns() - t_start
+            profile.update(prof)
+        return out
 
     # -- online maintenance -------------------------------------------------------------------------------
     def _requantize(self, nd: Node) -> None:

@@ -214,6 +214,12 @@ def test_hbc_online_insert_split_and_delete():
     truth = exact_search_fp32(q, allx, 10, "l2_squared")
     found = torch.tensor([idx.search(q[i], 10)[0] + [-1] * 10 for i in range(40)])[:, :10]
     assert recall_at_k(found, truth.ids, 10) > 0.8
+    # per-query profile: wider search scores more leaves and re-ranks more vectors
+    pa, pb = {}, {}
+    idx.search(q[0], 10, search_width=4, profile=pa)
+    idx.search(q[0], 10, search_width=32, profile=pb)
+    assert 1 <= pa["leaves"] <= 4 < pb["leaves"] <= 32 and pb["reranked"] >= pa["reranked"] >= 10
+    assert pa["internal_nodes"] >= 1 and pa["total_ns"] >= pa["leaf_ns"] + pa["internal_ns"] + pa["rerank_ns"] > 0
     # deletion: the deleted ids never come back
     gone = truth.ids[0, :5].tolist()
     assert idx.delete(gone) == 5 and idx.delete(gone) == 0
