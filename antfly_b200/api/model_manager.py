@@ -129,6 +129,26 @@ class ModelManager:
 
             model = LlamaModel.from_state_dict(LlamaConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = DecoderEmbedder(model, tok)
+        elif task == "rewriter" or (task == "generator" and cfg_d.get("model_type") in ("t5", "mt5")):
+            from ..models.t5 import T5Config, T5Model
+            from ..pipelines.seq2seq import Seq2SeqGenerator
+
+            if cfg_d.get("model_type") not in ("t5", "mt5"):
+                raise ModelNotFound(f"{name}: rewriters are T5-family encoder-decoder models "
+                                    f"(found {cfg_d.get('model_type')!r})")
+            model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
+            pipe = Seq2SeqGenerator(model, tok)
+        elif task in ("recognizer", "classifier"):
+            from ..pipelines.classification import TextClassifier, TokenClassifier
+
+            model = self._encoder(cfg_d, sd)
+            id2label = {int(k): v for k, v in (cfg_d.get("id2label") or {}).items()} or \
+                {i: f"LABEL_{i}" for i in range(model.cfg.num_labels)}
+            if task == "recognizer":
+                pipe = TokenClassifier(model, id2label, tok)
+            else:
+                pipe = TextClassifier(model, tok, id2label,
+                                      multi_label=cfg_d.get("problem_type") == "multi_label_classification")
         elif task in ("embedder", "reranker") and cfg_d.get("model_type") == "modernbert":
             from ..models.modernbert import ModernBertConfig, ModernBertModel
 
@@ -143,12 +163,6 @@ class ModelManager:
             cfg = BertConfig.from_hf(cfg_d)
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
-        elif cfg_d.get("model_type") in ("t5", "mt5"):
-            from ..models.t5 import T5Config, T5Model
-            from ..pipelines.seq2seq import Seq2SeqGenerator
-
-            model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
-            pipe = Seq2SeqGenerator(model, tok)
         else:
             if cfg_d.get("model_type") in ("gpt2", "gpt_neox", "opt", "gptj", "phi"):
                 from ..models.gpt import GptConfig, GptModel
@@ -162,6 +176,21 @@ class ModelManager:
                             prefix_cache=self.prefix_cache)
             pipe = Generator(eng, tok, mf.chat_template)
         return LoadedModel(name, task, pipe, tok, path, info={"weights": mf.weights, "capabilities": mf.capabilities})
+
+    def _encoder(self, cfg_d: dict, sd):
+        """BERT-family / ModernBERT / DeBERTa encoder with its classification head, picked by model_type."""
+        mt = cfg_d.get("model_type")
+        if "num_labels" not in cfg_d and cfg_d.get("id2label"):
+            cfg_d = dict(cfg_d, num_labels=len(cfg_d["id2label"]))
+        if mt == "modernbert":
+            from ..models.modernbert import ModernBertConfig, ModernBertModel
+
+            return ModernBertModel.from_state_dict(ModernBertConfig.from_hf(cfg_d), sd, device=self.device)
+        if mt == "deberta-v2":
+            from ..models.deberta import DebertaConfig, DebertaModel
+
+            return DebertaModel.from_state_dict(DebertaConfig.from_hf(cfg_d), sd, device=self.device)
+        return BertModel.from_state_dict(BertConfig.from_hf(cfg_d), sd, device=self.device)
 
     def get(self, name: str, task: str) -> LoadedModel:
         key = f"{task}:{name}"

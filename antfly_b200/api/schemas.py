@@ -197,3 +197,26 @@ class TableQueryRequest(BaseModel):
     pruner: Optional[Dict[str, Any]] = None
     reranker: Optional[Dict[str, Any]] = None
     fields: Optional[List[str]] = None
+
+
+class RewriteRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    inputs: List[str]
+    max_tokens: int = Field(default=128, gt=0)
+
+
+class ExtractionInput(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    id: Optional[str] = None
+    content: Union[str, List[Dict[str, Any]]]
+
+
+class ExtractionRequest(BaseModel):
+    """Schema-driven extraction (specs/openapi/ai/extraction.yaml): entity labels for a token-classification
+    model, classification tasks for a sequence-classification model."""
+    model_config = ConfigDict(extra="allow", protected_namespaces=())
+    model: str
+    inputs: List[ExtractionInput]
+    schema_: Dict[str, Any] = Field(alias="schema")
+    options: Dict[str, Any] = Field(default_factory=dict)

@@ -433,6 +433,85 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "search", 1, work)
 
+    # ---- rewrite (encoder-decoder text-to-text) and schema-driven extraction -------------------------------------
+    async def rewrite(request: Request):
+        req, bad = await parse(request, S.RewriteRequest)
+        if bad:
+            return bad
+
+        def work():
+            lm = mgr.get(req.model, "rewriter")
+            data, pt, ct = [], 0, 0
+            for i, text in enumerate(req.inputs):
+                out = lm.pipeline.generate(text, SamplingParams(max_tokens=req.max_tokens), raw_prompt=True)
+                data.append({"object": "rewrite", "index": i, "texts": [out.text]})
+                pt += out.prompt_tokens
+                ct += out.completion_tokens
+            return {"object": "list", "data": data, "model": req.model,
+                    "usage": {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct}}
+
+        return await asyncio.to_thread(run_guarded, "rewrite", max(1, len(req.inputs)), work)
+
+    async def extract(request: Request):
+        req, bad = await parse(request, S.ExtractionRequest)
+        if bad:
+            return bad
+
+        def text_of(content) -> str:
+            if isinstance(content, str):
+                return content
+            return "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type") == "text")
+
+        def work():
+            schema, opts = req.schema_, req.options
+            thr = float(opts.get("threshold", 0.0) or 0.0)
+            texts = [text_of(i.content) for i in req.inputs]
+            want_ents = [str(x) for x in schema.get("entities") or []]
+            tasks = schema.get("classifications") or []
+            if not want_ents and not tasks:
+                raise ValueError("schema needs entities and / or classifications")
+            data = [{"id": i.id} if i.id is not None else {} for i in req.inputs]
+            ntok = 0
+            if want_ents:
+                ner = mgr.get(req.model, "recognizer").pipeline
+                allowed = {w.lower() for w in want_ents}
+                for rec, text, ents in zip(data, texts, ner.entities(texts)):
+                    rec["entities"], cursor = [], 0
+                    for e in ents:
+                        if e.label.lower() not in allowed or e.score < thr:
+                            continue
+                        item = {"label": e.label, "text": (e.text or "").strip(), "score": e.score}
+                        if opts.get("include_spans", True) and item["text"]:
+                            at = text.lower().find(item["text"].lower(), cursor)
+                            if at < 0:
+                                at = text.lower().find(item["text"].lower())
+                            if at >= 0:
+                                item["start"], item["end"] = at, at + len(item["text"])
+                                item["text"] = text[at: at + len(item["text"])]
+                                cursor = item["end"]
+                        if not opts.get("include_confidence", True):
+                            item.pop("score")
+                        rec["entities"].append(item)
+            if tasks:
+                clf = mgr.get(req.model, "classifier").pipeline
+                known = {v.lower(): v for v in clf.id2label.values()}
+                ranked = clf.classify(texts, top_k=len(clf.id2label))
+                for rec, scores in zip(data, ranked):
+                    rec["classifications"] = []
+                    for t in tasks:
+                        labels = [str(l) for l in t.get("labels") or []]
+                        missing = [l for l in labels if l.lower() not in known]
+                        if missing:
+                            raise ValueError(f"classification {t.get('name')!r}: model has no label(s) {missing}")
+                        cand = [s for s in scores if s["label"].lower() in {l.lower() for l in labels}]
+                        keep = [s for s in cand if s["score"] >= thr] if t.get("multi_label") else cand[:1]
+                        for s in keep:
+                            rec["classifications"].append({"name": t.get("name", ""), "label": s["label"],
+                                                           "score": s["score"]})
+            return {"object": "extraction", "model": req.model, "data": data, "usage": {"inputs": len(texts)}}
+
+        return await asyncio.to_thread(run_guarded, "extract", max(1, len(req.inputs)), work)
+
     # ---- tables: documents + dense / sparse / full-text indexes, hybrid query ---------------------------------
     app.state.tables = {}
 
@@ -574,6 +653,8 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     for path in ("/ai/v1/generate", "/ai/v1/chat/completions"):
         app.add_api_route(path, generate, methods=["POST"])
     app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
+    app.add_api_route("/ai/v1/rewrite", rewrite, methods=["POST"])
+    app.add_api_route("/ai/v1/extract", extract, methods=["POST"])
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
     app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
     app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])

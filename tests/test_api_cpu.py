@@ -217,3 +217,96 @@ def test_table_create_batch_and_hybrid_query(client, index_type):
     assert "k2" not in ids
     assert client.post("/db/v1/tables/missing/query", json={"full_text_search": "x"}).status_code == 404
     assert client.post(f"/db/v1/tables/{t}/query", json={"limit": 0}).status_code == 400
+
+
+def _write_bert(dirpath, num_labels, id2label, seed):
+    import torch
+
+    from antfly_b200.formats import safetensors_io as st
+    from antfly_b200.models.bert import BertConfig, BertModel
+
+    dirpath.mkdir(parents=True)
+    cfg = BertConfig(hidden_size=64, num_hidden_layers=1, num_attention_heads=4, intermediate_size=128, vocab_size=300,
+                     num_labels=num_labels)
+    m = BertModel.random_init(cfg, device="cpu", seed=seed)
+    m.w["cls.w"] = m.w["cls.w"] * 40.0                   # decisive heads: random init gives near-uniform labels
+    st.save_file(m.state_dict_hf(), str(dirpath / "model.safetensors"))
+    (dirpath / "config.json").write_text(json.dumps({
+        "model_type": "bert", "hidden_size": 64, "num_hidden_layers": 1, "num_attention_heads": 4,
+        "intermediate_size": 128, "vocab_size": 300, "max_position_embeddings": 512, "num_labels": num_labels,
+        "id2label": {str(i): l for i, l in enumerate(id2label)}}))
+
+
+def _write_t5(dirpath):
+    import torch
+
+    from antfly_b200.formats import safetensors_io as st
+
+    dirpath.mkdir(parents=True)
+    g = torch.Generator().manual_seed(0)
+    sd = {"shared.weight": torch.randn(300, 64, generator=g)}
+    for stack, ff in (("encoder", 1), ("decoder", 2)):
+        for l in range(2):
+            s = f"{stack}.block.{l}.layer."
+            for n in "qkvo":
+                sd[s + f"0.SelfAttention.{n}.weight"] = torch.randn(64, 64, generator=g) * 0.2
+                if stack == "decoder":
+                    sd[s + f"1.EncDecAttention.{n}.weight"] = torch.randn(64, 64, generator=g) * 0.2
+            sd[s + "0.layer_norm.weight"] = torch.ones(64)
+            if stack == "decoder":
+                sd[s + "1.layer_norm.weight"] = torch.ones(64)
+            sd[s + f"{ff}.DenseReluDense.wi.weight"] = torch.randn(128, 64, generator=g) * 0.2
+            sd[s + f"{ff}.DenseReluDense.wo.weight"] = torch.randn(64, 128, generator=g) * 0.2
+            sd[s + f"{ff}.layer_norm.weight"] = torch.ones(64)
+        sd[f"{stack}.block.0.layer.0.SelfAttention.relative_attention_bias.weight"] = torch.randn(8, 4, generator=g)
+        sd[f"{stack}.final_layer_norm.weight"] = torch.ones(64)
+    st.save_file({k: v.contiguous() for k, v in sd.items()}, str(dirpath / "model.safetensors"))
+    (dirpath / "config.json").write_text(json.dumps({
+        "model_type": "t5", "vocab_size": 300, "d_model": 64, "d_kv": 16, "d_ff": 128, "num_layers": 2,
+        "num_heads": 4, "relative_attention_num_buckets": 8, "relative_attention_max_distance": 20,
+        "feed_forward_proj": "relu", "eos_token_id": 2, "decoder_start_token_id": 0}))
+
+
+def test_rewrite_and_extract_endpoints(tmp_path):
+    _write_t5(tmp_path / "rewriters" / "tiny-t5")
+    _write_bert(tmp_path / "recognizers" / "tiny-ner", 5, ["O", "B-PER", "I-PER", "B-LOC", "I-LOC"], 1)
+    _write_bert(tmp_path / "classifiers" / "tiny-clf", 3, ["negative", "neutral", "positive"], 2)
+    c = TestClient(create_app(ModelManager(models_dir=str(tmp_path), device="cpu")))
+    # rewrite: one object per input, usage accounting, greedy = deterministic
+    r = c.post("/ai/v1/rewrite", json={"model": "tiny-t5", "inputs": ["translate: hello", "paraphrase: cats"],
+                                      "max_tokens": 8})
+    body = r.json()
+    assert r.status_code == 200 and body["object"] == "list" and body["model"] == "tiny-t5"
+    assert [d["index"] for d in body["data"]] == [0, 1] and all(d["object"] == "rewrite" and len(d["texts"]) == 1
+                                                               for d in body["data"])
+    u = body["usage"]
+    assert u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"] and 0 < u["completion_tokens"] <= 16
+    assert c.post("/ai/v1/rewrite", json={"model": "tiny-t5", "inputs": ["translate: hello"],
+                                         "max_tokens": 8}).json()["data"][0]["texts"] == body["data"][0]["texts"]
+    assert c.post("/ai/v1/rewrite", json={"model": "nope", "inputs": ["x"]}).status_code == 404
+    # extract: entities restricted to the schema's labels, spans index the input text, classifications per task
+    text = "alice met bob in paris and then flew to rome"
+    r = c.post("/ai/v1/extract", json={"model": "tiny-ner", "inputs": [{"id": "d1", "content": text}],
+                                      "schema": {"entities": ["PER", "LOC"]}})
+    body = r.json()
+    assert r.status_code == 200 and body["object"] == "extraction" and body["data"][0]["id"] == "d1"
+    ents = body["data"][0]["entities"]
+    assert ents and all(e["label"] in ("PER", "LOC") and 0 <= e["score"] <= 1 for e in ents)
+    assert all(text[e["start"]:e["end"]] == e["text"] for e in ents if "start" in e)
+    only = c.post("/ai/v1/extract", json={"model": "tiny-ner", "inputs": [{"content": text}],
+                                         "schema": {"entities": ["LOC"]}}).json()["data"][0]["entities"]
+    assert all(e["label"] == "LOC" for e in only) and len(only) <= len(ents)
+    hi = c.post("/ai/v1/extract", json={"model": "tiny-ner", "inputs": [{"content": text}],
+                                       "schema": {"entities": ["PER", "LOC"]}, "options": {"threshold": 1.1}})
+    assert hi.json()["data"][0]["entities"] == []
+    r = c.post("/ai/v1/extract", json={"model": "tiny-clf", "inputs": [{"content": "great movie"},
+                                                                      {"content": [{"type": "text", "text": "bad"}]}],
+                                      "schema": {"classifications": [{"name": "sentiment",
+                                                                      "labels": ["negative", "positive"]}]}})
+    cls = [d["classifications"] for d in r.json()["data"]]
+    assert r.status_code == 200 and all(len(x) == 1 and x[0]["name"] == "sentiment" and
+                                        x[0]["label"] in ("negative", "positive") for x in cls)
+    assert c.post("/ai/v1/extract", json={"model": "tiny-clf", "inputs": [{"content": "x"}], "schema": {
+        "classifications": [{"name": "t", "labels": ["sarcastic"]}]}}).status_code == 400
+    assert c.post("/ai/v1/extract", json={"model": "tiny-clf", "inputs": [{"content": "x"}],
+                                         "schema": {}}).status_code == 400
