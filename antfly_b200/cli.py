@@ -1,6 +1,9 @@
 """Command line: ``python -m antfly_b200 <command>`` (the reference's ``antfly inference {run, embed, generate,
 ...}``, zig/pkg/inference/src/main.zig:92-157; generate / embed flags follow native_generate.zig / native_embed.zig).
 
+  export    safetensors checkpoint -> GGUF    --in DIR --out FILE --quant f32|f16|q8_0|q4_0
+  classify / recognize / rewrite            --model NAME --text ...
+  compare   embedder parity across devices    --model NAME --text ... --device-a cpu --device-b cuda
   run       start the HTTP server            --host --port --models-dir --preload task:name[:size]
   embed     embed texts                      --model --text ... [--dimensions N] [--print-timing]
   rerank    score documents against a query  --model --query Q --doc ... 
@@ -167,6 +170,68 @@ def cmd_quantize(args) -> int:
     return 0
 
 
+def cmd_export(args) -> int:
+    """Export a Llama-family safetensors checkpoint directory as one GGUF file (f32 / f16 / q8_0 / q4_0)."""
+    import os
+
+    from .formats import gguf as GG
+    from .formats import manifest as MF
+    from .formats import safetensors_io as ST
+
+    mf = MF.read_manifest(args.inp)
+    counts = GG.export_llama_gguf(args.out, ST.load_model_dir(args.inp), mf.config, args.quant)
+    print(json.dumps({"out": args.out, "bytes": os.path.getsize(args.out), "tensor_types": counts}))
+    return 0
+
+
+def cmd_classify(args) -> int:
+    lm = _manager(args).get(args.model, "classifier")
+    for text, ranked in zip(args.text, lm.pipeline.classify(args.text, top_k=args.top_k)):
+        print(json.dumps({"text": text, "labels": ranked}))
+    return 0
+
+
+def cmd_recognize(args) -> int:
+    lm = _manager(args).get(args.model, "recognizer")
+    for text, ents in zip(args.text, lm.pipeline.entities(args.text)):
+        print(json.dumps({"text": text, "entities": [
+            {"label": e.label, "text": e.text, "score": round(e.score, 4), "start_token": e.start_token,
+             "end_token": e.end_token} for e in ents]}))
+    return 0
+
+
+def cmd_rewrite(args) -> int:
+    from .runtime.sampling_params import SamplingParams
+
+    lm = _manager(args).get(args.model, "rewriter")
+    for text in args.text:
+        out = lm.pipeline.generate(text, SamplingParams(max_tokens=args.max_tokens), raw_prompt=True)
+        print(json.dumps({"input": text, "text": out.text, "tokens": out.completion_tokens}))
+        if args.print_timing:
+            print(out.timing_line(), file=sys.stderr)
+    return 0
+
+
+def cmd_compare(args) -> int:
+    """Run the same embedder on two devices (by default the CPU oracle path and the GPU kernels) and report how far
+    the embeddings are apart: the parity check a deployment runs after changing hardware or build."""
+    import torch
+
+    from .api.model_manager import ModelManager
+
+    devs = [args.device_a, args.device_b or ("cuda" if torch.cuda.is_available() else "cpu")]
+    embs = []
+    for d in devs:
+        mgr = ModelManager(models_dir=args.models_dir, device=d)
+        lm = _get(mgr, args.model, "embedder")
+        embs.append(lm.pipeline.embed(args.text)[0].float().cpu())
+    cos = torch.nn.functional.cosine_similarity(embs[0], embs[1], dim=-1)
+    rep = {"model": args.model, "devices": devs, "texts": len(args.text), "min_cosine": float(cos.min()),
+           "max_abs_diff": float((embs[0] - embs[1]).abs().max())}
+    print(json.dumps(rep))
+    return 0 if rep["min_cosine"] >= args.min_cosine else 1
+
+
 def cmd_list(args) -> int:
     print(json.dumps(_manager(args).list_models(), indent=2))
     return 0
@@ -202,6 +267,24 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--host"); p.add_argument("--port", type=int)
     p.add_argument("--preload", nargs="*"); p.add_argument("--max-concurrent-requests", type=int)
     p.add_argument("--max-queue-size", type=int); p.set_defaults(fn=cmd_run)
+    p = sub.add_parser("export", help="safetensors checkpoint directory -> GGUF")
+    p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
+    p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "q8_0", "q4_0"]); p.set_defaults(fn=cmd_export)
+    p = sub.add_parser("classify"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--top-k", type=int, default=1); p.set_defaults(fn=cmd_classify)
+    p = sub.add_parser("recognize"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.set_defaults(fn=cmd_recognize)
+    p = sub.add_parser("rewrite"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--max-tokens", type=int, default=128); p.add_argument("--print-timing", action="store_true")
+    p.set_defaults(fn=cmd_rewrite)
+    p = sub.add_parser("compare", help="same embedder on two devices: embedding parity report")
+    p.add_argument("--models-dir"); p.add_argument("--model", required=True)
+    p.add_argument("--text", nargs="+", required=True); p.add_argument("--device-a", default="cpu")
+    p.add_argument("--device-b"); p.add_argument("--min-cosine", type=float, default=0.99)
+    p.set_defaults(fn=cmd_compare)
     p = sub.add_parser("embed"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
     p.add_argument("--dimensions", type=int); p.add_argument("--print-timing", action="store_true")

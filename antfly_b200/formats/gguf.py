@@ -8,7 +8,7 @@ import ctypes
 import mmap
 import struct
 from dataclasses import dataclass
-from typing import Any, Dict, List, Tuple
+from typing import Optional, Any, Dict, List, Tuple
 
 import numpy as np
 import torch
@@ -131,6 +131,50 @@ def hf_name(gguf_name: str) -> str:
     if parts[0] == "blk" and len(parts) >= 4 and parts[2] in _LAYER:
         return f"model.layers.{parts[1]}.{_LAYER[parts[2]]}.{parts[3]}"
     return gguf_name
+
+
+def gguf_name(hf: str) -> str:
+    """Inverse of :func:`hf_name` for the Llama-family tensor names."""
+    for g, h in _GGUF_TO_HF.items():
+        if h == hf:
+            return g
+    parts = hf.split(".")
+    if len(parts) >= 6 and parts[0] == "model" and parts[1] == "layers":
+        mid = ".".join(parts[3:-1])
+        for g, h in _LAYER.items():
+            if h == mid:
+                return f"blk.{parts[2]}.{g}.{parts[-1]}"
+    return hf
+
+
+def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quant: str = "q8_0",
+                      tokens: Optional[List[str]] = None) -> Dict[str, int]:
+    """Write a Llama-family Hugging Face state dict as a GGUF v3 file: 2-D projection weights in ``quant`` (f32,
+    f16, q8_0, q4_0), norms and embeddings in f32 / f16; metadata keys are the ones :func:`llama_config_from_gguf`
+    reads back.  Returns {tensor type id: count}."""
+    ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8}[quant.lower()]
+    arch = config.get("model_type", "llama")
+    md = {"general.architecture": arch, "general.name": str(config.get("_name_or_path", "model")),
+          f"{arch}.block_count": int(config["num_hidden_layers"]),
+          f"{arch}.embedding_length": int(config["hidden_size"]),
+          f"{arch}.feed_forward_length": int(config["intermediate_size"]),
+          f"{arch}.attention.head_count": int(config["num_attention_heads"]),
+          f"{arch}.attention.head_count_kv": int(config.get("num_key_value_heads", config["num_attention_heads"])),
+          f"{arch}.rope.freq_base": float(config.get("rope_theta", 10000.0)),
+          f"{arch}.attention.layer_norm_rms_epsilon": float(config.get("rms_norm_eps", 1e-5)),
+          f"{arch}.vocab_size": int(config["vocab_size"])}
+    if tokens:
+        md["tokenizer.ggml.tokens"] = list(tokens)
+    tensors, counts = {}, {}
+    for name, t in sd.items():
+        if not isinstance(t, torch.Tensor) or not t.is_floating_point():
+            continue
+        quantisable = t.dim() == 2 and t.shape[1] % 32 == 0 and "embed_tokens" not in name and "norm" not in name
+        tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 else 0)
+        tensors[gguf_name(name)] = (tt, t.float())
+        counts[tt] = counts.get(tt, 0) + 1
+    write_gguf(path, md, tensors)
+    return counts
 
 
 def llama_config_from_gguf(md: Dict[str, Any]) -> dict:

@@ -229,7 +229,8 @@ def _write_bert(dirpath, num_labels, id2label, seed):
     cfg = BertConfig(hidden_size=64, num_hidden_layers=1, num_attention_heads=4, intermediate_size=128, vocab_size=300,
                      num_labels=num_labels)
     m = BertModel.random_init(cfg, device="cpu", seed=seed)
-    m.w["cls.w"] = m.w["cls.w"] * 40.0                   # decisive heads: random init gives near-uniform labels
+    if num_labels:
+        m.w["cls.w"] = m.w["cls.w"] * 40.0               # decisive heads: random init gives near-uniform labels
     st.save_file(m.state_dict_hf(), str(dirpath / "model.safetensors"))
     (dirpath / "config.json").write_text(json.dumps({
         "model_type": "bert", "hidden_size": 64, "num_hidden_layers": 1, "num_attention_heads": 4,

@@ -18,3 +18,64 @@ def test_cli_embed_rerank_generate_list(capsys, tmp_path):
     assert "generate_timing_ms:" in cap.err and "speculative: rounds=" in cap.err and "finish_reason:" in cap.err
     assert main(["list", "--models-dir", str(tmp_path)]) == 0
     assert "chunkers" in capsys.readouterr().out
+
+
+def test_cli_export_gguf_roundtrip_and_task_commands(capsys, tmp_path):
+    """safetensors -> GGUF (q8_0) -> loaded again by the GGUF reader with HF names; classify / recognize / rewrite /
+    compare subcommands over model directories."""
+    import torch
+
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.formats import safetensors_io as st
+    from tests.test_api_cpu import _write_bert, _write_t5
+
+    src = tmp_path / "generators" / "tiny-llama"
+    src.mkdir(parents=True)
+    H, F, V, L = 64, 128, 96, 2
+    g = torch.Generator().manual_seed(0)
+    sd = {"model.embed_tokens.weight": torch.randn(V, H, generator=g), "model.norm.weight": torch.ones(H),
+          "lm_head.weight": torch.randn(V, H, generator=g)}
+    for l in range(L):
+        p = f"model.layers.{l}."
+        for n, (o, i) in {"self_attn.q_proj": (H, H), "self_attn.k_proj": (32, H), "self_attn.v_proj": (32, H),
+                          "self_attn.o_proj": (H, H), "mlp.gate_proj": (F, H), "mlp.up_proj": (F, H),
+                          "mlp.down_proj": (H, F)}.items():
+            sd[p + n + ".weight"] = torch.randn(o, i, generator=g) * 0.1
+        sd[p + "input_layernorm.weight"] = torch.ones(H)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(H)
+    st.save_file(sd, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({
+        "model_type": "llama", "hidden_size": H, "intermediate_size": F, "num_hidden_layers": L,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "vocab_size": V, "rope_theta": 500000.0,
+        "rms_norm_eps": 1e-5}))
+    out = tmp_path / "tiny.gguf"
+    assert main(["export", "--in", str(src), "--out", str(out), "--quant", "q8_0"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["tensor_types"] == {"8": 15, "1": 1, "0": 5}      # projections + lm_head q8_0, embedding f16, norms f32
+    f = GG.GGUFFile(str(out))
+    cfg = GG.llama_config_from_gguf(f.metadata)
+    assert cfg["num_hidden_layers"] == L and cfg["num_key_value_heads"] == 2 and cfg["rope_theta"] == 500000.0
+    assert cfg["vocab_size"] == V
+    back = {GG.hf_name(n): f.tensor(n) for n in f.tensors}
+    assert set(back) == set(sd)
+    for n, t in sd.items():
+        tol = 0.02 * float(t.abs().max()) if t.dim() == 2 else 0.0
+        assert float((back[n] - t).abs().max()) <= tol + 1e-3, n
+
+    _write_bert(tmp_path / "classifiers" / "clf", 3, ["negative", "neutral", "positive"], 2)
+    _write_bert(tmp_path / "recognizers" / "ner", 3, ["O", "B-PER", "I-PER"], 1)
+    _write_bert(tmp_path / "embedders" / "emb", 0, [], 3)
+    _write_t5(tmp_path / "rewriters" / "t5")
+    md = ["--models-dir", str(tmp_path), "--device", "cpu"]
+    assert main(["classify", *md, "--model", "clf", "--text", "good", "bad", "--top-k", "2"]) == 0
+    rows = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert len(rows) == 2 and len(rows[0]["labels"]) == 2 and rows[0]["labels"][0]["score"] >= rows[0]["labels"][1]["score"]
+    assert main(["recognize", *md, "--model", "ner", "--text", "alice went home"]) == 0
+    assert "entities" in json.loads(capsys.readouterr().out)
+    assert main(["rewrite", *md, "--model", "t5", "--text", "paraphrase: hi", "--max-tokens", "5",
+                 "--print-timing"]) == 0
+    cap = capsys.readouterr()
+    assert json.loads(cap.out)["tokens"] <= 5 and "generate_timing_ms:" in cap.err
+    assert main(["compare", "--models-dir", str(tmp_path), "--model", "emb", "--text", "a b c", "hello",
+                 "--device-a", "cpu", "--device-b", "cpu"]) == 0
+    assert json.loads(capsys.readouterr().out)["min_cosine"] > 0.9999
