@@ -278,6 +278,11 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         req, bad = await parse(request, S.GenerateRequest)
         if bad:
             return bad
+        return await generate_from(req)
+
+    async def generate_from(req: S.GenerateRequest, framer=None):
+        """Runs one chat / generate request.  ``framer`` (None = the OpenAI-style wire format) turns the result, or
+        the stream of deltas, into another API's wire format."""
         if not req.messages:
             return _err(400, "invalid_request", "messages must not be empty")
         if req.max_tokens <= 0:
@@ -329,11 +334,12 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     content, calls = TC.parse_tool_calls(out.text, tool_fmt)
                     if calls:
                         message, finish = S.GenerateMessage(content=content or None, tool_calls=calls), "tool_calls"
-                return S.GenerateResponse(
+                resp = S.GenerateResponse(
                     id=rid, created=created, model=req.model,
                     choices=[S.GenerateChoice(message=message, finish_reason=finish)],
                     usage=S.GenerateUsage(prompt_tokens=out.prompt_tokens, completion_tokens=out.completion_tokens,
                                           total_tokens=out.prompt_tokens + out.completion_tokens)).model_dump()
+                return framer.response(resp) if framer is not None else resp
 
             return await asyncio.to_thread(run_guarded, "generate", 1, work)
 
@@ -346,10 +352,27 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
             return "data: " + json.dumps(body) + "\n\n"
 
+        if framer is not None:
+            framer.begin(rid, req.model)
+
+        def emit_start():
+            return framer.start() if framer is not None else chunk({"role": "assistant"})
+
+        def emit_text(t: str):
+            return framer.text(t) if framer is not None else chunk({"content": t})
+
+        def emit_calls(calls):
+            return framer.tool_calls(calls) if framer is not None else chunk(
+                {"tool_calls": [dict(c, index=i) for i, c in enumerate(calls)]})
+
+        def emit_finish(reason, out):
+            return framer.finish(reason, out.prompt_tokens, out.completion_tokens) if framer is not None else \
+                chunk({}, reason)
+
         def worker():
             def work():
                 lm = mgr.get(req.model, "generator")
-                loop.call_soon_threadsafe(q.put_nowait, chunk({"role": "assistant"}))
+                loop.call_soon_threadsafe(q.put_nowait, emit_start())
                 parser = None
                 if tool_fmt is not None:
                     from ..pipelines import tool_calls as TC
@@ -359,22 +382,23 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 def on_delta(d: str):
                     shown = parser.feed(d) if parser is not None else d
                     if shown:
-                        loop.call_soon_threadsafe(q.put_nowait, chunk({"content": shown}))
+                        loop.call_soon_threadsafe(q.put_nowait, emit_text(shown))
 
                 out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer), on_delta=on_delta)
                 finish = out.finish_reason
                 if parser is not None:
                     _, calls = parser.finish()
                     if calls:
-                        deltas = [dict(c, index=i) for i, c in enumerate(calls)]
-                        loop.call_soon_threadsafe(q.put_nowait, chunk({"tool_calls": deltas}))
+                        loop.call_soon_threadsafe(q.put_nowait, emit_calls(calls))
                         finish = "tool_calls"
-                loop.call_soon_threadsafe(q.put_nowait, chunk({}, finish))
+                loop.call_soon_threadsafe(q.put_nowait, emit_finish(finish, out))
                 return None
 
             res = run_guarded("generate", 1, work)
             if isinstance(res, JSONResponse):
-                loop.call_soon_threadsafe(q.put_nowait, "data: " + res.body.decode() + "\n\n")
+                err = res.body.decode()
+                loop.call_soon_threadsafe(q.put_nowait, framer.error(err) if framer is not None
+                                          else "data: " + err + "\n\n")
             loop.call_soon_threadsafe(q.put_nowait, None)
 
         threading.Thread(target=worker, daemon=True).start()
@@ -385,9 +409,35 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 if item is None:
                     break
                 yield item
-            yield "data: [DONE]\n\n"
+            if framer is None:
+                yield "data: [DONE]\n\n"
 
         return StreamingResponse(gen(), media_type="text/event-stream")
+
+    # ---- Anthropic Messages and OpenAI path compatibility -----------------------------------------------------
+    async def anthropic_messages(request: Request):
+        from .compat import AnthropicFramer, anthropic_to_generate
+
+        try:
+            body = json.loads(await request.body() or b"{}")
+            greq = S.GenerateRequest(**anthropic_to_generate(body))
+        except Exception as e:
+            return JSONResponse(status_code=400, content={"type": "error", "error": {
+                "type": "invalid_request_error", "message": str(e)}})
+        res = await generate_from(greq, AnthropicFramer())
+        if isinstance(res, JSONResponse) and res.status_code >= 400:
+            err = json.loads(res.body)
+            kind = {404: "not_found_error", 503: "overloaded_error", 504: "overloaded_error"}.get(
+                res.status_code, "invalid_request_error" if res.status_code < 500 else "api_error")
+            return JSONResponse(status_code=res.status_code, content={"type": "error", "error": {
+                "type": kind, "message": err.get("message", "")}})
+        return res
+
+    async def openai_models():
+        per_task = mgr.list_models()
+        now = int(time.time())
+        return {"object": "list", "data": [{"id": n, "object": "model", "created": now, "owned_by": "antfly"}
+                                           for t in ("generators", "embedders") for n in per_task.get(t, {})]}
 
     # ---- chunk ----------------------------------------------------------------------------------------
     async def chunk_ep(request: Request):
@@ -652,6 +702,10 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/ai/v1/rerank", rerank, methods=["POST"])
     for path in ("/ai/v1/generate", "/ai/v1/chat/completions"):
         app.add_api_route(path, generate, methods=["POST"])
+    app.add_api_route("/openai/v1/chat/completions", generate, methods=["POST"])
+    app.add_api_route("/openai/v1/embeddings", embed, methods=["POST"])
+    app.add_api_route("/openai/v1/models", openai_models, methods=["GET"])
+    app.add_api_route("/anthropic/v1/messages", anthropic_messages, methods=["POST"])
     app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
     app.add_api_route("/ai/v1/rewrite", rewrite, methods=["POST"])
     app.add_api_route("/ai/v1/extract", extract, methods=["POST"])

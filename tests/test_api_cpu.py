@@ -311,3 +311,60 @@ def test_rewrite_and_extract_endpoints(tmp_path):
         "classifications": [{"name": "t", "labels": ["sarcastic"]}]}}).status_code == 400
     assert c.post("/ai/v1/extract", json={"model": "tiny-clf", "inputs": [{"content": "x"}],
                                          "schema": {}}).status_code == 400
+
+
+def test_anthropic_messages_and_openai_path_compat(client):
+    """Messages-API wire format over the native generate handler (request translation, content blocks, stop reasons,
+    usage, named streaming events, error envelope) and the /openai/v1 path aliases."""
+    from antfly_b200.api.compat import anthropic_to_generate
+
+    body = {"model": "tiny-gen", "max_tokens": 6, "system": [{"type": "text", "text": "be brief"}],
+            "messages": [{"role": "user", "content": [{"type": "text", "text": "hi there"}]}], "temperature": 0}
+    g = anthropic_to_generate(body)
+    assert g["messages"][0] == {"role": "system", "content": "be brief"} and g["messages"][1]["content"] == "hi there"
+    t = anthropic_to_generate({"model": "m", "max_tokens": 5, "messages": [
+        {"role": "user", "content": "weather?"},
+        {"role": "assistant", "content": [{"type": "tool_use", "id": "toolu_1", "name": "get", "input": {"c": "x"}}]},
+        {"role": "user", "content": [{"type": "tool_result", "tool_use_id": "toolu_1", "content": "sunny"}]}],
+        "tools": [{"name": "get", "description": "d", "input_schema": {"type": "object"}}],
+        "tool_choice": {"type": "any"}, "stop_sequences": ["END"]})
+    assert [m["role"] for m in t["messages"]] == ["user", "assistant", "tool"]
+    assert t["messages"][1]["tool_calls"][0]["function"] == {"name": "get", "arguments": '{"c": "x"}'}
+    assert t["messages"][2] == {"role": "tool", "tool_call_id": "toolu_1", "content": "sunny"}
+    assert t["tools"][0]["function"]["name"] == "get" and t["tool_choice"] == "required" and t["stop"] == ["END"]
+
+    r = client.post("/anthropic/v1/messages", json=body)
+    m = r.json()
+    assert r.status_code == 200 and m["type"] == "message" and m["role"] == "assistant" and m["model"] == "tiny-gen"
+    assert m["id"].startswith("msg_") and m["stop_reason"] in ("max_tokens", "end_turn") and m["stop_sequence"] is None
+    assert m["usage"]["input_tokens"] > 0 and 0 < m["usage"]["output_tokens"] <= 6
+    assert all(b["type"] == "text" for b in m["content"])
+    # same tokens as the native endpoint (greedy)
+    n = client.post("/ai/v1/generate", json={"model": "tiny-gen", "max_tokens": 6, "temperature": 0, "messages": [
+        {"role": "system", "content": "be brief"}, {"role": "user", "content": "hi there"}]}).json()
+    assert (m["content"][0]["text"] if m["content"] else None) == n["choices"][0]["message"]["content"]
+    # streaming: named events in order, text deltas concatenate to the non-streamed text
+    with client.stream("POST", "/anthropic/v1/messages", json={**body, "stream": True}) as s:
+        raw = "".join(s.iter_text())
+    events = [blk.split("\n") for blk in raw.strip().split("\n\n")]
+    names = [e[0].split(": ", 1)[1] for e in events]
+    assert names[0] == "message_start" and names[-2:] == ["message_delta", "message_stop"] and "[DONE]" not in raw
+    datas = [json.loads(e[1].split(": ", 1)[1]) for e in events]
+    text = "".join(d["delta"]["text"] for d in datas if d["type"] == "content_block_delta")
+    assert text == (m["content"][0]["text"] if m["content"] else "")
+    if text:
+        assert names.count("content_block_start") == names.count("content_block_stop") == 1
+    md = datas[names.index("message_delta")]
+    assert md["delta"]["stop_reason"] == m["stop_reason"] and md["usage"]["output_tokens"] == m["usage"]["output_tokens"]
+    # errors use the Messages-API envelope
+    e = client.post("/anthropic/v1/messages", json={"model": "tiny-gen", "messages": [{"role": "user", "content": "x"}]})
+    assert e.status_code == 400 and e.json()["type"] == "error" and e.json()["error"]["type"] == "invalid_request_error"
+    e = client.post("/anthropic/v1/messages", json={**body, "model": "missing"})
+    assert e.status_code == 404 and e.json()["error"]["type"] == "not_found_error"
+    # OpenAI path aliases
+    o = client.post("/openai/v1/chat/completions", json={"model": "tiny-gen", "max_tokens": 4, "temperature": 0,
+                                                         "messages": [{"role": "user", "content": "hi"}]})
+    assert o.status_code == 200 and o.json()["object"] == "chat.completion"
+    ids = [x["id"] for x in client.get("/openai/v1/models").json()["data"]]
+    assert "tiny-gen" in ids and "tiny-embed" in ids
+    assert client.post("/openai/v1/embeddings", json={"model": "tiny-embed", "input": "x"}).status_code == 200
