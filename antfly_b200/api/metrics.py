@@ -13,6 +13,8 @@ class Metrics:
                                 ["endpoint", "status"], registry=r)
         self.latency = Histogram("antfly_inference_request_seconds", "Request latency", ["endpoint"], registry=r)
         self.tokens = Counter("antfly_inference_tokens_total", "Tokens processed", ["endpoint", "kind"], registry=r)
+        self.cache = Counter("antfly_inference_result_cache_total", "Result-cache lookups by endpoint and outcome",
+                             ["endpoint", "outcome"], registry=r)
         self.queue_depth = Gauge("antfly_inference_queue_depth", "Requests waiting for a slot", registry=r)
         self.queue_rejected = Counter("antfly_inference_queue_rejected_total", "Requests refused with 503", registry=r)
         self.loaded_models = Gauge("antfly_inference_loaded_models", "Models resident in GPU memory", registry=r)

@@ -29,6 +29,7 @@ from ..pipelines.embedding import INPUT_TYPE_ALIASES
 from ..runtime.sampling_params import SamplingParams
 from ..runtime.scheduler import QueueFull
 from . import schemas as S
+from .cache import ResultCache
 from .metrics import Metrics
 from .model_manager import ModelManager, ModelNotFound
 
@@ -104,11 +105,13 @@ def _err(status: int, code: str, message: str) -> JSONResponse:
 
 def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
                max_concurrent_requests: int = 64, max_queue_size: int = 256,
-               request_timeout_s: float = 0.0) -> FastAPI:
+               request_timeout_s: float = 0.0, result_cache_ttl_s: float = 120.0) -> FastAPI:
     app = FastAPI(title="antfly-b200 inference", version="0.1")
     mgr = manager or ModelManager()
     metrics = Metrics()
     queue = RequestQueue(max_concurrent_requests, max_queue_size)
+    cache = ResultCache(result_cache_ttl_s)
+    app.state.result_cache = cache
     gpu_lock = threading.Lock()  # one request drives the device at a time; batching happens inside pipelines
     app.state.manager, app.state.metrics, app.state.queue = mgr, metrics, queue
     app.state.indexes = indexes if indexes is not None else {}
@@ -207,7 +210,27 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                         rows.append(temb[ti]); ti += 1
                 emb = _torch.stack(rows)
             else:
-                emb, ntok = lm.pipeline.embed(texts, task_type, req.dimensions)
+                # per-text result cache: only texts not seen in the last two minutes reach the model
+                import torch as _torch
+
+                keys = [cache.key("embed", req.model, task_type, req.dimensions, t) for t in texts]
+                got = [cache.get(k) for k in keys]             # (embedding row, prompt tokens of that text)
+                todo = [i for i, r in enumerate(got) if r is None]
+                if todo:
+                    pipe, sub = lm.pipeline, [texts[i] for i in todo]
+                    if hasattr(pipe, "tokenize") and hasattr(pipe, "embed_ids"):
+                        seqs = pipe.tokenize(sub, task_type)
+                        new, counts = pipe.embed_ids(seqs, req.dimensions), [len(q) for q in seqs]
+                    else:
+                        new, total = pipe.embed(sub, task_type, req.dimensions)
+                        counts = [total // len(sub) + (1 if j < total % len(sub) else 0) for j in range(len(sub))]
+                    for i, row, c in zip(todo, new, counts):
+                        got[i] = (row.clone(), c)
+                        cache.put(keys[i], got[i])
+                metrics.cache.labels("embed", "hit").inc(len(texts) - len(todo))
+                metrics.cache.labels("embed", "miss").inc(len(todo))
+                emb = _torch.stack([g[0] for g in got])
+                ntok = sum(g[1] for g in got)                  # usage counts every text, cached or not
             metrics.tokens.labels("embed", "prompt").inc(ntok)
             data = [S.EmbeddingObject(embedding=row.tolist(), index=i) for i, row in enumerate(emb)]
             return S.EmbedResponse(data=data, model=req.model,
@@ -225,7 +248,17 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         def work():
             lm = mgr.get(req.model, "reranker")
-            scores, ntok = lm.pipeline.rerank(req.query, req.prompts)
+            keys = [cache.key("rerank", req.model, req.query, d) for d in req.prompts]
+            got = [cache.get(k) for k in keys]                 # (score, prompt tokens of that pair)
+            todo = [i for i, v in enumerate(got) if v is None]
+            if todo:
+                new, total = lm.pipeline.rerank(req.query, [req.prompts[i] for i in todo])
+                for j, (i, v) in enumerate(zip(todo, new)):
+                    got[i] = (float(v), total // len(todo) + (1 if j < total % len(todo) else 0))
+                    cache.put(keys[i], got[i])
+            metrics.cache.labels("rerank", "hit").inc(len(got) - len(todo))
+            metrics.cache.labels("rerank", "miss").inc(len(todo))
+            scores, ntok = [g[0] for g in got], sum(g[1] for g in got)
             metrics.tokens.labels("rerank", "prompt").inc(ntok)
             return S.RerankResponse(
                 data=[S.RerankObject(index=i, score=float(s)) for i, s in enumerate(scores)], model=req.model,

@@ -368,3 +368,36 @@ def test_anthropic_messages_and_openai_path_compat(client):
     ids = [x["id"] for x in client.get("/openai/v1/models").json()["data"]]
     assert "tiny-gen" in ids and "tiny-embed" in ids
     assert client.post("/openai/v1/embeddings", json={"model": "tiny-embed", "input": "x"}).status_code == 200
+
+
+def test_result_cache_serves_repeated_texts_and_expires():
+    from antfly_b200.api.cache import ResultCache
+
+    now = [0.0]
+    c = ResultCache(ttl_s=120, max_entries=3, clock=lambda: now[0])
+    k = ResultCache.key("embed", "m", None, None, "text")
+    assert k != ResultCache.key("embed", "m", None, None, "text ") and c.get(k) is None
+    c.put(k, [1.0])
+    now[0] = 119
+    assert c.get(k) == [1.0]
+    now[0] = 121
+    assert c.get(k) is None and len(c) == 0 and (c.hits, c.misses) == (1, 2)
+    for i in range(5):
+        c.put(i, i)
+    assert len(c) == 3 and c.get(0) is None and c.get(4) == 4          # bounded, oldest evicted
+
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register_random("e", "embedder")
+    mgr.register_random("r", "reranker")
+    cl = TestClient(create_app(mgr))
+    a = cl.post("/ai/v1/embed", json={"model": "e", "input": ["alpha", "beta"]}).json()
+    b = cl.post("/ai/v1/embed", json={"model": "e", "input": ["beta", "gamma", "alpha"]}).json()
+    assert b["data"][0]["embedding"] == a["data"][1]["embedding"] and b["data"][2]["embedding"] == a["data"][0]["embedding"]
+    assert b["usage"]["prompt_tokens"] > a["usage"]["prompt_tokens"]     # usage counts cached texts too
+    s1 = cl.post("/ai/v1/rerank", json={"model": "r", "query": "q", "prompts": ["x", "y"]}).json()
+    s2 = cl.post("/ai/v1/rerank", json={"model": "r", "query": "q", "prompts": ["y", "x"]}).json()
+    assert s2["data"][0]["score"] == s1["data"][1]["score"]
+    assert s2["usage"]["prompt_tokens"] == s1["usage"]["prompt_tokens"]
+    m = cl.get("/metrics").text
+    assert 'antfly_inference_result_cache_total{endpoint="embed",outcome="hit"} 2.0' in m
+    assert 'antfly_inference_result_cache_total{endpoint="rerank",outcome="hit"} 2.0' in m
