@@ -1,4 +1,4 @@
-"""LayerNorm-based decoder family: GPT-2, GPT-NeoX / Pythia, OPT, GPT-J and Phi (1 / 1.5 / 2), on the same
+"""LayerNorm-based decoder family: GPT-2, GPT-Neo, GPT-NeoX / Pythia, OPT, GPT-J, Phi (1 / 1.5 / 2) and Falcon, on the same
 paged-KV engine interface as :class:`antfly_b200.models.llama.LlamaModel`.
 
 What differs from the Llama family and how it maps onto the existing kernels (the reference covers these under one
@@ -14,11 +14,16 @@ What differs from the Llama family and how it maps onto the existing kernels (th
   ("consecutive pairs") rotary embedding, and the biased LM head both of them carry.
 * fused QKV layouts: GPT-2's ``c_attn`` is a transposed ``Conv1D`` [in, 3 * out]; GPT-NeoX interleaves q, k, v per
   head; both are re-packed at load time into the [q heads | k heads | v heads] rows the kernels expect.
+* GPT-Neo: unscaled attention scores (softmax scale 1) and layers that alternate between global attention and a
+  256-token sliding window.
+* Falcon: multi-query (one shared K / V head) or grouped K / V heads, rotary positions, bias-free linears, the
+  parallel block with one shared LayerNorm (7B) or two (``new_decoder_architecture``), whose fused QKV rows are
+  grouped per K / V head and are regrouped at load time.  ALiBi variants are not supported.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -30,7 +35,7 @@ from .llama import StepBatch
 
 @dataclass
 class GptConfig:
-    family: str = "gpt2"              # gpt2 | gpt_neox | opt | gptj | phi
+    family: str = "gpt2"              # gpt2 | gpt_neo | gpt_neox | opt | gptj | phi | falcon
     vocab_size: int = 50257
     hidden_size: int = 768
     num_hidden_layers: int = 12
@@ -47,11 +52,14 @@ class GptConfig:
     sliding_window: int = 0
     shared_norm: bool = False         # GPT-J / Phi: one LayerNorm feeds both the attention and the MLP branch
     rope_half_split: bool = True      # False: GPT-J pairs (2i, 2i + 1) instead of (i, i + rot/2)
+    num_kv_heads: int = 0             # 0: one K / V head per query head; Falcon: 1 (multi-query) or a group count
+    attn_scale: float = 0.0           # 0: 1 / sqrt(head_dim); GPT-Neo: 1
+    layer_windows: Optional[List[int]] = None   # per-layer sliding window (0 = global); GPT-Neo's local layers
 
     # Names the engine reads from every decoder config.
     @property
     def num_key_value_heads(self) -> int:
-        return self.num_attention_heads
+        return self.num_kv_heads or self.num_attention_heads
 
     @property
     def head_dim(self) -> int:
@@ -100,6 +108,31 @@ class GptConfig:
                        d["intermediate_size"], d.get("max_position_embeddings", 2048), d.get("layer_norm_eps", 1e-5),
                        act[d.get("hidden_act", "gelu_new")], float(theta), float(pct), True,
                        tie_word_embeddings=False, shared_norm=True)
+        if mt == "gpt_neo":
+            H, L = d["hidden_size"], d.get("num_layers", d.get("num_hidden_layers"))
+            kinds = d.get("attention_layers")
+            if not kinds:
+                kinds = [k for pat, rep in d.get("attention_types", [[["global"], L]]) for _ in range(rep) for k in pat]
+            win = int(d.get("window_size", 256))
+            return cls("gpt_neo", d["vocab_size"], H, L, d.get("num_heads", d.get("num_attention_heads")),
+                       d.get("intermediate_size") or 4 * H, d.get("max_position_embeddings", 2048),
+                       d.get("layer_norm_epsilon", 1e-5), act[d.get("activation_function", "gelu_new")],
+                       tie_word_embeddings=d.get("tie_word_embeddings", True), attn_scale=1.0,
+                       layer_windows=[win if k == "local" else 0 for k in kinds[:L]])
+        if mt == "falcon":
+            if d.get("alibi"):
+                raise ValueError("Falcon checkpoints with ALiBi positions are not supported")
+            H, nh = d["hidden_size"], d["num_attention_heads"]
+            new = bool(d.get("new_decoder_architecture", False))
+            par = bool(d.get("parallel_attn", True)) or new
+            nkv = d.get("num_kv_heads") or nh if new else (1 if d.get("multi_query", True) else nh)
+            n_ln = d.get("num_ln_in_parallel_attn") or (2 if new else 1)
+            rp = d.get("rope_parameters") or {}
+            return cls("falcon", d["vocab_size"], H, d["num_hidden_layers"], nh, d.get("ffn_hidden_size") or 4 * H,
+                       d.get("max_position_embeddings", 2048), d.get("layer_norm_epsilon", 1e-5),
+                       act[d.get("activation", "gelu")], float(d.get("rope_theta") or rp.get("rope_theta") or 10000.0),
+                       1.0, par, tie_word_embeddings=d.get("tie_word_embeddings", True),
+                       shared_norm=par and n_ln == 1, num_kv_heads=int(nkv))
         raise ValueError(f"unsupported model_type {mt!r}")
 
 
@@ -115,7 +148,7 @@ class GptModel:
     def __init__(self, cfg: GptConfig, weights: Dict[str, torch.Tensor]):
         self.cfg, self.w = cfg, weights
         self.device = weights["embed"].device
-        self.Hq = self.Hkv = cfg.num_attention_heads
+        self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         self.D = cfg.head_dim
         self.n_layers = cfg.num_hidden_layers
         self.rope_dim = int(round(self.D * cfg.rotary_pct)) if cfg.rotary_pct > 0 else 0
@@ -206,6 +239,65 @@ class GptModel:
                 w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.fc2.weight"]), t(sd[s + "mlp.fc2.bias"])
             w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layernorm.weight"]), t(sd[pre + "final_layernorm.bias"])
             w["lm_head"], w["lm_head.b"] = t(sd["lm_head.weight"]), t(sd["lm_head.bias"])
+        elif cfg.family == "gpt_neo":
+            pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
+            w["embed"], w["pos"] = t(sd[pre + "wte.weight"]), t(sd[pre + "wpe.weight"])
+            zeros = lambda n: torch.zeros(n, dtype=dtype, device=device)
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}h.{l}.", f"l{l}."
+                a = s + "attn.attention."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "ln_1.weight"]), t(sd[s + "ln_1.bias"])
+                w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "ln_2.weight"]), t(sd[s + "ln_2.bias"])
+                w[p + "qkv.w"] = t(torch.cat([sd[a + f"{n}_proj.weight"] for n in ("q", "k", "v")], 0))
+                w[p + "qkv.b"] = zeros(3 * H)
+                w[p + "o.w"], w[p + "o.b"] = t(sd[a + "out_proj.weight"]), t(sd[a + "out_proj.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.c_fc.weight"]), t(sd[s + "mlp.c_fc.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.c_proj.weight"]), t(sd[s + "mlp.c_proj.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "ln_f.weight"]), t(sd[pre + "ln_f.bias"])
+            w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
+                w["embed"]
+        elif cfg.family == "falcon":
+            pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
+            nkv = cfg.num_key_value_heads
+            w["embed"] = t(sd[pre + "word_embeddings.weight"])
+            zeros = lambda n: torch.zeros(n, dtype=dtype, device=device)
+
+            def regroup(x: torch.Tensor) -> torch.Tensor:
+                """Fused QKV rows (or bias entries) -> [q heads | k heads | v heads]."""
+                tail = x.shape[1:]
+                if grouped:      # per K / V head: its query heads, then k, then v
+                    g = x.view(nkv, nh // nkv + 2, D, *tail)
+                    return torch.cat([g[:, :-2].reshape(nh * D, *tail), g[:, -2].reshape(nkv * D, *tail),
+                                      g[:, -1].reshape(nkv * D, *tail)], 0)
+                if nkv == 1:     # multi-query: already [q heads | k | v]
+                    return x
+                g = x.view(nh, 3, D, *tail)   # per head: q, k, v
+                return g.permute(1, 0, 2, *range(3, 3 + len(tail))).reshape(3 * nh * D, *tail)
+
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}h.{l}.", f"l{l}."
+                two_ln = s + "ln_attn.weight" in sd
+                grouped = two_ln or (nkv not in (1, nh))
+                if two_ln:
+                    w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "ln_attn.weight"]), t(sd[s + "ln_attn.bias"])
+                    w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "ln_mlp.weight"]), t(sd[s + "ln_mlp.bias"])
+                else:
+                    w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "input_layernorm.weight"]), t(sd[s + "input_layernorm.bias"])
+                    if s + "post_attention_layernorm.weight" in sd:
+                        w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "post_attention_layernorm.weight"]), t(
+                            sd[s + "post_attention_layernorm.bias"])
+                a = s + "self_attention."
+                w[p + "qkv.w"] = t(regroup(sd[a + "query_key_value.weight"]))
+                w[p + "qkv.b"] = t(regroup(sd[a + "query_key_value.bias"])) if a + "query_key_value.bias" in sd else \
+                    zeros((nh + 2 * nkv) * D)
+                w[p + "o.w"] = t(sd[a + "dense.weight"])
+                w[p + "o.b"] = t(sd[a + "dense.bias"]) if a + "dense.bias" in sd else zeros(H)
+                for ours, theirs, n in (("fc", "dense_h_to_4h", cfg.intermediate_size), ("proj", "dense_4h_to_h", H)):
+                    w[p + ours + ".w"] = t(sd[s + f"mlp.{theirs}.weight"])
+                    w[p + ours + ".b"] = t(sd[s + f"mlp.{theirs}.bias"]) if s + f"mlp.{theirs}.bias" in sd else zeros(n)
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "ln_f.weight"]), t(sd[pre + "ln_f.bias"])
+            w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
+                w["embed"]
         else:
             raise ValueError(cfg.family)
         return cls(cfg, w)
@@ -222,7 +314,8 @@ class GptModel:
             p = f"l{l}."
             for n in ("ln1", "ln2"):
                 w[p + n + ".g"], w[p + n + ".b"] = torch.ones(H, dtype=dtype, device=device), rnd(H)
-            w[p + "qkv.w"], w[p + "qkv.b"] = rnd(3 * H, H), rnd(3 * H)
+            nq = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+            w[p + "qkv.w"], w[p + "qkv.b"] = rnd(nq, H), rnd(nq)
             w[p + "o.w"], w[p + "o.b"] = rnd(H, H), rnd(H)
             w[p + "fc.w"], w[p + "fc.b"] = rnd(F, H), rnd(F)
             w[p + "proj.w"], w[p + "proj.b"] = rnd(H, F), rnd(H)
@@ -234,7 +327,8 @@ class GptModel:
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
         cfg, w = self.cfg, self.w
-        Hq, D, eps = self.Hq, self.D, cfg.layer_norm_eps
+        Hq, Hkv, D, eps = self.Hq, self.Hkv, self.D, cfg.layer_norm_eps
+        scale = cfg.attn_scale or None
         T = b.ids.numel()
         act = _ACT[cfg.activation]
         x = Dn.embed_gather(b.ids, w["embed"])
@@ -249,10 +343,11 @@ class GptModel:
             p = f"l{l}."
             h = Dn.norm(x, w[p + "ln1.g"], w[p + "ln1.b"], eps=eps, rms=False)
             qkv = Dn.gemm_bf16(h, w[p + "qkv.w"], bias=w[p + "qkv.b"])
-            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache[l], v_cache[l], Hq, Hq, D, cfg.rope_theta,
+            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 rope_dim=rope_dim, half_split=cfg.rope_half_split)
+            window = cfg.layer_windows[l] if cfg.layer_windows else cfg.sliding_window
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    b.max_q_len, scale=scale, window=window, num_splits=b.attn_splits,
                                     scratch=attn_scratch)
             if cfg.parallel_residual:
                 # x + attn(ln1 x) + mlp(ln2 x): both branches read the same x

@@ -176,13 +176,30 @@ def _hf_gpt(kind: str):
                                      num_attention_heads=4, max_position_embeddings=64, partial_rotary_factor=0.5,
                                      resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0)
         return cfg, transformers.PhiForCausalLM(cfg)
+    if kind == "gpt_neo":
+        cfg = transformers.GPTNeoConfig(vocab_size=300, hidden_size=64, num_layers=4, num_heads=4, intermediate_size=128,
+                                        max_position_embeddings=64, window_size=6,
+                                        attention_types=[[["global", "local"], 2]], resid_dropout=0.0,
+                                        embed_dropout=0.0, attention_dropout=0.0)
+        return cfg, transformers.GPTNeoForCausalLM(cfg)
+    if kind.startswith("falcon"):
+        kw = {"falcon_mq": dict(multi_query=True, parallel_attn=True, new_decoder_architecture=False),
+              "falcon_mha": dict(multi_query=False, parallel_attn=True, new_decoder_architecture=False),
+              "falcon_new": dict(new_decoder_architecture=True, num_kv_heads=2),
+              "falcon_seq": dict(multi_query=True, parallel_attn=False, new_decoder_architecture=False,
+                                 bias=True)}[kind]
+        cfg = transformers.FalconConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                        alibi=False, hidden_dropout=0.0, attention_dropout=0.0,
+                                        max_position_embeddings=64, **kw)
+        return cfg, transformers.FalconForCausalLM(cfg)
     cfg = transformers.OPTConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
                                  ffn_dim=128, max_position_embeddings=64, word_embed_proj_dim=64, dropout=0.0,
                                  attention_dropout=0.0)
     return cfg, transformers.OPTForCausalLM(cfg)
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt", "gptj", "phi"])
+@pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt", "gptj", "phi", "gpt_neo",
+                                  "falcon_mq", "falcon_mha", "falcon_new", "falcon_seq"])
 def test_layernorm_decoders_match_transformers(kind):
     from antfly_b200.models.gpt import GptConfig, GptModel
 
