@@ -138,6 +138,21 @@ class ModelManager:
                                     f"(found {cfg_d.get('model_type')!r})")
             model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
             pipe = Seq2SeqGenerator(model, tok)
+        elif task == "transcriber":
+            import json as _json
+
+            from ..models.whisper import WhisperConfig, WhisperModel
+            from ..pipelines.transcription import Transcriber
+
+            if cfg_d.get("model_type") != "whisper":
+                raise ModelNotFound(f"{name}: transcribers are Whisper models (found {cfg_d.get('model_type')!r})")
+            gen = {}
+            gp = os.path.join(path, "generation_config.json")
+            if os.path.exists(gp):
+                with open(gp, encoding="utf-8") as f:
+                    gen = _json.load(f)
+            model = WhisperModel.from_state_dict(WhisperConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = Transcriber(model, tok, gen)
         elif task in ("recognizer", "classifier"):
             from ..pipelines.classification import TextClassifier, TokenClassifier
 

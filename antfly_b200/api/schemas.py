@@ -220,3 +220,12 @@ class ExtractionRequest(BaseModel):
     inputs: List[ExtractionInput]
     schema_: Dict[str, Any] = Field(alias="schema")
     options: Dict[str, Any] = Field(default_factory=dict)
+
+
+class TranscribeRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    audio: str                          # base64-encoded WAV
+    language: Optional[str] = None
+    task: str = "transcribe"
+    max_tokens: int = Field(default=224, gt=0)

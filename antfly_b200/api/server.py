@@ -535,6 +535,27 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "rewrite", max(1, len(req.inputs)), work)
 
+    async def transcribe(request: Request):
+        req, bad = await parse(request, S.TranscribeRequest)
+        if bad:
+            return bad
+        try:
+            audio = base64.b64decode(req.audio, validate=True)
+        except Exception:
+            return _err(400, "invalid_request", "audio must be base64")
+
+        def work():
+            lm = mgr.get(req.model, "transcriber")
+            out = lm.pipeline.transcribe(audio, language=req.language, task=req.task, max_new_tokens=req.max_tokens)
+            metrics.tokens.labels("transcribe", "completion").inc(out.completion_tokens)
+            return {"object": "list", "model": req.model,
+                    "data": [{"object": "transcription", "index": 0, "text": out.text, "segments": [
+                        {k: v for k, v in sgm.items() if k != "tokens"} for sgm in out.segments]}],
+                    "usage": {"prompt_tokens": out.prompt_tokens, "completion_tokens": out.completion_tokens,
+                              "total_tokens": out.prompt_tokens + out.completion_tokens}}
+
+        return await asyncio.to_thread(run_guarded, "transcribe", 1, work)
+
     async def extract(request: Request):
         req, bad = await parse(request, S.ExtractionRequest)
         if bad:
@@ -742,6 +763,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
     app.add_api_route("/ai/v1/rewrite", rewrite, methods=["POST"])
     app.add_api_route("/ai/v1/extract", extract, methods=["POST"])
+    app.add_api_route("/ai/v1/transcribe", transcribe, methods=["POST"])
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
     app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
     app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])

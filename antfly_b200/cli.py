@@ -212,6 +212,19 @@ def cmd_rewrite(args) -> int:
     return 0
 
 
+def cmd_transcribe(args) -> int:
+    lm = _manager(args).get(args.model, "transcriber")
+    for path in args.audio:
+        out = lm.pipeline.transcribe(path, language=args.language, max_new_tokens=args.max_tokens)
+        print(json.dumps({"audio": path, "text": out.text, "segments": [
+            {k: v for k, v in s.items() if k != "tokens"} for s in out.segments]}))
+        if args.print_timing:
+            t = out.timing_ms
+            print("transcribe_timing_ms: decode_audio=%.1f transcribe=%.1f total=%.1f" %
+                  (t["decode_audio"], t["transcribe"], t["total"]), file=sys.stderr)
+    return 0
+
+
 def cmd_compare(args) -> int:
     """Run the same embedder on two devices (by default the CPU oracle path and the GPU kernels) and report how far
     the embeddings are apart: the parity check a deployment runs after changing hardware or build."""
@@ -280,6 +293,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
     p.add_argument("--max-tokens", type=int, default=128); p.add_argument("--print-timing", action="store_true")
     p.set_defaults(fn=cmd_rewrite)
+    p = sub.add_parser("transcribe"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--audio", nargs="+", required=True, help="WAV files")
+    p.add_argument("--language"); p.add_argument("--max-tokens", type=int, default=224)
+    p.add_argument("--print-timing", action="store_true"); p.set_defaults(fn=cmd_transcribe)
     p = sub.add_parser("compare", help="same embedder on two devices: embedding parity report")
     p.add_argument("--models-dir"); p.add_argument("--model", required=True)
     p.add_argument("--text", nargs="+", required=True); p.add_argument("--device-a", default="cpu")

@@ -475,3 +475,60 @@ def test_t5_matches_transformers(ff, tied):
             want.append(nxt)
             dec.append(nxt)
     assert model.generate(src, max_new_tokens=10) == want
+
+
+def test_whisper_matches_transformers():
+    """Convolutional stem as GEMMs over unfolded windows, sinusoidal / learned positions, encoder, decoder with
+    self- and cross-attention caches, tied output projection, greedy transcription; log-mel front end against the
+    Hugging Face feature extractor."""
+    import numpy as np
+
+    from antfly_b200.models.whisper import WhisperConfig, WhisperModel
+    from antfly_b200.ops import audio_ops as AO
+
+    torch.manual_seed(6)
+    hf_cfg = transformers.WhisperConfig(vocab_size=300, num_mel_bins=80, d_model=64, encoder_layers=2,
+                                        encoder_attention_heads=4, decoder_layers=2, decoder_attention_heads=4,
+                                        encoder_ffn_dim=128, decoder_ffn_dim=128, max_source_positions=100,
+                                        max_target_positions=32, dropout=0.0, attention_dropout=0.0,
+                                        activation_dropout=0.0, decoder_start_token_id=1, eos_token_id=2,
+                                        pad_token_id=0, bos_token_id=1, suppress_tokens=None,
+                                        begin_suppress_tokens=None)
+    hf = transformers.WhisperForConditionalGeneration(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+            elif "layer_norm" not in n and "embed_positions" not in n:
+                p.mul_(2.0)
+    cfg = WhisperConfig.from_hf(hf_cfg.to_dict())
+    model = WhisperModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    mel = torch.randn(80, 200) * 0.5
+    tgt = [1] + torch.randint(3, 300, (9,)).tolist()
+    with torch.no_grad():
+        out = hf(input_features=mel[None], decoder_input_ids=torch.tensor([tgt]))
+    enc = model.encode(mel)
+    ref = out.encoder_last_hidden_state[0]
+    assert enc.shape == (100, 64) and float((enc.float() - ref).norm() / ref.norm()) < 0.02
+    full = model.decode(model.start_decoding(enc), tgt)
+    assert float((full - out.logits[0]).norm() / out.logits[0].norm()) < 0.03
+    assert float((full.argmax(-1) == out.logits[0].argmax(-1)).float().mean()) >= 0.9
+    state = model.start_decoding(enc)
+    step = torch.cat([model.decode(state, [t]) for t in tgt])
+    assert float((step - full).norm() / full.norm()) < 0.02
+    dec, want = [1], []
+    with torch.no_grad():
+        for _ in range(8):
+            nxt = int(hf(input_features=mel[None], decoder_input_ids=torch.tensor([dec])).logits[0, -1].argmax())
+            if nxt == 2:
+                break
+            want.append(nxt)
+            dec.append(nxt)
+    assert model.transcribe_ids(mel, [1], max_new_tokens=8) == want
+    # front end
+    fe = transformers.WhisperFeatureExtractor()
+    t = torch.arange(16000 * 2) / 16000
+    x = 0.3 * torch.sin(2 * np.pi * 440 * t) + 0.05 * torch.randn(t.numel())
+    want_f = torch.from_numpy(fe(x.numpy(), sampling_rate=16000, return_tensors="np")["input_features"][0])
+    got_f = AO.log_mel(x)
+    assert got_f.shape == (80, 3000) and float((got_f - want_f).abs().max()) < 1e-4
