@@ -65,6 +65,133 @@ def unpack_node(node_id: int, b: bytes) -> Node:
     return Node(node_id, bool(is_leaf), level, parent, cent, ids)
 
 
+# ----------------------------------------------------------------------------------------------------------
+# Quantised payloads: protobuf wire format of RaBitQuantizedVectorSet / NonQuantizedVectorSet
+# (go/pkg/antfly/lib/vector/quantize/quantize.proto, zig/lib/vector/src/proto.zig:38-200).  Scalars repeat packed
+# (edition 2023 default): floats as fixed32, uint64 code words and uint32 counts as varints.
+# ----------------------------------------------------------------------------------------------------------
+def _varint(v: int) -> bytes:
+    v &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b7 = v & 0x7F
+        v >>= 7
+        out.append(b7 | (0x80 if v else 0))
+        if not v:
+            return bytes(out)
+
+
+def _read_varint(b: bytes, pos: int) -> Tuple[int, int]:
+    v, shift = 0, 0
+    while True:
+        c = b[pos]
+        pos += 1
+        v |= (c & 0x7F) << shift
+        if not c & 0x80:
+            return v, pos
+        shift += 7
+        if shift > 63:
+            raise ValueError("varint too long")
+
+
+def _field(num: int, wire: int, payload: bytes) -> bytes:
+    head = _varint(num << 3 | wire)
+    return head + (_varint(len(payload)) if wire == 2 else b"") + payload
+
+
+def _floats(t: torch.Tensor) -> bytes:
+    return t.detach().float().cpu().contiguous().numpy().astype("<f4").tobytes()
+
+
+def encode_rabitq_set(qs) -> bytes:
+    """RaBitQSet -> RaBitQuantizedVectorSet bytes."""
+    n, width = qs.codes.shape
+    words = qs.codes.detach().cpu().reshape(-1).tolist()
+    codes = _field(1, 0, _varint(n)) + _field(2, 0, _varint(width)) + _field(3, 2, b"".join(_varint(w) for w in words))
+    out = b""
+    m = _METRICS[qs.metric]
+    if m:
+        out += _field(1, 0, _varint(m))
+    out += _field(2, 2, _floats(qs.centroid)) + _field(3, 2, codes)
+    out += _field(4, 2, b"".join(_varint(int(c)) for c in qs.code_counts.tolist()))
+    out += _field(5, 2, _floats(qs.centroid_distances)) + _field(6, 2, _floats(qs.inv_dot))
+    if qs.centroid_dot is not None:
+        out += _field(7, 2, _floats(qs.centroid_dot))
+    if qs.centroid_norm:
+        out += _field(8, 5, struct.pack("<f", float(qs.centroid_norm)))
+    return out
+
+
+def _parse(b: bytes):
+    pos = 0
+    while pos < len(b):
+        key, pos = _read_varint(b, pos)
+        num, wire = key >> 3, key & 7
+        if wire == 0:
+            v, pos = _read_varint(b, pos)
+        elif wire == 2:
+            n, pos = _read_varint(b, pos)
+            v, pos = b[pos:pos + n], pos + n
+        elif wire == 5:
+            v, pos = b[pos:pos + 4], pos + 4
+        elif wire == 1:
+            v, pos = b[pos:pos + 8], pos + 8
+        else:
+            raise ValueError(f"unsupported wire type {wire}")
+        yield num, wire, v
+
+
+def _unpack_floats(b: bytes) -> torch.Tensor:
+    return torch.frombuffer(bytearray(b), dtype=torch.float32).clone() if b else torch.zeros(0)
+
+
+def _unpack_varints(b: bytes) -> list:
+    out, pos = [], 0
+    while pos < len(b):
+        v, pos = _read_varint(b, pos)
+        out.append(v)
+    return out
+
+
+def decode_rabitq_set(b: bytes):
+    from .rabitq import RaBitQSet
+
+    f: Dict[int, object] = {}
+    for num, _wire, v in _parse(b):
+        f[num] = v
+    count = width = 0
+    words: list = []
+    for num, _wire, v in _parse(f.get(3, b"")):
+        if num == 1:
+            count = v
+        elif num == 2:
+            width = v
+        elif num == 3:
+            words = _unpack_varints(v)
+    if len(words) != count * width:
+        raise ValueError("code set size does not match count * width")
+    signed = [w - (1 << 64) if w >= 1 << 63 else w for w in words]       # int64 tensor holding the u64 bit pattern
+    codes = torch.tensor(signed, dtype=torch.int64).view(count, width) if count else torch.zeros((0, width),
+                                                                                                   dtype=torch.int64)
+    return RaBitQSet(_METRIC_NAMES[f.get(1, 0)], _unpack_floats(f.get(2, b"")), codes,
+                     torch.tensor(_unpack_varints(f.get(4, b"")), dtype=torch.int32), _unpack_floats(f.get(5, b"")),
+                     _unpack_floats(f.get(6, b"")), _unpack_floats(f[7]) if 7 in f else None,
+                     struct.unpack("<f", f[8])[0] if 8 in f else 0.0)
+
+
+def encode_vector_set(x: torch.Tensor) -> bytes:
+    """NonQuantizedVectorSet{vectors: Set{dims, count, data}} (the root's payload when it is kept exact)."""
+    n, d = x.shape
+    inner = _field(1, 0, _varint(d)) + _field(2, 0, _varint(n)) + _field(3, 2, _floats(x))
+    return _field(1, 2, inner)
+
+
+def decode_vector_set(b: bytes) -> torch.Tensor:
+    inner = next(v for num, _w, v in _parse(b) if num == 1)
+    f = {num: v for num, _w, v in _parse(inner)}
+    return _unpack_floats(f.get(3, b"")).view(f.get(2, 0), f.get(1, 0))
+
+
 def _write_ns(path: str, kv: Dict[bytes, bytes]) -> None:
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(kv)))
@@ -96,7 +223,9 @@ def save_hbc(index: HBCIndex, directory: str) -> None:
     _write_ns(os.path.join(directory, "nodes.kv"), nodes)
     _write_ns(os.path.join(directory, "meta.kv"), meta)
     _write_ns(os.path.join(directory, "vecs.kv"), vecs)
-    _write_ns(os.path.join(directory, "quant.kv"), {})  # quantised payloads are rebuilt from vectors on load
+    quant = {b"q:" + struct.pack(">Q", nd.id): encode_rabitq_set(nd.quant) for nd in index.nodes.values()
+             if getattr(nd, "quant", None) is not None}
+    _write_ns(os.path.join(directory, "quant.kv"), quant)
 
 
 def load_hbc(directory: str) -> HBCIndex:
@@ -120,10 +249,23 @@ def load_hbc(directory: str) -> HBCIndex:
             for m in nd.children:
                 idx.leaf_of[m] = nd.id
     if cfg.use_quantization:
+        qpath = os.path.join(directory, "quant.kv")
+        stored = _read_ns(qpath) if os.path.exists(qpath) else {}
         for nd in idx.nodes.values():
-            pts = idx.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
-                [idx.nodes[c].centroid for c in nd.children])
-            nd.quant = idx.quantizer.quantize(nd.centroid, pts)
+            blob = stored.get(b"q:" + struct.pack(">Q", nd.id))
+            pts = None
+            if blob is not None:
+                nd.quant = decode_rabitq_set(blob)
+                if nd.quant.codes.shape[0] != len(nd.children):
+                    blob = None                      # stale payload: fall back to re-quantising
+                elif cfg.metric == "cosine":
+                    pts = idx.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+                        [idx.nodes[c].centroid for c in nd.children])
+                    nd.quant.data_norms = pts.norm(dim=-1)
+            if blob is None:
+                pts = idx.vectors[torch.tensor(nd.children)] if nd.is_leaf else torch.stack(
+                    [idx.nodes[c].centroid for c in nd.children])
+                nd.quant = idx.quantizer.quantize(nd.centroid, pts)
     return idx
 
 
