@@ -229,3 +229,16 @@ class TranscribeRequest(BaseModel):
     language: Optional[str] = None
     task: str = "transcribe"
     max_tokens: int = Field(default=224, gt=0)
+
+
+class RerankMultimodalDocument(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    id: Optional[str] = None
+    content: Union[str, List[Dict[str, Any]]]
+
+
+class RerankMultimodalRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    query: str
+    documents: List[RerankMultimodalDocument]

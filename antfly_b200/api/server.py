@@ -266,6 +266,68 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "rerank", len(req.prompts), work)
 
+    async def rerank_multimodal(request: Request):
+        """Documents made of text and image content parts scored against a text query.  Text-only documents go to
+        the cross-encoder named by ``model``; documents with images need a dual-tower (CLIP) model, and a
+        document's score is the best cosine similarity between the query and any of its parts."""
+        req, bad = await parse(request, S.RerankMultimodalRequest)
+        if bad:
+            return bad
+        if not req.documents:
+            return _err(400, "invalid_request", "documents must not be empty")
+        from ..pipelines.multimodal import decode_data_url
+
+        docs = []          # per document: (texts, images)
+        for i, d in enumerate(req.documents):
+            texts, imgs = [], []
+            parts = [{"type": "text", "text": d.content}] if isinstance(d.content, str) else d.content
+            for p in parts:
+                if p.get("type") == "text":
+                    texts.append(p.get("text", ""))
+                elif p.get("type") in ("image_url", "image"):
+                    url = p.get("image_url") or p.get("url") or p.get("image")
+                    if isinstance(url, dict):
+                        url = url.get("url")
+                    try:
+                        imgs.append(decode_data_url(url))
+                    except Exception as e:
+                        return _err(400, "invalid_request", f"document {i}: {e}")
+                else:
+                    return _err(400, "invalid_request", f"document {i}: content part type {p.get('type')!r} "
+                                                        "is not supported")
+            if not texts and not imgs:
+                return _err(400, "invalid_request", f"document {i} is empty")
+            docs.append((texts, imgs))
+
+        def work():
+            import torch as _torch
+
+            if not any(imgs for _t, imgs in docs):
+                lm = mgr.get(req.model, "reranker")
+                scores, ntok = lm.pipeline.rerank(req.query, [" ".join(t) for t, _i in docs])
+            else:
+                lm = mgr.get(req.model, "embedder")
+                pipe = lm.pipeline
+                if not hasattr(pipe, "embed_images"):
+                    raise ValueError(f"model {req.model!r} cannot score images")
+                qv, ntok = pipe.embed([req.query])
+                scores = []
+                for texts, imgs in docs:
+                    parts = []
+                    if texts:
+                        tv, n = pipe.embed(texts)
+                        ntok += n
+                        parts.append(tv)
+                    if imgs:
+                        parts.append(pipe.embed_images(imgs).cpu().float())
+                    scores.append(float((_torch.cat(parts) @ qv[0].float()).max()))
+            metrics.tokens.labels("rerank", "prompt").inc(ntok)
+            return S.RerankResponse(
+                data=[S.RerankObject(index=i, score=float(s)) for i, s in enumerate(scores)], model=req.model,
+                usage=S.GenerateUsage(prompt_tokens=ntok, completion_tokens=0, total_tokens=ntok)).model_dump()
+
+        return await asyncio.to_thread(run_guarded, "rerank_multimodal", len(docs), work)
+
     # ---- generate / chat completions --------------------------------------------------------------------
     def sampling_from(req: S.GenerateRequest, tok) -> SamplingParams:
         stops: List[int] = []
@@ -754,6 +816,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     for path in ("/ai/v1/embed", "/ai/v1/embeddings"):
         app.add_api_route(path, embed, methods=["POST"])
     app.add_api_route("/ai/v1/rerank", rerank, methods=["POST"])
+    app.add_api_route("/ai/v1/rerank_multimodal", rerank_multimodal, methods=["POST"])
     for path in ("/ai/v1/generate", "/ai/v1/chat/completions"):
         app.add_api_route(path, generate, methods=["POST"])
     app.add_api_route("/openai/v1/chat/completions", generate, methods=["POST"])

@@ -156,6 +156,26 @@ def test_embed_images_and_text_with_a_clip_model():
     assert r.status_code == 400 and "data:" in r.json()["message"]
     r = c.post("/ai/v1/embed", json={"model": "tiny-clip", "input": [{"type": "audio", "text": "x"}]})
     assert r.status_code == 400
+    # multimodal rerank: image documents scored by the dual-tower model, text-only ones by the cross-encoder
+    mgr.register_random("tiny-rerank", "reranker")
+    r = c.post("/ai/v1/rerank_multimodal", json={"model": "tiny-clip", "query": "a photo", "documents": [
+        {"id": "a", "content": [{"type": "image_url", "image_url": {"url": url}}]},
+        {"id": "b", "content": [{"type": "text", "text": "a photo"}, {"type": "image_url", "image_url": {"url": url}}]},
+        {"content": "just text"}]})
+    body = r.json()
+    assert r.status_code == 200 and [d["index"] for d in body["data"]] == [0, 1, 2]
+    qv = c.post("/ai/v1/embed", json={"model": "tiny-clip", "input": "a photo"}).json()["data"][0]["embedding"]
+    iv = data[1]["embedding"]
+    assert abs(body["data"][0]["score"] - sum(x * y for x, y in zip(qv, iv))) < 1e-4
+    assert body["data"][1]["score"] >= body["data"][0]["score"] - 1e-6 and body["data"][1]["score"] > 0.999
+    r = c.post("/ai/v1/rerank_multimodal", json={"model": "tiny-rerank", "query": "q", "documents": [
+        {"content": "first"}, {"content": [{"type": "text", "text": "second"}]}]})
+    assert r.status_code == 200 and len(r.json()["data"]) == 2
+    r = c.post("/ai/v1/rerank_multimodal", json={"model": "tiny-rerank", "query": "q", "documents": [
+        {"content": [{"type": "image_url", "image_url": {"url": url}}]}]})
+    assert r.status_code in (400, 404)
+    assert c.post("/ai/v1/rerank_multimodal", json={"model": "tiny-clip", "query": "q",
+                                                   "documents": []}).status_code == 400
 
 
 def test_chunk_and_metrics(client):
