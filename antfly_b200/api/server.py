@@ -12,6 +12,7 @@ from __future__ import annotations
 import asyncio
 import base64
 import json
+import logging
 import struct
 import threading
 import time
@@ -28,6 +29,7 @@ from ..pipelines.chunking import chunk_text
 from ..pipelines.embedding import INPUT_TYPE_ALIASES
 from ..runtime.sampling_params import SamplingParams
 from ..runtime.scheduler import QueueFull
+from ..utils import logs as L
 from . import schemas as S
 from .cache import ResultCache
 from .metrics import Metrics
@@ -111,6 +113,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     metrics = Metrics()
     queue = RequestQueue(max_concurrent_requests, max_queue_size)
     cache = ResultCache(result_cache_ttl_s)
+    log = L.get("server")
     app.state.result_cache = cache
     gpu_lock = threading.Lock()  # one request drives the device at a time; batching happens inside pipelines
     app.state.manager, app.state.metrics, app.state.queue = mgr, metrics, queue
@@ -147,7 +150,11 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             return _err(500, "internal_error", f"{type(e).__name__}: {e}")
         finally:
             queue.release(units)
-            metrics.latency.labels(endpoint).observe(time.perf_counter() - t0)
+            dt = time.perf_counter() - t0
+            metrics.latency.labels(endpoint).observe(dt)
+            if log.isEnabledFor(logging.INFO):
+                L.event(log, logging.INFO, "request", endpoint=endpoint, units=units, duration_ms=round(dt * 1e3, 2),
+                        queue_waiting=queue.waiting)
             metrics.loaded_models.set(mgr.loaded_count())
             metrics.kernel_launches.set(N.launches())
 

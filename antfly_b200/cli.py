@@ -59,6 +59,10 @@ def cmd_run(args) -> int:
         over["api_url"] = "http://127.0.0.1:11433"
     cfg = load_config(args.config, **over)
     host, port = cfg.host_port
+    from .utils import logs
+
+    logs.event(logs.setup(cfg.log.level, cfg.log.style), 20, "starting", host=host, port=port,
+               models_dir=cfg.models_dir, keep_alive=cfg.keep_alive, max_loaded_models=cfg.max_loaded_models)
     mgr = ModelManager(models_dir=cfg.models_dir, device=args.device or cfg.device(), kv_blocks=args.kv_blocks,
                        prefix_cache=not args.no_prefix_cache, max_loaded_models=cfg.max_loaded_models,
                        keep_alive_s=cfg.keep_alive_s, max_memory_mb=cfg.max_memory_mb,

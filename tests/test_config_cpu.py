@@ -108,3 +108,25 @@ def test_keep_alive_limits_and_pinning(tmp_path):
             mem.get(n, "embedder")
         assert mem.loaded_count() == 2 and "embedder:a" not in mem._models
     assert one.unload("a", "embedder") and not one.unload("a", "embedder")
+
+
+def test_structured_logging_text_and_json():
+    import io
+    import logging
+
+    from antfly_b200.utils import logs
+
+    buf = io.StringIO()
+    lg = logs.setup("debug", "json", buf)
+    logs.event(logs.get("server"), logging.INFO, "request", endpoint="embed", units=3, duration_ms=1.5)
+    rec = json.loads(buf.getvalue().strip())
+    assert rec["msg"] == "request" and rec["endpoint"] == "embed" and rec["units"] == 3 and rec["level"] == "info"
+    assert rec["logger"] == "antfly_b200.server" and rec["ts"].endswith("Z")
+    buf = io.StringIO()
+    logs.setup("warning", "text", buf)
+    logs.event(logs.get("x"), logging.INFO, "hidden")
+    logs.event(logs.get("x"), logging.WARNING, "queue full", endpoint="generate", note="retry later")
+    line = buf.getvalue().strip()
+    assert "hidden" not in line and "warn" in line and "queue full endpoint=generate" in line
+    assert 'note="retry later"' in line and len(lg.handlers) == 1
+    logs.setup("info", "text", io.StringIO())
