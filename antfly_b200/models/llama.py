@@ -170,6 +170,8 @@ class LlamaModel:
         self.vocab_offset = tp_rank * self.vocab_local if tp_size > 1 else 0
         self._scratch: Dict[tuple, torch.Tensor] = {}
         self.moe_runtime = None   # set by offload_experts(): expert weights live in host memory
+        self.pp = None            # set by set_pipeline(): this model is one stage of a layer pipeline
+        self.layer_lo = 0
 
     # --------------------------------------------------------------------------------------------------
     @classmethod
@@ -229,9 +231,10 @@ class LlamaModel:
 
     @classmethod
     def from_state_dict(cls, cfg: LlamaConfig, sd: Dict[str, torch.Tensor], device="cuda", tp_rank: int = 0,
-                        tp_size: int = 1, comm=None) -> "LlamaModel":
+                        tp_size: int = 1, comm=None, layers: Optional[tuple] = None) -> "LlamaModel":
         """HF names (model.layers.N.self_attn.{q,k,v,o}_proj, mlp.{gate,up,down}_proj, ...) -> fused, sharded,
-        block-fp8 packed layout."""
+        block-fp8 packed layout.  ``layers`` = (first, last) loads only that range of decoder layers (a pipeline
+        stage); the stage is then wired with :meth:`set_pipeline`."""
         from ..parallel.sharding import shard_rows, shard_cols
 
         D = cfg.head_dim
@@ -239,7 +242,7 @@ class LlamaModel:
         w: Dict[str, object] = {}
         emb = sd[pre + "embed_tokens.weight"].to(torch.bfloat16)
         w["embed"] = emb.to(device)
-        for l in range(cfg.num_hidden_layers):
+        for l in range(*(layers or (0, cfg.num_hidden_layers))):
             s, p = f"{pre}layers.{l}.", f"l{l}."
             w[p + "ln1"] = sd[s + "input_layernorm.weight"].to(torch.bfloat16).to(device)
             w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
@@ -423,6 +426,15 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    def set_pipeline(self, stage, first_layer: int, last_layer: int) -> None:
+        """Make this model one stage of a pipeline over decoder layers [first_layer, last_layer): the first stage
+        embeds the tokens, every stage runs its layers on the hidden states it receives and passes them on, the
+        last stage applies the final norm and the LM head, and the logits are shared with every stage so that all
+        ranks sample the same tokens and keep their schedulers in step.  ``stage`` provides the transport
+        (:class:`antfly_b200.parallel.pipeline.PipelineStage`)."""
+        self.pp, self.layer_lo = stage, first_layer
+        self.n_layers = last_layer - first_layer
+
     def offload_experts(self, max_resident_per_layer: int, max_predicted: int = 2) -> "MoeRuntimeState":
         """Move the routed experts' weights to (pinned) host memory and keep at most ``max_resident_per_layer`` of
         each layer's experts on the device; absent experts are copied in when a step routes to them and the experts
@@ -479,23 +491,29 @@ class LlamaModel:
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         T = b.ids.numel()
         gp1, eps = cfg.norm_plus_one, cfg.rms_norm_eps
-        x = Dn.embed_gather(b.ids, w["embed"], scale=cfg.embed_scale)
-        h = Dn.norm(x, w["l0.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
-        for l in range(self.n_layers):
+        pp, lo = self.pp, self.layer_lo
+        hi = lo + self.n_layers
+        if pp is None or pp.is_first:
+            x = Dn.embed_gather(b.ids, w["embed"], scale=cfg.embed_scale)
+        else:
+            x = pp.recv_hidden(T, cfg.hidden_size, w[f"l{lo}.ln1"].device)
+        h = Dn.norm(x, w[f"l{lo}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
+        for l in range(lo, hi):
             p = f"l{l}."
+            k_cache_l, v_cache_l = k_cache[l - lo], v_cache[l - lo]
             qkv = self._linear(h, w[p + "qkv"], T)
-            q = A.rope_kv_write(qkv, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
+            q = A.rope_kv_write(qkv, b.positions, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, cfg.rope_theta,
                                 bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
                                 freq_scale=cfg.rope_freq_scale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
                                 norm_eps=eps, norm_plus_one=gp1)
-            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+            ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch)
             x = self._linear(ctx.view(T, Hq * D), w[p + "o"], T, residual=x)
             h = Dn.norm(x, w[p + "ln2"], eps=eps, rms=True, gamma_plus_one=gp1)
             if cfg.num_experts > 0:
                 x = (x.float() + self._moe_mlp(h, l, T)).to(torch.bfloat16)
-                if l + 1 < self.n_layers:
+                if l + 1 < hi:
                     h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
                 continue
             gu = self._linear(h, w[p + "gu"], T).float()  # columns alternate gate_i, up_i
@@ -507,24 +525,27 @@ class LlamaModel:
             else:
                 gate = torch.nn.functional.silu(gate)
             x = self._linear((gate * up).to(torch.bfloat16), w[p + "down"], T, residual=x)
-            nw = w["norm"] if l + 1 == self.n_layers else w[f"l{l + 1}.ln1"]
-            if l + 1 < self.n_layers:
-                h = Dn.norm(x, nw, eps=eps, rms=True, gamma_plus_one=gp1)
+            if l + 1 < hi:
+                h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
+        n_rows = T if b.logit_rows.numel() == T else b.logit_rows.numel()
+        if pp is not None and not pp.is_last:
+            pp.send_hidden(x)
+            return pp.share_logits(None, n_rows, cfg.hidden_size if self.return_hidden else self.vocab_local,
+                                   x.device)
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
         hl = Dn.norm(rows, w["norm"], eps=eps, rms=True, gamma_plus_one=gp1)
-        if self.return_hidden:
-            return hl
-        head = w["lm_head"]
-        if isinstance(head, Q.Fp8Weight):
-            return self._linear(hl, head, rows.shape[0])
-        return Dn.gemm_bf16(hl, head)
+        if not self.return_hidden:
+            head = w["lm_head"]
+            hl = self._linear(hl, head, rows.shape[0]) if isinstance(head, Q.Fp8Weight) else Dn.gemm_bf16(hl, head)
+        return hl if pp is None else pp.share_logits(hl, n_rows, hl.shape[1], hl.device)
 
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
                 attn_scratch: Optional[A.PagedAttnScratch] = None) -> torch.Tensor:
         """Runs the stack on one step batch; K/V of the step's tokens are written into
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
-        if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0:
+        if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
+                self.pp is not None:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

@@ -4,8 +4,8 @@ The reference plans a graph partition (zig/pkg/inference/src/graph/parallel_stra
 ``pipeline`` = cut the layer stack at attention boundaries into contiguous stages, one per device; ``tensor`` =
 replicate the graph and shard the weights by the Megatron rules.  The plan here is the same decision expressed on
 decoder layers: which layers a rank runs (pipeline) or which slice of every layer it holds (tensor), checked against
-the divisibility the kernels need.  The serving engine executes ``single`` and ``tensor`` plans; a pipeline plan
-is produced for completeness and for memory planning.
+the divisibility the kernels need.  ``tensor`` plans run through the fused tensor-parallel kernels; ``pipeline``
+plans through :mod:`antfly_b200.parallel.pipeline` (layer ranges per rank, hidden states sent rank to rank).
 """
 from __future__ import annotations
 

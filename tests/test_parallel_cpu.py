@@ -161,3 +161,75 @@ def test_rank_failure_is_detected_on_the_host():
     for p in procs:
         p.join(timeout=60)
     assert got["left"] == 1 and got["dead"] == [1]
+
+
+def _pp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import datetime
+
+    from antfly_b200.models.llama import LlamaConfig
+    from antfly_b200.parallel.pipeline import build_stage
+    from antfly_b200.parallel.strategy import plan_parallel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    cfg = LlamaConfig.tiny(num_hidden_layers=5)
+    plan = plan_parallel(cfg, world, "pipeline")
+    model = build_stage(cfg, _hf_llama_state(cfg), plan, rank, device="cpu")
+    assert model.n_layers == plan.ranks[rank].layers[1] - plan.ranks[rank].layers[0]
+    assert not any(k.startswith(f"l{plan.ranks[(rank + 1) % world].layers[0]}.") for k in model.w)
+    logits = _forward_logits_layers(model, cfg)
+    # the same stages drive the serving engine in lockstep: every rank generates the same tokens
+    eng = LLMEngine(model, num_blocks=16, page=16, max_batch=2, use_cuda_graph=False)
+    out = eng.generate([[5, 6, 7, 8, 9], [11, 12]], SamplingParams(max_tokens=5, ignore_eos=True))
+    q.put((rank, logits, [o.token_ids for o in out], model.pp.sent_bytes, model.pp.received_bytes))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _forward_logits_layers(model, cfg):
+    from antfly_b200.models.llama import StepBatch
+
+    lens = [9, 4]
+    T = sum(lens)
+    ids = (torch.arange(T, dtype=torch.int32) * 7 + 3) % cfg.vocab_size
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+    ql = torch.tensor(lens, dtype=torch.int32)
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    tables = torch.tensor([[0, 0], [1, 0]], dtype=torch.int32)
+    slots = torch.tensor(list(range(9)) + list(range(16, 20)), dtype=torch.int32)
+    b = StepBatch(ids, pos, slots, qs, ql, ql.clone(), tables, (qs + ql - 1).int(), max(lens), 1)
+    kc = torch.zeros((model.n_layers, 2, 16, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    return model.forward(b, kc, torch.zeros_like(kc)).float()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_pipeline_parallel_stages_match_single_rank(world):
+    """Layer ranges on separate ranks (each with only its layers' weights and KV cache), hidden states passed by
+    point-to-point sends, logits shared with every stage; also through the serving engine."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=300) for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    cfg = LlamaConfig.tiny(num_hidden_layers=5)
+    single = LlamaModel.from_state_dict(cfg, _hf_llama_state(cfg), device="cpu")
+    ref = _forward_logits_layers(single, cfg)
+    eng = LLMEngine(single, num_blocks=16, page=16, max_batch=2, use_cuda_graph=False)
+    want = [o.token_ids for o in eng.generate([[5, 6, 7, 8, 9], [11, 12]], SamplingParams(max_tokens=5,
+                                                                                            ignore_eos=True))]
+    for rank, logits, toks, sent, recv in got:
+        torch.testing.assert_close(logits, ref, atol=6e-2, rtol=5e-2)
+        assert toks == want
+        assert (sent > 0) == (rank < world - 1) and (recv > 0) == (rank > 0)
