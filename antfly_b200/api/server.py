@@ -345,7 +345,14 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     stops.append(ids[0])
         grammar = None
         fmt = (req.response_format or {}).get("type")
-        if req.grammar:
+        gbnf = req.grammar
+        if not gbnf and fmt == "json_schema":
+            # structured output: the schema is compiled into a grammar, so a non-conforming token is never sampled
+            from ..runtime.json_schema import json_schema_to_gbnf
+
+            js = (req.response_format or {}).get("json_schema") or {}
+            gbnf = json_schema_to_gbnf(js.get("schema", js) if isinstance(js, dict) else {})
+        if gbnf:
             # a GBNF grammar supplied with the request constrains the whole reply
             from ..runtime.grammar import GbnfGrammar, token_bytes_table
 
@@ -356,7 +363,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     tok._grammar_token_bytes = table
                 except Exception:
                     pass
-            grammar = GbnfGrammar(table, req.grammar, eos_id=tok.special.eos_id)
+            grammar = GbnfGrammar(table, gbnf, eos_id=tok.special.eos_id)
         elif fmt in ("json_object", "json"):
             # JSON mode: every sampled token must keep the reply a valid JSON prefix; the byte table of the
             # vocabulary is built once per tokenizer and shared by all requests.
@@ -416,11 +423,18 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             # engines are built with a bf16 cache; a per-request dtype cannot be honoured after the fact
             return _err(400, "invalid_request", f"cache_dtype {req.cache_dtype!r} is not supported by this server "
                                                 "(KV cache is bf16)")
-        if req.grammar:
-            try:  # reject a malformed grammar before any work is queued
+        if req.grammar or (req.response_format or {}).get("type") == "json_schema":
+            try:  # reject a malformed grammar / unsupported schema before any work is queued
                 from ..runtime.grammar import GbnfGrammar
+                from ..runtime.json_schema import json_schema_to_gbnf
 
-                GbnfGrammar([b"a"], req.grammar)
+                text = req.grammar
+                if not text:
+                    js = req.response_format.get("json_schema") or {}
+                    if not isinstance(js, dict) or not isinstance(js.get("schema", js), dict):
+                        raise ValueError("response_format.json_schema.schema must be an object")
+                    text = json_schema_to_gbnf(js.get("schema", js))
+                GbnfGrammar([b"a"], text)
             except ValueError as e:
                 return _err(400, "invalid_request", str(e))
         if not req.stream:

@@ -104,6 +104,21 @@ def test_generate_json_mode_gbnf_and_tools(client):
     assert r.json()["choices"][0]["finish_reason"] == "stop"
     r = client.post("/ai/v1/chat/completions", json=dict(base, grammar='root ::= undefined-rule'))
     assert r.status_code == 400 and "never defined" in r.json()["message"]
+    # structured output: a schema with only finite choices, so even random weights must produce a valid document
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}, "level": {"enum": ["low", "high"]},
+                                               "n": {"const": 7}}, "required": ["ok", "level", "n"]}
+    r = client.post("/ai/v1/chat/completions", json=dict(base, max_tokens=120, response_format={
+        "type": "json_schema", "json_schema": {"name": "verdict", "schema": schema}}))
+    assert r.status_code == 200, r.text
+    if r.json()["choices"][0]["finish_reason"] == "stop":
+        doc = json.loads(r.json()["choices"][0]["message"]["content"])
+        assert set(doc) == {"ok", "level", "n"} and isinstance(doc["ok"], bool) and doc["level"] in ("low", "high")
+        assert doc["n"] == 7
+    else:       # ran out of tokens inside optional whitespace: what was produced is still a valid prefix
+        assert (r.json()["choices"][0]["message"]["content"] or "").lstrip().startswith("{")
+    r = client.post("/ai/v1/chat/completions", json=dict(base, response_format={
+        "type": "json_schema", "json_schema": {"schema": {"$ref": "http://remote/schema"}}}))
+    assert r.status_code == 400 and "$ref" in r.json()["message"]
     tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object"}}}]
     r = client.post("/ai/v1/chat/completions", json=dict(base, tools=tools, tool_choice="sometimes"))
     assert r.status_code == 400

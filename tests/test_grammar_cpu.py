@@ -187,3 +187,82 @@ def test_gbnf_errors():
     with pytest.raises(ValueError):
         _gb('root ::= "unterminated')
     assert _gb('start ::= "x"', root="start").accept_text("x")
+
+
+def _matches(grammar: str, text: str) -> bool:
+    from antfly_b200.runtime.grammar import GbnfGrammar
+
+    g = GbnfGrammar([bytes([i]) for i in range(256)], grammar)
+    return g.accept_text(text) and g.complete
+
+
+def test_json_schema_compiles_to_a_grammar_that_accepts_exactly_valid_documents():
+    from antfly_b200.runtime.json_schema import json_schema_to_gbnf
+
+    schema = {
+        "type": "object",
+        "properties": {
+            "name": {"type": "string", "minLength": 1, "maxLength": 8},
+            "age": {"type": "integer"},
+            "tags": {"type": "array", "items": {"enum": ["a", "b", "c d"]}, "minItems": 1, "maxItems": 3},
+            "address": {"$ref": "#/$defs/addr"},
+            "score": {"type": ["number", "null"]},
+            "kind": {"const": "person"},
+        },
+        "required": ["name", "tags"],
+        "$defs": {"addr": {"type": "object", "properties": {"city": {"type": "string"},
+                                                              "zip": {"type": "string", "format": "uuid"}},
+                           "required": ["city"]}},
+    }
+    g = json_schema_to_gbnf(schema)
+    ok = ['{"name":"bob","tags":["a"]}',
+          ' { "name" : "x", "age": -12, "tags": ["a", "c d", "b"] } ',
+          '{"name":"bob","tags":["b"],"address":{"city":"Paris"},"score":null,"kind":"person"}',
+          '{"name":"bob","tags":["b"],"address":{"city":"P","zip":"123e4567-e89b-12d3-a456-426614174000"},"score":1.5e3}',
+          '{"name":"q\\"uote","tags":["a","a"]}']
+    bad = ['{"tags":["a"]}',                                   # required name missing
+           '{"name":"bob"}',                                   # required tags missing
+           '{"name":"","tags":["a"]}',                         # minLength
+           '{"name":"toolongname","tags":["a"]}',              # maxLength
+           '{"name":"bob","tags":[]}',                         # minItems
+           '{"name":"bob","tags":["a","a","a","a"]}',          # maxItems
+           '{"name":"bob","tags":["z"]}',                      # enum
+           '{"name":"bob","age":1.5,"tags":["a"]}',            # integer
+           '{"tags":["a"],"name":"bob"}',                      # declaration order is fixed
+           '{"name":"bob","tags":["a"],"extra":1}',            # no additional properties
+           '{"name":"bob","tags":["a"],"kind":"robot"}',       # const
+           '{"name":"bob","tags":["a"],"address":{}}',         # nested required
+           '{"name":"bob","tags":["a"]', '[1]', 'null']
+    for t in ok:
+        assert _matches(g, t), t
+    for t in bad:
+        assert not _matches(g, t), t
+
+
+def test_json_schema_recursion_additional_properties_and_anyof():
+    from antfly_b200.runtime.json_schema import json_schema_to_gbnf
+
+    tree = {"$ref": "#/definitions/node", "definitions": {"node": {
+        "type": "object", "properties": {"v": {"type": "integer"},
+                                         "kids": {"type": "array", "items": {"$ref": "#/definitions/node"}}},
+        "required": ["v"]}}}
+    g = json_schema_to_gbnf(tree)
+    assert _matches(g, '{"v":1,"kids":[{"v":2},{"v":3,"kids":[{"v":4,"kids":[]}]}]}')
+    assert not _matches(g, '{"v":1,"kids":[{"x":2}]}')
+    free = json_schema_to_gbnf({"type": "object", "properties": {"id": {"type": "integer"}}, "required": ["id"],
+                                "additionalProperties": {"type": "boolean"}})
+    assert _matches(free, '{"id":1,"a":true,"b":false}') and not _matches(free, '{"id":1,"a":3}')
+    assert _matches(free, '{"id":7}') and not _matches(free, '{"a":true}')
+    opt = json_schema_to_gbnf({"type": "object", "properties": {"a": {"type": "null"}, "b": {"type": "boolean"}}})
+    for t in ('{}', '{"a":null}', '{"b":true}', '{"a":null,"b":false}'):
+        assert _matches(opt, t), t
+    assert not _matches(opt, '{"b":true,"a":null}') and not _matches(opt, '{"a":null,}')
+    any_of = json_schema_to_gbnf({"anyOf": [{"type": "string", "format": "date"}, {"type": "array", "maxItems": 0},
+                                            {"type": "object"}]})
+    for t in ('"2024-02-29"', '[]', '{"anything":[1,{"x":null}]}'):
+        assert _matches(any_of, t), t
+    assert not _matches(any_of, '"yesterday"') and not _matches(any_of, '[1]')
+    with pytest.raises(ValueError):
+        json_schema_to_gbnf({"$ref": "http://elsewhere/schema"})
+    with pytest.raises(ValueError):
+        json_schema_to_gbnf({"type": "array", "minItems": 3, "maxItems": 1})
