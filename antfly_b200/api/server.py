@@ -415,6 +415,14 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 except Exception:
                     tool_fmt = "hermes"
                 decl = TC.format_tools_prompt(req.tools, tool_fmt, choice)
+                if not req.grammar and (req.response_format or {}).get("type") is None:
+                    # a forced call is also enforced: the reply can only be a call that fits the function's schema
+                    try:
+                        forced = TC.forced_call_grammar(req.tools, tool_fmt, choice)
+                    except ValueError as e:
+                        return _err(400, "invalid_request", str(e))
+                    if forced:
+                        req = req.model_copy(update={"grammar": forced})
                 if msgs and msgs[0].get("role") == "system":
                     msgs[0] = dict(msgs[0], content=(msgs[0].get("content") or "") + "\n\n" + decl)
                 else:

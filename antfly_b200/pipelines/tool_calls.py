@@ -96,6 +96,30 @@ def format_tools_prompt(tools: List[Dict[str, Any]], fmt: str = "hermes", choice
     return f"You have access to these tools:\n{decl}\n{how}{must}"
 
 
+def forced_call_grammar(tools: List[Dict[str, Any]], fmt: str, choice: ToolChoice) -> Optional[str]:
+    """GBNF grammar that makes the reply one syntactically valid tool call whose arguments validate against the
+    chosen function's parameter schema -- for ``tool_choice`` = "required" (any declared function) or a named
+    function.  None when the choice does not force a call or the format has no JSON call syntax."""
+    from ..runtime.json_schema import json_schema_to_gbnf
+
+    if choice.mode not in ("required", "function") or fmt not in ("hermes", "mistral", "llama3"):
+        return None
+    fns = [t.get("function", t) for t in tools]
+    if choice.mode == "function":
+        fns = [f for f in fns if f.get("name") == choice.function]
+        if not fns:
+            raise ValueError(f"tool_choice names an undeclared function {choice.function!r}")
+    key = "parameters" if fmt == "llama3" else "arguments"
+    calls = {"anyOf": [{"type": "object", "properties": {"name": {"const": f["name"]},
+                                                          key: f.get("parameters") or {"type": "object"}},
+                        "required": ["name", key]} for f in fns]}
+    body = json_schema_to_gbnf(calls)
+    body = body.replace("root ::=", "call ::=", 1)
+    wrap = {"hermes": 'root ::= "<tool_call>" call "</tool_call>"',
+            "mistral": 'root ::= "[TOOL_CALLS] [" call "]"', "llama3": "root ::= call"}[fmt]
+    return wrap + "\n" + body
+
+
 def _relaxed_object(text: str) -> Dict[str, Any]:
     """``{id:42,name:"x",flag:true}`` -> dict.  Accepts strict JSON too."""
     text = text.strip()

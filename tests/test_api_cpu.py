@@ -436,3 +436,22 @@ def test_result_cache_serves_repeated_texts_and_expires():
     m = cl.get("/metrics").text
     assert 'antfly_inference_result_cache_total{endpoint="embed",outcome="hit"} 2.0' in m
     assert 'antfly_inference_result_cache_total{endpoint="rerank",outcome="hit"} 2.0' in m
+
+
+def test_required_tool_choice_always_yields_a_valid_call(client):
+    tools = [{"type": "function", "function": {"name": "set_flag", "parameters": {
+        "type": "object", "properties": {"on": {"type": "boolean"}}, "required": ["on"]}}}]
+    r = client.post("/ai/v1/chat/completions", json={
+        "model": "tiny-gen", "messages": [{"role": "user", "content": "do it"}], "max_tokens": 120, "temperature": 0,
+        "tools": tools, "tool_choice": "required"})
+    assert r.status_code == 200, r.text
+    ch = r.json()["choices"][0]
+    if ch["finish_reason"] == "tool_calls":     # (random weights may spend the budget on optional whitespace)
+        call = ch["message"]["tool_calls"][0]["function"]
+        assert call["name"] == "set_flag" and isinstance(json.loads(call["arguments"])["on"], bool)
+    else:
+        assert ch["finish_reason"] == "length"
+    r = client.post("/ai/v1/chat/completions", json={
+        "model": "tiny-gen", "messages": [{"role": "user", "content": "x"}], "tools": tools,
+        "tool_choice": {"type": "function", "function": {"name": "missing"}}})
+    assert r.status_code == 400

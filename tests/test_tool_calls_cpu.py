@@ -74,3 +74,40 @@ def test_tool_choice_and_prompt_and_detection():
     assert detect_format(None, ["<|python_tag|>"]) == "llama3" and detect_format("plain") == "hermes"
     ids = {c["id"] for c in parse_tool_calls('<tool_call>{"name":"a","arguments":{}}</tool_call><tool_call>{"name":"b","arguments":{}}</tool_call>')[1]}
     assert len(ids) == 2
+
+
+def test_forced_call_grammar_constrains_name_and_arguments():
+    from antfly_b200.pipelines import tool_calls as TC
+    from antfly_b200.runtime.grammar import GbnfGrammar
+
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "unit": {"enum": ["c", "f"]}},
+        "required": ["city"]}}},
+        {"type": "function", "function": {"name": "ping"}}]
+
+    def ok(g, text):
+        m = GbnfGrammar([bytes([i]) for i in range(256)], g)
+        return m.accept_text(text) and m.complete
+
+    g = TC.forced_call_grammar(tools, "hermes", TC.parse_tool_choice("required"))
+    assert ok(g, '<tool_call>{"name":"get_weather","arguments":{"city":"Oslo","unit":"c"}}</tool_call>')
+    assert ok(g, '<tool_call>{"name": "ping", "arguments": {}}</tool_call>')
+    assert not ok(g, '<tool_call>{"name":"get_weather","arguments":{"unit":"c"}}</tool_call>')      # city required
+    assert not ok(g, '<tool_call>{"name":"other","arguments":{}}</tool_call>')
+    assert not ok(g, 'Sure! <tool_call>{"name":"ping","arguments":{}}</tool_call>')
+    one = TC.forced_call_grammar(tools, "mistral", TC.parse_tool_choice(
+        {"type": "function", "function": {"name": "get_weather"}}))
+    assert ok(one, '[TOOL_CALLS] [{"name":"get_weather","arguments":{"city":"x"}}]')
+    assert not ok(one, '[TOOL_CALLS] [{"name":"ping","arguments":{}}]')
+    l3 = TC.forced_call_grammar(tools, "llama3", TC.parse_tool_choice("required"))
+    assert ok(l3, '{"name":"ping","parameters":{"anything":1}}')
+    # what the grammar admits is what the parser extracts
+    text = '<tool_call>{"name":"get_weather","arguments":{"city":"Oslo"}}</tool_call>'
+    _, calls = TC.parse_tool_calls(text, "hermes")
+    assert calls[0]["function"]["name"] == "get_weather"
+    assert TC.forced_call_grammar(tools, "hermes", TC.parse_tool_choice("auto")) is None
+    assert TC.forced_call_grammar(tools, "gemma", TC.parse_tool_choice("required")) is None
+    import pytest
+
+    with pytest.raises(ValueError):
+        TC.forced_call_grammar(tools, "hermes", TC.parse_tool_choice({"type": "function", "function": {"name": "nope"}}))
