@@ -690,14 +690,26 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             if tasks:
                 clf = mgr.get(req.model, "classifier").pipeline
                 known = {v.lower(): v for v in clf.id2label.values()}
+                nli = {"entailment", "contradiction"} <= set(known)
                 ranked = clf.classify(texts, top_k=len(clf.id2label))
-                for rec, scores in zip(data, ranked):
+                for rec in data:
                     rec["classifications"] = []
-                    for t in tasks:
-                        labels = [str(l) for l in t.get("labels") or []]
-                        missing = [l for l in labels if l.lower() not in known]
-                        if missing:
-                            raise ValueError(f"classification {t.get('name')!r}: model has no label(s) {missing}")
+                for t in tasks:
+                    labels = [str(l) for l in t.get("labels") or []]
+                    missing = [l for l in labels if l.lower() not in known]
+                    if missing and nli:
+                        # labels the model was not trained on: zero-shot through entailment
+                        from ..pipelines.classification import ZeroShotClassifier
+
+                        zs = ZeroShotClassifier(clf.model, clf.tokenizer, clf.id2label,
+                                                opts.get("hypothesis_template", "This example is {}."))
+                        for rec, scores in zip(data, zs.classify(texts, labels, bool(t.get("multi_label")))):
+                            keep = [s for s in scores if s["score"] >= thr] if t.get("multi_label") else scores[:1]
+                            rec["classifications"] += [{"name": t.get("name", ""), **s} for s in keep]
+                        continue
+                    if missing:
+                        raise ValueError(f"classification {t.get('name')!r}: model has no label(s) {missing}")
+                    for rec, scores in zip(data, ranked):
                         cand = [s for s in scores if s["label"].lower() in {l.lower() for l in labels}]
                         keep = [s for s in cand if s["score"] >= thr] if t.get("multi_label") else cand[:1]
                         for s in keep:

@@ -51,6 +51,41 @@ class TextClassifier:
         return self.classify_ids([self.tokenizer.encode_for_model(t, self.max_length) for t in texts], top_k)
 
 
+class ZeroShotClassifier:
+    """Labels the model was never trained on, through a natural-language-inference cross-encoder: every (text,
+    label) pair becomes premise = text, hypothesis = ``template.format(label)``; a label's score is the probability
+    of *entailment* against *contradiction* for that pair, normalised over the labels (single-label) or taken as is
+    (multi-label).  The reference's classification pipeline offers the same mode for NLI checkpoints
+    (zig/pkg/inference/src/pipelines/classification.zig zero-shot path)."""
+
+    def __init__(self, model, tokenizer, id2label: Dict[int, str], template: str = "This example is {}.",
+                 max_length: int = 512):
+        names = {v.lower(): k for k, v in id2label.items()}
+        if "entailment" not in names or "contradiction" not in names:
+            raise ValueError("zero-shot classification needs a model with entailment / contradiction labels")
+        self.ent, self.con = names["entailment"], names["contradiction"]
+        self.model, self.tokenizer, self.template, self.max_length = model, tokenizer, template, max_length
+
+    def classify(self, texts: Sequence[str], labels: Sequence[str], multi_label: bool = False) -> List[List[dict]]:
+        tk = self.tokenizer
+        seqs, types = [], []
+        for t in texts:
+            for lab in labels:
+                ids, ty = tk.encode_pair(t, self.template.format(lab), self.max_length)
+                seqs.append(ids), types.append(ty)
+        b = pack_sequences(seqs, types, position_offset=self.model.cfg.position_offset)
+        logits = self.model.classify(b.to(self.model.device)).float().cpu()
+        pair = torch.softmax(logits[:, [self.con, self.ent]], -1)[:, 1].view(len(texts), len(labels))
+        if not multi_label:
+            ent = logits[:, self.ent].view(len(texts), len(labels))
+            pair = torch.softmax(ent, -1)
+        out = []
+        for row in pair:
+            order = torch.argsort(row, descending=True)
+            out.append([{"label": labels[int(i)], "score": float(row[int(i)])} for i in order])
+        return out
+
+
 def aggregate_bio(tags: Sequence[str], scores: Sequence[float], is_special: Optional[Sequence[bool]] = None,
                   is_continuation: Optional[Sequence[bool]] = None) -> List[Entity]:
     """Merge per-token BIO tags into entity spans.  ``is_special`` tokens never start or extend an entity;

@@ -346,6 +346,18 @@ def test_rewrite_and_extract_endpoints(tmp_path):
         "classifications": [{"name": "t", "labels": ["sarcastic"]}]}}).status_code == 400
     assert c.post("/ai/v1/extract", json={"model": "tiny-clf", "inputs": [{"content": "x"}],
                                          "schema": {}}).status_code == 400
+    # a model with entailment / contradiction labels classifies against labels it never saw (zero-shot)
+    _write_bert(tmp_path / "classifiers" / "tiny-nli", 3, ["contradiction", "neutral", "entailment"], 4)
+    r = c.post("/ai/v1/extract", json={"model": "tiny-nli", "inputs": [{"content": "the team won"}, {"content": "y"}],
+                                      "schema": {"classifications": [
+                                          {"name": "topic", "labels": ["sports", "politics", "cooking"]},
+                                          {"name": "tone", "labels": ["happy", "sad"], "multi_label": True}]}})
+    assert r.status_code == 200, r.text
+    for d in r.json()["data"]:
+        topic = [x for x in d["classifications"] if x["name"] == "topic"]
+        tone = [x for x in d["classifications"] if x["name"] == "tone"]
+        assert len(topic) == 1 and topic[0]["label"] in ("sports", "politics", "cooking") and 0 < topic[0]["score"] <= 1
+        assert all(x["label"] in ("happy", "sad") and 0 <= x["score"] <= 1 for x in tone) and len(tone) == 2
 
 
 def test_anthropic_messages_and_openai_path_compat(client):
