@@ -170,6 +170,7 @@ class LlamaModel:
         self.vocab_offset = tp_rank * self.vocab_local if tp_size > 1 else 0
         self._scratch: Dict[tuple, torch.Tensor] = {}
         self.moe_runtime = None   # set by offload_experts(): expert weights live in host memory
+        self.ep = None            # set by set_expert_parallel(): (rank, size, process group)
         self.pp = None            # set by set_pipeline(): this model is one stage of a layer pipeline
         self.layer_lo = 0
 
@@ -231,10 +232,12 @@ class LlamaModel:
 
     @classmethod
     def from_state_dict(cls, cfg: LlamaConfig, sd: Dict[str, torch.Tensor], device="cuda", tp_rank: int = 0,
-                        tp_size: int = 1, comm=None, layers: Optional[tuple] = None) -> "LlamaModel":
+                        tp_size: int = 1, comm=None, layers: Optional[tuple] = None,
+                        experts: Optional[tuple] = None) -> "LlamaModel":
         """HF names (model.layers.N.self_attn.{q,k,v,o}_proj, mlp.{gate,up,down}_proj, ...) -> fused, sharded,
         block-fp8 packed layout.  ``layers`` = (first, last) loads only that range of decoder layers (a pipeline
-        stage); the stage is then wired with :meth:`set_pipeline`."""
+        stage); the stage is then wired with :meth:`set_pipeline`.  ``experts`` = (rank, size) loads only the routed
+        experts ``e`` with ``e % size == rank`` (expert parallelism, wired with :meth:`set_expert_parallel`)."""
         from ..parallel.sharding import shard_rows, shard_cols
 
         D = cfg.head_dim
@@ -272,6 +275,8 @@ class LlamaModel:
                 w[p + "router"] = sd[moe + "gate.weight"].to(torch.bfloat16).to(device)
                 Fm = cfg.moe_intermediate_size
                 for e in range(cfg.num_experts):
+                    if experts is not None and e % experts[1] != experts[0]:
+                        continue
                     if moe + "experts.gate_up_proj" in sd:      # fused [E, 2F, H] (gate rows, then up rows) / [E, H, F]
                         gu = sd[moe + "experts.gate_up_proj"][e]
                         g_e, u_e, d_e = gu[:Fm], gu[Fm:], sd[moe + "experts.down_proj"][e]
@@ -426,6 +431,14 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    def set_expert_parallel(self, rank: int, size: int, group=None) -> None:
+        """Expert parallelism for mixture-of-experts layers: every rank runs the attention and the router on the
+        same tokens (so the routing is identical everywhere), computes only the experts it holds
+        (``e % size == rank``) and the partial outputs are summed across ranks with one all-reduce per MoE layer.
+        Expert weights, the bulk of a MoE checkpoint, are thereby split ``size`` ways with no token exchange; the
+        shared expert, if any, is computed on every rank after the reduction."""
+        self.ep = (rank, size, group)
+
     def set_pipeline(self, stage, first_layer: int, last_layer: int) -> None:
         """Make this model one stage of a pipeline over decoder layers [first_layer, last_layer): the first stage
         embeds the tokens, every stage runs its layers on the hidden states it receives and passes them on, the
@@ -464,17 +477,25 @@ class LlamaModel:
         out = torch.zeros((T, h.shape[1]), dtype=torch.float32, device=h.device)
         batches = route_batches(topi, topv, cfg.num_experts)
         rt = self.moe_runtime
+        mine = (lambda e: True) if self.ep is None else (lambda e: e % self.ep[1] == self.ep[0])
         if rt is not None:  # offloaded experts: load what this step needs, prefetch what the next is likely to
-            ws = rt.residency.ensure(l, batches.active)
+            active = [e for e in batches.active if mine(e)]
+            ws = rt.residency.ensure(l, active)
             rt.predictor.note(l, cfg.num_experts, batches.active)
-            rt.residency.prefetch(l, rt.predictor.predict(l, batches.active, rt.max_predicted)[0],
-                                  protect=batches.active)
+            rt.residency.prefetch(l, [e for e in rt.predictor.predict(l, batches.active, rt.max_predicted)[0]
+                                      if mine(e)], protect=active)
         for e, rows, wts in batches:
+            if not mine(e):
+                continue                       # another rank's expert
             gu, down = (ws[e]["gu"], ws[e]["down"]) if rt is not None else (w[p + f"e{e}.gu"], w[p + f"e{e}.down"])
             xe = h.index_select(0, rows)
             act = self._linear(xe, gu, rows.numel(), swiglu=True)
             ye = self._linear(act, down, rows.numel()).float()
             out.index_add_(0, rows, ye * wts[:, None])
+        if self.ep is not None:
+            import torch.distributed as dist
+
+            dist.all_reduce(out, group=self.ep[2])
         if p + "shared.gu" in w:
             act = self._linear(h, w[p + "shared.gu"], T, swiglu=True)
             ys = self._linear(act, w[p + "shared.down"], T).float()

@@ -6,6 +6,8 @@ replicate the graph and shard the weights by the Megatron rules.  The plan here 
 decoder layers: which layers a rank runs (pipeline) or which slice of every layer it holds (tensor), checked against
 the divisibility the kernels need.  ``tensor`` plans run through the fused tensor-parallel kernels; ``pipeline``
 plans through :mod:`antfly_b200.parallel.pipeline` (layer ranges per rank, hidden states sent rank to rank).
+Mixture-of-experts checkpoints can additionally split their routed experts across ranks
+(``LlamaModel.set_expert_parallel``: replicated routing, local experts, one all-reduce per MoE layer).
 """
 from __future__ import annotations
 

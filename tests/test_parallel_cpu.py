@@ -184,7 +184,7 @@ def _pp_worker(rank, world, port, q):
     # the same stages drive the serving engine in lockstep: every rank generates the same tokens
     eng = LLMEngine(model, num_blocks=16, page=16, max_batch=2, use_cuda_graph=False)
     out = eng.generate([[5, 6, 7, 8, 9], [11, 12]], SamplingParams(max_tokens=5, ignore_eos=True))
-    q.put((rank, logits, [o.token_ids for o in out], model.pp.sent_bytes, model.pp.received_bytes))
+    q.put((rank, logits.numpy(), [o.token_ids for o in out], model.pp.sent_bytes, model.pp.received_bytes))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -230,6 +230,61 @@ def test_pipeline_parallel_stages_match_single_rank(world):
     want = [o.token_ids for o in eng.generate([[5, 6, 7, 8, 9], [11, 12]], SamplingParams(max_tokens=5,
                                                                                             ignore_eos=True))]
     for rank, logits, toks, sent, recv in got:
-        torch.testing.assert_close(logits, ref, atol=6e-2, rtol=5e-2)
+        torch.testing.assert_close(torch.from_numpy(logits), ref, atol=6e-2, rtol=5e-2)
         assert toks == want
         assert (sent > 0) == (rank < world - 1) and (recv > 0) == (rank > 0)
+
+
+def _moe_state():
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    hf_cfg = transformers.MixtralConfig(vocab_size=320, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                                        num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                                        num_local_experts=6, num_experts_per_tok=2)
+    hf = transformers.MixtralForCausalLM(hf_cfg)
+    return hf_cfg.to_dict(), {k: v.detach().clone() for k, v in hf.state_dict().items()}
+
+
+def _ep_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    cfg_d, sd = _moe_state()
+    cfg = LlamaConfig.from_hf(cfg_d)
+    model = LlamaModel.from_state_dict(cfg, sd, device="cpu", experts=(rank, world))
+    model.set_expert_parallel(rank, world)
+    held = sorted({int(k.split(".e")[1].split(".")[0]) for k in model.w if ".e" in k and k.endswith(".gu")})
+    assert held == [e for e in range(6) if e % world == rank]
+    if rank == 1:
+        model.offload_experts(max_resident_per_layer=1)          # expert parallelism composes with host offload
+    logits = _forward_logits(model, cfg)
+    q.put((rank, logits.numpy()))          # by value: the worker may exit before the parent reads
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_expert_parallel_moe_matches_single_rank(world):
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    cfg_d, sd = _moe_state()
+    cfg = LlamaConfig.from_hf(cfg_d)
+    ref = _forward_logits(LlamaModel.from_state_dict(cfg, sd, device="cpu"), cfg)
+    for _rank, logits in got:
+        logits = torch.from_numpy(logits)
+        # same experts, same tokens; only the order of the fp32 sums over experts differs
+        torch.testing.assert_close(logits, ref, atol=3e-2, rtol=3e-2)
+        assert logits.argmax(-1).tolist() == ref.argmax(-1).tolist()
