@@ -179,7 +179,7 @@ class ModelManager:
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         else:
-            if cfg_d.get("model_type") in ("gpt2", "gpt_neo", "gpt_neox", "opt", "gptj", "phi", "falcon"):
+            if cfg_d.get("model_type") in ("gpt2", "gpt_neo", "gpt_neox", "opt", "gptj", "phi", "falcon", "bloom"):
                 from ..models.gpt import GptConfig, GptModel
 
                 model = GptModel.from_state_dict(GptConfig.from_hf(cfg_d), sd, device=self.device)

@@ -19,6 +19,9 @@ What differs from the Llama family and how it maps onto the existing kernels (th
 * Falcon: multi-query (one shared K / V head) or grouped K / V heads, rotary positions, bias-free linears, the
   parallel block with one shared LayerNorm (7B) or two (``new_decoder_architecture``), whose fused QKV rows are
   grouped per K / V head and are regrouped at load time.  ALiBi variants are not supported.
+* BLOOM: a LayerNorm on the token embeddings, no position embeddings at all -- attention scores get the ALiBi bias
+  ``slope_h * (key - query)`` instead.  The paged flash kernel has no bias input, so this family's attention runs
+  through the tensor-op reference path on either device (correct, not a tuned path).
 """
 from __future__ import annotations
 
@@ -29,13 +32,14 @@ import torch
 
 from ..ops import attention as A
 from ..ops import dense as Dn
+from ..ops import reference as R
 from ..ops import sampling as S
 from .llama import StepBatch
 
 
 @dataclass
 class GptConfig:
-    family: str = "gpt2"              # gpt2 | gpt_neo | gpt_neox | opt | gptj | phi | falcon
+    family: str = "gpt2"              # gpt2 | gpt_neo | gpt_neox | opt | gptj | phi | falcon | bloom
     vocab_size: int = 50257
     hidden_size: int = 768
     num_hidden_layers: int = 12
@@ -55,6 +59,7 @@ class GptConfig:
     num_kv_heads: int = 0             # 0: one K / V head per query head; Falcon: 1 (multi-query) or a group count
     attn_scale: float = 0.0           # 0: 1 / sqrt(head_dim); GPT-Neo: 1
     layer_windows: Optional[List[int]] = None   # per-layer sliding window (0 = global); GPT-Neo's local layers
+    alibi: bool = False               # BLOOM: linear position bias on the scores, no position embeddings
 
     # Names the engine reads from every decoder config.
     @property
@@ -119,6 +124,12 @@ class GptConfig:
                        d.get("layer_norm_epsilon", 1e-5), act[d.get("activation_function", "gelu_new")],
                        tie_word_embeddings=d.get("tie_word_embeddings", True), attn_scale=1.0,
                        layer_windows=[win if k == "local" else 0 for k in kinds[:L]])
+        if mt == "bloom":
+            H = d.get("hidden_size", d.get("n_embed"))
+            return cls("bloom", d["vocab_size"], H, d.get("n_layer", d.get("num_hidden_layers")),
+                       d.get("n_head", d.get("num_attention_heads")), 4 * H, 1 << 20,
+                       d.get("layer_norm_epsilon", 1e-5), "gelu_tanh",
+                       tie_word_embeddings=d.get("tie_word_embeddings", True), alibi=True)
         if mt == "falcon":
             if d.get("alibi"):
                 raise ValueError("Falcon checkpoints with ALiBi positions are not supported")
@@ -154,6 +165,7 @@ class GptModel:
         self.rope_dim = int(round(self.D * cfg.rotary_pct)) if cfg.rotary_pct > 0 else 0
         self.vocab_local, self.vocab_offset = weights["lm_head"].shape[0], 0
         self._zero_pos: Optional[torch.Tensor] = None
+        self._alibi: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------------------------------------------
     @classmethod
@@ -239,6 +251,28 @@ class GptModel:
                 w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.fc2.weight"]), t(sd[s + "mlp.fc2.bias"])
             w["lnf.g"], w["lnf.b"] = t(sd[pre + "final_layernorm.weight"]), t(sd[pre + "final_layernorm.bias"])
             w["lm_head"], w["lm_head.b"] = t(sd["lm_head.weight"]), t(sd["lm_head.bias"])
+        elif cfg.family == "bloom":
+            pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
+            w["embed"] = t(sd[pre + "word_embeddings.weight"])
+            w["embed.ln.g"] = t(sd[pre + "word_embeddings_layernorm.weight"])
+            w["embed.ln.b"] = t(sd[pre + "word_embeddings_layernorm.bias"])
+            for l in range(cfg.num_hidden_layers):
+                s, p = f"{pre}h.{l}.", f"l{l}."
+                w[p + "ln1.g"], w[p + "ln1.b"] = t(sd[s + "input_layernorm.weight"]), t(sd[s + "input_layernorm.bias"])
+                w[p + "ln2.g"], w[p + "ln2.b"] = t(sd[s + "post_attention_layernorm.weight"]), t(
+                    sd[s + "post_attention_layernorm.bias"])
+                a = s + "self_attention."
+                # rows are [head][q | k | v][D], as in GPT-NeoX
+                w[p + "qkv.w"] = t(sd[a + "query_key_value.weight"].view(nh, 3, D, H).permute(1, 0, 2, 3).reshape(
+                    3 * H, H))
+                w[p + "qkv.b"] = t(sd[a + "query_key_value.bias"].view(nh, 3, D).permute(1, 0, 2).reshape(3 * H))
+                w[p + "o.w"], w[p + "o.b"] = t(sd[a + "dense.weight"]), t(sd[a + "dense.bias"])
+                w[p + "fc.w"], w[p + "fc.b"] = t(sd[s + "mlp.dense_h_to_4h.weight"]), t(sd[s + "mlp.dense_h_to_4h.bias"])
+                w[p + "proj.w"], w[p + "proj.b"] = t(sd[s + "mlp.dense_4h_to_h.weight"]), t(
+                    sd[s + "mlp.dense_4h_to_h.bias"])
+            w["lnf.g"], w["lnf.b"] = t(sd[pre + "ln_f.weight"]), t(sd[pre + "ln_f.bias"])
+            w["lm_head"] = t(sd["lm_head.weight"]) if "lm_head.weight" in sd and not cfg.tie_word_embeddings else \
+                w["embed"]
         elif cfg.family == "gpt_neo":
             pre = "transformer." if any(k.startswith("transformer.") for k in sd) else ""
             w["embed"], w["pos"] = t(sd[pre + "wte.weight"]), t(sd[pre + "wpe.weight"])
@@ -332,8 +366,11 @@ class GptModel:
         T = b.ids.numel()
         act = _ACT[cfg.activation]
         x = Dn.embed_gather(b.ids, w["embed"])
-        if "pos" in w:
-            x = x + w["pos"].index_select(0, (b.positions + cfg.position_offset).long())
+        if "embed.ln.g" in w:
+            x = Dn.norm(x, w["embed.ln.g"], w["embed.ln.b"], eps=eps, rms=False)
+        if "pos" in w or cfg.alibi:
+            if "pos" in w:
+                x = x + w["pos"].index_select(0, (b.positions + cfg.position_offset).long())
             if self._zero_pos is None or self._zero_pos.numel() < T:
                 self._zero_pos = torch.zeros(max(T, 1024), dtype=torch.int32, device=x.device)
             rope_pos, rope_dim = self._zero_pos[:T], D  # identity rotation: the kernel only writes K / V
@@ -346,9 +383,15 @@ class GptModel:
             q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 rope_dim=rope_dim, half_split=cfg.rope_half_split)
             window = cfg.layer_windows[l] if cfg.layer_windows else cfg.sliding_window
-            ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, scale=scale, window=window, num_splits=b.attn_splits,
-                                    scratch=attn_scratch)
+            if cfg.alibi:
+                if self._alibi is None:
+                    self._alibi = R.alibi_slopes(Hq).to(q.device)
+                ctx = R.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                        scale, window, alibi=self._alibi).to(q.dtype)
+            else:
+                ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                        b.max_q_len, scale=scale, window=window, num_splits=b.attn_splits,
+                                        scratch=attn_scratch)
             if cfg.parallel_residual:
                 # x + attn(ln1 x) + mlp(ln2 x): both branches read the same x
                 a_out = Dn.gemm_bf16(ctx.view(T, Hq * D), w[p + "o.w"], bias=w[p + "o.b"], residual=x)
@@ -363,6 +406,12 @@ class GptModel:
         rows = x if b.logit_rows.numel() == T else x.index_select(0, b.logit_rows.long())
         hl = Dn.norm(rows, w["lnf.g"], w["lnf.b"], eps=eps, rms=False)
         return Dn.gemm_bf16(hl, w["lm_head"], bias=w.get("lm_head.b"))
+
+    @property
+    def graph_safe(self) -> bool:
+        """False when a step reads sizes back to the host (the tensor-op attention of the ALiBi family), which a
+        CUDA graph cannot capture."""
+        return not self.cfg.alibi
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
         return S.argmax(logits)

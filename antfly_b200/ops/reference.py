@@ -177,8 +177,20 @@ def varlen_attention(q, k, v, cu_seqlens, scale=None, causal=False, window=0):
     return out
 
 
+def alibi_slopes(num_heads: int) -> torch.Tensor:
+    """Per-head ALiBi slopes: a geometric sequence starting at 2^(-8 / n) for n = the largest power of two <= heads,
+    with the remaining heads interleaved from the sequence for 2n (Press et al., as used by BLOOM / MPT)."""
+    n = 2 ** math.floor(math.log2(num_heads))
+    base = 2.0 ** (-(2.0 ** -(math.log2(n) - 3)))
+    slopes = [base ** (i + 1) for i in range(n)]
+    if n < num_heads:
+        extra = 2.0 ** (-(2.0 ** -(math.log2(2 * n) - 3)))
+        slopes += [extra ** (2 * i + 1) for i in range(num_heads - n)]
+    return torch.tensor(slopes, dtype=torch.float32)
+
+
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale=None,
-                    sliding_window: int = 0):
+                    sliding_window: int = 0, alibi: Optional[torch.Tensor] = None):
     """Causal attention of packed query tokens against a paged KV cache.
 
     q: [T, Hq, D]; k_cache / v_cache: [num_blocks, page, Hkv, D]; block_tables: [B, max_blocks] int32;
@@ -186,6 +198,7 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
     sequence whose total length (already written to the cache) is kv_lens[b].  Matches the masks of the
     reference's gqaPagedAttentionDirect (zig/pkg/inference/src/ops/native_compute.zig:35093-35173): query at
     absolute position p sees keys at positions <= p, and > p - sliding_window when a window is set.
+    ``alibi`` [Hq] adds ``slope_h * (key position - query position)`` to the scores (linear position bias).
     """
     T, Hq, D = q.shape
     page, Hkv = k_cache.shape[1], k_cache.shape[2]
@@ -206,6 +219,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
         sc = qq @ kk.transpose(1, 2) * scale  # [Hq, ql, kl]
         qpos = torch.arange(kl - ql, kl, device=q.device)[:, None]
         kpos = torch.arange(kl, device=q.device)[None, :]
+        if alibi is not None:
+            sc = sc + alibi.to(sc.device).float()[:, None, None] * (kpos - qpos).float()[None]
         m = kpos <= qpos
         if sliding_window > 0:
             m = m & (kpos > qpos - sliding_window)

@@ -176,6 +176,14 @@ def _hf_gpt(kind: str):
                                      num_attention_heads=4, max_position_embeddings=64, partial_rotary_factor=0.5,
                                      resid_pdrop=0.0, embd_pdrop=0.0, attention_dropout=0.0)
         return cfg, transformers.PhiForCausalLM(cfg)
+    if kind == "bloom":
+        cfg = transformers.BloomConfig(vocab_size=300, hidden_size=64, n_layer=2, n_head=6 if False else 4,
+                                       hidden_dropout=0.0, attention_dropout=0.0)
+        return cfg, transformers.BloomForCausalLM(cfg)
+    if kind == "bloom6":
+        cfg = transformers.BloomConfig(vocab_size=300, hidden_size=96, n_layer=2, n_head=6, hidden_dropout=0.0,
+                                       attention_dropout=0.0)
+        return cfg, transformers.BloomForCausalLM(cfg)
     if kind == "gpt_neo":
         cfg = transformers.GPTNeoConfig(vocab_size=300, hidden_size=64, num_layers=4, num_heads=4, intermediate_size=128,
                                         max_position_embeddings=64, window_size=6,
@@ -199,7 +207,7 @@ def _hf_gpt(kind: str):
 
 
 @pytest.mark.parametrize("kind", ["gpt2", "neox_parallel", "neox_sequential", "opt", "gptj", "phi", "gpt_neo",
-                                  "falcon_mq", "falcon_mha", "falcon_new", "falcon_seq"])
+                                  "falcon_mq", "falcon_mha", "falcon_new", "falcon_seq", "bloom", "bloom6"])
 def test_layernorm_decoders_match_transformers(kind):
     from antfly_b200.models.gpt import GptConfig, GptModel
 
