@@ -129,14 +129,20 @@ class ModelManager:
 
             model = LlamaModel.from_state_dict(LlamaConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = DecoderEmbedder(model, tok)
-        elif task == "rewriter" or (task == "generator" and cfg_d.get("model_type") in ("t5", "mt5")):
+        elif task == "rewriter" or (task == "generator" and cfg_d.get("model_type") in ("t5", "mt5", "bart",
+                                                                                         "mbart")):
             from ..models.t5 import T5Config, T5Model
             from ..pipelines.seq2seq import Seq2SeqGenerator
 
-            if cfg_d.get("model_type") not in ("t5", "mt5"):
-                raise ModelNotFound(f"{name}: rewriters are T5-family encoder-decoder models "
+            if cfg_d.get("model_type") in ("bart", "mbart"):
+                from ..models.bart import BartConfig, BartModel
+
+                model = BartModel.from_state_dict(BartConfig.from_hf(cfg_d), sd, device=self.device)
+            elif cfg_d.get("model_type") in ("t5", "mt5"):
+                model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
+            else:
+                raise ModelNotFound(f"{name}: rewriters are T5- or BART-family encoder-decoder models "
                                     f"(found {cfg_d.get('model_type')!r})")
-            model = T5Model.from_state_dict(T5Config.from_hf(cfg_d), sd, device=self.device)
             pipe = Seq2SeqGenerator(model, tok)
         elif task == "transcriber":
             import json as _json

@@ -663,8 +663,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             texts = [text_of(i.content) for i in req.inputs]
             want_ents = [str(x) for x in schema.get("entities") or []]
             tasks = schema.get("classifications") or []
-            if not want_ents and not tasks:
-                raise ValueError("schema needs entities and / or classifications")
+            rel_schema = schema.get("relations") or []
+            if not want_ents and not tasks and not rel_schema:
+                raise ValueError("schema needs entities, relations and / or classifications")
             data = [{"id": i.id} if i.id is not None else {} for i in req.inputs]
             ntok = 0
             if want_ents:
@@ -687,6 +688,21 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                         if not opts.get("include_confidence", True):
                             item.pop("score")
                         rec["entities"].append(item)
+            if rel_schema:
+                # relation extraction: a sequence-to-sequence model writes triplets, which are parsed back
+                from ..pipelines.relations import RelationExtractor
+
+                rx = RelationExtractor(mgr.get(req.model, "rewriter").pipeline,
+                                       int(opts.get("max_tokens", 256) or 256))
+                types = [str(r.get("type")) for r in rel_schema if isinstance(r, dict) and r.get("type")]
+                for rec, text in zip(data, texts):
+                    ents, rels = rx.extract(text, types or None)
+                    base = len(rec.get("entities", []))
+                    for r in rels:
+                        r["source"]["entity_index"] += base
+                        r["target"]["entity_index"] += base
+                    rec["entities"] = rec.get("entities", []) + ents
+                    rec["relations"] = rels
             if tasks:
                 clf = mgr.get(req.model, "classifier").pipeline
                 known = {v.lower(): v for v in clf.id2label.values()}

@@ -10,9 +10,18 @@ from __future__ import annotations
 import time
 from typing import Callable, List, Optional
 
-from ..models.t5 import T5Model
+from ..models.t5 import T5Model  # noqa: F401  (the pipeline also drives BartModel: same interface)
 from ..runtime.sampling_params import SamplingParams
 from .generation import GenerationOutput
+
+
+def _takes_skip(tokenizer) -> bool:
+    import inspect
+
+    try:
+        return "skip_special" in inspect.signature(tokenizer.decode).parameters
+    except (TypeError, ValueError):
+        return False
 
 
 class Seq2SeqGenerator:
@@ -26,7 +35,9 @@ class Seq2SeqGenerator:
         return ids + [eos]                                     # T5 inputs end with </s>
 
     def generate(self, messages_or_prompt, params: Optional[SamplingParams] = None, raw_prompt: bool = False,
-                 on_delta: Optional[Callable[[str], None]] = None) -> GenerationOutput:
+                 on_delta: Optional[Callable[[str], None]] = None, keep_special: bool = False) -> GenerationOutput:
+        """``keep_special`` decodes marker tokens too (relation-extraction checkpoints write their structure with
+        added special tokens)."""
         t0 = time.perf_counter()
         if isinstance(messages_or_prompt, str):
             text = messages_or_prompt
@@ -43,19 +54,25 @@ class Seq2SeqGenerator:
         max_new = params.max_tokens if params is not None else 64
         state = self.model.start_decoding(self.model.encode(ids))
         t2 = time.perf_counter()
-        tok, out, emitted, reason = self.model.cfg.decoder_start_token_id, [], "", "length"
+        cfg = self.model.cfg
+        forced = getattr(cfg, "forced_bos_token_id", -1)
+        feed = [cfg.decoder_start_token_id] + ([forced] if forced is not None and forced >= 0 else [])
+        out, emitted, reason = [], "", "length"
+        dec = (lambda ids: self.tokenizer.decode(ids, skip_special=False)) if keep_special and _takes_skip(
+            self.tokenizer) else self.tokenizer.decode
         for _ in range(max_new):
-            tok = int(self.model.decode(state, [tok])[-1].argmax())
+            tok = int(self.model.decode(state, feed)[-1].argmax())
+            feed = [tok]
             if tok == self.model.cfg.eos_token_id:
                 reason = "stop"
                 break
             out.append(tok)
             if on_delta is not None:
-                full = self.tokenizer.decode(out)
+                full = dec(out)
                 if not full.endswith("�") and len(full) > len(emitted):
                     on_delta(full[len(emitted):])
                     emitted = full
         t3 = time.perf_counter()
-        return GenerationOutput(self.tokenizer.decode(out), out, reason, len(ids), len(out), {
+        return GenerationOutput(dec(out), out, reason, len(ids), len(out), {
             "prompt_format": 0.0, "tokenize": (t1 - t0) * 1e3, "prefill": (t2 - t1) * 1e3,
             "decode": (t3 - t2) * 1e3, "total": (t3 - t0) * 1e3})

@@ -84,8 +84,8 @@ class HFTokenizer(Tokenizer):
     def encode(self, text: str) -> List[int]:
         return self.tk.encode(text, add_special_tokens=False).ids
 
-    def decode(self, ids: Sequence[int]) -> str:
-        return self.tk.decode(list(ids), skip_special_tokens=True)
+    def decode(self, ids: Sequence[int], skip_special: bool = True) -> str:
+        return self.tk.decode(list(ids), skip_special_tokens=skip_special)
 
     # -- exact byte string of one token (grammar-constrained decoding needs bytes, not lossy text) -----------------
     _byte_decoder: Optional[Dict[str, int]] = None

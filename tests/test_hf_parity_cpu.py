@@ -540,3 +540,50 @@ def test_whisper_matches_transformers():
     want_f = torch.from_numpy(fe(x.numpy(), sampling_rate=16000, return_tensors="np")["input_features"][0])
     got_f = AO.log_mel(x)
     assert got_f.shape == (80, 3000) and float((got_f - want_f).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("scale", [False, True])
+def test_bart_matches_transformers(scale):
+    """Post-LayerNorm encoder-decoder with offset learned positions, embedding LayerNorm (and optional embedding
+    scale), cross attention, shared output projection with a logit bias; cached decoding and greedy output."""
+    from antfly_b200.models.bart import BartConfig, BartModel
+
+    torch.manual_seed(7)
+    hf_cfg = transformers.BartConfig(vocab_size=300, d_model=64, encoder_layers=2, decoder_layers=2,
+                                     encoder_attention_heads=4, decoder_attention_heads=4, encoder_ffn_dim=128,
+                                     decoder_ffn_dim=128, max_position_embeddings=64, scale_embedding=scale,
+                                     dropout=0.0, attention_dropout=0.0, activation_dropout=0.0, pad_token_id=1,
+                                     bos_token_id=0, eos_token_id=2, decoder_start_token_id=2,
+                                     forced_eos_token_id=None)
+    hf = transformers.BartForConditionalGeneration(hf_cfg).eval()
+    with torch.no_grad():
+        hf.final_logits_bias.normal_(0, 0.5)
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+            elif "layer_norm" not in n and "layernorm" not in n:
+                p.mul_(3.0)
+    cfg = BartConfig.from_hf(hf_cfg.to_dict())
+    model = BartModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    src = [0] + torch.randint(3, 300, (30,)).tolist() + [2]
+    tgt = [2, 0] + torch.randint(3, 300, (9,)).tolist()
+    with torch.no_grad():
+        out = hf(input_ids=torch.tensor([src]), decoder_input_ids=torch.tensor([tgt]))
+    enc = model.encode(src)
+    ref = out.encoder_last_hidden_state[0]
+    assert float((enc.float() - ref).norm() / ref.norm()) < 0.02
+    full = model.decode(model.start_decoding(enc), tgt)
+    assert float((full - out.logits[0]).norm() / out.logits[0].norm()) < 0.03
+    assert float((full.argmax(-1) == out.logits[0].argmax(-1)).float().mean()) >= 0.9
+    state = model.start_decoding(enc)
+    step = torch.cat([model.decode(state, [t]) for t in tgt])
+    assert float((step - full).norm() / full.norm()) < 0.02
+    dec, want = [2], []
+    with torch.no_grad():
+        for _ in range(8):
+            nxt = int(hf(input_ids=torch.tensor([src]), decoder_input_ids=torch.tensor([dec])).logits[0, -1].argmax())
+            if nxt == 2:
+                break
+            want.append(nxt)
+            dec.append(nxt)
+    assert model.generate(src, max_new_tokens=8) == want

@@ -179,3 +179,44 @@ def test_seq2seq_pipeline_t5_greedy_and_streaming():
     assert "".join(deltas) == out.text or out.text.endswith("�")
     out2 = pipe.generate([{"role": "user", "content": "rewrite: where is the cat"}], SamplingParams(max_tokens=12))
     assert out2.token_ids == out.token_ids
+
+
+def test_relation_triplets_are_parsed_from_linearised_text():
+    from antfly_b200.pipelines.relations import Triplet, parse_triplets, to_extraction
+
+    text = ("<s><triplet> Punta Cana <subj> Dominican Republic <obj> country <subj> La Altagracia <obj> located in "
+            "<triplet> Dominican Republic <subj> Punta Cana <obj> contains <triplet> dangling <subj> no relation</s>")
+    tr = parse_triplets(text)
+    assert tr == [Triplet("Punta Cana", "country", "Dominican Republic"),
+                  Triplet("Punta Cana", "located in", "La Altagracia"),
+                  Triplet("Dominican Republic", "contains", "Punta Cana")]
+    assert parse_triplets("no markers at all") == [] and parse_triplets("<triplet> a <subj> b") == []
+    assert parse_triplets("<triplet> a <subj> b <obj> r <triplet> a <subj> b <obj> r") == [Triplet("a", "r", "b")]
+    src = "Punta Cana is a resort town in the Dominican Republic."
+    ents, rels = to_extraction(tr, src, allowed=["COUNTRY", "contains"])
+    assert [e["text"] for e in ents] == ["Punta Cana", "Dominican Republic"]
+    assert src[ents[1]["start"]:ents[1]["end"]] == "Dominican Republic"
+    assert rels == [{"type": "country", "source": {"entity_index": 0}, "target": {"entity_index": 1}},
+                    {"type": "contains", "source": {"entity_index": 1}, "target": {"entity_index": 0}}]
+
+
+def test_seq2seq_pipeline_drives_bart_with_a_forced_first_token():
+    import torch
+
+    transformers = __import__("pytest").importorskip("transformers")
+    from antfly_b200.models.bart import BartConfig, BartModel
+    from antfly_b200.pipelines.seq2seq import Seq2SeqGenerator
+    from antfly_b200.runtime.sampling_params import SamplingParams
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.BartConfig(vocab_size=300, d_model=64, encoder_layers=1, decoder_layers=1,
+                                     encoder_attention_heads=4, decoder_attention_heads=4, encoder_ffn_dim=128,
+                                     decoder_ffn_dim=128, max_position_embeddings=64)
+    cfg = BartConfig.from_hf({**hf_cfg.to_dict(), "forced_bos_token_id": 0})       # as in mBART-style config.json
+    assert cfg.forced_bos_token_id == 0
+    model = BartModel.from_state_dict(cfg, transformers.BartForConditionalGeneration(hf_cfg).state_dict(),
+                                      device="cpu", dtype=torch.float32)
+    pipe = Seq2SeqGenerator(model, ByteTokenizer(vocab_size=300))
+    out = pipe.generate("summarize: a long story", SamplingParams(max_tokens=6))
+    assert out.token_ids == model.generate(pipe._encode("summarize: a long story"), max_new_tokens=6)
