@@ -107,8 +107,22 @@ def _err(status: int, code: str, message: str) -> JSONResponse:
 
 def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
                max_concurrent_requests: int = 64, max_queue_size: int = 256,
-               request_timeout_s: float = 0.0, result_cache_ttl_s: float = 120.0) -> FastAPI:
+               request_timeout_s: float = 0.0, result_cache_ttl_s: float = 120.0,
+               api_key: Optional[str] = None) -> FastAPI:
     app = FastAPI(title="antfly-b200 inference", version="0.1")
+    if api_key:
+        # shared deployments: every call except the liveness / readiness probes must carry the key
+        import hmac
+
+        @app.middleware("http")
+        async def _auth(request: Request, call_next):
+            if request.url.path not in ("/healthz", "/readyz"):
+                got = request.headers.get("authorization", "")
+                token = got[7:] if got.lower().startswith("bearer ") else request.headers.get("x-api-key", "")
+                if not hmac.compare_digest(token.encode(), api_key.encode()):
+                    return _err(401, "unauthorized", "missing or wrong API key")
+            return await call_next(request)
+
     mgr = manager or ModelManager()
     metrics = Metrics()
     queue = RequestQueue(max_concurrent_requests, max_queue_size)

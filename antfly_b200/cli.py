@@ -78,7 +78,8 @@ def cmd_run(args) -> int:
         for t in tasks:
             _get(mgr, name, t)
     serve(host, port, manager=mgr, max_concurrent_requests=cfg.max_concurrent_requests or 64,
-          max_queue_size=cfg.max_queue_size or 256, request_timeout_s=cfg.request_timeout_s)
+          max_queue_size=cfg.max_queue_size or 256, request_timeout_s=cfg.request_timeout_s,
+          api_key=cfg.api_key)
     return 0
 
 

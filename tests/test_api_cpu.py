@@ -467,3 +467,16 @@ def test_required_tool_choice_always_yields_a_valid_call(client):
         "model": "tiny-gen", "messages": [{"role": "user", "content": "x"}], "tools": tools,
         "tool_choice": {"type": "function", "function": {"name": "missing"}}})
     assert r.status_code == 400
+
+
+def test_api_key_guards_everything_but_the_probes():
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register_random("e", "embedder")
+    c = TestClient(create_app(mgr, api_key="s3cret"))
+    assert c.get("/healthz").status_code == 200 and c.get("/readyz").status_code == 200
+    r = c.post("/ai/v1/embed", json={"model": "e", "input": "x"})
+    assert r.status_code == 401 and r.json()["error"] == "unauthorized"
+    assert c.get("/ai/v1/models", headers={"Authorization": "Bearer wrong"}).status_code == 401
+    assert c.post("/ai/v1/embed", json={"model": "e", "input": "x"},
+                  headers={"Authorization": "Bearer s3cret"}).status_code == 200
+    assert c.get("/metrics", headers={"X-API-Key": "s3cret"}).status_code == 200
