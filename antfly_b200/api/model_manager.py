@@ -144,6 +144,21 @@ class ModelManager:
                 raise ModelNotFound(f"{name}: rewriters are T5- or BART-family encoder-decoder models "
                                     f"(found {cfg_d.get('model_type')!r})")
             pipe = Seq2SeqGenerator(model, tok)
+        elif task == "reader":
+            from ..models.trocr import TrOCRConfig, TrOCRModel
+            from ..pipelines.reading import Reader
+
+            if cfg_d.get("model_type") != "vision-encoder-decoder" or \
+                    (cfg_d.get("decoder") or {}).get("model_type") != "trocr":
+                raise ModelNotFound(f"{name}: readers are ViT + TrOCR vision encoder-decoder models")
+            pp = {}
+            ppath = os.path.join(path, "preprocessor_config.json")
+            if os.path.exists(ppath):
+                with open(ppath, encoding="utf-8") as f:
+                    pp = json.load(f)
+            model = TrOCRModel.from_state_dict(TrOCRConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = Reader(model, tok, pp.get("image_mean", (0.5, 0.5, 0.5)), pp.get("image_std", (0.5, 0.5, 0.5)),
+                          "bicubic" if pp.get("resample") == 3 else "bilinear")
         elif task == "transcriber":
             import json as _json
 

@@ -242,3 +242,11 @@ class RerankMultimodalRequest(BaseModel):
     model: str
     query: str
     documents: List[RerankMultimodalDocument]
+
+
+class ReadRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    images: List[Union[str, Dict[str, Any]]]      # {"url": "data:image/png;base64,..."} or the data URL itself
+    prompt: Optional[str] = None
+    max_tokens: int = Field(default=256, gt=0)

@@ -661,6 +661,33 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "transcribe", 1, work)
 
+    async def read(request: Request):
+        req, bad = await parse(request, S.ReadRequest)
+        if bad:
+            return bad
+        if not req.images:
+            return _err(400, "invalid_request", "images must not be empty")
+        from ..pipelines.multimodal import decode_data_url
+
+        imgs = []
+        for i, im in enumerate(req.images):
+            url = im.get("url") if isinstance(im, dict) else im
+            try:
+                imgs.append(decode_data_url(url))
+            except Exception as e:
+                return _err(400, "invalid_request", f"image {i}: {e}")
+
+        def work():
+            lm = mgr.get(req.model, "reader")
+            res = lm.pipeline.read(imgs, req.max_tokens)
+            n = sum(len(r.token_ids) for r in res)
+            metrics.tokens.labels("read", "completion").inc(n)
+            return {"object": "list", "model": req.model,
+                    "data": [{"object": "read", "index": i, "text": r.text} for i, r in enumerate(res)],
+                    "usage": {"prompt_tokens": 0, "completion_tokens": n, "total_tokens": n}}
+
+        return await asyncio.to_thread(run_guarded, "read", len(imgs), work)
+
     async def extract(request: Request):
         req, bad = await parse(request, S.ExtractionRequest)
         if bad:
@@ -898,6 +925,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/ai/v1/rewrite", rewrite, methods=["POST"])
     app.add_api_route("/ai/v1/extract", extract, methods=["POST"])
     app.add_api_route("/ai/v1/transcribe", transcribe, methods=["POST"])
+    app.add_api_route("/ai/v1/read", read, methods=["POST"])
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
     app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
     app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])

@@ -230,6 +230,18 @@ def cmd_transcribe(args) -> int:
     return 0
 
 
+def cmd_read(args) -> int:
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    lm = _manager(args).get(args.model, "reader")
+    imgs = [torch.from_numpy(np.asarray(Image.open(p).convert("RGB")).copy()) for p in args.image]
+    for path, r in zip(args.image, lm.pipeline.read(imgs, args.max_tokens)):
+        print(json.dumps({"image": path, "text": r.text}))
+    return 0
+
+
 def cmd_compare(args) -> int:
     """Run the same embedder on two devices (by default the CPU oracle path and the GPU kernels) and report how far
     the embeddings are apart: the parity check a deployment runs after changing hardware or build."""
@@ -302,6 +314,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--model", required=True); p.add_argument("--audio", nargs="+", required=True, help="WAV files")
     p.add_argument("--language"); p.add_argument("--max-tokens", type=int, default=224)
     p.add_argument("--print-timing", action="store_true"); p.set_defaults(fn=cmd_transcribe)
+    p = sub.add_parser("read", help="OCR: text of each image"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--image", nargs="+", required=True)
+    p.add_argument("--max-tokens", type=int, default=256); p.set_defaults(fn=cmd_read)
     p = sub.add_parser("compare", help="same embedder on two devices: embedding parity report")
     p.add_argument("--models-dir"); p.add_argument("--model", required=True)
     p.add_argument("--text", nargs="+", required=True); p.add_argument("--device-a", default="cpu")

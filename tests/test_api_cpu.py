@@ -480,3 +480,49 @@ def test_api_key_guards_everything_but_the_probes():
     assert c.post("/ai/v1/embed", json={"model": "e", "input": "x"},
                   headers={"Authorization": "Bearer s3cret"}).status_code == 200
     assert c.get("/metrics", headers={"X-API-Key": "s3cret"}).status_code == 200
+
+
+def test_read_endpoint_with_a_tiny_vision_encoder_decoder(tmp_path):
+    """/ai/v1/read: data-URL image -> device preprocessing -> ViT -> TrOCR decoder -> text."""
+    import base64
+    import io
+
+    import numpy as np
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    pil = pytest.importorskip("PIL.Image")
+    from antfly_b200.formats import safetensors_io as st
+
+    torch.manual_seed(0)
+    enc = transformers.ViTConfig(hidden_size=48, num_hidden_layers=1, num_attention_heads=4, intermediate_size=96,
+                                 image_size=32, patch_size=8)
+    dec = transformers.TrOCRConfig(vocab_size=300, d_model=64, decoder_layers=1, decoder_attention_heads=4,
+                                   decoder_ffn_dim=128, max_position_embeddings=40, cross_attention_hidden_size=48,
+                                   decoder_start_token_id=2, eos_token_id=2, pad_token_id=1)
+    hf_cfg = transformers.VisionEncoderDecoderConfig.from_encoder_decoder_configs(enc, dec)
+    hf = transformers.VisionEncoderDecoderModel(hf_cfg)
+    d = tmp_path / "readers" / "tiny-ocr"
+    d.mkdir(parents=True)
+    st.save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps(hf_cfg.to_dict(), default=str))
+    (d / "preprocessor_config.json").write_text(json.dumps({"image_mean": [0.5, 0.5, 0.5], "image_std": [0.5, 0.5, 0.5],
+                                                            "resample": 2, "size": {"height": 32, "width": 32}}))
+    mgr = ModelManager(models_dir=str(tmp_path), device="cpu")
+    c = TestClient(create_app(mgr))
+    buf = io.BytesIO()
+    img = np.random.default_rng(0).integers(0, 256, size=(20, 90, 3), dtype=np.uint8)
+    pil.fromarray(img).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    r = c.post("/ai/v1/read", json={"model": "tiny-ocr", "images": [{"url": url}, url], "max_tokens": 5})
+    body = r.json()
+    assert r.status_code == 200, r.text
+    assert body["object"] == "list" and [x["index"] for x in body["data"]] == [0, 1]
+    assert body["data"][0]["text"] == body["data"][1]["text"] and body["usage"]["completion_tokens"] <= 10
+    # same tokens as driving the model directly on the same preprocessed pixels
+    pipe = mgr.get("tiny-ocr", "reader").pipeline
+    direct = pipe.model.read_ids(pipe.preprocess(torch.from_numpy(img)), 5)
+    assert pipe.read([torch.from_numpy(img)], 5)[0].token_ids == direct
+    assert c.post("/ai/v1/read", json={"model": "tiny-ocr", "images": ["http://x/y.png"]}).status_code == 400
+    assert c.post("/ai/v1/read", json={"model": "tiny-ocr", "images": []}).status_code == 400
+    assert c.post("/ai/v1/read", json={"model": "nope", "images": [url]}).status_code == 404

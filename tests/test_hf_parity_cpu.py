@@ -587,3 +587,53 @@ def test_bart_matches_transformers(scale):
             want.append(nxt)
             dec.append(nxt)
     assert model.generate(src, max_new_tokens=8) == want
+
+
+@pytest.mark.parametrize("learned_pos", [True, False])
+def test_trocr_vision_encoder_decoder_matches_transformers(learned_pos):
+    """ViT encoder (patch GEMM, class token, pre-LayerNorm) + TrOCR decoder (cross attention from a different
+    width, learned or sinusoidal positions, embedding LayerNorm / scale), cached greedy decoding."""
+    from antfly_b200.models.trocr import TrOCRConfig, TrOCRModel
+
+    torch.manual_seed(8)
+    enc = transformers.ViTConfig(hidden_size=48, num_hidden_layers=2, num_attention_heads=4, intermediate_size=96,
+                                 image_size=32, patch_size=8, hidden_dropout_prob=0.0,
+                                 attention_probs_dropout_prob=0.0)
+    dec = transformers.TrOCRConfig(vocab_size=300, d_model=64, decoder_layers=2, decoder_attention_heads=4,
+                                   decoder_ffn_dim=128, max_position_embeddings=40, dropout=0.0,
+                                   attention_dropout=0.0, activation_dropout=0.0, cross_attention_hidden_size=48,
+                                   use_learned_position_embeddings=learned_pos, layernorm_embedding=learned_pos,
+                                   scale_embedding=not learned_pos, decoder_start_token_id=2, eos_token_id=2,
+                                   pad_token_id=1)
+    hf_cfg = transformers.VisionEncoderDecoderConfig.from_encoder_decoder_configs(enc, dec)
+    hf = transformers.VisionEncoderDecoderModel(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+            elif "norm" not in n and "position" not in n and "cls_token" not in n:
+                p.mul_(2.0)
+    cfg = TrOCRConfig.from_hf(hf_cfg.to_dict())
+    assert cfg.encoder.patch_size == 8 and cfg.decoder.use_learned_position_embeddings == learned_pos
+    model = TrOCRModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    pixels = torch.randn(3, 32, 32)
+    tgt = [2] + torch.randint(3, 300, (9,)).tolist()
+    with torch.no_grad():
+        out = hf(pixel_values=pixels[None], decoder_input_ids=torch.tensor([tgt]))
+    enc_h = model.encode(pixels)
+    ref = out.encoder_last_hidden_state[0]
+    assert enc_h.shape == (17, 48) and float((enc_h.float() - ref).norm() / ref.norm()) < 0.02
+    full = model.decode(model.start_decoding(enc_h), tgt)
+    assert float((full - out.logits[0]).norm() / out.logits[0].norm()) < 0.03
+    state = model.start_decoding(enc_h)
+    step = torch.cat([model.decode(state, [t]) for t in tgt])
+    assert float((step - full).norm() / full.norm()) < 0.02
+    dec_ids, want = [2], []
+    with torch.no_grad():
+        for _ in range(6):
+            nxt = int(hf(pixel_values=pixels[None], decoder_input_ids=torch.tensor([dec_ids])).logits[0, -1].argmax())
+            if nxt == 2:
+                break
+            want.append(nxt)
+            dec_ids.append(nxt)
+    assert model.read_ids(pixels, max_new_tokens=6) == want
