@@ -25,6 +25,9 @@ from ..runtime.engine import LLMEngine
 from ..tokenizer import ByteTokenizer, load_tokenizer
 
 
+COMPILED_ARTIFACT = "compiled.antfly_b200.safetensors"
+
+
 class ModelNotFound(KeyError):
     pass
 
@@ -107,6 +110,15 @@ class ModelManager:
     def _load_dir(self, name: str, task: str, path: str) -> LoadedModel:
         mf = MF.read_manifest(path)
         tok = load_tokenizer(path, mf.config.get("vocab_size", 0))
+        packed = os.path.join(path, COMPILED_ARTIFACT)
+        if task == "generator" and os.path.exists(packed):
+            # a compiled artifact holds the weights in the kernels' own layout: read and upload, nothing to pack
+            model = LlamaModel.from_artifact(packed, device=self.device)
+            eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
+                            use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id,
+                            prefix_cache=self.prefix_cache)
+            return LoadedModel(name, task, Generator(eng, tok, mf.chat_template), tok, path,
+                               info={"weights": "compiled", "capabilities": mf.capabilities})
         if mf.weights == "gguf":
             from ..formats import gguf as GG
 

@@ -189,6 +189,26 @@ def cmd_export(args) -> int:
     return 0
 
 
+def cmd_compile_artifact(args) -> int:
+    """Pack a Llama-family checkpoint directory into the kernels' own layout (fused, block-fp8) next to the original
+    weights; the server then loads that file instead of re-packing at every start."""
+    import os
+
+    from .api.model_manager import COMPILED_ARTIFACT
+    from .formats import manifest as MF
+    from .formats import safetensors_io as ST
+    from .models.llama import LlamaConfig, LlamaModel
+
+    t0 = time.perf_counter()
+    mf = MF.read_manifest(args.inp)
+    model = LlamaModel.from_state_dict(LlamaConfig.from_hf(mf.config), ST.load_model_dir(args.inp),
+                                       device=args.device or "cpu")
+    out = args.out or os.path.join(args.inp, COMPILED_ARTIFACT)
+    model.save_artifact(out)
+    print(json.dumps({"out": out, "bytes": os.path.getsize(out), "seconds": round(time.perf_counter() - t0, 2)}))
+    return 0
+
+
 def cmd_classify(args) -> int:
     lm = _manager(args).get(args.model, "classifier")
     for text, ranked in zip(args.text, lm.pipeline.classify(args.text, top_k=args.top_k)):
@@ -300,6 +320,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("export", help="safetensors checkpoint directory -> GGUF")
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
     p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "q8_0", "q4_0"]); p.set_defaults(fn=cmd_export)
+    p = sub.add_parser("compile-artifact", help="pack a checkpoint into the kernels' layout for fast loading")
+    p.add_argument("--in", dest="inp", required=True); p.add_argument("--out"); p.add_argument("--device")
+    p.set_defaults(fn=cmd_compile_artifact)
     p = sub.add_parser("classify"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
     p.add_argument("--top-k", type=int, default=1); p.set_defaults(fn=cmd_classify)

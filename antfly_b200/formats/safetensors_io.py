@@ -53,6 +53,15 @@ class SafetensorsFile:
         self._f.close()
 
 
+def read_metadata(path: str) -> Dict[str, str]:
+    """The ``__metadata__`` string map of a safetensors file (no tensor data is touched)."""
+    f = SafetensorsFile(path)
+    try:
+        return dict(f.metadata)
+    finally:
+        f.close()
+
+
 def load_file(path: str) -> Dict[str, torch.Tensor]:
     f = SafetensorsFile(path)
     return {k: f.tensor(k) for k in f.keys()}

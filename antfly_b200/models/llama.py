@@ -431,6 +431,56 @@ class LlamaModel:
             x, h = fz.norm_bcast(nw, x, T, cfg.rms_norm_eps, 1)
         return Q.gemm_mxfp8(h, w["lm_head"])
 
+    # -- compiled artifacts: the in-memory layout (fused, interleaved, block-fp8 packed) saved as it is ------------
+    ARTIFACT_FORMAT = "antfly_b200.llama.packed.v1"
+
+    def save_artifact(self, path: str) -> None:
+        """Write this model's weights exactly as the kernels consume them (fused QKV, interleaved gate / up, block
+        fp8 codes + scales) so that a later start only reads and uploads: no fusing, no re-quantising.  The
+        reference's counterpart is its compiled artifact (zig/pkg/inference/src/compiled_artifact.zig,
+        native_run_artifact.zig)."""
+        import dataclasses
+        import json
+
+        from ..formats import safetensors_io as ST
+
+        tensors, swiglu = {}, []
+        for name, v in self.w.items():
+            if isinstance(v, Q.Fp8Weight):
+                tensors[name + "::q"] = v.q.view(torch.uint8) if v.q.dtype != torch.uint8 else v.q
+                tensors[name + "::scales"] = v.scales
+                if v.interleaved_swiglu:
+                    swiglu.append(name)
+            elif isinstance(v, torch.Tensor):
+                if not (name == "lm_head" and v.data_ptr() == self.w["embed"].data_ptr()):
+                    tensors[name] = v
+        ST.save_file(tensors, path, {"format": self.ARTIFACT_FORMAT, "config": json.dumps(dataclasses.asdict(self.cfg)),
+                                     "swiglu": json.dumps(swiglu), "tp_rank": self.tp_rank, "tp_size": self.tp_size})
+
+    @classmethod
+    def from_artifact(cls, path: str, device="cuda", comm=None) -> "LlamaModel":
+        import json
+
+        from ..formats import safetensors_io as ST
+
+        meta = ST.read_metadata(path)
+        if meta.get("format") != cls.ARTIFACT_FORMAT:
+            raise ValueError(f"{path}: not a packed model artifact (format {meta.get('format')!r})")
+        cfg = LlamaConfig(**json.loads(meta["config"]))
+        swiglu = set(json.loads(meta.get("swiglu", "[]")))
+        raw = ST.load_file(path)
+        w: Dict[str, object] = {}
+        for name, t in raw.items():
+            if name.endswith("::q"):
+                base = name[:-3]
+                w[base] = Q.Fp8Weight(t.view(torch.float8_e4m3fn).to(device), raw[base + "::scales"].to(device),
+                                      base in swiglu)
+            elif not name.endswith("::scales"):
+                w[name] = t.to(device)
+        if "lm_head" not in w:
+            w["lm_head"] = w["embed"]
+        return cls(cfg, w, int(meta.get("tp_rank", 0)), int(meta.get("tp_size", 1)), comm)
+
     def set_expert_parallel(self, rank: int, size: int, group=None) -> None:
         """Expert parallelism for mixture-of-experts layers: every rank runs the attention and the router on the
         same tokens (so the routing is identical everywhere), computes only the experts it holds

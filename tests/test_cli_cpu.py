@@ -79,3 +79,42 @@ def test_cli_export_gguf_roundtrip_and_task_commands(capsys, tmp_path):
     assert main(["compare", "--models-dir", str(tmp_path), "--model", "emb", "--text", "a b c", "hello",
                  "--device-a", "cpu", "--device-b", "cpu"]) == 0
     assert json.loads(capsys.readouterr().out)["min_cosine"] > 0.9999
+
+
+def test_compile_artifact_is_loaded_instead_of_repacking(capsys, tmp_path):
+    """compile-artifact writes the packed layout; the model built from it is bit-identical to the one packed from
+    the checkpoint, and the model manager prefers it."""
+    import torch
+
+    from antfly_b200.api.model_manager import COMPILED_ARTIFACT, ModelManager
+    from antfly_b200.formats import safetensors_io as st
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from tests.test_parallel_cpu import _forward_logits, _hf_llama_state
+
+    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    src = tmp_path / "generators" / "tiny"
+    src.mkdir(parents=True)
+    st.save_file(_hf_llama_state(cfg), str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({
+        "model_type": "llama", "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+        "num_hidden_layers": 2, "num_attention_heads": cfg.num_attention_heads,
+        "num_key_value_heads": cfg.num_key_value_heads, "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta,
+        "rms_norm_eps": cfg.rms_norm_eps, "head_dim": cfg.head_dim, "tie_word_embeddings": False}))
+    assert main(["compile-artifact", "--in", str(src)]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["out"].endswith(COMPILED_ARTIFACT) and rep["bytes"] > 0
+    a = LlamaModel.from_artifact(rep["out"], device="cpu")
+    b = LlamaModel.from_state_dict(LlamaConfig.from_hf(json.loads((src / "config.json").read_text())),
+                                   st.load_model_dir(str(src)), device="cpu")
+    assert set(a.w) == set(b.w)
+    for k in a.w:
+        if hasattr(a.w[k], "q"):
+            assert torch.equal(a.w[k].q.view(torch.uint8), b.w[k].q.view(torch.uint8))
+            assert torch.equal(a.w[k].scales, b.w[k].scales) and a.w[k].interleaved_swiglu == b.w[k].interleaved_swiglu
+        else:
+            assert torch.equal(a.w[k], b.w[k])
+    assert torch.equal(_forward_logits(a, a.cfg), _forward_logits(b, b.cfg))
+    lm = ModelManager(models_dir=str(tmp_path), device="cpu", kv_blocks=32).get("tiny", "generator")
+    assert lm.info["weights"] == "compiled"
+    with __import__("pytest").raises(ValueError):
+        LlamaModel.from_artifact(str(src / "model.safetensors"), device="cpu")
