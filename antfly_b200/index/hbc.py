@@ -36,8 +36,15 @@ class HBCConfig:
     use_quantization: bool = True
     quantizer_seed: int = 42
     # kmeans: cluster every level (farthest-first seeding); hilbert_seeded: k-means seeded with the means of
-    # Hilbert-curve runs (the reference's default bulk build); hilbert: cut the curve order into runs, no clustering
+    # Hilbert-curve runs (the reference's default bulk build); hilbert: cut the curve order into runs, no clustering;
+    # recursive: split the set in two with 2-means until the pieces fit a leaf (top-down)
     bulk_build: str = "kmeans"
+    # hbc: beam search down the tree; flat_rabitq: score every leaf centroid with one quantised pass (blocks of
+    # flat_centroid_block_size), open the best flat_centroid_probe_count leaves (0: the search width) -- IVF-style
+    centroid_directory_mode: str = "hbc"
+    flat_centroid_block_size: int = 8192
+    flat_centroid_probe_count: int = 0
+    merge_below: float = 0.25           # a leaf that shrinks below this fraction of leaf_size is merged away
 
 
 @dataclass
@@ -103,6 +110,22 @@ class HBCIndex:
                 cents = km.centroids.float().cpu() if not x.is_cuda else km.centroids.float()
                 a = km.assignments.long()
                 members = [torch.nonzero(a == c).flatten() for c in range(cents.shape[0])]
+        elif cfg.bulk_build == "recursive":
+            members, work = [], [torch.arange(n)]
+            while work:
+                m = work.pop()
+                if m.numel() <= cfg.leaf_size:
+                    members.append(m)
+                    continue
+                km = kmeans(x[m].to(torch.bfloat16), 2, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
+                a = km.assignments.long()
+                left, right = m[a == 0], m[a == 1]
+                if left.numel() == 0 or right.numel() == 0:      # identical points: cut in the middle
+                    left, right = m[: m.numel() // 2], m[m.numel() // 2:]
+                work += [left, right]
+            cents = torch.stack([x[m].mean(0) for m in members])
+            if cfg.metric == "cosine":
+                cents = torch.nn.functional.normalize(cents, dim=-1)
         else:
             km = kmeans(x.to(torch.bfloat16), k, metric=cfg.metric, max_iter=cfg.kmeans_max_iter)
             cents = km.centroids.float().cpu() if not x.is_cuda else km.centroids.float()
@@ -185,6 +208,18 @@ class HBCIndex:
         cands: List[Tuple[float, int]] = []
         leaves, counter = 0, 1
         dmin = float("inf")
+        if cfg.centroid_directory_mode == "flat_rabitq":
+            # One quantised pass over every leaf centroid instead of walking the tree; the best leaves are then
+            # opened in order by the loop below (internal nodes are never pushed).
+            t0 = _time.perf_counter_ns()
+            probe = cfg.flat_centroid_probe_count or width
+            width = min(width, probe) if cfg.flat_centroid_probe_count else width
+            leaf_ids, est = self._directory(q)
+            top = torch.topk(est, min(probe, est.numel()), largest=False)
+            pq = [(float(d), i, leaf_ids[j]) for i, (d, j) in enumerate(zip(top.values.tolist(), top.indices.tolist()))]
+            heapq.heapify(pq)
+            prof["internal_ns"] += _time.perf_counter_ns() - t0
+            prof["internal_nodes"] = -(-len(leaf_ids) // cfg.flat_centroid_block_size)      # blocks scored
         while pq and leaves < width:
             bound, _, nid = heapq.heappop(pq)
             nd = self.nodes[nid]
@@ -226,6 +261,31 @@ class HBCIndex:
             prof["total_ns"] = _time.perf_counter_ns() - t_start
             profile.update(prof)
         return out
+
+    def _directory(self, q: torch.Tensor) -> Tuple[List[int], torch.Tensor]:
+        """Flat directory of the leaf centroids: quantised once (lazily, rebuilt after inserts / deletes), scored
+        for a query in blocks.  Returns (leaf node ids, estimated distance lower bounds)."""
+        d = getattr(self, "_dir", None)
+        if d is None:
+            leaf_ids = [nd.id for nd in self.nodes.values() if nd.is_leaf and nd.children]
+            blocks = []
+            bs = self.cfg.flat_centroid_block_size
+            for lo in range(0, len(leaf_ids), bs):
+                cents = torch.stack([self.nodes[i].centroid for i in leaf_ids[lo:lo + bs]])
+                mean = cents.mean(0)
+                if self.cfg.metric == "cosine":
+                    mean = torch.nn.functional.normalize(mean, dim=-1)
+                blocks.append(self.quantizer.quantize(mean, cents) if self.cfg.use_quantization else cents)
+            d = self._dir = (leaf_ids, blocks)
+        leaf_ids, blocks = d
+        est = []
+        for b in blocks:
+            if isinstance(b, RaBitQSet):
+                d_, e_ = self.quantizer.estimate(b, q)
+                est.append(d_ - e_)                      # lower bound, the beam's priority for internal nodes too
+            else:
+                est.append(R.distances(q[None], b, self.cfg.metric)[0])
+        return leaf_ids, torch.cat(est) if est else torch.zeros(0)
 
     # -- online maintenance -------------------------------------------------------------------------------
     def _requantize(self, nd: Node) -> None:
@@ -295,6 +355,7 @@ class HBCIndex:
         """Online batch insert: every vector descends greedily to its nearest leaf (exact centroid distances),
         leaves that grow past twice the leaf size are split, splits propagate upwards.  Mirrors the reference's
         online insert path (zig/lib/vectorindex/src/hbc_index.zig, spfresh_index.zig)."""
+        self._dir = None
         x = vectors.float().to(self.vectors.device)
         if self.cfg.metric == "cosine":
             x = torch.nn.functional.normalize(x, dim=-1)
@@ -335,14 +396,52 @@ class HBCIndex:
             leaf.children.remove(i)
             touched.add(leaf.id)
             n += 1
+        self._dir = None
+        floor = self.cfg.merge_below * self.cfg.leaf_size
         for nid in touched:
-            nd = self.nodes[nid]
+            nd = self.nodes.get(nid)
+            if nd is None:
+                continue
+            if len(nd.children) < floor and self._merge_leaf(nd):
+                continue
             if nd.children:
                 self._recentre(nd)
                 self._requantize(nd)
             else:
                 nd.quant = None
         return n
+
+    def _merge_leaf(self, nd: Node) -> bool:
+        """Fold an under-full leaf into its siblings (SPFresh-style posting merge): every remaining member moves to
+        the sibling leaf with the nearest centroid, the leaf is removed from its parent, and a sibling that grows
+        past twice the leaf size is split again.  Returns False when there is no sibling leaf to merge into."""
+        parent = self.nodes.get(nd.parent)
+        if parent is None:
+            return False
+        sibs = [self.nodes[c] for c in parent.children if c != nd.id and self.nodes[c].is_leaf]
+        if not sibs:
+            return False
+        grew = set()
+        if nd.children:
+            cents = torch.stack([sb.centroid for sb in sibs])
+            pts = self.vectors[torch.tensor(nd.children)]
+            near = torch.argmin(R.distances(pts, cents, self.cfg.metric), dim=1).tolist()
+            for v, j in zip(nd.children, near):
+                sibs[j].children.append(v)
+                self.leaf_of[v] = sibs[j].id
+                grew.add(sibs[j].id)
+        parent.children.remove(nd.id)
+        del self.nodes[nd.id]
+        for sid in grew:
+            sb = self.nodes[sid]
+            self._recentre(sb)
+            if len(sb.children) > 2 * self.cfg.leaf_size:
+                self._split(sb)
+            else:
+                self._requantize(sb)
+        self._recentre(parent)
+        self._requantize(parent)
+        return True
 
     def stats(self) -> dict:
         leaves = sum(1 for n in self.nodes.values() if n.is_leaf)

@@ -267,3 +267,55 @@ def test_hbc_online_insert_split_and_delete():
     gone = truth.ids[0, :5].tolist()
     assert idx.delete(gone) == 5 and idx.delete(gone) == 0
     assert not set(idx.search(q[0], 10)[0]) & set(gone)
+
+
+def test_hbc_flat_directory_mode_recursive_build_and_leaf_merge():
+    g = torch.Generator().manual_seed(5)
+    centers = torch.randn(16, 24, generator=g)
+    x = centers[torch.randint(0, 16, (2500,), generator=g)] + 0.25 * torch.randn(2500, 24, generator=g)
+    q = centers[torch.randint(0, 16, (30,), generator=g)] + 0.25 * torch.randn(30, 24, generator=g)
+    truth = exact_search_fp32(q, x, 10, "l2_squared")
+
+    def recall(idx, **kw):
+        found = torch.tensor([(idx.search(q[i], 10, **kw)[0] + [-1] * 10)[:10] for i in range(30)])
+        return recall_at_k(found, truth.ids, 10)
+
+    # top-down recursive build: every leaf fits, recall is in the same range as the bottom-up build
+    rec = HBCIndex.bulk_build(x, HBCConfig(24, "l2_squared", branching_factor=8, leaf_size=50, search_width=16,
+                                           bulk_build="recursive"))
+    assert max(len(n.children) for n in rec.nodes.values() if n.is_leaf) <= 50 and recall(rec) > 0.8
+    # flat directory: all leaf centroids are scored in blocks, the best `probe` leaves are opened
+    cfg = HBCConfig(24, "l2_squared", branching_factor=8, leaf_size=50, search_width=16,
+                    centroid_directory_mode="flat_rabitq", flat_centroid_block_size=16, epsilon=0.5)
+    flat = HBCIndex.bulk_build(x, cfg)
+    prof = {}
+    flat.search(q[0], 10, profile=prof)
+    n_leaves = sum(1 for n in flat.nodes.values() if n.is_leaf)
+    assert prof["internal_nodes"] == -(-n_leaves // 16) and 1 <= prof["leaves"] <= 16
+    r_flat = recall(flat)
+    assert r_flat > 0.7                   # 1-bit codes of 24-d centroids in 16-centroid blocks: a coarse directory
+    few = HBCIndex.bulk_build(x, HBCConfig(24, "l2_squared", branching_factor=8, leaf_size=50, search_width=16,
+                                           centroid_directory_mode="flat_rabitq", flat_centroid_probe_count=2))
+    p2 = {}
+    few.search(q[0], 10, profile=p2)
+    assert p2["leaves"] <= 2 and recall(few) <= r_flat + 1e-9
+    # the directory follows inserts and deletes
+    extra = centers[3] + 0.05 * torch.randn(40, 24, generator=g)
+    flat.insert(extra, torch.arange(10000, 10040))
+    ids, _ = flat.search(centers[3], 10)
+    assert len(set(ids) & set(range(10000, 10040))) >= 8
+    # deleting most of a leaf merges the rest into a sibling; nothing is lost, nothing deleted comes back
+    leaf = next(n for n in flat.nodes.values() if n.is_leaf and len(n.children) >= 20)
+    victims = [int(flat.ids[v]) for v in leaf.children[:-3]]
+    survivors = [int(flat.ids[v]) for v in leaf.children[-3:]]
+    before = sum(1 for n in flat.nodes.values() if n.is_leaf)
+    assert flat.delete(victims) == len(victims)
+    assert leaf.id not in flat.nodes and sum(1 for n in flat.nodes.values() if n.is_leaf) == before - 1
+    seen = [int(flat.ids[v]) for n in flat.nodes.values() if n.is_leaf for v in n.children]
+    assert set(survivors) <= set(seen) and not set(victims) & set(seen) and len(seen) == len(set(seen))
+    for s_id in survivors:
+        vec = flat.vectors[(flat.ids == s_id).nonzero()[0, 0]]
+        assert flat.search(vec, 1, search_width=64)[0] == [s_id]
+    for n in flat.nodes.values():
+        if not n.is_leaf:
+            assert all(c in flat.nodes and flat.nodes[c].parent == n.id for c in n.children)
