@@ -186,13 +186,13 @@ class ModelManager:
                     gen = _json.load(f)
             model = WhisperModel.from_state_dict(WhisperConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = Transcriber(model, tok, gen)
-        elif task in ("recognizer", "classifier"):
+        elif task in ("recognizer", "classifier", "chunker"):
             from ..pipelines.classification import TextClassifier, TokenClassifier
 
             model = self._encoder(cfg_d, sd)
             id2label = {int(k): v for k, v in (cfg_d.get("id2label") or {}).items()} or \
                 {i: f"LABEL_{i}" for i in range(model.cfg.num_labels)}
-            if task == "recognizer":
+            if task in ("recognizer", "chunker"):
                 pipe = TokenClassifier(model, id2label, tok)
             else:
                 pipe = TextClassifier(model, tok, id2label,

@@ -582,9 +582,19 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         req, bad = await parse(request, S.ChunkRequest)
         if bad:
             return bad
-        chunks = chunk_text(req.text, req.target_tokens, req.overlap_tokens, req.max_chunks)
-        metrics.requests.labels("chunk", "200").inc()
-        return {"chunks": chunks, "model": req.model}
+        if req.model in ("fixed", "", None):
+            chunks = chunk_text(req.text, req.target_tokens, req.overlap_tokens, req.max_chunks)
+            metrics.requests.labels("chunk", "200").inc()
+            return {"chunks": chunks, "model": req.model}
+
+        def work():
+            from ..pipelines.chunking import NeuralChunker
+
+            lm = mgr.get(req.model, "chunker")
+            ch = NeuralChunker(lm.pipeline).chunk(req.text, max_tokens=req.target_tokens, max_chunks=req.max_chunks)
+            return {"chunks": ch, "model": req.model}
+
+        return await asyncio.to_thread(run_guarded, "chunk", 1, work)
 
     # ---- vector search --------------------------------------------------------------------------------
     async def search(request: Request):

@@ -526,3 +526,38 @@ def test_read_endpoint_with_a_tiny_vision_encoder_decoder(tmp_path):
     assert c.post("/ai/v1/read", json={"model": "tiny-ocr", "images": ["http://x/y.png"]}).status_code == 400
     assert c.post("/ai/v1/read", json={"model": "tiny-ocr", "images": []}).status_code == 400
     assert c.post("/ai/v1/read", json={"model": "nope", "images": [url]}).status_code == 404
+
+
+def test_neural_chunker_splits_at_predicted_boundaries(tmp_path):
+    """A token-classification chunker model: chunks cover the text in order, respect the token cap, and are cut
+    where the model says so."""
+    import torch
+
+    from antfly_b200.pipelines.chunking import NeuralChunker
+
+    _write_bert(tmp_path / "chunkers" / "tiny-chunker", 2, ["O", "separator"], 5)
+    mgr = ModelManager(models_dir=str(tmp_path), device="cpu")
+    tagger = mgr.get("tiny-chunker", "chunker").pipeline
+    text = "First sentence here. Second one follows! And a third, somewhat longer, closes the paragraph.\n\nNew part."
+    ch = NeuralChunker(tagger).chunk(text, max_tokens=30, min_tokens=4)
+    assert ch and ch[0]["start_char"] == 0 and ch[-1]["end_char"] == len(text)
+    assert all(c["tokens"] <= 30 and c["text"] == text[c["start_char"]:c["end_char"]] for c in ch)
+    assert all(a["end_char"] <= b["start_char"] for a, b in zip(ch, ch[1:]))
+    assert "".join(c["text"] for c in ch).replace(" ", "") in text.replace(" ", "") or len(ch) > 1
+    # boundaries come from the model: forcing every token to be a separator yields chunks of exactly min_tokens
+    class Always:
+        tokenizer = tagger.tokenizer
+
+        def tag_ids(self, seqs):
+            return [(["separator"] * len(s), [1.0] * len(s)) for s in seqs]
+
+    every = NeuralChunker(Always()).chunk(text, max_tokens=30, min_tokens=5)
+    assert all(c["tokens"] == 5 for c in every[:-1]) and len(every) > 5
+    none = NeuralChunker(Always(), boundary_labels=("never",)).chunk(text, max_tokens=30)
+    assert all(c["tokens"] == 30 for c in none[:-1])
+    c = TestClient(create_app(mgr))
+    r = c.post("/ai/v1/chunk", json={"text": text, "model": "tiny-chunker", "target_tokens": 30})
+    assert r.status_code == 200 and r.json()["chunks"][0]["start_char"] == 0
+    assert c.post("/ai/v1/chunk", json={"text": text, "model": "missing"}).status_code == 404
+    assert c.post("/ai/v1/chunk", json={"text": "a b c d", "target_tokens": 2, "overlap_tokens": 0}).json()[
+        "chunks"][0]["text"] == "a b"
