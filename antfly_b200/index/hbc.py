@@ -223,9 +223,16 @@ class HBCIndex:
         while pq and leaves < width:
             bound, _, nid = heapq.heappop(pq)
             nd = self.nodes[nid]
-            if cfg.metric != "inner_product" and len(cands) >= rerank_n and bound > dmin * (1 + eps):
-                prof["pruned"] += 1
-                continue
+            # Dynamic pruning compares like with like (zig/lib/vectorindex/src/search.zig:56-79): the bound of a
+            # node's centroid against the smallest leaf-centroid bound met once enough candidates are held -- never
+            # against a member distance, which a centroid distance does not bound from below.
+            if cfg.metric != "inner_product" and len(cands) >= rerank_n:
+                if nd.is_leaf and bound < dmin:
+                    dmin = bound
+                elif dmin < float("inf") and (abs(bound) > abs(dmin * (1 + eps)) if nd.is_leaf
+                                              else bound > dmin * (1 + eps)):
+                    prof["pruned"] += 1
+                    continue
             t0 = _time.perf_counter_ns()
             d, e = self._score(nd, q)
             d, e = d.tolist(), e.tolist()
@@ -237,8 +244,6 @@ class HBCIndex:
                     cands.append((dist, vid))
                 if len(cands) > cap:
                     cands = heapq.nsmallest(cap, cands)
-                if len(cands) >= rerank_n:
-                    dmin = heapq.nsmallest(rerank_n, cands)[-1][0]
             else:
                 for cid, dist, err in zip(nd.children, d, e):
                     heapq.heappush(pq, (dist - err, counter, cid))

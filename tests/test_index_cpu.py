@@ -1,5 +1,6 @@
 """Index logic on the CPU: fusion / pruner, search-effort mapping, wire codecs, RaBitQ, HBC tree and artifacts."""
 import math
+import zlib
 
 import pytest
 import torch
@@ -259,8 +260,8 @@ def test_hbc_online_insert_split_and_delete():
     assert recall_at_k(found, truth.ids, 10) > 0.8
     # per-query profile: wider search scores more leaves and re-ranks more vectors
     pa, pb = {}, {}
-    idx.search(q[0], 10, search_width=4, profile=pa)
-    idx.search(q[0], 10, search_width=32, profile=pb)
+    idx.search(q[0], 10, search_width=4, epsilon=3.0, profile=pa)
+    idx.search(q[0], 10, search_width=32, epsilon=3.0, profile=pb)
     assert 1 <= pa["leaves"] <= 4 < pb["leaves"] <= 32 and pb["reranked"] >= pa["reranked"] >= 10
     assert pa["internal_nodes"] >= 1 and pa["total_ns"] >= pa["leaf_ns"] + pa["internal_ns"] + pa["rerank_ns"] > 0
     # deletion: the deleted ids never come back
@@ -282,7 +283,7 @@ def test_hbc_flat_directory_mode_recursive_build_and_leaf_merge():
 
     # top-down recursive build: every leaf fits, recall is in the same range as the bottom-up build
     rec = HBCIndex.bulk_build(x, HBCConfig(24, "l2_squared", branching_factor=8, leaf_size=50, search_width=16,
-                                           bulk_build="recursive"))
+                                           bulk_build="recursive", epsilon=1.0))
     assert max(len(n.children) for n in rec.nodes.values() if n.is_leaf) <= 50 and recall(rec) > 0.8
     # flat directory: all leaf centroids are scored in blocks, the best `probe` leaves are opened
     cfg = HBCConfig(24, "l2_squared", branching_factor=8, leaf_size=50, search_width=16,
@@ -319,3 +320,54 @@ def test_hbc_flat_directory_mode_recursive_build_and_leaf_merge():
     for n in flat.nodes.values():
         if not n.is_leaf:
             assert all(c in flat.nodes and flat.nodes[c].parent == n.id for c in n.children)
+
+
+def _dataset(kind: str, n: int, d: int, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    if kind == "clustered":
+        c = torch.randn(24, d, generator=g)
+        x = c[torch.randint(0, 24, (n,), generator=g)] + 0.3 * torch.randn(n, d, generator=g)
+        q = c[torch.randint(0, 24, (32,), generator=g)] + 0.3 * torch.randn(32, d, generator=g)
+    elif kind == "uniform":
+        x, q = torch.rand(n, d, generator=g) - 0.5, torch.rand(32, d, generator=g) - 0.5
+    else:                                  # heavy-tailed norms: what inner-product search has to cope with
+        x = torch.randn(n, d, generator=g) * torch.rand(n, 1, generator=g).pow(3) * 3
+        q = torch.randn(32, d, generator=g)
+    return x, q
+
+
+# expected recall@10 per (dataset, metric, index) with the tolerance the reference's recall tables use (a floor)
+RECALL_CASES = [
+    ("clustered", "l2_squared", "hbc", 0.85), ("clustered", "cosine", "hbc", 0.85),
+    ("clustered", "inner_product", "hbc", 0.75), ("uniform", "l2_squared", "hbc", 0.7),
+    ("uniform", "cosine", "hbc", 0.45), ("skewed", "inner_product", "hbc", 0.6),
+    ("clustered", "l2_squared", "hbc_hilbert_seeded", 0.85), ("clustered", "cosine", "hbc_flat", 0.7),
+    ("clustered", "l2_squared", "ivf", 0.9), ("clustered", "cosine", "ivf", 0.9),
+    ("uniform", "inner_product", "ivf", 0.7), ("clustered", "l2_squared", "flat", 1.0),
+    ("skewed", "inner_product", "flat", 1.0), ("uniform", "cosine", "flat", 0.99),
+]
+
+
+@pytest.mark.parametrize("dataset,metric,kind,floor", RECALL_CASES)
+def test_recall_table(dataset, metric, kind, floor):
+    from antfly_b200.index.ivf import IVFIndex
+
+    x, q = _dataset(dataset, 3000, 32, seed=zlib.crc32(f"{dataset}-{metric}".encode()) % 997)
+    xb, qb = x.to(torch.bfloat16).float(), q.to(torch.bfloat16).float()
+    truth = exact_search_fp32(qb, xb, 10, metric)
+    if kind == "flat":
+        idx = FlatIndex(xb, metric=metric)
+        idx.seed_cols, idx.cand_cap = 256, 512
+        found = idx.search(qb, 10).ids
+    elif kind == "ivf":
+        found = IVFIndex(xb, 40, metric=metric).search(qb, 10, nprobe=12).ids
+    else:
+        extra = {"hbc": {}, "hbc_hilbert_seeded": {"bulk_build": "hilbert_seeded"},
+                 "hbc_flat": {"centroid_directory_mode": "flat_rabitq"}}[kind]
+        # epsilon widens the centroid-distance pruning band; data without cluster structure needs a wide one
+        eps = 3.0 if dataset == "uniform" else 1.0
+        idx = HBCIndex.bulk_build(xb, HBCConfig(32, metric, branching_factor=8, leaf_size=60, search_width=24,
+                                                epsilon=eps, **extra))
+        found = torch.tensor([(idx.search(qb[i], 10)[0] + [-1] * 10)[:10] for i in range(32)])
+    r = recall_at_k(found, truth.ids, 10)
+    assert r >= floor, (dataset, metric, kind, r)
