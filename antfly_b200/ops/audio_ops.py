@@ -135,3 +135,65 @@ def log_mel(wave_16k: torch.Tensor, n_mels: int = 80, n_fft: int = 400, hop: int
     lg = torch.log10(mel.clamp(min=1e-10))
     lg = torch.maximum(lg, lg.max() - 8.0)
     return (lg + 4.0) / 4.0
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CLAP front end: 48 kHz, 1024-point FFT, hop 480, 64 HTK mel bands over 50 Hz .. 14 kHz, power in dB.
+CLAP_RATE, CLAP_FFT, CLAP_HOP, CLAP_MELS, CLAP_SECONDS = 48000, 1024, 480, 64, 10
+
+
+def mel_filterbank_htk(n_mels: int, n_fft: int, rate: int, fmin: float, fmax: float) -> torch.Tensor:
+    """[n_fft / 2 + 1, n_mels] triangular filters on the HTK mel scale (2595 log10(1 + f / 700)), not normalised."""
+    to_mel = lambda f: 2595.0 * math.log10(1.0 + f / 700.0)
+    freqs = torch.linspace(0, rate // 2, n_fft // 2 + 1, dtype=torch.float64)
+    mels = torch.linspace(to_mel(fmin), to_mel(fmax), n_mels + 2, dtype=torch.float64)
+    edges = 700.0 * (torch.pow(10.0, mels / 2595.0) - 1.0)
+    diff = edges[1:] - edges[:-1]
+    slopes = edges[None, :] - freqs[:, None]
+    fb = torch.clamp(torch.minimum(-slopes[:, :-2] / diff[:-1], slopes[:, 2:] / diff[1:]), min=0.0)
+    return fb.float()
+
+
+def clap_log_mel(wave: torch.Tensor) -> torch.Tensor:
+    """Mono 48 kHz waveform -> [frames, 64] mel power in dB (``10 log10(max(p, 1e-10))``), one frame per hop plus
+    one (centred frames over a reflect-padded signal)."""
+    x = wave.double()
+    key = ("clap", str(x.device))
+    if key not in _FB:
+        _FB[key] = (mel_filterbank_htk(CLAP_MELS, CLAP_FFT, CLAP_RATE, 50.0, 14000.0).double().to(x.device),
+                    torch.hann_window(CLAP_FFT, periodic=True, dtype=torch.float64, device=x.device))
+    fb, win = _FB[key]
+    spec = torch.stft(x, CLAP_FFT, CLAP_HOP, window=win, center=True, pad_mode="reflect", return_complex=True)
+    mel = (spec.abs().pow(2).T @ fb).clamp(min=1e-10)
+    return (10.0 * torch.log10(mel)).float()
+
+
+def clap_features(wave_48k: torch.Tensor, channels: int = 4) -> Tuple[torch.Tensor, bool]:
+    """Waveform -> ([channels, 1001, 64] features, is_longer), the input of the CLAP audio tower.
+
+    Clips of at most ten seconds are repeated a whole number of times, zero-padded to ten seconds and their
+    spectrogram is copied into every channel.  Longer clips are described by four planes: the whole spectrogram
+    shrunk to 1001 frames (bilinear, half-pixel centres) and three ten-second crops taken at the front, the middle and
+    the back -- fixed positions, where the training-time recipe drew them at random, so that an embedding is a
+    function of the audio alone (zig/pkg/inference/src/pipelines/audio.zig:111 ``clapInputFeatures``, :270)."""
+    n_max = CLAP_SECONDS * CLAP_RATE
+    frames = n_max // CLAP_HOP + 1
+    x = wave_48k.float().flatten()
+    if x.numel() > n_max:
+        mel = clap_log_mel(x)
+        total = mel.shape[0]
+        if total == frames:
+            return mel[None].expand(max(channels, 4), -1, -1).contiguous(), False
+        shrink = torch.nn.functional.interpolate(mel[None, None], size=(frames, CLAP_MELS), mode="bilinear",
+                                                 align_corners=False)[0, 0]
+        starts = [0, (total - frames) // 2, total - frames]
+        planes = [shrink] + [mel[s:s + frames] for s in starts]
+        out = torch.stack([planes[c % 4] for c in range(max(channels, 4))])
+        return out, True
+    if x.numel() == 0:
+        x = torch.zeros(n_max)
+    else:
+        x = x.repeat(n_max // x.numel())
+        x = torch.nn.functional.pad(x, (0, n_max - x.numel()))
+    mel = clap_log_mel(x)
+    return mel[None].expand(channels, -1, -1).contiguous(), False
