@@ -135,6 +135,12 @@ class ModelManager:
 
             model = ClipModel.from_state_dict(ClipConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = ClipEmbedder(model, tok)
+        elif task == "embedder" and cfg_d.get("model_type") == "clap":
+            from ..models.clap import ClapConfig, ClapModel
+            from ..pipelines.multimodal import ClapEmbedder
+
+            model = ClapModel.from_state_dict(ClapConfig.from_hf(cfg_d), sd, device=self.device)
+            pipe = ClapEmbedder(model, tok)
         elif task == "embedder" and cfg_d.get("model_type") in ("qwen2", "qwen3", "llama", "mistral", "gemma", "phi3"):
             # decoder-based embedding models (Qwen3-Embedding, E5-Mistral, ...): last-token pooling
             from ..pipelines.embedding import DecoderEmbedder

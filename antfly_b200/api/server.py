@@ -183,7 +183,8 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         req, bad = await parse(request, S.EmbedRequest)
         if bad:
             return bad
-        images = {}  # position in the input -> decoded image (content parts of type image_url / image)
+        images = {}  # position in the input -> decoded image (content parts of type image_url / image / media)
+        audios = {}  # position in the input -> encoded audio bytes (content parts of type audio / media)
         if isinstance(req.input, str):
             texts = [req.input]
         else:
@@ -205,6 +206,42 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     except Exception as e:
                         return _err(400, "invalid_request", f"content part {i}: {e}")
                     texts.append(None)
+                elif p.type in ("audio", "input_audio", "audio_url", "media"):
+                    # {"type": "media", "mime_type": "audio/wav" | "image/png", "data": base64 or a data: URL}
+                    # (zig/pkg/inference/src/server/server.zig:7389 resolveMediaContentPart); "audio" parts carry
+                    # the same payload under data / audio / url
+                    extra = p.model_extra or {}
+                    payload = extra.get("data") or extra.get("audio") or extra.get("input_audio") or extra.get("url") \
+                        or extra.get("audio_url")
+                    if isinstance(payload, dict):
+                        payload = payload.get("data") or payload.get("url")
+                    mime = (extra.get("mime_type") or "").split(";")[0].strip().lower()
+                    try:
+                        import base64 as _b64
+
+                        if not isinstance(payload, str) or not payload:
+                            raise ValueError("missing data")
+                        if payload.startswith("data:"):
+                            head, _, body = payload.partition(",")
+                            embedded = head[5:].split(";")[0].strip().lower()
+                            if mime and embedded and mime != embedded:
+                                raise ValueError(f"mime_type {mime!r} does not match the data URL's {embedded!r}")
+                            mime = mime or embedded
+                            payload = body
+                        raw = _b64.b64decode(payload, validate=True)
+                        if p.type == "media" and not mime:
+                            raise ValueError("media parts need a mime_type")
+                        if mime.startswith("image/"):
+                            from ..pipelines.multimodal import decode_image_bytes
+
+                            images[i] = decode_image_bytes(raw)
+                        elif mime.startswith("audio/") or (p.type != "media" and not mime):
+                            audios[i] = raw
+                        else:
+                            raise ValueError(f"unsupported media type {mime!r}")
+                    except Exception as e:
+                        return _err(400, "invalid_request", f"content part {i}: {e}")
+                    texts.append(None)
                 else:
                     return _err(400, "invalid_request", f"content part type {p.type!r} is not supported")
         if not texts:
@@ -213,20 +250,29 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         def work():
             lm = mgr.get(req.model, "embedder")
-            if images:
-                if not hasattr(lm.pipeline, "embed_images"):
+            if images or audios:
+                if images and not hasattr(lm.pipeline, "embed_images"):
                     raise ValueError(f"model {req.model!r} does not embed images")
+                if audios and not hasattr(lm.pipeline, "embed_audio"):
+                    raise ValueError(f"model {req.model!r} does not embed audio")
                 import torch as _torch
 
                 only_text = [t for t in texts if t is not None]
                 temb, ntok = lm.pipeline.embed(only_text, task_type, req.dimensions) if only_text else (None, 0)
-                iemb = lm.pipeline.embed_images([images[i] for i in sorted(images)]).cpu()
-                if req.dimensions:
-                    iemb = _torch.nn.functional.normalize(iemb[:, : req.dimensions], dim=-1)
-                rows, ti, ii = [], 0, 0
+                media = {}
+                if images:
+                    order = sorted(images)
+                    media.update(zip(order, lm.pipeline.embed_images([images[i] for i in order]).cpu()))
+                if audios:
+                    order = sorted(audios)
+                    media.update(zip(order, lm.pipeline.embed_audio([audios[i] for i in order]).cpu()))
+                rows, ti = [], 0
                 for i, t in enumerate(texts):
                     if t is None:
-                        rows.append(iemb[ii]); ii += 1
+                        row = media[i]
+                        if req.dimensions:
+                            row = _torch.nn.functional.normalize(row[: req.dimensions], dim=-1)
+                        rows.append(row)
                     else:
                         rows.append(temb[ti]); ti += 1
                 emb = _torch.stack(rows)

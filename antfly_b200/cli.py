@@ -93,12 +93,31 @@ def cmd_embed(args) -> int:
     mgr = _manager(args)
     lm = _get(mgr, args.model, "embedder")
     t0 = time.perf_counter()
-    emb, ntok = lm.pipeline.embed(args.text, dimensions=args.dimensions)
+    rows, ntok = [], 0
+    if args.text:
+        emb, ntok = lm.pipeline.embed(args.text, dimensions=args.dimensions)
+        rows += [("text", r) for r in emb]
+    # --image / --audio: files embedded by a dual-tower model into the same space as the texts
+    for kind, paths, fn in (("image", args.image, "embed_images"), ("audio", args.audio, "embed_audio")):
+        if not paths:
+            continue
+        if not hasattr(lm.pipeline, fn):
+            print(f"model {args.model!r} does not embed {kind} inputs", file=sys.stderr)
+            return 2
+        e = getattr(lm.pipeline, fn)(paths).cpu()
+        if args.dimensions:
+            import torch
+
+            e = torch.nn.functional.normalize(e[:, : args.dimensions], dim=-1)
+        rows += [(kind, r) for r in e]
+    if not rows:
+        print("nothing to embed: give --text, --image or --audio", file=sys.stderr)
+        return 2
     dt = time.perf_counter() - t0
-    for i, row in enumerate(emb):
-        print(json.dumps({"index": i, "embedding": [round(x, 6) for x in row.tolist()]}))
+    for i, (kind, row) in enumerate(rows):
+        print(json.dumps({"index": i, "input": kind, "embedding": [round(x, 6) for x in row.tolist()]}))
     if args.print_timing:
-        print(f"embed_timing_ms: total={dt * 1e3:.1f} texts={len(args.text)} tokens={ntok}", file=sys.stderr)
+        print(f"embed_timing_ms: total={dt * 1e3:.1f} inputs={len(rows)} tokens={ntok}", file=sys.stderr)
     return 0
 
 
@@ -346,7 +365,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--device-b"); p.add_argument("--min-cosine", type=float, default=0.99)
     p.set_defaults(fn=cmd_compare)
     p = sub.add_parser("embed"); common(p)
-    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", default=[])
+    p.add_argument("--image", nargs="+", default=[]); p.add_argument("--audio", nargs="+", default=[])
     p.add_argument("--dimensions", type=int); p.add_argument("--print-timing", action="store_true")
     p.set_defaults(fn=cmd_embed)
     p = sub.add_parser("rerank"); common(p)

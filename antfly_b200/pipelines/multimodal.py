@@ -106,3 +106,75 @@ class ClipEmbedder:
             seqs.append(([self.bos_id] if self.bos_id is not None else []) + ids +
                         ([self.eos_id] if self.eos_id is not None else []))
         return self.model.embed_text(seqs)
+
+
+AudioLike = Union[str, bytes, torch.Tensor, tuple]
+
+
+class ClapEmbedder:
+    """Audio / text embedding with a CLAP dual encoder.
+
+    ``embed_audio`` takes WAV bytes or paths, waveforms at 48 kHz, or ``(waveform, rate)`` pairs; each clip is
+    resampled to 48 kHz, turned into the tower's spectrogram planes (short clips repeated and padded to ten
+    seconds, long ones described by a shrunk overview plus three crops) and embedded.  ``embed_texts`` runs the
+    RoBERTa tower.  Rows are L2-normalised fp32 in the shared space (zig/pkg/inference/src/pipelines/embedding.zig:634
+    ``embedAudioPcm``)."""
+
+    def __init__(self, model, tokenizer=None, bos_id: Optional[int] = None, eos_id: Optional[int] = None):
+        self.model, self.tokenizer = model, tokenizer
+        self.bos_id, self.eos_id = bos_id, eos_id
+        if tokenizer is not None:
+            self.bos_id = bos_id if bos_id is not None else tokenizer.special.bos_id
+            self.eos_id = eos_id if eos_id is not None else tokenizer.special.eos_id
+
+    @property
+    def dim(self) -> int:
+        return self.model.cfg.projection_dim
+
+    def embed_audio(self, clips: Sequence[AudioLike], batch_size: int = 16) -> torch.Tensor:
+        from ..ops import audio_ops as Au
+
+        channels = 4 if self.model.cfg.audio.enable_fusion else 1
+        feats: List[torch.Tensor] = []
+        longer: List[bool] = []
+        for c in clips:
+            if isinstance(c, (bytes, bytearray, str)):
+                wave, rate = Au.read_wav(c)
+            elif isinstance(c, tuple):
+                wave, rate = torch.as_tensor(c[0]).float().flatten(), int(c[1])
+            else:
+                wave, rate = torch.as_tensor(c).float().flatten(), Au.CLAP_RATE
+            if rate != Au.CLAP_RATE:
+                wave = Au.resample(wave, rate, Au.CLAP_RATE)
+            f, is_long = Au.clap_features(wave, channels)
+            if not self.model.cfg.audio.enable_fusion:
+                f = f[:1]                                   # unfused towers see the first plane only
+            feats.append(f)
+            longer.append(is_long)
+        out = [self.model.embed_audio(torch.stack(feats[i:i + batch_size]), longer[i:i + batch_size])
+               for i in range(0, len(feats), batch_size)]
+        return torch.cat(out, 0) if out else torch.zeros((0, self.dim))
+
+    def embed_texts(self, texts: Sequence[str]) -> torch.Tensor:
+        if self.tokenizer is None:
+            raise RuntimeError("this embedder has no tokenizer")
+        limit = self.model.cfg.text.max_position_embeddings - self.model.cfg.text.position_offset
+        seqs = []
+        for t in texts:
+            ids = self.tokenizer.encode(t)[: limit - 2]
+            seqs.append(([self.bos_id] if self.bos_id is not None else []) + ids +
+                        ([self.eos_id] if self.eos_id is not None else []))
+        return self.model.embed_text(seqs)
+
+    def embed_token_ids(self, seqs: Sequence[Sequence[int]]) -> torch.Tensor:
+        return self.model.embed_text(seqs)
+
+    def embed(self, texts: Sequence[str], task_type: Optional[str] = None, dimensions: Optional[int] = None):
+        """The text-embedding contract of the HTTP endpoint: (fp32 [N, dims] on the host, prompt tokens)."""
+        e = self.embed_texts(texts).cpu()
+        if dimensions:
+            if dimensions > e.shape[1]:
+                raise ValueError(f"dimensions {dimensions} exceeds the model's {e.shape[1]}")
+            e = torch.nn.functional.normalize(e[:, :dimensions], dim=-1)
+        limit = self.model.cfg.text.max_position_embeddings - self.model.cfg.text.position_offset
+        return e, sum(min(len(self.tokenizer.encode(t)) + 2, limit) for t in texts)

@@ -90,3 +90,59 @@ def test_clap_front_end_matches_feature_extractor():
     # silence and a one-sample clip do not divide by zero
     assert torch.isfinite(A.clap_features(torch.zeros(0), 1)[0]).all()
     assert A.clap_features(torch.ones(1), 1)[0].shape == (1, 1001, 64)
+
+
+def test_embed_endpoint_takes_audio_media_parts():
+    """WAV bytes as a ``media`` content part beside text, through a CLAP embedder registered with the server."""
+    import base64
+    import io
+    import wave
+
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+    from antfly_b200.pipelines.multimodal import ClapEmbedder
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    hf_cfg, hf = _tiny(True)
+    model = ClapModel.from_state_dict(ClapConfig.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                      dtype=torch.float32)
+    # the tiny tower takes 16 mel bins x 256 frames; give the embedder a matching front end
+    pipe = ClapEmbedder(model, ByteTokenizer(200), bos_id=0, eos_id=2)
+    calls = []
+
+    def fake_features(wave_48k, channels=4):
+        calls.append(int(wave_48k.numel()))
+        g = torch.Generator().manual_seed(int(wave_48k.numel()))
+        return torch.randn(channels, 250, 16, generator=g) * 10 - 20, wave_48k.numel() > 480000
+
+    import antfly_b200.ops.audio_ops as Au
+    real = Au.clap_features
+    Au.clap_features = fake_features
+    try:
+        mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+        mgr.register("tiny-clap", "embedder", pipe, pipe.tokenizer)
+        c = TestClient(create_app(mgr))
+        buf = io.BytesIO()
+        with wave.open(buf, "wb") as w:
+            w.setnchannels(1); w.setsampwidth(2); w.setframerate(16000)
+            w.writeframes((np.sin(np.arange(8000) / 10.0) * 12000).astype("<i2").tobytes())
+        b64 = base64.b64encode(buf.getvalue()).decode()
+        r = c.post("/ai/v1/embed", json={"model": "tiny-clap", "input": [
+            {"type": "text", "text": "a dog barking"},
+            {"type": "media", "mime_type": "audio/wav", "data": b64},
+            {"type": "audio", "data": "data:audio/wav;base64," + b64}]})
+        assert r.status_code == 200, r.text
+        data = r.json()["data"]
+        assert len(data) == 3 and all(len(d["embedding"]) == 48 for d in data)
+        assert all(abs(sum(v * v for v in d["embedding"]) - 1.0) < 1e-3 for d in data)
+        assert data[1]["embedding"] == data[2]["embedding"]           # the same clip twice
+        assert calls == [24000, 24000]                                # 0.5 s at 16 kHz resampled to 48 kHz
+        r = c.post("/ai/v1/embed", json={"model": "tiny-clap", "input": [
+            {"type": "media", "mime_type": "audio/wav", "data": "data:image/png;base64," + b64}]})
+        assert r.status_code == 400 and "does not match" in r.json()["message"]
+        r = c.post("/ai/v1/embed", json={"model": "tiny-clap", "input": [{"type": "media", "data": b64}]})
+        assert r.status_code == 400 and "mime_type" in r.json()["message"]
+    finally:
+        Au.clap_features = real
