@@ -192,6 +192,25 @@ class ModelManager:
                     gen = _json.load(f)
             model = WhisperModel.from_state_dict(WhisperConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = Transcriber(model, tok, gen)
+        elif task in ("recognizer", "classifier") and any(k.startswith("count_embed.") for k in sd):
+            # GLiNER: labels are given per request, one model serves recognition, label scoring and relations
+            import json as _json
+
+            from ..models.deberta import DebertaConfig
+            from ..models.gliner import GlinerModel
+            from ..pipelines.gliner import GlinerConfig, GlinerPipeline
+
+            enc_cfg = cfg_d.get("encoder_config") or cfg_d
+            model = GlinerModel.from_state_dict(DebertaConfig.from_hf(enc_cfg), sd, device=self.device)
+            added: dict = {}
+            ap = os.path.join(path, "added_tokens.json")
+            if os.path.exists(ap):
+                with open(ap, encoding="utf-8") as f:
+                    added = _json.load(f)
+            gcfg = dict(cfg_d)
+            if "max_len" in gcfg and "max_length" not in gcfg:
+                gcfg["max_length"] = gcfg["max_len"]
+            pipe = GlinerPipeline(model, tok, GlinerConfig.from_files(gcfg, added))
         elif task in ("recognizer", "classifier", "chunker"):
             from ..pipelines.classification import TextClassifier, TokenClassifier
 

@@ -765,6 +765,50 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 raise ValueError("schema needs entities, relations and / or classifications")
             data = [{"id": i.id} if i.id is not None else {} for i in req.inputs]
             ntok = 0
+            zero_shot = None
+            if want_ents or tasks or rel_schema:
+                try:
+                    cand = mgr.get(req.model, "recognizer").pipeline
+                    zero_shot = cand if hasattr(cand, "extract_relations") else None
+                except Exception:
+                    zero_shot = None
+            if zero_shot is not None:
+                # a span model that takes its labels from the request answers the whole schema by itself
+                rel_types = [str(r.get("type")) for r in rel_schema if isinstance(r, dict) and r.get("type")]
+                if want_ents and rel_types:
+                    all_e, all_r = zero_shot.extract_relations(texts, want_ents, rel_types)
+                elif want_ents:
+                    all_e, all_r = zero_shot.recognize(texts, want_ents, threshold=thr or None), [[] for _ in texts]
+                else:
+                    all_e, all_r = [[] for _ in texts], [[] for _ in texts]
+                for rec, text, ents, rels in zip(data, texts, all_e, all_r):
+                    raw = text.encode("utf-8")
+
+                    def item(e):
+                        d = {"label": e.label, "text": e.text, "score": e.score}
+                        if opts.get("include_spans", True):       # character offsets, from the byte offsets
+                            d["start"] = len(raw[: e.start].decode("utf-8", "replace"))
+                            d["end"] = d["start"] + len(e.text)
+                        if not opts.get("include_confidence", True):
+                            d.pop("score")
+                        return d
+
+                    if want_ents:
+                        rec["entities"] = [item(e) for e in ents]
+                    if rel_types:
+                        pos = {(e.start, e.end, e.label): i for i, e in enumerate(ents)}
+                        rec["relations"] = [{
+                            "type": r.label, "score": r.score,
+                            "source": {**item(r.head), "entity_index": pos.get((r.head.start, r.head.end, r.head.label), -1)},
+                            "target": {**item(r.tail), "entity_index": pos.get((r.tail.start, r.tail.end, r.tail.label), -1)},
+                        } for r in rels]
+                for t in tasks:
+                    labels = [str(l) for l in t.get("labels") or []]
+                    for rec, text in zip(data, texts):
+                        got = zero_shot.classify(text, labels, threshold=thr, multi_label=bool(t.get("multi_label")))
+                        rec.setdefault("classifications", [])
+                        rec["classifications"] += [{"name": t.get("name", ""), "label": l, "score": sc} for l, sc in got]
+                want_ents, rel_schema, tasks = [], [], []
             if want_ents:
                 ner = mgr.get(req.model, "recognizer").pipeline
                 allowed = {w.lower() for w in want_ents}

@@ -237,6 +237,13 @@ def cmd_classify(args) -> int:
 
 def cmd_recognize(args) -> int:
     lm = _manager(args).get(args.model, "recognizer")
+    if hasattr(lm.pipeline, "recognize"):                 # zero-shot span model: the labels come from --labels
+        for text, ents in zip(args.text, lm.pipeline.recognize(args.text, args.labels or None,
+                                                               threshold=args.threshold)):
+            print(json.dumps({"text": text, "entities": [
+                {"label": e.label, "text": e.text, "score": round(e.score, 4), "start": e.start, "end": e.end}
+                for e in ents]}))
+        return 0
     for text, ents in zip(args.text, lm.pipeline.entities(args.text)):
         print(json.dumps({"text": text, "entities": [
             {"label": e.label, "text": e.text, "score": round(e.score, 4), "start_token": e.start_token,
@@ -347,6 +354,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--top-k", type=int, default=1); p.set_defaults(fn=cmd_classify)
     p = sub.add_parser("recognize"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--labels", nargs="+", default=[]); p.add_argument("--threshold", type=float)
     p.set_defaults(fn=cmd_recognize)
     p = sub.add_parser("rewrite"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
