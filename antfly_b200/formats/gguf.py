@@ -19,8 +19,9 @@ GGUF_MAGIC = b"GGUF"
 TYPE_NAMES = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
               11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K", 16: "IQ2_XXS", 17: "IQ2_XS", 18: "IQ3_XXS",
               19: "IQ1_S", 20: "IQ4_NL", 21: "IQ3_S", 22: "IQ2_S", 23: "IQ4_XS", 24: "I8", 25: "I16", 26: "I32",
-              27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16", 34: "TQ1_0", 35: "TQ2_0", 39: "MXFP4", 40: "NVFP4"}
-SUPPORTED = {0, 1, 2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 15, 20, 23, 30, 34, 35, 39, 40}
+              27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16", 34: "TQ1_0", 35: "TQ2_0", 36: "I2_S", 37: "I8_S", 39: "MXFP4",
+              40: "NVFP4"}
+SUPPORTED = {0, 1, 2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 15, 20, 23, 30, 34, 35, 36, 37, 39, 40}
 _SCALARS = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 
 
@@ -94,8 +95,25 @@ class GGUFFile:
         lib.afb_gguf_block_values.restype = ctypes.c_long
         n = int(np.prod(info.shape)) if info.shape else 1
         bv, bb = lib.afb_gguf_block_values(info.type), lib.afb_gguf_block_bytes(info.type)
-        nbytes = n // bv * bb
         start = self.data_start + info.offset
+        if info.type == 36:
+            # BitNet I2_S: whole 128-value blocks (the last one padded), then the tensor's fp32 scale at byte n / 4
+            # of a 32-byte tail (zig/pkg/inference/src/gguf/tensor_types.zig:248 byteLen)
+            padded = -(-n // bv) * bv
+            src = np.frombuffer(self._mm, dtype=np.uint8, count=padded // bv * bb, offset=start)
+            full = np.empty(padded, dtype=np.float32)
+            rc = lib.afb_gguf_dequantize(ctypes.c_int(36), src.ctypes.data_as(ctypes.c_void_p),
+                                         full.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(padded))
+            if rc != 0:
+                raise NotImplementedError("GGUF tensor type I2_S is not supported")
+            out = full[:n].copy()
+            tail = start + -(-n // 4)
+            if tail + 4 <= len(self._mm):
+                scale = float(np.frombuffer(self._mm, dtype="<f4", count=1, offset=tail)[0])
+                if np.isfinite(scale) and scale != 0.0:
+                    out *= scale
+            return torch.from_numpy(out).view(info.shape)
+        nbytes = n // bv * bb
         src = np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=start)
         out = np.empty(n, dtype=np.float32)
         rc = lib.afb_gguf_dequantize(ctypes.c_int(info.type), src.ctypes.data_as(ctypes.c_void_p),
@@ -121,7 +139,8 @@ _GGUF_TO_HF = {
 }
 _LAYER = {"attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
           "attn_output": "self_attn.o_proj", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj",
-          "ffn_down": "mlp.down_proj", "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm"}
+          "ffn_down": "mlp.down_proj", "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm",
+          "attn_sub_norm": "self_attn.attn_sub_norm", "ffn_sub_norm": "mlp.ffn_sub_norm"}   # BitNet
 
 
 def hf_name(gguf_name: str) -> str:
@@ -180,12 +199,30 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
 def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
     arch = md.get("general.architecture", "llama")
     g = lambda k, d=None: md.get(f"{arch}.{k}", d)
+    if arch.startswith("bitnet"):          # "bitnet" / "bitnet-b1.58": keys carry the file's own spelling
+        return {**llama_config_from_gguf({**md, "general.architecture": "llama",
+                                          **{"llama." + k[len(arch) + 1:]: v for k, v in md.items()
+                                             if k.startswith(arch + ".")}}),
+                "model_type": "bitnet", "tie_word_embeddings": True}
     return {"model_type": arch, "hidden_size": g("embedding_length"), "num_hidden_layers": g("block_count"),
             "num_attention_heads": g("attention.head_count"),
             "num_key_value_heads": g("attention.head_count_kv", g("attention.head_count")),
             "intermediate_size": g("feed_forward_length"), "rope_theta": g("rope.freq_base", 10000.0),
             "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
             "vocab_size": g("vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or None)}
+
+
+def pack_i2s(values: np.ndarray) -> bytes:
+    """fp32 values -> BitNet I2_S bytes: the tensor is ternarised against its mean magnitude (``round(v / mean|v|)``
+    clipped to [-1, 1]), 128 values go into 32 bytes (byte ``g`` holds values ``g``, ``g + 32``, ``g + 64``,
+    ``g + 96`` in bits 7-6, 5-4, 3-2, 1-0 as value + 1), and a 32-byte tail starts with the fp32 scale."""
+    a = np.asarray(values, dtype=np.float32).reshape(-1)
+    if a.size % 128:
+        raise ValueError("I2_S tensors hold a multiple of 128 values")
+    scale = max(float(np.abs(a).mean()), 1e-5) if a.size else 1.0
+    codes = (np.clip(np.rint(a / scale), -1, 1) + 1).astype(np.uint8).reshape(-1, 4, 32)
+    packed = (codes[:, 0] << 6) | (codes[:, 1] << 4) | (codes[:, 2] << 2) | codes[:, 3]
+    return packed.astype(np.uint8).tobytes() + struct.pack("<f", scale) + b"\0" * 28
 
 
 def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[int, torch.Tensor]]) -> None:
@@ -224,6 +261,8 @@ def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[int
             fn = lib.afb_gguf_quantize_q8_0 if ty == 8 else lib.afb_gguf_quantize_q4_0
             fn(a.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(a.size))
             raw = out.tobytes()
+        elif ty == 36:
+            raw = pack_i2s(a)
         else:
             raise NotImplementedError(ty)
         pad = (32 - len(raw) % 32) % 32

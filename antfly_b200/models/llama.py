@@ -48,7 +48,11 @@ class LlamaConfig:
     max_position_embeddings: int = 131072
     norm_plus_one: bool = False   # Gemma: RMSNorm scales by (1 + gamma)
     embed_scale: float = 1.0      # Gemma: token embeddings multiplied by sqrt(hidden)
-    gate_act: str = "silu"        # gated-MLP activation: silu (SwiGLU) or gelu_tanh (GeGLU, Gemma)
+    gate_act: str = "silu"        # gated-MLP activation: silu (SwiGLU), gelu_tanh (GeGLU, Gemma), relu2 (BitNet)
+    # BitNet b1.58: ternary weights with one scale per matrix, activations rounded to 8 bits per token before
+    # every projection, an extra RMS norm before the attention-output and the down projections
+    bitnet: bool = False
+    bitnet_scale_divides: bool = False   # packed checkpoints of the "bitlinear" kind store 1 / scale
     # Mixture of experts (Mixtral, Qwen2-MoE, Qwen3-MoE): 0 experts = dense MLP
     num_experts: int = 0
     num_experts_per_tok: int = 2
@@ -95,6 +99,11 @@ class LlamaConfig:
                 raise ValueError("models that mix dense and sparse MLP layers are not supported")
             cfg.qkv_bias = mt == "qwen2_moe"
             cfg.qk_norm = mt == "qwen3_moe"
+        if mt == "bitnet":
+            cfg.bitnet = True
+            cfg.gate_act = "relu2"
+            cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
+            cfg.bitnet_scale_divides = (d.get("quantization_config") or {}).get("linear_class") == "bitlinear"
         if mt == "gemma":
             cfg.norm_plus_one = True
             cfg.embed_scale = float(cfg.hidden_size) ** 0.5
@@ -153,6 +162,27 @@ class MoeRuntimeState:
     residency: ExpertResidency
     predictor: CoactivationPredictor
     max_predicted: int = 2
+
+
+def bitnet_ternary(weight: torch.Tensor, weight_scale: Optional[torch.Tensor], scale_divides: bool):
+    """One BitNet projection -> (ternary matrix with entries -1 / 0 / +1 as fp32, the scalar that multiplies it).
+
+    Full-precision weights are ternarised on load (``round(w / mean|w|)`` clipped to [-1, 1], scalar ``mean|w|``).
+    Packed checkpoints hold four 2-bit codes per byte -- byte row ``r`` carries output rows ``r``, ``r + R``,
+    ``r + 2R``, ``r + 3R`` (``R`` = packed rows) in bits 0-1, 2-3, 4-5, 6-7, each code being the value plus one --
+    and the scalar beside them."""
+    if weight.dtype == torch.uint8:
+        R_ = weight.shape[0]
+        t = torch.cat([((weight >> (2 * i)) & 3) for i in range(4)], 0).float() - 1.0
+        assert t.shape[0] == 4 * R_
+        sc = float(weight_scale.float().flatten()[0]) if weight_scale is not None else 1.0
+        return t, (1.0 / sc if scale_divides else sc)
+    wf = weight.float()
+    top = float(wf.abs().max())
+    if top > 0 and bool(((wf.abs() == top) | (wf == 0)).all()):
+        return torch.sign(wf), top           # already ternary times one scalar (decoded from a 2-bit file format)
+    m = float(wf.abs().mean().clamp(min=1e-5))
+    return (wf / m).round().clamp(-1, 1), m
 
 
 class LlamaModel:
@@ -247,6 +277,21 @@ class LlamaModel:
         w["embed"] = emb.to(device)
         for l in range(*(layers or (0, cfg.num_hidden_layers))):
             s, p = f"{pre}layers.{l}.", f"l{l}."
+            if cfg.bitnet:
+                assert tp_size == 1, "BitNet models run on one GPU"
+                sd = dict(sd)
+                ws = {}
+                for name in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                             "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"):
+                    sd[s + name + ".weight"], ws[name] = bitnet_ternary(
+                        sd[s + name + ".weight"], sd.get(s + name + ".weight_scale"), cfg.bitnet_scale_divides)
+                rows = lambda name: torch.full((sd[s + name + ".weight"].shape[0],), ws[name])
+                w[p + "qkv.ws"] = torch.cat([rows("self_attn." + n + "_proj") for n in "qkv"]).to(device)
+                w[p + "o.ws"] = rows("self_attn.o_proj").to(device)
+                w[p + "gu.ws"] = torch.stack([rows("mlp.gate_proj"), rows("mlp.up_proj")], 1).flatten().to(device)
+                w[p + "down.ws"] = rows("mlp.down_proj").to(device)
+                w[p + "attn_sub"] = sd[s + "self_attn.attn_sub_norm.weight"].to(torch.bfloat16).to(device)
+                w[p + "ffn_sub"] = sd[s + "mlp.ffn_sub_norm.weight"].to(torch.bfloat16).to(device)
             w[p + "ln1"] = sd[s + "input_layernorm.weight"].to(torch.bfloat16).to(device)
             w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
             if s + "self_attn.qkv_proj.weight" in sd:  # Phi-3: fused [q | k | v] rows
@@ -569,10 +614,23 @@ class LlamaModel:
         else:
             x = pp.recv_hidden(T, cfg.hidden_size, w[f"l{lo}.ln1"].device)
         h = Dn.norm(x, w[f"l{lo}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
+
+        def lin(a, key, residual=None):
+            if not cfg.bitnet:
+                return self._linear(a, w[key], T, residual=residual) if residual is not None else \
+                    self._linear(a, w[key], T)
+            # 8-bit activations are whole numbers up to 128 in magnitude and the weights are -1 / 0 / +1: both are
+            # exact in the GEMM's input formats and the fp32 accumulation is exact integer arithmetic
+            af = a.float()
+            amax = af.abs().amax(-1, keepdim=True).clamp(min=1e-5)
+            aq = (af * (127.0 / amax)).round().clamp(-128, 127).to(torch.bfloat16)
+            y = Q.gemm_w8a16(aq, w[key], partials=True).sum(0) * (amax / 127.0) * w[key + ".ws"]
+            return (y + residual.float()).to(torch.bfloat16) if residual is not None else y.to(torch.bfloat16)
+
         for l in range(lo, hi):
             p = f"l{l}."
             k_cache_l, v_cache_l = k_cache[l - lo], v_cache[l - lo]
-            qkv = self._linear(h, w[p + "qkv"], T)
+            qkv = lin(h, p + "qkv")
             q = A.rope_kv_write(qkv, b.positions, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, cfg.rope_theta,
                                 bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
                                 freq_scale=cfg.rope_freq_scale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
@@ -580,22 +638,30 @@ class LlamaModel:
             ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch)
-            x = self._linear(ctx.view(T, Hq * D), w[p + "o"], T, residual=x)
+            ctx = ctx.view(T, Hq * D)
+            if cfg.bitnet:
+                ctx = Dn.norm(ctx.contiguous(), w[p + "attn_sub"], eps=eps, rms=True)
+            x = lin(ctx, p + "o", residual=x)
             h = Dn.norm(x, w[p + "ln2"], eps=eps, rms=True, gamma_plus_one=gp1)
             if cfg.num_experts > 0:
                 x = (x.float() + self._moe_mlp(h, l, T)).to(torch.bfloat16)
                 if l + 1 < hi:
                     h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
                 continue
-            gu = self._linear(h, w[p + "gu"], T).float()  # columns alternate gate_i, up_i
+            gu = lin(h, p + "gu").float()  # columns alternate gate_i, up_i
             gate, up = gu[:, 0::2], gu[:, 1::2]
-            if cfg.gate_act == "gelu_tanh":
+            if cfg.gate_act == "relu2":
+                gate = torch.relu(gate).square()
+            elif cfg.gate_act == "gelu_tanh":
                 gate = torch.nn.functional.gelu(gate, approximate="tanh")
             elif cfg.gate_act == "gelu":
                 gate = torch.nn.functional.gelu(gate)
             else:
                 gate = torch.nn.functional.silu(gate)
-            x = self._linear((gate * up).to(torch.bfloat16), w[p + "down"], T, residual=x)
+            act = (gate * up).to(torch.bfloat16)
+            if cfg.bitnet:
+                act = Dn.norm(act.contiguous(), w[p + "ffn_sub"], eps=eps, rms=True)
+            x = lin(act, p + "down", residual=x)
             if l + 1 < hi:
                 h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
         n_rows = T if b.logit_rows.numel() == T else b.logit_rows.numel()

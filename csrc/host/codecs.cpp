@@ -109,12 +109,14 @@ long afb_gguf_block_bytes(int type) {
     case 10: return 84; case 11: return 110; case 12: return 144; case 13: return 176; case 14: return 210;
     case 15: return 292; case 20: return 18; case 23: return 136; case 34: return 54; case 35: return 66;
     case 39: return 17; case 40: return 36;
+    case 36: return 32; case 37: return 1;
     default: return -1;
   }
 }
 long afb_gguf_block_values(int type) {
   switch (type) {
-    case 0: case 1: case 30: return 1;
+    case 0: case 1: case 30: case 37: return 1;
+    case 36: return 128;
     case 2: case 3: case 6: case 7: case 8: case 20: case 39: return 32;
     case 40: return 64;
     case 10: case 11: case 12: case 13: case 14: case 15: case 23: case 34: case 35: return 256;
@@ -131,6 +133,21 @@ int afb_gguf_dequantize(int type, const uint8_t* src, float* dst, long n_values)
     case 30: { const uint16_t* h = reinterpret_cast<const uint16_t*>(src);
                for (long i = 0; i < n_values; ++i) { uint32_t b = static_cast<uint32_t>(h[i]) << 16; memcpy(&dst[i], &b, 4); }
                return 0; }
+    case 36: {  // I2_S (BitNet): 32 bytes carry 128 ternary values; byte g holds values g, g + 32, g + 64, g + 96
+                //  in bits 7-6, 5-4, 3-2, 1-0; codes 0 / 1 / 2 are -1 / 0 / +1.  The tensor's scale follows the blocks.
+      static const float kMap[4] = {-1.0f, 0.0f, 1.0f, 0.0f};
+      for (long b = 0; b < n_values / 128; ++b) {
+        const uint8_t* p = src + b * 32;
+        for (int g = 0; g < 32; ++g)
+          for (int lane = 0; lane < 4; ++lane) dst[b * 128 + lane * 32 + g] = kMap[(p[g] >> (6 - 2 * lane)) & 3];
+      }
+      return 0;
+    }
+    case 37: {  // I8_S: signed bytes
+      const int8_t* q = reinterpret_cast<const int8_t*>(src);
+      for (long i = 0; i < n_values; ++i) dst[i] = static_cast<float>(q[i]);
+      return 0;
+    }
     case 8: {
       for (long b = 0; b < n_values / 32; ++b) {
         const uint8_t* p = src + b * 34;

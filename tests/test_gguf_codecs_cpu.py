@@ -6,6 +6,7 @@ import ctypes
 
 import numpy as np
 import pytest
+import torch
 
 gguf = pytest.importorskip("gguf")
 
@@ -104,3 +105,40 @@ def test_per_element_decoder_matches_block_decoder(name):
         got = np.array([lib.afb_gguf_element(ctypes.c_int(int(qt)), blk.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(j))
                         for j in range(values)], dtype=np.float32)
         np.testing.assert_allclose(got, want[b], rtol=1e-6, atol=1e-6)
+
+
+def test_bitnet_i2s_and_i8s_decoding(tmp_path):
+    """BitNet's ternary type: lane order and code map as in the reference's golden vector
+    (zig/pkg/inference/src/gguf/quant_codec.zig:4010), the trailing scale, and a file round trip."""
+    import ctypes
+
+    from antfly_b200 import _native as N
+    from antfly_b200.formats import gguf as GG
+
+    lib = N.host()
+    raw = np.zeros(64, dtype=np.uint8)
+    raw[0], raw[32] = 0b11_10_01_00, 0b00_01_10_11
+    out = np.empty(256, dtype=np.float32)
+    assert lib.afb_gguf_dequantize(ctypes.c_int(36), raw.ctypes.data_as(ctypes.c_void_p),
+                                   out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(256)) == 0
+    assert [out[i] for i in (0, 32, 64, 96, 128, 160, 192, 224)] == [0.0, 1.0, 0.0, -1.0, -1.0, 0.0, 1.0, 0.0]
+    assert out[1] == -1.0                                        # an all-zero byte is four -1 codes
+    q = np.array([-3, 0, 127, -128], dtype=np.int8)
+    o4 = np.empty(4, dtype=np.float32)
+    assert lib.afb_gguf_dequantize(ctypes.c_int(37), q.ctypes.data_as(ctypes.c_void_p),
+                                   o4.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(4)) == 0
+    assert o4.tolist() == [-3.0, 0.0, 127.0, -128.0]
+
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(6, 128, generator=g)
+    path = str(tmp_path / "b.gguf")
+    GG.write_gguf(path, {"general.architecture": "bitnet"}, {"blk.0.attn_q.weight": (36, w), "x": (0, w[:1])})
+    f = GG.GGUFFile(path)
+    assert f.tensors["blk.0.attn_q.weight"].type_name == "I2_S"
+    got = f.tensor("blk.0.attn_q.weight")
+    m = float(w.abs().mean())
+    want = (w / m).round().clamp(-1, 1) * m
+    torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(f.tensor("x"), w[:1])            # the tensor after it starts where it should
+    with pytest.raises(ValueError):
+        GG.pack_i2s(np.zeros(100, dtype=np.float32))
