@@ -237,17 +237,42 @@ class ModelManager:
             model = BertModel.from_state_dict(cfg, sd, device=self.device)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         else:
+            vlm = None
             if cfg_d.get("model_type") in ("gpt2", "gpt_neo", "gpt_neox", "opt", "gptj", "phi", "falcon", "bloom"):
                 from ..models.gpt import GptConfig, GptModel
 
                 model = GptModel.from_state_dict(GptConfig.from_hf(cfg_d), sd, device=self.device)
+            elif cfg_d.get("model_type") == "qwen2_vl":
+                # decoder + vision tower in one checkpoint; images reach the decoder as soft tokens
+                import json as _json
+
+                from ..models import qwen2vl as QV
+                from ..pipelines.vlm import Qwen2VLAdapter, VlmTokens
+
+                text_d = dict(cfg_d.get("text_config") or {k: v for k, v in cfg_d.items() if k != "vision_config"})
+                text_d.setdefault("model_type", "qwen2_vl_text")
+                if "rope_scaling" not in text_d and cfg_d.get("rope_scaling"):
+                    text_d["rope_scaling"] = cfg_d["rope_scaling"]
+                model = LlamaModel.from_state_dict(LlamaConfig.from_hf(text_d), QV.text_state_dict(sd),
+                                                   device=self.device)
+                vision = QV.Qwen2VLVisionModel.from_state_dict(
+                    QV.Qwen2VLVisionConfig.from_hf(cfg_d.get("vision_config") or {}), sd, device=self.device)
+                pre = {}
+                pp = os.path.join(path, "preprocessor_config.json")
+                if os.path.exists(pp):
+                    with open(pp, encoding="utf-8") as f:
+                        pre = _json.load(f)
+                vlm = Qwen2VLAdapter(
+                    vision, VlmTokens(int(cfg_d.get("image_token_id", 151655)), cfg_d.get("vision_start_token_id"),
+                                      cfg_d.get("vision_end_token_id")),
+                    int(pre.get("min_pixels", 56 * 56)), int(pre.get("max_pixels", 14 * 14 * 4 * 1280)))
             else:
                 cfg = LlamaConfig.from_hf(cfg_d)
                 model = LlamaModel.from_state_dict(cfg, sd, device=self.device)
             eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
                             use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id,
                             prefix_cache=self.prefix_cache)
-            pipe = Generator(eng, tok, mf.chat_template)
+            pipe = Generator(eng, tok, mf.chat_template, vlm=vlm)
         return LoadedModel(name, task, pipe, tok, path, info={"weights": mf.weights, "capabilities": mf.capabilities})
 
     def _encoder(self, cfg_d: dict, sd):

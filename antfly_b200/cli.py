@@ -146,7 +146,8 @@ def cmd_generate(args) -> int:
                         min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
                         cache_compaction_ratio=args.cache_compaction_ratio)
     out = gen.generate(args.prompt, sp, raw_prompt=args.no_chat_template or args.raw_prompt,
-                       on_delta=(lambda d: (sys.stdout.write(d), sys.stdout.flush())) if args.stream else None)
+                       on_delta=(lambda d: (sys.stdout.write(d), sys.stdout.flush())) if args.stream else None,
+                       images=args.image or None)
     if not args.stream:
         print(out.text)
     else:
@@ -392,6 +393,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                    help="after prefill keep this fraction of the KV cache (attention-matching compaction)")
     p.add_argument("--no-bos", action="store_true"); p.add_argument("--no-chat-template", action="store_true")
     p.add_argument("--raw-prompt", action="store_true"); p.add_argument("--stream", action="store_true")
+    p.add_argument("--image", nargs="+", default=[])
     p.add_argument("--print-timing", action="store_true"); p.add_argument("--print-token-ids", action="store_true")
     p.add_argument("--print-finish-reason", action="store_true"); p.set_defaults(fn=cmd_generate)
     p = sub.add_parser("search")

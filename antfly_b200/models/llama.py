@@ -51,6 +51,7 @@ class LlamaConfig:
     gate_act: str = "silu"        # gated-MLP activation: silu (SwiGLU), gelu_tanh (GeGLU, Gemma), relu2 (BitNet)
     # BitNet b1.58: ternary weights with one scale per matrix, activations rounded to 8 bits per token before
     # every projection, an extra RMS norm before the attention-output and the down projections
+    mrope_sections: Optional[List[int]] = None   # Qwen2-VL: rotary pairs split between time / row / column streams
     bitnet: bool = False
     bitnet_scale_divides: bool = False   # packed checkpoints of the "bitlinear" kind store 1 / scale
     # Mixture of experts (Mixtral, Qwen2-MoE, Qwen3-MoE): 0 experts = dense MLP
@@ -84,8 +85,10 @@ class LlamaConfig:
         if d.get("use_sliding_window") is False:
             cfg.sliding_window = 0
         mt = d.get("model_type", "")
-        if mt == "qwen2":
+        if mt in ("qwen2", "qwen2_vl", "qwen2_vl_text"):
             cfg.qkv_bias = True
+        if rp.get("mrope_section"):
+            cfg.mrope_sections = [int(v) for v in rp["mrope_section"]]
         if mt == "qwen3":
             cfg.qk_norm = True
         if mt in ("mixtral", "qwen2_moe", "qwen3_moe"):
@@ -141,6 +144,11 @@ class StepBatch:
     logit_rows: torch.Tensor    # [R] token rows whose logits are wanted
     max_q_len: int = 1
     attn_splits: int = 1
+    # multimodal prompts: rows of this step whose embedding is a given vector instead of a table row, and three
+    # rotary position streams [3, T] (time / row / column) in place of ``positions``
+    embed_rows: Optional[torch.Tensor] = None
+    embed_vals: Optional[torch.Tensor] = None
+    pos3: Optional[torch.Tensor] = None
 
 
 def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> int:
@@ -611,8 +619,11 @@ class LlamaModel:
         hi = lo + self.n_layers
         if pp is None or pp.is_first:
             x = Dn.embed_gather(b.ids, w["embed"], scale=cfg.embed_scale)
+            if b.embed_rows is not None:         # soft tokens (image patches) replace their placeholders' rows
+                x.index_copy_(0, b.embed_rows.long(), b.embed_vals.to(x.dtype))
         else:
             x = pp.recv_hidden(T, cfg.hidden_size, w[f"l{lo}.ln1"].device)
+        zero_pos = torch.zeros_like(b.positions) if b.pos3 is not None else None
         h = Dn.norm(x, w[f"l{lo}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
 
         def lin(a, key, residual=None):
@@ -631,8 +642,21 @@ class LlamaModel:
             p = f"l{l}."
             k_cache_l, v_cache_l = k_cache[l - lo], v_cache[l - lo]
             qkv = lin(h, p + "qkv")
-            q = A.rope_kv_write(qkv, b.positions, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, cfg.rope_theta,
-                                bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
+            qkv_bias, rope_pos = w.get(p + "qkv.b"), b.positions
+            if b.pos3 is not None:
+                # three-stream rotation done here on the fused buffer; the cache-write kernel then rotates by
+                # position zero, which is the identity
+                from .qwen2vl import mrope_rotate
+
+                assert cfg.mrope_sections is not None and not cfg.qk_norm and cfg.rope_dim == D
+                if qkv_bias is not None:
+                    qkv = (qkv.float() + qkv_bias.float()).to(qkv.dtype)
+                nqk = (Hq + Hkv) * D
+                qkv[:, :nqk] = mrope_rotate(qkv[:, :nqk].view(T, Hq + Hkv, D), b.pos3, cfg.rope_theta,
+                                            cfg.mrope_sections).view(T, nqk)
+                qkv_bias, rope_pos = None, zero_pos
+            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, cfg.rope_theta,
+                                bias=qkv_bias, rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
                                 freq_scale=cfg.rope_freq_scale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
                                 norm_eps=eps, norm_plus_one=gp1)
             ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
@@ -682,7 +706,7 @@ class LlamaModel:
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
         if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
-                self.pp is not None:
+                self.pp is not None or b.embed_rows is not None or b.pos3 is not None:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

@@ -227,3 +227,18 @@ def mrope_rotate(x: torch.Tensor, pos3: torch.Tensor, theta: float, sections: Se
     xf = x.float()
     rot = torch.cat([-xf[..., D // 2:], xf[..., : D // 2]], -1)
     return (xf * cos + rot * sin).to(x.dtype)
+
+
+def text_state_dict(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """The decoder's tensors under the names a text-only Qwen2 checkpoint uses (``model.layers.*``, ``lm_head.*``),
+    whichever of the two published layouts (``model.language_model.*`` or ``model.*`` beside ``visual.*``) the
+    checkpoint has."""
+    out: Dict[str, torch.Tensor] = {}
+    for k, v in sd.items():
+        if k.startswith("model.language_model."):
+            out["model." + k[len("model.language_model."):]] = v
+        elif k.startswith(("model.visual.", "visual.")):
+            continue
+        else:
+            out[k] = v
+    return out

@@ -45,33 +45,55 @@ class ChatTemplate:
         self.source = source or DEFAULT_TEMPLATE
         self.template = env.from_string(self.source)
 
-    def apply(self, messages: Sequence[dict], add_generation_prompt: bool = True, **extra) -> str:
+    def apply(self, messages: Sequence[dict], add_generation_prompt: bool = True,
+              image_placeholder: Optional[str] = None, **extra) -> str:
         msgs = []
         for m in messages:
             c = m.get("content", "")
-            if isinstance(c, list):  # OpenAI content parts: keep the text parts
-                c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") == "text")
+            if isinstance(c, list):  # OpenAI content parts: text parts, and a placeholder where an image stands
+                c = "".join(
+                    p.get("text", "") if p.get("type") == "text" else
+                    (image_placeholder or "") if p.get("type") in ("image_url", "image") else ""
+                    for p in c if isinstance(p, dict))
             msgs.append({**m, "content": c})
         return self.template.render(messages=msgs, add_generation_prompt=add_generation_prompt, **extra)
 
 
 class Generator:
-    def __init__(self, engine: LLMEngine, tokenizer, chat_template: Optional[str] = None, add_bos: bool = True):
+    def __init__(self, engine: LLMEngine, tokenizer, chat_template: Optional[str] = None, add_bos: bool = True,
+                 vlm=None):
         self.engine, self.tokenizer, self.add_bos = engine, tokenizer, add_bos
+        self.vlm = vlm                  # image adapter (pipelines.vlm); None for text-only models
         self.template = ChatTemplate(chat_template)
         if engine.eos is None and tokenizer.special.eos_id is not None:
             engine.eos = tokenizer.special.eos_id
 
     def generate(self, messages_or_prompt, params: SamplingParams, raw_prompt: bool = False,
-                 on_delta: Optional[Callable[[str], None]] = None) -> GenerationOutput:
+                 on_delta: Optional[Callable[[str], None]] = None, images: Optional[Sequence] = None
+                 ) -> GenerationOutput:
+        """``images`` (or image parts inside chat messages) need a model with an image adapter; in a plain prompt
+        each image stands where the adapter's placeholder text is written (appended in front if it is absent)."""
         t0 = time.perf_counter()
+        images = list(images or [])
+        ph = self.vlm.placeholder if self.vlm is not None else None
         if isinstance(messages_or_prompt, str):
-            prompt = messages_or_prompt if raw_prompt else self.template.apply(
-                [{"role": "user", "content": messages_or_prompt}])
+            text = messages_or_prompt
+            if images and ph and text.count(ph) < len(images):
+                text = ph * (len(images) - text.count(ph)) + text
+            prompt = text if raw_prompt else self.template.apply([{"role": "user", "content": text}])
         else:
-            prompt = self.template.apply(messages_or_prompt)
+            if self.vlm is not None:
+                from .vlm import split_content
+
+                images = split_content(messages_or_prompt) + images
+            prompt = self.template.apply(messages_or_prompt, image_placeholder=ph)
+        if images and self.vlm is None:
+            raise ValueError("this model does not take images")
         t1 = time.perf_counter()
         ids = self.tokenizer.encode_prompt(prompt, add_bos=self.add_bos)
+        soft = None
+        if self.vlm is not None:
+            ids, soft = self.vlm.expand(ids, images)
         t2 = time.perf_counter()
         emitted = {"n": 0, "text": ""}
         collected: List[int] = []
@@ -88,7 +110,7 @@ class Generator:
                         on_delta(delta)
 
         p0, d0 = self.engine.timing["prefill_s"], self.engine.timing["decode_s"]
-        res = self.engine.generate([ids], params, on_token=on_token)[0]
+        res = self.engine.generate([ids], params, on_token=on_token, soft=[soft] if soft is not None else None)[0]
         t3 = time.perf_counter()
         toks = res.token_ids
         eos = self.engine.eos

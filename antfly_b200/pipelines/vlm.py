@@ -1,0 +1,89 @@
+"""Image inputs for generation: the adapter between a chat prompt with image parts and the decoder engine.
+
+A prompt reaches the adapter tokenised, with ONE placeholder token per image (what the chat template writes between
+the vision start / end markers).  The adapter decodes and patches each image, runs the vision tower, widens every
+placeholder to as many tokens as the image has merged patches, and describes the result to the engine: which prompt
+positions take a given embedding instead of a table row, and the three rotary position streams of the prompt.  The
+reference's adapter does the same around its Qwen2-VL session (zig/pkg/inference/src/pipelines/vlm_qwen2vl.zig); as
+there, prompts with images do not use speculative decoding or the prefix cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..models import qwen2vl as QV
+from .multimodal import ImageLike, load_image
+
+
+@dataclass
+class VlmTokens:
+    image: int                       # <|image_pad|>
+    vision_start: Optional[int] = None
+    vision_end: Optional[int] = None
+
+
+class Qwen2VLAdapter:
+    placeholder = "<|vision_start|><|image_pad|><|vision_end|>"
+
+    def __init__(self, vision: QV.Qwen2VLVisionModel, tokens: VlmTokens, min_pixels: int = 56 * 56,
+                 max_pixels: int = 14 * 14 * 4 * 1280):
+        self.vision, self.tokens = vision, tokens
+        self.min_pixels, self.max_pixels = min_pixels, max_pixels
+
+    def encode_images(self, images: Sequence[ImageLike]):
+        """-> (soft tokens [sum of merged patches, hidden], patch grid of each image)."""
+        patches, grids = [], []
+        for src in images:
+            p, g = QV.image_to_patches(load_image(src).cpu(), self.vision.cfg, self.min_pixels, self.max_pixels)
+            patches.append(p)
+            grids.append(g)
+        soft = self.vision.forward(torch.cat(patches, 0), grids)
+        return soft, grids
+
+    def expand(self, ids: Sequence[int], images: Sequence[ImageLike]) -> Tuple[List[int], Optional[dict]]:
+        """Prompt ids with one placeholder per image -> (ids with each placeholder repeated once per merged patch,
+        the engine's description of the soft tokens).  Without images the prompt is returned unchanged."""
+        n_ph = sum(1 for t in ids if t == self.tokens.image)
+        if not images:
+            if n_ph:
+                raise ValueError("the prompt has image placeholders but no images were given")
+            return list(ids), None
+        if n_ph != len(images):
+            raise ValueError(f"{len(images)} image(s) for {n_ph} placeholder(s) in the prompt")
+        soft, grids = self.encode_images(images)
+        m = self.vision.cfg.spatial_merge_size
+        out: List[int] = []
+        g = 0
+        for t in ids:
+            if t == self.tokens.image:
+                tt, h, w = grids[g]
+                out += [t] * (tt * (h // m) * (w // m))
+                g += 1
+            else:
+                out.append(t)
+        rows = [i for i, t in enumerate(out) if t == self.tokens.image]
+        pos3, delta = QV.rope_index(out, grids, self.tokens.image, m)
+        return out, {"rows": rows, "vals": soft, "pos3": pos3, "delta": delta}
+
+
+def split_content(messages: Sequence[dict]) -> List[ImageLike]:
+    """The images of a chat request, in reading order: content parts of type ``image_url`` (``{"url": data-URL}`` or a
+    bare string) and ``image`` (a data URL, a path, or a decoded array)."""
+    from .multimodal import decode_data_url
+
+    found: List[ImageLike] = []
+    for m in messages:
+        c = m.get("content")
+        if not isinstance(c, list):
+            continue
+        for p in c:
+            if not isinstance(p, dict) or p.get("type") not in ("image_url", "image"):
+                continue
+            v = p.get("image_url") if p.get("type") == "image_url" else p.get("image", p.get("url"))
+            if isinstance(v, dict):
+                v = v.get("url")
+            found.append(decode_data_url(v) if isinstance(v, str) and v.startswith("data:") else v)
+    return found

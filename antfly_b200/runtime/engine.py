@@ -57,6 +57,12 @@ class Request:
     t_first: Optional[float] = None
     row: int = -1  # row in the penalty-count table
     kv_removed: int = 0  # tokens dropped from the physical KV cache by compaction (logical positions keep counting)
+    # multimodal prompts: prompt positions whose embedding is given (image patches), those embeddings [n, H], the
+    # prompt's three rotary position streams [3, len(prompt)], and what to add to a cache index past the prompt
+    soft_rows: Optional[List[int]] = None
+    soft_vals: Optional[torch.Tensor] = None
+    pos3: Optional[torch.Tensor] = None
+    rope_delta: int = 0
 
     @property
     def tokens(self) -> List[int]:
@@ -142,11 +148,19 @@ class LLMEngine:
         self.timing = {"prefill_s": 0.0, "decode_s": 0.0}
 
     # ------------------------------------------------------------------------------------------------
-    def add_request(self, prompt: Sequence[int], params: SamplingParams) -> int:
+    def add_request(self, prompt: Sequence[int], params: SamplingParams, soft: Optional[dict] = None) -> int:
+        """``soft`` describes a multimodal prompt: ``rows`` (prompt positions of the placeholder tokens), ``vals``
+        (their embeddings, [len(rows), hidden]), ``pos3`` (rotary streams [3, len(prompt)]) and ``delta``.  Such
+        prompts neither use nor feed the prefix cache (equal token ids do not mean equal images)."""
         rid = self._next_id
         self._next_id += 1
         shared = 0
-        if self.prefix is not None:
+        if soft is not None:
+            if self.draft is not None:
+                raise ValueError("speculative decoding is not available for prompts with images")
+            if len(soft["rows"]) != soft["vals"].shape[0] or soft["pos3"].shape != (3, len(prompt)):
+                raise ValueError("soft-token description does not match the prompt")
+        if self.prefix is not None and soft is None:
             eid, n = self.prefix.lookup(prompt)
             if eid is not None:
                 try:
@@ -162,6 +176,9 @@ class LLMEngine:
             self.cache.alloc.detach(rid)
             raise
         r = Request(rid, list(prompt), params, t_admit=time.perf_counter())
+        if soft is not None:
+            r.soft_rows, r.soft_vals = [int(i) for i in soft["rows"]], soft["vals"].to(self.device)
+            r.pos3, r.rope_delta = soft["pos3"].to(torch.int64).cpu(), int(soft.get("delta", 0))
         if params.needs_penalties:
             r.row = self._rows_free.pop()
             if self.counts is None:
@@ -250,6 +267,27 @@ class LLMEngine:
         max_q = max(ql)
         splits = self._attn_splits(B, max(kvl)) if max_q * (self.model.Hq // self.model.Hkv) <= 16 else 1
         return StepBatch(d_ids, d_pos, d_slots, d_qs, d_ql, d_kvl, d_tab, d_rows, max_q, splits)
+
+    def _add_multimodal(self, batch: StepBatch, items: List[StepItem], reqs: List[Request]) -> None:
+        """Rotary streams for every token of the step, and the soft-token rows that fall inside its prefill chunks."""
+        pos, rows, vals = [], [], []
+        t0 = 0
+        for it, r in zip(items, reqs):
+            n = 1 if it.mode == "decode" else it.q_len
+            a = it.kv_before
+            if r.pos3 is not None and it.mode != "decode":
+                pos.append(r.pos3[:, a:a + n])
+                for j, p in enumerate(r.soft_rows):
+                    if a <= p < a + n:
+                        rows.append(t0 + p - a)
+                        vals.append(r.soft_vals[j])
+            else:
+                pos.append((torch.arange(a, a + n) + r.rope_delta)[None].expand(3, n))
+            t0 += n
+        batch.pos3 = torch.cat(pos, 1).to(self.device)
+        if rows:
+            batch.embed_rows = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            batch.embed_vals = torch.stack(vals)
 
     def _pick_tokens(self, logits: torch.Tensor, reqs: List[Request]) -> torch.Tensor:
         if any(r.params.grammar is not None for r in reqs):
@@ -361,7 +399,8 @@ class LLMEngine:
         if self.draft is not None and not any(r.params.grammar is not None and not r.finished
                                               for r in self.reqs.values()):
             snap = self.sched.snapshot()
-            if snap["decode"] > 0 and snap["waiting"] + snap["prefill"] == 0:
+            if snap["decode"] > 0 and snap["waiting"] + snap["prefill"] == 0 and not any(
+                    r.pos3 is not None for r in self.reqs.values()):
                 return self._spec_round()
         items = self.sched.claim_step()
         if not items:
@@ -369,7 +408,9 @@ class LLMEngine:
         t_start = time.perf_counter()
         reqs = [self.reqs[it.request_id] for it in items]
         try:
-            if all(it.mode == "decode" and it.q_len == 1 for it in items) and self.device.type == "cuda":
+            multimodal = any(r.pos3 is not None for r in reqs)
+            if all(it.mode == "decode" and it.q_len == 1 for it in items) and self.device.type == "cuda" \
+                    and not multimodal:
                 toks_dev = self._decode_static(items)
                 producing = list(range(len(items)))
             else:
@@ -380,6 +421,8 @@ class LLMEngine:
                     else:
                         seq_tokens.append(r.prompt[it.kv_before: it.kv_before + it.q_len])
                 batch = self._build_batch(items, seq_tokens)
+                if multimodal:
+                    self._add_multimodal(batch, items, reqs)
                 scratch = self._scratch_for(batch.ids.numel(), batch.attn_splits)
                 producing = [i for i, (it, r) in enumerate(zip(items, reqs))
                              if it.mode == "decode" or it.kv_before + it.q_len >= len(r.prompt)]
@@ -407,7 +450,7 @@ class LLMEngine:
                 ratio = r.params.cache_compaction_ratio
                 if ratio is not None and 0.0 < ratio < 1.0:
                     self.compact_request(it.request_id, ratio)
-                elif self.prefix is not None:
+                elif self.prefix is not None and r.pos3 is None:
                     self.prefix.insert(it.request_id, r.prompt)
         toks = toks_dev.cpu().tolist() if toks_dev is not None else []
         self.d2h_bytes += 4 * len(toks)
@@ -545,11 +588,13 @@ class LLMEngine:
         return produced
 
     # ------------------------------------------------------------------------------------------------
-    def generate(self, prompts: Sequence[Sequence[int]], params, on_token: Optional[Callable] = None
-                 ) -> List[GenerationResult]:
-        """Run prompts to completion.  ``params`` is one SamplingParams or one per prompt."""
+    def generate(self, prompts: Sequence[Sequence[int]], params, on_token: Optional[Callable] = None,
+                 soft: Optional[Sequence[Optional[dict]]] = None) -> List[GenerationResult]:
+        """Run prompts to completion.  ``params`` is one SamplingParams or one per prompt; ``soft`` holds, per
+        prompt, the multimodal description :meth:`add_request` takes (or None)."""
         plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
-        rids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        slist = list(soft) if soft is not None else [None] * len(prompts)
+        rids = [self.add_request(p, sp, sf) for p, sp, sf in zip(prompts, plist, slist)]
         emitted = {rid: 0 for rid in rids}
         while any(not self.reqs[rid].finished for rid in rids):
             n = self.step()

@@ -84,3 +84,169 @@ def test_rope_index_and_rotation_match_transformers():
     want_q, _ = M.apply_multimodal_rotary_pos_emb(q, q, cos, sin, [4, 6, 6])
     got = QV.mrope_rotate(x, pos, 10000.0, [4, 6, 6])
     torch.testing.assert_close(got, want_q[0].transpose(0, 1), atol=1e-5, rtol=1e-5)
+
+
+def _round_text_linears(hf):
+    from antfly_b200.ops import reference as R
+
+    with torch.no_grad():
+        for name, mod in hf.named_modules():
+            if isinstance(mod, torch.nn.Linear) and "visual" not in name:
+                q, e8 = R.quantize_block_fp8(mod.weight.data)
+                mod.weight.data.copy_(R.dequantize_block_fp8(q, e8))
+
+
+def test_decoder_with_image_tokens_matches_transformers():
+    """Prefill over text + image placeholders (soft tokens, three-stream rotary positions) and one decode step whose
+    rotary position runs behind its cache index."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel, StepBatch
+
+    hf_cfg, hf = _hf(1)
+    _round_text_linears(hf)
+    IMG = 300
+    grids = [(1, 4, 6), (1, 2, 4)]
+    ids = [5, 6, 302] + [IMG] * 6 + [303, 7, 8, 9, 302] + [IMG] * 2 + [303, 10, 11, 12]
+    S = len(ids) - 1
+    n_patches = sum(t * h * w for t, h, w in grids)
+    patches = torch.randn(n_patches, 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor(grids),
+                  mm_token_type_ids=torch.tensor([[int(t == IMG) for t in ids]])).logits[0].float()
+
+    d = hf_cfg.text_config.to_dict()
+    cfg = LlamaConfig.from_hf(d)
+    assert cfg.mrope_sections == [4, 6, 6] and cfg.qkv_bias
+    sd = hf.state_dict()
+    model = LlamaModel.from_state_dict(cfg, QV.text_state_dict(sd), device="cpu")
+    vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(hf_cfg.vision_config.to_dict()), sd,
+                                                   device="cpu", dtype=torch.float32)
+    soft = vision.forward(patches, grids)
+    pos3, delta = QV.rope_index(ids[:S], grids, IMG)
+    assert delta < 0 and soft.shape[0] == ids.count(IMG)
+
+    page, nblk = 16, 3
+    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    table = torch.arange(nblk, dtype=torch.int32)[None]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    idx = torch.arange(S, dtype=torch.int32)
+    rows = torch.tensor([i for i, t in enumerate(ids[:S]) if t == IMG])
+    prefill = StepBatch(i32(ids[:S]), idx, idx.clone(), i32([0]), i32([S]), i32([S]), table, idx.clone(), S, 1,
+                        embed_rows=rows, embed_vals=soft, pos3=pos3)
+    a = model.forward(prefill, k_cache, v_cache).float()
+    decode = StepBatch(i32(ids[S:]), i32([S + delta]), i32([S]), i32([0]), i32([1]), i32([S + 1]), table, i32([0]), 1, 1)
+    got = torch.cat([a, model.forward(decode, k_cache, v_cache).float()], 0)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.99, cos
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.8
+    assert float((got - want).abs().max()) < 0.08 * max(float(want.abs().max()), 1.0)
+
+
+def test_engine_generates_from_image_prompts():
+    """The adapter widens placeholders and describes the soft tokens; the engine prefills in chunks that cut through
+    the image, decodes with the rotary delta, and serves a text request in the same steps.  Greedy tokens must
+    equal a straight run of the model (one prefill over the whole prompt, then single-token steps)."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel, StepBatch
+    from antfly_b200.pipelines.vlm import Qwen2VLAdapter, VlmTokens, split_content
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    hf_cfg, hf = _hf(2)
+    sd = hf.state_dict()
+    cfg = LlamaConfig.from_hf(hf_cfg.text_config.to_dict())
+    model = LlamaModel.from_state_dict(cfg, QV.text_state_dict(sd), device="cpu")
+    vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(hf_cfg.vision_config.to_dict()), sd,
+                                                   device="cpu", dtype=torch.float32)
+    adapter = Qwen2VLAdapter(vision, VlmTokens(300, 302, 303), min_pixels=28 * 28, max_pixels=28 * 28 * 16)
+    img = torch.randint(0, 256, (60, 110, 3), generator=torch.Generator().manual_seed(7), dtype=torch.uint8)
+    prompt = [5, 6, 302, 300, 303, 7, 8, 9]
+    ids, soft = adapter.expand(prompt, [img])
+    n_img = ids.count(300)
+    assert n_img == soft["vals"].shape[0] == len(soft["rows"]) and n_img > 1 and soft["delta"] < 0
+    assert adapter.expand([1, 2], []) == ([1, 2], None)
+    with pytest.raises(ValueError):
+        adapter.expand(prompt, [])
+    with pytest.raises(ValueError):
+        adapter.expand([1, 2], [img])
+
+    # straight run
+    N_NEW = 5
+    page, nblk = 16, 8
+    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    table = torch.arange(nblk, dtype=torch.int32)[None]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    S = len(ids)
+    idx = torch.arange(S, dtype=torch.int32)
+    b = StepBatch(i32(ids), idx, idx.clone(), i32([0]), i32([S]), i32([S]), table, i32([S - 1]), S, 1,
+                  embed_rows=torch.tensor(soft["rows"]), embed_vals=soft["vals"], pos3=soft["pos3"])
+    want = [int(model.forward(b, k_cache, v_cache).float().argmax(-1)[0])]
+    for j in range(N_NEW - 1):
+        c = S + j
+        d = StepBatch(i32([want[-1]]), i32([c + soft["delta"]]), i32([c]), i32([0]), i32([1]), i32([c + 1]), table,
+                      i32([0]), 1, 1)
+        want.append(int(model.forward(d, k_cache, v_cache).float().argmax(-1)[0]))
+
+    eng = LLMEngine(model, num_blocks=32, max_batch=4, use_cuda_graph=False, prefill_chunk=8, max_step_tokens=16)
+    sp = SamplingParams(max_tokens=N_NEW, temperature=0.0)
+    res = eng.generate([ids, [11, 12, 13, 14]], sp, soft=[soft, None])
+    assert res[0].token_ids == want, (res[0].token_ids, want)
+    text_only = LLMEngine(model, num_blocks=32, max_batch=4, use_cuda_graph=False).generate([[11, 12, 13, 14]], sp)
+    assert res[1].token_ids == text_only[0].token_ids          # the text request is unaffected by its neighbour
+    with pytest.raises(ValueError):
+        eng.add_request(ids, sp, {**soft, "rows": soft["rows"][:-1]})
+
+    # chat content parts: images are collected in reading order
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "what is"}, {"type": "image", "image": img},
+                                         {"type": "image_url", "image_url": {"url": "x.png"}}]}]
+    found = split_content(msgs)
+    assert len(found) == 2 and found[0] is img and found[1] == "x.png"
+
+
+def test_generator_with_image_adapter_and_chat_parts():
+    """Generator level: a chat message with an image part renders the placeholder, the adapter widens it, and the
+    reply equals what the same prompt gives through the engine directly; a text-only model refuses images."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.pipelines.generation import ChatTemplate, Generator
+    from antfly_b200.pipelines.vlm import Qwen2VLAdapter, VlmTokens
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    hf_cfg, hf = _hf(3)
+    sd = hf.state_dict()
+    model = LlamaModel.from_state_dict(LlamaConfig.from_hf(hf_cfg.text_config.to_dict()), QV.text_state_dict(sd),
+                                       device="cpu")
+    vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(hf_cfg.vision_config.to_dict()), sd,
+                                                   device="cpu", dtype=torch.float32)
+    adapter = Qwen2VLAdapter(vision, VlmTokens(300), min_pixels=28 * 28, max_pixels=28 * 28 * 4)
+
+    class Tok(ByteTokenizer):                      # a byte tokenizer that knows the image placeholder as one token
+        def encode_prompt(self, text, add_bos=True):
+            ids = []
+            for i, piece in enumerate(text.split(adapter.placeholder)):
+                if i:
+                    ids += [302, 300, 303]
+                ids += self.encode(piece)
+            return ids
+
+    tok = Tok(290)
+    tmpl = "{% for m in messages %}{{ m['content'] }}{% endfor %}"
+    assert ChatTemplate(tmpl).apply([{"role": "user", "content": [{"type": "image", "image": 1},
+                                                                  {"type": "text", "text": "hi"}]}],
+                                    image_placeholder="<I>") == "<I>hi"
+    eng = LLMEngine(model, num_blocks=32, max_batch=2, use_cuda_graph=False)
+    gen = Generator(eng, tok, tmpl, add_bos=False, vlm=adapter)
+    img = torch.randint(0, 256, (50, 50, 3), generator=torch.Generator().manual_seed(1), dtype=torch.uint8)
+    sp = SamplingParams(max_tokens=4, temperature=0.0)
+    out = gen.generate([{"role": "user", "content": [{"type": "image", "image": img},
+                                                     {"type": "text", "text": "hi"}]}], sp)
+    ids, soft = adapter.expand([302, 300, 303] + tok.encode("hi"), [img])
+    want = eng.generate([ids], sp, soft=[soft])[0].token_ids
+    assert out.token_ids == want and out.prompt_tokens == len(ids)
+    same = gen.generate("hi", sp, images=[img], raw_prompt=True)             # placeholder put in front
+    assert same.token_ids == want
+    plain = Generator(eng, tok, tmpl, add_bos=False)
+    with pytest.raises(ValueError):
+        plain.generate("hi", sp, images=[img])
+    assert len(plain.generate("hi", sp).token_ids) == 4
