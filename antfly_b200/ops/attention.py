@@ -28,6 +28,21 @@ def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, 
     if not q.is_cuda:
         cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
         return R.varlen_attention(q, k, v, cu, scale, causal, window).to(torch.bfloat16)
+    if D not in (64, 128):
+        # The kernel is built for 64- and 128-wide heads.  Zero columns change neither a dot product nor the
+        # softmax (the scale is fixed from the true width), so other widths run zero-padded to the next size
+        # (vision towers with 80-wide heads, small test models); beyond 128 the tensor-op restatement runs.
+        if D > 128:
+            cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
+            return R.varlen_attention(q, k, v, cu, scale, causal, window).to(torch.bfloat16)
+        Dp = 64 if D < 64 else 128
+        pad = lambda t: torch.nn.functional.pad(t, (0, Dp - D)).contiguous()
+        o = varlen_attention(pad(q), pad(k), pad(v), starts, lens, max_len, causal, scale, None, window)
+        o = o[..., :D].contiguous()
+        if out is not None:
+            out.copy_(o)
+            return out
+        return o
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert k.stride(0) == v.stride(0)
     if out is None:

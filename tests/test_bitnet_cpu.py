@@ -46,13 +46,14 @@ def _hf():
     return cfg, hf
 
 
-def _run(model, cfg, ids, S):
+def _run(model, cfg, ids, S, device="cpu"):
     page, nblk = 16, 3
-    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16)
+    k_cache = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16,
+                          device=device)
     v_cache = torch.zeros_like(k_cache)
-    table = torch.arange(nblk, dtype=torch.int32)[None]
-    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
-    pos = torch.arange(S, dtype=torch.int32)
+    table = torch.arange(nblk, dtype=torch.int32, device=device)[None]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    pos = torch.arange(S, dtype=torch.int32, device=device)
     prefill = StepBatch(ids[:S].int(), pos, pos.clone(), i32([0]), i32([S]), i32([S]), table, pos.clone(), S, 1)
     a = model.forward(prefill, k_cache, v_cache).float()
     decode = StepBatch(ids[S:].int(), i32([S]), i32([S]), i32([0]), i32([1]), i32([S + 1]), table, i32([0]), 1, 1)

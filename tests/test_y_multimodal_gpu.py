@@ -1,0 +1,94 @@
+"""GPU runs of the audio, vision and span models against their own CPU (fp32-accumulate) paths, plus attention with
+head widths the kernel does not have natively (run zero-padded)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+transformers = pytest.importorskip("transformers")
+
+
+def _close(got, want, cos_min=0.995):
+    got, want = got.float().cpu(), want.float().cpu()
+    c = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
+    assert float(c) > cos_min, float(c)
+
+
+@pytest.mark.parametrize("D", [32, 80])
+def test_varlen_attention_padded_head_width(D):
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(D)
+    lens = torch.tensor([37, 5, 90], dtype=torch.int32)
+    starts = (torch.cumsum(lens, 0) - lens).to(torch.int32)
+    T = int(lens.sum())
+    q, k, v = (torch.randn(T, 4, D, generator=g).to(torch.bfloat16) for _ in range(3))
+    cu = torch.cat([starts.long(), torch.tensor([T])])
+    want = R.varlen_attention(q, k, v, cu)
+    got = A.varlen_attention(q.cuda(), k.cuda(), v.cuda(), starts.cuda(), lens.cuda(), 90)
+    assert got.shape == (T, 4, D)
+    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_qwen2vl_vision_tower_on_gpu():
+    from antfly_b200.models import qwen2vl as QV
+    import tests.test_qwen2vl_cpu as T
+
+    hf_cfg, hf = T._hf()
+    vc = QV.Qwen2VLVisionConfig.from_hf(hf_cfg.vision_config.to_dict())
+    sd = {k: v.to(torch.bfloat16).float() for k, v in hf.state_dict().items()}
+    cpu = QV.Qwen2VLVisionModel.from_state_dict(vc, sd, device="cpu", dtype=torch.float32)
+    gpu = QV.Qwen2VLVisionModel.from_state_dict(vc, sd, device="cuda")
+    grids = [(1, 4, 6), (1, 2, 2)]
+    patches = torch.randn(28, 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).float()
+    _close(gpu.forward(patches, grids), cpu.forward(patches, grids))
+
+
+@pytest.mark.parametrize("fusion", [False, True])
+def test_clap_audio_tower_on_gpu(fusion):
+    from antfly_b200.models.clap import ClapConfig, ClapModel
+    import tests.test_clap_cpu as T
+
+    hf_cfg, hf = T._tiny(fusion)
+    cfg = ClapConfig.from_hf(hf_cfg.to_dict())
+    sd = {k: (v.to(torch.bfloat16).float() if v.is_floating_point() else v) for k, v in hf.state_dict().items()}
+    cpu = ClapModel.from_state_dict(cfg, sd, device="cpu", dtype=torch.float32)
+    gpu = ClapModel.from_state_dict(cfg, sd, device="cuda")
+    feats = torch.randn(3, 4 if fusion else 1, 250, 16, generator=torch.Generator().manual_seed(3)) * 10 - 20
+    longer = [True, False, True]
+    _close(gpu.embed_audio(feats, longer), cpu.embed_audio(feats, longer), 0.99)
+    seqs = [[0, 5, 9, 2], [0, 7, 8, 11, 30, 2]]
+    _close(gpu.embed_text(seqs), cpu.embed_text(seqs), 0.99)
+
+
+def test_gliner_span_logits_on_gpu():
+    from antfly_b200.models.deberta import DebertaConfig
+    from antfly_b200.models.gliner import GlinerInput, GlinerModel
+    import tests.test_gliner_cpu as T
+
+    enc, head, cpu = T._build()
+    sd = {"encoder." + k: v for k, v in enc.state_dict().items()}
+    sd.update(head.state_dict())
+    gpu = GlinerModel.from_state_dict(DebertaConfig.from_hf(enc.config.to_dict()), sd, device="cuda")
+    inp = GlinerInput([5, 390, 20, 21, 390, 30, 391, 40, 41, 42, 43, 44], [0] * 7 + [1, 2, 2, 3, 4], 4)
+    a = gpu.span_logits([inp], [390], 3)[0]
+    b = cpu.span_logits([inp], [390], 3)[0]
+    assert a.shape == b.shape == (4, 3, 2)
+    _close(a, b, 0.98)
+
+
+def test_bitnet_forward_on_gpu():
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    import tests.test_bitnet_cpu as T
+
+    hf_cfg, hf = T._hf()
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    sd.pop("lm_head.weight", None)
+    cfg = LlamaConfig.from_hf(hf_cfg.to_dict())
+    ids = torch.randint(0, hf_cfg.vocab_size, (25,), generator=torch.Generator().manual_seed(5))
+    want = T._run(LlamaModel.from_state_dict(cfg, dict(sd), device="cpu"), cfg, ids, 24)
+    gpu = LlamaModel.from_state_dict(cfg, dict(sd), device="cuda")
+    got = T._run(gpu, cfg, ids.cuda(), 24, device="cuda")
+    cos = torch.nn.functional.cosine_similarity(got.float().cpu(), want, dim=-1)
+    assert float(cos.min()) > 0.99, cos
