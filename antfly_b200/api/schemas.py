@@ -244,6 +244,22 @@ class RerankMultimodalRequest(BaseModel):
     documents: List[RerankMultimodalDocument]
 
 
+class LayoutPage(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    words: List[str]
+    boxes: List[List[float]]                       # one [x0, y0, x1, y1] per word
+    width: Optional[float] = None                  # page size the boxes are measured in; without it boxes are 0..1000
+    height: Optional[float] = None
+    image: Optional[Union[str, Dict[str, Any]]] = None   # data URL of the page, optional
+
+
+class LayoutRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    pages: List[LayoutPage]
+    group: bool = True                             # join B- / I- tagged words into fields
+
+
 class ReadRequest(BaseModel):
     model_config = ConfigDict(extra="allow")
     model: str

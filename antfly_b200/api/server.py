@@ -744,6 +744,51 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "read", len(imgs), work)
 
+    async def layout(request: Request):
+        """Words with page boxes (from OCR or a PDF text layer), optionally the page image -> a label per word and
+        the fields they form, through a layout-aware token classifier."""
+        req, bad = await parse(request, S.LayoutRequest)
+        if bad:
+            return bad
+        if not req.pages:
+            return _err(400, "invalid_request", "pages must not be empty")
+        from ..pipelines.layout import group_entities, normalize_box
+        from ..pipelines.multimodal import decode_data_url
+
+        pages = []
+        for i, pg in enumerate(req.pages):
+            if len(pg.words) != len(pg.boxes) or any(len(b) != 4 for b in pg.boxes):
+                return _err(400, "invalid_request", f"page {i}: one [x0, y0, x1, y1] box per word is required")
+            if pg.width and pg.height:
+                boxes = [normalize_box(b, pg.width, pg.height) for b in pg.boxes]
+            else:
+                boxes = [tuple(int(v) for v in b) for b in pg.boxes]
+                if any(v < 0 or v > 1000 for b in boxes for v in b):
+                    return _err(400, "invalid_request", f"page {i}: boxes outside 0..1000 need width and height")
+            img = None
+            if pg.image is not None:
+                try:
+                    img = decode_data_url(pg.image.get("url") if isinstance(pg.image, dict) else pg.image)
+                except Exception as e:
+                    return _err(400, "invalid_request", f"page {i} image: {e}")
+            pages.append((pg.words, boxes, img))
+
+        def work():
+            lm = mgr.get(req.model, "recognizer")
+            if not hasattr(lm.pipeline, "label_words"):
+                raise ValueError(f"model {req.model!r} is not a layout model")
+            data = []
+            for i, (words, boxes, img) in enumerate(pages):
+                labels = lm.pipeline.label_words(words, boxes, img)
+                rec = {"object": "layout", "index": i, "words": [
+                    {"word": l.word, "box": list(l.box), "label": l.label, "score": l.score} for l in labels]}
+                if req.group:
+                    rec["entities"] = group_entities(labels)
+                data.append(rec)
+            return {"object": "list", "model": req.model, "data": data}
+
+        return await asyncio.to_thread(run_guarded, "layout", sum(len(p[0]) for p in pages), work)
+
     async def extract(request: Request):
         req, bad = await parse(request, S.ExtractionRequest)
         if bad:
@@ -1026,6 +1071,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/ai/v1/extract", extract, methods=["POST"])
     app.add_api_route("/ai/v1/transcribe", transcribe, methods=["POST"])
     app.add_api_route("/ai/v1/read", read, methods=["POST"])
+    app.add_api_route("/ai/v1/layout", layout, methods=["POST"])
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
     app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
     app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])
