@@ -9,7 +9,8 @@
   rerank    score documents against a query  --model --query Q --doc ... 
   generate  generate text                    --model --prompt P [--max-tokens --temperature --top-k --top-p --min-p
                                              --repetition-penalty --speculative-k --draft-layers --cache-dtype
-                                             --prefill-chunk-size --kv-budget-mb --no-bos --no-chat-template
+                                             --prefill-chunk-size --kv-budget-mb --host-budget-mb --backend-budget-mb
+                                             --scratch-budget-mb --combined-budget-mb --image --no-bos --no-chat-template
                                              --print-timing --print-token-ids --print-finish-reason]
   search    query a saved index              --index PATH --vector "0.1,0.2,..." | --packed B64 [--k --nprobe]
   quantize  pack a safetensors checkpoint to block-scaled fp8   --in DIR --out FILE
@@ -142,6 +143,16 @@ def cmd_generate(args) -> int:
         eng.spec_k = args.speculative_k
     if args.no_bos:
         gen.add_bos = False
+    if any((args.kv_budget_mb, args.host_budget_mb, args.backend_budget_mb, args.scratch_budget_mb,
+            args.combined_budget_mb)):
+        from .runtime.tiering import Limits, MemoryBudgetExceeded, budget_for_engine
+
+        try:
+            budget_for_engine(eng, Limits.from_mb(args.host_budget_mb, args.backend_budget_mb, args.combined_budget_mb,
+                                                  args.kv_budget_mb, args.scratch_budget_mb))
+        except MemoryBudgetExceeded as e:
+            print(str(e), file=sys.stderr)
+            return 3
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                         min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
                         cache_compaction_ratio=args.cache_compaction_ratio)
@@ -394,6 +405,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--no-bos", action="store_true"); p.add_argument("--no-chat-template", action="store_true")
     p.add_argument("--raw-prompt", action="store_true"); p.add_argument("--stream", action="store_true")
     p.add_argument("--image", nargs="+", default=[])
+    for flag in ("--host-budget-mb", "--backend-budget-mb", "--scratch-budget-mb", "--combined-budget-mb"):
+        p.add_argument(flag, type=int, default=0)
     p.add_argument("--print-timing", action="store_true"); p.add_argument("--print-token-ids", action="store_true")
     p.add_argument("--print-finish-reason", action="store_true"); p.set_defaults(fn=cmd_generate)
     p = sub.add_parser("search")

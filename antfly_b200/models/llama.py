@@ -551,16 +551,26 @@ class LlamaModel:
         self.pp, self.layer_lo = stage, first_layer
         self.n_layers = last_layer - first_layer
 
-    def offload_experts(self, max_resident_per_layer: int, max_predicted: int = 2) -> "MoeRuntimeState":
+    def offload_experts(self, max_resident_per_layer: int, max_predicted: int = 2, spill_path: Optional[str] = None,
+                        host_budget_bytes: int = 0) -> "MoeRuntimeState":
         """Move the routed experts' weights to (pinned) host memory and keep at most ``max_resident_per_layer`` of
         each layer's experts on the device; absent experts are copied in when a step routes to them and the experts
-        predicted for the next step are prefetched on a side stream.  For checkpoints whose experts exceed HBM."""
-        store = HostExpertStore(self.device)
+        predicted for the next step are prefetched on a side stream.  For checkpoints whose experts exceed HBM.
+        With ``spill_path`` the experts' home is that file instead, and at most ``host_budget_bytes`` of them are
+        cached in host memory (for checkpoints whose experts exceed host memory as well)."""
+        if spill_path is not None:
+            from ..runtime.moe import DiskExpertStore
+
+            store = DiskExpertStore(self.device, spill_path, host_budget_bytes)
+        else:
+            store = HostExpertStore(self.device)
         for l in range(self.n_layers):
             for e in range(self.cfg.num_experts):
                 gu, down = self.w.pop(f"l{l}.e{e}.gu", None), self.w.pop(f"l{l}.e{e}.down", None)
                 if gu is not None:
                     store.put(l, e, {"gu": gu, "down": down})
+        if spill_path is not None:
+            store.seal()
         stream = torch.cuda.Stream() if self.device.type == "cuda" else None
         self.moe_runtime = MoeRuntimeState(store, ExpertResidency(store.load, max_resident_per_layer, stream),
                                            CoactivationPredictor(), max_predicted)

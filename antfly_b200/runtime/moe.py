@@ -199,3 +199,60 @@ class HostExpertStore:
                 ts = [v] if isinstance(v, torch.Tensor) else [getattr(v, "q", None), getattr(v, "scales", None)]
                 tot += sum(t.numel() * t.element_size() for t in ts if isinstance(t, torch.Tensor))
         return tot
+
+
+class DiskExpertStore:
+    """Expert weights whose home is a file on disk (NVMe): ``put`` collects them, ``seal`` writes one safetensors
+    file and reopens it memory-mapped, ``load`` brings one expert to the device through a bounded pinned-host
+    cache (:class:`antfly_b200.runtime.tiering.TieredStore`: least recently used experts leave the host tier when
+    its budget is full, and come back from the file on their next use).  The third tier under
+    :class:`HostExpertStore` for checkpoints whose experts exceed host memory too."""
+
+    def __init__(self, device, path: str, host_budget_bytes: int = 0):
+        self.device, self.path, self.host_budget = torch.device(device), path, int(host_budget_bytes)
+        self._staged: Dict[str, torch.Tensor] = {}
+        self._flags: Dict[Hashable, Dict[str, bool]] = {}
+        self.store = None
+
+    def put(self, layer: int, expert: int, weights: Dict[str, object]) -> None:
+        if self.store is not None:
+            raise RuntimeError("the store is sealed")
+        self._flags[(layer, expert)] = {}
+        for n, v in weights.items():
+            key = f"l{layer}.e{expert}.{n}"
+            if isinstance(v, torch.Tensor):
+                self._staged[key] = v.to("cpu")
+            else:                                       # block-fp8 weight: codes (as bytes) + scales
+                q = v.q.to("cpu")
+                self._staged[key + "::q"] = q.view(torch.uint8) if q.dtype != torch.uint8 else q
+                self._staged[key + "::scales"] = v.scales.to("cpu")
+                self._flags[(layer, expert)][n] = bool(v.interleaved_swiglu)
+
+    def seal(self) -> None:
+        from ..formats.safetensors_io import save_file
+        from .tiering import Limits, RunBudget, SafetensorsSource, TieredStore
+
+        save_file(self._staged, self.path)
+        self._names = {k for k in self._staged}
+        self._staged = {}
+        self.store = TieredStore(SafetensorsSource(self.path), self.device, RunBudget(Limits(host=self.host_budget)),
+                                 start_worker=False)
+
+    def load(self, layer: int, expert: int) -> Dict[str, object]:
+        from ..ops.quant import Fp8Weight
+        from .tiering import Tier
+
+        if self.store is None:
+            self.seal()
+        out: Dict[str, object] = {}
+        pre = f"l{layer}.e{expert}."
+        host = lambda k: self.store.get(k, Tier.HOST).to(self.device, non_blocking=True)
+        for n, swiglu in self._flags[(layer, expert)].items():
+            out[n] = Fp8Weight(host(pre + n + "::q").view(torch.float8_e4m3fn), host(pre + n + "::scales"), swiglu)
+        for k in self._names:
+            if k.startswith(pre) and "::" not in k:
+                out[k[len(pre):]] = host(k)
+        return out
+
+    def bytes(self) -> int:
+        return self.store.budget.host_total if self.store is not None else 0

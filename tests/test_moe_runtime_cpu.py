@@ -93,3 +93,15 @@ def test_moe_model_with_offloaded_experts_matches_resident_model():
     st = rt.residency.stats
     assert st["misses"] > 0 and st["evictions"] > 0 and st["hits"] > 0
     assert all(rt.residency.resident_count(l) <= 3 for l in range(cfg.num_hidden_layers))
+    # third tier: the experts live in a file, a bounded host cache sits between it and the device
+    import tempfile, os
+
+    with tempfile.TemporaryDirectory() as d:
+        disk = LlamaModel.from_state_dict(cfg, sd, device="cpu")
+        one = sum(v.nbytes() for k, v in disk.w.items() if k.startswith("l0.e0."))
+        rd = disk.offload_experts(max_resident_per_layer=2, max_predicted=1, spill_path=os.path.join(d, "experts.st"),
+                                  host_budget_bytes=3 * one)
+        assert os.path.getsize(os.path.join(d, "experts.st")) > cfg.num_hidden_layers * cfg.num_experts * one * 0.9
+        torch.testing.assert_close(run(disk), want, atol=0, rtol=0)
+        ts = rd.store.store.stats
+        assert ts["disk_reads"] > 0 and ts["evictions"] > 0 and rd.store.bytes() <= 3 * one
