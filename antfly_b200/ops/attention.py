@@ -28,14 +28,14 @@ def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, 
     if not q.is_cuda:
         cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
         return R.varlen_attention(q, k, v, cu, scale, causal, window).to(torch.bfloat16)
-    if D not in (64, 128):
-        # The kernel is built for 64- and 128-wide heads.  Zero columns change neither a dot product nor the
+    if D not in (64, 128, 256):
+        # The kernel is built for 64-, 128- and 256-wide heads.  Zero columns change neither a dot product nor the
         # softmax (the scale is fixed from the true width), so other widths run zero-padded to the next size
-        # (vision towers with 80-wide heads, small test models); beyond 128 the tensor-op restatement runs.
-        if D > 128:
+        # (vision towers with 80-wide heads, small test models); beyond 256 the tensor-op restatement runs.
+        if D > 256:
             cu = torch.cat([starts.long(), (starts[-1:] + lens[-1:]).long()])
             return R.varlen_attention(q, k, v, cu, scale, causal, window).to(torch.bfloat16)
-        Dp = 64 if D < 64 else 128
+        Dp = 64 if D < 64 else 128 if D < 128 else 256
         pad = lambda t: torch.nn.functional.pad(t, (0, Dp - D)).contiguous()
         o = varlen_attention(pad(q), pad(k), pad(v), starts, lens, max_len, causal, scale, None, window)
         o = o[..., :D].contiguous()

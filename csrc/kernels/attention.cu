@@ -93,7 +93,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* s
   constexpr int CH = D / 8;
   constexpr int ROWS_PER_PASS = 128 / CH;
   const int ch = threadIdx.x % CH, r0 = threadIdx.x / CH;
-  const int dst0 = r0 * D + ((ch ^ (r0 & 7)) * 8);  // ROWS_PER_PASS is a multiple of 8: row & 7 == r0 & 7
+  const int dst0 = r0 * D + ((ch ^ (r0 & 7)) * 8);  // valid when ROWS_PER_PASS is a multiple of 8: row & 7 == r0 & 7
   const int* table = PAGED ? p.block_tables + static_cast<size_t>(b) * p.max_blocks : nullptr;
   const size_t row_elems = PAGED ? static_cast<size_t>(p.Hkv) * D : static_cast<size_t>(p.kv_stride);
   const size_t col_off = static_cast<size_t>(hk) * D + ch * 8;
@@ -118,7 +118,8 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* s
     } else {
       off = static_cast<size_t>(kv_row_start + kk) * row_elems + col_off;
     }
-    const int dst = dst0 + i * ROWS_PER_PASS * D;
+    // With fewer than 8 rows per pass (256-wide heads) the swizzle term changes from pass to pass.
+    const int dst = (ROWS_PER_PASS % 8 == 0) ? dst0 + i * ROWS_PER_PASS * D : row * D + ((ch ^ (row & 7)) * 8);
     cp_async_16(sK + dst, (PAGED ? p.k_cache : p.k) + off, valid ? 16 : 0);
     cp_async_16(sV + dst, (PAGED ? p.v_cache : p.v) + off, valid ? 16 : 0);
   }
@@ -784,9 +785,9 @@ int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v,
                      void* mx_sf0, void* mx_sf1, cudaStream_t stream) {
   using namespace afb;
   if (B <= 0 || T <= 0) return 0;
-  if (Hq % Hkv != 0 || (D != 64 && D != 128)) {
-    set_last_error("afb_attention: head_dim must be 64 or 128 and Hq a multiple of Hkv (D=%d Hq=%d Hkv=%d)", D, Hq,
-                   Hkv);
+  if (Hq % Hkv != 0 || (D != 64 && D != 128 && D != 256)) {
+    set_last_error("afb_attention: head_dim must be 64, 128 or 256 and Hq a multiple of Hkv (D=%d Hq=%d Hkv=%d)", D,
+                   Hq, Hkv);
     return -1;
   }
   if ((q_stride & 7) || (kv_stride & 7) || (out_stride & 3)) {
@@ -840,7 +841,7 @@ int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v,
     rc = split_keys ? launch_attn<DD, false, true>(p, B, max_rows, stream)                         \
                     : launch_attn<DD, false, false>(p, B, max_rows, stream);                       \
   }
-  if (D == 64) { AFB_ATTN_DISPATCH(64) } else { AFB_ATTN_DISPATCH(128) }
+  if (D == 64) { AFB_ATTN_DISPATCH(64) } else if (D == 128) { AFB_ATTN_DISPATCH(128) } else { AFB_ATTN_DISPATCH(256) }
 #undef AFB_ATTN_DISPATCH
   if (rc) return rc;
   if (num_splits > 1) {

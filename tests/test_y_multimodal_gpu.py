@@ -92,3 +92,42 @@ def test_bitnet_forward_on_gpu():
     got = T._run(gpu, cfg, ids.cuda(), 24, device="cuda")
     cos = torch.nn.functional.cosine_similarity(got.float().cpu(), want, dim=-1)
     assert float(cos.min()) > 0.99, cos
+
+
+# -- 256-wide heads (Gemma-class decoders) through the same attention kernels ----------------------------------
+@pytest.mark.parametrize("causal", [False, True])
+def test_varlen_attention_head_width_256(causal):
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+    from tests.test_attention_gpu import _rand
+
+    D, Hq, Hkv = 256, 4, 2
+    lens = torch.tensor([1, 17, 64, 65, 200, 33], dtype=torch.int32)
+    starts = (torch.cumsum(lens, 0) - lens).int()
+    T = int(lens.sum())
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=1, scale=0.5)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    out = A.varlen_attention(q, k, v, starts.cuda(), lens.cuda(), int(lens.max()), causal=causal)
+    cu = torch.cat([starts, torch.tensor([T], dtype=torch.int32)])
+    torch.testing.assert_close(out.float(), R.varlen_attention(q, k, v, cu, causal=causal), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 1), (8, 2), (16, 1)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_decode_head_width_256(Hq, Hkv, splits):
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+    from tests.test_attention_gpu import _build_paged, _rand
+
+    D = 256
+    kv_lens = [1, 15, 16, 17, 300, 1030, 64]
+    B = len(kv_lens)
+    kc, vc, bt = _build_paged(B, kv_lens, Hkv, D, 16, seed=5)
+    q = _rand(B, Hq, D, seed=9, scale=0.5)
+    q_starts = torch.arange(B, dtype=torch.int32, device="cuda")
+    q_lens = torch.ones(B, dtype=torch.int32, device="cuda")
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    out = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=splits)
+    torch.testing.assert_close(out.float(), R.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl), atol=2e-2, rtol=2e-2)
