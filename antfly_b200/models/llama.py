@@ -52,6 +52,12 @@ class LlamaConfig:
     # BitNet b1.58: ternary weights with one scale per matrix, activations rounded to 8 bits per token before
     # every projection, an extra RMS norm before the attention-output and the down projections
     mrope_sections: Optional[List[int]] = None   # Qwen2-VL: rotary pairs split between time / row / column streams
+    # Gemma-3: a norm after attention and after the MLP as well as before them, a fixed softmax scale, and layers
+    # that alternate between a sliding window with its own rotary base and global attention
+    post_norms: bool = False
+    attn_scale: float = 0.0                       # 0: 1 / sqrt(head_dim)
+    layer_windows: Optional[List[int]] = None     # per layer: window length, 0 = global
+    layer_rope: Optional[List[List[float]]] = None  # per layer: [theta, frequency scale]
     bitnet: bool = False
     bitnet_scale_divides: bool = False   # packed checkpoints of the "bitlinear" kind store 1 / scale
     # Mixture of experts (Mixtral, Qwen2-MoE, Qwen3-MoE): 0 experts = dense MLP
@@ -107,6 +113,25 @@ class LlamaConfig:
             cfg.gate_act = "relu2"
             cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
             cfg.bitnet_scale_divides = (d.get("quantization_config") or {}).get("linear_class") == "bitlinear"
+        if mt in ("gemma3_text", "gemma3"):
+            cfg.norm_plus_one, cfg.qk_norm, cfg.post_norms = True, True, True
+            cfg.embed_scale = float(cfg.hidden_size) ** 0.5
+            cfg.gate_act = "gelu_tanh"
+            cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
+            cfg.attn_scale = float(d.get("query_pre_attn_scalar") or cfg.head_dim) ** -0.5
+            kinds = d.get("layer_types") or [
+                "full_attention" if (i + 1) % int(d.get("sliding_window_pattern", 6) or 6) == 0 else "sliding_attention"
+                for i in range(cfg.num_hidden_layers)]
+            win = int(d.get("sliding_window") or 0)
+            per = {k: v for k, v in rp.items() if isinstance(v, dict)}        # newer files: one entry per layer kind
+            g_par, l_par = per.get("full_attention", rp), per.get("sliding_attention", {})
+            g_theta = float(g_par.get("rope_theta") or d.get("rope_theta") or 1000000.0)
+            g_scale = 1.0 / float(g_par["factor"]) if g_par.get("rope_type", g_par.get("type")) == "linear" and \
+                g_par.get("factor") else 1.0
+            l_theta = float(l_par.get("rope_theta") or d.get("rope_local_base_freq") or 10000.0)
+            cfg.layer_windows = [win if k == "sliding_attention" else 0 for k in kinds]
+            cfg.layer_rope = [[l_theta, 1.0] if k == "sliding_attention" else [g_theta, g_scale] for k in kinds]
+            cfg.sliding_window, cfg.rope_theta, cfg.rope_freq_scale = 0, g_theta, g_scale
         if mt == "gemma":
             cfg.norm_plus_one = True
             cfg.embed_scale = float(cfg.hidden_size) ** 0.5
@@ -301,7 +326,12 @@ class LlamaModel:
                 w[p + "attn_sub"] = sd[s + "self_attn.attn_sub_norm.weight"].to(torch.bfloat16).to(device)
                 w[p + "ffn_sub"] = sd[s + "mlp.ffn_sub_norm.weight"].to(torch.bfloat16).to(device)
             w[p + "ln1"] = sd[s + "input_layernorm.weight"].to(torch.bfloat16).to(device)
-            w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
+            if cfg.post_norms:     # four norms per layer; "post_attention" here is the one on the attention output
+                w[p + "ln2"] = sd[s + "pre_feedforward_layernorm.weight"].to(torch.bfloat16).to(device)
+                w[p + "post_attn"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
+                w[p + "post_ffn"] = sd[s + "post_feedforward_layernorm.weight"].to(torch.bfloat16).to(device)
+            else:
+                w[p + "ln2"] = sd[s + "post_attention_layernorm.weight"].to(torch.bfloat16).to(device)
             if s + "self_attn.qkv_proj.weight" in sd:  # Phi-3: fused [q | k | v] rows
                 nq, nk = cfg.num_attention_heads * D, cfg.num_key_value_heads * D
                 fused = sd[s + "self_attn.qkv_proj.weight"]
@@ -665,17 +695,23 @@ class LlamaModel:
                 qkv[:, :nqk] = mrope_rotate(qkv[:, :nqk].view(T, Hq + Hkv, D), b.pos3, cfg.rope_theta,
                                             cfg.mrope_sections).view(T, nqk)
                 qkv_bias, rope_pos = None, zero_pos
-            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, cfg.rope_theta,
+            theta, fscale = cfg.layer_rope[l] if cfg.layer_rope else (cfg.rope_theta, cfg.rope_freq_scale)
+            window = cfg.layer_windows[l] if cfg.layer_windows else cfg.sliding_window
+            q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, theta,
                                 bias=qkv_bias, rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
-                                freq_scale=cfg.rope_freq_scale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
+                                freq_scale=fscale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
                                 norm_eps=eps, norm_plus_one=gp1)
             ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
-                                    scratch=attn_scratch)
+                                    b.max_q_len, scale=cfg.attn_scale or None, window=window,
+                                    num_splits=b.attn_splits, scratch=attn_scratch)
             ctx = ctx.view(T, Hq * D)
             if cfg.bitnet:
                 ctx = Dn.norm(ctx.contiguous(), w[p + "attn_sub"], eps=eps, rms=True)
-            x = lin(ctx, p + "o", residual=x)
+            if cfg.post_norms:
+                a_out = Dn.norm(lin(ctx, p + "o"), w[p + "post_attn"], eps=eps, rms=True, gamma_plus_one=gp1)
+                x = (x.float() + a_out.float()).to(torch.bfloat16)
+            else:
+                x = lin(ctx, p + "o", residual=x)
             h = Dn.norm(x, w[p + "ln2"], eps=eps, rms=True, gamma_plus_one=gp1)
             if cfg.num_experts > 0:
                 x = (x.float() + self._moe_mlp(h, l, T)).to(torch.bfloat16)
@@ -695,7 +731,11 @@ class LlamaModel:
             act = (gate * up).to(torch.bfloat16)
             if cfg.bitnet:
                 act = Dn.norm(act.contiguous(), w[p + "ffn_sub"], eps=eps, rms=True)
-            x = lin(act, p + "down", residual=x)
+            if cfg.post_norms:
+                m_out = Dn.norm(lin(act, p + "down"), w[p + "post_ffn"], eps=eps, rms=True, gamma_plus_one=gp1)
+                x = (x.float() + m_out.float()).to(torch.bfloat16)
+            else:
+                x = lin(act, p + "down", residual=x)
             if l + 1 < hi:
                 h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
         n_rows = T if b.logit_rows.numel() == T else b.logit_rows.numel()
@@ -716,7 +756,7 @@ class LlamaModel:
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
         if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
-                self.pp is not None or b.embed_rows is not None or b.pos3 is not None:
+                self.pp is not None or b.embed_rows is not None or b.pos3 is not None or cfg.post_norms:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

@@ -48,6 +48,17 @@ def _hf_decoder(kind: str):
     elif kind == "gemma":
         cfg = transformers.GemmaConfig(**{**common, "head_dim": 64, "hidden_activation": "gelu_pytorch_tanh"})
         m = transformers.GemmaForCausalLM(cfg)
+    elif kind == "gemma3":
+        cfg = transformers.Gemma3TextConfig(**{**common, "head_dim": 64, "query_pre_attn_scalar": 48,
+                                               "sliding_window": 8, "num_hidden_layers": 3,
+                                               "layer_types": ["sliding_attention", "full_attention",
+                                                               "sliding_attention"],
+                                               "rope_parameters": {
+                                                   "sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                                   "full_attention": {"rope_type": "linear", "factor": 4.0,
+                                                                      "rope_theta": 1000000.0}}})
+        cfg.tie_word_embeddings = False
+        m = transformers.Gemma3ForCausalLM(cfg)
     elif kind == "phi3":
         cfg = transformers.Phi3Config(**{**common, "pad_token_id": 0})
         m = transformers.Phi3ForCausalLM(cfg)
@@ -73,8 +84,8 @@ def _hf_decoder(kind: str):
     return cfg, m.eval().float()
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "phi3", "mixtral",
-                                  "qwen2_moe", "qwen3_moe"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "gemma3", "phi3",
+                                  "mixtral", "qwen2_moe", "qwen3_moe"])
 def test_decoder_matches_transformers(kind):
     torch.manual_seed(0)
     hf_cfg, hf = _hf_decoder(kind)
@@ -83,7 +94,7 @@ def test_decoder_matches_transformers(kind):
             if n.endswith("bias"):
                 p.normal_(0, 0.05)
             elif "norm" in n:
-                p.uniform_(-0.3, 0.3) if kind == "gemma" else p.uniform_(0.5, 1.5)
+                p.uniform_(-0.3, 0.3) if kind.startswith("gemma") else p.uniform_(0.5, 1.5)
     _round_linears_to_fp8_grid(hf)
     cfg = LlamaConfig.from_hf(hf_cfg.to_dict())
     if kind == "llama_tied":
