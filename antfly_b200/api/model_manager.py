@@ -275,6 +275,21 @@ class ModelManager:
                     vision, VlmTokens(int(cfg_d.get("image_token_id", 151655)), cfg_d.get("vision_start_token_id"),
                                       cfg_d.get("vision_end_token_id")),
                     int(pre.get("min_pixels", 56 * 56)), int(pre.get("max_pixels", 14 * 14 * 4 * 1280)))
+            elif cfg_d.get("model_type") == "gemma3" and cfg_d.get("vision_config"):
+                from ..models.gemma3v import Gemma3VisionModel, SiglipVisionConfig
+                from ..models.qwen2vl import text_state_dict
+                from ..pipelines.vlm import Gemma3Adapter
+
+                text_d = dict(cfg_d.get("text_config") or {})
+                text_d.setdefault("model_type", "gemma3_text")
+                model = LlamaModel.from_state_dict(LlamaConfig.from_hf(text_d), text_state_dict(sd), device=self.device)
+                vision = Gemma3VisionModel.from_state_dict(
+                    SiglipVisionConfig.from_hf(cfg_d["vision_config"]), sd, device=self.device,
+                    tokens_per_image=int(cfg_d.get("mm_tokens_per_image", 256)),
+                    norm_eps=float(text_d.get("rms_norm_eps", 1e-6)))
+                vlm = Gemma3Adapter(vision, int(cfg_d.get("image_token_index", 262144)),
+                                    int(cfg_d.get("boi_token_index", 255999)), int(cfg_d.get("eoi_token_index", 256000)),
+                                    tok.encode("\n\n"))
             else:
                 cfg = LlamaConfig.from_hf(cfg_d)
                 model = LlamaModel.from_state_dict(cfg, sd, device=self.device)

@@ -174,6 +174,10 @@ class StepBatch:
     embed_rows: Optional[torch.Tensor] = None
     embed_vals: Optional[torch.Tensor] = None
     pos3: Optional[torch.Tensor] = None
+    # runs of rows (image tokens) that attend to one another in both directions: (q_starts, q_lens, kv_lens,
+    # block_tables, longest run, row indices), each run described like a sequence of its own whose keys end where
+    # the run ends
+    bidir: Optional[tuple] = None
 
 
 def pick_split_k(n_out: int, k_in: int, m_tokens: int, sm_count: int = 148) -> int:
@@ -704,6 +708,13 @@ class LlamaModel:
             ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, scale=cfg.attn_scale or None, window=window,
                                     num_splits=b.attn_splits, scratch=attn_scratch)
+            if b.bidir is not None:
+                # second pass over the image runs without the causal mask (their keys are already in the cache);
+                # its rows replace the causal ones
+                bs, bl, bk, bt, bmax, brow = b.bidir
+                both = A.paged_attention(q, k_cache_l, v_cache_l, bt, bs, bl, bk, bmax, scale=cfg.attn_scale or None,
+                                         window=window, causal=False, decode=False)
+                ctx.index_copy_(0, brow, both.index_select(0, brow))
             ctx = ctx.view(T, Hq * D)
             if cfg.bitnet:
                 ctx = Dn.norm(ctx.contiguous(), w[p + "attn_sub"], eps=eps, rms=True)
@@ -756,7 +767,8 @@ class LlamaModel:
         k_cache / v_cache [L, num_blocks, page, Hkv, D].  Returns bf16 logits [R, vocab_local]."""
         cfg, w = self.cfg, self.w
         if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
-                self.pp is not None or b.embed_rows is not None or b.pos3 is not None or cfg.post_norms:
+                self.pp is not None or b.embed_rows is not None or b.pos3 is not None or cfg.post_norms or \
+                b.bidir is not None:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

@@ -71,8 +71,9 @@ class PagedAttnScratch:
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, max_q_len: int,
                     scale: Optional[float] = None, window: int = 0, decode: Optional[bool] = None,
                     num_splits: int = 1, scratch: Optional[PagedAttnScratch] = None,
-                    out: Optional[torch.Tensor] = None, mx_terms: int = 0):
-    """Causal attention of packed query tokens q [T, Hq, D] against the paged cache
+                    out: Optional[torch.Tensor] = None, mx_terms: int = 0, causal: bool = True):
+    """Causal attention (``causal=False``: every query row of a sequence sees all of its ``kv_lens`` keys, within a
+    two-sided ``window`` if one is set) of packed query tokens q [T, Hq, D] against the paged cache
     k_cache / v_cache [num_blocks, page, Hkv, D].  ``decode`` selects the split-keys organisation (<= 16
     (position, head-in-group) rows per KV head); default: when max_q_len * group <= 16.
     ``mx_terms`` 1 or 2 returns the context rows [T, Hq * D] as MX-fp8 activations
@@ -83,7 +84,7 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
         y = R.paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale,
-                              window).to(torch.bfloat16)
+                              window, causal=causal).to(torch.bfloat16)
         if mx_terms:
             from . import quant as Q
 
@@ -115,8 +116,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
         N.ptr(q), _c_long(q.stride(0)), None, None, _c_long(0), N.ptr(k_cache), N.ptr(v_cache),
         N.ptr(block_tables), _c_int(block_tables.shape[1]), _c_int(page), N.ptr(q_starts), N.ptr(q_lens),
         N.ptr(kv_lens), N.ptr(out), _c_long(out.stride(0) if out is not None else Hq * D), N.ptr(part_o),
-        N.ptr(part_lse), _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_q_len), _c_int(1),
-        _c_int(window), _c_float(scale), _c_int(1), _c_int(1 if decode else 0), _c_int(num_splits),
+        N.ptr(part_lse), _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(max_q_len),
+        _c_int(1 if causal else 0), _c_int(window), _c_float(scale), _c_int(1), _c_int(1 if decode else 0), _c_int(num_splits),
         N.ptr(mx.q0 if mx else None), N.ptr(mx.q1 if mx else None), N.ptr(mx.sf0 if mx else None),
         N.ptr(mx.sf1 if mx else None), N.stream_ptr(),
     )

@@ -190,7 +190,7 @@ def alibi_slopes(num_heads: int) -> torch.Tensor:
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale=None,
-                    sliding_window: int = 0, alibi: Optional[torch.Tensor] = None):
+                    sliding_window: int = 0, alibi: Optional[torch.Tensor] = None, causal: bool = True):
     """Causal attention of packed query tokens against a paged KV cache.
 
     q: [T, Hq, D]; k_cache / v_cache: [num_blocks, page, Hkv, D]; block_tables: [B, max_blocks] int32;
@@ -221,9 +221,11 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
         kpos = torch.arange(kl, device=q.device)[None, :]
         if alibi is not None:
             sc = sc + alibi.to(sc.device).float()[:, None, None] * (kpos - qpos).float()[None]
-        m = kpos <= qpos
+        m = (kpos <= qpos) if causal else torch.ones_like(kpos <= qpos)
         if sliding_window > 0:
             m = m & (kpos > qpos - sliding_window)
+            if not causal:                       # two-sided window, as in the packed (non-paged) attention
+                m = m & (kpos < qpos + sliding_window)
         sc = sc.masked_fill(~m, float("-inf"))
         out[qs:qs + ql] = (sc.softmax(-1) @ vv).transpose(0, 1)
     return out

@@ -87,3 +87,41 @@ def split_content(messages: Sequence[dict]) -> List[ImageLike]:
                 v = v.get("url")
             found.append(decode_data_url(v) if isinstance(v, str) and v.startswith("data:") else v)
     return found
+
+
+class Gemma3Adapter:
+    """Gemma-3 images: every ``<start_of_image>`` in the prompt becomes a blank line, the begin marker, 256 soft
+    tokens, the end marker and another blank line; the soft tokens of one image attend to one another in both
+    directions, so the engine prefills such a prompt in one piece (zig/pkg/inference/src/pipelines/vlm_gemma3.zig)."""
+
+    placeholder = "<start_of_image>"
+
+    def __init__(self, vision, image_token: int, boi_token: int, eoi_token: int, newline_ids: Sequence[int] = ()):
+        self.vision, self.image, self.boi, self.eoi = vision, image_token, boi_token, eoi_token
+        self.newline_ids = list(newline_ids)
+
+    def expand(self, ids: Sequence[int], images: Sequence[ImageLike]) -> Tuple[List[int], Optional[dict]]:
+        from ..models.gemma3v import gemma3_pixels
+
+        n_ph = sum(1 for t in ids if t == self.boi)
+        if not images:
+            if n_ph:
+                raise ValueError("the prompt has image placeholders but no images were given")
+            return list(ids), None
+        if n_ph != len(images):
+            raise ValueError(f"{len(images)} image(s) for {n_ph} placeholder(s) in the prompt")
+        size = self.vision.cfg.image_size
+        px = torch.stack([gemma3_pixels(load_image(s).cpu(), size) for s in images])
+        soft = self.vision.soft_tokens(px)                                   # [images, tokens, hidden]
+        n_tok = soft.shape[1]
+        out: List[int] = []
+        spans = []
+        for t in ids:
+            if t == self.boi:
+                out += self.newline_ids + [self.boi]
+                spans.append((len(out), len(out) + n_tok))
+                out += [self.image] * n_tok + [self.eoi] + self.newline_ids
+            else:
+                out.append(t)
+        rows = [i for a, b in spans for i in range(a, b)]
+        return out, {"rows": rows, "vals": soft.reshape(-1, soft.shape[-1]), "bidir": spans}

@@ -63,6 +63,7 @@ class Request:
     soft_vals: Optional[torch.Tensor] = None
     pos3: Optional[torch.Tensor] = None
     rope_delta: int = 0
+    bidir_spans: Optional[List[tuple]] = None     # [start, end) prompt ranges that attend in both directions
 
     @property
     def tokens(self) -> List[int]:
@@ -158,7 +159,8 @@ class LLMEngine:
         if soft is not None:
             if self.draft is not None:
                 raise ValueError("speculative decoding is not available for prompts with images")
-            if len(soft["rows"]) != soft["vals"].shape[0] or soft["pos3"].shape != (3, len(prompt)):
+            if len(soft["rows"]) != soft["vals"].shape[0] or (
+                    soft.get("pos3") is not None and soft["pos3"].shape != (3, len(prompt))):
                 raise ValueError("soft-token description does not match the prompt")
         if self.prefix is not None and soft is None:
             eid, n = self.prefix.lookup(prompt)
@@ -178,7 +180,11 @@ class LLMEngine:
         r = Request(rid, list(prompt), params, t_admit=time.perf_counter())
         if soft is not None:
             r.soft_rows, r.soft_vals = [int(i) for i in soft["rows"]], soft["vals"].to(self.device)
-            r.pos3, r.rope_delta = soft["pos3"].to(torch.int64).cpu(), int(soft.get("delta", 0))
+            if soft.get("pos3") is not None:
+                r.pos3, r.rope_delta = soft["pos3"].to(torch.int64).cpu(), int(soft.get("delta", 0))
+            if soft.get("bidir"):
+                r.bidir_spans = [(int(a), int(b)) for a, b in soft["bidir"]]
+                self.sched.set_atomic_prefill(rid)       # a run must see its later tokens: no chunking
         if params.needs_penalties:
             r.row = self._rows_free.pop()
             if self.counts is None:
@@ -271,23 +277,35 @@ class LLMEngine:
     def _add_multimodal(self, batch: StepBatch, items: List[StepItem], reqs: List[Request]) -> None:
         """Rotary streams for every token of the step, and the soft-token rows that fall inside its prefill chunks."""
         pos, rows, vals = [], [], []
+        runs = []                                   # (first row in the step, length, keys up to the run's end, item)
         t0 = 0
-        for it, r in zip(items, reqs):
+        for i, (it, r) in enumerate(zip(items, reqs)):
             n = 1 if it.mode == "decode" else it.q_len
             a = it.kv_before
-            if r.pos3 is not None and it.mode != "decode":
-                pos.append(r.pos3[:, a:a + n])
+            if r.soft_rows is not None and it.mode != "decode":
                 for j, p in enumerate(r.soft_rows):
                     if a <= p < a + n:
                         rows.append(t0 + p - a)
                         vals.append(r.soft_vals[j])
+                for s0, s1 in r.bidir_spans or []:
+                    if a <= s0 and s1 <= a + n:
+                        runs.append((t0 + s0 - a, s1 - s0, s1 - r.kv_removed, i))
+            if r.pos3 is not None and it.mode != "decode":
+                pos.append(r.pos3[:, a:a + n])
             else:
                 pos.append((torch.arange(a, a + n) + r.rope_delta)[None].expand(3, n))
             t0 += n
-        batch.pos3 = torch.cat(pos, 1).to(self.device)
+        if any(r.pos3 is not None for r in reqs):
+            batch.pos3 = torch.cat(pos, 1).to(self.device)
         if rows:
             batch.embed_rows = torch.tensor(rows, dtype=torch.int64, device=self.device)
             batch.embed_vals = torch.stack(vals)
+        if runs:
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+            which = torch.tensor([u[3] for u in runs], dtype=torch.int64, device=self.device)
+            row_idx = torch.cat([torch.arange(u[0], u[0] + u[1]) for u in runs]).to(self.device)
+            batch.bidir = (i32([u[0] for u in runs]), i32([u[1] for u in runs]), i32([u[2] for u in runs]),
+                           batch.block_tables.index_select(0, which).contiguous(), max(u[1] for u in runs), row_idx)
 
     def _pick_tokens(self, logits: torch.Tensor, reqs: List[Request]) -> torch.Tensor:
         if any(r.params.grammar is not None for r in reqs):
@@ -400,7 +418,7 @@ class LLMEngine:
                                               for r in self.reqs.values()):
             snap = self.sched.snapshot()
             if snap["decode"] > 0 and snap["waiting"] + snap["prefill"] == 0 and not any(
-                    r.pos3 is not None for r in self.reqs.values()):
+                    r.soft_rows is not None for r in self.reqs.values()):
                 return self._spec_round()
         items = self.sched.claim_step()
         if not items:
@@ -408,7 +426,7 @@ class LLMEngine:
         t_start = time.perf_counter()
         reqs = [self.reqs[it.request_id] for it in items]
         try:
-            multimodal = any(r.pos3 is not None for r in reqs)
+            multimodal = any(r.soft_rows is not None for r in reqs)
             if all(it.mode == "decode" and it.q_len == 1 for it in items) and self.device.type == "cuda" \
                     and not multimodal:
                 toks_dev = self._decode_static(items)
@@ -450,7 +468,7 @@ class LLMEngine:
                 ratio = r.params.cache_compaction_ratio
                 if ratio is not None and 0.0 < ratio < 1.0:
                     self.compact_request(it.request_id, ratio)
-                elif self.prefix is not None and r.pos3 is None:
+                elif self.prefix is not None and r.soft_rows is None:
                     self.prefix.insert(it.request_id, r.prompt)
         toks = toks_dev.cpu().tolist() if toks_dev is not None else []
         self.d2h_bytes += 4 * len(toks)

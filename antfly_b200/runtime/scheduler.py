@@ -48,6 +48,7 @@ def _lib():
         lib.afb_sched_destroy.argtypes = [ctypes.c_void_p]
         lib.afb_sched_admit.argtypes = [ctypes.c_void_p, _i64, _int, _int]
         lib.afb_sched_set_decode_width.argtypes = [ctypes.c_void_p, _i64, _int]
+        lib.afb_sched_set_atomic_prefill.argtypes = [ctypes.c_void_p, _i64, _int]
         lib.afb_sched_claim_step.argtypes = [ctypes.c_void_p, _pi64, _pint, _pint, _pint, _int]
         lib.afb_sched_complete_step.argtypes = [ctypes.c_void_p, _int, _pi64, _pint, _pint]
         lib.afb_sched_fail_step.argtypes = [ctypes.c_void_p]
@@ -90,6 +91,10 @@ class StepScheduler:
             raise QueueFull("generation queue is full")
         if rc != 0:
             raise ValueError("duplicate request id or empty prompt")
+
+    def set_atomic_prefill(self, request_id: int, on: bool = True) -> None:
+        """The request's prompt is prefilled in one step, never in chunks."""
+        self.lib.afb_sched_set_atomic_prefill(self.h, request_id, 1 if on else 0)
 
     def set_decode_width(self, request_id: int, width: int) -> None:
         self.lib.afb_sched_set_decode_width(self.h, request_id, width)

@@ -36,6 +36,7 @@ struct Request {
   Phase phase = kWaiting;
   bool in_flight = false;
   int claimed_q = 0;
+  bool atomic_prefill = false;  // the whole prompt goes into one step (prompts whose tokens attend to later ones)
 };
 
 struct Sched {
@@ -106,6 +107,17 @@ int afb_sched_admit_prefilled(void* h, int64_t id, int prompt_len, int max_new_t
   return 0;
 }
 
+// A request flagged here is never prefilled in chunks: its prompt is claimed whole, as the leader of a step if
+// it does not fit beside other items.
+int afb_sched_set_atomic_prefill(void* h, int64_t id, int on) {
+  Sched* s = static_cast<Sched*>(h);
+  std::lock_guard<std::mutex> g(s->mu);
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end()) return -1;
+  it->second.atomic_prefill = on != 0;
+  return 0;
+}
+
 int afb_sched_set_decode_width(void* h, int64_t id, int width) {
   Sched* s = static_cast<Sched*>(h);
   std::lock_guard<std::mutex> g(s->mu);
@@ -164,11 +176,12 @@ int afb_sched_claim_step(void* h, int64_t* ids, int* modes, int* q_lens, int* kv
       if ((r.phase != kWaiting && r.phase != kPrefill) || r.in_flight) continue;
       if (items >= std::min(s->max_items, max_out) && items > 0) break;
       const int remaining = r.prompt_len - r.prompt_done;
-      int chunk = std::min(remaining, s->prefill_chunk);
+      int chunk = r.atomic_prefill ? remaining : std::min(remaining, s->prefill_chunk);
       if (items > 0) {
         const int room = s->max_query_tokens - qtok;
         if (room <= 0) break;
         if (chunk > room) {
+          if (r.atomic_prefill) continue;  // waits for a step it can lead or fit into whole
           // Shrink to the budget, but never below min_chunk unless it finishes the prompt.
           if (room < s->min_chunk && room < remaining) continue;
           chunk = room;
