@@ -131,3 +131,24 @@ def test_paged_decode_head_width_256(Hq, Hkv, splits):
     kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
     out = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, num_splits=splits)
     torch.testing.assert_close(out.float(), R.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("window", [0, 40])
+def test_paged_attention_without_causal_mask(window):
+    """Runs of image tokens attend in both directions: paged keys, no causal mask, optionally a two-sided window."""
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+    from tests.test_attention_gpu import _build_paged, _rand
+
+    D, Hq, Hkv = 64, 8, 2
+    kv_lens, q_lens = [70, 300, 33], [64, 256, 33]
+    B = len(kv_lens)
+    kc, vc, bt = _build_paged(B, kv_lens, Hkv, D, 16, seed=3)
+    T = sum(q_lens)
+    q = _rand(T, Hq, D, seed=4)
+    ql = torch.tensor(q_lens, dtype=torch.int32, device="cuda")
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    out = A.paged_attention(q, kc, vc, bt, qs, ql, kvl, max(q_lens), window=window, causal=False, decode=False)
+    ref = R.paged_attention(q, kc, vc, bt, qs, ql, kvl, sliding_window=window, causal=False)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
