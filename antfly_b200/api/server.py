@@ -733,6 +733,28 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             except Exception as e:
                 return _err(400, "invalid_request", f"image {i}: {e}")
 
+        extra = req.model_extra or {}
+
+        def work_multistage():
+            # whole pages: find the text regions, read each, return them in reading order
+            from ..pipelines.ocr_multistage import MultiStageOCR, RegionPostProcessor
+
+            lm = mgr.get(req.model, "reader")
+            post = RegionPostProcessor(**{k: extra[k] for k in ("threshold", "box_threshold", "unclip_ratio",
+                                                                "min_box_area") if k in extra})
+            ocr = MultiStageOCR(lm.pipeline, post=post)
+            data = []
+            for i, im in enumerate(imgs):
+                r = ocr.run(im, req.max_tokens)
+                data.append({"object": "read", "index": i, "text": r.full_text, "regions": [
+                    {"bbox": [round(v, 1) for v in g.bbox], "confidence": g.confidence, "text": g.text,
+                     **({"label": g.label} if g.label else {})} for g in r.regions]})
+            return {"object": "list", "model": req.model, "data": data,
+                    "usage": {"prompt_tokens": 0, "completion_tokens": 0, "total_tokens": 0}}
+
+        if extra.get("multistage"):
+            return await asyncio.to_thread(run_guarded, "read", len(imgs), work_multistage)
+
         def work():
             lm = mgr.get(req.model, "reader")
             res = lm.pipeline.read(imgs, req.max_tokens)
