@@ -939,7 +939,26 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                         for s in keep:
                             rec["classifications"].append({"name": t.get("name", ""), "label": s["label"],
                                                            "score": s["score"]})
-            return {"object": "extraction", "model": req.model, "data": data, "usage": {"inputs": len(texts)}}
+            out = {"object": "extraction", "model": req.model, "data": data, "usage": {"inputs": len(texts)}}
+            if opts.get("resolve"):
+                # one graph over all inputs: similar mentions of a type become one entity, relations are re-keyed
+                from types import SimpleNamespace as _NS
+
+                from ..pipelines.resolver import ResolverConfig, build_knowledge_graph
+
+                mk = lambda e: _NS(text=e.get("text", ""), label=e.get("label", ""), score=float(e.get("score", 1.0)))
+                kg = build_knowledge_graph(
+                    [[mk(e) for e in rec.get("entities", [])] for rec in data],
+                    [[_NS(head=mk(r["source"]), tail=mk(r["target"]), label=r.get("type", ""),
+                          score=float(r.get("score", 1.0))) for r in rec.get("relations", [])] for rec in data],
+                    ResolverConfig(similarity_threshold=float(opts.get("similarity_threshold", 0.85)),
+                                   type_must_match=bool(opts.get("type_must_match", True))))
+                out["knowledge_graph"] = {
+                    "entities": [{"id": e.id, "name": e.canonical_name, "label": e.label, "score": e.score,
+                                  "mentions": e.mentions, "inputs": e.text_indices} for e in kg.entities],
+                    "relations": [{"source": r.head_id, "target": r.tail_id, "type": r.label, "score": r.score,
+                                   "inputs": r.text_indices} for r in kg.relations]}
+            return out
 
         return await asyncio.to_thread(run_guarded, "extract", max(1, len(req.inputs)), work)
 

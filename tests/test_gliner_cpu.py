@@ -197,3 +197,36 @@ def test_extract_endpoint_with_a_span_model():
         assert text[e["start"]:e["end"]] == e["text"]          # character offsets, although "ë" is two bytes
     assert isinstance(rec["relations"], list)
     assert len(rec["classifications"]) == 1 and rec["classifications"][0]["label"] in ("travel", "sport")
+
+
+def test_extract_resolve_option_builds_a_graph():
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+
+    class Fake:                                   # a span model stand-in with fixed answers
+        def recognize(self, texts, labels, threshold=None):
+            E = G.GlinerEntity
+            return [[E("Ada Lovelace", "person", 0, 12, 0.9), E("London", "city", 20, 26, 0.8)],
+                    [E("ada lovelace", "person", 0, 12, 0.7)]][: len(texts)]
+
+        def extract_relations(self, texts, ents, rels):
+            e = self.recognize(texts, ents)
+            return e, [[G.GlinerRelation(e[0][0], e[0][1], "lives in", 0.6)], []][: len(texts)]
+
+        def classify(self, *a, **k):
+            return []
+
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register("fake", "recognizer", Fake(), None)
+    c = TestClient(create_app(mgr))
+    r = c.post("/ai/v1/extract", json={"model": "fake", "inputs": [{"content": "Ada Lovelace lived in London"},
+                                                                    {"content": "ada lovelace again"}],
+                                       "schema": {"entities": ["person", "city"], "relations": [{"type": "lives in"}]},
+                                       "options": {"resolve": True}})
+    assert r.status_code == 200, r.text
+    kg = r.json()["knowledge_graph"]
+    assert [e["name"] for e in kg["entities"]] == ["Ada Lovelace", "London"] and kg["entities"][0]["inputs"] == [0, 1]
+    assert kg["relations"] == [{"source": "entity-0", "target": "entity-1", "type": "lives in", "score": 0.6,
+                                "inputs": [0]}]
