@@ -231,6 +231,26 @@ class ModelManager:
             else:
                 pipe = TextClassifier(model, tok, id2label,
                                       multi_label=cfg_d.get("problem_type") == "multi_label_classification")
+        elif task in ("embedder", "reranker") and cfg_d.get("model_type") == "colqwen2":
+            # page-image retrieval by late interaction over a Qwen2-VL backbone
+            from ..models import qwen2vl as QV
+            from ..pipelines.vlm import ColQwenEmbedder, Qwen2VLAdapter, VlmTokens
+
+            vd = cfg_d.get("vlm_config") or {}
+            text_d = dict(vd.get("text_config") or {k: v for k, v in vd.items() if k != "vision_config"})
+            text_d.setdefault("model_type", "qwen2_vl_text")
+            core = {k[len("vlm."):] if k.startswith("vlm.") else k: v for k, v in sd.items()}
+            model = LlamaModel.from_state_dict(
+                LlamaConfig.from_hf(text_d),
+                QV.text_state_dict({k: v for k, v in core.items() if not k.startswith("embedding_proj_layer")}),
+                device=self.device)
+            vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(vd.get("vision_config") or {}),
+                                                           core, device=self.device)
+            adapter = Qwen2VLAdapter(vision, VlmTokens(int(vd.get("image_token_id", 151655))))
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            pw = core["embedding_proj_layer.weight"].to(dt).to(self.device)
+            pb = core["embedding_proj_layer.bias"].to(dt).to(self.device) if "embedding_proj_layer.bias" in core else None
+            pipe = ColQwenEmbedder(model, adapter, pw, pb, tok)
         elif task in ("embedder", "reranker") and cfg_d.get("model_type") == "modernbert":
             from ..models.modernbert import ModernBertConfig, ModernBertModel
 

@@ -375,6 +375,13 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             else:
                 lm = mgr.get(req.model, "embedder")
                 pipe = lm.pipeline
+                if hasattr(pipe, "rerank_pages"):
+                    # late interaction: token vectors of the query against token vectors of each document's parts
+                    scores, ntok = pipe.rerank_pages(req.query, docs)
+                    metrics.tokens.labels("rerank", "prompt").inc(ntok)
+                    return S.RerankResponse(
+                        data=[S.RerankObject(index=i, score=float(s)) for i, s in enumerate(scores)], model=req.model,
+                        usage=S.GenerateUsage(prompt_tokens=ntok, completion_tokens=0, total_tokens=ntok)).model_dump()
                 if not hasattr(pipe, "embed_images"):
                     raise ValueError(f"model {req.model!r} cannot score images")
                 qv, ntok = pipe.embed([req.query])

@@ -237,6 +237,8 @@ def text_state_dict(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     for k, v in sd.items():
         if k.startswith("model.language_model."):
             out["model." + k[len("model.language_model."):]] = v
+        elif k.startswith("language_model."):               # retrieval checkpoints: the bare backbone
+            out["model." + k[len("language_model."):]] = v
         elif k.startswith(("model.visual.", "visual.")):
             continue
         else:

@@ -125,3 +125,95 @@ class Gemma3Adapter:
                 out.append(t)
         rows = [i for a, b in spans for i in range(a, b)]
         return out, {"rows": rows, "vals": soft.reshape(-1, soft.shape[-1]), "bidir": spans}
+
+
+class ColQwenEmbedder:
+    """Late-interaction retrieval over page images (ColQwen2): a query or an image is run through the Qwen2-VL
+    decoder, every token's final hidden state is projected to a small vector and L2-normalised, and a query is
+    scored against a page by summing, over the query's tokens, the best dot product with any of the page's tokens
+    (the MaxSim kernel).  The reference's multimodal reranker does the same
+    (zig/pkg/inference/src/pipelines/multimodal_reranker_colqwen_impl.zig)."""
+
+    def __init__(self, model, adapter: Qwen2VLAdapter, proj_w: torch.Tensor, proj_b: Optional[torch.Tensor],
+                 tokenizer=None, page: int = 16):
+        self.model, self.adapter, self.tokenizer, self.page = model, adapter, tokenizer, page
+        self.proj_w, self.proj_b = proj_w, proj_b
+
+    @property
+    def dim(self) -> int:
+        return self.proj_w.shape[0]
+
+    def _hidden(self, ids: Sequence[int], soft: Optional[dict]) -> torch.Tensor:
+        from ..models.llama import StepBatch
+
+        m, dev, page = self.model, self.model.device, self.page
+        n = len(ids)
+        nblk = (n + page - 1) // page
+        kc = torch.zeros((m.n_layers, nblk, page, m.Hkv, m.D), dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros_like(kc)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        idx = torch.arange(n, dtype=torch.int32, device=dev)
+        b = StepBatch(i32(list(ids)), idx, idx.clone(), i32([0]), i32([n]), i32([n]),
+                      torch.arange(nblk, dtype=torch.int32, device=dev)[None], idx.clone(), n, 1)
+        if soft is not None:
+            b.embed_rows = torch.tensor(soft["rows"], dtype=torch.int64, device=dev)
+            b.embed_vals, b.pos3 = soft["vals"].to(dev), soft["pos3"].to(dev)
+        prev, m.return_hidden = m.return_hidden, True
+        try:
+            return m.forward(b, kc, vc)
+        finally:
+            m.return_hidden = prev
+
+    def _project(self, h: torch.Tensor) -> torch.Tensor:
+        from ..ops import dense as Dn
+
+        e = Dn.gemm_bf16(h.to(self.proj_w.dtype).contiguous(), self.proj_w, bias=self.proj_b,
+                         out_dtype=torch.float32).float()
+        return torch.nn.functional.normalize(e, dim=-1)
+
+    def embed_ids(self, ids: Sequence[int], images: Sequence[ImageLike] = ()) -> torch.Tensor:
+        """Prompt ids (one image placeholder per image) -> [tokens, dim] unit vectors."""
+        full, soft = self.adapter.expand(ids, list(images))
+        return self._project(self._hidden(full, soft))
+
+    def score(self, query: torch.Tensor, pages: Sequence[torch.Tensor]) -> List[float]:
+        """MaxSim of one query's token vectors against each page's."""
+        from ..ops import dense as Dn
+
+        if not pages:
+            return []
+        lens = torch.tensor([p.shape[0] for p in pages], dtype=torch.int32)
+        starts = (torch.cumsum(lens, 0) - lens).to(torch.int32)
+        dev = query.device
+        d = torch.cat(list(pages), 0).to(dev)
+        return Dn.maxsim(query.to(torch.bfloat16).contiguous(), d.to(torch.bfloat16).contiguous(), starts.to(dev),
+                         lens.to(dev)).float().cpu().tolist()
+
+    # query / page prompts as the retrieval checkpoints were trained: the page is one image followed by a fixed
+    # instruction, the query is the text followed by a few padding-like suffix tokens
+    page_prompt = "<|im_start|>user\n<|vision_start|><|image_pad|><|vision_end|>Describe the image.<|im_end|><|endoftext|>"
+    query_prefix, query_suffix = "Query: ", "<|endoftext|>" * 10
+
+    def rerank_pages(self, query: str, docs: Sequence[Tuple[Sequence[str], Sequence[ImageLike]]]):
+        """``docs`` = (texts, images) per document -> (one score per document: the best MaxSim over its parts,
+        prompt tokens spent)."""
+        if self.tokenizer is None:
+            raise RuntimeError("this model has no tokenizer")
+        enc = lambda t: list(self.tokenizer.encode_prompt(t, add_bos=False))
+        q_ids = enc(self.query_prefix + query + self.query_suffix)
+        qv = self.embed_ids(q_ids)
+        ntok, parts, owner = len(q_ids), [], []
+        for i, (texts, images) in enumerate(docs):
+            for t in texts:
+                ids = enc(self.query_prefix + t + self.query_suffix)
+                ntok += len(ids)
+                parts.append(self.embed_ids(ids)); owner.append(i)
+            for im in images:
+                v = self.embed_ids(enc(self.page_prompt), [im])
+                ntok += v.shape[0]
+                parts.append(v); owner.append(i)
+        raw = self.score(qv, parts)
+        scores = [float("-inf")] * len(docs)
+        for s_, i in zip(raw, owner):
+            scores[i] = max(scores[i], s_)
+        return [0.0 if s_ == float("-inf") else s_ for s_ in scores], ntok

@@ -250,3 +250,101 @@ def test_generator_with_image_adapter_and_chat_parts():
     with pytest.raises(ValueError):
         plain.generate("hi", sp, images=[img])
     assert len(plain.generate("hi", sp).token_ids) == 4
+
+
+def test_colqwen_token_embeddings_and_maxsim_match_transformers():
+    """ColQwen2: per-token projected, normalised decoder states for a page image and for a text query; the
+    late-interaction score equals the sum over query tokens of the best page-token dot product."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.pipelines.vlm import ColQwenEmbedder, Qwen2VLAdapter, VlmTokens
+
+    vlm_cfg, _ = _hf(5)
+    torch.manual_seed(5)
+    cfg = transformers.ColQwen2Config(vlm_config=vlm_cfg, embedding_dim=24)
+    hf = transformers.ColQwen2ForRetrieval(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.normal_(0, 0.05)
+    _round_text_linears(hf.vlm)
+    sd = {k[len("vlm."):] if k.startswith("vlm.") else k: v for k, v in hf.state_dict().items()}
+    model = LlamaModel.from_state_dict(LlamaConfig.from_hf(vlm_cfg.text_config.to_dict()), QV.text_state_dict(
+        {k: v for k, v in sd.items() if not k.startswith("embedding_proj_layer")}), device="cpu")
+    vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(vlm_cfg.vision_config.to_dict()), sd,
+                                                   device="cpu", dtype=torch.float32)
+
+    class FixedPatches(Qwen2VLAdapter):              # feed the same patches to both implementations
+        def encode_images(self, images):
+            return self.vision.forward(images[0][0], [images[0][1]]), [images[0][1]]
+
+    ad = FixedPatches(vision, VlmTokens(300, 302, 303))
+    emb = ColQwenEmbedder(model, ad, sd["embedding_proj_layer.weight"].float(), sd["embedding_proj_layer.bias"].float())
+    grid = (1, 4, 6)
+    patches = torch.randn(24, 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(6))
+    page_ids = [302, 300, 303, 7, 8]
+    got_page = emb.embed_ids(page_ids, [(patches, grid)])
+    full = [302] + [300] * 6 + [303, 7, 8]
+    with torch.no_grad():
+        want_page = hf(input_ids=torch.tensor([full]), pixel_values=patches[None], image_grid_thw=torch.tensor([grid]),
+                       attention_mask=torch.ones(1, len(full), dtype=torch.long),
+                       mm_token_type_ids=torch.tensor([[int(t == 300) for t in full]])).embeddings[0]
+        q_ids = [11, 12, 13, 14]
+        want_q = hf(input_ids=torch.tensor([q_ids]), attention_mask=torch.ones(1, 4, dtype=torch.long)).embeddings[0]
+    got_q = emb.embed_ids(q_ids)
+    assert got_page.shape == want_page.shape == (10, 24) and emb.dim == 24
+    assert float(torch.nn.functional.cosine_similarity(got_page, want_page, dim=-1).min()) > 0.98
+    assert float(torch.nn.functional.cosine_similarity(got_q, want_q, dim=-1).min()) > 0.98
+    other = torch.nn.functional.normalize(torch.randn(7, 24, generator=torch.Generator().manual_seed(8)), dim=-1)
+    s = emb.score(got_q, [got_page, other])
+    ref = [float((got_q.bfloat16().float() @ p.bfloat16().float().T).max(-1).values.sum()) for p in (got_page, other)]
+    assert s == pytest.approx(ref, abs=2e-2) and emb.score(got_q, []) == []
+
+
+def test_colqwen_rerank_pages_through_the_endpoint():
+    import base64
+    import io
+
+    pil = pytest.importorskip("PIL.Image")
+    import numpy as np
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.pipelines.vlm import ColQwenEmbedder, Qwen2VLAdapter, VlmTokens
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    hf_cfg, hf = _hf(6)
+    sd = hf.state_dict()
+    model = LlamaModel.from_state_dict(LlamaConfig.from_hf(hf_cfg.text_config.to_dict()), QV.text_state_dict(sd),
+                                       device="cpu")
+    vision = QV.Qwen2VLVisionModel.from_state_dict(QV.Qwen2VLVisionConfig.from_hf(hf_cfg.vision_config.to_dict()), sd,
+                                                   device="cpu", dtype=torch.float32)
+
+    class Tok(ByteTokenizer):
+        def encode_prompt(self, text, add_bos=True):
+            ids = []
+            for i, piece in enumerate(text.split("<|image_pad|>")):
+                if i:
+                    ids.append(300)
+                ids += self.encode(piece)
+            return ids
+
+    g = torch.Generator().manual_seed(0)
+    emb = ColQwenEmbedder(model, Qwen2VLAdapter(vision, VlmTokens(300), 28 * 28, 28 * 28 * 4),
+                          torch.randn(16, 128, generator=g) * 0.1, None, Tok(290))
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register("tiny-colqwen", "embedder", emb, emb.tokenizer)
+    c = TestClient(create_app(mgr))
+    buf = io.BytesIO()
+    pil.fromarray(np.random.default_rng(0).integers(0, 256, size=(40, 60, 3), dtype=np.uint8)).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    r = c.post("/ai/v1/rerank_multimodal", json={"model": "tiny-colqwen", "query": "invoice total", "documents": [
+        {"content": [{"type": "image_url", "image_url": {"url": url}}]},
+        {"content": [{"type": "text", "text": "invoice total"}, {"type": "image_url", "image_url": {"url": url}}]}]})
+    assert r.status_code == 200, r.text
+    d = r.json()["data"]
+    want, _ = emb.rerank_pages("invoice total", [([], [__import__("antfly_b200.pipelines.multimodal", fromlist=["x"])
+                                                       .decode_data_url(url)])])
+    assert d[0]["score"] == pytest.approx(want[0], abs=1e-3)
+    assert d[1]["score"] >= d[0]["score"] - 1e-6           # the second document also holds the query text itself
