@@ -152,3 +152,60 @@ def test_paged_attention_without_causal_mask(window):
     out = A.paged_attention(q, kc, vc, bt, qs, ql, kvl, max(q_lens), window=window, causal=False, decode=False)
     ref = R.paged_attention(q, kc, vc, bt, qs, ql, kvl, sliding_window=window, causal=False)
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+def _prefill_logits(model, cfg, ids, device, **extra):
+    from antfly_b200.models.llama import StepBatch
+
+    S, page, nblk = len(ids), 16, 4
+    kc = torch.zeros((cfg.num_hidden_layers, nblk, page, model.Hkv, cfg.head_dim), dtype=torch.bfloat16, device=device)
+    vc = torch.zeros_like(kc)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    idx = torch.arange(S, dtype=torch.int32, device=device)
+    mv = lambda v: tuple(t.to(device) if isinstance(t, torch.Tensor) else t for t in v) if isinstance(v, tuple) else (
+        v.to(device) if isinstance(v, torch.Tensor) else v)
+    b = StepBatch(i32(ids), idx, idx.clone(), i32([0]), i32([S]), i32([S]),
+                  torch.arange(nblk, dtype=torch.int32, device=device)[None], idx.clone(), S, 1,
+                  **{k: mv(v) for k, v in extra.items()})
+    return model.forward(b, kc, vc).float().cpu()
+
+
+def test_qwen2vl_decoder_with_image_tokens_on_gpu():
+    from antfly_b200.models import qwen2vl as QV
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    import tests.test_qwen2vl_cpu as T
+
+    hf_cfg, hf = T._hf(1)
+    sd = QV.text_state_dict(hf.state_dict())
+    cfg = LlamaConfig.from_hf(hf_cfg.text_config.to_dict())
+    grids = [(1, 4, 6)]
+    ids = [5, 6, 302] + [300] * 6 + [303, 7, 8, 9]
+    pos3, _ = QV.rope_index(ids, grids, 300)
+    soft = torch.randn(6, cfg.hidden_size, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    rows = torch.tensor([3, 4, 5, 6, 7, 8])
+    extra = dict(embed_rows=rows, embed_vals=soft, pos3=pos3)
+    want = _prefill_logits(LlamaModel.from_state_dict(cfg, dict(sd), device="cpu"), cfg, ids, "cpu", **extra)
+    got = _prefill_logits(LlamaModel.from_state_dict(cfg, dict(sd), device="cuda"), cfg, ids, "cuda", **extra)
+    assert float(torch.nn.functional.cosine_similarity(got, want, dim=-1).min()) > 0.99
+
+
+def test_gemma3_decoder_with_two_way_image_attention_on_gpu():
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.models.qwen2vl import text_state_dict
+    import tests.test_gemma3v_cpu as T
+
+    hf_cfg, hf = T._hf(1)
+    sd = text_state_dict(hf.state_dict())
+    cfg = LlamaConfig.from_hf(hf_cfg.text_config.to_dict())
+    ids = [2, 5, 6, 301] + [300] * 4 + [302, 7, 8, 9, 10, 11, 12]
+    soft = torch.randn(4, cfg.hidden_size, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    rows = torch.tensor([4, 5, 6, 7])
+
+    def extra(dev):
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        table = torch.arange(4, dtype=torch.int32, device=dev)[None]
+        return dict(embed_rows=rows, embed_vals=soft, bidir=(i32([4]), i32([4]), i32([8]), table, 4, rows.to(dev)))
+
+    want = _prefill_logits(LlamaModel.from_state_dict(cfg, dict(sd), device="cpu"), cfg, ids, "cpu", **extra("cpu"))
+    got = _prefill_logits(LlamaModel.from_state_dict(cfg, dict(sd), device="cuda"), cfg, ids, "cuda", **extra("cuda"))
+    assert float(torch.nn.functional.cosine_similarity(got, want, dim=-1).min()) > 0.99
