@@ -211,6 +211,15 @@ class ModelManager:
             if "max_len" in gcfg and "max_length" not in gcfg:
                 gcfg["max_length"] = gcfg["max_len"]
             pipe = GlinerPipeline(model, tok, GlinerConfig.from_files(gcfg, added))
+        elif task == "classifier" and cfg_d.get("model_type") == "layoutlmv3":
+            from ..models.layoutlmv3 import LayoutLMv3Config, LayoutLMv3Model
+            from ..pipelines.layout import DocumentClassifier
+
+            model = LayoutLMv3Model.from_state_dict(LayoutLMv3Config.from_hf(cfg_d), sd, device=self.device)
+            id2label = {int(k): v for k, v in (cfg_d.get("id2label") or {}).items()} or \
+                {i: f"LABEL_{i}" for i in range(model.cfg.num_labels)}
+            pipe = DocumentClassifier(model, tok, id2label, int(cfg_d.get("bos_token_id", 0) or 0),
+                                      int(cfg_d.get("eos_token_id", 2) or 2))
         elif task == "recognizer" and cfg_d.get("model_type") == "layoutlmv3":
             from ..models.layoutlmv3 import LayoutLMv3Config, LayoutLMv3Model
             from ..pipelines.layout import LayoutTokenClassifier

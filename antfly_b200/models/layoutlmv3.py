@@ -229,3 +229,14 @@ class LayoutLMv3Model:
                 t = t.to(w["cls.w"].dtype).contiguous()
             out.append(Dn.gemm_bf16(t, w["cls.w"], bias=w["cls.b"], out_dtype=torch.float32).float())
         return out
+
+    def sequence_logits(self, docs: Sequence[Document]) -> torch.Tensor:
+        """Document-level classification: the head (dense, tanh, projection) on each document's first token ->
+        fp32 [documents, num_labels] (zig/pkg/inference/src/pipelines/document_classification.zig)."""
+        w = self.w
+        if "cls.dense.w" not in w:
+            raise ValueError("this checkpoint has no document classification head")
+        first = torch.stack([h[0] for h in self.encode(docs)]).contiguous()
+        t = torch.tanh(Dn.gemm_bf16(first, w["cls.dense.w"], bias=w["cls.dense.b"], out_dtype=torch.float32).float())
+        return Dn.gemm_bf16(t.to(w["cls.w"].dtype).contiguous(), w["cls.w"], bias=w["cls.b"],
+                            out_dtype=torch.float32).float()

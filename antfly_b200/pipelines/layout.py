@@ -105,3 +105,29 @@ def group_entities(labels: Sequence[WordLabel]) -> List[dict]:
             out.append(cur)
     return [{"label": e["label"], "text": " ".join(e["words"]), "box": list(e["box"]),
              "score": sum(e["scores"]) / len(e["scores"])} for e in out]
+
+
+class DocumentClassifier:
+    """Page-level labels (invoice / letter / form ...) from a LayoutLMv3 sequence-classification checkpoint: the
+    first window of the page's words, their boxes and the page image decide."""
+
+    def __init__(self, model: LayoutLMv3Model, tokenizer, id2label: Dict[int, str], bos_id: int = 0, eos_id: int = 2):
+        self._tok = LayoutTokenClassifier(model, tokenizer, id2label, bos_id, eos_id)
+        self.model, self.id2label = model, id2label
+
+    def classify(self, words: Sequence[str], boxes: Sequence[Sequence[int]], image: Optional[torch.Tensor] = None,
+                 top_k: int = 1) -> List[dict]:
+        t = self._tok
+        px = page_pixels(image, self.model.cfg.input_size) if image is not None and self.model.cfg.visual_embed else None
+        ids, bx = [t.bos_id], [(0, 0, 0, 0)]
+        for w, b in zip(words, boxes):
+            sub = list(t.tok.encode(w))
+            if len(ids) + len(sub) + 1 > t.window:
+                break
+            ids += sub
+            bx += [tuple(int(v) for v in b)] * len(sub)
+        doc = Document(ids + [t.eos_id], bx + [(0, 0, 0, 0)], px)
+        pr = torch.softmax(self.model.sequence_logits([doc])[0].cpu(), -1)
+        top = torch.topk(pr, min(max(top_k, 1), pr.numel()))
+        return [{"label": self.id2label.get(int(i), str(int(i))), "score": float(s)}
+                for s, i in zip(top.values.tolist(), top.indices.tolist())]

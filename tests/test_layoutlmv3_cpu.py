@@ -131,3 +131,32 @@ def test_layout_endpoint():
     assert c.post("/ai/v1/layout", json={"model": "tiny-layout", "pages": [bad]}).status_code == 400
     far = {"words": ["x"], "boxes": [[0, 0, 5000, 10]]}
     assert c.post("/ai/v1/layout", json={"model": "tiny-layout", "pages": [far]}).status_code == 400
+
+
+def test_document_classification_head_matches_transformers():
+    from antfly_b200.pipelines.layout import DocumentClassifier
+    from antfly_b200.tokenizer.tokenizer import ByteTokenizer
+
+    torch.manual_seed(4)
+    hf_cfg, _ = _hf(4)
+    hf = transformers.LayoutLMv3ForSequenceClassification(hf_cfg).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias") or "rel_pos" in n:
+                p.normal_(0, 0.2)
+    model = LayoutLMv3Model.from_state_dict(LayoutLMv3Config.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                            dtype=torch.float32)
+    g = torch.Generator().manual_seed(1)
+    docs = [_doc(g, 7), _doc(g, 15)]
+    got = model.sequence_logits(docs)
+    for d, lg in zip(docs, got):
+        with torch.no_grad():
+            want = hf(input_ids=torch.tensor([d.ids]), bbox=torch.tensor([d.boxes]), pixel_values=d.pixels[None]).logits[0]
+        torch.testing.assert_close(lg, want, atol=5e-2, rtol=5e-2)
+    clf = DocumentClassifier(model, ByteTokenizer(290), {0: "invoice", 1: "letter", 2: "form", 3: "memo"})
+    out = clf.classify(["Total", "due"], [(10, 10, 60, 30), (70, 10, 100, 30)], top_k=2)
+    assert len(out) == 2 and out[0]["score"] >= out[1]["score"] and out[0]["label"] in ("invoice", "letter", "form", "memo")
+    token_only = LayoutLMv3Model.from_state_dict(LayoutLMv3Config.from_hf(_hf(5)[0].to_dict()), _hf(5)[1].state_dict(),
+                                                 device="cpu", dtype=torch.float32)
+    with pytest.raises(ValueError):
+        token_only.sequence_logits(docs)
