@@ -357,7 +357,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--max-queue-size", type=int); p.set_defaults(fn=cmd_run)
     p = sub.add_parser("export", help="safetensors checkpoint directory -> GGUF")
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
-    p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "q8_0", "q4_0"]); p.set_defaults(fn=cmd_export)
+    p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "q8_0", "q4_0", "i2_s"]); p.set_defaults(fn=cmd_export)
     p = sub.add_parser("compile-artifact", help="pack a checkpoint into the kernels' layout for fast loading")
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out"); p.add_argument("--device")
     p.set_defaults(fn=cmd_compile_artifact)

@@ -171,7 +171,7 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
     """Write a Llama-family Hugging Face state dict as a GGUF v3 file: 2-D projection weights in ``quant`` (f32,
     f16, q8_0, q4_0), norms and embeddings in f32 / f16; metadata keys are the ones :func:`llama_config_from_gguf`
     reads back.  Returns {tensor type id: count}."""
-    ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8}[quant.lower()]
+    ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8, "i2_s": 36}[quant.lower()]   # i2_s: BitNet ternary projections
     arch = config.get("model_type", "llama")
     md = {"general.architecture": arch, "general.name": str(config.get("_name_or_path", "model")),
           f"{arch}.block_count": int(config["num_hidden_layers"]),
@@ -189,6 +189,8 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
         if not isinstance(t, torch.Tensor) or not t.is_floating_point():
             continue
         quantisable = t.dim() == 2 and t.shape[1] % 32 == 0 and "embed_tokens" not in name and "norm" not in name
+        if ty == 36:      # ternary only where the model is ternary (the projections), whole 128-value blocks
+            quantisable = quantisable and name.endswith("_proj.weight") and t.numel() % 128 == 0
         tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 else 0)
         tensors[gguf_name(name)] = (tt, t.float())
         counts[tt] = counts.get(tt, 0) + 1

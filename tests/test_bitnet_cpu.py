@@ -123,3 +123,28 @@ def test_bitnet_gguf_names_config_and_decoded_weights(tmp_path):
     t, sc = bitnet_ternary(dec, None, False)
     m = float(w.abs().mean())
     assert abs(sc - m) < 1e-6 and torch.equal(t, (w / m).round().clamp(-1, 1))
+
+
+def test_bitnet_gguf_export_round_trip(tmp_path):
+    """Export the tiny BitNet to GGUF with ternary (I2_S) projections, read it back through the name / config
+    mapping, and get the same logits as from the original weights."""
+    from antfly_b200.formats import gguf as GG
+
+    hf_cfg, hf = _hf()
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    sd.pop("lm_head.weight", None)
+    d = hf_cfg.to_dict()
+    path = str(tmp_path / "bitnet.gguf")
+    counts = GG.export_llama_gguf(path, sd, d, quant="i2_s")
+    assert counts[36] == 2 * 7                                   # seven projections per layer, two layers
+    f = GG.GGUFFile(path)
+    back = {GG.hf_name(n): f.tensor(n) for n in f.tensors}
+    assert "model.layers.0.self_attn.attn_sub_norm.weight" in back
+    cfg_d = {k: v for k, v in GG.llama_config_from_gguf(f.metadata).items() if v is not None}
+    cfg = LlamaConfig.from_hf(cfg_d)
+    assert cfg.bitnet and cfg.num_hidden_layers == 2 and cfg.gate_act == "relu2"
+    ids = torch.randint(0, hf_cfg.vocab_size, (25,), generator=torch.Generator().manual_seed(5))
+    want = _run(LlamaModel.from_state_dict(LlamaConfig.from_hf(d), dict(sd), device="cpu"), cfg, ids, 24)
+    got = _run(LlamaModel.from_state_dict(cfg, back, device="cpu"), cfg, ids, 24)
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.999, cos                         # embeddings / norms went through fp16
