@@ -10,3 +10,7 @@ __version__ = "0.1.0"
 # Nothing here needs the multicast mapping, so ask the allocator not to create it (honoured where the installed
 # PyTorch knows the switch; set before the allocator's first use).
 _os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+# NCCL would likewise bind its own buffers to NVLink multicast objects (NVLS) for the bootstrap / baseline
+# collectives; the same hazard applies when a rank goes away, and nothing here depends on in-switch reduction.
+# A caller that wants NVLS back sets the variable before importing the package.
+_os.environ.setdefault("NCCL_NVLS_ENABLE", "0")

@@ -45,7 +45,7 @@ def _newest_header_mtime() -> float:
     m = 0.0
     for p in list((CSRC / "common").glob("*")) + list((CSRC / "host").glob("*.h")) + list(
         (CSRC / "kernels").glob("*.cuh")
-    ):
+    ) + list((CSRC / "include").glob("*.h")):
         m = max(m, p.stat().st_mtime)
     return m
 

@@ -72,9 +72,27 @@ def stream_ptr() -> ctypes.c_void_p:
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    """Device address of a tensor for a native launcher.  The launchers run on the calling THREAD's current device
+    and stream, so a CUDA tensor of another device is refused here: launching on GPU 0's stream with pointers
+    into GPU 1's memory would be an illegal-address fault.  Threads that serve a model enter
+    ``device_of(model_device)`` (or ``torch.cuda.device``) first."""
     if t is None:
         return ctypes.c_void_p(0)
+    if t.is_cuda and t.device.index != torch.cuda.current_device():
+        raise NativeError(f"tensor on cuda:{t.device.index} passed to a kernel launcher while this thread's current "
+                          f"device is cuda:{torch.cuda.current_device()}; wrap the call in device_of(tensor.device)")
     return ctypes.c_void_p(t.data_ptr())
+
+
+def device_of(device):
+    """Context manager that makes `device` current in this thread for the launches inside it (a no-op context for
+    CPU devices).  The current CUDA device is per host thread and starts at 0 in every new thread."""
+    import contextlib
+
+    d = torch.device(device) if device is not None else None
+    if d is None or d.type != "cuda":
+        return contextlib.nullcontext()
+    return torch.cuda.device(d)
 
 
 def status(clear: bool = True) -> int:
@@ -83,13 +101,32 @@ def status(clear: bool = True) -> int:
     return int(cuda().afb_status_read(1 if clear else 0))
 
 
-def poison_waits() -> int:
-    """Make every bounded kernel wait (running, queued or future) give up at once; see ``afb_poison_waits``.
-    For watchdogs and signal handlers: the GPU drains before the process goes away.  ``status()`` clears it."""
+def poison_waits(device: int | None = None) -> int:
+    """Make every bounded kernel wait (running, queued or future) on `device` give up at once; see
+    ``afb_poison_waits_on``.  For watchdogs and signal handlers: the GPU drains before the process goes away.
+    `device` is the CUDA device index whose kernels are to be drained; a timer or signal-helper thread must pass
+    it, because the current device is per thread and such a thread starts on device 0.  None = this thread's
+    current device.  ``status()`` clears the poison."""
     try:
-        return int(cuda().afb_poison_waits())
+        lib = cuda()
+        if device is None:
+            return int(lib.afb_poison_waits())
+        return int(lib.afb_poison_waits_on(ctypes.c_int(int(device))))
     except Exception:
         return -1
+
+
+# Longer than the cross-GPU wait limit compiled into the kernels (AFB_PEER_WAIT_NS, 2 s).
+DRAIN_SECONDS = 3.0
+
+
+def drain_for_exit(device: int | None = None) -> None:
+    """Called on the way out of a process that may have kernels in cross-GPU waits (watchdog, SIGTERM): poison
+    the waits of `device`, then give the GPU longer than one wait limit to run dry before the caller exits."""
+    import time
+
+    poison_waits(device)
+    time.sleep(DRAIN_SECONDS)
 
 
 _launch_counter = 0

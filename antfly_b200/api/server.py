@@ -34,6 +34,7 @@ from . import schemas as S
 from .cache import ResultCache
 from .metrics import Metrics
 from .model_manager import ModelManager, ModelNotFound
+from .._native import device_of as N_device_of
 
 
 class QueueTimeout(QueueFull):
@@ -149,7 +150,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             return r
         metrics.queue_depth.set(queue.waiting)
         try:
-            with gpu_lock:
+            # Handlers run on worker threads, whose current CUDA device starts at 0: select the manager's device
+            # for the kernel launches inside.
+            with gpu_lock, N_device_of(mgr.device):
                 out = fn()
             metrics.requests.labels(endpoint, "200").inc()
             return out

@@ -118,8 +118,18 @@ class FlatIndex:
         return torch.where(top_i >= 0, self.ids[(top_i - self.id_offset).clamp_min(0).long()],
                            torch.full_like(top_i, -1).to(self.ids.dtype))
 
-    def _search(self, queries: torch.Tensor, k: int, map_ids: bool = True) -> SearchResult:
+    def _search(self, queries: torch.Tensor, k: int, map_ids: bool = True, push=None,
+                safe: bool = False) -> SearchResult:
+        """push: peer targets of a sharded search (``MergeWorkspace.push_targets``); the select that ends the walk
+        then also stores the result into every rank's merge buffer.  In that mode a candidate-buffer overflow is
+        not repaired here: it travels with the pushed rows and the caller repeats the search with safe=True on
+        all ranks."""
         qb, row = self.prepare_queries(queries)
+        if push is not None:
+            assert self.ids is None, "sharded search pushes row ids; user id maps are applied after the merge"
+            map_ids = False
+        if safe:
+            return self._search_safe(qb, row, k, map_ids, push)
         nq = qb.shape[0]
         dev = self.device
         cap = max(self.cand_cap, 2 * k)
@@ -131,23 +141,26 @@ class FlatIndex:
         top_i = torch.full((nq, k), -1, dtype=torch.int32, device=dev)
         lo = 0
         chunk = min(self.n, min(self.seed_cols, cap))
-        pending = []  # chunks whose overflow flag still has to be checked
+        # One sticky overflow word for the whole walk (set by any chunk's select, never cleared).
+        ovf = torch.zeros((1,), dtype=torch.int32, device=dev) if dev.type == "cuda" else None
+        any_ovf = 0
         while lo < self.n:
             hi = min(self.n, lo + chunk)
             count.zero_()
             cn = self.col_norm[lo:hi] if self.col_norm is not None else None
             IX.score_filter(qb, self._rows(lo, hi), row, cn, self.form.scale, self.form.clamp_zero, thr, cand_val,
                             cand_idx, count, col_offset=lo + self.id_offset)
-            top_v, top_i, thr, ovf = IX.topk_select([(top_v, top_i, None, k), (cand_val, cand_idx, count, cap)], nq, k,
-                                                    k + cap)
-            pending.append((lo, hi, ovf))
+            top_v, top_i, thr, o = IX.topk_select([(top_v, top_i, None, k), (cand_val, cand_idx, count, cap)], nq, k,
+                                                  k + cap, overflow=ovf, push=push if hi == self.n else None)
+            if isinstance(o, int):
+                any_ovf |= o
             lo = hi
             chunk = max(chunk, lo)  # geometric growth: expected appends per query per chunk stay ~k
-        if any(int(o) if not isinstance(o, int) else o for _, _, o in pending):
+        if push is None and (any_ovf or (ovf is not None and int(ovf))):
             return self._search_safe(qb, row, k, map_ids)
         return SearchResult(top_v, self._map_ids(top_i) if map_ids else top_i)
 
-    def _search_safe(self, qb, row, k, map_ids: bool = True) -> SearchResult:
+    def _search_safe(self, qb, row, k, map_ids: bool = True, push=None) -> SearchResult:
         """Fallback when a candidate buffer overflowed (adversarially ordered data): fixed small chunks whose
         full score set fits the buffer."""
         nq = qb.shape[0]
@@ -166,7 +179,7 @@ class FlatIndex:
             IX.score_filter(qb, self._rows(lo, hi), row, cn, self.form.scale, self.form.clamp_zero, thr, cand_val,
                             cand_idx, count, col_offset=lo + self.id_offset)
             top_v, top_i, thr, _ = IX.topk_select([(top_v, top_i, None, k), (cand_val, cand_idx, count, cap)], nq, k,
-                                                  k + cap)
+                                                  k + cap, push=push if hi == self.n else None)
         return SearchResult(top_v, self._map_ids(top_i) if map_ids else top_i)
 
 

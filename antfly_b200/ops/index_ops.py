@@ -98,9 +98,16 @@ def assign_argmin(x, c, col_term, scale, row_term=None, want_best: bool = True):
     return assign, best
 
 
-def topk_select(sources: Sequence[tuple], n_queries: int, k: int, max_total: int, want_threshold: bool = True):
+def topk_select(sources: Sequence[tuple], n_queries: int, k: int, max_total: int, want_threshold: bool = True,
+                overflow: Optional[torch.Tensor] = None, push=None, wait=None, src_flags=None):
     """sources: (vals [Q, stride], idxs [Q, stride], counts [Q] or None, fixed_len).  Tensors may live on peer GPUs
-    (any address this device can read).  Returns (top_val [Q, k] ascending, top_idx [Q, k], thr [Q], overflow)."""
+    (any address this device can read).  Returns (top_val [Q, k] ascending, top_idx [Q, k], thr [Q], overflow).
+
+    overflow: an int32 [1] tensor to set (never cleared) instead of a fresh one -- one sticky word per search.
+    push: (vals, ids, flags, counters) ctypes pointer arrays of the ranks that also receive the result (the push
+    half of the sharded merge); the pushed flag is this call's overflow OR the sticky word's value on entry.
+    wait: (counter tensor, target) -- the merge half waits, bounded, for the counter before reading the sources.
+    src_flags: per source an int32 [Q] tensor whose non-zero entries are OR-ed into overflow."""
     dev = sources[0][0].device
     if dev.type != "cuda":
         vals, idxs = [], []
@@ -132,10 +139,17 @@ def topk_select(sources: Sequence[tuple], n_queries: int, k: int, max_total: int
     out_v = torch.empty((n_queries, k), dtype=torch.float32, device=dev)
     out_i = torch.empty((n_queries, k), dtype=torch.int32, device=dev)
     thr = torch.empty((n_queries,), dtype=torch.float32, device=dev) if want_threshold else None
-    ovf = torch.zeros((1,), dtype=torch.int32, device=dev)
-    rc = N.cuda().afb_topk_select(vals, idxs, counts, stride, fixed, _c_int(n), _c_int(n_queries), _c_int(k),
-                                  _c_int(max_total), N.ptr(out_v), N.ptr(out_i), N.ptr(thr), N.ptr(ovf),
-                                  N.stream_ptr())
+    ovf = overflow if overflow is not None else torch.zeros((1,), dtype=torch.int32, device=dev)
+    n_push = len(push[0]) if push is not None else 0
+    null = ctypes.c_void_p(0)
+    flags = PI(*[(f.data_ptr() if f is not None else 0) for f in src_flags]) if src_flags is not None else null
+    rc = N.cuda().afb_topk_select_x(
+        vals, idxs, counts, stride, fixed, _c_int(n), _c_int(n_queries), _c_int(k), _c_int(max_total), N.ptr(out_v),
+        N.ptr(out_i), N.ptr(thr), N.ptr(ovf), push[0] if push else null, push[1] if push else null,
+        push[2] if push else null, push[3] if push else null, _c_int(n_push),
+        N.ptr(overflow) if (push is not None and overflow is not None) else null,
+        N.ptr(wait[0]) if wait is not None else null, _c_int(int(wait[1]) if wait is not None else 0), flags,
+        N.stream_ptr())
     N.check(rc, "afb_topk_select")
     N.count_launch()
     return out_v, out_i, thr, ovf

@@ -372,6 +372,8 @@ class TieredStore:
             self._cv.notify_all()
 
     def _run(self) -> None:
+        if self.gpu:
+            torch.cuda.set_device(self.device)  # a new thread starts on device 0
         while True:
             with self._cv:
                 job = self._pop()

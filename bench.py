@@ -88,44 +88,22 @@ def _log(msg):
 
 
 def _dist_setup(n_gpus):
-    import faulthandler
-
     import torch
     import torch.distributed as dist
 
-    # A multi-rank run that stops making progress dumps every thread's Python stack and exits instead of
-    # sitting in a collective until the launcher's limit.
-    limit = int(os.environ.get("ANTFLY_B200_BENCH_WATCHDOG_S", "0"))
-
-    def _drain_and_exit(code):
-        # Never leave the process while kernels sit in cross-GPU waits: poison the waits so everything queued
-        # drains in microseconds, give the GPU a moment, then go.
-        try:
-            from antfly_b200 import _native as N
-
-            N.poison_waits()
-            time.sleep(1.0)
-        finally:
-            os._exit(code)
-
-    if limit > 0:
-        import threading
-
-        def _watchdog():
-            faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
-            _drain_and_exit(3)
-
-        t = threading.Timer(limit, _watchdog)
-        t.daemon = True
-        t.start()
-    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
-        import signal
-
-        signal.signal(signal.SIGTERM, lambda *_: _drain_and_exit(4))
+    import antfly_b200  # noqa: F401  (multicast-off defaults before NCCL / the symmetric allocator start)
+    from antfly_b200.parallel.launch import install_exit_guards
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # A run that stops making progress dumps every thread's Python stack, drains THIS rank's GPU (poison the
+    # bounded kernel waits, wait out one wait limit) and exits, instead of sitting in a collective until some outer
+    # limit kills it without warning; SIGTERM takes the same path.  The default leaves ample room for a cold
+    # start (first import on a fresh machine, an 8B model build, prefill).
+    limit = int(os.environ.get("ANTFLY_B200_BENCH_WATCHDOG_S", "600" if world > 1 else "0"))
+    if world > 1 or limit > 0:
+        install_exit_guards(local, watchdog_s=limit)
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -145,18 +123,12 @@ def _max_over_ranks(x: float, world: int) -> float:
 
 
 def _finish(world):
-    """Multi-rank exit: process-group teardown can block while captured graphs still hold NCCL work, so ranks
-    meet at a barrier, flush and leave without running destructors."""
+    """Multi-rank exit: GPU idle, every rank here, process group destroyed, then leave (see finish_ranks)."""
     if world <= 1:
         return
-    import torch
-    import torch.distributed as dist
+    from antfly_b200.parallel.launch import finish_ranks
 
-    torch.cuda.synchronize()
-    dist.barrier()
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+    finish_ranks()
 
 
 def _barrier(world):

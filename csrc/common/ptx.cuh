@@ -51,6 +51,30 @@ struct PeerDeadline {
   }
 };
 
+// Counters that other GPUs bump (monotonic; never reset, so there is no reset to race with).  The producer's
+// stores to this GPU's memory are ordered before its red.release; the consumer's ld.acquire orders its reads
+// after them.  The comparison is wrap-safe.
+__device__ __forceinline__ int peer_ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void peer_red_release_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded: false (status recorded) when the counter has not reached `target` within AFB_PEER_WAIT_NS, or at once
+// when an earlier cross-GPU wait of this file already expired or the host poisoned the waits.
+__device__ __forceinline__ bool peer_wait_counter(const int* p, int target) {
+  PeerDeadline dl;
+  for (uint32_t it = 0; it < AFB_SPIN_LIMIT; ++it) {
+    if (peer_ld_acquire(p) - target >= 0) return true;
+    if (dl.expired()) break;
+    __nanosleep(40);
+  }
+  status_set(kStatusPeerFlagTimeout);
+  return false;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

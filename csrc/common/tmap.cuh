@@ -64,7 +64,33 @@ inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 
 const char* last_error();
 void set_last_error(const char* fmt, ...);
 
+// One-time, PER-DEVICE kernel set-up.  The shared-memory opt-in of cudaFuncSetAttribute and the occupancy of a
+// kernel belong to the device that is current when they are asked for, so a process that drives several GPUs
+// has to repeat them on each.  `state` is a call-site (or template-instantiation) static.
+//
+// tmem_cols > 0 also checks the tensor-memory residency invariant of the tcgen05 kernels: they allocate their
+// TMEM columns BEFORE griddepcontrol.wait, i.e. possibly while CTAs of the preceding kernel still hold theirs,
+// and tcgen05.alloc blocks (without a bound) until columns are free.  That can only be safe if every CTA that
+// the SM can hold at once gets its columns: resident CTAs x columns <= 512.  A configuration that breaks it is
+// rejected here, at launch time, instead of deadlocking on the device.
+struct PerDeviceOnce {
+  unsigned char done[64];
+};
+int configure_kernel_once(PerDeviceOnce* state, const void* kernel, size_t dyn_smem_bytes, int threads,
+                          int tmem_cols, const char* name);
+// Number of SMs of the current device (cached per device).
+int device_sm_count();
+
 }  // namespace afb
+
+// Runs configure_kernel_once for `kernel` with a static of its own; returns -1 from the calling launcher on error.
+#define AFB_CONFIGURE_KERNEL(kernel, smem, threads, tmem_cols)                                              \
+  do {                                                                                                      \
+    static afb::PerDeviceOnce _afb_once = {};                                                               \
+    if (afb::configure_kernel_once(&_afb_once, reinterpret_cast<const void*>(kernel), (smem), (threads),    \
+                                   (tmem_cols), #kernel))                                                   \
+      return -1;                                                                                            \
+  } while (0)
 
 #define AFB_CHECK_CUDA(expr)                                                              \
   do {                                                                                    \

@@ -15,14 +15,25 @@
  *
  *   - The scratch is a file-scope `static __device__` array of AFB_NOALLOC_SCRATCH_BYTES (4 MiB + 32 KiB).  Every
  *     GPU that loads the library holds that much memory for it until the process exits.
- *   - A call is rejected (return value -1, message through afb_last_error()) when
+ *   - A call with num_splits > 1 is rejected (return value -1, message through afb_last_error()) when
  *     num_splits * T * Hq * (D + 1) * 4 bytes exceed the array, i.e. when num_splits * T * Hq > 8192 for D = 128.
+ *     A call with num_splits = 1 writes `out` directly, uses no scratch and has no such limit.
  *   - The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with that
- *     device current) and remembers it.  Make that first call outside of any stream capture.
- *   - No call allocates or frees: no cudaMalloc / cudaFree, no allocating library routine.
+ *     device current) and remembers it.  Make that first call outside of any stream capture.  Two host threads
+ *     that make the first call on a device at the same moment both do the lookup and store the same value; the
+ *     table is filled without a lock and that is harmless.
+ *   - The entry point itself calls no cudaMalloc / cudaFree and no allocating library routine.  The array is part
+ *     of the library's device image, though, and with lazy module loading (the CUDA default) the driver places
+ *     that image on a device when the library's first kernel or symbol is used there: the array's 4 MiB + 32 KiB
+ *     are taken from the device at THAT moment.  A process that sizes its own pool to the last byte should make
+ *     one warm-up call per device (any small valid call) before it commits the pool.
  *   - All calls on a device share the one array, and it keeps the previous call's contents.  Nothing in it has to
- *     start at zero: each call overwrites every slot it later reads.  Two calls whose kernels overlap on the GPU
- *     (different streams, no dependency between them) race on the array; serialise them.
+ *     start at zero: the split kernels write the partial rows of every token that belongs to a sequence before
+ *     the merge reads them.  Rows of `out` for token slots that belong to NO sequence (a padded batch, T larger
+ *     than the sum of q_lens) are unspecified: the merge fills them from whatever earlier calls left in the
+ *     array (a caller that indexes `out` through q_starts / q_lens never reads them).  Two calls
+ *     whose kernels overlap on the GPU (different streams, no dependency between them) race on the array;
+ *     serialise them.
  *
  * Inputs and outputs are the caller's, exactly as for afb_attention: q [T, Hq, D] bf16 with token pitch q_stride
  * elements, k_cache / v_cache [num_blocks, page, Hkv, D] bf16, block_tables [B, max_blocks] int32, q_starts /

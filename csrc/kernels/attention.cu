@@ -678,12 +678,8 @@ int launch_attn_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   const int smem_tiles = STAGES * 2 * kTileKeys * D * 2;
   const int smem_merge = SPLIT_KEYS ? (4 * 16 * D + 128) * 4 : 0;
   const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(flash_attn_kernel<D, PAGED, SPLIT_KEYS, STAGES>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
-  }
+  // 128 KiB covers every instantiation's request (the opt-in is a ceiling, not a reservation).
+  AFB_CONFIGURE_KERNEL((flash_attn_kernel<D, PAGED, SPLIT_KEYS, STAGES>), smem, 128, 0);
   AFB_CHECK_CUDA(launch_pdl(flash_attn_kernel<D, PAGED, SPLIT_KEYS, STAGES>, grid, dim3(128), smem, stream, p));
   return 0;
 }
@@ -702,24 +698,14 @@ int launch_decode_t_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   const int smem_tiles = STAGES * 2 * kTileKeys * D * 2;
   const int smem_merge = (4 * 8 * D + 64) * 4;
   const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(decode_attn_t_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        smem));
-    configured = true;
-  }
+  AFB_CONFIGURE_KERNEL((decode_attn_t_kernel<D, STAGES>), smem, 128, 0);
   AFB_CHECK_CUDA(launch_pdl(decode_attn_t_kernel<D, STAGES>, grid, dim3(128), smem, stream, p));
   return 0;
 }
 
 template <int D>
 int launch_decode_t(const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    AFB_CHECK_CUDA(cudaGetDevice(&dev));
-    AFB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  }
+  const int sms = device_sm_count();
   const long ctas = static_cast<long>(grid.x) * grid.y * grid.z;
   static int forced = -1;
   if (forced < 0) {
@@ -737,12 +723,7 @@ int launch_attn(const AttnParams& p, int B, int max_rows, cudaStream_t stream) {
   if constexpr (SPLIT_KEYS && PAGED) {
     if (max_rows <= 8 && !transposed_decode_disabled()) return launch_decode_t<D>(p, grid, stream);
     // A decode grid that leaves at most two CTAs per SM gets a deeper ring.
-    static int sms = 0;
-    if (!sms) {
-      int dev = 0;
-      AFB_CHECK_CUDA(cudaGetDevice(&dev));
-      AFB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = device_sm_count();
     const long ctas = static_cast<long>(grid.x) * grid.y * grid.z;
     if (ctas <= 2L * sms) return launch_attn_s<D, PAGED, SPLIT_KEYS, 3>(p, grid, stream);
   }
@@ -868,11 +849,16 @@ int afb_paged_decode_attention_noalloc(const void* q, long q_stride, const void*
   using namespace afb;
   if (B <= 0 || T <= 0) return 0;
   if (num_splits < 1) num_splits = 1;
-  if (Hkv <= 0 || Hq % Hkv != 0 || max_q_len * (Hq / Hkv) > 16) {
+  if (D != 64 && D != 128 && D != 256) {
+    set_last_error("afb_paged_decode_attention_noalloc: head_dim must be 64, 128 or 256 (got %d)", D);
+    return -1;
+  }
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv != 0 || max_q_len * (Hq / Hkv) > 16) {
     set_last_error("afb_paged_decode_attention_noalloc: needs q_len * (Hq / Hkv) <= 16 (decode shapes only)");
     return -1;
   }
-  const size_t rows = static_cast<size_t>(num_splits) * T * Hq;
+  // A single split writes `out` directly and touches no scratch, so no size limit applies to it.
+  const size_t rows = num_splits > 1 ? static_cast<size_t>(num_splits) * T * Hq : 0;
   const size_t o_bytes = (rows * D * sizeof(float) + 255) / 256 * 256;
   const size_t need = o_bytes + rows * sizeof(float);
   if (need > AFB_NOALLOC_SCRATCH_BYTES) {

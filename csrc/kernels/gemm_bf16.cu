@@ -227,12 +227,9 @@ int launch_gemm(const void* A, const void* B, GemmParams p, int lda, int ldb, in
   CUtensorMap ta, tb;
   if (make_tmap_2d(&ta, A, 2, p.M, p.K, static_cast<uint64_t>(lda) * 2, 128, 64, 3)) return -1;
   if (make_tmap_2d(&tb, B, 2, p.N, p.K, static_cast<uint64_t>(ldb) * 2, BN, 64, 3)) return -1;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        L::kTotal));
-    configured = true;
-  }
+  static_assert(static_cast<long>(BN) * 227 * 1024 <= 512L * L::kTotal,
+                "tensor-memory share of a CTA exceeds its shared-memory share");
+  AFB_CONFIGURE_KERNEL((gemm_bf16_kernel<BN, STAGES>), L::kTotal, 192, BN);
   dim3 grid((p.N + BN - 1) / BN, (p.M + 127) / 128, splits);
   gemm_bf16_kernel<BN, STAGES><<<grid, 192, L::kTotal, stream>>>(ta, tb, p);
   AFB_CHECK_CUDA(cudaGetLastError());

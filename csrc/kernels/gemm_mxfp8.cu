@@ -164,7 +164,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   const int sfx_tile = t0 / 128;
   const int sfx_row0 = t0 % 128;  // first row of this tile inside the atom
 
-  griddep_launch();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -183,6 +182,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Dependents may start launching only now that this CTA HOLDS its tensor memory.  The dependent grid begins
+  // once every CTA of this grid has passed this point (or exited), so no CTA of this grid can ever be left
+  // waiting in tcgen05.alloc (an unbounded hardware wait) for columns held by dependents that are themselves
+  // parked in griddepcontrol.wait until this grid completes.
+  griddep_launch();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -418,11 +422,14 @@ int launch_mx(const void* W, const void* X0, const void* X1, MxParams p, int spl
   if (make_tmap_2d(&tw, W, 1, p.N, p.K, static_cast<uint64_t>(p.K), 128, 128, 3)) return -1;
   if (make_tmap_2d(&tx0, X0, 1, p.M, p.K, static_cast<uint64_t>(p.K), BT, 128, 3)) return -1;
   if (make_tmap_2d(&tx1, TERMS == 2 ? X1 : X0, 1, p.M, p.K, static_cast<uint64_t>(p.K), BT, 128, 3)) return -1;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_mxfp8_kernel<BT, STAGES, TERMS>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
+  {
+    constexpr int D_COLS = BT < 32 ? 32 : BT;
+    constexpr int TMEM_COLS = D_COLS <= 32 ? 64 : (D_COLS <= 96 ? 128 : 256);  // as in the kernel
+    // Any mix of tcgen05 CTAs that shared memory lets an SM hold must also fit its 512 TMEM columns: every
+    // kernel's share of tensor memory is at most its share of shared memory.
+    static_assert(static_cast<long>(TMEM_COLS) * 227 * 1024 <= 512L * L::kTotal,
+                  "tensor-memory share of a CTA exceeds its shared-memory share");
+    AFB_CONFIGURE_KERNEL((gemm_mxfp8_kernel<BT, STAGES, TERMS>), L::kTotal, 192, TMEM_COLS);
   }
   dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
   if (p.mode == 4 && splits > 1) {

@@ -330,16 +330,11 @@ int launch_persistent(const void* A, const void* B, PersistParams p, int lda, in
   CUtensorMap ta, tb;
   if (make_tmap_2d(&ta, A, 2, p.M, p.K, static_cast<uint64_t>(lda) * 2, 128, 64, 3)) return -1;
   if (make_tmap_2d(&tb, B, 2, p.N, p.K, static_cast<uint64_t>(ldb) * 2, kPBN, 64, 3)) return -1;
-  static bool configured = false;
-  static int sm_count = 148;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kPSmem));
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    configured = true;
-  }
+  // The persistent kernel takes all 512 tensor-memory columns, so it must be alone on its SM: its shared
+  // memory has to exceed half of what an SM offers.
+  static_assert(kPSmem > 227 * 1024 / 2, "a CTA that allocates all of tensor memory must own the SM");
+  AFB_CONFIGURE_KERNEL((gemm_persistent_kernel<MODE>), kPSmem, 320, 512);
+  const int sm_count = device_sm_count();
   p.m_tiles = (p.M + 127) / 128;
   p.n_tiles = (p.N + kPBN - 1) / kPBN;
   long work = MODE == kArgmin ? p.m_tiles : static_cast<long>(p.m_tiles) * p.n_tiles;

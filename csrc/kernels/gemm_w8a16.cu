@@ -292,11 +292,11 @@ int launch_w8(const void* W, const void* S, const void* X, W8Params p, int ldx, 
   if (make_tmap_2d(&tw, W, 1, p.N, p.K, static_cast<uint64_t>(p.K), 128, 64, 0)) return -1;
   if (make_tmap_2d(&ts, S, 1, p.K / 32, p.N, static_cast<uint64_t>(p.N), 2, 128, 0)) return -1;
   if (make_tmap_2d(&tx, X, 2, p.M, p.K, static_cast<uint64_t>(ldx) * 2, BT, 64, 3)) return -1;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(gemm_w8a16_kernel<BT, RAW, ST, XST>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
+  {
+    constexpr int TMEM_COLS = BT < 32 ? 32 : BT;  // as in the kernel
+    static_assert(static_cast<long>(TMEM_COLS) * 227 * 1024 <= 512L * L::kTotal,
+                  "tensor-memory share of a CTA exceeds its shared-memory share");
+    AFB_CONFIGURE_KERNEL((gemm_w8a16_kernel<BT, RAW, ST, XST>), L::kTotal, 352, TMEM_COLS);
   }
   dim3 grid((p.N + 127) / 128, (p.M + BT - 1) / BT, splits);
   gemm_w8a16_kernel<BT, RAW, ST, XST><<<grid, 352, L::kTotal, stream>>>(tw, ts, tx, p);

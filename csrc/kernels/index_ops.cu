@@ -34,6 +34,21 @@ struct SelectParams {
   int* out_idx;    // [Q, k]
   float* out_thr;  // [Q] k-th best distance (+inf when fewer than k candidates), optional
   int* overflow;   // set to 1 when some query had more candidates than sort_cap
+  // Cross-GPU merge of a sharded search, push side (the tail of a shard's local search): the k best of query q
+  // are ALSO stored into every rank's merge buffer (slot of this rank) through peer pointers, with one flag
+  // word per query saying whether any candidate buffer of this shard overflowed, and every rank's arrival
+  // counter is bumped once per query CTA (red.release.sys after the stores).
+  float* push_val[8];  // rank o's [Q, k] value slot for this rank
+  int* push_idx[8];
+  int* push_flag[8];   // rank o's [Q] overflow flags for this rank
+  int* push_ready[8];  // rank o's arrival counter
+  int n_push;
+  const int* sticky_overflow;  // overflow word of the earlier selects of this search (they have completed)
+  // Merge side: wait (bounded) until this rank's own arrival counter has reached wait_target before reading the
+  // sources, which are then all in local memory; src_flag[s][q] != 0 is OR-ed into *overflow.
+  const int* wait_ready;
+  int wait_target;
+  const int* src_flag[kMaxSources];
 };
 
 __global__ void topk_select_kernel(SelectParams p) {
@@ -42,13 +57,27 @@ __global__ void topk_select_kernel(SelectParams p) {
   int* si = reinterpret_cast<int*>(sel_smem + static_cast<size_t>(p.sort_cap) * 4);
   __shared__ int s_total;
   const int q = blockIdx.x;
-  if (threadIdx.x == 0) s_total = 0;
+  __shared__ int s_ovf;
+  if (threadIdx.x == 0) {
+    s_total = 0;
+    s_ovf = 0;
+    // Every rank's list has landed in this GPU's memory once the counter reads the target.  On expiry the status
+    // word is set (the host sees it) and the kernel carries on over whatever is there, so it still terminates.
+    if (p.wait_ready) peer_wait_counter(p.wait_ready, p.wait_target);
+  }
   for (int i = threadIdx.x; i < p.sort_cap; i += blockDim.x) { sv[i] = INFINITY; si[i] = 0x7fffffff; }
   __syncthreads();
   for (int s = 0; s < p.n_src; ++s) {
+    if (p.src_flag[s] && threadIdx.x == 0 && p.src_flag[s][q] != 0) {
+      s_ovf = 1;
+      if (p.overflow) *p.overflow = 1;
+    }
     int n = p.counts[s] ? p.counts[s][q] : p.fixed_len[s];
     if (p.counts[s] && n > p.fixed_len[s]) {  // producer overflowed its buffer
-      if (threadIdx.x == 0 && p.overflow) *p.overflow = 1;
+      if (threadIdx.x == 0) {
+        s_ovf = 1;
+        if (p.overflow) *p.overflow = 1;
+      }
       n = p.fixed_len[s];
     }
     __shared__ int s_base;
@@ -59,7 +88,10 @@ __global__ void topk_select_kernel(SelectParams p) {
     const int* ix = p.idxs[s] + static_cast<size_t>(q) * p.stride[s];
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       if (base + i < p.sort_cap) { sv[base + i] = v[i]; si[base + i] = ix[i]; }
-      else if (p.overflow) *p.overflow = 1;
+      else {
+        s_ovf = 1;
+        if (p.overflow) *p.overflow = 1;
+      }
     }
     __syncthreads();
   }
@@ -87,6 +119,26 @@ __global__ void topk_select_kernel(SelectParams p) {
     p.out_idx[static_cast<size_t>(q) * p.k + i] = ok ? si[i] : -1;
   }
   if (p.out_thr && threadIdx.x == 0) p.out_thr[q] = (total >= p.k) ? sv[p.k - 1] : INFINITY;
+  // A rank whose status word carries a cross-GPU timeout pushes nothing more (its counters and its peers' no
+  // longer agree; rows of a later search must not complete a slower peer's older arrival target).
+  if (p.n_push && !(status_peek() & kStatusPeerFlagTimeout)) {
+    for (int o = 0; o < p.n_push; ++o) {
+      float* pv = p.push_val[o] + static_cast<size_t>(q) * p.k;
+      int* pi = p.push_idx[o] + static_cast<size_t>(q) * p.k;
+      for (int i = threadIdx.x; i < p.k; i += blockDim.x) {
+        const bool ok = i < total;
+        pv[i] = ok ? sv[i] : INFINITY;
+        pi[i] = ok ? si[i] : -1;
+      }
+    }
+    __syncthreads();  // every thread's peer stores are issued (and s_ovf is final) before the release below
+    if (threadIdx.x == 0) {
+      const int flag = (s_ovf || (p.sticky_overflow && *p.sticky_overflow)) ? 1 : 0;
+      for (int o = 0; o < p.n_push; ++o) p.push_flag[o][q] = flag;
+      __threadfence_system();
+      for (int o = 0; o < p.n_push; ++o) peer_red_release_add(p.push_ready[o], 1);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -256,11 +308,37 @@ extern "C" {
 
 // Sources: n_src lists; list s holds for query q `counts[s][q]` (or fixed_len[s] when counts[s] is null) pairs at
 // vals[s] + q*stride[s].  Pointers may be peer-GPU addresses.
+int afb_topk_select_x(const float* const* vals, const int* const* idxs, const int* const* counts,
+                      const long* stride, const int* fixed_len, int n_src, int n_queries, int k, int max_total,
+                      float* out_val, int* out_idx, float* out_thr, int* overflow, void* const* push_val,
+                      void* const* push_idx, void* const* push_flag, void* const* push_ready, int n_push,
+                      const int* sticky_overflow, const int* wait_ready, int wait_target,
+                      const int* const* src_flag, cudaStream_t stream);
+
 int afb_topk_select(const float* const* vals, const int* const* idxs, const int* const* counts, const long* stride,
                     const int* fixed_len, int n_src, int n_queries, int k, int max_total, float* out_val,
                     int* out_idx, float* out_thr, int* overflow, cudaStream_t stream) {
+  return afb_topk_select_x(vals, idxs, counts, stride, fixed_len, n_src, n_queries, k, max_total, out_val, out_idx,
+                           out_thr, overflow, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, nullptr,
+                           stream);
+}
+
+// As afb_topk_select, plus the two halves of the cross-GPU merge of a sharded search (see SelectParams):
+// n_push > 0 also stores each query's k best into n_push ranks' merge buffers and bumps their arrival counters;
+// wait_ready != null first waits, bounded, for this rank's own counter to reach wait_target.  A wait that runs
+// out sets the status word (afb_status_read) and the kernel finishes over what is there.
+int afb_topk_select_x(const float* const* vals, const int* const* idxs, const int* const* counts,
+                      const long* stride, const int* fixed_len, int n_src, int n_queries, int k, int max_total,
+                      float* out_val, int* out_idx, float* out_thr, int* overflow, void* const* push_val,
+                      void* const* push_idx, void* const* push_flag, void* const* push_ready, int n_push,
+                      const int* sticky_overflow, const int* wait_ready, int wait_target,
+                      const int* const* src_flag, cudaStream_t stream) {
   using namespace afb;
   if (n_queries <= 0) return 0;
+  if (n_push < 0 || n_push > 8) {
+    set_last_error("afb_topk_select: at most 8 ranks to push to (got %d)", n_push);
+    return -1;
+  }
   if (n_src < 1 || n_src > kMaxSources) {
     set_last_error("afb_topk_select: between 1 and %d sources (got %d)", kMaxSources, n_src);
     return -1;
@@ -271,19 +349,23 @@ int afb_topk_select(const float* const* vals, const int* const* idxs, const int*
     set_last_error("afb_topk_select: at most 16384 candidates per query fit the shared-memory sort (asked %d)", max_total);
     return -1;
   }
-  SelectParams p;
+  SelectParams p = {};
   for (int s = 0; s < n_src; ++s) {
     p.vals[s] = vals[s]; p.idxs[s] = idxs[s]; p.counts[s] = counts ? counts[s] : nullptr;
     p.stride[s] = stride[s]; p.fixed_len[s] = fixed_len[s];
+    p.src_flag[s] = src_flag ? src_flag[s] : nullptr;
   }
+  for (int o = 0; o < n_push; ++o) {
+    p.push_val[o] = reinterpret_cast<float*>(push_val[o]);
+    p.push_idx[o] = reinterpret_cast<int*>(push_idx[o]);
+    p.push_flag[o] = reinterpret_cast<int*>(push_flag[o]);
+    p.push_ready[o] = reinterpret_cast<int*>(push_ready[o]);
+  }
+  p.n_push = n_push; p.sticky_overflow = sticky_overflow; p.wait_ready = wait_ready; p.wait_target = wait_target;
   p.n_src = n_src; p.k = k; p.sort_cap = cap; p.out_val = out_val; p.out_idx = out_idx; p.out_thr = out_thr;
   p.overflow = overflow;
   const int smem = cap * 8;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8));
-    configured = true;
-  }
+  AFB_CONFIGURE_KERNEL(topk_select_kernel, 16384 * 8, 256, 0);
   topk_select_kernel<<<n_queries, 256, smem, stream>>>(p);
   AFB_CHECK_CUDA(cudaGetLastError());
   return 0;

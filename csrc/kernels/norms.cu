@@ -560,11 +560,7 @@ int afb_norm_tp(const void* x, const void* partials, int num_partials, long part
     return -1;
   }
   const size_t smem = static_cast<size_t>(H) * 4;
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
-    configured = true;
-  }
+  AFB_CONFIGURE_KERNEL(norm_kernel, 16384 * 4, 256, 0);
   const bool plain = x && !p.num_partials && !y_f32 && !q0 && !ag_world && !wait_flags && (y || sum_out);
   if (plain && rows >= 512 && H % 256 == 0 && H <= 1024) {
     const int grid = (rows + 7) / 8;

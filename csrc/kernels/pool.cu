@@ -30,6 +30,10 @@ struct PoolParams {
 
 __global__ void pool_kernel(PoolParams p) {
   __shared__ float red[32];
+  // Once a cross-GPU wait of this rank has timed out (or the host poisoned the waits) the hand-off counters of
+  // the ranks no longer agree: push nothing more, so that rows of a later step can never complete a slower
+  // peer's older arrival target.  The peers' own waits then run out and report.
+  if (p.n_peers && (status_peek() & kStatusPeerFlagTimeout)) p.n_peers = 0;
   const int b = blockIdx.x;
   const int start = p.starts[b], len = p.lens[b];
   const int H = p.H;
@@ -174,9 +178,24 @@ __global__ void splade_pool_kernel(const __nv_bfloat16* logits, const int* start
   out[static_cast<size_t>(b) * V + v] = m;
 }
 
+// Consumer side of a push-style hand-off: returns once `*counter` (bumped by other GPUs with red.release.sys after
+// their stores into this GPU's memory) has reached `target`, or records kStatusPeerFlagTimeout after the
+// cross-GPU wait limit and returns anyway.  Kernels launched after it on the stream see the pushed data.
+__global__ void peer_counter_wait_kernel(const int* counter, int target) {
+  if (threadIdx.x == 0) peer_wait_counter(counter, target);
+}
+
 }  // namespace afb
 
 extern "C" {
+
+// Stream-ordered bounded wait for an arrival counter in this GPU's memory that peers increment (monotonic,
+// wrap-safe compare).  On expiry the status word is set; the call itself always returns 0 once launched.
+int afb_peer_counter_wait(const int* counter, int target, cudaStream_t stream) {
+  afb::peer_counter_wait_kernel<<<1, 32, 0, stream>>>(counter, target);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 int afb_pool_gather(const void* h, const int* starts, const int* lens, const int* mask, float* out, int B, int H,
                     int mode, int normalize, void* const* peer_out, void* const* peer_ready, int n_peers,
@@ -226,11 +245,7 @@ int afb_maxsim(const void* q, int nq, const void* d, const int* starts, const in
     set_last_error("afb_maxsim: query of %d tokens x %d dims does not fit in shared memory", nq, D);
     return -1;
   }
-  static bool configured = false;
-  if (!configured) {
-    AFB_CHECK_CUDA(cudaFuncSetAttribute(maxsim_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    configured = true;
-  }
+  AFB_CONFIGURE_KERNEL(maxsim_kernel, 200 * 1024, 256, 0);
   maxsim_kernel<<<n_docs, 256, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q), nq,
                                                reinterpret_cast<const __nv_bfloat16*>(d), starts, lens, out, D);
   AFB_CHECK_CUDA(cudaGetLastError());

@@ -66,10 +66,19 @@ std::vector<StatusPoisoner>& poisoners() {
 }
 }  // namespace
 void register_status_poisoner(StatusPoisoner fn) { poisoners().push_back(fn); }
-int poison_all(int code) {
-  // A stream of its own, non-blocking with respect to the default stream, so the writes overtake whatever
-  // kernels are queued or spinning on the compute streams.
-  static cudaStream_t s = nullptr;
+int poison_all(int code, int device) {
+  // The current device belongs to the calling host thread: a watchdog or timer thread starts on device 0
+  // whatever the main thread selected, and the status words are per-device copies.  So the caller names the
+  // device (negative = keep the thread's current one) and the write goes to that device's words, on a stream of
+  // that device: non-blocking with respect to the default stream, so the writes overtake whatever kernels are
+  // queued or spinning on the compute streams.
+  if (device >= 0 && cudaSetDevice(device) != cudaSuccess) return -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  static cudaStream_t streams[64] = {nullptr};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  cudaStream_t& s = streams[dev];
   if (!s && cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return -1;
   int rc = 0;
   for (auto fn : poisoners()) rc |= fn(code, s);
@@ -87,6 +96,54 @@ bool pdl_enabled() {
 }
 
 const char* last_error() { return g_err; }
+
+int configure_kernel_once(PerDeviceOnce* state, const void* kernel, size_t dyn_smem_bytes, int threads,
+                          int tmem_cols, const char* name) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_error("%s: no current CUDA device", name);
+    return -1;
+  }
+  // Racing first calls from two host threads both do the same idempotent set-up and store the same byte.
+  if (state->done[dev]) return 0;
+  if (dyn_smem_bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dyn_smem_bytes));
+    if (e != cudaSuccess) {
+      set_last_error("%s: cannot opt in to %zu bytes of shared memory on device %d: %s", name, dyn_smem_bytes, dev,
+                     cudaGetErrorString(e));
+      return -1;
+    }
+  }
+  if (tmem_cols > 0) {
+    int resident = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, threads, dyn_smem_bytes);
+    if (e != cudaSuccess) {
+      set_last_error("%s: occupancy query failed: %s", name, cudaGetErrorString(e));
+      return -1;
+    }
+    if (resident * tmem_cols > 512) {
+      set_last_error("%s: %d resident CTAs x %d tensor-memory columns exceed the 512 columns of an SM; a CTA "
+                     "could block in tcgen05.alloc behind dependents parked in griddepcontrol.wait", name, resident,
+                     tmem_cols);
+      return -1;
+    }
+  }
+  state->done[dev] = 1;
+  return 0;
+}
+
+int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!sms[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
 
 void set_last_error(const char* fmt, ...) {
   va_list ap;
@@ -171,7 +228,11 @@ int afb_status_read(int clear) {
 // queued right now (a CUDA graph full of cross-GPU hand-offs whose peer will never answer): the timeout code is
 // written into each status word from a side stream.  Call before tearing a process down on a watchdog or signal,
 // so the GPU drains in microseconds and is idle when the process exits.  afb_status_read(1) clears it again.
-int afb_poison_waits() { return afb::poison_all(afb::kStatusPeerFlagTimeout); }
+int afb_poison_waits() { return afb::poison_all(afb::kStatusPeerFlagTimeout, -1); }
+// The same for a named device: for a thread other than the one that launched the work (watchdog timers, signal
+// helpers), whose current device is 0 by default.  Leaves `device` current in the calling thread.
+int afb_poison_waits_on(int device) { return afb::poison_all(afb::kStatusPeerFlagTimeout, device); }
+int afb_device_sm_count() { return afb::device_sm_count(); }
 
 // Programmatic dependent launch on (1) / off (0) for the kernels that support it; default on, or
 // ANTFLY_B200_PDL=0 in the environment.

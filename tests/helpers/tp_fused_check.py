@@ -1,10 +1,12 @@
 """Multi-rank check run under torchrun: the fused peer-memory tensor-parallel step (one-shot all-reduce form and
 reduce-scatter / all-gather form) must reproduce the NCCL-baseline step (same shards, same inputs), eagerly and
 under CUDA-graph replay, with no kernel wait timing out.  With one rank the pushes go to the rank's own buffers."""
-import os, sys, faulthandler, torch, torch.distributed as dist
+import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
-faulthandler.dump_traceback_later(120, exit=True)
+import antfly_b200  # first: sets the multicast-off defaults before NCCL or the symmetric allocator start
+from antfly_b200.parallel.launch import install_exit_guards, finish_ranks
 rank=int(os.environ['RANK']); world=int(os.environ['WORLD_SIZE']); local=int(os.environ['LOCAL_RANK'])
+install_exit_guards(local, watchdog_s=120)
 torch.cuda.set_device(local); dev=torch.device('cuda',local)
 dist.init_process_group('nccl', device_id=dev)
 from antfly_b200 import _native as N
@@ -73,4 +75,5 @@ for one_shot in (True, False):
     dist.barrier()
 ok = all_ok
 print(f"rank {rank}: TP_FUSED_CHECK {'OK' if ok else 'FAILED'}", flush=True)
-dist.barrier(); sys.stdout.flush(); os._exit(0)
+del gr
+finish_ranks()
