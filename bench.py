@@ -435,6 +435,37 @@ def bench_cpu(args):
     return 0
 
 
+def _reference_arm(args):
+    """The reference itself.  What of it can exist on this machine is its CUDA kernel file, compiled unchanged and
+    driven with its own launch geometry (baseline/ref_cuda.py): enough for the BERT-base embed and rerank
+    configurations.  Its CUDA backend has no RoPE, grouped-query or paged attention
+    (zig/pkg/inference/src/ops/cuda/cuda_compute.zig:1256-1267 return unsupportedCt()), no index code runs on a
+    GPU at all, and its Zig / Go host code does not build here, so the decode and kNN workloads have no reference
+    arm."""
+    if args.workload in ("embed", "rerank"):
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import ref_bench
+
+        return ref_bench.run(args, _clock_sampler, _clock_summary)
+    why = {"decode": "the reference's CUDA backend has no RoPE / grouped-query / paged attention (cuda_compute.zig:1256-1267 "
+                     "return unsupportedCt()) and admits no Llama-class model; its Zig and Go sources have no Python "
+                     "package (pip: 'neither setup.py nor pyproject.toml found') and neither toolchain is installed. "
+                     "--workload embed and rerank have a reference arm",
+           "knn": "the reference's vector index is CPU-only Zig / Go code that cannot be built here (no zig, no go)",
+           "cpu": "the reference's CPU backend is Zig and cannot be built here (no zig toolchain)"}
+    print(json.dumps({"impl": "reference", "unavailable": why.get(args.workload, why["decode"])}))
+    return 0
+
+
+def _torch_nccl_arm(args):
+    """A constructed stand-in, NOT the reference: the same models as plain PyTorch modules (cuBLAS matmul, SDPA)
+    with torch.distributed NCCL collectives -- the path "that only calls libraries"."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import torch_nccl
+
+    return torch_nccl.run(args, _clock_sampler, _clock_summary)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -456,11 +487,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the headline config)")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "reference is Zig/Go with no Python package (pip: 'neither setup.py nor "
-                                         "pyproject.toml found'); no zig/go toolchain here; its CUDA backend has no "
-                                         "RoPE/GQA/paged-attention ops, so Llama decode cannot run on it"}))
-        return 0
+        return _reference_arm(args)
+    if args.impl == "torch_nccl":
+        return _torch_nccl_arm(args)
     if args.workload == "decode":
         bench_decode(args)
     elif args.workload == "embed":
