@@ -288,3 +288,116 @@ def test_expert_parallel_moe_matches_single_rank(world):
         # same experts, same tokens; only the order of the fp32 sums over experts differs
         torch.testing.assert_close(logits, ref, atol=3e-2, rtol=3e-2)
         assert logits.argmax(-1).tolist() == ref.argmax(-1).tolist()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Elastic recovery: a 4-rank tensor-parallel generation loses a rank between steps; the survivors detect it by
+# heartbeat, re-form a 2-rank group, re-shard the weights from the checkpoint, re-prefill prompt + accepted tokens
+# and finish with the tokens a fresh 2-rank run produces.
+# ---------------------------------------------------------------------------------------------------------------
+_EL_PROMPTS = [[5, 6, 7, 8, 9, 10, 11], [21, 22, 23]]
+_EL_GEN = 8
+_EL_FAIL_STEP = 4
+
+
+def _elastic_engine_factory(cfg, sd):
+    from antfly_b200.models.llama import LlamaModel
+    from antfly_b200.parallel.comm import TpComm
+    from antfly_b200.runtime.engine import LLMEngine
+
+    def build(tp_rank, tp_size):
+        comm = TpComm(tp_rank, tp_size, torch.device("cpu")) if tp_size > 1 else None
+        model = LlamaModel.from_state_dict(cfg, sd, device="cpu", tp_rank=tp_rank, tp_size=tp_size, comm=comm)
+        return LLMEngine(model, num_blocks=32, page=16, max_batch=4, use_cuda_graph=False)
+
+    return build
+
+
+def _elastic_worker(uid, world, store_port, fail_uid, q):
+    from antfly_b200.parallel.health import ElasticGroup, GroupLost, elastic_generate
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    store = dist.TCPStore("127.0.0.1", store_port, is_master=False, timeout=__import__("datetime").timedelta(seconds=60))
+    group = ElasticGroup(store, uid, list(range(world)), backend="gloo", timeout_s=8.0, dead_after_s=1.5)
+    group.form()
+    cfg = _tp_cfg(4)
+    build = _elastic_engine_factory(cfg, _hf_llama_state(cfg))
+
+    def before_step(step_no, g):
+        if fail_uid is not None and uid == fail_uid and step_no == _EL_FAIL_STEP and g.world == world:
+            q.put(("left", uid, None))
+            q.close()
+            q.join_thread()   # the message is on its way before the process goes
+            os._exit(0)   # leaves between steps: nothing in flight; the others learn of it on the host
+
+    try:
+        res = elastic_generate(group, build, _EL_PROMPTS, SamplingParams(max_tokens=_EL_GEN, ignore_eos=True),
+                               before_step=before_step)
+        q.put(("done", uid, res))
+    except GroupLost:
+        q.put(("spare", uid, None))
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def _run_elastic(world, fail_uid):
+    import datetime
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    store = dist.TCPStore("127.0.0.1", port, is_master=True, timeout=datetime.timedelta(seconds=60),
+                          wait_for_workers=False)  # outlives every rank: hosted by the launcher
+    procs = [ctx.Process(target=_elastic_worker, args=(u, world, port, fail_uid, q)) for u in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    del store
+    return got
+
+
+def test_elastic_recovery_regroups_from_four_ranks_to_two_and_matches_a_fresh_two_rank_run():
+    got = _run_elastic(4, fail_uid=3)
+    kinds = sorted((k, u) for k, u, _ in got)
+    assert ("left", 3) in kinds
+    finished = {u: r for k, u, r in got if k == "done"}
+    spares = [u for k, u, _ in got if k == "spare"]
+    assert sorted(finished) == [0, 1] and spares == [2]          # three survivors: the group of two is ranks 0, 1
+    for res in finished.values():
+        assert res["regroups"] == 1 and res["world"] == 2 and res["members"] == [0, 1]
+    fresh = _run_elastic(2, fail_uid=None)
+    want = [r for k, u, r in fresh if k == "done"][0]["tokens"]
+    assert all(len(t) == _EL_GEN for t in want)
+    for res in finished.values():
+        assert res["tokens"] == want
+
+
+def test_largest_power_of_two_group_and_first_proposal_wins():
+    from antfly_b200.parallel.health import ElasticGroup, largest_power_of_two_group
+
+    assert largest_power_of_two_group([0, 1, 2, 4, 5, 6, 7]) == [0, 1, 2, 4]
+    assert largest_power_of_two_group([3, 1, 6]) == [1, 3]
+    assert largest_power_of_two_group([5]) == [5]
+
+    class FakeStore(dict):
+        def set(self, k, v): self[k] = v.encode() if isinstance(v, str) else v
+        def get(self, k): return self[k]
+        def check(self, ks): return all(k in self for k in ks)
+        def compare_set(self, k, expect, new):
+            if k not in self:
+                self[k] = new.encode()
+            return self[k]
+
+    store = FakeStore()
+    import time as _t
+    now = repr(_t.time())
+    for r in (0, 1, 2):
+        store.set(f"afb/hb/{r}", now)
+    a = ElasticGroup(store, 0, [0, 1, 2, 3], dead_after_s=5.0)
+    assert a.check() == [3]
+    store.set("afb/regroup/1", "1,2")       # another survivor's proposal got there first
+    b = ElasticGroup(store, 1, [0, 1, 2, 3], dead_after_s=5.0)
+    b.form = lambda: None
+    assert b.regroup() == [1, 2] and b.rank == 0 and b.world == 2 and b.epoch == 1
