@@ -364,6 +364,51 @@ class ModelManager:
             self._make_room_locked(keep=key)
         return lm
 
+    def get_generator(self, name: str, draft_model: Optional[str] = None,
+                      cache_dtype: Optional[str] = None) -> LoadedModel:
+        """The generator ``name`` as the request wants it served: with a separate draft model for speculative
+        decoding (``draft_model``, loaded like any generator) and / or a KV cache of another dtype
+        (``cache_dtype``: f16 / bf16 plain, fp8 / int8 / int4 / polar4 / turbo3 quantised, f32 on the CPU path).
+        A variant shares the base model's weights and gets an engine -- KV pool, scheduler, graphs -- of its own;
+        variants are cached and evicted like models.  Reference: per-request ``draft_model`` / ``cache_dtype``
+        (specs/openapi/inference/api.yaml:2299-2443; zig/pkg/inference/src/runtime/kv/pool.zig:26-35)."""
+        from ..runtime.kv_cache import KV_CODECS, KV_DTYPES
+
+        base = self.get(name, "generator")
+        kv = None if cache_dtype in (None, "", "bf16", "bfloat16", "f16") else cache_dtype
+        if kv is not None and kv not in KV_CODECS and kv not in KV_DTYPES:
+            raise ValueError(f"unknown cache_dtype {cache_dtype!r}")
+        if kv == "f32" and self.device.type == "cuda":
+            raise ValueError("cache_dtype 'f32' is not available on the GPU (the kernels read bf16 or quantised caches)")
+        if not draft_model and kv is None:
+            return base
+        key = f"generator:{name}|draft={draft_model or ''}|kv={kv or ''}"
+        now = self._clock()
+        with self._lock:
+            if key in self._models:
+                self._models.move_to_end(key)
+                self._models[key].last_used = now
+                return self._models[key]
+        eng0 = base.pipeline.engine
+        draft = None
+        if draft_model:
+            if draft_model == name:
+                raise ValueError("draft_model must differ from the model it drafts for")
+            draft = self.get(draft_model, "generator").pipeline.engine.model
+            if draft.cfg.vocab_size != eng0.model.cfg.vocab_size:
+                raise ValueError(f"draft model {draft_model!r} has a different vocabulary than {name!r}")
+        eng = LLMEngine(eng0.model, num_blocks=self.kv_blocks, page=eng0.page, max_batch=self.max_batch,
+                        use_cuda_graph=self.device.type == "cuda", eos_token_id=eng0.eos,
+                        prefix_cache=self.prefix_cache, kv_dtype=kv or "bf16", draft_model=draft)
+        pipe = Generator(eng, base.tokenizer, base.pipeline.template.source, add_bos=base.pipeline.add_bos,
+                         vlm=base.pipeline.vlm)
+        lm = LoadedModel(name, "generator", pipe, base.tokenizer, base.path,
+                         info=dict(base.info, draft_model=draft_model, cache_dtype=kv or "bf16"), last_used=now)
+        with self._lock:
+            self._models[key] = lm
+            self._make_room_locked(keep=key)
+        return lm
+
     # -- eviction ------------------------------------------------------------------------------------------
     def _drop_locked(self, key: str) -> None:
         self._models.pop(key, None)

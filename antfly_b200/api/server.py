@@ -451,7 +451,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                               min_p=req.min_p, repetition_penalty=req.repetition_penalty,
                               frequency_penalty=req.frequency_penalty, presence_penalty=req.presence_penalty,
                               stop_token_ids=stops, seed=req.seed, grammar=grammar,
-                              cache_compaction_ratio=req.cache_compaction_ratio)
+                              cache_compaction_ratio=req.cache_compaction_ratio, speculative_k=req.speculative_k)
 
     async def generate(request: Request):
         req, bad = await parse(request, S.GenerateRequest)
@@ -497,10 +497,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     msgs[0] = dict(msgs[0], content=(msgs[0].get("content") or "") + "\n\n" + decl)
                 else:
                     msgs.insert(0, {"role": "system", "content": decl})
-        if req.cache_dtype not in (None, "bf16", "f16"):
-            # engines are built with a bf16 cache; a per-request dtype cannot be honoured after the fact
-            return _err(400, "invalid_request", f"cache_dtype {req.cache_dtype!r} is not supported by this server "
-                                                "(KV cache is bf16)")
+        if req.cache_dtype == "f32" and mgr.device.type == "cuda":
+            return _err(400, "invalid_request", "cache_dtype 'f32' is not available on the GPU (the kernels read "
+                                                "bf16 or quantised caches); use f16, fp8, int8 or int4")
         if req.grammar or (req.response_format or {}).get("type") == "json_schema":
             try:  # reject a malformed grammar / unsupported schema before any work is queued
                 from ..runtime.grammar import GbnfGrammar
@@ -517,7 +516,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 return _err(400, "invalid_request", str(e))
         if not req.stream:
             def work():
-                lm = mgr.get(req.model, "generator")
+                lm = mgr.get_generator(req.model, req.draft_model, req.cache_dtype)
                 out = lm.pipeline.generate(msgs, sampling_from(req, lm.tokenizer))
                 metrics.tokens.labels("generate", "prompt").inc(out.prompt_tokens)
                 metrics.tokens.labels("generate", "completion").inc(out.completion_tokens)
@@ -565,7 +564,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         def worker():
             def work():
-                lm = mgr.get(req.model, "generator")
+                lm = mgr.get_generator(req.model, req.draft_model, req.cache_dtype)
                 loop.call_soon_threadsafe(q.put_nowait, emit_start())
                 parser = None
                 if tool_fmt is not None:

@@ -8,7 +8,7 @@
   embed     embed texts                      --model --text ... [--dimensions N] [--print-timing]
   rerank    score documents against a query  --model --query Q --doc ... 
   generate  generate text                    --model --prompt P [--max-tokens --temperature --top-k --top-p --min-p
-                                             --repetition-penalty --speculative-k --draft-layers --cache-dtype
+                                             --repetition-penalty --speculative-k --draft-layers --draft-model --cache-dtype
                                              --prefill-chunk-size --kv-budget-mb --host-budget-mb --backend-budget-mb
                                              --scratch-budget-mb --combined-budget-mb --image --no-bos --no-chat-template
                                              --print-timing --print-token-ids --print-finish-reason]
@@ -136,9 +136,21 @@ def cmd_generate(args) -> int:
 
     mgr = _manager(args)
     lm = _get(mgr, args.model, "generator")
+    if args.draft_model or args.cache_dtype not in (None, "bf16", "f16"):
+        # --draft-model: a second generator drafts for speculative decoding; --cache-dtype: KV cache codec
+        try:
+            lm = mgr.get_generator(args.model, args.draft_model, args.cache_dtype)
+        except ValueError as e:
+            print(str(e), file=sys.stderr)
+            return 2
     gen = lm.pipeline
     eng = gen.engine
+    if args.draft_model:
+        eng.spec_k = args.speculative_k
     if args.draft_layers:
+        if args.draft_model:
+            print("--draft-layers and --draft-model are alternatives", file=sys.stderr)
+            return 2
         eng.draft = eng.model.draft_view(args.draft_layers)
         eng.spec_k = args.speculative_k
     if args.no_bos:
@@ -398,7 +410,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--top-k", type=int, default=0); p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--min-p", type=float, default=0.0); p.add_argument("--repetition-penalty", type=float, default=1.0)
     p.add_argument("--seed", type=int); p.add_argument("--speculative-k", type=int, default=4)
-    p.add_argument("--draft-layers", type=int, default=0); p.add_argument("--cache-dtype", default="bf16")
+    p.add_argument("--draft-layers", type=int, default=0)
+    p.add_argument("--draft-model", help="a second generator that drafts tokens for speculative decoding")
+    p.add_argument("--cache-dtype", default="bf16",
+                   choices=["bf16", "f16", "f32", "fp8", "int8", "int4", "polar4", "turbo3"])
     p.add_argument("--prefill-chunk-size", type=int, default=2048); p.add_argument("--kv-budget-mb", type=int, default=0)
     p.add_argument("--cache-compaction-ratio", type=float,
                    help="after prefill keep this fraction of the KV cache (attention-matching compaction)")

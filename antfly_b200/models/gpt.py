@@ -390,7 +390,7 @@ class GptModel:
                                         scale, window, alibi=self._alibi).to(q.dtype)
             else:
                 ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                        b.max_q_len, scale=scale, window=window, num_splits=b.attn_splits,
+                                        b.max_q_len, max_kv=b.max_kv, scale=scale, window=window, num_splits=b.attn_splits,
                                         scratch=attn_scratch)
             if cfg.parallel_residual:
                 # x + attn(ln1 x) + mlp(ln2 x): both branches read the same x

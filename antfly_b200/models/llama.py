@@ -169,6 +169,7 @@ class StepBatch:
     logit_rows: torch.Tensor    # [R] token rows whose logits are wanted
     max_q_len: int = 1
     attn_splits: int = 1
+    max_kv: int = 0             # largest kv_lens entry when the host knows it (0: unknown); bounds page expansion
     # multimodal prompts: rows of this step whose embedding is a given vector instead of a table row, and three
     # rotary position streams [3, T] (time / row / column) in place of ``positions``
     embed_rows: Optional[torch.Tensor] = None
@@ -464,7 +465,7 @@ class LlamaModel:
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
                                 q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=self.act_terms)
             o_w: Q.Fp8Weight = w[p + "o"]
             S = fz.gemm_push(ctx, o_w, T, pick_split_k(o_w.out_features, o_w.in_features, T))
@@ -501,7 +502,7 @@ class LlamaModel:
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
                                 q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=mxt)
             o_w: Q.Fp8Weight = w[p + "o"]
             fz.gemm_bcast(ctx, o_w, T, pick_split_k(o_w.out_features, o_w.in_features, T), 0)
@@ -706,13 +707,13 @@ class LlamaModel:
                                 freq_scale=fscale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
                                 norm_eps=eps, norm_plus_one=gp1)
             ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, scale=cfg.attn_scale or None, window=window,
+                                    b.max_q_len, max_kv=b.max_kv, scale=cfg.attn_scale or None, window=window,
                                     num_splits=b.attn_splits, scratch=attn_scratch)
             if b.bidir is not None:
                 # second pass over the image runs without the causal mask (their keys are already in the cache);
                 # its rows replace the causal ones
                 bs, bl, bk, bt, bmax, brow = b.bidir
-                both = A.paged_attention(q, k_cache_l, v_cache_l, bt, bs, bl, bk, bmax, scale=cfg.attn_scale or None,
+                both = A.paged_attention(q, k_cache_l, v_cache_l, bt, bs, bl, bk, bmax, max_kv=b.max_kv, scale=cfg.attn_scale or None,
                                          window=window, causal=False, decode=False)
                 ctx.index_copy_(0, brow, both.index_select(0, brow))
             ctx = ctx.view(T, Hq * D)
@@ -792,7 +793,7 @@ class LlamaModel:
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
                                 q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, window=cfg.sliding_window, num_splits=b.attn_splits,
+                                    b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=mxt)
             o_w: Q.Fp8Weight = w[p + "o"]
             parts = self._reduce(self._linear(ctx if mxt else ctx.view(T, Hq * D), o_w, T, partials=True,

@@ -71,15 +71,23 @@ class PagedAttnScratch:
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, max_q_len: int,
                     scale: Optional[float] = None, window: int = 0, decode: Optional[bool] = None,
                     num_splits: int = 1, scratch: Optional[PagedAttnScratch] = None,
-                    out: Optional[torch.Tensor] = None, mx_terms: int = 0, causal: bool = True):
+                    out: Optional[torch.Tensor] = None, mx_terms: int = 0, causal: bool = True, max_kv: int = 0):
     """Causal attention (``causal=False``: every query row of a sequence sees all of its ``kv_lens`` keys, within a
     two-sided ``window`` if one is set) of packed query tokens q [T, Hq, D] against the paged cache
     k_cache / v_cache [num_blocks, page, Hkv, D].  ``decode`` selects the split-keys organisation (<= 16
     (position, head-in-group) rows per KV head); default: when max_q_len * group <= 16.
+    ``k_cache`` / ``v_cache`` may also be :class:`antfly_b200.ops.kv_quant.CodecLayer` objects (a cache kept in a
+    quantised codec); ``max_kv`` (the largest ``kv_lens`` entry, known on the host) then bounds the pages that a
+    prefill step expands.
     ``mx_terms`` 1 or 2 returns the context rows [T, Hq * D] as MX-fp8 activations
     (:class:`antfly_b200.ops.quant.MxAct`) for the output projection: emitted by the split merge kernel when the
     KV range is split, by a quantisation pass otherwise."""
     T, Hq, D = q.shape
+    from .kv_quant import CodecLayer
+
+    if isinstance(k_cache, CodecLayer):
+        return _paged_attention_codec(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, max_q_len, scale,
+                                      window, decode, num_splits, scratch, out, mx_terms, causal, max_kv)
     page, Hkv = k_cache.shape[1], k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
@@ -91,8 +99,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
             return Q.quantize_mx(y.reshape(T, Hq * D), terms=mx_terms)
         return y
     if k_cache.dtype != torch.bfloat16:
-        raise NotImplementedError("the GPU attention kernels read a bf16 KV cache; an fp8 cache is supported on the "
-                                  "write side and on the CPU path only")
+        raise NotImplementedError("this entry reads a bf16 KV cache; quantised caches are passed as CodecLayer "
+                                  "objects (ops.kv_quant)")
     G = Hq // Hkv
     if decode is None:
         decode = max_q_len * G <= 16
@@ -132,6 +140,73 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
     return out
 
 
+def _paged_attention_codec(q, kl, vl, block_tables, q_starts, q_lens, kv_lens, max_q_len, scale, window, decode,
+                           num_splits, scratch, out, mx_terms, causal, max_kv):
+    """Attention over a cache kept in a quantised codec (fp8 / int8 / int4 / polar4 / turbo3).
+
+    * One new token per sequence: keys are scored straight from their codes.  An fp8 cache on the GPU takes the
+      tensor-core decode kernel with the codes expanded in shared memory (``afb_attention_kv8``); the other codecs
+      take the code-scoring kernel of ``attention_kvq.cu``.
+    * Several query rows per sequence (prefill chunks, speculative verification): the pages the step can see are
+      expanded to a bf16 scratch with a block table of its own and the bf16 kernels run on that; the cache itself
+      stays compressed.  (turbo3 keys expand to their 3-bit base values.)
+    """
+    from . import kv_quant as KQ
+
+    T, Hq, D = q.shape
+    Hkv, page, codec = kl.Hkv, kl.page, kl.codec
+    B = q_starts.numel()
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    G = Hq // Hkv
+    single = max_q_len == 1 and T == B and causal
+    ctx = None
+    if single and q.is_cuda and codec == "fp8" and G <= 8 and D in (64, 128, 256):
+        mx = None
+        if mx_terms and num_splits > 1 and (Hq * D) % 128 == 0:
+            from . import quant as Q
+
+            mx = Q.new_mx(T, Hq * D, mx_terms, q.device)
+        elif out is None:
+            out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+        part_o = part_lse = None
+        if num_splits > 1:
+            if scratch is None:
+                scratch = PagedAttnScratch(T, Hq, D, num_splits, q.device)
+            part_o, part_lse = scratch.part_o, scratch.part_lse
+        rc = N.cuda().afb_attention_kv8(
+            N.ptr(q), _c_long(q.stride(0)), N.ptr(kl.data), N.ptr(vl.data), N.ptr(block_tables),
+            _c_int(block_tables.shape[1]), _c_int(page), N.ptr(q_starts), N.ptr(q_lens), N.ptr(kv_lens), N.ptr(out),
+            _c_long(out.stride(0) if out is not None else Hq * D), N.ptr(part_o), N.ptr(part_lse), _c_int(B),
+            _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D), _c_int(1), _c_int(window), _c_float(scale), _c_float(1.0),
+            _c_float(1.0), _c_int(num_splits), N.ptr(mx.q0 if mx else None), N.ptr(mx.q1 if mx else None),
+            N.ptr(mx.sf0 if mx else None), N.ptr(mx.sf1 if mx else None), N.stream_ptr())
+        N.check(rc, "afb_attention_kv8")
+        N.count_launch(2 if num_splits > 1 else 1)
+        if mx is not None:
+            return mx
+        ctx = out
+    elif single and (not q.is_cuda or G <= 8):
+        ctx = KQ.decode_attention(codec, q.contiguous(), kl.data, vl.data, block_tables, kv_lens, Hkv, scale,
+                                  window=window, out=out)
+    if ctx is None:
+        nb = block_tables.shape[1]
+        if max_kv > 0:
+            nb = min(nb, (max_kv + page - 1) // page)
+        tab = block_tables[:, :nb]
+        rows = (tab.long().clamp_min(0) * page)[:, :, None] + torch.arange(page, device=tab.device)[None, None, :]
+        rows = rows.reshape(-1).int()
+        kb = kl.expand(rows).view(B * nb, page, Hkv, D)
+        vb = vl.expand(rows).view(B * nb, page, Hkv, D)
+        new_tab = torch.arange(B * nb, dtype=torch.int32, device=tab.device).view(B, nb)
+        return paged_attention(q, kb, vb, new_tab, q_starts, q_lens, kv_lens, max_q_len, scale, window, decode,
+                               num_splits, scratch, out, mx_terms, causal)
+    if mx_terms:
+        from . import quant as Q
+
+        return Q.quantize_mx(ctx.reshape(T, Hq * D), terms=mx_terms)
+    return ctx
+
+
 def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cache, Hq: int, Hkv: int, D: int,
                   theta: float, *, partials: Optional[torch.Tensor] = None, bias=None, rope_dim: Optional[int] = None,
                   half_split: bool = True, freq_scale: float = 1.0, q_norm_w=None, k_norm_w=None,
@@ -142,6 +217,24 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
     src = qkv if qkv is not None else partials[0]
     T = src.shape[0]
     rd = rope_dim or D
+    from .kv_quant import CodecLayer
+
+    if isinstance(k_cache, CodecLayer):
+        if k_cache.codec == "fp8" and src.is_cuda:
+            # e4m3 rows are exactly the [Hkv, D] byte layout the kernel's fp8 store writes: no staging
+            k_cache, v_cache = k_cache.data, v_cache.data
+        else:
+            # rotate / normalise into a bf16 staging "cache" of T single-token rows, then encode into the codec
+            ks = torch.zeros((1, T, Hkv, D), dtype=torch.float32 if not src.is_cuda else torch.bfloat16,
+                             device=src.device)
+            vs = torch.zeros_like(ks)
+            q_res = rope_kv_write(qkv, positions, torch.arange(T, dtype=torch.int32, device=src.device), ks, vs, Hq,
+                                  Hkv, D, theta, partials=partials, bias=bias, rope_dim=rope_dim,
+                                  half_split=half_split, freq_scale=freq_scale, q_norm_w=q_norm_w, k_norm_w=k_norm_w,
+                                  norm_eps=norm_eps, norm_plus_one=norm_plus_one, q_out=q_out)
+            k_cache.write(slots, ks[0])
+            v_cache.write(slots, vs[0])
+            return q_res
     if not src.is_cuda:
         row = (qkv.float() if qkv is not None else 0) + (partials.float().sum(0) if partials is not None else 0)
         if bias is not None:

@@ -238,3 +238,89 @@ class QuantizedPagedKV:
 
     def bytes_per_token(self) -> int:
         return self.k.shape[2] + self.v.shape[2]
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Codec caches inside the generation engine
+# ----------------------------------------------------------------------------------------------------------
+def expand_rows(codec: str, cache_rows: torch.Tensor, row_idx: torch.Tensor, heads: int, D: int,
+                value: bool = False, scale: float = 1.0) -> torch.Tensor:
+    """Decodes code rows ``cache_rows[row_idx]`` (cache_rows uint8 [N, row_bytes]) to bf16 [n, heads, D]."""
+    n = row_idx.numel()
+    if not cache_rows.is_cuda:
+        rows = cache_rows[row_idx.long().clamp_min(0)]
+        return (decode_rows(codec, rows, heads, D, value) * scale).to(torch.bfloat16)
+    out = torch.empty((n, heads, D), dtype=torch.bfloat16, device=cache_rows.device)
+    rc = N.cuda().afb_kvq_expand_rows(N.ptr(cache_rows), N.ptr(row_idx.int().contiguous()), N.ptr(out), _c_long(n),
+                                      _c_long(cache_rows.shape[0]), _c_int(heads), _c_int(D), _c_int(CODECS[codec]),
+                                      _c_int(1 if value else 0), _c_float(scale), N.stream_ptr())
+    N.check(rc, "afb_kvq_expand_rows")
+    N.count_launch()
+    return out
+
+
+class CodecLayer:
+    """One layer's keys (or values) of a paged cache kept in a quantised codec: bytes [num_blocks, page, row_bytes].
+    The attention and KV-write wrappers (``ops.attention``) recognise this type where they otherwise take a
+    bf16 cache tensor [num_blocks, page, Hkv, D]."""
+
+    def __init__(self, codec: str, data: torch.Tensor, Hkv: int, D: int, value: bool):
+        self.codec, self.data, self.Hkv, self.D, self.value = codec, data, Hkv, D, value
+
+    @property
+    def device(self):
+        return self.data.device
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.data.is_cuda
+
+    @property
+    def page(self) -> int:
+        return self.data.shape[1]
+
+    @property
+    def num_blocks(self) -> int:
+        return self.data.shape[0]
+
+    def rows(self) -> torch.Tensor:
+        return self.data.view(-1, self.data.shape[2])
+
+    def write(self, slots: torch.Tensor, x: torch.Tensor) -> None:
+        """x [T, Hkv, D]; slots [T] = block * page + offset.  A negative slot (a padded token) is sent to the spare
+        row behind the last block, so no data-dependent filtering -- and no host synchronisation -- is needed."""
+        spare = self.data.shape[0] * self.data.shape[1] - 1
+        s = torch.where(slots >= 0, slots, torch.full_like(slots, spare)).long()
+        self.rows().index_copy_(0, s, encode_rows_torch(self.codec, x, value=self.value))
+
+    def expand(self, row_idx: torch.Tensor) -> torch.Tensor:
+        return expand_rows(self.codec, self.rows(), row_idx, self.Hkv, self.D, self.value)
+
+
+class CodecCache:
+    """All layers' keys (or values) in a codec: ``cache[l]`` is a :class:`CodecLayer`.  One spare block follows the
+    allocator's blocks (the target of padded tokens' writes)."""
+
+    def __init__(self, codec: str, n_layers: int, num_blocks: int, page: int, Hkv: int, D: int, device, value: bool):
+        if codec not in CODECS:
+            raise ValueError(f"unknown KV codec {codec!r}")
+        self.codec, self.Hkv, self.D, self.value = codec, Hkv, D, value
+        self.data = torch.zeros((n_layers, num_blocks + 1, page, row_bytes(codec, Hkv, D, value)), dtype=torch.uint8,
+                                device=device)
+
+    def __getitem__(self, l: int) -> CodecLayer:
+        return CodecLayer(self.codec, self.data[l], self.Hkv, self.D, self.value)
+
+    @property
+    def shape(self):
+        return self.data.shape
+
+    def numel(self) -> int:
+        return self.data.numel()
+
+    def element_size(self) -> int:
+        return 1
+
+    @property
+    def device(self):
+        return self.data.device

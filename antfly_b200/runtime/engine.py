@@ -64,6 +64,7 @@ class Request:
     pos3: Optional[torch.Tensor] = None
     rope_delta: int = 0
     bidir_spans: Optional[List[tuple]] = None     # [start, end) prompt ranges that attend in both directions
+    draft_attached: bool = False                  # has a sequence in the separate draft model's KV cache
 
     @property
     def tokens(self) -> List[int]:
@@ -113,13 +114,17 @@ class LLMEngine:
                  max_step_tokens: int = 8192, prefill_chunk: int = 2048, kv_dtype: str = "bf16",
                  use_cuda_graph: bool = True, draft_layers: int = 0, spec_k: int = 4, eos_token_id: Optional[int] = None,
                  max_seq_len: int = 8192 + 1024, max_queue: int = 0, prefix_cache: bool = False,
-                 prefix_cache_entries: int = 256):
+                 prefix_cache_entries: int = 256, draft_model: Optional[LlamaModel] = None,
+                 draft_num_blocks: Optional[int] = None):
+        """``draft_layers`` > 0: self-speculative draft (the target's first layers, sharing its KV cache).
+        ``draft_model``: a separate, smaller model with the same vocabulary as the draft (the reference's
+        ``draft_model`` request field, zig/pkg/inference/src/pipelines/generation.zig:1563-1745): it gets a paged KV
+        cache and block tables of its own, drafts K <= 16 tokens greedily per round, the target verifies them in
+        one pass with each request's sampler, and both caches are truncated to what was accepted."""
         self.model = model
         self.device = model.device
         self.page = page
-        if self.device.type == "cuda" and kv_dtype not in ("bf16", "bfloat16", "f16"):
-            raise ValueError(f"KV cache dtype {kv_dtype!r} is not available on the GPU path (bf16 only); "
-                             "the CPU path also accepts fp8")
+        self.kv_dtype = kv_dtype
         self.cache = PagedKvCache(model.n_layers, num_blocks, model.Hkv, model.D, page, kv_dtype, self.device)
         self.max_batch = max_batch
         self.max_blocks = (max_seq_len + page - 1) // page
@@ -133,6 +138,13 @@ class LLMEngine:
         self._static: Dict[tuple, _StaticStep] = {}
         self._attn_scratch: Optional[A.PagedAttnScratch] = None
         self.draft = model.draft_view(draft_layers) if draft_layers > 0 else None
+        self.draft_cache: Optional[PagedKvCache] = None
+        if draft_model is not None:
+            if draft_model.cfg.vocab_size != model.cfg.vocab_size:
+                raise ValueError("the draft model must share the target's vocabulary")
+            self.draft = draft_model
+            self.draft_cache = PagedKvCache(draft_model.n_layers, draft_num_blocks or num_blocks, draft_model.Hkv,
+                                            draft_model.D, page, kv_dtype, self.device)
         # Prompts that begin with already-prefilled tokens reuse those KV blocks (not with a sliding window, whose
         # trimming releases the very blocks a later prompt would share).
         self.prefix: Optional[PrefixCache] = None
@@ -199,6 +211,9 @@ class LLMEngine:
     def _retire(self, r: Request, reason: str) -> None:
         r.finished, r.finish_reason = True, reason
         self.cache.alloc.detach(r.rid)
+        if self.draft_cache is not None and r.draft_attached:
+            self.draft_cache.alloc.detach(r.rid)
+            r.draft_attached = False
         if r.row >= 0:
             self._rows_free.append(r.row)
             r.row = -1
@@ -272,7 +287,7 @@ class LLMEngine:
         d_tab = take(B * self.max_blocks).view(B, self.max_blocks)
         max_q = max(ql)
         splits = self._attn_splits(B, max(kvl)) if max_q * (self.model.Hq // self.model.Hkv) <= 16 else 1
-        return StepBatch(d_ids, d_pos, d_slots, d_qs, d_ql, d_kvl, d_tab, d_rows, max_q, splits)
+        return StepBatch(d_ids, d_pos, d_slots, d_qs, d_ql, d_kvl, d_tab, d_rows, max_q, splits, max_kv=max(kvl))
 
     def _add_multimodal(self, batch: StepBatch, items: List[StepItem], reqs: List[Request]) -> None:
         """Rotary streams for every token of the step, and the soft-token rows that fall inside its prefill chunks."""
@@ -487,13 +502,15 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------------
     def compact_request(self, rid: int, ratio: float, n_ref: int = 64, keep_recent: int = 16) -> int:
         """Attention-matching compaction of one sequence's KV cache (all layers, every KV head) to about ``ratio``
-        of its tokens; the sequence moves to fresh blocks (its old ones may be shared with cached prefixes) and
-        the freed blocks return to the pool.  Returns the number of tokens removed.  Not combined with
+        of its tokens (plain bf16 / f32 caches only); the sequence moves to fresh blocks (its old ones may be
+        shared with cached prefixes) and the freed blocks return to the pool.  Returns the number of tokens removed.  Not combined with
         speculative decoding."""
         from .kv_compaction import compact_layer
 
         if self.draft is not None:
             raise ValueError("KV compaction cannot be combined with speculative decoding")
+        if self.cache.codec is not None:
+            raise ValueError(f"KV compaction needs a plain cache; this engine keeps its cache as {self.cache.codec}")
         r = self.reqs[rid]
         alloc, page = self.cache.alloc, self.page
         N = alloc.length(rid)
@@ -525,13 +542,17 @@ class LLMEngine:
         """One speculative round for every decoding sequence: K greedy draft steps on the shallow model (which
         shares the target's first layers and their KV cache), one target pass over K+1 positions, verify/accept,
         KV rollback of the rejected tail."""
-        K = self.spec_k
         items = self.sched.claim_step()
         if not items:
             return 0
         reqs = [self.reqs[it.request_id] for it in items]
+        # Draft length of the round: the smallest of what the requests ask for (default: the engine's), 1..16.
+        K = max(1, min(16, min((r.params.speculative_k or self.spec_k) for r in reqs)))
         B = len(items)
         alloc = self.cache.alloc
+        separate = self.draft_cache is not None
+        if separate:
+            self._draft_catch_up(items, reqs)
         # Reserve K+1 slots per sequence up front; the draft fills the first K progressively.
         base_len = [it.kv_before for it in items]
         all_slots, tables = [], np.zeros((B, self.max_blocks), dtype=np.int32)
@@ -550,9 +571,25 @@ class LLMEngine:
         cur = last
         splits = self._attn_splits(B, max(base_len) + K + 1)
         scratch = self._scratch_for(B * (K + 1), splits)
+        if separate:
+            # The draft model writes K entries (last, d0 .. d_{K-2}) into ITS cache through ITS block tables.
+            dalloc = self.draft_cache.alloc
+            dtab_np = np.zeros((B, self.max_blocks), dtype=np.int32)
+            dslots = []
+            for i, it in enumerate(items):
+                dslots.append(dalloc.append(it.request_id, K))
+                bt = dalloc.block_table(it.request_id)
+                dtab_np[i, : len(bt)] = bt
+            dk, dv = self.draft_cache.k, self.draft_cache.v
+            draft_tab = torch.from_numpy(dtab_np).to(self.device)
+            draft_slots = torch.from_numpy(np.stack(dslots)).to(self.device)  # [B, K]
+            self.h2d_bytes += dtab_np.nbytes
+        else:
+            dk, dv, draft_tab, draft_slots = self.cache.k, self.cache.v, d_tab, slots_t
         for j in range(K):
-            b = StepBatch(cur, base + j, slots_t[:, j].contiguous(), ar, ones, base + j + 1, d_tab, ar, 1, splits)
-            lg = self.draft.forward(b, self.cache.k, self.cache.v, scratch)
+            b = StepBatch(cur, base + j, draft_slots[:, j].contiguous(), ar, ones, base + j + 1, draft_tab, ar, 1,
+                          splits)
+            lg = self.draft.forward(b, dk, dv, scratch)
             cur = self.draft.greedy_tokens(lg)
             drafts.append(cur)
         draft = torch.stack(drafts, 1).contiguous()  # [B, K]
@@ -563,7 +600,7 @@ class LLMEngine:
         vb = StepBatch(ver_ids, pos.contiguous(), slots_t.reshape(-1).contiguous(), ar * (K + 1),
                        ones * (K + 1), base + K + 1, d_tab,
                        torch.arange(B * (K + 1), dtype=torch.int32, device=self.device), K + 1,
-                       splits if (K + 1) * G <= 16 else 1)
+                       splits if (K + 1) * G <= 16 else 1, max_kv=max(base_len) + K + 1)
         logits = self.model.forward(vb, self.cache.k, self.cache.v, scratch)
         if all(r.params.greedy and not r.params.needs_penalties for r in reqs):
             target = self.model.greedy_tokens(logits)
@@ -601,9 +638,55 @@ class LLMEngine:
             if not done:
                 # KV holds last + the m matched drafts; the correction/bonus token enters the cache next round.
                 alloc.truncate(it.request_id, base_len[i] + n_added)
+                if separate:
+                    # The draft wrote last, d0 .. d_{K-2}: keep last + the matched drafts it has seen.  When all K
+                    # matched it is one entry short (d_{K-1}); the next round's catch-up feeds it.
+                    self.draft_cache.alloc.truncate(it.request_id, base_len[i] + min(n_added, K))
         self.sched.complete_step(items, tokens_out, finished)
         self.steps += 1
         return produced
+
+    def _draft_catch_up(self, items: List[StepItem], reqs: List[Request]) -> None:
+        """Brings the separate draft model's KV cache up to the target's: every token of a sequence except the one
+        about to be fed (prompt on the first round, tokens produced by non-speculative steps, the last matched
+        draft after a fully accepted round) runs through the draft model as a prefill chunk."""
+        dalloc = self.draft_cache.alloc
+        chunk = 2048
+        while True:
+            rows, seqs = [], []
+            budget = chunk
+            for it, r in zip(items, reqs):
+                if not r.draft_attached:
+                    dalloc.attach(r.rid)
+                    r.draft_attached = True
+                have, want = dalloc.length(r.rid), it.kv_before
+                if have > want:            # the target rolled back further than the draft (never with equal K)
+                    dalloc.truncate(r.rid, want)
+                    have = want
+                if have < want and budget > 0:
+                    n = min(want - have, budget)
+                    budget -= n
+                    rows.append((r.rid, have, n))
+                    seqs.append(r.tokens[have: have + n])
+            if not rows:
+                return
+            B = len(rows)
+            ids, pos, slots, qs, ql, kvl, last_rows = [], [], [], [], [], [], []
+            tables = np.zeros((B, self.max_blocks), dtype=np.int32)
+            t0 = 0
+            for i, ((rid, have, n), toks) in enumerate(zip(rows, seqs)):
+                sl = dalloc.append(rid, n)
+                ids.extend(toks); pos.extend(range(have, have + n)); slots.extend(sl.tolist())
+                qs.append(t0); ql.append(n); kvl.append(have + n); last_rows.append(t0 + n - 1)
+                bt = dalloc.block_table(rid)
+                tables[i, : len(bt)] = bt
+                t0 += n
+            dev = self.device
+            ti = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
+            self.h2d_bytes += 4 * (3 * t0 + 4 * B) + tables.nbytes
+            b = StepBatch(ti(ids), ti(pos), ti(slots), ti(qs), ti(ql), ti(kvl), torch.from_numpy(tables).to(dev),
+                          ti(last_rows[:1]), max(ql), 1)
+            self.draft.forward(b, self.draft_cache.k, self.draft_cache.v, None)
 
     # ------------------------------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], params, on_token: Optional[Callable] = None,

@@ -19,7 +19,12 @@ _i64 = ctypes.c_int64
 _int = ctypes.c_int
 _pint = ctypes.POINTER(ctypes.c_int)
 
-KV_DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f16": torch.bfloat16, "fp8": torch.float8_e4m3fn}
+# Plain tensor caches [layers, blocks, page, Hkv, D].  "f16" is served from bf16 storage (same size; the kernels
+# read bf16).  "f32" exists on the CPU path only (tests and the dequantised-cache reference).
+KV_DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f16": torch.bfloat16, "f32": torch.float32}
+# Caches kept in a quantised codec: byte rows, see ops/kv_quant.py (the reference's pool dtypes,
+# zig/pkg/inference/src/runtime/kv/pool.zig:26-35 and runtime/kv/turboquant.zig).
+KV_CODECS = ("fp8", "int8", "int4", "polar4", "turbo3")
 
 
 class KvOutOfBlocks(RuntimeError):
@@ -150,9 +155,21 @@ class PagedKvCache:
     def __init__(self, n_layers: int, num_blocks: int, n_kv_heads: int, head_dim: int, page: int = 16,
                  dtype: str = "bf16", device="cuda"):
         self.page, self.num_blocks = page, num_blocks
-        self.dtype = KV_DTYPES[dtype]
         self.kv_scale = 1.0
         self.alloc = BlockAllocator(num_blocks, page)
+        self.codec: Optional[str] = None
+        if dtype in KV_CODECS:
+            from ..ops.kv_quant import CodecCache
+
+            self.codec, self.dtype = dtype, torch.uint8
+            self.k = CodecCache(dtype, n_layers, num_blocks, page, n_kv_heads, head_dim, device, value=False)
+            self.v = CodecCache(dtype, n_layers, num_blocks, page, n_kv_heads, head_dim, device, value=True)
+            return
+        if dtype not in KV_DTYPES:
+            raise ValueError(f"unknown KV cache dtype {dtype!r}; one of {sorted(set(KV_DTYPES) | set(KV_CODECS))}")
+        if dtype == "f32" and torch.device(device).type == "cuda":
+            raise ValueError("an f32 KV cache is available on the CPU path only (the GPU kernels read bf16 or codecs)")
+        self.dtype = KV_DTYPES[dtype]
         shape = (n_layers, num_blocks, page, n_kv_heads, head_dim)
         self.k = torch.zeros(shape, dtype=self.dtype, device=device)
         self.v = torch.zeros(shape, dtype=self.dtype, device=device)
@@ -172,12 +189,21 @@ class PagedKvCache:
         s = torch.from_numpy(src.copy()).to(self.k.device)
         d = torch.from_numpy(dst.copy()).to(self.k.device)
         for l in range(self.k.shape[0]):
-            A.kv_copy_blocks(self.k[l], self.v[l], s, d)
+            if self.codec is not None:      # byte rows: a block copy is a block copy
+                kd, vd = self.k.data[l], self.v.data[l]
+                kd[d.long()] = kd[s.long()]
+                vd[d.long()] = vd[s.long()]
+            else:
+                A.kv_copy_blocks(self.k[l], self.v[l], s, d)
         return len(src)
 
 
 def estimate_kv_bytes(n_layers: int, n_kv_heads: int, head_dim: int, tokens: int, dtype: str = "bf16") -> int:
     """HBM needed to hold ``tokens`` tokens of KV (the reference's estimateGptGeneration,
     zig/pkg/inference/src/runtime/tier/memory.zig:455, reduced to the device tier)."""
-    el = 1 if dtype == "fp8" else 2
+    if dtype in KV_CODECS:
+        from ..ops.kv_quant import row_bytes
+
+        return n_layers * tokens * (row_bytes(dtype, n_kv_heads, head_dim) + row_bytes(dtype, n_kv_heads, head_dim, True))
+    el = 4 if dtype == "f32" else 2
     return 2 * n_layers * n_kv_heads * head_dim * tokens * el

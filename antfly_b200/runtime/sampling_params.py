@@ -20,6 +20,7 @@ class SamplingParams:
     seed: Optional[int] = None
     cache_compaction_ratio: Optional[float] = None  # in (0, 1): compact the KV cache to this fraction after prefill
     grammar: Optional[object] = None  # antfly_b200.runtime.grammar.JsonGrammar: constrains every sampled token
+    speculative_k: Optional[int] = None  # draft tokens per speculative round (1..16); None: the engine's default
 
     @property
     def greedy(self) -> bool:

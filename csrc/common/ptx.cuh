@@ -444,6 +444,20 @@ __device__ __forceinline__ float e8m0_to_float(uint8_t e) {
   return __uint_as_float(bits);
 }
 
+// Four packed e4m3 bytes -> four bf16 (two bf16x2 words: elements 0,1 and 2,3) without conversion instructions:
+// the 7 exponent + mantissa bits dropped into bf16 bit positions 10..4 read as the same value times 2^-120
+// (subnormals included), so one packed bf16 multiply by `scale2` = bf16x2(2^120 * s) finishes the job exactly
+// for any power-of-two s.  kE4m3ToBf16Unit is the multiplier for s = 1.
+constexpr uint32_t kE4m3ToBf16Unit = 0x7B807B80u;  // bf16 2^120 in both lanes (exponent field 247)
+__device__ __forceinline__ void e4m3x4_to_bf16x4(uint32_t w, uint32_t scale2, uint32_t& lo01, uint32_t& hi23) {
+  const uint32_t lo = __byte_perm(w, 0u, 0x1404);  // bytes 0,1 -> high byte of each 16-bit lane
+  const uint32_t hi = __byte_perm(w, 0u, 0x3424);  // bytes 2,3
+  const uint32_t blo = ((lo >> 4) & 0x07F007F0u) | (lo & 0x80008000u);
+  const uint32_t bhi = ((hi >> 4) & 0x07F007F0u) | (hi & 0x80008000u);
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo01) : "r"(blo), "r"(scale2));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi23) : "r"(bhi), "r"(scale2));
+}
+
 // Two packed e4m3 bytes -> two floats.
 __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
   uint32_t h2;

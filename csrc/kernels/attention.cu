@@ -53,6 +53,7 @@ struct AttnParams {
   int causal, window;
   float scale_log2;  // softmax scale * log2(e)
   int num_splits;
+  float v_scale;     // fp8 caches: factor that turns stored value codes back into values (1 for bf16 caches)
 };
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, int src_bytes) {
@@ -122,6 +123,60 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* sK, __nv_bfloat16* s
     const int dst = (ROWS_PER_PASS % 8 == 0) ? dst0 + i * ROWS_PER_PASS * D : row * D + ((ch ^ (row & 7)) * 8);
     cp_async_16(sK + dst, (PAGED ? p.k_cache : p.k) + off, valid ? 16 : 0);
     cp_async_16(sV + dst, (PAGED ? p.v_cache : p.v) + off, valid ? 16 : 0);
+  }
+}
+
+// fp8 (e4m3) paged cache: a 64-key tile arrives as raw bytes, row-major [64][D], through the same cp.async ring at
+// half the traffic; each thread then expands the 16-byte chunks IT loaded (so only its own cp.async groups need to
+// have landed) into the swizzled bf16 work tile the ldmatrix / mma code reads.
+template <int D>
+__device__ __forceinline__ void load_kv_tile8(uint8_t* rK, uint8_t* rV, const AttnParams& p, int b, int hk, int k0,
+                                              int kv_len) {
+  constexpr int CH = D / 16;
+  constexpr int ROWS_PER_PASS = 128 / CH;
+  const int ch = threadIdx.x % CH, r0 = threadIdx.x / CH;
+  const int* table = p.block_tables + static_cast<size_t>(b) * p.max_blocks;
+  const size_t row_bytes = static_cast<size_t>(p.Hkv) * D;
+  const size_t col_off = static_cast<size_t>(hk) * D + ch * 16;
+  const uint8_t* k8 = reinterpret_cast<const uint8_t*>(p.k_cache);
+  const uint8_t* v8 = reinterpret_cast<const uint8_t*>(p.v_cache);
+#pragma unroll
+  for (int i = 0; i < kTileKeys / ROWS_PER_PASS; ++i) {
+    const int row = r0 + i * ROWS_PER_PASS;
+    const int key = k0 + row;
+    const bool valid = key < kv_len;
+    const int kk = valid ? key : 0;
+    int blk, in_page;
+    if (p.page_shift >= 0) { blk = table[kk >> p.page_shift]; in_page = kk & (p.page - 1); }
+    else { blk = table[kk / p.page]; in_page = kk % p.page; }
+    const size_t off = (static_cast<size_t>(blk) * p.page + in_page) * row_bytes + col_off;
+    cp_async_16(rK + row * D + ch * 16, k8 + off, valid ? 16 : 0);
+    cp_async_16(rV + row * D + ch * 16, v8 + off, valid ? 16 : 0);
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void expand_kv_tile8(const uint8_t* rK, const uint8_t* rV, __nv_bfloat16* sK,
+                                                __nv_bfloat16* sV) {
+  constexpr int CH = D / 16;
+  constexpr int ROWS_PER_PASS = 128 / CH;
+  const int ch = threadIdx.x % CH, r0 = threadIdx.x / CH;
+#pragma unroll
+  for (int i = 0; i < kTileKeys / ROWS_PER_PASS; ++i) {
+    const int row = r0 + i * ROWS_PER_PASS;
+    const int c0 = ((2 * ch) ^ (row & 7)) * 8, c1 = ((2 * ch + 1) ^ (row & 7)) * 8;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint4 v = *reinterpret_cast<const uint4*>((which ? rV : rK) + row * D + ch * 16);
+      uint32_t o[8];
+      e4m3x4_to_bf16x4(v.x, kE4m3ToBf16Unit, o[0], o[1]);
+      e4m3x4_to_bf16x4(v.y, kE4m3ToBf16Unit, o[2], o[3]);
+      e4m3x4_to_bf16x4(v.z, kE4m3ToBf16Unit, o[4], o[5]);
+      e4m3x4_to_bf16x4(v.w, kE4m3ToBf16Unit, o[6], o[7]);
+      __nv_bfloat16* dst = which ? sV : sK;
+      *reinterpret_cast<uint4*>(dst + row * D + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(dst + row * D + c1) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
   }
 }
 
@@ -416,12 +471,16 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return r;
 }
 
-template <int D, int STAGES>
+// KV8: the cache holds e4m3 bytes (see load_kv_tile8): the ring carries raw tiles and one bf16 work tile pair sits
+// behind it.
+template <int D, int STAGES, bool KV8>
 __global__ void __launch_bounds__(128) decode_attn_t_kernel(AttnParams p) {
   constexpr int KSTEPS = D / 16;  // 16-wide steps over the head dimension
   constexpr int NDB = D / 16;     // 16-row blocks of O^T
   extern __shared__ __align__(128) uint8_t smem_attn[];
   __nv_bfloat16* sKV = reinterpret_cast<__nv_bfloat16*>(smem_attn);
+  constexpr int RAW_TILE = kTileKeys * D;  // bytes of one raw fp8 tile (K or V)
+  __nv_bfloat16* sWork = reinterpret_cast<__nv_bfloat16*>(smem_attn + STAGES * 2 * RAW_TILE);  // KV8 only
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   griddep_launch();
@@ -479,22 +538,38 @@ __global__ void __launch_bounds__(128) decode_attn_t_kernel(AttnParams p) {
 #pragma unroll
   for (int s0 = 0; s0 < STAGES - 1; ++s0) {
     if (s0 < ntiles) {
-      __nv_bfloat16* nK = sKV + s0 * 2 * TILE_ELEMS;
-      load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + s0) * kTileKeys, kv_len, q_start);
+      if constexpr (KV8) {
+        uint8_t* rK = smem_attn + s0 * 2 * RAW_TILE;
+        load_kv_tile8<D>(rK, rK + RAW_TILE, p, b, hk, (t_begin + s0) * kTileKeys, kv_len);
+      } else {
+        __nv_bfloat16* nK = sKV + s0 * 2 * TILE_ELEMS;
+        load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + s0) * kTileKeys, kv_len, q_start);
+      }
     }
     cp_async_commit();
   }
   const int mi = lane >> 3, rin = lane & 7;
   for (int it = 0; it < ntiles; ++it) {
     const int stage = it % STAGES;
-    const __nv_bfloat16* sK = sKV + stage * 2 * TILE_ELEMS;
+    const __nv_bfloat16* sK = KV8 ? sWork : sKV + stage * 2 * TILE_ELEMS;
     const __nv_bfloat16* sV = sK + TILE_ELEMS;
     if (it + STAGES - 1 < ntiles) {
-      __nv_bfloat16* nK = sKV + ((it + STAGES - 1) % STAGES) * 2 * TILE_ELEMS;
-      load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + STAGES - 1) * kTileKeys, kv_len, q_start);
+      if constexpr (KV8) {
+        uint8_t* rK = smem_attn + ((it + STAGES - 1) % STAGES) * 2 * RAW_TILE;
+        load_kv_tile8<D>(rK, rK + RAW_TILE, p, b, hk, (t_begin + it + STAGES - 1) * kTileKeys, kv_len);
+      } else {
+        __nv_bfloat16* nK = sKV + ((it + STAGES - 1) % STAGES) * 2 * TILE_ELEMS;
+        load_kv_tile<D, true>(nK, nK + TILE_ELEMS, p, b, hk, (t_begin + it + STAGES - 1) * kTileKeys, kv_len, q_start);
+      }
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();
+    if constexpr (KV8) {
+      // Each thread expands the chunks it loaded itself (its own groups have landed); the work tile is free:
+      // the barrier that ends the previous iteration followed every warp's last read of it.
+      const uint8_t* rK = smem_attn + stage * 2 * RAW_TILE;
+      expand_kv_tile8<D>(rK, rK + RAW_TILE, sWork, sWork + TILE_ELEMS);
+    }
     __syncthreads();
 
     const int k0 = (t_begin + it) * kTileKeys + warp * 16;  // first key of this warp's slab
@@ -615,7 +690,7 @@ __global__ void __launch_bounds__(128) decode_attn_t_kernel(AttnParams p) {
         acc += f * sO[(w * 8 + r) * D + col];
       }
     }
-    const float val = L > 0.0f ? acc / L : 0.0f;
+    const float val = (L > 0.0f ? acc / L : 0.0f) * (KV8 ? p.v_scale : 1.0f);
     const int tok = q_start + r / G;
     const int head = hk * G + r % G;
     if (p.num_splits == 1) {
@@ -693,14 +768,24 @@ inline bool transposed_decode_disabled() {
   return v == 1;
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool KV8 = false>
 int launch_decode_t_s(const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  const int smem_tiles = STAGES * 2 * kTileKeys * D * 2;
+  // bf16 cache: a ring of bf16 tile pairs.  fp8 cache: a ring of raw byte tile pairs plus one bf16 work pair.
+  const int smem_tiles = KV8 ? (STAGES * 2 * kTileKeys * D + 2 * kTileKeys * D * 2) : STAGES * 2 * kTileKeys * D * 2;
   const int smem_merge = (4 * 8 * D + 64) * 4;
   const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
-  AFB_CONFIGURE_KERNEL((decode_attn_t_kernel<D, STAGES>), smem, 128, 0);
-  AFB_CHECK_CUDA(launch_pdl(decode_attn_t_kernel<D, STAGES>, grid, dim3(128), smem, stream, p));
+  AFB_CONFIGURE_KERNEL((decode_attn_t_kernel<D, STAGES, KV8>), smem, 128, 0);
+  AFB_CHECK_CUDA(launch_pdl(decode_attn_t_kernel<D, STAGES, KV8>, grid, dim3(128), smem, stream, p));
   return 0;
+}
+
+// fp8 cache, decode organisation with at most 8 rows per KV head (the only fp8-reading tensor-core path).
+template <int D>
+int launch_decode_t8(const AttnParams& p, int B, cudaStream_t stream) {
+  dim3 grid(1, p.Hkv, B * p.num_splits);
+  const long ctas = static_cast<long>(grid.y) * grid.z;
+  if (ctas <= 2L * device_sm_count()) return launch_decode_t_s<D, 3, true>(p, grid, stream);
+  return launch_decode_t_s<D, 2, true>(p, grid, stream);
 }
 
 template <int D>
@@ -811,6 +896,7 @@ int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v,
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.num_splits = num_splits;
+  p.v_scale = 1.0f;
   const int G = Hq / Hkv;
   const int max_rows = max_q_len * G;
   int rc;
@@ -824,6 +910,75 @@ int afb_attention_mx(const void* q, long q_stride, const void* k, const void* v,
   }
   if (D == 64) { AFB_ATTN_DISPATCH(64) } else if (D == 128) { AFB_ATTN_DISPATCH(128) } else { AFB_ATTN_DISPATCH(256) }
 #undef AFB_ATTN_DISPATCH
+  if (rc) return rc;
+  if (num_splits > 1) {
+    const int rows_per_cta = 128 / (D / 4);
+    AFB_CHECK_CUDA(launch_pdl(attn_merge_kernel, dim3((T * Hq + rows_per_cta - 1) / rows_per_cta), dim3(128), 0, stream,
+                              static_cast<const float*>(part_o), static_cast<const float*>(part_lse), p.out, out_stride,
+                              T * Hq, Hq, D, num_splits, reinterpret_cast<uint8_t*>(mx_q0),
+                              reinterpret_cast<uint8_t*>(mx_q1), reinterpret_cast<uint8_t*>(mx_sf0),
+                              reinterpret_cast<uint8_t*>(mx_sf1)));
+  }
+  return 0;
+}
+
+// Paged decode attention over an fp8 (e4m3) cache, k_cache / v_cache [num_blocks, page, Hkv, D] bytes: the
+// tensor-core decode kernel with the codes expanded to bf16 in shared memory, so the cache crosses HBM at one byte
+// per element.  Decode shapes only (q_len * Hq / Hkv <= 8 rows per KV head); k_scale / v_scale turn stored codes
+// back into values (1 when keys and values were stored unscaled).  Same split-KV scratch contract as afb_attention.
+int afb_attention_kv8(const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_tables,
+                      int max_blocks, int page, const int* q_starts, const int* q_lens, const int* kv_lens, void* out,
+                      long out_stride, float* part_o, float* part_lse, int B, int T, int Hq, int Hkv, int D,
+                      int max_q_len, int window, float scale, float k_scale, float v_scale, int num_splits,
+                      void* mx_q0, void* mx_q1, void* mx_sf0, void* mx_sf1, cudaStream_t stream) {
+  using namespace afb;
+  if (B <= 0 || T <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv != 0 || (D != 64 && D != 128 && D != 256) || max_q_len * (Hq / Hkv) > 8) {
+    set_last_error("afb_attention_kv8: needs head_dim 64 / 128 / 256 and q_len * (Hq / Hkv) <= 8 (D=%d Hq=%d Hkv=%d "
+                   "q_len=%d)", D, Hq, Hkv, max_q_len);
+    return -1;
+  }
+  if ((q_stride & 7) || (out_stride & 3) || ((static_cast<long>(Hkv) * D) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)) {
+    set_last_error("afb_attention_kv8: q stride must be a multiple of 8 elements and cache rows 16-byte aligned");
+    return -1;
+  }
+  if (!(scale > 0.0f) || !(k_scale > 0.0f) || !(v_scale > 0.0f)) {
+    set_last_error("afb_attention_kv8: scales must be positive");
+    return -1;
+  }
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && (!part_o || !part_lse)) {
+    set_last_error("afb_attention_kv8: num_splits > 1 needs partial buffers");
+    return -1;
+  }
+  if (mx_q0 && (num_splits < 2 || (Hq * D) % 128 != 0 || !mx_sf0)) {
+    set_last_error("afb_attention_kv8: MX output needs num_splits > 1 and Hq * D a multiple of 128");
+    return -1;
+  }
+  if (!out && !mx_q0) {
+    set_last_error("afb_attention_kv8: no output buffer");
+    return -1;
+  }
+  AttnParams p = {};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
+  p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache);  // read as bytes by the fp8 tile loader
+  p.v_cache = reinterpret_cast<const __nv_bfloat16*>(v_cache);
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.page = page;
+  p.page_shift = -1;
+  if (page > 0 && (page & (page - 1)) == 0) {
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < page) ++p.page_shift;
+  }
+  p.q_starts = q_starts; p.q_lens = q_lens; p.kv_lens = kv_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
+  p.part_o = part_o; p.part_lse = part_lse;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = 1; p.window = window;
+  p.scale_log2 = scale * k_scale * 1.4426950408889634f;
+  p.num_splits = num_splits;
+  p.v_scale = v_scale;
+  int rc = D == 64 ? launch_decode_t8<64>(p, B, stream)
+                   : D == 128 ? launch_decode_t8<128>(p, B, stream) : launch_decode_t8<256>(p, B, stream);
   if (rc) return rc;
   if (num_splits > 1) {
     const int rows_per_cta = 128 / (D / 4);

@@ -158,9 +158,49 @@ __global__ void __launch_bounds__(kKvqWarps * 32) kvq_decode_attn_kernel(const K
   }
 }
 
+// Expands cache rows to bf16: out[i, h, d] = element (h, d) of code row row_idx[i], times `scale`.  One CTA per
+// row; used to hand a prefill chunk's keys and values to the tensor-core attention kernels (which read bf16) while
+// the cache itself stays in its codec.  turbo3 keys expand to their 3-bit base values (the residual sketch only
+// enters direct code scoring).  Row ids are range-checked; a bad one records kStatusBadIndex and writes zeros.
+__global__ void kvq_expand_rows_kernel(const uint8_t* cache, long row_bytes, const int* row_idx, __nv_bfloat16* out,
+                                       int heads, int D, int codec, int is_value, float scale, long num_rows) {
+  const long i = blockIdx.x;
+  const long row = row_idx[i];
+  const int n = heads * D;
+  __nv_bfloat16* dst = out + i * n;
+  if (row < 0 || row >= num_rows) {
+    if (threadIdx.x == 0) status_set(kStatusBadIndex);
+    for (int e = threadIdx.x; e < n; e += blockDim.x) dst[e] = __float2bfloat16(0.0f);
+    return;
+  }
+  const uint8_t* src = cache + row * row_bytes;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int h = e / D, d = e % D;
+    const float v = is_value ? kvq::value_elem(codec, src, heads, D, h, d) : kvq::key_elem(codec, src, heads, D, h, d);
+    dst[e] = __float2bfloat16(v * scale);
+  }
+}
+
 }  // namespace afb
 
 extern "C" {
+
+// cache: byte rows [num_rows, row_bytes] in `codec`; row_idx int32 [n]; out bf16 [n, heads * D].
+int afb_kvq_expand_rows(const void* cache, const int* row_idx, void* out, long n, long num_rows, int heads, int D,
+                        int codec, int is_value, float scale, cudaStream_t stream) {
+  using namespace afb;
+  if (n <= 0) return 0;
+  const long rb = is_value ? kvq::value_row_bytes(codec, heads, D) : kvq::key_row_bytes(codec, heads, D);
+  if (rb <= 0 || n > 0x7fffffffL) {
+    set_last_error("afb_kvq_expand_rows: unsupported codec / head size, or too many rows");
+    return -1;
+  }
+  kvq_expand_rows_kernel<<<static_cast<unsigned>(n), 256, 0, stream>>>(
+      reinterpret_cast<const uint8_t*>(cache), rb, row_idx, reinterpret_cast<__nv_bfloat16*>(out), heads, D, codec,
+      is_value, scale, num_rows);
+  AFB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 // q [B, Hq, D] bf16 (one decode token per sequence); caches are byte arrays of [num_blocks, page] codec rows.
 int afb_kvq_decode_attention(const void* q, long q_stride, const void* k_cache, const void* v_cache,

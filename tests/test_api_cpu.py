@@ -561,3 +561,31 @@ def test_neural_chunker_splits_at_predicted_boundaries(tmp_path):
     assert c.post("/ai/v1/chunk", json={"text": text, "model": "missing"}).status_code == 404
     assert c.post("/ai/v1/chunk", json={"text": "a b c d", "target_tokens": 2, "overlap_tokens": 0}).json()[
         "chunks"][0]["text"] == "a b"
+
+
+def test_generate_with_draft_model_and_cache_dtype_per_request():
+    """``draft_model`` loads a second generator as the speculative draft (own KV cache), ``speculative_k`` sets the
+    round length, ``cache_dtype`` selects the KV-cache codec; greedy output never depends on the draft, and the
+    speculative stats show up in the metrics."""
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu", kv_blocks=128, max_batch=4)
+    mgr.register_random("target", "generator", seed=0)
+    mgr.register_random("small", "generator", seed=7)
+    c = TestClient(create_app(mgr))
+    base = {"model": "target", "messages": [{"role": "user", "content": "hello there"}], "max_tokens": 9, "temperature": 0}
+    plain = c.post("/ai/v1/chat/completions", json=base).json()["choices"][0]["message"]["content"]
+    r = c.post("/ai/v1/chat/completions", json=dict(base, draft_model="small", speculative_k=3))
+    assert r.status_code == 200, r.text
+    assert r.json()["choices"][0]["message"]["content"] == plain
+    variant = mgr.get_generator("target", "small", None)
+    assert variant.pipeline.engine.draft_cache is not None and variant.pipeline.engine.spec.rounds > 0
+    assert variant.pipeline.engine.model is mgr.get("target", "generator").pipeline.engine.model   # weights shared
+    # quantised caches: served, and a different engine per dtype
+    for dt in ("fp8", "int8", "int4", "f16", "f32"):
+        r = c.post("/ai/v1/chat/completions", json=dict(base, cache_dtype=dt))
+        assert r.status_code == 200, (dt, r.text)
+    assert mgr.get_generator("target", None, "int8").pipeline.engine.cache.codec == "int8"
+    assert mgr.get_generator("target", None, "f16") is mgr.get("target", "generator")
+    # errors: unknown draft model, draft equal to the target
+    assert c.post("/ai/v1/chat/completions", json=dict(base, draft_model="nope")).status_code == 404
+    assert c.post("/ai/v1/chat/completions", json=dict(base, draft_model="target")).status_code == 400
+    assert c.post("/ai/v1/chat/completions", json=dict(base, cache_dtype="int3")).status_code in (400, 422)
