@@ -131,7 +131,10 @@ class LLMEngine:
         self.sched = StepScheduler(SchedulerPolicy(max_step_items=max_batch, max_step_query_tokens=max_step_tokens,
                                                    prefill_chunk=prefill_chunk, min_chunk=32, decode_streak=4,
                                                    page=page, max_queue=max_queue))
-        self.use_graph = use_cuda_graph and self.device.type == "cuda" and getattr(model, "graph_safe", True)
+        # Decode steps are captured in CUDA graphs when nothing in a step depends on the data; the integer codecs
+        # encode new rows with tensor ops (and turbo3 builds its sign table on first use), so they run eagerly.
+        self.use_graph = (use_cuda_graph and self.device.type == "cuda" and getattr(model, "graph_safe", True)
+                          and self.cache.codec in (None, "fp8"))
         self.eos = eos_token_id
         self.reqs: Dict[int, Request] = {}
         self._next_id = 1

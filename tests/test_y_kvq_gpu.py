@@ -46,3 +46,88 @@ def test_bad_block_id_is_skipped_and_reported():
     out = cache.attend(q, bt, torch.tensor([20], dtype=torch.int32).cuda())
     assert N.status() & 32                                         # the bad-index code; the keys were skipped
     assert bool(torch.isfinite(out.float()).all())
+
+
+@pytest.mark.parametrize("codec", ["fp8", "int8", "int4", "polar4", "turbo3"])
+def test_expand_rows_matches_the_host_decoder(codec):
+    """The kernel that hands prefill steps a bf16 copy of the pages they can see: every element equals the C++
+    decoder's value rounded to bf16; an out-of-range row id is reported and written as zeros."""
+    from antfly_b200 import _native as N
+    from antfly_b200.ops import kv_quant as KQ
+
+    g = torch.Generator().manual_seed(3)
+    Hkv, D, n = 4, 128, 200
+    for value in (False, True):
+        x = torch.randn(n, Hkv, D, generator=g) * 0.5
+        rows = KQ.encode_rows(codec, x, value=value)
+        idx = torch.randperm(n, generator=g)[:77].int()
+        got = KQ.expand_rows(codec, rows.cuda(), idx.cuda(), Hkv, D, value=value)
+        want = KQ.decode_rows(codec, rows[idx.long()], Hkv, D, value=value).to(torch.bfloat16)
+        assert N.status() == 0
+        assert torch.equal(got.cpu(), want)
+    bad = torch.tensor([0, n + 5], dtype=torch.int32).cuda()
+    out = KQ.expand_rows(codec, rows.cuda(), bad, Hkv, D, value=True)
+    assert N.status() & 32 and float(out[1].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (8, 2, 64), (8, 1, 128), (4, 2, 256)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_fp8_cache_tensor_core_decode_matches_fp32_reference(Hq, Hkv, D, splits):
+    """afb_attention_kv8: e4m3 codes expanded to bf16 in shared memory, tensor-core decode, against fp32 attention
+    over the dequantised cache."""
+    from antfly_b200 import _native as N
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import kv_quant as KQ
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(Hq * 7 + D)
+    B, page, nblk = 6, 16, 80
+    lens = [1, 17, 64, 200, 333, 500]
+    kl = KQ.CodecCache("fp8", 1, nblk, page, Hkv, D, "cuda", value=False)[0]
+    vl = KQ.CodecCache("fp8", 1, nblk, page, Hkv, D, "cuda", value=True)[0]
+    ref_k = torch.zeros((nblk + 1, page, Hkv, D))
+    ref_v = torch.zeros_like(ref_k)
+    bt = torch.zeros((B, 32), dtype=torch.int32)
+    perm = torch.randperm(nblk, generator=g)
+    off = 0
+    for b, n in enumerate(lens):
+        nb = (n + page - 1) // page
+        bt[b, :nb] = perm[off: off + nb].int()
+        off += nb
+        k = torch.randn(n, Hkv, D, generator=g) * 0.5
+        v = torch.randn(n, Hkv, D, generator=g)
+        t = torch.arange(n)
+        slots = (bt[b, t // page].long() * page + t % page).int()
+        kl.write(slots.cuda(), k.cuda())
+        vl.write(slots.cuda(), v.cuda())
+        ref_k.view(-1, Hkv, D)[slots.long()] = k.to(torch.float8_e4m3fn).float()
+        ref_v.view(-1, Hkv, D)[slots.long()] = v.to(torch.float8_e4m3fn).float()
+    q = torch.randn(B, Hq, D, generator=g).to(torch.bfloat16)
+    ar = torch.arange(B, dtype=torch.int32)
+    kv_lens = torch.tensor(lens, dtype=torch.int32)
+    for window in (0, 70):
+        got = A.paged_attention(q.cuda(), kl, vl, bt.cuda(), ar.cuda(), torch.ones_like(ar).cuda(), kv_lens.cuda(), 1,
+                                window=window, num_splits=splits)
+        assert N.status() == 0
+        want = R.paged_attention(q, ref_k, ref_v, bt, ar, torch.ones_like(ar), kv_lens, D ** -0.5, window)
+        torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("codec", ["fp8", "int8", "int4"])
+def test_engine_with_quantised_cache_on_gpu_matches_its_cpu_run(codec):
+    """The whole path on the device (KV write into the codec, prefill through page expansion, decode through the
+    code-reading kernels, graph capture) produces the tokens of the same engine on the CPU oracle path."""
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    cfg = LlamaConfig.tiny(num_hidden_layers=2)
+    prompts = [[7, 8, 9, 10] * 9, [100, 101, 102], [5] * 21]
+    sp = SamplingParams(max_tokens=8)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        model = LlamaModel.random_init(cfg, device=dev, seed=0)
+        eng = LLMEngine(model, num_blocks=64, page=16, max_batch=4, max_step_tokens=64, kv_dtype=codec)
+        outs.append([r.token_ids for r in eng.generate(prompts, sp)])
+    same = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y))
+    assert same >= 0.8 * sum(len(x) for x in outs[0]), outs   # bf16 kernels vs fp32 oracle: near-ties may flip
