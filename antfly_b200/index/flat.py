@@ -27,6 +27,9 @@ from .distance import score_form
 class SearchResult:
     distances: torch.Tensor  # [Q, k] ascending, +inf padded
     ids: torch.Tensor        # [Q, k] int32 (or int64 after id mapping), -1 padded
+    # set by the searches that do not synchronise with the host: a device int32 [1] that is non-zero when a
+    # candidate buffer overflowed and the result may miss neighbours (the caller repeats on the safe path)
+    overflow: Optional[torch.Tensor] = None
 
 
 class FlatIndex:
@@ -118,8 +121,13 @@ class FlatIndex:
         return torch.where(top_i >= 0, self.ids[(top_i - self.id_offset).clamp_min(0).long()],
                            torch.full_like(top_i, -1).to(self.ids.dtype))
 
+    def search_nosync(self, queries: torch.Tensor, k: int) -> SearchResult:
+        """As ``search`` on the fast path, without looking at the overflow flag on the host: the flag comes back in
+        ``SearchResult.overflow`` for the caller to check when it reads the results anyway."""
+        return self._search(queries, k, nosync=True)
+
     def _search(self, queries: torch.Tensor, k: int, map_ids: bool = True, push=None,
-                safe: bool = False) -> SearchResult:
+                safe: bool = False, nosync: bool = False) -> SearchResult:
         """push: peer targets of a sharded search (``MergeWorkspace.push_targets``); the select that ends the walk
         then also stores the result into every rank's merge buffer.  In that mode a candidate-buffer overflow is
         not repaired here: it travels with the pushed rows and the caller repeats the search with safe=True on
@@ -156,6 +164,9 @@ class FlatIndex:
                 any_ovf |= o
             lo = hi
             chunk = max(chunk, lo)  # geometric growth: expected appends per query per chunk stay ~k
+        if nosync:
+            flag = ovf if ovf is not None else torch.tensor([any_ovf], dtype=torch.int32)
+            return SearchResult(top_v, self._map_ids(top_i) if map_ids else top_i, overflow=flag)
         if push is None and (any_ovf or (ovf is not None and int(ovf))):
             return self._search_safe(qb, row, k, map_ids)
         return SearchResult(top_v, self._map_ids(top_i) if map_ids else top_i)

@@ -125,3 +125,62 @@ def merge_over_group(res: SearchResult, k: int, world: int, group=None) -> Searc
     srcs = [(v, i, None, k) for v, i in zip(vals, ids)]
     tv, ti, _, _ = IX.topk_select(srcs, nq, k, world * k)
     return SearchResult(tv, ti)
+
+
+class ShardedIVFIndex:
+    """IVF over a database split across ranks: the k-means centroids are trained jointly (the update's sums and
+    counts are all-reduced, so every rank holds the same centroids and probes the same lists); every rank keeps the
+    members of all lists that fall into its shard, searches them with the fixed launch sequence of
+    :class:`IVFIndex`, and the final select pushes into every rank's merge buffer."""
+
+    def __init__(self, local_vectors: torch.Tensor, n_lists: int, metric: str, rank: int, world: int,
+                 rows_per_rank: int, max_queries: int = 1024, max_k: int = 128, group=None, train_sample: int = 0,
+                 max_iter: int = 16):
+        from .ivf import IVFIndex
+
+        self.rank, self.world, self.group = rank, world, group
+        all_reduce = None
+        if world > 1:
+            def all_reduce(t):
+                dist.all_reduce(t, group=group)
+                return t
+        init = None
+        if world > 1:
+            # one seed set for everybody: rank 0 draws n_lists of its rows, all ranks start Lloyd from them
+            dev = local_vectors.device
+            g = torch.Generator(device=dev).manual_seed(0)
+            pick = torch.randperm(local_vectors.shape[0], generator=g, device=dev)[:n_lists]
+            init = local_vectors[pick].float().contiguous()
+            if init.shape[0] < n_lists:
+                init = torch.cat([init, torch.randn(n_lists - init.shape[0], init.shape[1], device=dev)], 0)
+            dist.broadcast(init, src=0, group=group)
+        self.local = IVFIndex(local_vectors, n_lists, metric=metric, max_iter=max_iter, train_sample=train_sample,
+                              id_offset=rank * rows_per_rank, all_reduce=all_reduce, init_centroids=init)
+        self.device = self.local.x.device
+        self.max_queries, self.max_k = max_queries, max_k
+        self.ws: Optional[MergeWorkspace] = None
+        if world > 1 and self.device.type == "cuda":
+            self.ws = MergeWorkspace(rank, world, self.device, max_queries, max_k, group)
+
+    def search(self, queries: torch.Tensor, k: int, nprobe: int = 64) -> SearchResult:
+        if self.world == 1:
+            return self.local.search(queries, k, nprobe)
+        if self.ws is None:
+            return merge_over_group(self.local.search(queries, k, nprobe), k, self.world, self.group)
+        nq = queries.shape[0]
+        assert nq <= self.max_queries and k <= self.max_k
+        ws = self.ws
+        par, target = ws.sched.next(nq)
+        # pushed ids must be global: map sorted rows to ids before the push select
+        res = self.local.search(queries, k, nprobe, check=False)
+        ovf_local = res.overflow
+        IX.topk_select([(res.distances.contiguous(), res.ids.contiguous(), None, k)], nq, k, k,
+                       overflow=ovf_local, push=ws.push_targets(par))
+        tv, ti, _, ovf = ws.merge(par, target, nq, k)
+        if int(ovf):  # every rank sees the same flags: all repeat on the safe path together
+            par, target = ws.sched.next(nq)
+            safe = self.local._search_host(queries, k, nprobe)
+            IX.topk_select([(safe.distances.contiguous(), safe.ids.contiguous(), None, k)], nq, k, k,
+                           push=ws.push_targets(par))
+            tv, ti, _, _ = ws.merge(par, target, nq, k)
+        return SearchResult(tv, ti)

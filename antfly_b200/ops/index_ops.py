@@ -111,8 +111,13 @@ def topk_select(sources: Sequence[tuple], n_queries: int, k: int, max_total: int
     dev = sources[0][0].device
     if dev.type != "cuda":
         vals, idxs = [], []
-        for v, ix, cnt, fl in sources:
+        flag = 0
+        for si, (v, ix, cnt, fl) in enumerate(sources):
             for_q_v, for_q_i = [], []
+            if cnt is not None and bool((cnt[:n_queries] > fl).any()):
+                flag = 1            # a producer counted more candidates than its buffer holds
+            if src_flags is not None and src_flags[si] is not None and bool((src_flags[si][:n_queries] != 0).any()):
+                flag = 1
             for qi in range(n_queries):
                 n = min(int(cnt[qi]), fl) if cnt is not None else fl
                 for_q_v.append(v[qi, :n]); for_q_i.append(ix[qi, :n])
@@ -128,7 +133,11 @@ def topk_select(sources: Sequence[tuple], n_queries: int, k: int, max_total: int
                 out_i[qi, :order.numel()] = ix[order].int()
                 if v.numel() >= k:
                     thr[qi] = out_v[qi, k - 1]
-        return out_v, out_i, thr, 0
+        if overflow is not None:
+            if flag:
+                overflow.fill_(1)
+            return out_v, out_i, thr, overflow
+        return out_v, out_i, thr, flag
     n = len(sources)
     PF, PI = ctypes.c_void_p * n, ctypes.c_void_p * n
     vals = PF(*[s[0].data_ptr() for s in sources])
@@ -194,3 +203,44 @@ def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     N.check(rc, "afb_gather_rows")
     N.count_launch()
     return out
+
+
+def ivf_scan(x, col_term, q, row_term, threshold, list_off, pair_off, pair_query, cand_val, cand_idx, cand_count,
+             scale: float, clamp_zero: bool) -> None:
+    """Grouped scoring of posting lists: for every list l, the rows x[list_off[l] : list_off[l + 1]] against the
+    queries pair_query[pair_off[l] : pair_off[l + 1]]; pairs with distance < threshold[query] (all pairs when
+    threshold is None) are appended as (distance, row) to the query's candidate list.  One launch, no host
+    synchronisation; cand_count may end above the capacity (the select that follows reports it)."""
+    n_lists = list_off.numel() - 1
+    cap = cand_val.shape[1]
+    if not x.is_cuda:
+        lo_h, po_h, pq_h = list_off.tolist(), pair_off.tolist(), pair_query.tolist()
+        for l in range(n_lists):
+            a, b = lo_h[l], lo_h[l + 1]
+            if b <= a or po_h[l + 1] <= po_h[l]:
+                continue
+            rows = x[a:b].float()
+            for qi in pq_h[po_h[l]:po_h[l + 1]]:
+                if qi < 0:
+                    continue
+                d = scale * (rows @ q[qi].float())
+                if row_term is not None:
+                    d = d + row_term[qi]
+                if col_term is not None:
+                    d = d + col_term[a:b]
+                if clamp_zero:
+                    d = d.clamp_min(0)
+                hit = torch.nonzero(d < threshold[qi]).flatten() if threshold is not None else torch.arange(b - a)
+                c = int(cand_count[qi])
+                take = max(0, min(hit.numel(), cap - c))
+                cand_val[qi, c:c + take] = d[hit[:take]]
+                cand_idx[qi, c:c + take] = (hit[:take] + a).int()
+                cand_count[qi] = c + hit.numel()
+        return
+    rc = N.cuda().afb_ivf_scan(
+        N.ptr(x), _c_long(x.stride(0)), N.ptr(col_term), N.ptr(q), _c_long(q.stride(0)), N.ptr(row_term),
+        N.ptr(threshold), N.ptr(list_off), N.ptr(pair_off), N.ptr(pair_query), N.ptr(cand_val), N.ptr(cand_idx),
+        N.ptr(cand_count), _c_int(n_lists), _c_int(q.shape[0]), _c_int(pair_query.numel()), _c_long(x.shape[0]),
+        _c_int(x.shape[1]), _c_int(cap), _c_float(scale), _c_int(1 if clamp_zero else 0), N.stream_ptr())
+    N.check(rc, "afb_ivf_scan")
+    N.count_launch()

@@ -12,7 +12,8 @@ engine before the timed region (prefill is not part of the decode metric; its ti
 `value`   : tokens/s over K decode steps timed with CUDA events around a host-sync-free burst (graph replays).
 `e2e`     : tokens/s over K steps of LLMEngine.step(), each with its pinned-memory H2D of the step's inputs and
             a D2H read of the sampled tokens (wall clock between synchronisations).
-Other workloads: --workload embed | knn | rerank | cpu.
+Other workloads: --workload embed | rerank | knn (--knn-index flat|ivf, --knn-storage bf16|fp8) | spec | cpu.
+Other arms: --impl reference (the reference's CUDA kernels; embed and rerank) | torch_nccl (library stand-in).
 """
 from __future__ import annotations
 
@@ -28,117 +29,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
-def _clock_sampler():
-    """Starts nvidia-smi sampling SM clocks and throttle reasons every 50 ms for the GPUs of this job.  Only local
-    rank 0 samples (for all of the job's GPUs); started before the warm-up steps because the tool takes longer to
-    produce its first line than a short timed region lasts.  Returns None on the other ranks."""
-    if int(os.environ.get("LOCAL_RANK", "0")) != 0:
-        return None
-    q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-    n = int(os.environ.get("WORLD_SIZE", "1"))
-    try:
-        return subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50",
-                                 "-i", ",".join(str(i) for i in range(n))], stdout=subprocess.PIPE, text=True)
-    except Exception:
-        return None
-
-
-def _clock_summary(proc, t_begin=None, t_end=None):
-    """Median SM clock and the throttle reasons seen between t_begin and t_end (datetime, local time); if the
-    window caught no sample, all samples since the sampler started (warm-up and timed steps) are used."""
-    import datetime
-
-    if proc is None:
-        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["not sampled on this rank"], "samples": 0}
-    proc.terminate()
-    try:
-        out, _ = proc.communicate(timeout=5)
-    except Exception:
-        proc.kill()
-        out = ""
-    rows = []
-    for line in out.strip().splitlines():
-        f = [x.strip() for x in line.split(",")]
-        if len(f) < 10:
-            continue
-        try:
-            ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
-            rows.append((ts, float(f[2]), float(f[3]), f[6:10]))
-        except ValueError:
-            continue
-    window = [r for r in rows if t_begin is not None and t_end is not None and t_begin <= r[0] <= t_end]
-    scope = "timed region"
-    if not window:
-        window, scope = rows, "warm-up and timed steps"
-    sm, mx, reasons = [r[1] for r in window], [r[2] for r in window], set()
-    for r in window:
-        for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
-            if v.lower().startswith("active"):
-                reasons.add(name)
-    return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-            "reasons": sorted(reasons), "samples": len(sm), "scope": scope}
-
-
-def _log(msg):
-    if os.environ.get("ANTFLY_B200_BENCH_VERBOSE"):
-        print(f"[bench rank {os.environ.get('RANK', '0')} t={time.perf_counter():.1f}] {msg}", file=sys.stderr,
-              flush=True)
-
-
-def _dist_setup(n_gpus):
-    import torch
-    import torch.distributed as dist
-
-    import antfly_b200  # noqa: F401  (multicast-off defaults before NCCL / the symmetric allocator start)
-    from antfly_b200.parallel.launch import install_exit_guards
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    # A run that stops making progress dumps every thread's Python stack, drains THIS rank's GPU (poison the
-    # bounded kernel waits, wait out one wait limit) and exits, instead of sitting in a collective until some outer
-    # limit kills it without warning; SIGTERM takes the same path.  The default leaves ample room for a cold
-    # start (first import on a fresh machine, an 8B model build, prefill).
-    limit = int(os.environ.get("ANTFLY_B200_BENCH_WATCHDOG_S", "600" if world > 1 else "0"))
-    if world > 1 or limit > 0:
-        install_exit_guards(local, watchdog_s=limit)
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return rank, world, local
-
-
-def _max_over_ranks(x: float, world: int) -> float:
-    if world == 1:
-        return x
-    import torch
-    import torch.distributed as dist
-
-    t = torch.tensor([x], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def _finish(world):
-    """Multi-rank exit: GPU idle, every rank here, process group destroyed, then leave (see finish_ranks)."""
-    if world <= 1:
-        return
-    from antfly_b200.parallel.launch import finish_ranks
-
-    finish_ranks()
-
-
-def _barrier(world):
-    import torch
-
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-    torch.cuda.synchronize()
+from antfly_b200.utils.benchlib import (barrier as _barrier, clock_sampler as _clock_sampler,  # noqa: E402
+                                        clock_summary as _clock_summary, dist_setup as _dist_setup,
+                                        finish as _finish, log as _log, max_over_ranks as _max_over_ranks)
 
 
 def bench_decode(args):
@@ -392,6 +285,91 @@ def bench_rerank(args):
     _finish(world)
 
 
+def bench_spec(args):
+    """Speculative decoding, RAG-style: Llama-3-70B architecture (80 layers, hidden 8192, 64 heads / 8 KV heads, FFN
+    28672), block-fp8, tensor parallel over the ranks; the draft is the target's first 8 layers with the shared
+    embedding and LM head, 4 draft tokens per round; 16 prompts of 8192 uniform-random token ids, 512 generated
+    tokens each.  A step is one speculative round of the whole batch (draft x 4, one verify pass, accept).  Reports
+    tokens/s over the timed rounds, the acceptance rate and the median time to first token."""
+    import datetime
+
+    import torch
+
+    from antfly_b200 import _native as N
+    from antfly_b200.models.llama import LlamaConfig, LlamaModel
+    from antfly_b200.runtime.engine import LLMEngine
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    rank, world, local = _dist_setup(args.gpus)
+    cfg = LlamaConfig.llama3_70b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    comm = None
+    if world > 1:
+        from antfly_b200.parallel.comm import TpComm
+
+        comm = TpComm(rank, world, torch.device("cuda", local), hidden=cfg.hidden_size, max_tokens=8192)
+    model = LlamaModel.random_init(cfg, device=torch.device("cuda", local), seed=0, tp_rank=rank, tp_size=world,
+                                   comm=comm)
+    B, P, G, Kd = args.spec_batch, args.spec_prompt_len, args.spec_gen_len, 4
+    total = P + G + 32
+    eng = LLMEngine(model, num_blocks=B * ((total + 15) // 16) + 8, page=16, max_batch=B, max_step_tokens=8192,
+                    prefill_chunk=2048, max_seq_len=total, draft_layers=min(8, cfg.num_hidden_layers), spec_k=Kd)
+    g = torch.Generator().manual_seed(4321)
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g).tolist()
+    sp = SamplingParams(max_tokens=G, ignore_eos=True)
+    _barrier(world)
+    rids = [eng.add_request(p, sp) for p in prompts]
+    while eng.sched.snapshot()["waiting"] + eng.sched.snapshot()["prefill"] > 0:
+        eng.step()
+    _barrier(world)
+    ttft = sorted((eng.reqs[r].t_first - eng.reqs[r].t_admit) for r in rids if eng.reqs[r].t_first)
+    W, K = args.warmup, args.steps
+    assert W >= 3
+    clocks = _clock_sampler()
+    for _ in range(W):
+        eng.step()
+    st0 = eng.spec
+    a0, d0, m0 = st0.accepted, st0.drafted, st0.matched
+    h2d0, d2h0, l0 = eng.h2d_bytes, eng.d2h_bytes, N.launches()
+    _barrier(world)
+    tb = datetime.datetime.now()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t1 = time.perf_counter()
+    e0.record()
+    for _ in range(K):
+        if not eng.has_work():
+            break
+        eng.step()
+    e1.record()
+    _barrier(world)
+    wall = _max_over_ranks(time.perf_counter() - t1, world)
+    ms = _max_over_ranks(e0.elapsed_time(e1), world)
+    clk = _clock_summary(clocks, tb, datetime.datetime.now())
+    toks = eng.spec.accepted - a0
+    drafted, matched = eng.spec.drafted - d0, eng.spec.matched - m0
+    if rank == 0:
+        print(json.dumps({
+            "metric": "speculative decode tok/s @70B TP", "value": round(toks / (ms / 1e3), 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations, block-scaled fp8 (e4m3 + e8m0/32) weights",
+            "data": "synthetic: uniform-random token ids, random-init weights",
+            "config": {"model": "Llama-3-70B architecture" + (f" ({cfg.num_hidden_layers} layers)" if args.layers else ""),
+                       "draft": "first 8 layers + shared embedding and LM head, 4 tokens per round",
+                       "global_batch": B, "seq_len": P, "gen_len": G, "parallelism": f"tp{world}",
+                       "acceptance_rate": round(matched / max(drafted, 1), 4),
+                       "tokens_per_round_per_sequence": round(toks / max(K * B, 1), 3),
+                       "ttft_p50_s": round(ttft[len(ttft) // 2], 4) if ttft else None,
+                       "l2": "weights + KV read per round far exceed L2", "kernel_status": N.status()},
+            "clocks": clk,
+            "e2e": {"value": round(toks / wall, 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int((eng.h2d_bytes - h2d0) / max(K, 1)),
+                    "d2h_bytes_per_step": int((eng.d2h_bytes - d2h0) / max(K, 1))},
+            "gpu_launches": int(N.launches() - l0)}))
+    _finish(world)
+
+
 def bench_cpu(args):
     """The CPU fp32 plumbing config: 6-layer BERT-style bi-encoder (hidden 384, 12 heads, FFN 1536) on 32 x 128
     token ids, mean pool + L2 normalise, then exact cosine top-10 against 100k x 384 unit vectors; all in the
@@ -472,14 +450,22 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="decode", choices=["decode", "embed", "knn", "rerank", "cpu"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "embed", "knn", "rerank", "cpu", "spec"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--tp-path", default="fused", choices=["fused", "fused2", "nccl"],
                     help="tensor-parallel collectives: fused into the kernels over peer memory as one-shot "
                          "all-reduces (fused) or as reduce-scatter + all-gather (fused2), or the NCCL baseline")
-    ap.add_argument("--knn-rows", type=int, default=2_000_000, help="database rows per GPU for --workload knn")
+    ap.add_argument("--knn-rows", type=int, default=12_500_000,
+                    help="database rows per GPU for --workload knn (100M rows over 8 GPUs = 12.5M each)")
+    ap.add_argument("--knn-index", default="flat", choices=["flat", "ivf"])
+    ap.add_argument("--knn-storage", default="bf16", choices=["bf16", "fp8"])
+    ap.add_argument("--knn-lists", type=int, default=16384)
+    ap.add_argument("--knn-nprobe", type=int, default=64)
+    ap.add_argument("--spec-batch", type=int, default=16)
+    ap.add_argument("--spec-prompt-len", type=int, default=8192)
+    ap.add_argument("--spec-gen-len", type=int, default=512)
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="debug: time one rank's shard of a tp-way split on a single GPU with no communication")
     ap.add_argument("--force-fused", action="store_true",
@@ -498,6 +484,8 @@ def main():
         bench_rerank(args)
     elif args.workload == "cpu":
         return bench_cpu(args)
+    elif args.workload == "spec":
+        bench_spec(args)
     else:
         from antfly_b200.index.bench_knn import bench_knn
 

@@ -39,6 +39,16 @@ for it in range(2):
     same = recall_at_k(res.ids, full.ids, 20)
     ok = ok and same > 0.999 and bool(torch.allclose(res.distances, full.distances, atol=1e-3))
     print(f"rank {rank}: sharded search agreement={same:.4f}", flush=True)
+# sharded IVF: jointly trained centroids, local list scans, the same pushed merge
+from antfly_b200.index.ivf import IVFIndex
+from antfly_b200.index.sharded import ShardedIVFIndex
+siv = ShardedIVFIndex(x[rank * 4000:(rank + 1) * 4000], 32, "cosine", rank, world, 4000, max_queries=64, max_k=32)
+for it in range(2):
+    res = siv.search(q, 20, nprobe=32)             # all lists probed: must equal the exact search
+    full = FlatIndex(x, metric="cosine").search(q, 20)
+    same = recall_at_k(res.ids, full.ids, 20)
+    ok = ok and same > 0.999
+    print(f"rank {rank}: sharded ivf (all lists) agreement={same:.4f}", flush=True)
 st = N.status()
 print(f"rank {rank}: DP_SHARDED_CHECK {'OK' if ok and st == 0 else 'FAILED'} status={st}", flush=True)
 finish_ranks()

@@ -371,3 +371,80 @@ def test_recall_table(dataset, metric, kind, floor):
         found = torch.tensor([(idx.search(qb[i], 10)[0] + [-1] * 10)[:10] for i in range(32)])
     r = recall_at_k(found, truth.ids, 10)
     assert r >= floor, (dataset, metric, kind, r)
+
+
+@pytest.mark.parametrize("metric", ["l2_squared", "cosine", "inner_product"])
+@pytest.mark.parametrize("nprobe", [1, 5, 12])
+def test_ivf_fixed_launch_sequence_equals_the_host_driven_walk(metric, nprobe):
+    """The one-sequence search (pair sort, seed list-scan, thresholded list-scan, select) returns exactly what the
+    host-driven walk over the probed lists returns."""
+    from antfly_b200.index.ivf import IVFIndex
+
+    x, q = _dataset("clustered", 3000, 32, seed=11)
+    xb, qb = x.to(torch.bfloat16).float(), q.to(torch.bfloat16).float()
+    idx = IVFIndex(xb, 40, metric=metric)
+    a = idx.search(qb, 10, nprobe=nprobe)
+    b = idx._search_host(qb, 10, nprobe=nprobe)
+    assert torch.equal(a.ids, b.ids)
+    torch.testing.assert_close(a.distances, b.distances, atol=1e-5, rtol=1e-5)
+
+
+def test_ivf_search_makes_no_host_round_trip_between_its_launches():
+    """Inside ``search(check=False)`` nothing reads a device value on the host: the kernel wrappers (whose CPU
+    fallbacks are exempt here) are the only places where data is touched."""
+    from antfly_b200.index import ivf as IVF
+    from antfly_b200.ops import index_ops as IX
+
+    x, q = _dataset("clustered", 2000, 32, seed=5)
+    idx = IVF.IVFIndex(x.to(torch.bfloat16).float(), 32, metric="cosine")
+    counts = {"n": 0, "exempt": 0}
+
+    def counting(name):
+        orig = getattr(torch.Tensor, name)
+
+        def f(self, *a, **k):
+            if not counts["exempt"]:
+                counts["n"] += 1
+            return orig(self, *a, **k)
+        return name, orig, f
+
+    def exempt(fn):
+        def g(*a, **k):
+            counts["exempt"] += 1
+            try:
+                return fn(*a, **k)
+            finally:
+                counts["exempt"] -= 1
+        return g
+
+    patched = [counting(n) for n in ("item", "tolist", "cpu", "numpy", "__int__", "__bool__", "__float__", "__index__")]
+    wrapped = {n: getattr(IX, n) for n in ("ivf_scan", "topk_select", "score_filter", "row_sqnorm")}
+    try:
+        for n, fn in wrapped.items():
+            setattr(IX, n, exempt(fn))
+        for n, _, f in patched:
+            setattr(torch.Tensor, n, f)
+        res = idx.search(q.to(torch.bfloat16).float(), 10, nprobe=8, check=False)
+    finally:
+        for n, orig, _ in patched:
+            setattr(torch.Tensor, n, orig)
+        for n, fn in wrapped.items():
+            setattr(IX, n, fn)
+    assert counts["n"] == 0
+    assert res.overflow is not None and int(res.overflow) == 0
+
+
+def test_ivf_overflow_is_reported_and_repaired():
+    """A candidate buffer that is too small for the thresholded pass: ``check=False`` reports it, ``check=True``
+    repeats on the safe path and returns the exact probed-list result."""
+    from antfly_b200.index.ivf import IVFIndex
+
+    x, q = _dataset("uniform", 3000, 32, seed=9)
+    xb, qb = x.to(torch.bfloat16).float(), q.to(torch.bfloat16).float()
+    idx = IVFIndex(xb, 8, metric="l2_squared")
+    want = idx._search_host(qb, 10, nprobe=8)
+    idx.cand_cap = 16
+    flagged = idx.search(qb, 10, nprobe=8, check=False)
+    assert int(flagged.overflow) == 1
+    got = idx.search(qb, 10, nprobe=8)
+    assert torch.equal(got.ids, want.ids)
