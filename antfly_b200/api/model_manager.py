@@ -61,7 +61,8 @@ def _param_bytes(pipeline) -> int:
 class ModelManager:
     def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
                  kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True, keep_alive_s: float = 0.0,
-                 max_memory_mb: int = 0, strategies: Optional[Dict[str, str]] = None, clock=time.time):
+                 max_memory_mb: int = 0, strategies: Optional[Dict[str, str]] = None, clock=time.time,
+                 tensor_parallel: Optional[tuple] = None):
         """``max_loaded_models`` 0 = unlimited; ``keep_alive_s`` > 0 unloads directory-backed models idle for that
         long (checked on every access and by :meth:`evict_idle`); ``max_memory_mb`` > 0 is an advisory budget on
         parameter bytes, enforced by unloading least-recently-used models; ``strategies`` maps model names to
@@ -75,6 +76,16 @@ class ModelManager:
         self.kv_blocks, self.max_batch, self.prefix_cache = kv_blocks, max_batch, prefix_cache
         self._models: "OrderedDict[str, LoadedModel]" = OrderedDict()
         self._lock = threading.Lock()
+        # (rank, world, comm): BERT-family encoders and cross-encoders are sharded over the ranks of a
+        # tensor-parallel job (every rank serves the same requests in lockstep), the reference's
+        # TERMITE_MLX_DISTRIBUTED_MODE=tensor_parallel deployment (zig/pkg/inference/docs/RERANKING.md:32-43)
+        self.tensor_parallel = tensor_parallel
+
+    def _tp(self, model):
+        if self.tensor_parallel is not None and isinstance(model, BertModel):
+            rank, world, comm = self.tensor_parallel
+            return model.tensor_parallel(rank, world, comm)
+        return model
 
     # -- registration of in-memory models ------------------------------------------------------------------
     def register(self, name: str, task: str, pipeline, tokenizer, info: Optional[dict] = None) -> LoadedModel:
@@ -93,7 +104,7 @@ class ModelManager:
             cfg = cfgs[size]
             if task == "reranker":
                 cfg.num_labels = 1
-            model = BertModel.random_init(cfg, device=dev, seed=seed)
+            model = self._tp(BertModel.random_init(cfg, device=dev, seed=seed))
             tok = ByteTokenizer(cfg.vocab_size)
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
             return self.register(name, task, pipe, tok, {"hidden_size": cfg.hidden_size, "random_init": True})
@@ -272,7 +283,7 @@ class ModelManager:
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         elif task in ("embedder", "reranker"):
             cfg = BertConfig.from_hf(cfg_d)
-            model = BertModel.from_state_dict(cfg, sd, device=self.device)
+            model = self._tp(BertModel.from_state_dict(cfg, sd, device=self.device))
             pipe = Embedder(model, tok) if task == "embedder" else CrossEncoderReranker(model, tok)
         else:
             vlm = None
@@ -341,7 +352,7 @@ class ModelManager:
             from ..models.deberta import DebertaConfig, DebertaModel
 
             return DebertaModel.from_state_dict(DebertaConfig.from_hf(cfg_d), sd, device=self.device)
-        return BertModel.from_state_dict(BertConfig.from_hf(cfg_d), sd, device=self.device)
+        return self._tp(BertModel.from_state_dict(BertConfig.from_hf(cfg_d), sd, device=self.device))
 
     def get(self, name: str, task: str) -> LoadedModel:
         key = f"{task}:{name}"

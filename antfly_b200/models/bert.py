@@ -107,6 +107,35 @@ class BertModel:
         self.w = weights
         self.device = weights["emb.word"].device
         self.dtype = weights["emb.word"].dtype
+        self.tp_rank, self.tp_size, self.comm = 0, 1, None
+
+    def tensor_parallel(self, rank: int, world: int, comm) -> "BertModel":
+        """This rank's shard of the encoder under the Megatron split the reference uses for its BERT / RoBERTa
+        encoder and cross-encoder (zig/pkg/inference/src/architectures/bert.zig:309-352): query / key / value and the
+        FFN's first linear are column-parallel (whole heads, a slice of the intermediate features), the attention
+        output and the FFN's second linear are row-parallel and followed by an all-reduce (``comm.all_reduce``, the
+        reference's all_sum at ops/mlx_compute.zig:1549); their biases are added once, after the reduction.
+        Embeddings, LayerNorms and heads stay replicated."""
+        cfg = self.cfg
+        H, F, nh = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads
+        if world == 1:
+            return self
+        if H % world or nh % world or F % world:
+            raise ValueError(f"hidden {H}, heads {nh} and intermediate size {F} must all be divisible by {world} ranks")
+        hs, fs = H // world, F // world
+        w = dict(self.w)
+        for l in range(cfg.num_hidden_layers):
+            p = f"l{l}."
+            qkv_w, qkv_b = self.w[p + "qkv.w"], self.w[p + "qkv.b"]
+            rows = torch.cat([torch.arange(i * H + rank * hs, i * H + (rank + 1) * hs) for i in range(3)]).to(qkv_w.device)
+            w[p + "qkv.w"], w[p + "qkv.b"] = qkv_w[rows].contiguous(), qkv_b[rows].contiguous()
+            w[p + "o.w"] = self.w[p + "o.w"][:, rank * hs:(rank + 1) * hs].contiguous()
+            w[p + "ff1.w"] = self.w[p + "ff1.w"][rank * fs:(rank + 1) * fs].contiguous()
+            w[p + "ff1.b"] = self.w[p + "ff1.b"][rank * fs:(rank + 1) * fs].contiguous()
+            w[p + "ff2.w"] = self.w[p + "ff2.w"][:, rank * fs:(rank + 1) * fs].contiguous()
+        m = BertModel(cfg, w)
+        m.tp_rank, m.tp_size, m.comm = rank, world, comm
+        return m
 
     # ------------------------------------------------------------------------------------------------
     @classmethod
@@ -219,6 +248,8 @@ class BertModel:
         x = Dn.bert_embed_ln(b.ids, b.positions, b.type_ids, w["emb.word"], w["emb.pos"], w["emb.type"],
                              w["emb.ln.g"], w["emb.ln.b"], cfg.layer_norm_eps)
         T = x.shape[0]
+        if self.tp_size > 1:
+            return self._encode_tp(b, x)
         for l in range(cfg.num_hidden_layers):
             p = f"l{l}."
             qkv = Dn.gemm_bf16(x, w[p + "qkv.w"], bias=w[p + "qkv.b"])
@@ -230,6 +261,28 @@ class BertModel:
             x = Dn.norm(h, w[p + "ln1.g"], w[p + "ln1.b"], eps=cfg.layer_norm_eps)
             f = Dn.gemm_bf16(x, w[p + "ff1.w"], bias=w[p + "ff1.b"], act=cfg.hidden_act)
             h = Dn.gemm_bf16(f, w[p + "ff2.w"], bias=w[p + "ff2.b"], residual=x)
+            x = Dn.norm(h, w[p + "ln2.g"], w[p + "ln2.b"], eps=cfg.layer_norm_eps)
+        return x
+
+    def _encode_tp(self, b: PackedBatch, x: torch.Tensor) -> torch.Tensor:
+        """Tensor-parallel layers: local heads / local FFN slice, two all-reduces per layer (fp32 partial sums, so
+        the result does not depend on how a bf16 rounding of each rank's partial would fall)."""
+        cfg, w = self.cfg, self.w
+        H, nh = cfg.hidden_size, cfg.num_attention_heads
+        D, hs, nl = H // nh, H // self.tp_size, nh // self.tp_size
+        T = x.shape[0]
+        for l in range(cfg.num_hidden_layers):
+            p = f"l{l}."
+            qkv = Dn.gemm_bf16(x, w[p + "qkv.w"], bias=w[p + "qkv.b"])
+            q, k, v = (qkv[:, i * hs:(i + 1) * hs].view(T, nl, D) for i in range(3))
+            ctx = A.varlen_attention(q, k, v, b.starts, b.lens, b.max_len).view(T, hs)
+            part = Dn.gemm_bf16(ctx, w[p + "o.w"], out_dtype=torch.float32)
+            part = self.comm.all_reduce(part)
+            h = (part + w[p + "o.b"].float() + x.float()).to(x.dtype)
+            x = Dn.norm(h, w[p + "ln1.g"], w[p + "ln1.b"], eps=cfg.layer_norm_eps)
+            f = Dn.gemm_bf16(x, w[p + "ff1.w"], bias=w[p + "ff1.b"], act=cfg.hidden_act)
+            part = self.comm.all_reduce(Dn.gemm_bf16(f, w[p + "ff2.w"], out_dtype=torch.float32))
+            h = (part + w[p + "ff2.b"].float() + x.float()).to(x.dtype)
             x = Dn.norm(h, w[p + "ln2.g"], w[p + "ln2.b"], eps=cfg.layer_norm_eps)
         return x
 

@@ -401,3 +401,60 @@ def test_largest_power_of_two_group_and_first_proposal_wins():
     b = ElasticGroup(store, 1, [0, 1, 2, 3], dead_after_s=5.0)
     b.form = lambda: None
     assert b.regroup() == [1, 2] and b.rank == 0 and b.world == 2 and b.epoch == 1
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Tensor-parallel encoder / cross-encoder: the reference's one real tensor-parallel consumer; it verifies a 2-rank
+# run against the single-rank scores within 5e-4 (zig/pkg/inference/docs/RERANKING.md:109-112,
+# scripts/verify_cross_encoder_rerank.sh).
+# ---------------------------------------------------------------------------------------------------------------
+def _bert_pairs():
+    from antfly_b200.models.bert import pack_sequences
+
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(5, 500, (int(n),), generator=g).tolist() for n in (12, 30, 7, 19)]
+    types = [[0] * (len(s) // 2) + [1] * (len(s) - len(s) // 2) for s in seqs]
+    return pack_sequences(seqs, types)
+
+
+def _bert_tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    from antfly_b200.models.bert import BertConfig, BertModel
+    from antfly_b200.parallel.comm import TpComm, init_process_group
+
+    init_process_group(backend="gloo", timeout_s=60)
+    cfg = BertConfig(hidden_size=128, num_hidden_layers=3, num_attention_heads=4, intermediate_size=256,
+                     vocab_size=512, num_labels=1)
+    full = BertModel.random_init(cfg, device="cpu", seed=0, dtype=torch.float32)
+    model = full.tensor_parallel(rank, world, TpComm(rank, world, torch.device("cpu")))
+    assert model.w["l0.qkv.w"].shape == (3 * 128 // world, 128) and model.w["l0.ff2.w"].shape == (128, 256 // world)
+    b = _bert_pairs()
+    q.put((rank, torch.sigmoid(model.classify(b)).flatten().tolist(), model.embed(b).numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_cross_encoder_matches_single_rank_within_reference_tolerance(world):
+    from antfly_b200.models.bert import BertConfig, BertModel
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_bert_tp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    cfg = BertConfig(hidden_size=128, num_hidden_layers=3, num_attention_heads=4, intermediate_size=256,
+                     vocab_size=512, num_labels=1)
+    single = BertModel.random_init(cfg, device="cpu", seed=0, dtype=torch.float32)
+    b = _bert_pairs()
+    want = torch.sigmoid(single.classify(b)).flatten()
+    want_emb = single.embed(b)
+    for _rank, scores, emb in got:
+        assert (torch.tensor(scores) - want).abs().max() <= 5e-4
+        torch.testing.assert_close(torch.from_numpy(emb), want_emb, atol=5e-4, rtol=1e-3)
