@@ -17,6 +17,56 @@ _c_long = ctypes.c_long
 _c_float = ctypes.c_float
 
 
+# The tcgen05 / tensor-memory flash kernel (csrc/kernels/attention_tc.cu) serves the compute-bound shapes -- encoder
+# attention and paged prefill with 64- or 128-wide heads -- when it is switched on: ANTFLY_B200_ATTN_TC=1 in the
+# environment or set_tensor_core_attention(True).  It is off by default until it has been validated on the
+# hardware it runs on; the mma.sync kernel in attention.cu is the default and the fallback.
+_TC = {"on": None}
+
+
+def tensor_core_attention_enabled() -> bool:
+    if _TC["on"] is None:
+        import os
+
+        _TC["on"] = os.environ.get("ANTFLY_B200_ATTN_TC", "0") == "1"
+    return bool(_TC["on"])
+
+
+def set_tensor_core_attention(on: bool) -> None:
+    _TC["on"] = bool(on)
+
+
+def attention_tc(q, k, v, starts, lens, kv_lens, max_q_len: int, causal: bool, window: int = 0,
+                 scale: Optional[float] = None, out: Optional[torch.Tensor] = None, k_cache=None, v_cache=None,
+                 block_tables=None) -> torch.Tensor:
+    """Direct entry to the tensor-core flash kernel.  Contiguous mode: k / v [T, Hkv, D] views (kv_lens = lens).
+    Paged mode: k_cache / v_cache [num_blocks, page, Hkv, D] + block_tables, query rows = the last lens[b]
+    positions of kv_lens[b] keys.  D in (64, 128).  Raises NativeError for shapes the kernel does not take."""
+    T, Hq, D = q.shape
+    paged = k_cache is not None
+    Hkv = k_cache.shape[2] if paged else k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    assert q.is_cuda and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D
+    if out is None:
+        out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
+    if paged:
+        assert k_cache.dtype == torch.bfloat16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+        page, nblk = k_cache.shape[1], k_cache.shape[0]
+        args = (None, None, _c_long(0), N.ptr(k_cache), N.ptr(v_cache), N.ptr(block_tables),
+                _c_int(block_tables.shape[1]), _c_int(page), _c_long(nblk))
+    else:
+        assert k.stride(2) == 1 and k.stride(1) == D and v.stride(1) == D and k.stride(0) == v.stride(0)
+        args = (N.ptr(k), N.ptr(v), _c_long(k.stride(0)), None, None, None, _c_int(0), _c_int(16), _c_long(0))
+    rc = N.cuda().afb_attention_tc(
+        N.ptr(q), _c_long(q.stride(0)), *args, N.ptr(starts), N.ptr(lens), N.ptr(kv_lens), N.ptr(out),
+        _c_long(out.stride(0)), _c_int(starts.numel()), _c_int(T), _c_int(Hq), _c_int(Hkv), _c_int(D),
+        _c_int(max_q_len), _c_int(1 if causal else 0), _c_int(window), _c_float(scale), _c_int(1 if paged else 0),
+        N.stream_ptr())
+    N.check(rc, "afb_attention_tc")
+    N.count_launch()
+    return out
+
+
 def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, scale: Optional[float] = None,
                      out: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
     """q [T, Hq, D], k/v [T, Hkv, D] (may be strided views of one fused QKV buffer); sequences are the packed
@@ -48,6 +98,9 @@ def varlen_attention(q, k, v, starts, lens, max_len: int, causal: bool = False, 
     if out is None:
         out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     B = starts.numel()
+    if tensor_core_attention_enabled() and D in (64, 128) and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0 \
+            and out.stride(0) % 8 == 0 and out.stride(1) == D:
+        return attention_tc(q, k, v, starts, lens, lens, max_len, causal, window, scale, out)
     rc = N.cuda().afb_attention(
         N.ptr(q), _c_long(q.stride(0)), N.ptr(k), N.ptr(v), _c_long(k.stride(0)), None, None, None, _c_int(0),
         _c_int(16), N.ptr(starts), N.ptr(lens), N.ptr(lens), N.ptr(out), _c_long(out.stride(0)), None, None,
@@ -106,6 +159,16 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
         decode = max_q_len * G <= 16
     if not decode:
         num_splits = 1
+        if (tensor_core_attention_enabled() and causal and D in (64, 128) and page % 8 == 0
+                and (128 if D == 64 else 64) % page == 0 and q.stride(0) % 8 == 0 and k_cache.is_contiguous()
+                and v_cache.is_contiguous()):
+            o = attention_tc(q, None, None, q_starts, q_lens, kv_lens, max_q_len, True, window, scale, out,
+                             k_cache=k_cache, v_cache=v_cache, block_tables=block_tables)
+            if mx_terms:
+                from . import quant as Q
+
+                return Q.quantize_mx(o.view(T, Hq * D), terms=mx_terms)
+            return o
     mx = None
     if mx_terms and num_splits > 1 and (Hq * D) % 128 == 0:
         from . import quant as Q
