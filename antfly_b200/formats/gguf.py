@@ -19,9 +19,10 @@ GGUF_MAGIC = b"GGUF"
 TYPE_NAMES = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
               11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K", 16: "IQ2_XXS", 17: "IQ2_XS", 18: "IQ3_XXS",
               19: "IQ1_S", 20: "IQ4_NL", 21: "IQ3_S", 22: "IQ2_S", 23: "IQ4_XS", 24: "I8", 25: "I16", 26: "I32",
-              27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16", 34: "TQ1_0", 35: "TQ2_0", 36: "I2_S", 37: "I8_S", 39: "MXFP4",
-              40: "NVFP4"}
-SUPPORTED = {0, 1, 2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 15, 20, 23, 30, 34, 35, 36, 37, 39, 40}
+              27: "I64", 28: "F64", 29: "IQ1_M", 30: "BF16", 34: "TQ1_0", 35: "TQ2_0", 36: "I2_S", 37: "I8_S", 38: "TL1", 39: "MXFP4",
+              40: "NVFP4", 41: "Q1_0"}
+SUPPORTED = {0, 1, 2, 3, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25, 26, 27, 28, 29, 30,
+             34, 35, 36, 37, 39, 40, 41}
 _SCALARS = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 
 
@@ -88,6 +89,18 @@ class GGUFFile:
     def tensor(self, name: str) -> torch.Tensor:
         """Dequantised fp32 tensor."""
         info = self.tensors[name]
+        bitnet = str(self.metadata.get("general.architecture", "")) in ("bitnet", "bitnet-b1.58")
+        if info.type == 38 or (info.type == 39 and bitnet):
+            # BitNet lookup-table layouts: whole-tensor tilings, not block formats (formats/bitnet_tl.py)
+            from . import bitnet_tl as TL
+
+            if len(info.shape) != 2:
+                raise NotImplementedError("TL1 / TL2 tensors are matrices")
+            rows, cols = info.shape
+            nbytes = TL.tl1_nbytes(rows, cols) if info.type == 38 else TL.tl2_nbytes(rows, cols)
+            src = np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=self.data_start + info.offset)
+            fn = TL.dequantize_tl1 if info.type == 38 else TL.dequantize_tl2
+            return torch.from_numpy(fn(src, rows, cols))
         if info.type not in SUPPORTED:
             raise NotImplementedError(f"GGUF tensor type {info.type_name} is not supported")
         lib = N.host()

@@ -100,6 +100,11 @@ const float kMxfp4Values[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, 
 
 extern "C" {
 
+// IQ codebook formats, Q8_1, Q1_0 and the plain integer / f64 types live in gguf_iq.cpp.
+long afb_gguf_iq_block_bytes(int type);
+long afb_gguf_iq_block_values(int type);
+int afb_gguf_iq_dequantize(int type, const uint8_t* src, float* dst, long n_values);
+
 // type ids (ggml numbering): 0 F32, 1 F16, 2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K,
 // 13 Q5_K, 14 Q6_K, 15 Q8_K, 20 IQ4_NL, 23 IQ4_XS, 30 BF16, 34 TQ1_0, 35 TQ2_0, 39 MXFP4, 40 NVFP4.
 long afb_gguf_block_bytes(int type) {
@@ -110,7 +115,7 @@ long afb_gguf_block_bytes(int type) {
     case 15: return 292; case 20: return 18; case 23: return 136; case 34: return 54; case 35: return 66;
     case 39: return 17; case 40: return 36;
     case 36: return 32; case 37: return 1;
-    default: return -1;
+    default: return afb_gguf_iq_block_bytes(type);
   }
 }
 long afb_gguf_block_values(int type) {
@@ -120,7 +125,7 @@ long afb_gguf_block_values(int type) {
     case 2: case 3: case 6: case 7: case 8: case 20: case 39: return 32;
     case 40: return 64;
     case 10: case 11: case 12: case 13: case 14: case 15: case 23: case 34: case 35: return 256;
-    default: return -1;
+    default: return afb_gguf_iq_block_values(type);
   }
 }
 
@@ -425,7 +430,7 @@ int afb_gguf_dequantize(int type, const uint8_t* src, float* dst, long n_values)
       }
       return 0;
     }
-    default: return -1;
+    default: return afb_gguf_iq_dequantize(type, src, dst, n_values);
   }
 }
 

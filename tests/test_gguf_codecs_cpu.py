@@ -13,12 +13,13 @@ gguf = pytest.importorskip("gguf")
 from antfly_b200 import _native as N
 
 TYPES = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS",
-         "TQ1_0", "TQ2_0", "MXFP4", "NVFP4"]
+         "TQ1_0", "TQ2_0", "MXFP4", "NVFP4", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"]
 
 # byte offsets of the fp16 scale fields inside a block (random bytes there could be inf / NaN)
 HALF_FIELDS = {"Q4_0": [0], "Q4_1": [0, 2], "Q5_0": [0], "Q5_1": [0, 2], "Q8_0": [0], "Q2_K": [80, 82], "Q3_K": [108],
                "Q4_K": [0, 2], "Q5_K": [0, 2], "Q6_K": [208], "IQ4_NL": [0], "IQ4_XS": [0], "TQ1_0": [52],
-               "TQ2_0": [64], "MXFP4": [], "NVFP4": []}
+               "TQ2_0": [64], "MXFP4": [], "NVFP4": [], "IQ2_XXS": [0], "IQ2_XS": [0], "IQ2_S": [0], "IQ3_XXS": [0],
+               "IQ3_S": [0], "IQ1_S": [0], "IQ1_M": []}
 
 
 def _ours(type_id: int, raw: np.ndarray, n: int) -> np.ndarray:
@@ -52,6 +53,13 @@ def test_dequantize_matches_gguf_package(name):
         raw[:, :4] = rng.integers(0x18, 0x60, size=(blocks, 4))
     if name == "TQ1_0":
         raw[:, :52] = rng.integers(0, 243, size=(blocks, 52))  # five base-3 digits per byte
+    if name == "IQ1_M":
+        # the block's f16 scale is spread over the top nibbles of the four scale words: keep it finite
+        scale = rng.uniform(0.1, 2.0, size=blocks).astype(np.float16).view(np.uint16)
+        words = raw[:, 48:56].copy().view(np.uint16).reshape(blocks, 4)
+        for i in range(4):
+            words[:, i] = (words[:, i] & 0x0FFF) | (((scale >> (4 * i)) & 0xF) << 12).astype(np.uint16)
+        raw[:, 48:56] = words.view(np.uint8).reshape(blocks, 8)
     try:
         want = gguf.quants.dequantize(raw.reshape(-1), qt).astype(np.float32).reshape(-1)
     except NotImplementedError:
@@ -142,3 +150,77 @@ def test_bitnet_i2s_and_i8s_decoding(tmp_path):
     torch.testing.assert_close(f.tensor("x"), w[:1])            # the tensor after it starts where it should
     with pytest.raises(ValueError):
         GG.pack_i2s(np.zeros(100, dtype=np.float32))
+
+
+
+def test_simple_types_q8_1_q1_0_and_integers():
+    """Q8_1 (f16 d, f16 sum, 32 int8), Q1_0 (f16 d, 128 sign bits; the reference's quantizeQ1_0Block writes scale =
+    mean |x| and bit = x >= 0, zig/pkg/inference/src/gguf/quant_codec.zig:677-693) and the plain I8 / I16 / I32 /
+    I64 / F64 element types."""
+    rng = np.random.default_rng(5)
+    x = rng.normal(size=64).astype(np.float32)
+    d = np.abs(x.reshape(2, 32)).max(1) / 127.0
+    q = np.round(x.reshape(2, 32) / d[:, None]).astype(np.int8)
+    blk = np.zeros((2, 36), dtype=np.uint8)
+    blk[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(2, 2)
+    blk[:, 4:] = q.view(np.uint8)
+    got = _ours(9, blk.reshape(-1), 64)
+    np.testing.assert_allclose(got, (d.astype(np.float16).astype(np.float32)[:, None] * q).reshape(-1), rtol=1e-6)
+    y = rng.normal(size=256).astype(np.float32).reshape(2, 128)
+    blk = np.zeros((2, 18), dtype=np.uint8)
+    sc = np.abs(y).mean(1).astype(np.float16)
+    blk[:, 0:2] = sc.view(np.uint8).reshape(2, 2)
+    blk[:, 2:] = np.packbits((y >= 0).astype(np.uint8), axis=1, bitorder="little")
+    got = _ours(41, blk.reshape(-1), 256).reshape(2, 128)
+    np.testing.assert_array_equal(got, np.where(y >= 0, 1.0, -1.0) * sc.astype(np.float32)[:, None])
+    for tid, dt in ((24, np.int8), (25, np.int16), (26, np.int32), (27, np.int64), (28, np.float64)):
+        v = (rng.normal(size=17) * 100).astype(dt)
+        np.testing.assert_allclose(_ours(tid, v.view(np.uint8), 17), v.astype(np.float32))
+
+
+def test_bitnet_tl1_tl2_layouts_match_the_reference_golden_cases():
+    """The reference's own unit tests as golden vectors (zig/pkg/inference/src/gguf/quant_codec.zig:4061-4200):
+    a TL1 matrix of 0x44 bytes with byte 0 = 0x84 and scale 2; a TL2 matrix with two 0xd0 code bytes, one sign
+    byte and scale 3; plus a round trip of random ternary matrices through an encoder that inverts the index maps."""
+    from antfly_b200.formats import bitnet_tl as TL
+
+    rows = cols = 1536
+    raw = np.full(rows * cols // 4 + 32, 0x44, dtype=np.uint8)
+    raw[0] = 0x84
+    raw[rows * cols // 4: rows * cols // 4 + 4] = np.array([2.0], dtype="<f4").view(np.uint8)
+    v = TL.dequantize_tl1(raw, rows, cols)
+    assert (v[0, 0], v[0, 1], v[0, 2]) == (2.0, 2.0, 0.0)
+    assert TL.tl1_nbytes(rows, cols) == raw.size
+
+    n = TL.tl2_nbytes(rows, cols)
+    raw = np.zeros(n, dtype=np.uint8)
+    raw[0] = raw[1] = 0xD0
+    raw[rows * cols // 6 + 3] = 0x80
+    raw[n - 32: n - 28] = np.array([3.0], dtype="<f4").view(np.uint8)
+    v = TL.dequantize_tl2(raw, rows, cols)
+    assert v[0, :4].tolist() == [3.0, 3.0, 3.0, 0.0]
+    assert v[1, :3].tolist() == [-3.0, -3.0, -3.0]
+
+    # every (row, column) of a preset shape with a pair tail maps to its own code / sign position
+    rows, cols = 1024, 4096
+    n = TL.tl2_nbytes(rows, cols)
+    raw = np.zeros(n, dtype=np.uint8)
+    three_cols = cols - cols % 96
+    v_len, s_len = rows * three_cols // 6, rows * three_cols // 24
+    raw[v_len + s_len: v_len + s_len + rows * (cols - three_cols) // 4] = 0x44      # pair code 4 = (0, 0)
+    raw[n - 32: n - 28] = np.array([2.0], dtype="<f4").view(np.uint8)
+    base = TL.dequantize_tl2(raw, rows, cols)
+    assert not base.any()
+    rng = np.random.default_rng(0)
+    raw[:v_len] = rng.integers(0, 256, v_len, dtype=np.uint8) & 0xDD | 0x11        # codes in 1..13
+    raw[v_len:v_len + s_len] = rng.integers(0, 256, s_len, dtype=np.uint8)
+    full = TL.dequantize_tl2(raw, rows, cols)
+    tri = np.abs(full[:, :three_cols]).reshape(rows, -1, 3) / 2.0
+    assert set(np.unique(full)) <= {-2.0, 0.0, 2.0}
+    # flipping one sign byte flips exactly eight triples
+    raw2 = raw.copy()
+    raw2[v_len + 7] ^= 0xFF
+    diff = (TL.dequantize_tl2(raw2, rows, cols) != full)
+    changed = diff[:, :three_cols].reshape(rows, -1, 3).any(-1).sum()
+    nonzero = (tri.reshape(rows, -1, 3).any(-1))
+    assert 1 <= changed <= 8 and not diff[:, three_cols:].any() and nonzero.any()
