@@ -158,6 +158,14 @@ class ModelManager:
 
             model = LlamaModel.from_state_dict(LlamaConfig.from_hf(cfg_d), sd, device=self.device)
             pipe = DecoderEmbedder(model, tok)
+        elif task == "generator" and cfg_d.get("model_type") in ("qwen3_5", "qwen3_5_text", "qwen3_next"):
+            # hybrid decoder (delta-rule + gated attention layers): per-sequence state kept by the model
+            from ..models.qwen35 import Qwen35Config, Qwen35Model
+            from ..pipelines.generation import StatefulGenerator
+
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            model = Qwen35Model.from_state_dict(Qwen35Config.from_hf(cfg_d), sd, device=self.device, dtype=dt)
+            pipe = StatefulGenerator(model, tok, mf.chat_template)
         elif task == "rewriter" or (task == "generator" and cfg_d.get("model_type") in ("t5", "mt5", "bart",
                                                                                          "mbart")):
             from ..models.t5 import T5Config, T5Model

@@ -120,3 +120,79 @@ class Generator:
             "prefill": (self.engine.timing["prefill_s"] - p0) * 1e3,
             "decode": (self.engine.timing["decode_s"] - d0) * 1e3, "total": (t3 - t0) * 1e3})
         return out
+
+
+class StatefulGenerator:
+    """Generation pipeline for decoders that carry a per-sequence state of their own instead of block tables in
+    the paged-KV engine (hybrid recurrent / attention decoders such as Qwen3.5, and decoders with per-layer cache
+    geometries such as Gemma-4): same interface as :class:`Generator`, one request at a time.  The model provides
+    ``forward(ids, state) -> (logits [T, vocab], state)``; sampling follows the request's temperature / top-k /
+    top-p / min-p on the last position's logits (greedy at temperature <= 0)."""
+
+    def __init__(self, model, tokenizer, chat_template: Optional[str] = None, add_bos: bool = True,
+                 eos_token_id: Optional[int] = None):
+        self.model, self.tokenizer, self.add_bos = model, tokenizer, add_bos
+        self.template = ChatTemplate(chat_template)
+        self.vlm = None
+        self.eos = eos_token_id if eos_token_id is not None else tokenizer.special.eos_id
+
+    def _pick(self, logits, params: SamplingParams, gen) -> int:
+        import torch
+
+        if params.greedy:
+            return int(logits.argmax())
+        lg = logits.float() / params.temperature
+        if params.top_k:
+            kth = lg.topk(min(params.top_k, lg.numel())).values[-1]
+            lg = lg.masked_fill(lg < kth, float("-inf"))
+        p = lg.softmax(-1)
+        if params.top_p < 1.0:
+            sp, si = p.sort(descending=True)
+            keep = (sp.cumsum(0) - sp) < params.top_p
+            p = torch.zeros_like(p).scatter(0, si[keep], sp[keep])
+        if params.min_p > 0.0:
+            p = p.masked_fill(p < params.min_p * p.max(), 0.0)
+        return int(torch.multinomial(p / p.sum(), 1, generator=gen))
+
+    def generate(self, messages_or_prompt, params: SamplingParams, raw_prompt: bool = False,
+                 on_delta: Optional[Callable[[str], None]] = None, images=None) -> GenerationOutput:
+        import torch
+
+        if images:
+            raise ValueError("this model does not take images")
+        t0 = time.perf_counter()
+        if isinstance(messages_or_prompt, str):
+            prompt = messages_or_prompt if raw_prompt else self.template.apply(
+                [{"role": "user", "content": messages_or_prompt}])
+        else:
+            prompt = self.template.apply(messages_or_prompt)
+        t1 = time.perf_counter()
+        ids = self.tokenizer.encode_prompt(prompt, add_bos=self.add_bos)
+        t2 = time.perf_counter()
+        dev = self.model.device
+        gen = torch.Generator(device="cpu")
+        if params.seed is not None:
+            gen.manual_seed(params.seed)
+        logits, st = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev))
+        t3 = time.perf_counter()
+        toks: List[int] = []
+        shown = ""
+        finish = "length"
+        for _ in range(params.max_tokens):
+            tok = self._pick(logits[-1].cpu(), params, gen)
+            toks.append(tok)
+            if (not params.ignore_eos and tok == self.eos) or tok in params.stop_token_ids:
+                finish = "stop"
+                break
+            if on_delta is not None:
+                full = self.tokenizer.decode(toks)
+                if not full.endswith("\ufffd"):
+                    if full[len(shown):]:
+                        on_delta(full[len(shown):])
+                    shown = full
+            logits, st = self.model.forward(torch.tensor([tok], dtype=torch.int64, device=dev), st)
+        t4 = time.perf_counter()
+        text_ids = [t for t in toks if t != self.eos]
+        return GenerationOutput(self.tokenizer.decode(text_ids), toks, finish, len(ids), len(toks), {
+            "prompt_format": (t1 - t0) * 1e3, "tokenize": (t2 - t1) * 1e3, "prefill": (t3 - t2) * 1e3,
+            "decode": (t4 - t3) * 1e3, "total": (t4 - t0) * 1e3})
