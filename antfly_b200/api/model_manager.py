@@ -166,6 +166,27 @@ class ModelManager:
             dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             model = Qwen35Model.from_state_dict(Qwen35Config.from_hf(cfg_d), sd, device=self.device, dtype=dt)
             pipe = StatefulGenerator(model, tok, mf.chat_template)
+        elif task == "generator" and cfg_d.get("model_type") in ("gemma4", "gemma4_text"):
+            # Gemma-4: per-layer cache geometries and KV-shared layers, so it carries its own per-sequence state.
+            from ..models.gemma4 import Gemma4Config, Gemma4TextModel
+            from ..models.gemma4v import Gemma4Multimodal
+            from ..pipelines.generation import StatefulGenerator
+
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            if cfg_d.get("model_type") == "gemma4" and cfg_d.get("vision_config") and \
+                    any(k.startswith("model.vision_tower.") for k in sd):
+                model = Gemma4Multimodal.from_state_dict(cfg_d, sd, device=self.device, dtype=dt)
+                pre = {}
+                pp = os.path.join(path, "preprocessor_config.json") if os.path.isdir(path) else None
+                if pp and os.path.exists(pp):
+                    import json as _json
+                    with open(pp, encoding="utf-8") as f:
+                        pre = _json.load(f)
+                model.max_soft_tokens = int(pre.get("max_soft_tokens", 280))
+            else:
+                text_d = cfg_d.get("text_config") or cfg_d
+                model = Gemma4TextModel.from_state_dict(Gemma4Config.from_hf(text_d), sd, device=self.device, dtype=dt)
+            pipe = StatefulGenerator(model, tok, mf.chat_template)
         elif task == "rewriter" or (task == "generator" and cfg_d.get("model_type") in ("t5", "mt5", "bart",
                                                                                          "mbart")):
             from ..models.t5 import T5Config, T5Model

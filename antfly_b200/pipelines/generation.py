@@ -158,7 +158,7 @@ class StatefulGenerator:
                  on_delta: Optional[Callable[[str], None]] = None, images=None) -> GenerationOutput:
         import torch
 
-        if images:
+        if images and not hasattr(self.model, "prepare_images"):
             raise ValueError("this model does not take images")
         t0 = time.perf_counter()
         if isinstance(messages_or_prompt, str):
@@ -173,7 +173,10 @@ class StatefulGenerator:
         gen = torch.Generator(device="cpu")
         if params.seed is not None:
             gen.manual_seed(params.seed)
-        logits, st = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev))
+        extra = {}
+        if images:
+            ids, extra = self.model.prepare_images(ids, images, bos_id=self.tokenizer.special.bos_id)
+        logits, st = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), None, **extra)
         t3 = time.perf_counter()
         toks: List[int] = []
         shown = ""
