@@ -202,6 +202,22 @@ class ModelManager:
                 raise ModelNotFound(f"{name}: rewriters are T5- or BART-family encoder-decoder models "
                                     f"(found {cfg_d.get('model_type')!r})")
             pipe = Seq2SeqGenerator(model, tok)
+        elif task == "reader" and cfg_d.get("model_type") == "florence2":
+            from ..models.florence2 import Florence2Model
+            from ..pipelines.reading import FlorenceReader
+
+            pp = {}
+            ppath = os.path.join(path, "preprocessor_config.json")
+            if os.path.exists(ppath):
+                with open(ppath, encoding="utf-8") as f:
+                    pp = json.load(f)
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            model = Florence2Model.from_state_dict(cfg_d, sd, device=self.device, dtype=dt)
+            size = pp.get("size") or {}
+            pipe = FlorenceReader(model, tok, pp.get("image_mean", (0.485, 0.456, 0.406)),
+                                  pp.get("image_std", (0.229, 0.224, 0.225)),
+                                  "bilinear" if pp.get("resample") == 2 else "bicubic",
+                                  int(size.get("height", model.vcfg.image_size)))
         elif task == "reader":
             from ..models.trocr import TrOCRConfig, TrOCRModel
             from ..pipelines.reading import Reader

@@ -766,7 +766,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         def work():
             lm = mgr.get(req.model, "reader")
-            res = lm.pipeline.read(imgs, req.max_tokens)
+            res = lm.pipeline.read(imgs, req.max_tokens, prompt=req.prompt)
             n = sum(len(r.token_ids) for r in res)
             metrics.tokens.labels("read", "completion").inc(n)
             return {"object": "list", "model": req.model,

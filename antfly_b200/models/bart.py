@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -97,11 +97,17 @@ class BartModel:
         return cls(cfg, w)
 
     # ------------------------------------------------------------------------------------------------------
-    def _embed(self, ids: Sequence[int], first_pos: int, stack: str) -> torch.Tensor:
+    def _embed(self, ids: Optional[Sequence[int]], first_pos: int, stack: str,
+               token_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Token rows (scaled) + learned positions -> LayerNorm.  ``token_embeds`` [T, d_model] replaces the table
+        lookup (already scaled): a caller that mixes in rows of another modality builds them itself."""
         w = self.w
-        tok = torch.tensor(list(ids), device=self.device)
-        pos = torch.arange(first_pos, first_pos + len(ids), device=self.device) + 2      # the table's two-row offset
-        x = w["shared"].index_select(0, tok).float() * self.scale + w[stack + ".pos"].index_select(0, pos).float()
+        if token_embeds is None:
+            tok = torch.tensor(list(ids), device=self.device)
+            token_embeds = w["shared"].index_select(0, tok).float() * self.scale
+        n = token_embeds.shape[0]
+        pos = torch.arange(first_pos, first_pos + n, device=self.device) + 2             # the table's two-row offset
+        x = token_embeds.float() + w[stack + ".pos"].index_select(0, pos).float()
         return Dn.norm(x.to(w["shared"].dtype), w[stack + ".lne.g"], w[stack + ".lne.b"], eps=1e-5)
 
     def _attend(self, q, k, v, nh: int, causal: bool) -> torch.Tensor:
@@ -121,11 +127,11 @@ class BartModel:
         h = Dn.gemm_bf16(m, w[p + "fc2.w"], bias=w[p + "fc2.b"], residual=x)
         return Dn.norm(h, w[p + "ln2.g"], w[p + "ln2.b"], eps=1e-5)
 
-    def encode(self, ids: Sequence[int]) -> torch.Tensor:
+    def encode(self, ids: Optional[Sequence[int]], token_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         H, nh = cfg.d_model, cfg.encoder_attention_heads
         D = H // nh
-        x = self._embed(ids, 0, "enc")
+        x = self._embed(ids, 0, "enc", token_embeds)
         T = x.shape[0]
         starts = torch.zeros(1, dtype=torch.int32, device=self.device)
         lens = torch.full((1,), T, dtype=torch.int32, device=self.device)
