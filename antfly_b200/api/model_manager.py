@@ -166,6 +166,14 @@ class ModelManager:
             dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
             model = Qwen35Model.from_state_dict(Qwen35Config.from_hf(cfg_d), sd, device=self.device, dtype=dt)
             pipe = StatefulGenerator(model, tok, mf.chat_template)
+        elif task == "generator" and str(cfg_d.get("model_type", "")).replace("-", "_").startswith("deepseek_v4"):
+            # single-latent attention with compressed long-range rows: the cache is the model's own state
+            from ..models.deepseek_v4 import DeepseekV4Config, DeepseekV4Model
+            from ..pipelines.generation import StatefulGenerator
+
+            dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+            model = DeepseekV4Model.from_state_dict(DeepseekV4Config.from_hf(cfg_d), sd, device=self.device, dtype=dt)
+            pipe = StatefulGenerator(model, tok, mf.chat_template)
         elif task == "generator" and cfg_d.get("model_type") in ("gemma4", "gemma4_text"):
             # Gemma-4: per-layer cache geometries and KV-shared layers, so it carries its own per-sequence state.
             from ..models.gemma4 import Gemma4Config, Gemma4TextModel
