@@ -453,6 +453,12 @@ class ModelManager:
                 self._models.move_to_end(key)
                 self._models[key].last_used = now
                 return self._models[key]
+        if not hasattr(base.pipeline, "engine"):
+            lm = self._stateful_variant(base, name, draft_model, kv, now)
+            with self._lock:
+                self._models[key] = lm
+                self._make_room_locked(keep=key)
+            return lm
         eng0 = base.pipeline.engine
         draft = None
         if draft_model:
@@ -472,6 +478,35 @@ class ModelManager:
             self._models[key] = lm
             self._make_room_locked(keep=key)
         return lm
+
+    def _stateful_variant(self, base: LoadedModel, name: str, draft_model: Optional[str], kv: Optional[str],
+                          now: float) -> LoadedModel:
+        """Variants of a generator that keeps its own per-sequence cache (no paged engine): the only one is Gemma-4
+        with its multi-token-prediction assistant as ``draft_model``
+        (zig/pkg/inference/src/pipelines/generation.zig:1566, 3028-3110)."""
+        from ..models.gemma4 import Gemma4Assistant, Gemma4TextModel
+        from ..pipelines.generation import StatefulGenerator
+
+        if kv is not None:
+            raise ValueError(f"{name!r} keeps a cache layout of its own; cache_dtype is not available for it")
+        target = getattr(base.pipeline.model, "text", base.pipeline.model)
+        if not isinstance(target, Gemma4TextModel):
+            raise ValueError(f"speculative decoding with a draft model is not available for {name!r}")
+        path = MF.resolve_model_path(draft_model, self.models_dir, "generators")
+        if path is None:
+            raise ModelNotFound(f"model {draft_model!r} not found under {self.models_dir} (generators/)")
+        mf = MF.read_manifest(path)
+        if mf.config.get("model_type") != "gemma4_assistant":
+            raise ValueError(f"{name!r} drafts with a Gemma-4 assistant checkpoint; {draft_model!r} is "
+                             f"{mf.config.get('model_type')!r}")
+        dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        asst = Gemma4Assistant.from_state_dict(mf.config, ST.load_model_dir(path), target, device=self.device, dtype=dt)
+        if asst.body.cfg.vocab_size != target.cfg.vocab_size:
+            raise ValueError(f"draft model {draft_model!r} has a different vocabulary than {name!r}")
+        pipe = StatefulGenerator(base.pipeline.model, base.tokenizer, base.pipeline.template.source,
+                                 add_bos=base.pipeline.add_bos, assistant=asst)
+        return LoadedModel(name, "generator", pipe, base.tokenizer, base.path,
+                           info=dict(base.info, draft_model=draft_model), last_used=now)
 
     # -- eviction ------------------------------------------------------------------------------------------
     def _drop_locked(self, key: str) -> None:

@@ -103,12 +103,14 @@ def _rope_half(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> to
 class Gemma4State:
     kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)   # layer -> (K, V) [Hkv, t, D]
     length: int = 0
+    last_hidden: Optional[torch.Tensor] = None      # final-norm hidden row of the newest token
 
 
 class Gemma4TextModel:
     def __init__(self, cfg: Gemma4Config, weights: Dict[str, torch.Tensor]):
         self.cfg, self.w = cfg, weights
         self.device, self.dtype = weights["embed"].device, weights["embed"].dtype
+        self.query_only = False            # an assistant body: no keys / values of its own, see Gemma4Assistant
         c = cfg
         L = c.num_hidden_layers
         first_shared = L - c.num_kv_shared_layers
@@ -186,7 +188,7 @@ class Gemma4TextModel:
         inv = self.inv_freq[kind]
         q = _rope_half(_rms(self._lin(h, w[p + "q"]).view(T, Hq, D), w[p + "qn"], c.rms_norm_eps), pos, inv)
         src = self.kv_source[l]
-        if src != l:
+        if src != l or self.query_only:
             kk, vv = st.kv[src]
         else:
             kraw = self._lin(h, w[p + "k"]).view(T, Hkv, D)
@@ -265,6 +267,20 @@ class Gemma4TextModel:
             proj = (self._lin(x, w["ple.proj"]) * c.hidden_size ** -0.5).view(T, L, P)
             del x_text
             ple = (_rms(proj, w["ple.norm"], c.rms_norm_eps) + tok_part) * 2.0 ** -0.5
+        x = self._layers(x, ple, st, pos)
+        st.length += T
+        hidden = _rms(x, w["norm"], c.rms_norm_eps)
+        logits = self._lin(hidden, w["lm_head"])
+        if c.final_logit_softcapping:
+            logits = torch.tanh(logits / c.final_logit_softcapping) * c.final_logit_softcapping
+        st.last_hidden = hidden[-1]
+        return logits, st
+
+    def _layers(self, x: torch.Tensor, ple: Optional[torch.Tensor], st: Gemma4State, pos: torch.Tensor) -> torch.Tensor:
+        """The decoder stack on embedded rows x [T, hidden] at positions ``pos``; appends to (or, for a query-only
+        body, only reads) the caches in ``st``.  Returns the rows before the final norm."""
+        c, w = self.cfg, self.w
+        P = c.hidden_size_per_layer_input if ple is not None else 0
         for l in range(c.num_hidden_layers):
             p = f"l{l}."
             h = _rms(x, w[p + "ln1"], c.rms_norm_eps)
@@ -282,11 +298,14 @@ class Gemma4TextModel:
                 g = _gelu_tanh(self._lin(x, w[p + "ple.gate"])) * ple[:, l]
                 x = x + _rms(self._lin(g, w[p + "ple.proj"]), w[p + "ple.norm"], c.rms_norm_eps)
             x = x * w[p + "scalar"]
-        st.length += T
-        logits = self._lin(_rms(x, w["norm"], c.rms_norm_eps), w["lm_head"])
-        if c.final_logit_softcapping:
-            logits = torch.tanh(logits / c.final_logit_softcapping) * c.final_logit_softcapping
-        return logits, st
+        return x
+
+    @staticmethod
+    def truncate(st: Gemma4State, length: int) -> None:
+        """Forget everything after the first ``length`` tokens (rejected speculative tokens)."""
+        for l, (k, v) in list(st.kv.items()):
+            st.kv[l] = (k[:, :length], v[:, :length])
+        st.length = length
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int, eos_token_id: Optional[int] = None) -> List[int]:
         ids = torch.tensor(list(prompt), dtype=torch.int64, device=self.device)
@@ -298,4 +317,137 @@ class Gemma4TextModel:
             if eos_token_id is not None and tok == eos_token_id:
                 break
             logits, st = self.forward(torch.tensor([tok], dtype=torch.int64, device=self.device), st)
+        return out
+
+
+def kv_donor_layers(cfg: Gemma4Config) -> Tuple[Optional[int], Optional[int]]:
+    """(sliding, full): the last layer of each kind that owns its cache; None when the model has no KV-shared tail
+    (zig/pkg/inference/src/architectures/gemma4_mtp.zig targetKvDonorLayer)."""
+    if cfg.num_kv_shared_layers == 0 or cfg.num_hidden_layers <= cfg.num_kv_shared_layers:
+        return None, None
+    own = cfg.layer_types[: cfg.num_hidden_layers - cfg.num_kv_shared_layers]
+    last = lambda kind: max((i for i, t in enumerate(own) if t == kind), default=None)
+    return last("sliding_attention"), last("full_attention")
+
+
+class Gemma4Assistant:
+    """Gemma-4 multi-token-prediction assistant: a compact *query-only* decoder that drafts tokens for a target model.
+
+    One draft step (gemma4_mtp.zig draftToken): concatenate the target's (scaled) embedding of the newest token with
+    an activation of target width (first the target's final hidden row of that token, then the assistant's own
+    projection), map it to the assistant width with ``pre_projection``, run the assistant's layers (they have no
+    keys / values of their own: every layer attends to the *target's* cache of the last cache-owning layer of its
+    kind, at the newest token's position), take the final-norm hidden row, read logits off the assistant's tied
+    embedding, and project the row back to target width with ``post_projection`` for the next chained step.
+    With ordered embeddings the argmax only looks at the tokens of the ``centroid_intermediate_top_k`` best
+    vocabulary clusters (``masked_embedding.centroids`` scores clusters, ``masked_embedding.token_ordering`` lists
+    each cluster's tokens)."""
+
+    def __init__(self, body: Gemma4TextModel, target: Gemma4TextModel, extra: Dict[str, torch.Tensor],
+                 num_centroids: int = 0, centroid_top_k: int = 0, ordered: bool = False):
+        slide, full = kv_donor_layers(target.cfg)
+        if slide is None or full is None:
+            raise ValueError("the target has no KV-shared tail with a sliding and a full donor layer")
+        if extra["pre"].shape[1] != 2 * target.cfg.hidden_size:
+            raise ValueError("assistant backbone width does not match the target's hidden size")
+        self.body, self.target, self.x = body, target, extra
+        body.query_only = True
+        body.kv_source = {l: slide if t == "sliding_attention" else full for l, t in enumerate(body.cfg.layer_types)}
+        self.num_centroids, self.centroid_top_k, self.ordered = num_centroids, centroid_top_k, ordered
+        self.drafted = self.matched = self.rounds = 0
+
+    @classmethod
+    def from_state_dict(cls, hf_config: dict, sd: Dict[str, torch.Tensor], target: Gemma4TextModel, device="cuda",
+                        dtype=torch.bfloat16) -> "Gemma4Assistant":
+        tc = dict(hf_config.get("text_config") or hf_config)
+        tc.setdefault("num_kv_shared_layers", 0)
+        cfg = Gemma4Config.from_hf(tc)
+        cfg.num_kv_shared_layers = 0
+        cfg.hidden_size_per_layer_input = 0
+        body = Gemma4TextModel.from_state_dict(cfg, sd, device=device, dtype=dtype)
+        t = lambda x: x.to(dtype).to(device).contiguous()
+        extra = {"pre": t(sd["pre_projection.weight"]), "post": t(sd["post_projection.weight"])}
+        if "masked_embedding.centroids.weight" in sd:
+            extra["centroids"] = t(sd["masked_embedding.centroids.weight"])
+            extra["ordering"] = sd["masked_embedding.token_ordering"].to(device).long()
+        return cls(body, target, extra, int(hf_config.get("num_centroids", 0)),
+                   int(hf_config.get("centroid_intermediate_top_k", 0)), bool(hf_config.get("use_ordered_embeddings")))
+
+    def _pick(self, hidden: torch.Tensor, logits: torch.Tensor) -> int:
+        """Argmax of the draft logits; with ordered embeddings only over the tokens of the best clusters."""
+        V = logits.numel()
+        nc, k = self.num_centroids, self.centroid_top_k
+        if not (self.ordered and nc and k and "centroids" in self.x and V % nc == 0):
+            return int(logits.argmax())
+        cl = self.body._lin(hidden[None], self.x["centroids"])[0]
+        top = cl.topk(min(k, nc)).indices
+        size = V // nc
+        cand = self.x["ordering"].view(nc, size)[top].flatten()
+        cand = cand[(cand >= 0) & (cand < V)]
+        if cand.numel() == 0:
+            return int(logits.argmax())
+        return int(cand[logits[cand].argmax()])
+
+    def draft(self, token: int, activation: torch.Tensor, st: Gemma4State, k: int) -> List[int]:
+        """``k`` chained draft tokens after ``token`` (the newest token of ``st``, whose final hidden row is
+        ``activation``).  Reads the target's caches; changes nothing."""
+        tgt, body = self.target, self.body
+        pos = torch.tensor([st.length - 1], device=body.device)
+        scale = torch.tensor(tgt.cfg.hidden_size ** 0.5, dtype=tgt.dtype).to(tgt.device)
+        out: List[int] = []
+        act = activation.float()
+        for _ in range(k):
+            emb = (tgt.w["embed"][token] * scale).float()
+            x = body._lin(torch.cat([emb, act])[None], self.x["pre"])
+            h = _rms(body._layers(x, None, st, pos), body.w["norm"], body.cfg.rms_norm_eps)
+            logits = body._lin(h, body.w["embed"])[0]
+            token = self._pick(h[0], logits)
+            out.append(token)
+            act = body._lin(h, self.x["post"])[0]
+        return out
+
+    @torch.no_grad()
+    def stream(self, prompt: Sequence[int], max_new_tokens: int, k: int = 4, forward_kwargs: Optional[dict] = None):
+        """Greedy generation of the *target*, sped up by drafting; yields tokens as they are accepted.  Every round
+        drafts ``k`` tokens, the target scores them in one pass, the longest agreeing prefix is kept plus the
+        target's own next token (a correction after a mismatch, a bonus after full agreement); the rejected tail is
+        cut from the target's caches.  The tokens equal the target's plain greedy output.  ``forward_kwargs``:
+        extra inputs of the prompt pass (image soft tokens)."""
+        tgt = self.target
+        dev = tgt.device
+        k = max(1, min(int(k), 16))
+        logits, st = tgt.forward(torch.tensor(list(prompt), dtype=torch.int64, device=dev), None,
+                                 **(forward_kwargs or {}))
+        last = int(logits[-1].argmax())
+        n = 1
+        yield last
+        if n >= max_new_tokens:
+            return
+        nxt, st = tgt.forward(torch.tensor([last], device=dev), st)            # the cache now covers the newest token
+        while n < max_new_tokens:
+            kk = min(k, max_new_tokens - n)
+            drafts = self.draft(last, st.last_hidden, st, kk)
+            base = st.length
+            ver, st = tgt.forward(torch.tensor(drafts, device=dev), st)
+            want = [int(nxt[-1].argmax())] + [int(r.argmax()) for r in ver]
+            m = 0
+            while m < kk and drafts[m] == want[m]:
+                m += 1
+            self.rounds, self.drafted, self.matched = self.rounds + 1, self.drafted + kk, self.matched + m
+            for tok in (drafts[:m] + [want[m]])[: max_new_tokens - n]:
+                n += 1
+                yield tok
+            if n >= max_new_tokens:
+                return
+            last = want[m]
+            tgt.truncate(st, base + m)
+            nxt, st = tgt.forward(torch.tensor([last], device=dev), st)
+
+    def generate(self, prompt: Sequence[int], max_new_tokens: int, k: int = 4,
+                 eos_token_id: Optional[int] = None) -> List[int]:
+        out: List[int] = []
+        for tok in self.stream(prompt, max_new_tokens, k):
+            out.append(tok)
+            if eos_token_id is not None and tok == eos_token_id:
+                break
         return out

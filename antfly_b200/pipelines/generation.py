@@ -130,8 +130,9 @@ class StatefulGenerator:
     top-p / min-p on the last position's logits (greedy at temperature <= 0)."""
 
     def __init__(self, model, tokenizer, chat_template: Optional[str] = None, add_bos: bool = True,
-                 eos_token_id: Optional[int] = None):
+                 eos_token_id: Optional[int] = None, assistant=None):
         self.model, self.tokenizer, self.add_bos = model, tokenizer, add_bos
+        self.assistant = assistant          # drafts for greedy requests (``stream(ids, n, k, forward_kwargs)``)
         self.template = ChatTemplate(chat_template)
         self.vlm = None
         self.eos = eos_token_id if eos_token_id is not None else tokenizer.special.eos_id
@@ -176,13 +177,25 @@ class StatefulGenerator:
         extra = {}
         if images:
             ids, extra = self.model.prepare_images(ids, images, bos_id=self.tokenizer.special.bos_id)
-        logits, st = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), None, **extra)
-        t3 = time.perf_counter()
+        k = getattr(params, "speculative_k", None) or 4
+        drafting = self.assistant is not None and params.greedy and not images
+        marks = {}
+
+        def plain():
+            logits, st = self.model.forward(torch.tensor(ids, dtype=torch.int64, device=dev), None, **extra)
+            marks["prefill"] = time.perf_counter()
+            for _ in range(params.max_tokens):
+                tok = self._pick(logits[-1].cpu(), params, gen)
+                yield tok
+                logits, st = self.model.forward(torch.tensor([tok], dtype=torch.int64, device=dev), st)
+
+        # Drafting serves greedy, text-only requests (the verifier compares argmaxes); others decode token by token.
+        source = self.assistant.stream(ids, params.max_tokens, k) if drafting else plain()
         toks: List[int] = []
         shown = ""
         finish = "length"
-        for _ in range(params.max_tokens):
-            tok = self._pick(logits[-1].cpu(), params, gen)
+        for tok in source:
+            marks.setdefault("prefill", time.perf_counter())
             toks.append(tok)
             if (not params.ignore_eos and tok == self.eos) or tok in params.stop_token_ids:
                 finish = "stop"
@@ -193,7 +206,10 @@ class StatefulGenerator:
                     if full[len(shown):]:
                         on_delta(full[len(shown):])
                     shown = full
-            logits, st = self.model.forward(torch.tensor([tok], dtype=torch.int64, device=dev), st)
+            if len(toks) >= params.max_tokens:
+                break
+        source.close()
+        t3 = marks.get("prefill", time.perf_counter())
         t4 = time.perf_counter()
         text_ids = [t for t in toks if t != self.eos]
         return GenerationOutput(self.tokenizer.decode(text_ids), toks, finish, len(ids), len(toks), {

@@ -237,3 +237,131 @@ def test_gemma4_loads_through_the_model_manager_and_answers_about_an_image(tmp_p
         want.append(int(lg.argmax()))
         seq = torch.cat([seq, torch.tensor([[want[-1]]])], 1)
     assert out.token_ids == want
+
+
+def _assistant(target, hf_target_cfg, seed=3, **extra_cfg):
+    """A random query-only assistant whose head geometry fits the target's caches."""
+    from antfly_b200.models.gemma4 import Gemma4Assistant
+
+    torch.manual_seed(seed)
+    acfg = transformers.Gemma4TextConfig(
+        vocab_size=hf_target_cfg.vocab_size, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=hf_target_cfg.num_key_value_heads, head_dim=hf_target_cfg.head_dim,
+        global_head_dim=hf_target_cfg.global_head_dim, sliding_window=hf_target_cfg.sliding_window,
+        hidden_size_per_layer_input=0, vocab_size_per_layer_input=hf_target_cfg.vocab_size, num_kv_shared_layers=0,
+        layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=True)
+    hf_a = transformers.Gemma4ForCausalLM(acfg).eval().float()
+    sd = {k: v for k, v in hf_a.state_dict().items()
+          if not any(s in k for s in ("k_proj", "v_proj", "k_norm"))}
+    sd["pre_projection.weight"] = torch.randn(32, 2 * hf_target_cfg.hidden_size) * 0.2
+    sd["post_projection.weight"] = torch.randn(hf_target_cfg.hidden_size, 32) * 0.2
+    conf = {"model_type": "gemma4_assistant", "backbone_hidden_size": hf_target_cfg.hidden_size,
+            "text_config": acfg.to_dict(), **extra_cfg}
+    if extra_cfg.get("num_centroids"):
+        nc = extra_cfg["num_centroids"]
+        sd["masked_embedding.centroids.weight"] = torch.randn(nc, 32)
+        sd["masked_embedding.token_ordering"] = torch.randperm(hf_target_cfg.vocab_size).float()
+    return Gemma4Assistant.from_state_dict(conf, sd, target, device="cpu", dtype=torch.float32), sd
+
+
+def test_mtp_assistant_drafts_from_the_targets_caches_and_never_changes_the_output():
+    from antfly_b200.models.gemma4 import Gemma4Config, Gemma4TextModel, kv_donor_layers
+
+    hf_cfg, hf = _hf()
+    cfg = Gemma4Config.from_hf(hf_cfg.to_dict())
+    target = Gemma4TextModel.from_state_dict(cfg, hf.state_dict(), device="cpu", dtype=torch.float32)
+    assert kv_donor_layers(cfg) == (3, 2)
+    asst, _ = _assistant(target, hf_cfg)
+    assert asst.body.kv_source == {0: 3, 1: 2} and asst.body.query_only
+    prompt = [5, 9, 17, 33, 2, 71, 8]
+    plain = target.generate(prompt, 14)
+    for k in (1, 3, 5):
+        assert asst.generate(prompt, 14, k=k) == plain
+    assert asst.rounds > 0 and asst.drafted >= asst.matched >= 0
+    # a draft step reads the caches and leaves them alone; chained steps feed the projected activation forward
+    logits, st = target.forward(torch.tensor(prompt))
+    before = {l: (k.clone(), v.clone()) for l, (k, v) in st.kv.items()}
+    d3 = asst.draft(prompt[-1], st.last_hidden, st, 3)
+    assert len(d3) == 3 and st.length == len(prompt)
+    assert all(torch.equal(st.kv[l][0], before[l][0]) and torch.equal(st.kv[l][1], before[l][1]) for l in before)
+    assert asst.draft(prompt[-1], st.last_hidden, st, 1) == d3[:1]
+    # an assistant that always agrees with the target is accepted whole: k drafts + 1 bonus token per round
+    n0 = len(prompt)
+    asst.draft = lambda token, act, state, k: (plain + [0] * 8)[state.length - n0: state.length - n0 + k]
+    asst.rounds = asst.drafted = asst.matched = 0
+    assert asst.generate(prompt, 13, k=4) == plain[:13]
+    assert asst.matched == asst.drafted and asst.rounds == 3           # 1 + 3 * (4 + 1) >= 13
+
+
+def test_mtp_masked_embedding_argmax_only_sees_the_best_clusters():
+    from antfly_b200.models.gemma4 import Gemma4Config, Gemma4TextModel
+
+    hf_cfg, hf = _hf()
+    target = Gemma4TextModel.from_state_dict(Gemma4Config.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                             dtype=torch.float32)
+    asst, sd = _assistant(target, hf_cfg, num_centroids=10, centroid_intermediate_top_k=2,
+                          use_ordered_embeddings=True)
+    g = torch.Generator().manual_seed(0)
+    hidden, logits = torch.randn(32, generator=g), torch.randn(200, generator=g)
+    got = asst._pick(hidden, logits)
+    cl = sd["masked_embedding.centroids.weight"] @ hidden
+    best = cl.topk(2).indices.tolist()
+    order = sd["masked_embedding.token_ordering"].long().view(10, 20)
+    cand = torch.cat([order[b] for b in best])
+    assert got == int(cand[logits[cand].argmax()])
+    assert got != int(logits.argmax()) or int(logits.argmax()) in cand.tolist()
+    asst.ordered = False
+    assert asst._pick(hidden, logits) == int(logits.argmax())
+
+
+def test_mtp_needs_a_target_with_shared_kv_donors():
+    from antfly_b200.models.gemma4 import Gemma4Config, Gemma4TextModel
+
+    hf_cfg, hf = _hf(num_kv_shared_layers=0)
+    target = Gemma4TextModel.from_state_dict(Gemma4Config.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                             dtype=torch.float32)
+    with pytest.raises(ValueError):
+        _assistant(target, hf_cfg)
+
+
+def test_mtp_assistant_as_the_draft_model_of_a_request(tmp_path):
+    import json
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import safetensors_io as st
+    from antfly_b200.models.gemma4 import Gemma4Config, Gemma4TextModel
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    hf_cfg, hf = _hf(vocab_size=600, vocab_size_per_layer_input=600)
+    d = tmp_path / "generators" / "tiny-g4"
+    d.mkdir(parents=True)
+    st.save_file({k: v.contiguous() for k, v in hf.state_dict().items() if k != "lm_head.weight"},
+                 str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps(dict(hf_cfg.to_dict(), model_type="gemma4_text"), default=str))
+    target = Gemma4TextModel.from_state_dict(Gemma4Config.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                             dtype=torch.float32)
+    asst, sd = _assistant(target, hf_cfg)
+    a = tmp_path / "generators" / "tiny-g4-assistant"
+    a.mkdir(parents=True)
+    st.save_file({k: v.contiguous() for k, v in sd.items() if k != "lm_head.weight"}, str(a / "model.safetensors"))
+    conf = {"model_type": "gemma4_assistant", "backbone_hidden_size": hf_cfg.hidden_size,
+            "text_config": asst.body.cfg.__dict__ | {"model_type": "gemma4_text"}}
+    (a / "config.json").write_text(json.dumps(conf, default=str))
+    mgr = ModelManager(models_dir=str(tmp_path), device="cpu")
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    plain = mgr.get_generator("tiny-g4").pipeline.generate("hello world", sp, raw_prompt=True)
+    lm = mgr.get_generator("tiny-g4", draft_model="tiny-g4-assistant")
+    assert lm is mgr.get_generator("tiny-g4", draft_model="tiny-g4-assistant")        # cached variant
+    pipe = lm.pipeline
+    deltas = []
+    fast = pipe.generate("hello world", sp, raw_prompt=True, on_delta=deltas.append)
+    assert fast.token_ids == plain.token_ids and fast.text == plain.text and len(fast.token_ids) == 12
+    assert "".join(deltas) == fast.text[: len("".join(deltas))] and pipe.assistant.rounds > 0
+    # sampling requests decode without the assistant
+    rounds = pipe.assistant.rounds
+    pipe.generate("hello world", SamplingParams(max_tokens=4, temperature=0.8, seed=1, ignore_eos=True), raw_prompt=True)
+    assert pipe.assistant.rounds == rounds
+    with pytest.raises(ValueError):
+        mgr.get_generator("tiny-g4", cache_dtype="fp8")
+    with pytest.raises(ValueError):
+        mgr.get_generator("tiny-g4", draft_model="tiny-g4")                           # not an assistant checkpoint
