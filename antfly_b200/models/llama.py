@@ -66,6 +66,11 @@ class LlamaConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True   # renormalise the selected experts' weights to sum to one
     shared_expert_intermediate_size: int = 0
+    # Gemma-2: scaled attention scores and final logits pass through cap * tanh(x / cap)
+    attn_logit_softcapping: float = 0.0
+    final_logit_softcapping: float = 0.0
+    # a learned per-head sink logit in the attention softmax (checkpoints that carry ``self_attn.sinks``)
+    attn_sinks: bool = False
 
     def __post_init__(self):
         if not self.head_dim:
@@ -132,6 +137,19 @@ class LlamaConfig:
             cfg.layer_windows = [win if k == "sliding_attention" else 0 for k in kinds]
             cfg.layer_rope = [[l_theta, 1.0] if k == "sliding_attention" else [g_theta, g_scale] for k in kinds]
             cfg.sliding_window, cfg.rope_theta, cfg.rope_freq_scale = 0, g_theta, g_scale
+        if mt == "gemma2":
+            cfg.norm_plus_one, cfg.post_norms = True, True
+            cfg.embed_scale = float(cfg.hidden_size) ** 0.5
+            cfg.gate_act = "gelu_tanh"
+            cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
+            cfg.attn_scale = float(d.get("query_pre_attn_scalar") or cfg.head_dim) ** -0.5
+            cfg.attn_logit_softcapping = float(d.get("attn_logit_softcapping") or 0.0)
+            cfg.final_logit_softcapping = float(d.get("final_logit_softcapping") or 0.0)
+            kinds = d.get("layer_types") or ["sliding_attention" if i % 2 == 0 else "full_attention"
+                                             for i in range(cfg.num_hidden_layers)]
+            win = int(d.get("sliding_window") or 0)
+            cfg.layer_windows = [win if k == "sliding_attention" else 0 for k in kinds]
+            cfg.sliding_window = 0
         if mt == "gemma":
             cfg.norm_plus_one = True
             cfg.embed_scale = float(cfg.hidden_size) ** 0.5
@@ -357,6 +375,10 @@ class LlamaModel:
                 w[p + "qn"] = sd[s + "self_attn.q_norm.weight"].to(torch.bfloat16).to(device)
                 w[p + "kn"] = sd[s + "self_attn.k_norm.weight"].to(torch.bfloat16).to(device)
             w[p + "o"] = Q.pack_fp8(shard_cols(sd[s + "self_attn.o_proj.weight"], tp_rank, tp_size).to(device))
+            if s + "self_attn.sinks" in sd:                     # one sink logit per query head (this rank's heads)
+                cfg.attn_sinks = True
+                w[p + "sinks"] = shard_rows(sd[s + "self_attn.sinks"].float().reshape(-1, 1), tp_rank,
+                                            tp_size).flatten().to(device)
             if cfg.num_experts > 0:
                 assert tp_size == 1, "mixture-of-experts models run on one GPU"
                 moe = s + ("block_sparse_moe." if s + "block_sparse_moe.gate.weight" in sd else "mlp.")
@@ -706,9 +728,15 @@ class LlamaModel:
                                 bias=qkv_bias, rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
                                 freq_scale=fscale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
                                 norm_eps=eps, norm_plus_one=gp1)
-            ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                    b.max_q_len, max_kv=b.max_kv, scale=cfg.attn_scale or None, window=window,
-                                    num_splits=b.attn_splits, scratch=attn_scratch)
+            if cfg.attn_sinks or cfg.attn_logit_softcapping:
+                # a softmax with an extra term: the kernel that carries it (bf16 caches)
+                ctx = A.paged_attention_sink(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                             scale=cfg.attn_scale or None, window=window, sinks=w.get(p + "sinks"),
+                                             softcap=cfg.attn_logit_softcapping)
+            else:
+                ctx = A.paged_attention(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
+                                        b.max_q_len, max_kv=b.max_kv, scale=cfg.attn_scale or None, window=window,
+                                        num_splits=b.attn_splits, scratch=attn_scratch)
             if b.bidir is not None:
                 # second pass over the image runs without the causal mask (their keys are already in the cache);
                 # its rows replace the causal ones
@@ -760,6 +788,9 @@ class LlamaModel:
         if not self.return_hidden:
             head = w["lm_head"]
             hl = self._linear(hl, head, rows.shape[0]) if isinstance(head, Q.Fp8Weight) else Dn.gemm_bf16(hl, head)
+            if cfg.final_logit_softcapping:
+                cap = cfg.final_logit_softcapping
+                hl = (torch.tanh(hl.float() / cap) * cap).to(hl.dtype)
         return hl if pp is None else pp.share_logits(hl, n_rows, hl.shape[1], hl.device)
 
     def forward(self, b: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -769,7 +800,7 @@ class LlamaModel:
         cfg, w = self.cfg, self.w
         if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
                 self.pp is not None or b.embed_rows is not None or b.pos3 is not None or cfg.post_norms or \
-                b.bidir is not None:
+                b.bidir is not None or cfg.attn_sinks or cfg.attn_logit_softcapping or cfg.final_logit_softcapping:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

@@ -190,7 +190,8 @@ def alibi_slopes(num_heads: int) -> torch.Tensor:
 
 
 def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale=None,
-                    sliding_window: int = 0, alibi: Optional[torch.Tensor] = None, causal: bool = True):
+                    sliding_window: int = 0, alibi: Optional[torch.Tensor] = None, causal: bool = True,
+                    sinks: Optional[torch.Tensor] = None, softcap: float = 0.0):
     """Causal attention of packed query tokens against a paged KV cache.
 
     q: [T, Hq, D]; k_cache / v_cache: [num_blocks, page, Hkv, D]; block_tables: [B, max_blocks] int32;
@@ -199,6 +200,8 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
     reference's gqaPagedAttentionDirect (zig/pkg/inference/src/ops/native_compute.zig:35093-35173): query at
     absolute position p sees keys at positions <= p, and > p - sliding_window when a window is set.
     ``alibi`` [Hq] adds ``slope_h * (key position - query position)`` to the scores (linear position bias).
+    ``sinks`` [Hq]: a per-head logit that takes part in the softmax without a value (attention sinks);
+    ``softcap`` > 0: scaled scores become ``softcap * tanh(score / softcap)`` before masking.
     """
     T, Hq, D = q.shape
     page, Hkv = k_cache.shape[1], k_cache.shape[2]
@@ -226,8 +229,15 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
             m = m & (kpos > qpos - sliding_window)
             if not causal:                       # two-sided window, as in the packed (non-paged) attention
                 m = m & (kpos < qpos + sliding_window)
+        if softcap > 0:
+            sc = softcap * torch.tanh(sc / softcap)
         sc = sc.masked_fill(~m, float("-inf"))
-        out[qs:qs + ql] = (sc.softmax(-1) @ vv).transpose(0, 1)
+        if sinks is not None:
+            col = sinks.to(sc.device).float()[:, None, None].expand(Hq, ql, 1)
+            pr = torch.cat([sc, col], -1).softmax(-1)[..., :-1]
+        else:
+            pr = sc.softmax(-1)
+        out[qs:qs + ql] = (pr @ vv).transpose(0, 1)
     return out
 
 

@@ -189,3 +189,47 @@ def test_paged_decode_sliding_window_and_legacy_agree(Hq, Hkv):
     for splits in (1, 3):
         out = A.paged_attention(q, kc, vc, bt, q_starts, q_lens, kvl, 1, window=window, num_splits=splits)
         torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 64), (4, 4, 128), (6, 3, 80), (4, 1, 256)])
+@pytest.mark.parametrize("sinks,softcap,window", [(True, 0.0, 0), (False, 30.0, 0), (True, 20.0, 37)])
+def test_sink_softcap_attention_kernel_matches_fp32_reference(Hq, Hkv, D, sinks, softcap, window):
+    """afb_attention_sink (one warp per (token, head), sink logit and tanh cap inside the softmax) on mixed prefill /
+    decode rows against the fp32 oracle; an out-of-range block id is skipped and reported."""
+    import torch
+
+    from antfly_b200 import _native as N
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(Hq * 31 + D)
+    page, nblk = 16, 64
+    q_lens = [1, 40, 1, 150, 3]
+    kv_lens = [1, 40, 300, 150, 131]
+    B = len(q_lens)
+    T = sum(q_lens)
+    kc = (torch.randn(nblk, page, Hkv, D, generator=g) * 0.5).to(torch.bfloat16)
+    vc = torch.randn(nblk, page, Hkv, D, generator=g).to(torch.bfloat16)
+    perm = torch.randperm(nblk, generator=g)
+    bt = torch.zeros((B, 20), dtype=torch.int32)
+    off = 0
+    for b, n in enumerate(kv_lens):
+        nb = (n + page - 1) // page
+        bt[b, :nb] = perm[off: off + nb].int()
+        off += nb
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    ql = torch.tensor(q_lens, dtype=torch.int32)
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    kl = torch.tensor(kv_lens, dtype=torch.int32)
+    sk = torch.randn(Hq, generator=g) if sinks else None
+    got = A.paged_attention_sink(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), qs.cuda(), ql.cuda(), kl.cuda(),
+                                 window=window, sinks=sk.cuda() if sinks else None, softcap=softcap)
+    assert N.status() == 0
+    want = R.paged_attention(q, kc, vc, bt, qs, ql, kl, D ** -0.5, window, sinks=sk, softcap=softcap)
+    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    bad = bt.clone()
+    bad[2, 3] = nblk + 7
+    out = A.paged_attention_sink(q.cuda(), kc.cuda(), vc.cuda(), bad.cuda(), qs.cuda(), ql.cuda(), kl.cuda(),
+                                 sinks=sk.cuda() if sinks else None, softcap=softcap)
+    assert N.status() & 32 and bool(torch.isfinite(out.float()).all())

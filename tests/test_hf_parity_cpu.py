@@ -48,6 +48,13 @@ def _hf_decoder(kind: str):
     elif kind == "gemma":
         cfg = transformers.GemmaConfig(**{**common, "head_dim": 64, "hidden_activation": "gelu_pytorch_tanh"})
         m = transformers.GemmaForCausalLM(cfg)
+    elif kind == "gemma2":
+        cfg = transformers.Gemma2Config(**{**common, "head_dim": 64, "query_pre_attn_scalar": 48, "sliding_window": 8,
+                                           "num_hidden_layers": 3, "attn_logit_softcapping": 4.0,
+                                           "final_logit_softcapping": 3.0,
+                                           "hidden_activation": "gelu_pytorch_tanh"})
+        cfg.tie_word_embeddings = False
+        m = transformers.Gemma2ForCausalLM(cfg)
     elif kind == "gemma3":
         cfg = transformers.Gemma3TextConfig(**{**common, "head_dim": 64, "query_pre_attn_scalar": 48,
                                                "sliding_window": 8, "num_hidden_layers": 3,
@@ -84,7 +91,7 @@ def _hf_decoder(kind: str):
     return cfg, m.eval().float()
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "gemma3", "phi3",
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "gemma2", "gemma3", "phi3",
                                   "mixtral", "qwen2_moe", "qwen3_moe"])
 def test_decoder_matches_transformers(kind):
     torch.manual_seed(0)
