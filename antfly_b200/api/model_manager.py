@@ -62,7 +62,7 @@ class ModelManager:
     def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
                  kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True, keep_alive_s: float = 0.0,
                  max_memory_mb: int = 0, strategies: Optional[Dict[str, str]] = None, clock=time.time,
-                 tensor_parallel: Optional[tuple] = None):
+                 tensor_parallel: Optional[tuple] = None, gguf_native: Optional[bool] = None):
         """``max_loaded_models`` 0 = unlimited; ``keep_alive_s`` > 0 unloads directory-backed models idle for that
         long (checked on every access and by :meth:`evict_idle`); ``max_memory_mb`` > 0 is an advisory budget on
         parameter bytes, enforced by unloading least-recently-used models; ``strategies`` maps model names to
@@ -80,6 +80,9 @@ class ModelManager:
         # tensor-parallel job (every rank serves the same requests in lockstep), the reference's
         # TERMITE_MLX_DISTRIBUTED_MODE=tensor_parallel deployment (zig/pkg/inference/docs/RERANKING.md:32-43)
         self.tensor_parallel = tensor_parallel
+        # GGUF generators: keep the projections in their block formats and expand them inside the kernels instead
+        # of re-packing to block fp8 at load time (default: the ANTFLY_B200_GGUF_NATIVE environment switch)
+        self.gguf_native = os.environ.get("ANTFLY_B200_GGUF_NATIVE", "0") == "1" if gguf_native is None else gguf_native
 
     def _tp(self, model):
         if self.tensor_parallel is not None and isinstance(model, BertModel):
@@ -134,8 +137,16 @@ class ModelManager:
             from ..formats import gguf as GG
 
             f = GG.GGUFFile(os.path.join(path, mf.weight_files[0]))
-            sd = {GG.hf_name(n): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
             cfg_d = {k: v for k, v in GG.llama_config_from_gguf(f.metadata).items() if v is not None}
+            if task == "generator" and self.gguf_native and cfg_d.get("model_type") in (
+                    "llama", "mistral", "qwen2", "qwen3", "phi3"):
+                model = LlamaModel.from_gguf_native(LlamaConfig.from_hf(cfg_d), f, device=self.device)
+                eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
+                                use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id,
+                                prefix_cache=self.prefix_cache)
+                return LoadedModel(name, task, Generator(eng, tok, mf.chat_template), tok, path,
+                                   info={"weights": "gguf-native", "capabilities": mf.capabilities})
+            sd = {GG.hf_name(n): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
         elif mf.weights == "safetensors":
             sd, cfg_d = ST.load_model_dir(path), mf.config
         else:

@@ -22,6 +22,7 @@ import torch
 
 from ..ops import attention as A
 from ..ops import dense as Dn
+from ..ops.gguf_ops import DEVICE_TYPES as GGUF_DEVICE_TYPES, GgufWeight
 from ..ops import quant as Q
 from ..ops import sampling as S
 from ..runtime.moe import CoactivationPredictor, ExpertResidency, HostExpertStore, route_batches
@@ -251,8 +252,8 @@ class LlamaModel:
         self.Hkv = max(cfg.num_key_value_heads // tp_size, 1)
         self.D = cfg.head_dim
         self.n_layers = cfg.num_hidden_layers
-        self.vocab_local = weights["lm_head"].out_features if isinstance(weights["lm_head"], Q.Fp8Weight) else \
-            weights["lm_head"].shape[0]
+        self.vocab_local = weights["lm_head"].out_features \
+            if isinstance(weights["lm_head"], (Q.Fp8Weight, GgufWeight)) else weights["lm_head"].shape[0]
         self.vocab_offset = tp_rank * self.vocab_local if tp_size > 1 else 0
         self._scratch: Dict[tuple, torch.Tensor] = {}
         self.moe_runtime = None   # set by offload_experts(): expert weights live in host memory
@@ -441,8 +442,68 @@ class LlamaModel:
         return (T <= self.mx_max_tokens and self.act_terms > 0 and c.hidden_size % 128 == 0
                 and (c.intermediate_size // self.tp_size) % 128 == 0 and (self.Hq * self.D) % 128 == 0)
 
+    @classmethod
+    def from_gguf_native(cls, cfg: LlamaConfig, gguf_file, device="cuda") -> "LlamaModel":
+        """A dense Llama-family GGUF checkpoint served from its own block formats: every projection stored as Q8_0,
+        Q4_0, MXFP4, Q4_K, Q5_K or Q6_K stays in those bytes on the device (a fused projection keeps one segment per
+        part, so mixed-format files work) and is expanded inside the kernels; other tensors (norms, embeddings,
+        F16 / F32 projections) load as usual.  Decode batches then move 4.25 - 8.5 bits per weight instead of the
+        re-packed 8.25.  The counterpart of the reference running GGUF tensors directly through its quantised
+        matmuls (zig/pkg/inference/src/graph/quant_matmul.zig:17-60)."""
+        from ..formats import gguf as GG
+
+        if cfg.num_experts > 0 or cfg.bitnet:
+            raise NotImplementedError("native GGUF serving covers dense, non-ternary decoders")
+        f = gguf_file
+        names = {GG.hf_name(n): n for n in f.tensors}
+
+        def native(hf: str):
+            info = f.tensors[names[hf]]
+            return info.type in GGUF_DEVICE_TYPES and len(info.shape) == 2 and info.shape[1] % 32 == 0
+
+        def seg(hf: str):
+            info = f.tensors[names[hf]]
+            return torch.from_numpy(f.raw(names[hf]).copy()).to(device), info.type, int(info.shape[0])
+
+        def weight(parts, interleave=False):
+            """GgufWeight when every part is in a device format, else a re-packed fp8 weight of the parts."""
+            K = int(f.tensors[names[parts[0]]].shape[1])
+            if all(native(h) for h in parts):
+                return GgufWeight([seg(h) for h in parts], K, interleave)
+            mats = [f.tensor(names[h]).to(torch.bfloat16) for h in parts]
+            if interleave:
+                return Q.pack_fp8(torch.stack(mats, 1).reshape(-1, K).to(device))
+            return Q.pack_fp8(torch.cat(mats, 0).to(device))
+
+        w: Dict[str, object] = {}
+        emb = f.tensor(names["model.embed_tokens.weight"]).to(torch.bfloat16)
+        w["embed"] = emb.to(device)
+        for l in range(cfg.num_hidden_layers):
+            s_, p = f"model.layers.{l}.", f"l{l}."
+            w[p + "ln1"] = f.tensor(names[s_ + "input_layernorm.weight"]).to(torch.bfloat16).to(device)
+            w[p + "ln2"] = f.tensor(names[s_ + "post_attention_layernorm.weight"]).to(torch.bfloat16).to(device)
+            w[p + "qkv"] = weight([s_ + f"self_attn.{n}_proj.weight" for n in "qkv"])
+            if s_ + "self_attn.q_proj.bias" in names:
+                w[p + "qkv.b"] = torch.cat([f.tensor(names[s_ + f"self_attn.{n}_proj.bias"]) for n in "qkv"]).to(
+                    torch.bfloat16).to(device)
+            w[p + "o"] = weight([s_ + "self_attn.o_proj.weight"])
+            w[p + "gu"] = weight([s_ + "mlp.gate_proj.weight", s_ + "mlp.up_proj.weight"], interleave=True)
+            w[p + "down"] = weight([s_ + "mlp.down_proj.weight"])
+        w["norm"] = f.tensor(names["model.norm.weight"]).to(torch.bfloat16).to(device)
+        if "lm_head.weight" in names and not cfg.tie_word_embeddings:
+            w["lm_head"] = weight(["lm_head.weight"])
+        else:
+            w["lm_head"] = w["embed"]
+        m = cls(cfg, w)
+        m.native_gguf = True
+        return m
+
     def _linear(self, h, w: "Q.Fp8Weight", T: int, **kw) -> torch.Tensor:
         """h is bf16 [T, K] or already-quantised MX activations."""
+        if isinstance(w, GgufWeight):               # weights served from their GGUF block bytes
+            y = w(h)
+            res = kw.get("residual")
+            return (y.float() + res.float()).to(torch.bfloat16) if res is not None else y
         if isinstance(h, Q.MxAct):
             return Q.gemm_mxfp8(h, w, **kw)
         if self._use_mx(T) and h.shape[1] % 128 == 0:
@@ -458,6 +519,7 @@ class LlamaModel:
         return y
 
     fused = None  # antfly_b200.parallel.fused.FusedTp when the peer-memory path is enabled
+    native_gguf = False  # True: projections are GgufWeight objects (quantised bytes expanded inside the kernels)
     return_hidden = False  # True: forward returns the final-norm hidden states of the wanted rows, not logits
 
     @property
@@ -787,7 +849,8 @@ class LlamaModel:
         hl = Dn.norm(rows, w["norm"], eps=eps, rms=True, gamma_plus_one=gp1)
         if not self.return_hidden:
             head = w["lm_head"]
-            hl = self._linear(hl, head, rows.shape[0]) if isinstance(head, Q.Fp8Weight) else Dn.gemm_bf16(hl, head)
+            hl = self._linear(hl, head, rows.shape[0]) if isinstance(head, (Q.Fp8Weight, GgufWeight)) else \
+                Dn.gemm_bf16(hl, head)
             if cfg.final_logit_softcapping:
                 cap = cfg.final_logit_softcapping
                 hl = (torch.tanh(hl.float() / cap) * cap).to(hl.dtype)
@@ -800,7 +863,8 @@ class LlamaModel:
         cfg, w = self.cfg, self.w
         if cfg.norm_plus_one or cfg.embed_scale != 1.0 or cfg.gate_act != "silu" or cfg.num_experts > 0 or \
                 self.pp is not None or b.embed_rows is not None or b.pos3 is not None or cfg.post_norms or \
-                b.bidir is not None or cfg.attn_sinks or cfg.attn_logit_softcapping or cfg.final_logit_softcapping:
+                b.bidir is not None or cfg.attn_sinks or cfg.attn_logit_softcapping or cfg.final_logit_softcapping or \
+                self.native_gguf:
             return self._forward_general(b, k_cache, v_cache, attn_scratch)
         if (self.fused is not None and self._use_mx(b.ids.numel())
                 and b.logit_rows.numel() == b.ids.numel() and isinstance(w["lm_head"], Q.Fp8Weight)

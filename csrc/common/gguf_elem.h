@@ -121,5 +121,74 @@ AFB_HD float element(int type, const uint8_t* p, int j) {
   }
 }
 
+// Values [32 * sub, 32 * sub + 32) of the block at p, decoded together: the per-sub-block scale / offset is worked
+// out once and every packed byte is read once.  Same values as element(type, p, 32 * sub + i).
+// The fused matrix-vector kernel (kernels/gemm_gguf.cu) calls this with a compile-time `type`.
+AFB_HD void decode32(int type, const uint8_t* p, int sub, float* out) {
+  switch (type) {
+    case 8: {  // Q8_0
+      const float d = load_half(p);
+      for (int i = 0; i < 32; ++i) out[i] = d * static_cast<float>(static_cast<int8_t>(p[2 + i]));
+      return;
+    }
+    case 2: {  // Q4_0
+      const float d = load_half(p);
+      for (int i = 0; i < 16; ++i) {
+        const uint8_t b = p[2 + i];
+        out[i] = d * static_cast<float>(static_cast<int>(b & 0xF) - 8);
+        out[i + 16] = d * static_cast<float>(static_cast<int>(b >> 4) - 8);
+      }
+      return;
+    }
+    case 39: {  // MXFP4
+      union { uint32_t u; float f; } sc;
+      sc.u = p[0] ? (static_cast<uint32_t>(p[0]) << 23) : 0x00400000u;
+      for (int i = 0; i < 16; ++i) {
+        const uint8_t b = p[1 + i];
+        out[i] = e2m1_value(b & 0xF) * sc.f;
+        out[i + 16] = e2m1_value(b >> 4) * sc.f;
+      }
+      return;
+    }
+    case 12: {  // Q4_K: sub-block = (group, half): 32 nibbles of the group's 32 bytes
+      const int group = sub >> 1, hi = sub & 1;
+      int sc, mn;
+      k4_scale_min(sub, p + 4, &sc, &mn);
+      const float d = load_half(p) * sc, m = load_half(p + 2) * mn;
+      const uint8_t* q = p + 16 + group * 32;
+      for (int i = 0; i < 32; ++i) out[i] = d * static_cast<float>(hi ? (q[i] >> 4) : (q[i] & 0xF)) - m;
+      return;
+    }
+    case 13: {  // Q5_K
+      const int group = sub >> 1, hi = sub & 1;
+      int sc, mn;
+      k4_scale_min(sub, p + 4, &sc, &mn);
+      const float d = load_half(p) * sc, m = load_half(p + 2) * mn;
+      const uint8_t* q = p + 48 + group * 32;
+      for (int i = 0; i < 32; ++i) {
+        const int v = (hi ? (q[i] >> 4) : (q[i] & 0xF)) + (((p[16 + i] >> sub) & 1) << 4);
+        out[i] = d * static_cast<float>(v) - m;
+      }
+      return;
+    }
+    case 14: {  // Q6_K: sub-block = (half, quarter)
+      const int half = sub >> 2, quarter = sub & 3;
+      const uint8_t* ql = p + half * 64 + ((quarter & 1) ? 32 : 0);
+      const uint8_t* qh = p + 128 + half * 32;
+      const int8_t* sc = reinterpret_cast<const int8_t*>(p + 192) + half * 8 + 2 * quarter;
+      const float d = load_half(p + 208);
+      const float d0 = d * sc[0], d1 = d * sc[1];
+      for (int i = 0; i < 32; ++i) {
+        const int nib = (quarter & 2) ? (ql[i] >> 4) : (ql[i] & 0xF);
+        const int v = (nib | (((qh[i] >> (2 * quarter)) & 3) << 4)) - 32;
+        out[i] = (i < 16 ? d0 : d1) * static_cast<float>(v);
+      }
+      return;
+    }
+    default:
+      for (int i = 0; i < 32; ++i) out[i] = 0.0f;
+  }
+}
+
 }  // namespace gguf
 }  // namespace afb

@@ -541,4 +541,50 @@ void afb_kv_decode_int4(const uint8_t* src, float* dst, int n) {
   }
 }
 
+// Values [32 * sub, 32 * sub + 32) of one GGUF block through the decoder the fused matrix-vector kernel uses.
+void afb_gguf_decode32(int type, const uint8_t* block, int sub, float* out) {
+  afb::gguf::decode32(type, block, sub, out);
+}
+
+// The fused GGUF matrix-vector kernel's work split (kernels/gemm_gguf.cu) replayed on the host with the same index
+// arithmetic: CTA -> 4 warps -> 2 rows each; K in chunks of 1024 values, lane l of a chunk owns sub-block l; per-lane
+// partial sums are added lane by lane.  x [M, ldx] and out [M, N] are fp32 here.  Returns the number of
+// (row, sub-block) units visited, or -1 for a type without a fused kernel.
+long afb_gguf_mul_mv_host(int type, const uint8_t* W, const float* X, float* out, int M, int N, int K, long ldx) {
+  const long bv = afb::gguf::block_values(type), bb = afb::gguf::block_bytes(type);
+  if (bv < 0 || K % bv) return -1;
+  const int kWarps = 4, kRows = 2, kChunk = 1024;
+  const long row_bytes = static_cast<long>(K / bv) * bb;
+  const int ctas = (N + kWarps * kRows - 1) / (kWarps * kRows);
+  long units = 0;
+  for (int cta = 0; cta < ctas; ++cta)
+    for (int warp = 0; warp < kWarps; ++warp) {
+      const int n0 = (cta * kWarps + warp) * kRows;
+      for (int r = 0; r < kRows; ++r) {
+        const int n = n0 + r;
+        if (n >= N) continue;
+        for (int m = 0; m < M; ++m) {
+          float lanes[32] = {0};
+          for (int kc = 0; kc < K; kc += kChunk)
+            for (int lane = 0; lane < 32; ++lane) {
+              const int k0 = kc + lane * 32;
+              if (k0 >= K) continue;
+              const long blk = k0 / bv;
+              const int sub = static_cast<int>((k0 % bv) / 32);
+              float wv[32];
+              afb::gguf::decode32(type, W + n * row_bytes + blk * bb, sub, wv);
+              float s = 0.0f;
+              for (int i = 0; i < 32; ++i) s = fmaf(wv[i], X[m * ldx + k0 + i], s);
+              lanes[lane] += s;
+              if (m == 0) ++units;
+            }
+          float v = 0.0f;
+          for (int lane = 0; lane < 32; ++lane) v += lanes[lane];
+          out[static_cast<long>(m) * N + n] = v;
+        }
+      }
+    }
+  return units;
+}
+
 }  // extern "C"
