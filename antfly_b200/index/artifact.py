@@ -6,7 +6,10 @@ little-endian record {version u32 = 1, dims u32, branching_factor u32, leaf_size
 active_count u64, node_count u64, use_quantization u8, quantizer_seed u64, metric u8}; node keys
 ``n:<u64 BE id>:<suffix>`` with the packed node value ``HBN1`` + header {is_leaf u8, level u16, parent u64} +
 centroid_len u32 + ids_len u32 + centroid f32s + ids u64s; ``v:<id>`` raw f32 vector; ``l:<id>`` vector -> leaf.
-The namespaces are persisted here as one sorted key/value file each (the reference stores them in LMDB / LSM).
+The namespaces are persisted either as one sorted key/value file each, or as the named databases ``hbc_nodes``,
+``hbc_meta``, ``hbc_quant``, ``hbc_vecs`` of an LMDB environment, the container the reference's default storage
+backend uses (zig/pkg/antfly/src/storage/hbc_adapter.zig:1435-1438; formats/lmdb_io.py reads and writes the file
+format), so an index directory written by either side opens on the other.
 (2) GPU index shards (flat / IVF) as safetensors bundles: centroids, posting offsets, sorted vectors, ids.
 """
 from __future__ import annotations
@@ -210,7 +213,28 @@ def _read_ns(path: str) -> Dict[bytes, bytes]:
     return out
 
 
-def save_hbc(index: HBCIndex, directory: str) -> None:
+LMDB_NAMES = {"nodes": "hbc_nodes", "meta": "hbc_meta", "quant": "hbc_quant", "vecs": "hbc_vecs"}
+
+
+def _namespaces(directory: str) -> Dict[str, Dict[bytes, bytes]]:
+    """The four namespaces of an index directory, from whichever container it holds."""
+    if os.path.exists(os.path.join(directory, "data.mdb")):
+        from ..formats.lmdb_io import LmdbReader
+
+        with LmdbReader(directory) as r:
+            have = set(r.databases())
+            return {ns: dict(r.items(name)) if name in have else {} for ns, name in LMDB_NAMES.items()}
+    out = {}
+    for ns in LMDB_NAMES:
+        path = os.path.join(directory, ns + ".kv")
+        out[ns] = _read_ns(path) if os.path.exists(path) else {}
+    return out
+
+
+def save_hbc(index: HBCIndex, directory: str, container: str = "files") -> None:
+    """``container``: "files" (one sorted file per namespace) or "lmdb" (one LMDB environment)."""
+    if container not in ("files", "lmdb"):
+        raise ValueError(f"unknown index container {container!r}")
     os.makedirs(directory, exist_ok=True)
     nodes = {node_key(nd.id, "p"): pack_node(nd) for nd in index.nodes.values()}
     meta = {META_KEY: pack_metadata(index.cfg, index.root, int(index.vectors.shape[0]), len(index.nodes))}
@@ -220,24 +244,33 @@ def save_hbc(index: HBCIndex, directory: str) -> None:
         vid = int(index.ids[i])
         vecs[b"v:" + struct.pack(">Q", vid)] = x[i].numpy().astype("<f4").tobytes()
         vecs[b"l:" + struct.pack(">Q", vid)] = struct.pack("<Q", index.leaf_of.get(i, 0))
-    _write_ns(os.path.join(directory, "nodes.kv"), nodes)
-    _write_ns(os.path.join(directory, "meta.kv"), meta)
-    _write_ns(os.path.join(directory, "vecs.kv"), vecs)
     quant = {b"q:" + struct.pack(">Q", nd.id): encode_rabitq_set(nd.quant) for nd in index.nodes.values()
              if getattr(nd, "quant", None) is not None}
-    _write_ns(os.path.join(directory, "quant.kv"), quant)
+    spaces = {"nodes": nodes, "meta": meta, "vecs": vecs, "quant": quant}
+    if container == "lmdb":
+        from ..formats.lmdb_io import write_lmdb
+
+        write_lmdb(directory, {LMDB_NAMES[ns]: kv for ns, kv in spaces.items()})
+        return
+    for ns, kv in spaces.items():
+        _write_ns(os.path.join(directory, ns + ".kv"), kv)
 
 
 def load_hbc(directory: str) -> HBCIndex:
-    md = unpack_metadata(_read_ns(os.path.join(directory, "meta.kv"))[META_KEY])
+    spaces = _namespaces(directory)
+    if META_KEY not in spaces["meta"]:
+        raise FileNotFoundError(f"{directory}: no HBC index metadata (neither *.kv files nor an LMDB environment)")
+    md = unpack_metadata(spaces["meta"][META_KEY])
     cfg = HBCConfig(md["dims"], md["metric"], md["branching_factor"], md["leaf_size"],
                     use_quantization=md["use_quantization"], quantizer_seed=md["quantizer_seed"])
     idx = HBCIndex(cfg)
-    for k, v in _read_ns(os.path.join(directory, "nodes.kv")).items():
+    for k, v in spaces["nodes"].items():
+        if not k.startswith(b"n:") or not k.endswith(b":p"):
+            continue
         nid = struct.unpack(">Q", k[2:10])[0]
         idx.nodes[nid] = unpack_node(nid, v)
     idx.root = md["root_node"]
-    vecs = _read_ns(os.path.join(directory, "vecs.kv"))
+    vecs = spaces["vecs"]
     vids = sorted(struct.unpack(">Q", k[2:])[0] for k in vecs if k.startswith(b"v:"))
     rows = [torch.frombuffer(bytearray(vecs[b"v:" + struct.pack(">Q", v)]), dtype=torch.float32) for v in vids]
     idx.vectors = torch.stack(rows) if rows else torch.zeros(0, cfg.dims)
@@ -249,8 +282,7 @@ def load_hbc(directory: str) -> HBCIndex:
             for m in nd.children:
                 idx.leaf_of[m] = nd.id
     if cfg.use_quantization:
-        qpath = os.path.join(directory, "quant.kv")
-        stored = _read_ns(qpath) if os.path.exists(qpath) else {}
+        stored = spaces["quant"]
         for nd in idx.nodes.values():
             blob = stored.get(b"q:" + struct.pack(">Q", nd.id))
             pts = None
