@@ -144,8 +144,12 @@ def cmd_generate(args) -> int:
             print(str(e), file=sys.stderr)
             return 2
     gen = lm.pipeline
-    eng = gen.engine
-    if args.draft_model:
+    eng = getattr(gen, "engine", None)           # None: a model that keeps its own sequence state (no paged engine)
+    if eng is None and (args.draft_layers or any((args.kv_budget_mb, args.host_budget_mb, args.backend_budget_mb,
+                                                  args.scratch_budget_mb, args.combined_budget_mb))):
+        print("--draft-layers and the memory budgets apply to models served by the paged engine", file=sys.stderr)
+        return 2
+    if args.draft_model and eng is not None:
         eng.spec_k = args.speculative_k
     if args.draft_layers:
         if args.draft_model:
@@ -168,6 +172,8 @@ def cmd_generate(args) -> int:
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                         min_p=args.min_p, repetition_penalty=args.repetition_penalty, seed=args.seed,
                         cache_compaction_ratio=args.cache_compaction_ratio)
+    if eng is None and args.draft_model:
+        sp.speculative_k = args.speculative_k
     out = gen.generate(args.prompt, sp, raw_prompt=args.no_chat_template or args.raw_prompt,
                        on_delta=(lambda d: (sys.stdout.write(d), sys.stdout.flush())) if args.stream else None,
                        images=args.image or None)
@@ -181,9 +187,68 @@ def cmd_generate(args) -> int:
         print("finish_reason:", out.finish_reason, file=sys.stderr)
     if args.print_timing:
         print(out.timing_line(), file=sys.stderr)
-        if eng.draft is not None:
+        if eng is not None and eng.draft is not None:
             print(eng.spec.line(), file=sys.stderr)
     return 0
+
+
+def cmd_run_artifact(args) -> int:
+    """Generate straight from a compiled artifact file (weights already in the kernels' layout): the reference's
+    ``run-artifact`` (zig/pkg/inference/src/native_run_artifact.zig)."""
+    import os
+
+    from .models.llama import LlamaModel
+    from .pipelines.generation import Generator
+    from .runtime.engine import LLMEngine
+    from .runtime.sampling_params import SamplingParams
+    from .tokenizer import load_tokenizer
+
+    import torch
+
+    device = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model = LlamaModel.from_artifact(args.artifact, device=device)
+    tok = load_tokenizer(args.tokenizer_dir or os.path.dirname(os.path.abspath(args.artifact)), model.cfg.vocab_size)
+    eng = LLMEngine(model, num_blocks=args.kv_blocks, use_cuda_graph=device == "cuda", eos_token_id=tok.special.eos_id)
+    out = Generator(eng, tok).generate(args.prompt, SamplingParams(max_tokens=args.max_tokens,
+                                                                    temperature=args.temperature, seed=args.seed),
+                                       raw_prompt=args.raw_prompt)
+    print(out.text)
+    if args.print_timing:
+        print(out.timing_line(), file=sys.stderr)
+    return 0
+
+
+def cmd_extract(args) -> int:
+    """Schema-driven extraction (entities, relations, classifications) over texts: the request the ``/ai/v1/extract``
+    endpoint takes, answered in-process (zig/pkg/inference/src/main.zig ``extract``)."""
+    from fastapi.testclient import TestClient
+
+    from .api.server import create_app
+
+    schema = {}
+    if args.entities:
+        schema["entities"] = args.entities
+    if args.relations:
+        schema["relations"] = [{"type": r} for r in args.relations]
+    if args.classify:
+        schema["classifications"] = [{"name": "label", "labels": args.classify}]
+    if args.schema:
+        with open(args.schema, encoding="utf-8") as f:
+            schema = json.load(f)
+    body = {"model": args.model, "inputs": [{"id": str(i), "content": t} for i, t in enumerate(args.text)],
+            "schema": schema, "options": {"threshold": args.threshold, "resolve": args.resolve}}
+    r = TestClient(create_app(_manager(args))).post("/ai/v1/extract", json=body)
+    print(json.dumps(r.json(), indent=None if args.compact else 2))
+    return 0 if r.status_code == 200 else 2
+
+
+def cmd_bench(args) -> int:
+    """Forwards to ``bench.py`` at the repository root (one process; multi-GPU runs go through torchrun)."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return subprocess.call([sys.executable, os.path.join(root, "bench.py")] + list(args.rest))
 
 
 def cmd_search(args) -> int:
@@ -424,6 +489,21 @@ def main(argv: Optional[List[str]] = None) -> int:
         p.add_argument(flag, type=int, default=0)
     p.add_argument("--print-timing", action="store_true"); p.add_argument("--print-token-ids", action="store_true")
     p.add_argument("--print-finish-reason", action="store_true"); p.set_defaults(fn=cmd_generate)
+    p = sub.add_parser("run-artifact", help="generate from a compiled artifact file")
+    p.add_argument("--artifact", required=True); p.add_argument("--prompt", required=True)
+    p.add_argument("--tokenizer-dir"); p.add_argument("--device"); p.add_argument("--kv-blocks", type=int, default=1024)
+    p.add_argument("--max-tokens", type=int, default=128); p.add_argument("--temperature", type=float, default=0.0)
+    p.add_argument("--seed", type=int); p.add_argument("--raw-prompt", action="store_true")
+    p.add_argument("--print-timing", action="store_true"); p.set_defaults(fn=cmd_run_artifact)
+    p = sub.add_parser("extract", help="entities / relations / classifications by schema"); common(p)
+    p.add_argument("--model", required=True); p.add_argument("--text", nargs="+", required=True)
+    p.add_argument("--entities", nargs="*", default=[]); p.add_argument("--relations", nargs="*", default=[])
+    p.add_argument("--classify", nargs="*", default=[], help="labels of one classification task")
+    p.add_argument("--schema", help="JSON file with the full schema"); p.add_argument("--threshold", type=float, default=0.0)
+    p.add_argument("--resolve", action="store_true"); p.add_argument("--compact", action="store_true")
+    p.set_defaults(fn=cmd_extract)
+    p = sub.add_parser("bench", help="forwards its arguments to bench.py")
+    p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("search")
     p.add_argument("--index", required=True); p.add_argument("--vector"); p.add_argument("--packed")
     p.add_argument("--k", type=int, default=10); p.add_argument("--nprobe", type=int, default=64)
@@ -433,6 +513,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.set_defaults(fn=cmd_quantize)
     p = sub.add_parser("list"); common(p); p.set_defaults(fn=cmd_list)
     p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)
+    raw = list(sys.argv[1:] if argv is None else argv)
+    if raw and raw[0] == "bench":              # everything after the command belongs to bench.py, options included
+        return cmd_bench(argparse.Namespace(rest=raw[1:]))
     args = ap.parse_args(argv)
     return args.fn(args)
 

@@ -247,8 +247,120 @@ class ByteTokenizer(Tokenizer):
         return bs.decode("utf-8", errors="replace")
 
 
+_BYTE_LEVEL_INV: Dict[str, int] = {}
+
+
+def _byte_level_inverse() -> Dict[str, int]:
+    """Character -> byte of the byte-level BPE alphabet: printable Latin-1 bytes stand for themselves, the other 68
+    bytes are spelled as the code points from U+0100 upwards, in byte order."""
+    if not _BYTE_LEVEL_INV:
+        keep = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+        extra = 0
+        for b in range(256):
+            if b in keep:
+                _BYTE_LEVEL_INV[chr(b)] = b
+            else:
+                _BYTE_LEVEL_INV[chr(256 + extra)] = b
+                extra += 1
+    return _BYTE_LEVEL_INV
+
+
+class GGUFTokenizer(Tokenizer):
+    """The tokenizer a GGUF file carries in its metadata (``tokenizer.ggml.*``).
+
+    ``gpt2`` models: byte-level BPE from the token list and the merge list, control tokens as added tokens -- what
+    the reference builds (zig/pkg/inference/src/server/model_manager.zig:406-466).  ``llama`` models: the
+    SentencePiece-style BPE of those files (space -> U+2581 with a leading one, adjacent pieces merged in order of
+    the vocabulary's scores, ``<0xXX>`` byte tokens for characters the vocabulary lacks)."""
+
+    def __init__(self, metadata: dict):
+        md = metadata
+        self.kind = str(md.get("tokenizer.ggml.model", ""))
+        self.tokens: List[str] = [str(t) for t in md.get("tokenizer.ggml.tokens") or []]
+        if not self.tokens or self.kind not in ("gpt2", "llama"):
+            raise ValueError(f"no usable tokenizer in the GGUF metadata (model {self.kind!r})")
+        self.vocab_size = len(self.tokens)
+        self.types = [int(t) for t in md.get("tokenizer.ggml.token_type") or []] or [1] * self.vocab_size
+        tid = lambda k: int(md[k]) if md.get(k) is not None and 0 <= int(md[k]) < self.vocab_size else None
+        bos, eos = tid("tokenizer.ggml.bos_token_id"), tid("tokenizer.ggml.eos_token_id")
+        pad, unk = tid("tokenizer.ggml.padding_token_id"), tid("tokenizer.ggml.unknown_token_id")
+        self.special = SpecialTokens(cls_id=bos or 0, sep_id=eos or 0, pad_id=pad or 0, unk_id=unk or 0,
+                                     bos_id=bos, eos_id=eos)
+        self.chat_template = md.get("tokenizer.chat_template")
+        self.index = {t: i for i, t in enumerate(self.tokens)}
+        self.control = {i for i, t in enumerate(self.types) if t == 3} | {x for x in (bos, eos, pad) if x is not None}
+        if self.kind == "gpt2":
+            from tokenizers import Tokenizer as _T, decoders, models, pre_tokenizers
+
+            merges = [tuple(m.split(" ", 1)) for m in md.get("tokenizer.ggml.merges") or []]
+            self.tk = _T(models.BPE(vocab=dict(self.index), merges=merges))
+            self.tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+            self.tk.decoder = decoders.ByteLevel()
+            self.tk.add_special_tokens([self.tokens[i] for i in sorted(self.control)])
+        else:
+            self.scores = [float(x) for x in md.get("tokenizer.ggml.scores") or [0.0] * self.vocab_size]
+            self.bytes = {int(t[3:5], 16): i for i, t in enumerate(self.tokens)
+                          if len(t) == 6 and t.startswith("<0x") and t.endswith(">")}
+            self.add_space_prefix = bool(md.get("tokenizer.ggml.add_space_prefix", True))
+
+    @classmethod
+    def from_file(cls, path: str) -> "GGUFTokenizer":
+        from ..formats.gguf import GGUFFile
+
+        return cls(GGUFFile(path).metadata)
+
+    def _spm(self, text: str) -> List[int]:
+        if not text:
+            return []
+        s = text.replace(" ", "\u2581")
+        if self.add_space_prefix:
+            s = "\u2581" + s
+        parts = list(s)
+        while len(parts) > 1:                       # merge the best-scoring adjacent pair that is a piece
+            best, at = None, -1
+            for i in range(len(parts) - 1):
+                j = self.index.get(parts[i] + parts[i + 1])
+                if j is not None and (best is None or self.scores[j] > best):
+                    best, at = self.scores[j], i
+            if at < 0:
+                break
+            parts[at:at + 2] = [parts[at] + parts[at + 1]]
+        out: List[int] = []
+        for p in parts:
+            j = self.index.get(p)
+            if j is not None:
+                out.append(j)
+                continue
+            for b in p.encode("utf-8"):             # byte fallback, else the unknown token
+                out.append(self.bytes.get(b, self.special.unk_id))
+        return out
+
+    def encode(self, text: str) -> List[int]:
+        if self.kind == "gpt2":
+            return list(self.tk.encode(text, add_special_tokens=False).ids)
+        return self._spm(text)
+
+    def token_bytes(self, token_id: int) -> bytes:
+        t = int(token_id)
+        if t in self.control or not 0 <= t < self.vocab_size:
+            return b""
+        if self.kind == "gpt2":                     # token text is bytes spelled in the byte-level alphabet
+            return bytes(_byte_level_inverse()[c] for c in self.tokens[t] if c in _byte_level_inverse())
+        piece = self.tokens[t]
+        if len(piece) == 6 and piece.startswith("<0x") and piece.endswith(">"):
+            return bytes([int(piece[3:5], 16)])
+        return piece.replace("\u2581", " ").encode("utf-8")
+
+    def decode(self, ids: Sequence[int]) -> str:
+        ids = [int(i) for i in ids if int(i) not in self.control]
+        if self.kind == "gpt2":
+            return self.tk.decode(ids, skip_special_tokens=True)
+        text = b"".join(self.token_bytes(i) for i in ids).decode("utf-8", "replace")
+        return text[1:] if self.add_space_prefix and text.startswith(" ") else text
+
+
 def load_tokenizer(model_dir: str, vocab_size: int = 0) -> Tokenizer:
-    """tokenizer.json -> HFTokenizer; vocab.txt -> WordPiece; otherwise the byte tokenizer
+    """tokenizer.json -> HFTokenizer; vocab.txt -> WordPiece; a GGUF file's own tokenizer; otherwise the byte tokenizer
     (selection order of zig/pkg/inference/src/server/model_manager.zig:383-520)."""
     cfg = {}
     for name in ("tokenizer_config.json", "special_tokens_map.json"):
@@ -272,4 +384,10 @@ def load_tokenizer(model_dir: str, vocab_size: int = 0) -> Tokenizer:
     vt = os.path.join(model_dir, "vocab.txt")
     if os.path.exists(vt):
         return WordPieceTokenizer.from_vocab_file(vt, lower=cfg.get("do_lower_case", True))
+    for name in sorted(os.listdir(model_dir)) if os.path.isdir(model_dir) else []:
+        if name.endswith(".gguf"):                      # the tokenizer the weights file carries in its metadata
+            try:
+                return GGUFTokenizer.from_file(os.path.join(model_dir, name))
+            except (ValueError, ImportError, KeyError):
+                break
     return ByteTokenizer(vocab_size or 512)

@@ -118,3 +118,32 @@ def test_compile_artifact_is_loaded_instead_of_repacking(capsys, tmp_path):
     assert lm.info["weights"] == "compiled"
     with __import__("pytest").raises(ValueError):
         LlamaModel.from_artifact(str(src / "model.safetensors"), device="cpu")
+    # run-artifact: the same tokens as the served model, straight from the artifact file
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    capsys.readouterr()
+    assert main(["run-artifact", "--artifact", rep["out"], "--device", "cpu", "--kv-blocks", "32", "--prompt", "hi",
+                 "--max-tokens", "5", "--raw-prompt", "--print-timing"]) == 0
+    cap = capsys.readouterr()
+    want = lm.pipeline.generate("hi", SamplingParams(max_tokens=5), raw_prompt=True).text
+    assert cap.out.rstrip("\n") == want and "generate_timing_ms:" in cap.err
+
+
+def test_cli_extract_answers_a_schema_in_process(capsys, tmp_path):
+    from tests.test_api_cpu import _write_bert
+
+    _write_bert(tmp_path / "recognizers" / "tiny-ner", 5, ["O", "B-PER", "I-PER", "B-LOC", "I-LOC"], 1)
+    assert main(["extract", "--models-dir", str(tmp_path), "--device", "cpu", "--model", "tiny-ner", "--text",
+                 "alice met bob in paris", "--entities", "PER", "LOC", "--compact"]) == 0
+    body = json.loads(capsys.readouterr().out)
+    assert body["object"] == "extraction" and body["data"][0]["id"] == "0"
+    assert all(e["label"] in ("PER", "LOC") for e in body["data"][0]["entities"])
+    assert main(["extract", "--models-dir", str(tmp_path), "--device", "cpu", "--model", "nope", "--text", "x",
+                 "--entities", "PER", "--compact"]) == 2
+    capsys.readouterr()
+
+
+def test_cli_bench_forwards_to_the_bench_script(capfd):
+    assert main(["bench", "--impl", "reference", "--workload", "cpu"]) == 0
+    line = [l for l in capfd.readouterr().out.splitlines() if l.startswith("{")][-1]
+    assert json.loads(line)["impl"] == "reference" and "unavailable" in json.loads(line)
