@@ -104,6 +104,7 @@ class Gemma4State:
     kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)   # layer -> (K, V) [Hkv, t, D]
     length: int = 0
     last_hidden: Optional[torch.Tensor] = None      # final-norm hidden row of the newest token
+    groups: Optional[torch.Tensor] = None           # image number of the current call's tokens (-1 = text)
 
 
 class Gemma4TextModel:
@@ -207,7 +208,7 @@ class Gemma4TextModel:
         mask = kpos <= qpos
         if sliding:
             mask = mask & (kpos > qpos - c.sliding_window)
-            grp = getattr(self, "_groups", None)
+            grp = st.groups
             if grp is not None and n_keys == T:           # whole prompt in one call: image tokens see their image
                 gq = grp.to(h.device)
                 mask = mask | ((gq[:, None] == gq[None, :]) & (gq[:, None] >= 0))
@@ -250,7 +251,7 @@ class Gemma4TextModel:
         if soft_rows is not None:
             ids = ids.clone()
             ids[soft_rows.long()] = pad_token_id
-        self._groups = vision_groups
+        st.groups = vision_groups              # (kept on the sequence's state: requests may run concurrently)
         pos = torch.arange(st.length, st.length + T, device=ids.device)
         scale = torch.tensor(c.hidden_size ** 0.5, dtype=self.dtype)      # the reference model rounds the scale too
         x = (w["embed"][ids] * scale.to(w["embed"].device)).float()
