@@ -188,6 +188,19 @@ def paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens
     if k_cache.dtype != torch.bfloat16:
         raise NotImplementedError("this entry reads a bf16 KV cache; quantised caches are passed as CodecLayer "
                                   "objects (ops.kv_quant)")
+    if D not in (64, 128, 256):
+        # Head widths the tensor-core kernels are not built for (80 / 96-wide heads of some small decoders): the
+        # general one-warp-per-row kernel reads the cache at its own width.
+        if not causal or D % 8 or D > 256:
+            raise NotImplementedError(f"paged attention needs a head width that is a multiple of 8 up to 256 "
+                                      f"(non-causal: 64, 128 or 256); got {D}")
+        y = paged_attention_sink(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale=scale,
+                                 window=window, out=out)
+        if mx_terms:
+            from . import quant as Q
+
+            return Q.quantize_mx(y.reshape(T, Hq * D), terms=mx_terms)
+        return y
     G = Hq // Hkv
     if decode is None:
         decode = max_q_len * G <= 16

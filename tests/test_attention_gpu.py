@@ -233,3 +233,27 @@ def test_sink_softcap_attention_kernel_matches_fp32_reference(Hq, Hkv, D, sinks,
     out = A.paged_attention_sink(q.cuda(), kc.cuda(), vc.cuda(), bad.cuda(), qs.cuda(), ql.cuda(), kl.cuda(),
                                  sinks=sk.cuda() if sinks else None, softcap=softcap)
     assert N.status() & 32 and bool(torch.isfinite(out.float()).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [80, 96])
+def test_paged_attention_with_head_widths_outside_the_tensor_core_set(D):
+    """80- and 96-wide heads go through the general kernel at their own width (prefill rows and decode rows)."""
+    import torch
+
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(D)
+    Hq, Hkv, page, nblk = 8, 4, 16, 32
+    q_lens, kv_lens = [1, 33, 1], [70, 33, 5]
+    kc = (torch.randn(nblk, page, Hkv, D, generator=g) * 0.5).to(torch.bfloat16)
+    vc = torch.randn(nblk, page, Hkv, D, generator=g).to(torch.bfloat16)
+    bt = torch.randperm(nblk, generator=g).int()[:15].view(3, 5)
+    q = torch.randn(sum(q_lens), Hq, D, generator=g).to(torch.bfloat16)
+    ql = torch.tensor(q_lens, dtype=torch.int32)
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    kl = torch.tensor(kv_lens, dtype=torch.int32)
+    got = A.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), qs.cuda(), ql.cuda(), kl.cuda(), 33)
+    want = R.paged_attention(q, kc, vc, bt, qs, ql, kl, D ** -0.5, 0)
+    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
