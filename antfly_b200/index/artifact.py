@@ -190,9 +190,17 @@ def encode_vector_set(x: torch.Tensor) -> bytes:
 
 
 def decode_vector_set(b: bytes) -> torch.Tensor:
-    inner = next(v for num, _w, v in _parse(b) if num == 1)
-    f = {num: v for num, _w, v in _parse(inner)}
-    return _unpack_floats(f.get(3, b"")).view(f.get(2, 0), f.get(1, 0))
+    """NonQuantizedVectorSet (field 1 wraps the Set) or a bare Set{dims, count, data}, the form of the reference's
+    checked-in ``.pbvec`` recall fixtures (zig/lib/vector/src/proto.zig, zig/bench/vectors/recall_common.zig:56)."""
+    fields = list(_parse(b))
+    if fields and fields[0][0] == 1 and fields[0][1] == 2:
+        fields = list(_parse(fields[0][2]))
+    f = {num: v for num, _w, v in fields}
+    x = _unpack_floats(f.get(3, b""))
+    dims, count = int(f.get(1, 0)), int(f.get(2, 0))
+    if x.numel() != dims * count:
+        raise ValueError("vector set size does not match dims * count")
+    return x.view(count, dims)
 
 
 def _write_ns(path: str, kv: Dict[bytes, bytes]) -> None:
