@@ -242,6 +242,72 @@ def cmd_extract(args) -> int:
     return 0 if r.status_code == 200 else 2
 
 
+def cmd_cuda_info(args) -> int:
+    """Device report in the reference's ``cuda-info`` key: value form (zig/pkg/inference/src/cuda_info.zig), plus
+    what this build adds (SM count, memory, library paths); ``--smoke`` runs the tiny end-to-end check."""
+    import torch
+
+    if not torch.cuda.is_available():
+        print("cuda: unavailable\nreason: no CUDA device visible to this process")
+        return 1
+    from . import _native as N
+
+    dev = torch.cuda.current_device()
+    prop = torch.cuda.get_device_properties(dev)
+    print("cuda: available")
+    print(f"driver_version: {torch.version.cuda}")
+    print(f"device_count: {torch.cuda.device_count()}")
+    print(f"selected_device: {dev}")
+    print(f"device_name: {prop.name}")
+    print(f"compute_capability: sm_{prop.major}{prop.minor}")
+    print(f"multiprocessors: {prop.multi_processor_count}")
+    print(f"memory_bytes: {prop.total_memory}")
+    print(f"artifacts: {N._LIB_DIR}")
+    if prop.major != 10:
+        print("note: the kernels are built for sm_100a only")
+    if args.smoke:
+        rc = cmd_smoke(args)
+        print("smoke: ok" if rc == 0 else "smoke: failed")
+        return rc
+    return 0
+
+
+def cmd_dequant(args) -> int:
+    """Raw blocks of one GGUF tensor type on stdin -> fp32 values on stdout (the reference's ``dequant_cli``,
+    zig/pkg/inference/src/dequant_cli.zig)."""
+    import numpy as np
+    import torch
+
+    from .formats import gguf as GG
+    from .ops import gguf_ops as G
+
+    names = {v.lower(): k for k, v in GG.TYPE_NAMES.items()}
+    key = args.format.lower()
+    if key not in names and not key.isdigit():
+        print(f"unknown format: {args.format}", file=sys.stderr)
+        return 2
+    type_id = int(key) if key.isdigit() else names[key]
+    try:
+        bv, bb = G.block_geometry(type_id)
+    except NotImplementedError:
+        print(f"no block size for {args.format}", file=sys.stderr)
+        return 2
+    raw = (open(args.input, "rb") if args.input else sys.stdin.buffer).read()
+    if len(raw) % bb:
+        print(f"input size {len(raw)} not a multiple of block size {bb}", file=sys.stderr)
+        return 2
+    n = len(raw) // bb * bv
+    out = G.dequantize(torch.from_numpy(np.frombuffer(raw, dtype=np.uint8).copy()), type_id, (n,), torch.float32)
+    data = out.numpy().astype("<f4").tobytes()
+    if args.output:
+        with open(args.output, "wb") as f:
+            f.write(data)
+    else:
+        sys.stdout.buffer.write(data)
+        sys.stdout.buffer.flush()
+    return 0
+
+
 def cmd_bench(args) -> int:
     """Forwards to ``bench.py`` at the repository root (one process; multi-GPU runs go through torchrun)."""
     import os
@@ -372,7 +438,7 @@ def cmd_read(args) -> int:
 
     lm = _manager(args).get(args.model, "reader")
     imgs = [torch.from_numpy(np.asarray(Image.open(p).convert("RGB")).copy()) for p in args.image]
-    for path, r in zip(args.image, lm.pipeline.read(imgs, args.max_tokens)):
+    for path, r in zip(args.image, lm.pipeline.read(imgs, args.max_tokens, prompt=args.prompt)):
         print(json.dumps({"image": path, "text": r.text}))
     return 0
 
@@ -455,6 +521,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--print-timing", action="store_true"); p.set_defaults(fn=cmd_transcribe)
     p = sub.add_parser("read", help="OCR: text of each image"); common(p)
     p.add_argument("--model", required=True); p.add_argument("--image", nargs="+", required=True)
+    p.add_argument("--prompt", help="task prompt of models that take one (Florence-2: <OCR>, <CAPTION>, ...)")
     p.add_argument("--max-tokens", type=int, default=256); p.set_defaults(fn=cmd_read)
     p = sub.add_parser("compare", help="same embedder on two devices: embedding parity report")
     p.add_argument("--models-dir"); p.add_argument("--model", required=True)
@@ -502,6 +569,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--schema", help="JSON file with the full schema"); p.add_argument("--threshold", type=float, default=0.0)
     p.add_argument("--resolve", action="store_true"); p.add_argument("--compact", action="store_true")
     p.set_defaults(fn=cmd_extract)
+    p = sub.add_parser("cuda-info", help="device report"); p.add_argument("--smoke", action="store_true")
+    p.set_defaults(fn=cmd_cuda_info)
+    p = sub.add_parser("dequant", help="GGUF blocks on stdin -> fp32 on stdout")
+    p.add_argument("format", help="tensor type name (q4_k, iq2_xs, ...) or id"); p.add_argument("--input")
+    p.add_argument("--output"); p.set_defaults(fn=cmd_dequant)
     p = sub.add_parser("bench", help="forwards its arguments to bench.py")
     p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("search")

@@ -147,3 +147,29 @@ def test_cli_bench_forwards_to_the_bench_script(capfd):
     assert main(["bench", "--impl", "reference", "--workload", "cpu"]) == 0
     line = [l for l in capfd.readouterr().out.splitlines() if l.startswith("{")][-1]
     assert json.loads(line)["impl"] == "reference" and "unavailable" in json.loads(line)
+
+
+def test_cli_dequant_and_cuda_info(capsys, tmp_path):
+    import numpy as np
+    import torch
+
+    raw = bytearray()
+    for b in range(3):
+        raw += np.float16(0.5 * (b + 1)).tobytes() + bytes((np.arange(32, dtype=np.int8) - 16 + b).view(np.uint8))
+    (tmp_path / "in.bin").write_bytes(bytes(raw))
+    assert main(["dequant", "q8_0", "--input", str(tmp_path / "in.bin"), "--output", str(tmp_path / "out.bin")]) == 0
+    out = np.frombuffer((tmp_path / "out.bin").read_bytes(), dtype="<f4")
+    want = np.concatenate([0.5 * (b + 1) * (np.arange(32) - 16 + b) for b in range(3)]).astype(np.float32)
+    assert np.array_equal(out, want)
+    assert main(["dequant", "8", "--input", str(tmp_path / "in.bin"), "--output", str(tmp_path / "o2.bin")]) == 0
+    assert (tmp_path / "o2.bin").read_bytes() == (tmp_path / "out.bin").read_bytes()
+    (tmp_path / "bad.bin").write_bytes(b"123")
+    assert main(["dequant", "q8_0", "--input", str(tmp_path / "bad.bin")]) == 2
+    assert main(["dequant", "no_such_format", "--input", str(tmp_path / "in.bin")]) == 2
+    capsys.readouterr()
+    rc = main(["cuda-info"])
+    text = capsys.readouterr().out
+    if torch.cuda.is_available():
+        assert rc == 0 and "device_name:" in text and "compute_capability: sm_" in text
+    else:
+        assert rc == 1 and text.startswith("cuda: unavailable")
