@@ -101,6 +101,7 @@ class GenerateRequest(BaseModel):
     mode: Optional[str] = None
     grammar: Optional[str] = None
     response_format: Optional[Dict[str, Any]] = None
+    compiled_target: Optional[str] = None       # the reference's compiled-graph hint (partitioned | whole-model); no effect here
     tools: Optional[List[Dict[str, Any]]] = None
     tool_choice: Optional[Union[str, Dict[str, Any]]] = None
 
@@ -127,11 +128,17 @@ class GenerateResponse(BaseModel):
 
 
 class ChunkRequest(BaseModel):
-    text: str
-    model: str = "fixed"
-    target_tokens: int = 500
-    overlap_tokens: int = 50
-    max_chunks: int = 0
+    """``input`` (a string, or a content part: ``{"type": "text", "text": ...}`` /
+    ``{"type": "media", "mime_type": "audio/wav", "data": <base64>}``) with ``config`` {model, max_chunks, threshold,
+    text: {target_tokens, overlap_tokens, separator}, audio: {window_duration_ms, overlap_duration_ms}}; ``text``
+    and the flat option fields are the older spelling and still accepted."""
+    input: Union[str, Dict[str, Any], None] = None
+    text: Optional[str] = None
+    config: Dict[str, Any] = Field(default_factory=dict)
+    model: Optional[str] = None
+    target_tokens: Optional[int] = None
+    overlap_tokens: Optional[int] = None
+    max_chunks: Optional[int] = None
 
 
 class ErrorBody(BaseModel):

@@ -637,17 +637,76 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         req, bad = await parse(request, S.ChunkRequest)
         if bad:
             return bad
-        if req.model in ("fixed", "", None):
-            chunks = chunk_text(req.text, req.target_tokens, req.overlap_tokens, req.max_chunks)
+        cfg = dict(req.config or {})
+        topt, aopt = dict(cfg.get("text") or {}), dict(cfg.get("audio") or {})
+        model = cfg.get("model") or req.model or "fixed"
+        max_chunks = int(cfg.get("max_chunks") or req.max_chunks or 0)
+        target = int(topt.get("target_tokens") or req.target_tokens or 500)
+        overlap = topt.get("overlap_tokens")
+        overlap = int(overlap if overlap is not None else (req.overlap_tokens if req.overlap_tokens is not None else 50))
+        part = req.input if req.input is not None else req.text
+        if part is None:
+            return _err(400, "invalid_request", "input is required")
+        binary = None
+        if isinstance(part, dict):
+            if part.get("type") == "text" or "text" in part:
+                part = str(part.get("text") or "")
+            else:
+                import base64
+
+                try:
+                    binary = (str(part.get("mime_type") or "application/octet-stream"),
+                              base64.b64decode(part.get("data") or "", validate=False))
+                except Exception as e:
+                    return _err(400, "invalid_request", f"media data is not base64: {e}")
+
+        def usage(n):
+            return {"prompt_tokens": n, "completion_tokens": 0, "total_tokens": n}
+
+        def pack(chunks, used, ntok):
+            import base64
+
+            data = []
+            for i, c in enumerate(chunks):
+                o = {"object": "chunk", "index": i, "id": int(c.get("id", i)), "mime_type": c.get("mime_type", "text/plain")}
+                for k in ("text", "start_char", "end_char", "start_time_ms", "end_time_ms", "frame_index", "frame_delay_ms"):
+                    if k in c:
+                        o[k] = c[k]
+                if "data" in c:
+                    o["data"] = base64.b64encode(c["data"]).decode()
+                data.append(o)
+            # ``chunks`` is the older response field, kept beside the reference's ``data``
+            return {"object": "list", "data": data, "chunks": data, "model": used, "usage": usage(ntok),
+                    "cache_hit": False}
+
+        if binary is not None:
+            from ..pipelines.chunking import chunk_binary
+
+            try:
+                ch = chunk_binary(binary[0], binary[1], int(aopt.get("window_duration_ms") or 30000),
+                                  int(aopt.get("overlap_duration_ms") or 0), max_chunks)
+            except Exception as e:
+                return _err(400, "invalid_request", str(e))
             metrics.requests.labels("chunk", "200").inc()
-            return {"chunks": chunks, "model": req.model}
+            return pack(ch, "fixed", 0)
+        text = str(part)
+        from ..pipelines.chunking import _tokens
+
+        if model in ("fixed", "", None):
+            try:
+                chunks = chunk_text(text, target, overlap, max_chunks, str(topt.get("separator") or "\n\n"))
+            except ValueError as e:
+                return _err(400, "invalid_request", str(e))
+            metrics.requests.labels("chunk", "200").inc()
+            return pack(chunks, "fixed", len(_tokens(text)))
 
         def work():
             from ..pipelines.chunking import NeuralChunker
 
-            lm = mgr.get(req.model, "chunker")
-            ch = NeuralChunker(lm.pipeline).chunk(req.text, max_tokens=req.target_tokens, max_chunks=req.max_chunks)
-            return {"chunks": ch, "model": req.model}
+            lm = mgr.get(model, "chunker")
+            kw = {"threshold": float(cfg["threshold"])} if cfg.get("threshold") is not None else {}
+            ch = NeuralChunker(lm.pipeline, **kw).chunk(text, max_tokens=target, max_chunks=max_chunks)
+            return pack(ch, model, len(_tokens(text)))
 
         return await asyncio.to_thread(run_guarded, "chunk", 1, work)
 

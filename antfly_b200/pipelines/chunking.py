@@ -2,32 +2,177 @@
 preference; zig/pkg/inference/src/pipelines/chunking.zig)."""
 from __future__ import annotations
 
-from typing import List
+import re
+from typing import List, Tuple
+
+
+_TOKEN = re.compile(r"\w+|[^\w\s]", re.UNICODE)
+DEFAULT_MAX_CHUNKS = 50
+
+
+def _tokens(text: str) -> List[Tuple[int, int]]:
+    """(start, end) character spans of the chunker's token model: words and single punctuation marks.  (The
+    reference counts with an embedded subword tokenizer, zig/lib/chunker/src/fixed_text.zig:35; only the counts
+    differ, not the structure of the result.)"""
+    return [m.span() for m in _TOKEN.finditer(text)]
+
+
+def _split(text: str, start: int, sep: str) -> List[Tuple[str, int]]:
+    """Pieces of ``text`` between occurrences of ``sep`` with their absolute start; a ". " separator keeps the
+    full stop with the sentence."""
+    if not sep:
+        return [(text, start)]
+    out, at = [], 0
+    while at <= len(text):
+        nxt = text.find(sep, at)
+        if nxt < 0:
+            nxt = len(text)
+        end = nxt + 1 if sep == ". " and nxt < len(text) else nxt
+        out.append((text[at:end], start + at))
+        if nxt == len(text):
+            break
+        at = nxt + len(sep)
+    return out
+
+
+def _flatten(sections: List[Tuple[str, int]], target: int) -> List[Tuple[str, int, int]]:
+    """Sections above the target are split by ever finer separators (newline, sentence, space), at last into token
+    windows: -> (text, start, tokens)."""
+    out: List[Tuple[str, int, int]] = []
+    for text, start in sections:
+        spans = _tokens(text)
+        if len(spans) <= target:
+            out.append((text, start, len(spans)))
+            continue
+        for sep in ("\n", ". ", " "):
+            finer = _split(text, start, sep)
+            if len(finer) > 1:
+                out.extend(_flatten(finer, target))
+                break
+        else:
+            for i in range(0, len(spans), target):
+                a, b = spans[i][0], spans[min(i + target, len(spans)) - 1][1]
+                out.append((text[a:b], start + a, min(target, len(spans) - i)))
+    return out
 
 
 def chunk_text(text: str, target_tokens: int = 500, overlap_tokens: int = 50, max_chunks: int = 0,
                separator: str = "\n\n") -> List[dict]:
-    words = text.split()
-    if not words:
+    """Fixed-size chunking the way the reference's ``fixed`` chunker does it (zig/lib/chunker/src/fixed_text.zig):
+    the text is cut at the separator (falling back to newlines, then sentences, when it does not occur), sections
+    are packed greedily up to ``target_tokens``, every chunk after the first starts with the last
+    ``overlap_tokens`` tokens of its predecessor, and at most ``max_chunks`` (default 50) chunks are returned.
+    Chunks are spans of the source: ``text[start_char:end_char]``."""
+    if not text:
         return []
-    step = max(target_tokens - overlap_tokens, 1)
-    chunks, i, pos = [], 0, 0
-    # Character offsets are tracked so callers can map chunks back into the source text.
-    offsets, cursor = [], 0
-    for w in words:
-        cursor = text.index(w, cursor)
-        offsets.append(cursor)
-        cursor += len(w)
-    while i < len(words):
-        j = min(len(words), i + target_tokens)
-        start, end = offsets[i], offsets[j - 1] + len(words[j - 1])
-        chunks.append({"id": len(chunks), "text": text[start:end], "start_char": start, "end_char": end})
-        if max_chunks and len(chunks) >= max_chunks:
-            break
-        if j == len(words):
-            break
-        i += step
+    target = target_tokens if target_tokens > 0 else 500
+    limit = max_chunks if max_chunks > 0 else DEFAULT_MAX_CHUNKS
+    sep = separator or "\n\n"
+    if overlap_tokens >= target:
+        raise ValueError("overlap_tokens must be smaller than target_tokens")
+    sections = _split(text, 0, sep)
+    if len(sections) <= 1 and sep != "\n":
+        sections = _split(text, 0, "\n")
+    if len(sections) <= 1:
+        sections = _split(text, 0, ". ")
+    chunks: List[dict] = []
+
+    def emit(cur):
+        a, b = cur[0][1], cur[-1][1] + len(cur[-1][0])
+        chunks.append({"id": len(chunks), "text": text[a:b], "start_char": a, "end_char": b})
+
+    cur: List[Tuple[str, int, int]] = []
+    count = 0
+    for sec in _flatten(sections, target):
+        if count > 0 and count + sec[2] > target:
+            emit(cur)
+            if len(chunks) >= limit:
+                return chunks
+            prev = chunks[-1]
+            cur, count = [], 0
+            if overlap_tokens > 0:
+                spans = _tokens(prev["text"])
+                if len(spans) > overlap_tokens:
+                    a = spans[len(spans) - overlap_tokens][0]
+                    cur, count = [(prev["text"][a:], prev["start_char"] + a, overlap_tokens)], overlap_tokens
+                elif spans:
+                    cur, count = [(prev["text"], prev["start_char"], len(spans))], len(spans)
+        cur.append(sec)
+        count += sec[2]
+    if cur and len(chunks) < limit:
+        emit(cur)
     return chunks
+
+
+def chunk_wav(data: bytes, window_ms: int = 30000, overlap_ms: int = 0, max_chunks: int = 0) -> List[dict]:
+    """Fixed windows over a WAV file, each returned as a mono 16-bit WAV of its own with its time span
+    (zig/lib/chunker/src/fixed_multimodal.zig chunkWav)."""
+    import io
+    import wave
+
+    import numpy as np
+
+    with wave.open(io.BytesIO(data), "rb") as w:
+        rate, ch, width, n = w.getframerate(), w.getnchannels(), w.getsampwidth(), w.getnframes()
+        raw = w.readframes(n)
+    if width == 2:
+        x = np.frombuffer(raw, dtype="<i2").astype(np.float32) / 32768.0
+    elif width == 1:
+        x = (np.frombuffer(raw, dtype=np.uint8).astype(np.float32) - 128.0) / 128.0
+    elif width == 4:
+        x = np.frombuffer(raw, dtype="<i4").astype(np.float32) / 2147483648.0
+    else:
+        raise ValueError(f"unsupported WAV sample width {width}")
+    x = x.reshape(-1, ch).mean(1) if ch > 1 else x
+    win = rate * (window_ms if window_ms > 0 else 30000) // 1000
+    ovl = rate * max(overlap_ms, 0) // 1000
+    if win == 0:
+        raise ValueError("audio window is shorter than one sample")
+    if ovl >= win:
+        raise ValueError("audio overlap must be shorter than the window")
+    out, off = [], 0
+    while off < len(x):
+        end = min(off + win, len(x))
+        buf = io.BytesIO()
+        with wave.open(buf, "wb") as w:
+            w.setnchannels(1)
+            w.setsampwidth(2)
+            w.setframerate(rate)
+            w.writeframes((np.clip(x[off:end], -1.0, 1.0) * 32767.0).round().astype("<i2").tobytes())
+        out.append({"id": len(out), "mime_type": "audio/wav", "data": buf.getvalue(),
+                    "start_time_ms": off * 1000.0 / rate, "end_time_ms": end * 1000.0 / rate})
+        if max_chunks and len(out) >= max_chunks:
+            break
+        off += win - ovl
+    return out
+
+
+def chunk_gif(data: bytes, max_chunks: int = 0) -> List[dict]:
+    """Frames of an animated GIF as PNG images with their display delay (fixed_multimodal.zig chunkGif)."""
+    import io
+
+    from PIL import Image, ImageSequence
+
+    out = []
+    with Image.open(io.BytesIO(data)) as im:
+        for i, frame in enumerate(ImageSequence.Iterator(im)):
+            buf = io.BytesIO()
+            frame.convert("RGBA").save(buf, format="PNG")
+            out.append({"id": i, "mime_type": "image/png", "data": buf.getvalue(), "frame_index": i,
+                        "frame_delay_ms": int(frame.info.get("duration", 0))})
+            if max_chunks and len(out) >= max_chunks:
+                break
+    return out
+
+
+def chunk_binary(mime_type: str, data: bytes, window_ms: int = 30000, overlap_ms: int = 0,
+                 max_chunks: int = 0) -> List[dict]:
+    """WAV audio in windows, GIF animations in frames, anything else as one chunk."""
+    if mime_type == "audio/wav":
+        return chunk_wav(data, window_ms, overlap_ms, max_chunks)
+    if mime_type == "image/gif":
+        return chunk_gif(data, max_chunks)
+    return [{"id": 0, "mime_type": mime_type, "data": data}]
 
 
 class NeuralChunker:
