@@ -778,7 +778,8 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             out = lm.pipeline.transcribe(audio, language=req.language, task=req.task, max_new_tokens=req.max_tokens)
             metrics.tokens.labels("transcribe", "completion").inc(out.completion_tokens)
             return {"object": "list", "model": req.model,
-                    "data": [{"object": "transcription", "index": 0, "text": out.text, "segments": [
+                    "data": [{"object": "transcription", "index": 0, "text": out.text,
+                              **({"language": out.language} if out.language else {}), "segments": [
                         {k: v for k, v in sgm.items() if k != "tokens"} for sgm in out.segments]}],
                     "usage": {"prompt_tokens": out.prompt_tokens, "completion_tokens": out.completion_tokens,
                               "total_tokens": out.prompt_tokens + out.completion_tokens}}

@@ -25,6 +25,7 @@ class Transcription:
     prompt_tokens: int
     completion_tokens: int
     timing_ms: Dict[str, float] = field(default_factory=dict)
+    language: Optional[str] = None          # forced, or detected from the first window (multilingual checkpoints)
 
 
 class Transcriber:
@@ -53,6 +54,18 @@ class Transcriber:
             ids.append(int(g["no_timestamps_token_id"]))
         return ids
 
+    def detect_language(self, mel: torch.Tensor) -> Optional[str]:
+        """The language token the decoder finds most likely right after the start token (logits restricted to the
+        checkpoint's language tokens); None for English-only checkpoints or ones without a language table."""
+        lang_ids = self.gen.get("lang_to_id") or {}
+        if not lang_ids or not self.gen.get("is_multilingual", True):
+            return None
+        start = int(self.gen.get("decoder_start_token_id", self.model.cfg.decoder_start_token_id))
+        logits = self.model.decode(self.model.start_decoding(self.model.encode(mel)), [start])[-1].float()
+        keys = list(lang_ids)
+        ids = torch.tensor([int(lang_ids[k]) for k in keys], device=logits.device)
+        return keys[int(logits[ids].argmax())].strip("<|>")
+
     def transcribe(self, audio: Union[bytes, str, torch.Tensor], sample_rate: Optional[int] = None,
                    language: Optional[str] = None, task: str = "transcribe",
                    max_new_tokens: int = 224) -> Transcription:
@@ -63,6 +76,10 @@ class Transcriber:
             wav, rate = AO.read_wav(audio)
         wav = AO.resample(wav, rate)
         t1 = time.perf_counter()
+        if not language:                                      # multilingual checkpoint, nothing forced: detect once
+            first = AO.log_mel(wav[: self.chunk].to(self.model.device), self.model.cfg.num_mel_bins,
+                               n_samples=self.frames * 160)
+            language = self.detect_language(first)
         prompt = self.prompt(language, task)
         suppress = [int(t) for t in (self.gen.get("suppress_tokens") or []) if 0 <= int(t) < self.model.cfg.vocab_size]
         segments, n_prompt, n_out = [], 0, 0
@@ -79,4 +96,4 @@ class Transcriber:
         t2 = time.perf_counter()
         return Transcription(" ".join(s["text"] for s in segments if s["text"]).strip(), segments, n_prompt, n_out,
                              {"decode_audio": (t1 - t0) * 1e3, "transcribe": (t2 - t1) * 1e3,
-                              "total": (t2 - t0) * 1e3})
+                              "total": (t2 - t0) * 1e3}, language=language.strip("<|>") if language else None)

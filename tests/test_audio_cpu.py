@@ -114,3 +114,15 @@ def test_transcription_pipeline_and_endpoint(tmp_path):
     assert c.post("/ai/v1/transcribe", json={"model": "tiny-whisper",
                                              "audio": base64.b64encode(b"junk").decode()}).status_code == 400
     assert c.post("/ai/v1/transcribe", json={"model": "none", "audio": "AAAA"}).status_code == 404
+    # the forced language is echoed; with none forced the decoder's most likely language token is used
+    assert body["data"][0]["language"] == "en" and out.language == "en"
+    auto = pipe.transcribe(_wav_bytes(x, 8000), max_new_tokens=4)
+    mel = AO.log_mel(AO.resample(x, 8000), n_samples=pipe.frames * 160)
+    logits = pipe.model.decode(pipe.model.start_decoding(pipe.model.encode(mel)), [258])[-1]
+    want = "en" if float(logits[259]) >= float(logits[260]) else "de"
+    assert auto.language == want and auto.prompt_tokens == 4
+    assert auto.segments[0]["tokens"] == pipe.model.transcribe_ids(
+        mel, [258, 259 if want == "en" else 260, 261, 263], 4, [1])
+    r = c.post("/ai/v1/transcribe", json={"model": "tiny-whisper", "max_tokens": 4,
+                                          "audio": base64.b64encode(_wav_bytes(x, 8000)).decode()})
+    assert r.json()["data"][0]["language"] == want
