@@ -830,7 +830,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             n = sum(len(r.token_ids) for r in res)
             metrics.tokens.labels("read", "completion").inc(n)
             return {"object": "list", "model": req.model,
-                    "data": [{"object": "read", "index": i, "text": r.text} for i, r in enumerate(res)],
+                    "data": [{"object": "read", "index": i, "text": r.text,
+                              **({"regions": r.regions} if getattr(r, "regions", None) else {})}
+                             for i, r in enumerate(res)],
                     "usage": {"prompt_tokens": 0, "completion_tokens": n, "total_tokens": n}}
 
         return await asyncio.to_thread(run_guarded, "read", len(imgs), work)

@@ -4,6 +4,7 @@ TrOCR checkpoints are trained on; the reference's reader task (zig/pkg/inference
 go/pkg/termite/lib/pipelines/vision2seq.go) has the same single-image contract for this model family."""
 from __future__ import annotations
 
+import re
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Sequence
@@ -19,6 +20,38 @@ class ReadResult:
     text: str
     token_ids: List[int]
     timing_ms: Dict[str, float] = field(default_factory=dict)
+    regions: List[dict] = field(default_factory=list)      # [{text, bbox [x1, y1, x2, y2] in pixels}] when the task has them
+
+
+_LOC = re.compile(r"<loc_(\d+)>")
+
+
+def parse_location_text(text: str, width: int, height: int, quads: bool = False) -> List[dict]:
+    """Florence-2 region outputs -> regions.  The model writes a label (or a line of text) and its box as location
+    tokens ``<loc_0>`` .. ``<loc_999>`` (thousandths of the image side): four per box for detection and region
+    captions (several boxes may follow one label), eight per quadrilateral for OCR with regions (``quads``), in either order
+    (text first or boxes first).  Boxes come back in pixels as [x1, y1, x2, y2] (quadrilaterals as their bounds)."""
+    out: List[dict] = []
+    pos, label = 0, ""
+    for m in re.finditer(r"((?:<loc_\d+>)+)", text):
+        before = text[pos:m.start()].replace("<s>", "").replace("</s>", "").replace("<pad>", "").strip()
+        if before:
+            label = before
+        nums = [int(v) for v in _LOC.findall(m.group(1))]
+        step = 8 if quads else 4
+        for i in range(0, len(nums) - step + 1, step):
+            xs = [nums[j] for j in range(i, i + step, 2)]
+            ys = [nums[j] for j in range(i + 1, i + step, 2)]
+            box = [min(xs), min(ys), max(xs), max(ys)]
+            out.append({"text": label, "bbox": [round((box[0] + 0.5) / 1000 * width, 1),
+                                                round((box[1] + 0.5) / 1000 * height, 1),
+                                                round((box[2] + 0.5) / 1000 * width, 1),
+                                                round((box[3] + 0.5) / 1000 * height, 1)]})
+        pos = m.end()
+    trailing = text[pos:].replace("<s>", "").replace("</s>", "").strip()
+    if trailing and out and not out[-1]["text"]:      # boxes-first order: the text follows its box
+        out[-1]["text"] = trailing
+    return out
 
 
 class Reader:
@@ -79,6 +112,11 @@ class FlorenceReader:
             t1 = time.perf_counter()
             toks = self.model.generate(ids, px, max_new_tokens, self.no_repeat_ngram_size)
             t2 = time.perf_counter()
-            text = self.tokenizer.decode(toks).replace("<s>", "").replace("</s>", "").strip()
-            out.append(ReadResult(text, toks, {"preprocess": (t1 - t0) * 1e3, "decode": (t2 - t1) * 1e3}))
+            raw = self.tokenizer.decode(toks)
+            regions = parse_location_text(raw, int(img.shape[1]), int(img.shape[0]),
+                                          quads=(prompt or "<OCR>") == "<OCR_WITH_REGION>") if "<loc_" in raw else []
+            text = _LOC.sub(" ", raw).replace("<s>", "").replace("</s>", "").strip() if regions else \
+                raw.replace("<s>", "").replace("</s>", "").strip()
+            out.append(ReadResult(" ".join(text.split()) if regions else text, toks,
+                                  {"preprocess": (t1 - t0) * 1e3, "decode": (t2 - t1) * 1e3}, regions))
         return out

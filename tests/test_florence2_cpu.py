@@ -169,3 +169,16 @@ def test_florence2_reader_through_the_http_endpoint(tmp_path):
     # a different task prompt changes the encoder input (and, for this random model, usually the output)
     r2 = client.post("/ai/v1/read", json={"model": "tiny-florence", "images": [url], "max_tokens": 6})
     assert r2.status_code == 200
+
+
+def test_location_tokens_become_pixel_regions():
+    from antfly_b200.pipelines.reading import parse_location_text
+
+    od = "car<loc_100><loc_200><loc_500><loc_600>person<loc_0><loc_0><loc_999><loc_999><loc_10><loc_20><loc_30><loc_40>"
+    r = parse_location_text(od, 1000, 500)
+    assert [x["text"] for x in r] == ["car", "person", "person"]
+    assert r[0]["bbox"] == [100.5, 100.2, 500.5, 300.2] and r[1]["bbox"] == [0.5, 0.2, 999.5, 499.8]
+    ocr = "</s><s>Hello<loc_10><loc_20><loc_110><loc_20><loc_110><loc_60><loc_10><loc_60>"
+    q = parse_location_text(ocr, 1000, 1000, quads=True)
+    assert len(q) == 1 and q[0]["text"] == "Hello" and q[0]["bbox"] == [10.5, 20.5, 110.5, 60.5]
+    assert parse_location_text("no boxes here", 10, 10) == []
