@@ -892,17 +892,58 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 return content
             return "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type") == "text")
 
+        def images_of(content):
+            if isinstance(content, str):
+                return []
+            out = []
+            for p in content:
+                if isinstance(p, dict) and p.get("type") in ("image_url", "image"):
+                    url = p.get("image_url") or p.get("url") or p.get("image")
+                    out.append(url.get("url") if isinstance(url, dict) else url)
+            return out
+
         def work():
             schema, opts = req.schema_, req.options
             thr = float(opts.get("threshold", 0.0) or 0.0)
             texts = [text_of(i.content) for i in req.inputs]
+            pictures = [images_of(i.content) for i in req.inputs]
+            if any(pictures):
+                # image inputs: a reader turns every image into text first, extraction then runs on that text
+                # (zig/pkg/inference/src/server/server.zig extractImages: read document text -> run extraction)
+                from ..pipelines.multimodal import decode_data_url
+
+                ropt = opts.get("reader") or {}
+                rname = ropt.get("model") if isinstance(ropt, dict) else None
+                if not rname:
+                    raise ValueError("inputs with images need options.reader.model (a reader model name)")
+                reader = mgr.get(str(rname), "reader").pipeline
+                for k, urls in enumerate(pictures):
+                    if not urls:
+                        continue
+                    imgs = [decode_data_url(u) for u in urls]
+                    read = reader.read(imgs, int(opts.get("max_tokens", 256) or 256), prompt=ropt.get("prompt"))
+                    texts[k] = "\n".join([t for t in [texts[k]] + [r.text for r in read] if t])
             want_ents = [str(x) for x in schema.get("entities") or []]
             tasks = schema.get("classifications") or []
             rel_schema = schema.get("relations") or []
-            if not want_ents and not tasks and not rel_schema:
-                raise ValueError("schema needs entities, relations and / or classifications")
+            structures = schema.get("structures") or {}
+            if not want_ents and not tasks and not rel_schema and not structures:
+                raise ValueError("schema needs entities, relations, classifications and / or structures")
             data = [{"id": i.id} if i.id is not None else {} for i in req.inputs]
             ntok = 0
+            if structures:
+                from ..pipelines import extraction as EX
+
+                span_model = mgr.get(req.model, "recognizer").pipeline
+                if not hasattr(span_model, "recognize") or not hasattr(span_model, "classify"):
+                    raise ValueError("structures need a zero-shot span model (a GLiNER-style recognizer)")
+                cfg = EX.ExtractionConfig(
+                    threshold=float(opts["threshold"]) if opts.get("threshold") is not None else 0.3,
+                    flat_ner=bool(opts.get("flat_ner", True)), include_confidence=bool(opts.get("include_confidence", False)),
+                    include_spans=bool(opts.get("include_spans", False)), cluster_gap=int(opts.get("cluster_gap", 0) or 0))
+                canon = EX.canonical_structures(structures)
+                for rec, text in zip(data, texts):
+                    rec["structures"] = EX.extract_structures(span_model, text, canon, cfg)
             zero_shot = None
             if want_ents or tasks or rel_schema:
                 try:
