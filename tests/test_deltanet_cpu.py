@@ -58,3 +58,27 @@ def test_recurrence_matches_the_library_restatement():
     got, gs = gated_delta_rule(q, k, v, g, beta, s0)
     torch.testing.assert_close(got, want[0], atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(gs, ws[0], atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("T,chunk", [(64, 64), (150, 64), (37, 16), (5, 8), (1, 4)])
+def test_chunked_delta_rule_equals_the_recurrence(T, chunk):
+    from antfly_b200.models.deltanet import gated_delta_rule, gated_delta_rule_chunked
+
+    g_ = torch.Generator().manual_seed(T)
+    H, Dk, Dv = 3, 16, 24
+    q, k = torch.randn(T, H, Dk, generator=g_), torch.randn(T, H, Dk, generator=g_)
+    v = torch.randn(T, H, Dv, generator=g_)
+    g = -torch.rand(T, H, generator=g_) * 1.5                       # log decays, some strong
+    beta = torch.rand(T, H, generator=g_)
+    s0 = torch.randn(H, Dk, Dv, generator=g_) * 0.5
+    for state in (None, s0):
+        want_o, want_s = gated_delta_rule(q, k, v, g, beta, state)
+        got_o, got_s = gated_delta_rule_chunked(q, k, v, g, beta, state, chunk=chunk)
+        torch.testing.assert_close(got_o, want_o, atol=2e-4, rtol=2e-4)
+        torch.testing.assert_close(got_s, want_s, atol=2e-4, rtol=2e-4)
+    # a long prompt in one chunked call, then recurrent decode steps, equals the recurrence throughout
+    o1, s1 = gated_delta_rule_chunked(q, k, v, g, beta, None, chunk=chunk)
+    o2, s2 = gated_delta_rule(q[-1:], k[-1:], v[-1:], g[-1:], beta[-1:], gated_delta_rule(q[:-1], k[:-1], v[:-1], g[:-1],
+                                                                                       beta[:-1])[1]) if T > 1 else (o1, s1)
+    torch.testing.assert_close(o1[-1:], o2, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(s1, s2, atol=2e-4, rtol=2e-4)

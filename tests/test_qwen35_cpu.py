@@ -58,3 +58,23 @@ def test_greedy_generation_matches_transformers():
             want.append(nxt)
             seq = torch.cat([seq, torch.tensor([[nxt]])], 1)
     assert model.generate(prompt, 8) == want
+
+
+def test_long_prompt_through_the_chunked_delta_rule_matches_transformers():
+    """Prompts of 32 tokens and more take the chunked (matrix-product) form of the delta rule in the recurrent
+    layers; a prompt split over two calls carries the state from the chunked form into the next call."""
+    from antfly_b200.models import deltanet
+    from antfly_b200.models.qwen35 import Qwen35Config, Qwen35Model
+
+    hf_cfg, hf = _hf()
+    model = Qwen35Model.from_state_dict(Qwen35Config.from_hf(hf_cfg.to_dict()), hf.state_dict(), device="cpu",
+                                        dtype=torch.float32)
+    ids = torch.randint(0, 160, (1, 150), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        want = hf(ids).logits[0]
+    assert 150 >= deltanet.CHUNKED_FROM
+    got, _ = model.forward(ids[0])
+    torch.testing.assert_close(got, want, atol=5e-4, rtol=3e-3)
+    a, st = model.forward(ids[0, :100])
+    b, st = model.forward(ids[0, 100:], st)
+    torch.testing.assert_close(torch.cat([a, b]), want, atol=5e-4, rtol=3e-3)
