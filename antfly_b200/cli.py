@@ -574,6 +574,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("dequant", help="GGUF blocks on stdin -> fp32 on stdout")
     p.add_argument("format", help="tensor type name (q4_k, iq2_xs, ...) or id"); p.add_argument("--input")
     p.add_argument("--output"); p.set_defaults(fn=cmd_dequant)
+    sub.add_parser("kv-distortion", help="score error of the quantised KV-cache key codecs")
     p = sub.add_parser("bench", help="forwards its arguments to bench.py")
     p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
     p = sub.add_parser("search")
@@ -588,6 +589,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     raw = list(sys.argv[1:] if argv is None else argv)
     if raw and raw[0] == "bench":              # everything after the command belongs to bench.py, options included
         return cmd_bench(argparse.Namespace(rest=raw[1:]))
+    if raw and raw[0] == "kv-distortion":      # score error of the KV-cache key codecs (utils/kv_distortion.py)
+        from .utils import kv_distortion
+        kv_distortion.main(raw[1:])
+        return 0
     args = ap.parse_args(argv)
     return args.fn(args)
 
