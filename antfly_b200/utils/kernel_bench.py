@@ -5,6 +5,8 @@ host launch cost is excluded, rotating through several weight copies so every la
     python -m antfly_b200.utils.kernel_bench w8a16 --m 64 --n 4096 --k 4096 --split 4
     python -m antfly_b200.utils.kernel_bench gemm  --m 8192 --n 8192 --k 8192
     python -m antfly_b200.utils.kernel_bench attn  --batch 64 --ctx 2048
+    python -m antfly_b200.utils.kernel_bench gguf  --type q4_k --m 1 --n 14336 --k 4096   (the reference's Q4_K shapes)
+    python -m antfly_b200.utils.kernel_bench sinkattn --batch 64 --ctx 2048
     ... --plain N : no graph, N eager launches (the form to put under ncu)
 """
 from __future__ import annotations
@@ -36,7 +38,8 @@ def _graph_time(fns, reps: int = 10) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["w8a16", "mxfp8", "gemm", "pgemm", "attn", "norm", "encattn"])
+    ap.add_argument("kernel", choices=["w8a16", "mxfp8", "gemm", "pgemm", "attn", "sinkattn", "norm", "encattn", "gguf"])
+    ap.add_argument("--type", default="q4_k", help="gguf: tensor type of the weight (q4_0, q8_0, q4_k, q6_k, ...)")
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -109,6 +112,37 @@ def main() -> None:
         fns = [(lambda i=i: A.paged_attention(q, kcs[i], vcs[i], tables, ar, ones, kvl, 1, num_splits=args.splits,
                                                scratch=scratch)) for i in range(copies)]
         nbytes, flops = 2 * B * ctx * Hkv * D * 2, 4.0 * B * Hq * ctx * D
+    elif args.kernel == "sinkattn":
+        B, ctx, Hq, Hkv, D, page = args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, 16
+        nblk = (ctx + page - 1) // page
+        copies = args.copies or 4
+        kcs = [torch.randn(B * nblk, page, Hkv, D, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        vcs = [torch.randn(B * nblk, page, Hkv, D, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        tables = torch.arange(B * nblk, dtype=torch.int32, device=dev).view(B, nblk)
+        q = torch.randn(B, Hq, D, device=dev).to(torch.bfloat16)
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        ones = torch.ones_like(ar)
+        kvl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        sinks = torch.zeros(Hq, device=dev)
+        out = torch.empty_like(q)
+        fns = [(lambda i=i: A.paged_attention_sink(q, kcs[i], vcs[i], tables, ar, ones, kvl, sinks=sinks, out=out))
+               for i in range(copies)]
+        nbytes, flops = 2 * B * ctx * Hkv * D * 2, 4.0 * B * Hq * ctx * D
+    elif args.kernel == "gguf":
+        from ..formats import gguf as GF
+        from ..ops import gguf_ops as GO
+
+        M, Nn, K = args.m, args.n, args.k
+        ids = {v.lower(): k for k, v in GF.TYPE_NAMES.items()}
+        tid = int(args.type) if args.type.isdigit() else ids[args.type.lower()]
+        bv, bb = GO.block_geometry(tid)
+        wbytes = Nn * (K // bv) * bb
+        copies = args.copies or max(2, min(16, (300 << 20) // wbytes + 1))
+        # timing only: zero bytes decode to finite values in every format, so the outputs stay finite
+        ws = [torch.zeros(wbytes, dtype=torch.uint8, device=dev) for _ in range(copies)]
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        fns = [(lambda w=w: GO.linear_gguf(x, w, tid, Nn, K)) for w in ws]
+        nbytes, flops = wbytes + 2 * M * (K + Nn), 2.0 * M * Nn * K
     elif args.kernel == "encattn":
         B, L, Hq, D = args.batch, args.ctx, args.heads, args.head_dim
         T = B * L
