@@ -573,6 +573,13 @@ class ModelManager:
                         nm = os.path.relpath(dirpath, root)
                         out[t].setdefault(nm, {"name": nm, "loaded": False})
                         dirs[:] = []
+            # pulled models live under <owner>/<name>; their manifest says what they are
+            from .. import registry
+
+            for e in registry.discover(self.models_dir):
+                group = e.kind + "s"
+                if group in out and not any(e.name in names for names in out.values()):
+                    out[group].setdefault(e.name, {"name": e.name, "loaded": False, "variant": e.variant})
         out["chunkers"].setdefault("fixed", {"name": "fixed", "loaded": True})
         return out
 

@@ -468,6 +468,28 @@ def cmd_list(args) -> int:
     return 0
 
 
+def cmd_pull(args) -> int:
+    """Fetch a model (``[hf:]owner/name[:variant]``) into the models directory from a hub or a mirror directory
+    (the reference's ``pull``, zig/pkg/inference/src/registry/registry.zig:225-251)."""
+    from . import registry as R
+
+    last = {"name": None}
+
+    def progress(name, done, total):
+        if last["name"] != name:
+            last["name"] = name
+            print(f"  {name}" + (f" ({total} bytes)" if total else ""), file=sys.stderr)
+
+    try:
+        for ref in args.refs:
+            dest = R.pull(ref, args.models_dir, R.Hub(args.hub, args.token), args.tasks, args.capabilities, progress)
+            print(dest)
+    except R.RegistryError as e:
+        print(f"pull failed: {e}", file=sys.stderr)
+        return 1
+    return 0
+
+
 def cmd_smoke(args) -> int:
     import importlib.util
     import os
@@ -585,6 +607,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
     p.set_defaults(fn=cmd_quantize)
     p = sub.add_parser("list"); common(p); p.set_defaults(fn=cmd_list)
+    p = sub.add_parser("pull", help="fetch models into the models directory")
+    p.add_argument("refs", nargs="+", help="[hf:]owner/name[:variant] (auto, gguf, gguf:Q4_K_M, safetensors, mmproj)")
+    p.add_argument("--models-dir"); p.add_argument("--token")
+    p.add_argument("--hub", help="hub URL, or a mirror directory laid out owner/name ($HF_ENDPOINT by default)")
+    p.add_argument("--tasks", help="comma-separated tasks for the manifest (embed, rerank, generate, ...)")
+    p.add_argument("--capabilities", help="comma-separated capabilities for the manifest")
+    p.set_defaults(fn=cmd_pull)
     p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)
     raw = list(sys.argv[1:] if argv is None else argv)
     if raw and raw[0] == "bench":              # everything after the command belongs to bench.py, options included

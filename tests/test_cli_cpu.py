@@ -173,3 +173,22 @@ def test_cli_dequant_and_cuda_info(capsys, tmp_path):
         assert rc == 0 and "device_name:" in text and "compute_capability: sm_" in text
     else:
         assert rc == 1 and text.startswith("cuda: unavailable")
+
+
+def test_cli_pull_from_a_mirror_directory(capsys, tmp_path):
+    import os
+
+    repo = tmp_path / "mirror" / "acme" / "enc"
+    repo.mkdir(parents=True)
+    (repo / "config.json").write_text(json.dumps({"architectures": ["BertModel"], "model_type": "bert"}))
+    (repo / "model.safetensors").write_bytes(b"\0" * 16)
+    (repo / "model.onnx").write_bytes(b"\0" * 16)
+    models = tmp_path / "models"
+    assert main(["pull", "hf:acme/enc", "--hub", str(tmp_path / "mirror"), "--models-dir", str(models)]) == 0
+    cap = capsys.readouterr()
+    dest = cap.out.strip().splitlines()[-1]
+    assert dest.endswith("acme/enc") and "model.safetensors" in cap.err
+    assert sorted(os.listdir(dest)) == ["config.json", "model.safetensors", "model_manifest.json"]
+    assert json.load(open(os.path.join(dest, "model_manifest.json")))["tasks"] == ["embed"]
+    assert main(["pull", "acme/gone", "--hub", str(tmp_path / "mirror"), "--models-dir", str(models)]) == 1
+    assert "pull failed" in capsys.readouterr().err
