@@ -386,8 +386,9 @@ class GptModel:
             if cfg.alibi:
                 if self._alibi is None:
                     self._alibi = R.alibi_slopes(Hq).to(q.device)
-                ctx = R.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
-                                        scale, window, alibi=self._alibi).to(q.dtype)
+                # the position bias changes the scores, so the kernel that carries per-score terms serves it
+                ctx = A.paged_attention_sink(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens,
+                                             b.kv_lens, scale=scale, window=window, alibi=self._alibi).to(q.dtype)
             else:
                 ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                         b.max_q_len, max_kv=b.max_kv, scale=scale, window=window, num_splits=b.attn_splits,
@@ -409,9 +410,9 @@ class GptModel:
 
     @property
     def graph_safe(self) -> bool:
-        """False when a step reads sizes back to the host (the tensor-op attention of the ALiBi family), which a
-        CUDA graph cannot capture."""
-        return not self.cfg.alibi
+        """Every step is a fixed launch sequence with no read-back to the host (the ALiBi family included: its
+        position bias is applied inside the attention kernel), so decode buckets can be captured as CUDA graphs."""
+        return True
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
         return S.argmax(logits)

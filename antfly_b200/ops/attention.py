@@ -123,16 +123,17 @@ class PagedAttnScratch:
 
 def paged_attention_sink(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale: Optional[float] = None,
                          window: int = 0, sinks: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal paged attention whose softmax has a per-head sink logit (``sinks`` fp32 [Hq]) and / or a soft cap on
-    the scaled scores: the variants that change the normalisation, served by a kernel of their own
+                         out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal paged attention whose softmax has a per-head sink logit (``sinks`` fp32 [Hq]), a soft cap on the scaled
+    scores and / or a linear position bias (``alibi`` fp32 [Hq] slopes times key position minus query position): the
+    variants that change the scores or the normalisation, served by a kernel of their own
     (csrc/kernels/attention_sink.cu; one warp per (token, head)).  Same tensors as :func:`paged_attention`, bf16
     caches only."""
     T, Hq, D = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not q.is_cuda:
         return R.paged_attention(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv_lens, scale, window,
-                                 sinks=sinks, softcap=softcap).to(torch.bfloat16)
+                                 sinks=sinks, softcap=softcap, alibi=alibi).to(torch.bfloat16)
     if k_cache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16:
         raise NotImplementedError("attention with sinks / soft cap reads bf16 queries and a bf16 KV cache")
     assert q.stride(2) == 1 and q.stride(1) == D and k_cache.is_contiguous() and v_cache.is_contiguous()
@@ -145,10 +146,11 @@ def paged_attention_sink(q, k_cache, v_cache, block_tables, q_starts, q_lens, kv
     token_seq = (torch.searchsorted(q_starts.int(), torch.arange(T, dtype=torch.int32, device=q.device), right=True)
                  - 1).clamp_min(0).int()
     sk = sinks.float().contiguous() if sinks is not None else None
+    al = alibi.float().contiguous() if alibi is not None else None
     rc = N.cuda().afb_attention_sink(
         N.ptr(q), _c_long(q.stride(0)), N.ptr(k_cache), N.ptr(v_cache), N.ptr(block_tables),
         _c_int(block_tables.shape[1]), _c_int(page), _c_int(nblk), N.ptr(token_seq), N.ptr(q_starts), N.ptr(q_lens),
-        N.ptr(kv_lens), N.ptr(sk), N.ptr(out), _c_long(out.stride(0)), _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv),
+        N.ptr(kv_lens), N.ptr(sk), N.ptr(al), N.ptr(out), _c_long(out.stride(0)), _c_int(B), _c_int(T), _c_int(Hq), _c_int(Hkv),
         _c_int(D), _c_int(window), _c_float(scale), _c_float(softcap), N.stream_ptr())
     N.check(rc, "afb_attention_sink")
     N.count_launch()

@@ -2,8 +2,10 @@
 //   * a learned per-head *sink* logit that joins the softmax denominator without contributing a value
 //     (the reference's attention-with-sinks contract: zig/pkg/inference/src/graph/backend_contracts.zig:508-542,
 //      CPU implementation zig/pkg/inference/src/ops/native_compute.zig:35108-35160), and
-//   * a soft cap on the scaled scores, s <- cap * tanh(s / cap) (Gemma-2 style attention logit capping).
-// Both are one extra term per row, but they change the normalisation, so they cannot be applied after the fact to
+//   * a soft cap on the scaled scores, s <- cap * tanh(s / cap) (Gemma-2 style attention logit capping),
+//   * a linear position bias, s <- s + slope[head] * (key position - query position) (ALiBi, BLOOM's only position
+//     signal; the reference applies it in its decoder attention, zig/pkg/inference/src/architectures/gpt.zig:4894).
+// Each is one extra term per score, but they change the normalisation, so they cannot be applied after the fact to
 // the output of a kernel that does not also return its log-sum-exp.
 //
 // Organisation: one warp per (query token, query head).  Keys are visited in chunks of 128: in the score pass every
@@ -37,6 +39,7 @@ struct SinkAttnParams {
   const int* q_lens;     // [B]
   const int* kv_lens;    // [B]
   const float* sinks;    // [Hq] or null
+  const float* alibi;    // [Hq] slopes or null
   __nv_bfloat16* out;
   long out_stride;
   int max_blocks, page, num_blocks;
@@ -66,6 +69,7 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(const SinkAt
   int lo = 0;
   if (p.window > 0 && qpos + 1 > p.window) lo = qpos + 1 - p.window;
   const int hi = qpos + 1;  // keys [lo, hi)
+  const float slope = p.alibi ? p.alibi[head] : 0.0f;
   const __nv_bfloat16* qrow = p.q + static_cast<long>(tok) * p.q_stride + static_cast<long>(head) * D;
   for (int d = lane; d < D; d += 32) q_s[d] = __bfloat162float(qrow[d]);
   __syncwarp();
@@ -108,6 +112,7 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(const SinkAt
           }
           s = dot * p.scale;
           if (p.softcap > 0.0f) s = p.softcap * tanhf(s / p.softcap);
+          s += slope * static_cast<float>(key - qpos);
         }
       }
       sc[t] = s;
@@ -160,13 +165,14 @@ __global__ void __launch_bounds__(kSinkWarps * 32) sink_attn_kernel(const SinkAt
 
 extern "C" {
 
-// Paged causal attention with optional per-head sink logits (sinks: float [Hq] or null) and an optional soft cap on
-// the scaled scores (softcap <= 0: none).  q [T, Hq, D] bf16 (row stride q_stride), caches
+// Paged causal attention with optional per-head sink logits (sinks: float [Hq] or null), an optional soft cap on
+// the scaled scores (softcap <= 0: none) and optional per-head linear position slopes (alibi: float [Hq] or null).  q [T, Hq, D] bf16 (row stride q_stride), caches
 // [num_blocks, page, Hkv, D] bf16, token_seq [T] = the sequence of every query row, out [T, Hq, D] bf16.
 int afb_attention_sink(const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_tables,
                        int max_blocks, int page, int num_blocks, const int* token_seq, const int* q_starts,
-                       const int* q_lens, const int* kv_lens, const float* sinks, void* out, long out_stride, int B,
-                       int T, int Hq, int Hkv, int D, int window, float scale, float softcap, cudaStream_t stream) {
+                       const int* q_lens, const int* kv_lens, const float* sinks, const float* alibi, void* out,
+                       long out_stride, int B, int T, int Hq, int Hkv, int D, int window, float scale, float softcap,
+                       cudaStream_t stream) {
   using namespace afb;
   if (B <= 0 || T <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0 || D <= 0 || D > 256 || (D & 7)) {
@@ -186,7 +192,7 @@ int afb_attention_sink(const void* q, long q_stride, const void* k_cache, const 
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_stride = q_stride;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache); p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.block_tables = block_tables; p.token_seq = token_seq; p.q_starts = q_starts; p.q_lens = q_lens;
-  p.kv_lens = kv_lens; p.sinks = sinks; p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
+  p.kv_lens = kv_lens; p.sinks = sinks; p.alibi = alibi; p.out = static_cast<__nv_bfloat16*>(out); p.out_stride = out_stride;
   p.max_blocks = max_blocks; p.page = page; p.num_blocks = num_blocks;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.window = window; p.scale = scale; p.softcap = softcap;
   const long rows = static_cast<long>(T) * Hq;

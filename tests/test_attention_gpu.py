@@ -236,6 +236,44 @@ def test_sink_softcap_attention_kernel_matches_fp32_reference(Hq, Hkv, D, sinks,
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("Hq,Hkv,D,window", [(8, 8, 64, 0), (16, 16, 128, 0), (6, 2, 80, 29)])
+def test_alibi_position_bias_in_the_attention_kernel(Hq, Hkv, D, window):
+    """Per-head slopes times (key position - query position) are added to the scores inside afb_attention_sink; mixed
+    prefill / decode rows against the fp32 oracle."""
+    import torch
+
+    from antfly_b200 import _native as N
+    from antfly_b200.ops import attention as A
+    from antfly_b200.ops import reference as R
+
+    g = torch.Generator().manual_seed(Hq + D)
+    page, nblk = 16, 48
+    q_lens, kv_lens = [1, 33, 5, 130], [200, 33, 70, 130]
+    B, T = len(q_lens), sum(q_lens)
+    kc = (torch.randn(nblk, page, Hkv, D, generator=g) * 0.5).to(torch.bfloat16)
+    vc = torch.randn(nblk, page, Hkv, D, generator=g).to(torch.bfloat16)
+    perm = torch.randperm(nblk, generator=g)
+    bt = torch.zeros((B, 16), dtype=torch.int32)
+    off = 0
+    for b, n in enumerate(kv_lens):
+        nb = (n + page - 1) // page
+        bt[b, :nb] = perm[off: off + nb].int()
+        off += nb
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    ql = torch.tensor(q_lens, dtype=torch.int32)
+    qs = (torch.cumsum(ql, 0) - ql).int()
+    kl = torch.tensor(kv_lens, dtype=torch.int32)
+    slopes = R.alibi_slopes(Hq)
+    got = A.paged_attention_sink(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), qs.cuda(), ql.cuda(), kl.cuda(),
+                                 window=window, alibi=slopes.cuda())
+    assert N.status() == 0
+    want = R.paged_attention(q, kc, vc, bt, qs, ql, kl, D ** -0.5, window, alibi=slopes)
+    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    plain = R.paged_attention(q, kc, vc, bt, qs, ql, kl, D ** -0.5, window)
+    assert (want - plain).abs().max() > 1e-2                       # the bias does change the result
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("D", [80, 96])
 def test_paged_attention_with_head_widths_outside_the_tensor_core_set(D):
     """80- and 96-wide heads go through the general kernel at their own width (prefill rows and decode rows)."""
