@@ -116,7 +116,7 @@ class ClipModel:
         H, nh = tc.hidden_size, tc.num_attention_heads
         D = H // nh
         T = x.shape[0]
-        fused_act = tc.hidden_act if tc.hidden_act in ("gelu", "gelu_new", "gelu_tanh", "relu") else None
+        fused_act = tc.hidden_act if tc.hidden_act in Dn.ACT else None
         for l in range(tc.num_hidden_layers):
             p = f"{prefix}.l{l}."
             h = Dn.norm(x, w[p + "ln1.g"], w[p + "ln1.b"], eps=tc.layer_norm_eps)

@@ -820,17 +820,8 @@ class LlamaModel:
                 if l + 1 < hi:
                     h = Dn.norm(x, w[f"l{l + 1}.ln1"], eps=eps, rms=True, gamma_plus_one=gp1)
                 continue
-            gu = lin(h, p + "gu").float()  # columns alternate gate_i, up_i
-            gate, up = gu[:, 0::2], gu[:, 1::2]
-            if cfg.gate_act == "relu2":
-                gate = torch.relu(gate).square()
-            elif cfg.gate_act == "gelu_tanh":
-                gate = torch.nn.functional.gelu(gate, approximate="tanh")
-            elif cfg.gate_act == "gelu":
-                gate = torch.nn.functional.gelu(gate)
-            else:
-                gate = torch.nn.functional.silu(gate)
-            act = (gate * up).to(torch.bfloat16)
+            # columns alternate gate_i, up_i; activation and product in one elementwise kernel
+            act = Dn.gated_act(lin(h, p + "gu"), cfg.gate_act, interleaved=True).to(torch.bfloat16)
             if cfg.bitnet:
                 act = Dn.norm(act.contiguous(), w[p + "ffn_sub"], eps=eps, rms=True)
             if cfg.post_norms:

@@ -143,7 +143,7 @@ class ModernBertModel:
             h = Dn.norm(x, w[p + "ln2.g"], w.get(p + "ln2.b"), eps=cfg.norm_eps)
             ag = Dn.gemm_bf16(h, w[p + "wi.w"], bias=w.get(p + "wi.b"))
             I = ag.shape[1] // 2
-            m = (R.act_fn(ag[:, :I].float(), cfg.hidden_activation) * ag[:, I:].float()).to(ag.dtype)
+            m = Dn.gated_act(ag, cfg.hidden_activation)
             x = Dn.gemm_bf16(m, w[p + "wo.w"], bias=w.get(p + "wo.b"), residual=x)
         return Dn.norm(x, w["lnf.g"], w.get("lnf.b"), eps=cfg.norm_eps)
 

@@ -125,8 +125,11 @@ class Qwen2VLVisionModel:
                                      qkv[:, 2 * H:].view(T, nh, D), starts, lens, max(lens_l), causal=False).view(T, H)
             x = Dn.gemm_bf16(ctx.to(dt), w[p + "o.w"], bias=w[p + "o.b"], residual=x)
             h = Dn.norm(x, w[p + "norm2.g"], w[p + "norm2.b"], eps=1e-6)
-            m = Dn.gemm_bf16(h, w[p + "fc1.w"], bias=w[p + "fc1.b"])
-            x = Dn.gemm_bf16(_act(m, c.hidden_act), w[p + "fc2.w"], bias=w[p + "fc2.b"], residual=x)
+            if c.hidden_act in Dn.ACT:                       # the activation rides in the GEMM's epilogue
+                m = Dn.gemm_bf16(h, w[p + "fc1.w"], bias=w[p + "fc1.b"], act=c.hidden_act)
+            else:
+                m = _act(Dn.gemm_bf16(h, w[p + "fc1.w"], bias=w[p + "fc1.b"]), c.hidden_act)
+            x = Dn.gemm_bf16(m, w[p + "fc2.w"], bias=w[p + "fc2.b"], residual=x)
         k = c.spatial_merge_size ** 2
         x = Dn.norm(x, w["merge.ln.g"], w["merge.ln.b"], eps=1e-6).view(T // k, k * H)
         m = Dn.gemm_bf16(x.contiguous(), w["merge.fc1.w"], bias=w["merge.fc1.b"], act="gelu")

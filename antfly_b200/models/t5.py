@@ -153,7 +153,7 @@ class T5Model:
         if cfg.gated:
             ag = Dn.gemm_bf16(x, w[p + "wi"])
             F = ag.shape[1] // 2
-            h = (R.act_fn(ag[:, :F].float(), cfg.act) * ag[:, F:].float()).to(ag.dtype)
+            h = Dn.gated_act(ag, cfg.act)
         else:
             h = Dn.gemm_bf16(x, w[p + "wi"], act=cfg.act)
         return h

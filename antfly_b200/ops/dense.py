@@ -15,7 +15,11 @@ import torch
 from .. import _native as N
 from . import reference as R
 
-ACT = {None: 0, "none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "gelu_new": 2, "relu": 3, "silu": 4}
+ACT = {None: 0, "none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "gelu_new": 2, "relu": 3, "silu": 4,
+       "quick_gelu": 5}
+
+GATE_ACT = {"gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "gelu_new": 2, "gelu_pytorch_tanh": 2, "relu": 3, "silu": 4,
+            "swish": 4, "quick_gelu": 5, "relu2": 6}
 
 _c_int = ctypes.c_int
 _c_long = ctypes.c_long
@@ -25,6 +29,35 @@ _c_float = ctypes.c_float
 def _bf16(t: torch.Tensor) -> torch.Tensor:
     assert t.dtype == torch.bfloat16 and t.is_cuda, "expected a CUDA bf16 tensor"
     return t
+
+
+def gated_act(gu: torch.Tensor, act: str = "silu", interleaved: bool = False, limit: float = 0.0,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(gate) * up`` -> [T, F] (in the input's dtype) from the [T, 2F] output of a fused gate / up projection: halves
+    (gate = columns [0, F), up = [F, 2F)) or ``interleaved`` (gate_j, up_j adjacent).  One elementwise kernel
+    (csrc/kernels/gated_act.cu) instead of a chain of tensor ops; ``limit`` > 0 clamps gate from above and up to
+    [-limit, limit] first (clamped SwiGLU)."""
+    T, F2 = gu.shape
+    F = F2 // 2
+    if not gu.is_cuda or gu.dtype != torch.bfloat16:
+        y = R.gated_act(gu, act, interleaved, limit).to(gu.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    gu = _bf16(gu)
+    if gu.stride(1) != 1:
+        gu = gu.contiguous()
+    if out is None:
+        out = torch.empty((T, F), dtype=torch.bfloat16, device=gu.device)
+    assert out.stride(1) == 1 and out.shape == (T, F)
+    up = gu if interleaved else gu[:, F:]
+    rc = N.cuda().afb_gated_act(N.ptr(gu), N.ptr(up), N.ptr(out), _c_long(gu.stride(0)), _c_long(out.stride(0)),
+                                _c_long(T), _c_int(F), _c_int(GATE_ACT[act]), _c_int(1 if interleaved else 0),
+                                _c_float(limit), N.stream_ptr())
+    N.check(rc, "afb_gated_act")
+    N.count_launch()
+    return out
 
 
 def gemm_bf16(

@@ -24,6 +24,10 @@ def act_fn(x: torch.Tensor, act: Optional[str]) -> torch.Tensor:
         return F.relu(x)
     if act == "silu":
         return F.silu(x)
+    if act == "quick_gelu":
+        return x * torch.sigmoid(1.702 * x)
+    if act == "relu2":
+        return F.relu(x).square()
     raise ValueError(f"unknown activation {act}")
 
 
@@ -267,6 +271,19 @@ def linear_w8(x, q, e8, bias=None, act=None, residual=None):
     """x @ dequant(q, e8).T with the weight rounded to bf16 after scaling (exact for power-of-two scales)."""
     w = dequantize_block_fp8(q, e8).to(torch.bfloat16)
     return linear(x, w, bias, act, residual)
+
+
+def gated_act(gu: torch.Tensor, act: str = "silu", interleaved: bool = False, limit: float = 0.0) -> torch.Tensor:
+    """act(gate) * up in fp32 from one GEMM output [T, 2F]: halves (gate | up) or interleaved (gate_j, up_j
+    adjacent).  ``limit`` > 0 clamps gate from above and up to [-limit, limit] first."""
+    y = gu.float()
+    if interleaved:
+        g, u = y[..., 0::2], y[..., 1::2]
+    else:
+        g, u = y[..., : y.shape[-1] // 2], y[..., y.shape[-1] // 2:]
+    if limit > 0:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return act_fn(g, act) * u
 
 
 def swiglu_interleaved(y: torch.Tensor) -> torch.Tensor:

@@ -426,6 +426,8 @@ __device__ __forceinline__ float gelu_erf(float x) {
 }
 __device__ __forceinline__ float gelu_tanh(float x) { return gelu_erf(x); }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// x * sigmoid(1.702 x): the activation of the original CLIP checkpoints and of Qwen2-VL's vision blocks.
+__device__ __forceinline__ float quick_gelu(float x) { return x / (1.0f + __expf(-1.702f * x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -26,7 +26,7 @@ struct GemmParams {
   const __nv_bfloat16* residual;
   int M, N, K;
   int ldc, ldr;
-  int act;      // 0 none, 1 gelu(erf), 2 gelu(tanh), 3 relu, 4 silu
+  int act;      // 0 none, 1 gelu(erf), 2 gelu(tanh), 3 relu, 4 silu, 5 quick-gelu
   int out_f32;  // 1: fp32 output
   int kb_per_split;
   float alpha;
@@ -38,6 +38,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     case 2: return gelu_tanh(v);
     case 3: return fmaxf(v, 0.0f);
     case 4: return silu(v);
+    case 5: return quick_gelu(v);
     default: return v;
   }
 }
@@ -164,6 +165,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             } else if (p.act == 4) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+            } else if (p.act == 5) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = quick_gelu(v[j]);
             }
             if (p.residual) {
               const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + nbase;

@@ -60,6 +60,7 @@ __device__ __forceinline__ float persist_act(float v, int act) {
     case 2: return gelu_tanh(v);
     case 3: return fmaxf(v, 0.0f);
     case 4: return silu(v);
+    case 5: return quick_gelu(v);
     default: return v;
   }
 }
@@ -226,6 +227,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           } else if (p.act == 4) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+          } else if (p.act == 5) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = quick_gelu(v[j]);
           }
           if (p.residual) {
             const __nv_bfloat16* rp = p.residual + static_cast<size_t>(row) * p.ldr + nbase;
