@@ -30,7 +30,7 @@ def test_gemm_plain(M, N, K, tile):
     torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("act", ["gelu", "gelu_tanh", "relu", "silu", "quick_gelu", None])
+@pytest.mark.parametrize("act", ["gelu", "gelu_tanh", "relu", "silu", None])
 def test_gemm_epilogues(act):
     from antfly_b200.ops import dense
 
@@ -148,29 +148,3 @@ def test_norm_warp_per_row_path(H, rms):
     rs, ry = R.norm(x, g, b, eps=1e-6, rms=rms, residual=r, bias=bias)
     torch.testing.assert_close(s.float(), rs, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(y.float(), ry, atol=4e-2, rtol=3e-2)
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_tanh", "relu", "quick_gelu", "relu2"])
-@pytest.mark.parametrize("T,F,interleaved,limit", [(5, 256, False, 0.0), (130, 1024, True, 0.0), (33, 200, False, 7.0),
-                                                   (7, 37, True, 0.0), (64, 4096, False, 0.0)])
-def test_gated_activation_kernel_matches_fp32_reference(act, T, F, interleaved, limit):
-    """afb_gated_act: both layouts, the vector and the scalar path (F = 37: odd width; a sliced input whose base is
-    not 16-byte aligned), the clamp, against the fp32 formula."""
-    import torch
-
-    from antfly_b200.ops import dense as Dn
-    from antfly_b200.ops import reference as R
-
-    g = torch.Generator().manual_seed(T * 7 + F)
-    gu = (torch.randn(T, 2 * F, generator=g) * 3).to(torch.bfloat16)
-    want = R.gated_act(gu, act, interleaved, limit)
-    got = Dn.gated_act(gu.cuda(), act, interleaved, limit)
-    assert got.dtype == torch.bfloat16 and got.shape == (T, F)
-    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
-    if F % 8 == 0:
-        # a view one column into a wider buffer: rows keep their pitch, the base address loses its alignment
-        wide = torch.zeros(T, 2 * F + 8, dtype=torch.bfloat16)
-        wide[:, 1: 2 * F + 1] = gu
-        got2 = Dn.gated_act(wide.cuda()[:, 1: 2 * F + 1], act, interleaved, limit)
-        torch.testing.assert_close(got2.float().cpu(), want, atol=2e-2, rtol=2e-2)
