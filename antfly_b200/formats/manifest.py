@@ -30,6 +30,11 @@ def resolve_model_path(name: str, models_dir: Optional[str] = None, task: Option
     for c in cands:
         if os.path.isdir(c):
             return c
+    # registry form: "[hf:]owner/name[:variant]" names the directory a pull wrote, models_dir/owner/name
+    bare = name[3:] if name.startswith("hf:") else name
+    bare = bare.split(":", 1)[0]
+    if bare != name and "/" in bare:
+        return resolve_model_path(bare, models_dir, task)
     return None
 
 

@@ -197,3 +197,13 @@ def test_pull_over_http_with_token_resume_and_checksum(tmp_path):
 def test_unreachable_hub_is_a_registry_error(tmp_path):
     with pytest.raises(R.RegistryError):
         R.pull("a/b", str(tmp_path), R.Hub("http://127.0.0.1:9", timeout=2.0))
+
+
+def test_registry_form_names_resolve_to_the_pulled_directory(tmp_path):
+    from antfly_b200.formats.manifest import resolve_model_path
+
+    (tmp_path / "acme" / "tiny").mkdir(parents=True)
+    want = str(tmp_path / "acme" / "tiny")
+    assert resolve_model_path("acme/tiny", str(tmp_path)) == want
+    assert resolve_model_path("hf:acme/tiny:gguf:Q4_K_M", str(tmp_path)) == want
+    assert resolve_model_path("acme/none:gguf", str(tmp_path)) is None
