@@ -138,6 +138,9 @@ class ModelManager:
 
             f = GG.GGUFFile(os.path.join(path, mf.weight_files[0]))
             cfg_d = {k: v for k, v in GG.llama_config_from_gguf(f.metadata).items() if v is not None}
+            if "rope_freqs.weight" in f.tensors and "rope_scaling" not in cfg_d:
+                cfg_d["rope_scaling"] = GG.rope_factors_config(f.tensor("rope_freqs.weight").float().flatten().tolist(),
+                                                               cfg_d.pop("rope_attention_factor", 1.0))
             if task == "generator" and self.gguf_native and cfg_d.get("model_type") in (
                     "llama", "mistral", "qwen2", "qwen3", "phi3"):
                 model = LlamaModel.from_gguf_native(LlamaConfig.from_hf(cfg_d), f, device=self.device)

@@ -197,7 +197,30 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
           f"{arch}.vocab_size": int(config["vocab_size"])}
     if tokens:
         md["tokenizer.ggml.tokens"] = list(tokens)
+    if config.get("max_position_embeddings"):
+        md[f"{arch}.context_length"] = int(config["max_position_embeddings"])
+    if config.get("head_dim"):
+        md[f"{arch}.attention.key_length"] = int(config["head_dim"])
     tensors, counts = {}, {}
+    # frequency-dependent rotary scaling travels the way converted Llama-3.1 files carry it: one divisor per rotary
+    # pair in rope_freqs.weight (plus the attention factor, when there is one)
+    rope = config.get("rope_parameters") or config.get("rope_scaling") or {}
+    kind = rope.get("rope_type", rope.get("type"))
+    if kind == "linear" and rope.get("factor"):
+        md[f"{arch}.rope.scaling.type"], md[f"{arch}.rope.scaling.factor"] = "linear", float(rope["factor"])
+    elif kind in ("llama3", "yarn", "longrope", "su", "factors"):
+        from ..models.rope_scaling import rope_frequencies
+
+        hd = int(config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"])
+        theta = float(config.get("rope_theta") or rope.get("rope_theta") or 10000.0)
+        full = dict(rope)
+        if "original_max_position_embeddings" not in full and config.get("original_max_position_embeddings"):
+            full["original_max_position_embeddings"] = config["original_max_position_embeddings"]
+        inv, att = rope_frequencies(full, theta, hd, int(config.get("max_position_embeddings") or 0))
+        base = [theta ** (-2.0 * j / hd) for j in range(hd // 2)]
+        tensors["rope_freqs.weight"] = (0, torch.tensor([b / f for b, f in zip(base, inv)], dtype=torch.float32))
+        if att != 1.0:
+            md[f"{arch}.rope.scaling.attn_factor"] = float(att)
     for name, t in sd.items():
         if not isinstance(t, torch.Tensor) or not t.is_floating_point():
             continue
@@ -219,12 +242,32 @@ def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
                                           **{"llama." + k[len(arch) + 1:]: v for k, v in md.items()
                                              if k.startswith(arch + ".")}}),
                 "model_type": "bitnet", "tie_word_embeddings": True}
-    return {"model_type": arch, "hidden_size": g("embedding_length"), "num_hidden_layers": g("block_count"),
-            "num_attention_heads": g("attention.head_count"),
-            "num_key_value_heads": g("attention.head_count_kv", g("attention.head_count")),
-            "intermediate_size": g("feed_forward_length"), "rope_theta": g("rope.freq_base", 10000.0),
-            "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
-            "vocab_size": g("vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or None)}
+    out = {"model_type": arch, "hidden_size": g("embedding_length"), "num_hidden_layers": g("block_count"),
+           "num_attention_heads": g("attention.head_count"),
+           "num_key_value_heads": g("attention.head_count_kv", g("attention.head_count")),
+           "intermediate_size": g("feed_forward_length"), "rope_theta": g("rope.freq_base", 10000.0),
+           "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
+           "vocab_size": g("vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or None),
+           "head_dim": g("attention.key_length"), "max_position_embeddings": g("context_length")}
+    # context extension declared in the metadata: linear position scaling or yarn (a per-pair divisor tensor,
+    # rope_freqs.weight, is attached by the loader that has the tensors at hand: see rope_factors_config)
+    if g("rope.scaling.attn_factor") and not g("rope.scaling.type"):
+        out["rope_attention_factor"] = float(g("rope.scaling.attn_factor"))     # goes with a rope_freqs.weight tensor
+    kind = g("rope.scaling.type")
+    if kind in ("linear", "yarn") and g("rope.scaling.factor"):
+        rope = {"rope_type": kind, "factor": float(g("rope.scaling.factor"))}
+        if g("rope.scaling.original_context_length"):
+            rope["original_max_position_embeddings"] = int(g("rope.scaling.original_context_length"))
+        if g("rope.scaling.attn_factor"):
+            rope["attention_factor"] = float(g("rope.scaling.attn_factor"))
+        out["rope_scaling"] = rope
+    return out
+
+
+def rope_factors_config(factors, attention_factor: float = 1.0) -> dict:
+    """The ``rope_freqs.weight`` tensor of a GGUF file (one divisor per rotary pair; how converted Llama-3.1 files carry
+    their frequency scaling) as a ``rope_scaling`` entry."""
+    return {"rope_type": "factors", "factors": [float(v) for v in factors], "attention_factor": float(attention_factor)}
 
 
 def pack_i2s(values: np.ndarray) -> bytes:

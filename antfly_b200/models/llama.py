@@ -41,6 +41,10 @@ class LlamaConfig:
     rope_dim: int = 0
     rope_half_split: bool = True
     rope_freq_scale: float = 1.0
+    # frequency-dependent context extension (llama3, yarn, longrope): a table of rope_dim / 2 frequencies and the
+    # factor that multiplies cos / sin; None: the closed-form frequencies
+    rope_inv_freq: Optional[List[float]] = None
+    rope_mscale: float = 1.0
     rms_norm_eps: float = 1e-5
     tie_word_embeddings: bool = False
     qkv_bias: bool = False        # Qwen2
@@ -84,8 +88,8 @@ class LlamaConfig:
         keys = {f for f in cls.__dataclass_fields__}
         cfg = cls(**{k: v for k, v in d.items() if k in keys and v is not None})
         # RoPE settings: top-level ``rope_theta`` (older config.json files) or the ``rope_parameters`` /
-        # ``rope_scaling`` dictionary (newer ones); linear position scaling and partial rotary factors are honoured,
-        # frequency-dependent schemes (llama3, yarn) fall back to the unscaled frequencies.
+        # ``rope_scaling`` dictionary (newer ones); linear position scaling is a scalar, the frequency-dependent
+        # schemes (llama3, yarn, longrope) become a frequency table once head_dim / rope_dim are settled below.
         rp = d.get("rope_parameters") or d.get("rope_scaling") or {}
         if d.get("rope_theta") is None and rp.get("rope_theta") is not None:
             cfg.rope_theta = float(rp["rope_theta"])
@@ -156,6 +160,14 @@ class LlamaConfig:
             cfg.embed_scale = float(cfg.hidden_size) ** 0.5
             cfg.gate_act = "gelu_tanh"
             cfg.tie_word_embeddings = d.get("tie_word_embeddings", True)
+        if not cfg.layer_rope and not cfg.mrope_sections:
+            from .rope_scaling import rope_frequencies
+
+            rope = dict(rp)
+            if "original_max_position_embeddings" not in rope and d.get("original_max_position_embeddings"):
+                rope["original_max_position_embeddings"] = d["original_max_position_embeddings"]   # Phi-3 long
+            cfg.rope_inv_freq, cfg.rope_mscale = rope_frequencies(
+                rope, cfg.rope_theta, cfg.rope_dim or cfg.head_dim, int(d.get("max_position_embeddings") or 0))
         return cfg
 
     @classmethod
@@ -260,6 +272,9 @@ class LlamaModel:
         self.ep = None            # set by set_expert_parallel(): (rank, size, process group)
         self.pp = None            # set by set_pipeline(): this model is one stage of a layer pipeline
         self.layer_lo = 0
+        # rotary frequency table of a context-extension scheme, on the model's device (None: closed form)
+        self.rope_table = torch.tensor(cfg.rope_inv_freq, dtype=torch.float32, device=self.device) \
+            if cfg.rope_inv_freq else None
 
     # --------------------------------------------------------------------------------------------------
     @classmethod
@@ -547,7 +562,8 @@ class LlamaModel:
             q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
-                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps,
+                                inv_freq=self.rope_table, rope_mscale=cfg.rope_mscale)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=self.act_terms)
@@ -584,7 +600,8 @@ class LlamaModel:
             q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
-                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps,
+                                inv_freq=self.rope_table, rope_mscale=cfg.rope_mscale)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=mxt)
@@ -789,7 +806,8 @@ class LlamaModel:
             q = A.rope_kv_write(qkv, rope_pos, b.slots, k_cache_l, v_cache_l, Hq, Hkv, D, theta,
                                 bias=qkv_bias, rope_dim=cfg.rope_dim, half_split=cfg.rope_half_split,
                                 freq_scale=fscale, q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"),
-                                norm_eps=eps, norm_plus_one=gp1)
+                                norm_eps=eps, norm_plus_one=gp1, inv_freq=self.rope_table,
+                                rope_mscale=cfg.rope_mscale)
             if cfg.attn_sinks or cfg.attn_logit_softcapping:
                 # a softmax with an extra term: the kernel that carries it (bf16 caches)
                 ctx = A.paged_attention_sink(q, k_cache_l, v_cache_l, b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
@@ -877,7 +895,8 @@ class LlamaModel:
             q = A.rope_kv_write(None, b.positions, b.slots, k_cache[l], v_cache[l], Hq, Hkv, D, cfg.rope_theta,
                                 partials=parts, bias=w.get(p + "qkv.b"), rope_dim=cfg.rope_dim,
                                 half_split=cfg.rope_half_split, freq_scale=cfg.rope_freq_scale,
-                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps)
+                                q_norm_w=w.get(p + "qn"), k_norm_w=w.get(p + "kn"), norm_eps=cfg.rms_norm_eps,
+                                inv_freq=self.rope_table, rope_mscale=cfg.rope_mscale)
             ctx = A.paged_attention(q, k_cache[l], v_cache[l], b.block_tables, b.q_starts, b.q_lens, b.kv_lens,
                                     b.max_q_len, max_kv=b.max_kv, window=cfg.sliding_window, num_splits=b.attn_splits,
                                     scratch=attn_scratch, mx_terms=mxt)

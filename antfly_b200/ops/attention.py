@@ -323,9 +323,11 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
                   theta: float, *, partials: Optional[torch.Tensor] = None, bias=None, rope_dim: Optional[int] = None,
                   half_split: bool = True, freq_scale: float = 1.0, q_norm_w=None, k_norm_w=None,
                   norm_eps: float = 1e-6, norm_plus_one: bool = False, q_out: Optional[torch.Tensor] = None,
-                  kv_scale: float = 1.0) -> torch.Tensor:
+                  kv_scale: float = 1.0, inv_freq: Optional[torch.Tensor] = None,
+                  rope_mscale: float = 1.0) -> torch.Tensor:
     """Takes fused QKV rows (bf16, or fp32 split-K partials), applies optional head RMS-norm and RoPE to Q and
-    K, writes K/V into the cache at ``slots`` and returns Q [T, Hq, D] bf16."""
+    K, writes K/V into the cache at ``slots`` and returns Q [T, Hq, D] bf16.  ``inv_freq`` (fp32 [rope_dim / 2] on
+    the tensors' device) replaces the closed-form frequencies and ``rope_mscale`` then scales cos / sin."""
     src = qkv if qkv is not None else partials[0]
     T = src.shape[0]
     rd = rope_dim or D
@@ -343,7 +345,8 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
             q_res = rope_kv_write(qkv, positions, torch.arange(T, dtype=torch.int32, device=src.device), ks, vs, Hq,
                                   Hkv, D, theta, partials=partials, bias=bias, rope_dim=rope_dim,
                                   half_split=half_split, freq_scale=freq_scale, q_norm_w=q_norm_w, k_norm_w=k_norm_w,
-                                  norm_eps=norm_eps, norm_plus_one=norm_plus_one, q_out=q_out)
+                                  norm_eps=norm_eps, norm_plus_one=norm_plus_one, q_out=q_out, inv_freq=inv_freq,
+                                  rope_mscale=rope_mscale)
             k_cache.write(slots, ks[0])
             v_cache.write(slots, vs[0])
             return q_res
@@ -357,8 +360,8 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
             qh = R.norm(qh, q_norm_w, eps=norm_eps, rms=True, gamma_plus_one=norm_plus_one, round_sum_bf16=False)[1]
         if k_norm_w is not None:
             kh = R.norm(kh, k_norm_w, eps=norm_eps, rms=True, gamma_plus_one=norm_plus_one, round_sum_bf16=False)[1]
-        qh = R.rope(qh, positions, theta, rd, half_split, freq_scale)
-        kh = R.rope(kh, positions, theta, rd, half_split, freq_scale)
+        qh = R.rope(qh, positions, theta, rd, half_split, freq_scale, inv_freq, rope_mscale)
+        kh = R.rope(kh, positions, theta, rd, half_split, freq_scale, inv_freq, rope_mscale)
         kc = k_cache.view(-1, Hkv, D)
         vc = v_cache.view(-1, Hkv, D)
         ok = slots >= 0
@@ -371,13 +374,17 @@ def rope_kv_write(qkv: Optional[torch.Tensor], positions, slots, k_cache, v_cach
     pstride = 0 if partials is None else partials.stride(0)
     kv_fp8 = 1 if k_cache.dtype in (torch.float8_e4m3fn, torch.uint8) else 0
     num_slots = k_cache.shape[0] * k_cache.shape[1]
-    rc = N.cuda().afb_rope_kv_write(
+    args = (
         N.ptr(qkv), N.ptr(partials), _c_int(nparts), _c_long(pstride), N.ptr(bias), N.ptr(positions), N.ptr(slots),
         N.ptr(q_norm_w), N.ptr(k_norm_w), N.ptr(q_out), N.ptr(k_cache), N.ptr(v_cache), _c_int(T), _c_int(Hq),
         _c_int(Hkv), _c_int(D), _c_int(rd), _c_int(1 if half_split else 0), _c_float(theta), _c_float(freq_scale),
         _c_float(norm_eps), _c_int(1 if norm_plus_one else 0), _c_int(kv_fp8), _c_float(kv_scale),
-        _c_long(num_slots), N.stream_ptr(),
-    )
+        _c_long(num_slots))
+    if inv_freq is None:
+        rc = N.cuda().afb_rope_kv_write(*args, N.stream_ptr())
+    else:
+        assert inv_freq.dtype == torch.float32 and inv_freq.is_cuda and inv_freq.numel() == rd // 2
+        rc = N.cuda().afb_rope_kv_write_x(*args, N.ptr(inv_freq), _c_float(rope_mscale), N.stream_ptr())
     N.check(rc, "afb_rope_kv_write")
     N.count_launch()
     return q_out

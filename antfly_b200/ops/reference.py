@@ -129,16 +129,22 @@ def splade_pool(logits, starts, lens):
 # Rotary embedding (zig/lib/linalg/src/attention.zig:65-86)
 # ----------------------------------------------------------------------------------------------------------
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: Optional[int] = None,
-         half_split: bool = True, freq_scale: float = 1.0) -> torch.Tensor:
+         half_split: bool = True, freq_scale: float = 1.0, inv_freq: Optional[torch.Tensor] = None,
+         mscale: float = 1.0) -> torch.Tensor:
     """x: [T, heads, D]; rotates the first rope_dim dims.  half_split pairs (j, j+rope_dim/2) (Llama);
-    otherwise consecutive pairs (2j, 2j+1)."""
+    otherwise consecutive pairs (2j, 2j+1).  ``inv_freq`` [rope_dim / 2] replaces the closed-form frequencies and
+    ``mscale`` then multiplies cos / sin (context-extension schemes)."""
     T, Hh, D = x.shape
     rd = rope_dim or D
     xf = x.float().clone()
-    j = torch.arange(rd // 2, device=x.device, dtype=torch.float32)
-    freq = theta ** (-2.0 * j / rd)
+    if inv_freq is not None:
+        freq = inv_freq.to(x.device).float()
+    else:
+        j = torch.arange(rd // 2, device=x.device, dtype=torch.float32)
+        freq = theta ** (-2.0 * j / rd)
+        mscale = 1.0
     ang = positions.float()[:, None] * freq_scale * freq[None, :]
-    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    c, s = ang.cos()[:, None, :] * mscale, ang.sin()[:, None, :] * mscale
     if half_split:
         a, b = xf[..., : rd // 2], xf[..., rd // 2: rd]
         xf[..., : rd // 2], xf[..., rd // 2: rd] = a * c - b * s, a * s + b * c

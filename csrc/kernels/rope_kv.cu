@@ -36,6 +36,10 @@ struct RopeKvParams {
   int kv_fp8;                 // 1: caches are e4m3 bytes scaled by kv_scale_inv
   float kv_scale_inv;
   long num_slots;
+  // Context-extension schemes (llama3, yarn, longrope): a table of rope_dim / 2 frequencies replaces the
+  // closed form, and cos / sin are multiplied by the scheme's attention factor.  Null: the closed form.
+  const float* inv_freq;
+  float rope_mscale;
 };
 
 __device__ __forceinline__ float load_val(const RopeKvParams& p, size_t t, int row_width, int col) {
@@ -116,9 +120,11 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
     for (int j = lane; j < half; j += 32, ++cnt) {
       float x = a[cnt], y = b[cnt];
       if (j < rh) {
-        const float freq = exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(rd) * p.log2_theta);
+        const float freq = p.inv_freq ? p.inv_freq[j]
+                                      : exp2f(-2.0f * static_cast<float>(j) / static_cast<float>(rd) * p.log2_theta);
         float sn, cs;
         sincosf(pos * p.freq_scale * freq, &sn, &cs);
+        if (p.inv_freq) { sn *= p.rope_mscale; cs *= p.rope_mscale; }
         const float rx = x * cs - y * sn, ry = x * sn + y * cs;
         x = rx; y = ry;
       }
@@ -170,11 +176,31 @@ __global__ void kv_copy_blocks_kernel(uint4* k_cache, uint4* v_cache, const int*
 
 extern "C" {
 
+// As afb_rope_kv_write, with the rotary frequencies taken from a table (inv_freq: rope_dim / 2 floats in device
+// memory) and cos / sin scaled by rope_mscale: the frequency-dependent context-extension schemes.
+int afb_rope_kv_write_x(const void* qkv, const float* partials, int num_partials, long partial_stride,
+                        const void* bias, const int* positions, const int* slots, const void* q_norm_w,
+                        const void* k_norm_w, void* q_out, void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D,
+                        int rope_dim, int half_split, float theta, float freq_scale, float norm_eps, int norm_plus_one,
+                        int kv_fp8, float kv_scale, long num_slots, const float* inv_freq, float rope_mscale,
+                        cudaStream_t stream);
+
 int afb_rope_kv_write(const void* qkv, const float* partials, int num_partials, long partial_stride,
                       const void* bias, const int* positions, const int* slots, const void* q_norm_w,
                       const void* k_norm_w, void* q_out, void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D,
                       int rope_dim, int half_split, float theta, float freq_scale, float norm_eps, int norm_plus_one,
                       int kv_fp8, float kv_scale, long num_slots, cudaStream_t stream) {
+  return afb_rope_kv_write_x(qkv, partials, num_partials, partial_stride, bias, positions, slots, q_norm_w, k_norm_w,
+                             q_out, k_cache, v_cache, T, Hq, Hkv, D, rope_dim, half_split, theta, freq_scale, norm_eps,
+                             norm_plus_one, kv_fp8, kv_scale, num_slots, nullptr, 1.0f, stream);
+}
+
+int afb_rope_kv_write_x(const void* qkv, const float* partials, int num_partials, long partial_stride,
+                        const void* bias, const int* positions, const int* slots, const void* q_norm_w,
+                        const void* k_norm_w, void* q_out, void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D,
+                        int rope_dim, int half_split, float theta, float freq_scale, float norm_eps, int norm_plus_one,
+                        int kv_fp8, float kv_scale, long num_slots, const float* inv_freq, float rope_mscale,
+                        cudaStream_t stream) {
   using namespace afb;
   if (T <= 0) return 0;
   if (D > 256 || (D & 1) || rope_dim > D || (rope_dim & 1)) {
@@ -193,6 +219,7 @@ int afb_rope_kv_write(const void* qkv, const float* partials, int num_partials, 
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rope_dim = rope_dim; p.half_split = half_split;
   p.log2_theta = log2f(theta); p.freq_scale = freq_scale; p.norm_eps = norm_eps; p.norm_plus_one = norm_plus_one;
   p.kv_fp8 = kv_fp8; p.kv_scale_inv = kv_scale > 0.0f ? 1.0f / kv_scale : 1.0f; p.num_slots = num_slots;
+  p.inv_freq = inv_freq; p.rope_mscale = rope_mscale;
   const int total_heads = Hq + 2 * Hkv;
   // Few tokens (decode): spread the heads of a token over several CTAs; many tokens: one CTA per token.
   int groups = T >= 1024 ? 1 : (total_heads + 7) / 8;

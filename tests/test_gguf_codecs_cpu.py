@@ -2,6 +2,7 @@
 finite scale fields are decoded by both and must agree exactly (same arithmetic in fp32), for every block format
 the C++ decoder knows; plus the NVFP4 golden vector from the reference's own unit test
 (zig/pkg/inference/src/gguf/quant_codec.zig:4327-4340)."""
+import math
 import ctypes
 
 import numpy as np
@@ -330,3 +331,44 @@ def test_llama_served_from_its_gguf_blocks_matches_the_dequantised_model(tmp_pat
     # (the re-packed model rounds the weights a second time, to fp8; a random model's near-ties may then flip and
     #  the continuations part ways, so only the first token is compared)
     assert len(out_a.token_ids) == 6 and out_a.token_ids[0] == out_b.token_ids[0], (out_a.token_ids, out_b.token_ids)
+
+
+def test_rotary_scaling_survives_a_gguf_round_trip(tmp_path):
+    """A llama3-scaled checkpoint exported to GGUF carries its per-pair divisors in rope_freqs.weight; loading the
+    file through the model manager restores the same frequency table (and linear / yarn metadata are read)."""
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.models.llama import LlamaConfig
+
+    torch.manual_seed(0)
+    rope = {"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0,
+            "high_freq_factor": 4.0, "original_max_position_embeddings": 32}
+    hf_cfg = transformers.LlamaConfig(vocab_size=600, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                                      tie_word_embeddings=False, rope_parameters=rope)
+    hf = transformers.LlamaForCausalLM(hf_cfg).eval().float()
+    want = LlamaConfig.from_hf(hf_cfg.to_dict())
+    assert want.rope_inv_freq is not None
+    d = tmp_path / "generators" / "scaled"
+    d.mkdir(parents=True)
+    GG.export_llama_gguf(str(d / "model.gguf"), hf.state_dict(), hf_cfg.to_dict(), quant="q8_0")
+    f = GG.GGUFFile(str(d / "model.gguf"))
+    assert "rope_freqs.weight" in f.tensors and f.tensor("rope_freqs.weight").numel() == 8
+    for native in (False, True):
+        lm = ModelManager(models_dir=str(tmp_path), device="cpu", gguf_native=native).get("scaled", "generator")
+        cfg = lm.pipeline.engine.model.cfg
+        assert cfg.max_position_embeddings == 256 and cfg.rope_mscale == 1.0
+        torch.testing.assert_close(torch.tensor(cfg.rope_inv_freq), torch.tensor(want.rope_inv_freq), rtol=1e-5, atol=0)
+    # scaling declared in the metadata alone
+    md = {"general.architecture": "llama", "llama.embedding_length": 64, "llama.block_count": 1,
+          "llama.attention.head_count": 4, "llama.feed_forward_length": 128, "llama.vocab_size": 600,
+          "llama.context_length": 4096, "llama.rope.scaling.type": "yarn", "llama.rope.scaling.factor": 4.0,
+          "llama.rope.scaling.original_context_length": 1024}
+    cfg = LlamaConfig.from_hf({k: v for k, v in GG.llama_config_from_gguf(md).items() if v is not None})
+    assert cfg.rope_inv_freq is not None and abs(cfg.rope_mscale - (0.1 * math.log(4.0) + 1.0)) < 1e-6
+    md["llama.rope.scaling.type"] = "linear"
+    cfg = LlamaConfig.from_hf({k: v for k, v in GG.llama_config_from_gguf(md).items() if v is not None})
+    assert cfg.rope_inv_freq is None and cfg.rope_freq_scale == 0.25

@@ -82,6 +82,24 @@ def _hf_decoder(kind: str):
                                           num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[],
                                           norm_topk_prob=True)
         m = transformers.Qwen3MoeForCausalLM(cfg)
+    elif kind == "llama31":
+        cfg = transformers.LlamaConfig(**common, rope_parameters={
+            "rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0, "low_freq_factor": 1.0,
+            "high_freq_factor": 4.0, "original_max_position_embeddings": 32})
+        m = transformers.LlamaForCausalLM(cfg)
+    elif kind == "llama_yarn":
+        cfg = transformers.LlamaConfig(**common, rope_parameters={
+            "rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 64,
+            "beta_fast": 8.0, "beta_slow": 1.0})
+        m = transformers.LlamaForCausalLM(cfg)
+    elif kind == "phi3_long":
+        g = torch.Generator().manual_seed(5)
+        cfg = transformers.Phi3Config(**{**common, "pad_token_id": 0, "original_max_position_embeddings": 64,
+                                         "rope_parameters": {
+                                             "rope_type": "longrope", "rope_theta": 10000.0,
+                                             "short_factor": (1.0 + torch.rand(16, generator=g)).tolist(),
+                                             "long_factor": (2.0 + torch.rand(16, generator=g)).tolist()}})
+        m = transformers.Phi3ForCausalLM(cfg)
     elif kind == "llama_tied":
         common["tie_word_embeddings"] = True
         cfg = transformers.LlamaConfig(**common)
@@ -92,7 +110,7 @@ def _hf_decoder(kind: str):
 
 
 @pytest.mark.parametrize("kind", ["llama", "qwen2", "qwen3", "mistral", "llama_tied", "gemma", "gemma2", "gemma3", "phi3",
-                                  "mixtral", "qwen2_moe", "qwen3_moe"])
+                                  "mixtral", "qwen2_moe", "qwen3_moe", "llama31", "llama_yarn", "phi3_long"])
 def test_decoder_matches_transformers(kind):
     torch.manual_seed(0)
     hf_cfg, hf = _hf_decoder(kind)
@@ -106,6 +124,9 @@ def test_decoder_matches_transformers(kind):
     cfg = LlamaConfig.from_hf(hf_cfg.to_dict())
     if kind == "llama_tied":
         assert cfg.tie_word_embeddings
+    if kind in ("llama31", "llama_yarn", "phi3_long"):                  # a frequency table replaces the closed form
+        assert cfg.rope_inv_freq is not None and len(cfg.rope_inv_freq) == cfg.rope_dim // 2
+        assert (cfg.rope_mscale > 1.0) == (kind != "llama31")
     sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
     if kind == "llama_tied":
         sd.pop("lm_head.weight", None)
@@ -134,6 +155,9 @@ def test_decoder_matches_transformers(kind):
     assert float(agree) >= 0.8, (kind, float(agree))
     scale = float(want.abs().max())
     assert float((got - want).abs().max()) < 0.08 * max(scale, 1.0), (kind, float((got - want).abs().max()), scale)
+    if kind in ("llama_yarn", "phi3_long"):
+        # with the closed-form frequencies instead of the table the error is three to four times this bound
+        assert float((got - want).abs().max()) < 0.012, float((got - want).abs().max())
 
 
 @pytest.mark.parametrize("head", [False, True])

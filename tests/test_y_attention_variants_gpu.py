@@ -143,3 +143,32 @@ def test_paged_attention_with_head_widths_outside_the_tensor_core_set(D):
     got = A.paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), qs.cuda(), ql.cuda(), kl.cuda(), 33)
     want = R.paged_attention(q, kc, vc, bt, qs, ql, kl, D ** -0.5, 0)
     torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("kind", ["llama3", "yarn"])
+def test_rope_kv_write_with_a_frequency_table(kind):
+    """Context-extension schemes: the kernel reads rope_dim / 2 frequencies from a table and scales cos / sin by the
+    scheme's attention factor; against the fp32 formula, and different from the closed-form rotation."""
+    from antfly_b200.models.rope_scaling import rope_frequencies
+    from antfly_b200.ops import attention as A
+
+    T, Hq, Hkv, D, page = 29, 8, 2, 128, 16
+    rope = {"llama3": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                       "original_max_position_embeddings": 8192},
+            "yarn": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 4096}}[kind]
+    inv, ms = rope_frequencies(rope, 500000.0, D, 131072)
+    table = torch.tensor(inv, dtype=torch.float32)
+    qkv = _rand(T, (Hq + 2 * Hkv) * D, seed=30)
+    pos = torch.randint(0, 100000, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(8 * page, device="cuda")[:T].int()
+    kc = torch.zeros(8, page, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q = A.rope_kv_write(qkv, pos, slots, kc, vc, Hq, Hkv, D, 500000.0, inv_freq=table.cuda(), rope_mscale=ms)
+    kc2, vc2 = torch.zeros_like(kc).cpu(), torch.zeros_like(vc).cpu()
+    qr = A.rope_kv_write(qkv.cpu(), pos.cpu(), slots.cpu(), kc2, vc2, Hq, Hkv, D, 500000.0, inv_freq=table,
+                         rope_mscale=ms)
+    torch.testing.assert_close(q.float().cpu(), qr.float(), atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(kc.float().cpu(), kc2.float(), atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(vc.float().cpu(), vc2.float(), atol=1e-2, rtol=1e-2)
+    plain = A.rope_kv_write(qkv, pos, slots, torch.zeros_like(kc), torch.zeros_like(vc), Hq, Hkv, D, 500000.0)
+    assert float((plain.float() - q.float()).abs().max()) > 0.5
