@@ -179,11 +179,49 @@ def gguf_name(hf: str) -> str:
     return hf
 
 
+# Architectures whose converted files store the Q / K projection rows re-ordered so that the rotary pairs of a head
+# are adjacent (row 2j and 2j + 1 of a head are rows j and j + D/2 of the Hugging Face layout): llama.cpp's converter
+# does this for its "llama" architecture (Llama and Mistral checkpoints) and rotates consecutive pairs at run time; the
+# reference follows the same convention (zig/pkg/inference/src/models/gpt.zig:1277-1281).  The attention scores are
+# the same either way -- a permutation applied to both q and k -- so such files are served as they are, with the
+# consecutive-pair rotation, and only a comparison against a Hugging Face model needs the rows put back.
+PAIRED_ROPE_ARCHS = ("llama", "mistral")
+
+
+def pair_rope_rows(w: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Hugging Face row order of a Q / K projection -> rotary pairs adjacent (the stored order of those files)."""
+    rows = w.shape[0]
+    return w.reshape(n_head, 2, rows // n_head // 2, *w.shape[1:]).transpose(1, 2).reshape(w.shape)
+
+
+def unpair_rope_rows(w: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Inverse of :func:`pair_rope_rows`."""
+    rows = w.shape[0]
+    return w.reshape(n_head, rows // n_head // 2, 2, *w.shape[1:]).transpose(1, 2).reshape(w.shape)
+
+
+def to_hf_row_order(sd: Dict[str, torch.Tensor], config: dict) -> Dict[str, torch.Tensor]:
+    """A state dict read from a file of one of :data:`PAIRED_ROPE_ARCHS` (Hugging Face tensor names) with the Q / K
+    rows back in the Hugging Face order, for loading into a transformers model."""
+    if config.get("model_type") not in PAIRED_ROPE_ARCHS:
+        return dict(sd)
+    nh, nkv = int(config["num_attention_heads"]), int(config.get("num_key_value_heads") or config["num_attention_heads"])
+    out = {}
+    for k, v in sd.items():
+        if k.endswith(("self_attn.q_proj.weight", "self_attn.q_proj.bias")):
+            v = unpair_rope_rows(v, nh)
+        elif k.endswith(("self_attn.k_proj.weight", "self_attn.k_proj.bias")):
+            v = unpair_rope_rows(v, nkv)
+        out[k] = v
+    return out
+
+
 def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quant: str = "q8_0",
                       tokens: Optional[List[str]] = None) -> Dict[str, int]:
     """Write a Llama-family Hugging Face state dict as a GGUF v3 file: 2-D projection weights in ``quant`` (f32,
     f16, q8_0, q4_0), norms and embeddings in f32 / f16; metadata keys are the ones :func:`llama_config_from_gguf`
-    reads back.  Returns {tensor type id: count}."""
+    reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  Returns
+    {tensor type id: count}."""
     ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8, "i2_s": 36}[quant.lower()]   # i2_s: BitNet ternary projections
     arch = config.get("model_type", "llama")
     md = {"general.architecture": arch, "general.name": str(config.get("_name_or_path", "model")),
@@ -221,9 +259,16 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
         tensors["rope_freqs.weight"] = (0, torch.tensor([b / f for b, f in zip(base, inv)], dtype=torch.float32))
         if att != 1.0:
             md[f"{arch}.rope.scaling.attn_factor"] = float(att)
+    nh = int(config["num_attention_heads"])
+    nkv = int(config.get("num_key_value_heads", nh))
     for name, t in sd.items():
         if not isinstance(t, torch.Tensor) or not t.is_floating_point():
             continue
+        if arch in PAIRED_ROPE_ARCHS:
+            if name.endswith(("self_attn.q_proj.weight", "self_attn.q_proj.bias")):
+                t = pair_rope_rows(t, nh)
+            elif name.endswith(("self_attn.k_proj.weight", "self_attn.k_proj.bias")):
+                t = pair_rope_rows(t, nkv)
         quantisable = t.dim() == 2 and t.shape[1] % 32 == 0 and "embed_tokens" not in name and "norm" not in name
         if ty == 36:      # ternary only where the model is ternary (the projections), whole 128-value blocks
             quantisable = quantisable and name.endswith("_proj.weight") and t.numel() % 128 == 0
@@ -241,7 +286,7 @@ def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
         return {**llama_config_from_gguf({**md, "general.architecture": "llama",
                                           **{"llama." + k[len(arch) + 1:]: v for k, v in md.items()
                                              if k.startswith(arch + ".")}}),
-                "model_type": "bitnet", "tie_word_embeddings": True}
+                "model_type": "bitnet", "tie_word_embeddings": True, "rope_half_split": True}
     out = {"model_type": arch, "hidden_size": g("embedding_length"), "num_hidden_layers": g("block_count"),
            "num_attention_heads": g("attention.head_count"),
            "num_key_value_heads": g("attention.head_count_kv", g("attention.head_count")),
@@ -249,6 +294,8 @@ def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
            "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-5),
            "vocab_size": g("vocab_size", len(md.get("tokenizer.ggml.tokens", [])) or None),
            "head_dim": g("attention.key_length"), "max_position_embeddings": g("context_length")}
+    if arch in PAIRED_ROPE_ARCHS:
+        out["rope_half_split"] = False          # Q / K rows are stored with their rotary pairs adjacent
     # context extension declared in the metadata: linear position scaling or yarn (a per-pair divisor tensor,
     # rope_freqs.weight, is attached by the loader that has the tensors at hand: see rope_factors_config)
     if g("rope.scaling.attn_factor") and not g("rope.scaling.type"):

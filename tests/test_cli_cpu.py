@@ -56,7 +56,8 @@ def test_cli_export_gguf_roundtrip_and_task_commands(capsys, tmp_path):
     cfg = GG.llama_config_from_gguf(f.metadata)
     assert cfg["num_hidden_layers"] == L and cfg["num_key_value_heads"] == 2 and cfg["rope_theta"] == 500000.0
     assert cfg["vocab_size"] == V
-    back = {GG.hf_name(n): f.tensor(n) for n in f.tensors}
+    assert cfg["rope_half_split"] is False                       # llama files store Q / K rows with rotary pairs adjacent
+    back = GG.to_hf_row_order({GG.hf_name(n): f.tensor(n) for n in f.tensors}, cfg)
     assert set(back) == set(sd)
     for n, t in sd.items():
         tol = 0.02 * float(t.abs().max()) if t.dim() == 2 else 0.0

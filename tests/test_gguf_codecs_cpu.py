@@ -306,7 +306,8 @@ def test_llama_served_from_its_gguf_blocks_matches_the_dequantised_model(tmp_pat
     assert len(native.w["l0.qkv"].segments) == 3 and native.w["l0.qkv"].out_features == 64 + 32 + 32
     bits = native.w["l1.down"].nbytes() * 8 / (64 * 128)
     assert abs(bits - (8.5 if quant == "q8_0" else 4.5)) < 1e-6
-    sd = {GG.hf_name(n): f.tensor(n) for n in f.tensors}
+    assert not cfg.rope_half_split                       # llama files keep the rotary pairs of Q / K rows adjacent
+    sd = GG.to_hf_row_order({GG.hf_name(n): f.tensor(n) for n in f.tensors}, hf_cfg.to_dict())
     with torch.no_grad():
         hf.load_state_dict({k: v.reshape(hf.state_dict()[k].shape) for k, v in sd.items()})
     ids = torch.randint(0, 600, (12,), generator=torch.Generator().manual_seed(1))
@@ -372,3 +373,30 @@ def test_rotary_scaling_survives_a_gguf_round_trip(tmp_path):
     md["llama.rope.scaling.type"] = "linear"
     cfg = LlamaConfig.from_hf({k: v for k, v in GG.llama_config_from_gguf(md).items() if v is not None})
     assert cfg.rope_inv_freq is None and cfg.rope_freq_scale == 0.25
+
+
+def test_rotary_row_pairing_of_llama_files():
+    """Row 2j / 2j + 1 of a head in the stored order are rows j / j + D/2 of the Hugging Face order; the inverse
+    restores it; architectures with half-split rotation at run time are left alone."""
+    import torch
+
+    from antfly_b200.formats import gguf as GG
+
+    H, D, K = 3, 8, 5
+    w = torch.arange(H * D * K, dtype=torch.float32).reshape(H * D, K)
+    p = GG.pair_rope_rows(w, H)
+    for h in range(H):
+        for j in range(D // 2):
+            assert torch.equal(p[h * D + 2 * j], w[h * D + j]) and torch.equal(p[h * D + 2 * j + 1], w[h * D + j + D // 2])
+    assert torch.equal(GG.unpair_rope_rows(p, H), w)
+    b = torch.arange(H * D, dtype=torch.float32)
+    assert torch.equal(GG.unpair_rope_rows(GG.pair_rope_rows(b, H), H), b)
+    md = lambda arch: {"general.architecture": arch, f"{arch}.attention.head_count": 4}
+    assert GG.llama_config_from_gguf(md("llama"))["rope_half_split"] is False
+    assert "rope_half_split" not in GG.llama_config_from_gguf(md("qwen2"))
+    sd = {"model.layers.0.self_attn.q_proj.weight": p, "model.layers.0.self_attn.v_proj.weight": w}
+    same = GG.to_hf_row_order(sd, {"model_type": "qwen3", "num_attention_heads": H})
+    assert torch.equal(same["model.layers.0.self_attn.q_proj.weight"], p)
+    back = GG.to_hf_row_order(sd, {"model_type": "llama", "num_attention_heads": H})
+    assert torch.equal(back["model.layers.0.self_attn.q_proj.weight"], w)
+    assert torch.equal(back["model.layers.0.self_attn.v_proj.weight"], w)
