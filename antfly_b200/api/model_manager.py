@@ -138,18 +138,23 @@ class ModelManager:
 
             f = GG.GGUFFile(os.path.join(path, mf.weight_files[0]))
             cfg_d = {k: v for k, v in GG.llama_config_from_gguf(f.metadata).items() if v is not None}
+            cfg_d.setdefault("tie_word_embeddings", "output.weight" not in f.tensors)   # no output matrix: tied
             if "rope_freqs.weight" in f.tensors and "rope_scaling" not in cfg_d:
                 cfg_d["rope_scaling"] = GG.rope_factors_config(f.tensor("rope_freqs.weight").float().flatten().tolist(),
                                                                cfg_d.pop("rope_attention_factor", 1.0))
             if task == "generator" and self.gguf_native and cfg_d.get("model_type") in (
-                    "llama", "mistral", "qwen2", "qwen3", "phi3"):
+                    "llama", "mistral", "qwen2", "qwen3"):
                 model = LlamaModel.from_gguf_native(LlamaConfig.from_hf(cfg_d), f, device=self.device)
                 eng = LLMEngine(model, num_blocks=self.kv_blocks, max_batch=self.max_batch,
                                 use_cuda_graph=self.device.type == "cuda", eos_token_id=tok.special.eos_id,
                                 prefix_cache=self.prefix_cache)
                 return LoadedModel(name, task, Generator(eng, tok, mf.chat_template), tok, path,
                                    info={"weights": "gguf-native", "capabilities": mf.capabilities})
-            sd = {GG.hf_name(n): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
+            arch = cfg_d.get("model_type")
+            sd = {GG.hf_name(n, arch): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
+            if arch == "gemma":
+                # converted Gemma files store 1 + gamma in their norm tensors; the model adds the 1 itself
+                sd = {k: (v - 1.0 if k.endswith("norm.weight") else v) for k, v in sd.items()}
         elif mf.weights == "safetensors":
             sd, cfg_d = ST.load_model_dir(path), mf.config
         else:

@@ -153,27 +153,33 @@ _GGUF_TO_HF = {
 _LAYER = {"attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj",
           "attn_output": "self_attn.o_proj", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj",
           "ffn_down": "mlp.down_proj", "attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm",
-          "attn_sub_norm": "self_attn.attn_sub_norm", "ffn_sub_norm": "mlp.ffn_sub_norm"}   # BitNet
+          "attn_sub_norm": "self_attn.attn_sub_norm", "ffn_sub_norm": "mlp.ffn_sub_norm",   # BitNet
+          "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",              # Qwen3, Gemma-3
+          "attn_qkv": "self_attn.qkv_proj"}                                                   # Phi-3 (fused)
+# per architecture: names that mean something else there
+_LAYER_ARCH = {"phi3": {"ffn_up": "mlp.gate_up_proj"}}                                        # gate and up stacked
 
 
-def hf_name(gguf_name: str) -> str:
+def hf_name(gguf_name: str, arch: Optional[str] = None) -> str:
     if gguf_name in _GGUF_TO_HF:
         return _GGUF_TO_HF[gguf_name]
     parts = gguf_name.split(".")
-    if parts[0] == "blk" and len(parts) >= 4 and parts[2] in _LAYER:
-        return f"model.layers.{parts[1]}.{_LAYER[parts[2]]}.{parts[3]}"
+    if parts[0] == "blk" and len(parts) >= 4:
+        mid = _LAYER_ARCH.get(arch or "", {}).get(parts[2]) or _LAYER.get(parts[2])
+        if mid:
+            return f"model.layers.{parts[1]}.{mid}.{parts[3]}"
     return gguf_name
 
 
-def gguf_name(hf: str) -> str:
+def gguf_name(hf: str, arch: Optional[str] = None) -> str:
     """Inverse of :func:`hf_name` for the Llama-family tensor names."""
     for g, h in _GGUF_TO_HF.items():
         if h == hf:
             return g
     parts = hf.split(".")
-    if len(parts) >= 6 and parts[0] == "model" and parts[1] == "layers":
+    if len(parts) >= 5 and parts[0] == "model" and parts[1] == "layers":
         mid = ".".join(parts[3:-1])
-        for g, h in _LAYER.items():
+        for g, h in list(_LAYER_ARCH.get(arch or "", {}).items()) + list(_LAYER.items()):
             if h == mid:
                 return f"blk.{parts[2]}.{g}.{parts[-1]}"
     return hf
@@ -269,11 +275,13 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
                 t = pair_rope_rows(t, nh)
             elif name.endswith(("self_attn.k_proj.weight", "self_attn.k_proj.bias")):
                 t = pair_rope_rows(t, nkv)
+        if arch == "gemma" and name.endswith("norm.weight"):
+            t = t.float() + 1.0      # converted Gemma files hold 1 + gamma (the loader takes the 1 off again)
         quantisable = t.dim() == 2 and t.shape[1] % 32 == 0 and "embed_tokens" not in name and "norm" not in name
         if ty == 36:      # ternary only where the model is ternary (the projections), whole 128-value blocks
             quantisable = quantisable and name.endswith("_proj.weight") and t.numel() % 128 == 0
         tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 else 0)
-        tensors[gguf_name(name)] = (tt, t.float())
+        tensors[gguf_name(name, arch)] = (tt, t.float())
         counts[tt] = counts.get(tt, 0) + 1
     write_gguf(path, md, tensors)
     return counts

@@ -501,6 +501,9 @@ class LlamaModel:
             if s_ + "self_attn.q_proj.bias" in names:
                 w[p + "qkv.b"] = torch.cat([f.tensor(names[s_ + f"self_attn.{n}_proj.bias"]) for n in "qkv"]).to(
                     torch.bfloat16).to(device)
+            if cfg.qk_norm:
+                w[p + "qn"] = f.tensor(names[s_ + "self_attn.q_norm.weight"]).to(torch.bfloat16).to(device)
+                w[p + "kn"] = f.tensor(names[s_ + "self_attn.k_norm.weight"]).to(torch.bfloat16).to(device)
             w[p + "o"] = weight([s_ + "self_attn.o_proj.weight"])
             w[p + "gu"] = weight([s_ + "mlp.gate_proj.weight", s_ + "mlp.up_proj.weight"], interleave=True)
             w[p + "down"] = weight([s_ + "mlp.down_proj.weight"])

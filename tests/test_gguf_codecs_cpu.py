@@ -400,3 +400,67 @@ def test_rotary_row_pairing_of_llama_files():
     back = GG.to_hf_row_order(sd, {"model_type": "llama", "num_attention_heads": H})
     assert torch.equal(back["model.layers.0.self_attn.q_proj.weight"], w)
     assert torch.equal(back["model.layers.0.self_attn.v_proj.weight"], w)
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "phi3", "gemma"])
+def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
+    """Per-head Q / K norms (attn_q_norm / attn_k_norm) and Phi-3's fused attn_qkv / stacked ffn_up survive export and
+    loading, Gemma's norm tensors travel as 1 + gamma; the model served from the file agrees with transformers."""
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.models.llama import StepBatch
+
+    torch.manual_seed(0)
+    common = dict(vocab_size=600, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=False)
+    if kind == "qwen3":
+        hf_cfg = transformers.Qwen3Config(**common, head_dim=32)
+        hf = transformers.Qwen3ForCausalLM(hf_cfg).eval().float()
+        with torch.no_grad():
+            for n, p in hf.named_parameters():
+                if n.endswith(("q_norm.weight", "k_norm.weight")):
+                    p.uniform_(0.5, 1.5)
+    elif kind == "gemma":
+        hf_cfg = transformers.GemmaConfig(**{**common, "head_dim": 16, "hidden_activation": "gelu_pytorch_tanh"})
+        hf = transformers.GemmaForCausalLM(hf_cfg).eval().float()
+        with torch.no_grad():
+            for n, p in hf.named_parameters():
+                if "norm" in n:
+                    p.uniform_(-0.3, 0.3)
+    else:
+        hf_cfg = transformers.Phi3Config(**common, pad_token_id=0)
+        hf = transformers.Phi3ForCausalLM(hf_cfg).eval().float()
+    d = tmp_path / "generators" / kind
+    d.mkdir(parents=True)
+    GG.export_llama_gguf(str(d / "model.gguf"), hf.state_dict(), hf_cfg.to_dict(), quant="q8_0")
+    f = GG.GGUFFile(str(d / "model.gguf"))
+    if kind == "qwen3":
+        assert "blk.0.attn_q_norm.weight" in f.tensors and "blk.1.attn_k_norm.weight" in f.tensors
+        assert f.metadata["qwen3.attention.key_length"] == 32
+    elif kind == "gemma":
+        stored = f.tensor("blk.0.attn_norm.weight")
+        torch.testing.assert_close(stored, hf.state_dict()["model.layers.0.input_layernorm.weight"] + 1.0,
+                                   atol=1e-6, rtol=0)
+    else:
+        assert "blk.0.attn_qkv.weight" in f.tensors and "blk.0.ffn_up.weight" in f.tensors
+        assert GG.hf_name("blk.0.ffn_up.weight", "phi3") == "model.layers.0.mlp.gate_up_proj.weight"
+        assert GG.hf_name("blk.0.ffn_up.weight", "llama") == "model.layers.0.mlp.up_proj.weight"
+    ids = torch.randint(0, 600, (12,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    pos = torch.arange(12, dtype=torch.int32)
+    for native in ((False, True) if kind == "qwen3" else (False,)):
+        lm = ModelManager(models_dir=str(tmp_path), device="cpu", gguf_native=native).get(kind, "generator")
+        model = lm.pipeline.engine.model
+        assert lm.info.get("weights") == ("gguf-native" if native else lm.info.get("weights"))
+        D = model.cfg.head_dim
+        kc = torch.zeros((2, 2, 16, 2, D), dtype=torch.bfloat16)
+        b = StepBatch(ids.int(), pos, pos.clone(), i32([0]), i32([12]), i32([12]),
+                      torch.arange(2, dtype=torch.int32)[None], pos.clone(), 12, 1)
+        got = model.forward(b, kc, torch.zeros_like(kc)).float()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        assert float(cos.min()) > 0.99, (kind, native, cos)
