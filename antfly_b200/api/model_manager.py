@@ -124,6 +124,8 @@ class ModelManager:
     def _load_dir(self, name: str, task: str, path: str) -> LoadedModel:
         mf = MF.read_manifest(path)
         tok = load_tokenizer(path, mf.config.get("vocab_size", 0))
+        if mf.chat_template is None:                 # a GGUF-only directory: the template travels in the file's metadata
+            mf.chat_template = getattr(tok, "chat_template", None)
         packed = os.path.join(path, COMPILED_ARTIFACT)
         if task == "generator" and os.path.exists(packed):
             # a compiled artifact holds the weights in the kernels' own layout: read and upload, nothing to pack

@@ -223,7 +223,8 @@ def to_hf_row_order(sd: Dict[str, torch.Tensor], config: dict) -> Dict[str, torc
 
 
 def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quant: str = "q8_0",
-                      tokens: Optional[List[str]] = None) -> Dict[str, int]:
+                      tokens: Optional[List[str]] = None, extra_metadata: Optional[Dict[str, Any]] = None
+                      ) -> Dict[str, int]:
     """Write a Llama-family Hugging Face state dict as a GGUF v3 file: 2-D projection weights in ``quant`` (f32,
     f16, q8_0, q4_0), norms and embeddings in f32 / f16; metadata keys are the ones :func:`llama_config_from_gguf`
     reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  Returns
@@ -241,6 +242,7 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
           f"{arch}.vocab_size": int(config["vocab_size"])}
     if tokens:
         md["tokenizer.ggml.tokens"] = list(tokens)
+    md.update(extra_metadata or {})              # tokenizer tables, chat template, ...
     if config.get("max_position_embeddings"):
         md[f"{arch}.context_length"] = int(config["max_position_embeddings"])
     if config.get("head_dim"):

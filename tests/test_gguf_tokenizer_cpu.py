@@ -80,3 +80,29 @@ def test_model_directory_with_only_a_gguf_file_uses_its_tokenizer(tmp_path):
     assert tok.encode("ab ab") == [toks.index("▁ab")] * 2
     assert tok.encode("é") == [toks.index("▁")] + [3 + b for b in "é".encode()]     # byte fallback
     assert tok.decode(tok.encode("ab é")) == "ab é"
+
+
+def test_gguf_only_generator_gets_tokenizer_and_chat_template_from_the_file(tmp_path):
+    import torch
+    import transformers
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.runtime.sampling_params import SamplingParams
+
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "a", "b", "▁a", "ab", "▁ab"]
+    template = "{% for m in messages %}<s>{{ m['role'] }}: {{ m['content'] }}</s>{% endfor %}assistant:"
+    md = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.scores": [0.0] * 259 + [-1.0, -2.0, -3.0, -0.5, -0.7, -0.1],
+          "tokenizer.ggml.token_type": [2, 3, 3] + [6] * 256 + [1] * 6, "tokenizer.ggml.bos_token_id": 1,
+          "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.unknown_token_id": 0, "tokenizer.chat_template": template}
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=len(toks), hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128)
+    hf = transformers.LlamaForCausalLM(cfg)
+    d = tmp_path / "generators" / "chatty"
+    d.mkdir(parents=True)
+    GG.export_llama_gguf(str(d / "model.gguf"), hf.state_dict(), cfg.to_dict(), tokens=toks, extra_metadata=md)
+    lm = ModelManager(models_dir=str(tmp_path), device="cpu").get("chatty", "generator")
+    assert lm.pipeline.template.source == template and lm.tokenizer.vocab_size == len(toks)
+    out = lm.pipeline.generate([{"role": "user", "content": "ab"}], SamplingParams(max_tokens=3, ignore_eos=True))
+    assert len(out.token_ids) == 3 and out.prompt_tokens > 4
