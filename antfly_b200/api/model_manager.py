@@ -154,6 +154,8 @@ class ModelManager:
                                    info={"weights": "gguf-native", "capabilities": mf.capabilities})
             arch = cfg_d.get("model_type")
             sd = {GG.hf_name(n, arch): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
+            if cfg_d.get("num_experts"):
+                sd = GG.fuse_expert_tensors(sd)
             if arch == "gemma":
                 # converted Gemma files store 1 + gamma in their norm tensors; the model adds the 1 itself
                 sd = {k: (v - 1.0 if k.endswith("norm.weight") else v) for k, v in sd.items()}

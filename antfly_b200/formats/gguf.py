@@ -222,6 +222,68 @@ def to_hf_row_order(sd: Dict[str, torch.Tensor], config: dict) -> Dict[str, torc
     return out
 
 
+_EXPERT_STACKS = {"ffn_gate_exps": "gate", "ffn_up_exps": "up", "ffn_down_exps": "down"}
+_SHARED_EXPERT = {"ffn_gate_shexp": "mlp.shared_expert.gate_proj", "ffn_up_shexp": "mlp.shared_expert.up_proj",
+                  "ffn_down_shexp": "mlp.shared_expert.down_proj", "ffn_gate_inp_shexp": "mlp.shared_expert_gate",
+                  "ffn_gate_inp": "mlp.gate"}
+
+
+def fuse_expert_tensors(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """The expert tensors of a mixture-of-experts file under the names the decoder loader reads:
+    ``blk.N.ffn_gate_exps`` [E, F, H] and ``ffn_up_exps`` become ``mlp.experts.gate_up_proj`` [E, 2F, H] (gate rows,
+    then up rows), ``ffn_down_exps`` [E, H, F] becomes ``mlp.experts.down_proj``, the router ``ffn_gate_inp`` becomes
+    ``mlp.gate``, a shared expert keeps its three projections and its gate."""
+    out, stacks = {}, {}
+    for name, t in sd.items():
+        parts = name.split(".")
+        if parts[0] == "blk" and len(parts) == 4 and parts[2] in _EXPERT_STACKS:
+            stacks.setdefault(parts[1], {})[_EXPERT_STACKS[parts[2]]] = t
+        elif parts[0] == "blk" and len(parts) == 4 and parts[2] in _SHARED_EXPERT:
+            out[f"model.layers.{parts[1]}.{_SHARED_EXPERT[parts[2]]}.{parts[3]}"] = t
+        else:
+            out[name] = t
+    for layer, st in stacks.items():
+        out[f"model.layers.{layer}.mlp.experts.gate_up_proj"] = torch.cat([st["gate"], st["up"]], 1)
+        out[f"model.layers.{layer}.mlp.experts.down_proj"] = st["down"]
+    return out
+
+
+def split_expert_tensors(sd: Dict[str, torch.Tensor], n_experts: int) -> Dict[str, torch.Tensor]:
+    """Inverse of :func:`fuse_expert_tensors` for export: fused or per-expert Hugging Face names -> the stacked
+    per-projection tensors (under their file names) plus everything else unchanged."""
+    out = {}
+    per = {}
+    for name, t in sd.items():
+        parts = name.split(".")
+        if len(parts) >= 5 and parts[0] == "model" and parts[1] == "layers":
+            layer, rest = parts[2], ".".join(parts[3:])
+            moe = rest.split(".", 1)[1] if rest.startswith(("mlp.", "block_sparse_moe.")) else None
+            if moe == "experts.gate_up_proj":
+                F = t.shape[1] // 2
+                out[f"blk.{layer}.ffn_gate_exps.weight"], out[f"blk.{layer}.ffn_up_exps.weight"] = t[:, :F], t[:, F:]
+                continue
+            if moe == "experts.down_proj":
+                out[f"blk.{layer}.ffn_down_exps.weight"] = t
+                continue
+            if moe and moe.startswith("experts.") and moe.count(".") == 3:            # experts.<e>.<proj>.weight
+                _, e, proj, _w = moe.split(".")
+                kind = {"w1": "gate", "gate_proj": "gate", "w3": "up", "up_proj": "up", "w2": "down",
+                        "down_proj": "down"}[proj]
+                per.setdefault((layer, kind), {})[int(e)] = t
+                continue
+            if moe == "gate.weight":
+                out[f"blk.{layer}.ffn_gate_inp.weight"] = t
+                continue
+            inv = {v: k for k, v in _SHARED_EXPERT.items()}
+            if rest.rsplit(".", 1)[0] in inv:
+                out[f"blk.{layer}.{inv[rest.rsplit('.', 1)[0]]}.{parts[-1]}"] = t
+                continue
+        out[name] = t
+    for (layer, kind), ts in per.items():
+        out[f"blk.{layer}.ffn_{kind}_exps.weight"] = torch.stack([ts[e] for e in range(n_experts)])
+    return out
+
+
 def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quant: str = "q8_0",
                       tokens: Optional[List[str]] = None, extra_metadata: Optional[Dict[str, Any]] = None
                       ) -> Dict[str, int]:
@@ -230,7 +292,11 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
     reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  Returns
     {tensor type id: count}."""
     ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8, "i2_s": 36}[quant.lower()]   # i2_s: BitNet ternary projections
-    arch = config.get("model_type", "llama")
+    arch = {"mixtral": "llama", "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe"}.get(
+        config.get("model_type", "llama"), config.get("model_type", "llama"))
+    n_exp = int(config.get("num_local_experts") or config.get("num_experts") or 0)
+    if n_exp:
+        sd = split_expert_tensors(sd, n_exp)
     md = {"general.architecture": arch, "general.name": str(config.get("_name_or_path", "model")),
           f"{arch}.block_count": int(config["num_hidden_layers"]),
           f"{arch}.embedding_length": int(config["hidden_size"]),
@@ -242,6 +308,12 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
           f"{arch}.vocab_size": int(config["vocab_size"])}
     if tokens:
         md["tokenizer.ggml.tokens"] = list(tokens)
+    if n_exp:
+        md[f"{arch}.expert_count"] = n_exp
+        md[f"{arch}.expert_used_count"] = int(config.get("num_experts_per_tok", 2))
+        md[f"{arch}.expert_feed_forward_length"] = int(config.get("moe_intermediate_size") or config["intermediate_size"])
+        if config.get("shared_expert_intermediate_size"):
+            md[f"{arch}.expert_shared_feed_forward_length"] = int(config["shared_expert_intermediate_size"])
     md.update(extra_metadata or {})              # tokenizer tables, chat template, ...
     if config.get("max_position_embeddings"):
         md[f"{arch}.context_length"] = int(config["max_position_embeddings"])
@@ -279,10 +351,11 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
                 t = pair_rope_rows(t, nkv)
         if arch == "gemma" and name.endswith("norm.weight"):
             t = t.float() + 1.0      # converted Gemma files hold 1 + gamma (the loader takes the 1 off again)
-        quantisable = t.dim() == 2 and t.shape[1] % 32 == 0 and "embed_tokens" not in name and "norm" not in name
+        quantisable = t.dim() in (2, 3) and t.shape[-1] % 32 == 0 and "embed_tokens" not in name and \
+            "norm" not in name and "ffn_gate_inp" not in name
         if ty == 36:      # ternary only where the model is ternary (the projections), whole 128-value blocks
             quantisable = quantisable and name.endswith("_proj.weight") and t.numel() % 128 == 0
-        tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 else 0)
+        tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 and "ffn_gate_inp" not in name else 0)
         tensors[gguf_name(name, arch)] = (tt, t.float())
         counts[tt] = counts.get(tt, 0) + 1
     write_gguf(path, md, tensors)
@@ -306,6 +379,17 @@ def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
            "head_dim": g("attention.key_length"), "max_position_embeddings": g("context_length")}
     if arch in PAIRED_ROPE_ARCHS:
         out["rope_half_split"] = False          # Q / K rows are stored with their rotary pairs adjacent
+    n_exp = int(g("expert_count") or 0)
+    if n_exp > 0:
+        # mixture-of-experts files: Mixtral is written under the "llama" architecture, the Qwen families under
+        # their own; expert weights come as one stacked tensor per projection (see fuse_expert_tensors)
+        out["model_type"] = {"llama": "mixtral", "qwen2moe": "qwen2_moe", "qwen3moe": "qwen3_moe"}.get(arch, arch)
+        out["num_local_experts"] = out["num_experts"] = n_exp
+        out["num_experts_per_tok"] = int(g("expert_used_count") or 2)
+        out["moe_intermediate_size"] = int(g("expert_feed_forward_length") or g("feed_forward_length") or 0) or None
+        out["shared_expert_intermediate_size"] = int(g("expert_shared_feed_forward_length") or 0) or None
+        out["norm_topk_prob"] = arch != "qwen2moe"
+        out["decoder_sparse_step"], out["mlp_only_layers"] = 1, []
     # context extension declared in the metadata: linear position scaling or yarn (a per-pair divisor tensor,
     # rope_freqs.weight, is attached by the loader that has the tensors at hand: see rope_factors_config)
     if g("rope.scaling.attn_factor") and not g("rope.scaling.type"):

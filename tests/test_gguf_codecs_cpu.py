@@ -464,3 +464,61 @@ def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
         got = model.forward(b, kc, torch.zeros_like(kc)).float()
         cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
         assert float(cos.min()) > 0.99, (kind, native, cos)
+
+
+@pytest.mark.parametrize("kind", ["mixtral", "qwen2_moe", "qwen3_moe"])
+def test_mixture_of_experts_gguf_round_trip(tmp_path, kind):
+    """Expert weights travel as one stacked tensor per projection (ffn_gate_exps / ffn_up_exps / ffn_down_exps), the
+    router as ffn_gate_inp, a shared expert as *_shexp; Mixtral goes under the llama architecture with expert counts
+    in the metadata.  The model loaded from the file agrees with transformers."""
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.models.llama import StepBatch
+
+    torch.manual_seed(0)
+    common = dict(vocab_size=600, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=False)
+    if kind == "mixtral":
+        hf_cfg = transformers.MixtralConfig(**common, num_local_experts=4, num_experts_per_tok=2)
+        hf = transformers.MixtralForCausalLM(hf_cfg)
+    elif kind == "qwen2_moe":
+        hf_cfg = transformers.Qwen2MoeConfig(**common, moe_intermediate_size=96, shared_expert_intermediate_size=160,
+                                             num_experts=4, num_experts_per_tok=2, decoder_sparse_step=1,
+                                             mlp_only_layers=[])
+        hf = transformers.Qwen2MoeForCausalLM(hf_cfg)
+    else:
+        hf_cfg = transformers.Qwen3MoeConfig(**common, head_dim=32, moe_intermediate_size=96, num_experts=4,
+                                             num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[],
+                                             norm_topk_prob=True)
+        hf = transformers.Qwen3MoeForCausalLM(hf_cfg)
+    hf = hf.eval().float()
+    d = tmp_path / "generators" / kind
+    d.mkdir(parents=True)
+    GG.export_llama_gguf(str(d / "model.gguf"), hf.state_dict(), hf_cfg.to_dict(), quant="q8_0")
+    f = GG.GGUFFile(str(d / "model.gguf"))
+    arch = {"mixtral": "llama", "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe"}[kind]
+    assert f.metadata["general.architecture"] == arch and f.metadata[f"{arch}.expert_count"] == 4
+    F = 128 if kind == "mixtral" else 96
+    assert tuple(f.tensors["blk.0.ffn_gate_exps.weight"].shape) == (4, F, 64)
+    assert tuple(f.tensors["blk.1.ffn_down_exps.weight"].shape) == (4, 64, F)
+    assert tuple(f.tensors["blk.0.ffn_gate_inp.weight"].shape) == (4, 64) and f.tensors["blk.0.ffn_gate_inp.weight"].type == 0
+    assert ("blk.0.ffn_up_shexp.weight" in f.tensors) == (kind == "qwen2_moe")
+    cfg_d = GG.llama_config_from_gguf(f.metadata)
+    assert cfg_d["model_type"] == kind and cfg_d["num_experts"] == 4 and cfg_d["norm_topk_prob"] == (kind != "qwen2_moe")
+    lm = ModelManager(models_dir=str(tmp_path), device="cpu").get(kind, "generator")
+    model = lm.pipeline.engine.model
+    assert model.cfg.num_experts == 4 and model.cfg.rope_half_split == (kind != "mixtral")
+    ids = torch.randint(0, 600, (12,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+    pos = torch.arange(12, dtype=torch.int32)
+    kc = torch.zeros((2, 2, 16, 2, model.cfg.head_dim), dtype=torch.bfloat16)
+    b = StepBatch(ids.int(), pos, pos.clone(), i32([0]), i32([12]), i32([12]), torch.arange(2, dtype=torch.int32)[None],
+                  pos.clone(), 12, 1)
+    got = model.forward(b, kc, torch.zeros_like(kc)).float()
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+    assert float(cos.min()) > 0.98, (kind, cos)
