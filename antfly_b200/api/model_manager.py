@@ -156,7 +156,7 @@ class ModelManager:
             sd = {GG.hf_name(n, arch): f.tensor(n) for n in f.tensors if f.tensors[n].type in GG.SUPPORTED}
             if cfg_d.get("num_experts"):
                 sd = GG.fuse_expert_tensors(sd)
-            if arch == "gemma":
+            if arch in GG.GEMMA_ARCHS:
                 # converted Gemma files store 1 + gamma in their norm tensors; the model adds the 1 itself
                 sd = {k: (v - 1.0 if k.endswith("norm.weight") else v) for k, v in sd.items()}
         elif mf.weights == "safetensors":

@@ -157,7 +157,11 @@ _LAYER = {"attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": 
           "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",              # Qwen3, Gemma-3
           "attn_qkv": "self_attn.qkv_proj"}                                                   # Phi-3 (fused)
 # per architecture: names that mean something else there
-_LAYER_ARCH = {"phi3": {"ffn_up": "mlp.gate_up_proj"}}                                        # gate and up stacked
+_GEMMA_POST = {"ffn_norm": "pre_feedforward_layernorm", "post_attention_norm": "post_attention_layernorm",
+               "post_ffw_norm": "post_feedforward_layernorm"}                                 # norms on both sides
+_LAYER_ARCH = {"phi3": {"ffn_up": "mlp.gate_up_proj"},                                        # gate and up stacked
+               "gemma2": _GEMMA_POST, "gemma3": _GEMMA_POST, "gemma3_text": _GEMMA_POST}
+GEMMA_ARCHS = ("gemma", "gemma2", "gemma3")
 
 
 def hf_name(gguf_name: str, arch: Optional[str] = None) -> str:
@@ -292,7 +296,7 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
     reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  Returns
     {tensor type id: count}."""
     ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8, "i2_s": 36}[quant.lower()]   # i2_s: BitNet ternary projections
-    arch = {"mixtral": "llama", "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe"}.get(
+    arch = {"mixtral": "llama", "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe", "gemma3_text": "gemma3"}.get(
         config.get("model_type", "llama"), config.get("model_type", "llama"))
     n_exp = int(config.get("num_local_experts") or config.get("num_experts") or 0)
     if n_exp:
@@ -308,6 +312,25 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
           f"{arch}.vocab_size": int(config["vocab_size"])}
     if tokens:
         md["tokenizer.ggml.tokens"] = list(tokens)
+    if arch in ("gemma2", "gemma3"):
+        if config.get("sliding_window"):
+            md[f"{arch}.attention.sliding_window"] = int(config["sliding_window"])
+        for key in ("attn_logit_softcapping", "final_logit_softcapping"):
+            if config.get(key):
+                md[f"{arch}.{key}"] = float(config[key])
+        if config.get("query_pre_attn_scalar"):
+            md[f"{arch}.attention.query_pre_attn_scalar"] = float(config["query_pre_attn_scalar"])
+        if arch == "gemma3":
+            rp = config.get("rope_parameters") or {}
+            full, local = rp.get("full_attention", rp), rp.get("sliding_attention", {})
+            md[f"{arch}.rope.freq_base"] = float(full.get("rope_theta") or config.get("rope_theta") or 1000000.0)
+            md[f"{arch}.rope.local_freq_base"] = float(local.get("rope_theta") or config.get("rope_local_base_freq")
+                                                       or 10000.0)
+            if full.get("rope_type") == "linear" and full.get("factor"):
+                md[f"{arch}.rope.scaling.type"], md[f"{arch}.rope.scaling.factor"] = "linear", float(full["factor"])
+            kinds = config.get("layer_types")
+            if kinds:
+                md[f"{arch}.attention.layer_types"] = [1 if k == "sliding_attention" else 0 for k in kinds]
     if n_exp:
         md[f"{arch}.expert_count"] = n_exp
         md[f"{arch}.expert_used_count"] = int(config.get("num_experts_per_tok", 2))
@@ -349,7 +372,7 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
                 t = pair_rope_rows(t, nh)
             elif name.endswith(("self_attn.k_proj.weight", "self_attn.k_proj.bias")):
                 t = pair_rope_rows(t, nkv)
-        if arch == "gemma" and name.endswith("norm.weight"):
+        if arch in GEMMA_ARCHS and name.endswith("norm.weight"):
             t = t.float() + 1.0      # converted Gemma files hold 1 + gamma (the loader takes the 1 off again)
         quantisable = t.dim() in (2, 3) and t.shape[-1] % 32 == 0 and "embed_tokens" not in name and \
             "norm" not in name and "ffn_gate_inp" not in name
@@ -402,6 +425,23 @@ def llama_config_from_gguf(md: Dict[str, Any]) -> dict:
         if g("rope.scaling.attn_factor"):
             rope["attention_factor"] = float(g("rope.scaling.attn_factor"))
         out["rope_scaling"] = rope
+    if arch in ("gemma2", "gemma3"):
+        # Converted files carry the window and the soft caps; the layer pattern, the local rotary base and the
+        # query scale are fixed per family there, so the defaults of the configuration reader apply when the
+        # optional keys this module's own exporter adds (layer_types, local_freq_base, query_pre_attn_scalar) are absent.
+        out["sliding_window"] = g("attention.sliding_window")
+        out["attn_logit_softcapping"], out["final_logit_softcapping"] = g("attn_logit_softcapping"), g("final_logit_softcapping")
+        out["query_pre_attn_scalar"] = g("attention.query_pre_attn_scalar") or g("attention.key_length")
+        if arch == "gemma3":
+            glob = {"rope_type": "default", "rope_theta": float(g("rope.freq_base", 1000000.0))}
+            if out.get("rope_scaling", {}).get("rope_type") == "linear":
+                glob = dict(out.pop("rope_scaling"), rope_theta=glob["rope_theta"])
+            out["rope_parameters"] = {"full_attention": glob, "sliding_attention": {
+                "rope_type": "default", "rope_theta": float(g("rope.local_freq_base", 10000.0))}}
+            out.pop("rope_theta", None)
+            kinds = g("attention.layer_types")
+            if kinds:
+                out["layer_types"] = ["sliding_attention" if k else "full_attention" for k in kinds]
     return out
 
 

@@ -402,7 +402,7 @@ def test_rotary_row_pairing_of_llama_files():
     assert torch.equal(back["model.layers.0.self_attn.v_proj.weight"], w)
 
 
-@pytest.mark.parametrize("kind", ["qwen3", "phi3", "gemma"])
+@pytest.mark.parametrize("kind", ["qwen3", "phi3", "gemma", "gemma2", "gemma3"])
 def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
     """Per-head Q / K norms (attn_q_norm / attn_k_norm) and Phi-3's fused attn_qkv / stacked ffn_up survive export and
     loading, Gemma's norm tensors travel as 1 + gamma; the model served from the file agrees with transformers."""
@@ -423,9 +423,30 @@ def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
             for n, p in hf.named_parameters():
                 if n.endswith(("q_norm.weight", "k_norm.weight")):
                     p.uniform_(0.5, 1.5)
-    elif kind == "gemma":
-        hf_cfg = transformers.GemmaConfig(**{**common, "head_dim": 16, "hidden_activation": "gelu_pytorch_tanh"})
-        hf = transformers.GemmaForCausalLM(hf_cfg).eval().float()
+    elif kind.startswith("gemma"):
+        extra = {"head_dim": 16, "hidden_activation": "gelu_pytorch_tanh"}
+        if kind == "gemma":
+            hf_cfg = transformers.GemmaConfig(**{**common, **extra})
+            hf = transformers.GemmaForCausalLM(hf_cfg)
+        elif kind == "gemma2":
+            hf_cfg = transformers.Gemma2Config(**{**common, **extra, "query_pre_attn_scalar": 24, "sliding_window": 8,
+                                                  "num_hidden_layers": 3, "attn_logit_softcapping": 4.0,
+                                                  "final_logit_softcapping": 3.0})
+            hf_cfg.tie_word_embeddings = False
+            hf = transformers.Gemma2ForCausalLM(hf_cfg)
+        else:
+            hf_cfg = transformers.Gemma3TextConfig(**{**common, **extra, "query_pre_attn_scalar": 24,
+                                                      "sliding_window": 8, "num_hidden_layers": 3,
+                                                      "layer_types": ["sliding_attention", "full_attention",
+                                                                      "sliding_attention"],
+                                                      "rope_parameters": {
+                                                          "sliding_attention": {"rope_type": "default",
+                                                                                "rope_theta": 10000.0},
+                                                          "full_attention": {"rope_type": "linear", "factor": 4.0,
+                                                                             "rope_theta": 1000000.0}}})
+            hf_cfg.tie_word_embeddings = False
+            hf = transformers.Gemma3ForCausalLM(hf_cfg)
+        hf = hf.eval().float()
         with torch.no_grad():
             for n, p in hf.named_parameters():
                 if "norm" in n:
@@ -440,7 +461,9 @@ def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
     if kind == "qwen3":
         assert "blk.0.attn_q_norm.weight" in f.tensors and "blk.1.attn_k_norm.weight" in f.tensors
         assert f.metadata["qwen3.attention.key_length"] == 32
-    elif kind == "gemma":
+    elif kind.startswith("gemma"):
+        if kind != "gemma":
+            assert "blk.0.post_attention_norm.weight" in f.tensors and "blk.2.post_ffw_norm.weight" in f.tensors
         stored = f.tensor("blk.0.attn_norm.weight")
         torch.testing.assert_close(stored, hf.state_dict()["model.layers.0.input_layernorm.weight"] + 1.0,
                                    atol=1e-6, rtol=0)
@@ -458,7 +481,7 @@ def test_qwen3_and_phi3_gguf_names_round_trip_and_serve(tmp_path, kind):
         model = lm.pipeline.engine.model
         assert lm.info.get("weights") == ("gguf-native" if native else lm.info.get("weights"))
         D = model.cfg.head_dim
-        kc = torch.zeros((2, 2, 16, 2, D), dtype=torch.bfloat16)
+        kc = torch.zeros((model.cfg.num_hidden_layers, 2, 16, 2, D), dtype=torch.bfloat16)
         b = StepBatch(ids.int(), pos, pos.clone(), i32([0]), i32([12]), i32([12]),
                       torch.arange(2, dtype=torch.int32)[None], pos.clone(), 12, 1)
         got = model.forward(b, kc, torch.zeros_like(kc)).float()
