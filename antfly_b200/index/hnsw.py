@@ -44,6 +44,7 @@ def _lib():
         lib.afb_hnsw_stats.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         lib.afb_hnsw_get_metadata.restype = ctypes.c_long
         lib.afb_hnsw_get_metadata.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_long]
+        lib.afb_hnsw_get_vector.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]
         lib.afb_hnsw_check.argtypes = [ctypes.c_void_p]
         lib.afb_hnsw_save.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
         lib._hnsw_typed = True
@@ -139,6 +140,13 @@ class HNSWIndex:
             if n <= cap:
                 return buf.raw[:n]
             cap = n
+
+    def get_vector(self, id_: int) -> Optional[torch.Tensor]:
+        """The stored vector of an id (unit-normalised under the cosine metric), or None."""
+        out = np.empty(self.dim, dtype=np.float32)
+        if self._lib.afb_hnsw_get_vector(self._h, id_, out.ctypes.data) != 0:
+            return None
+        return torch.from_numpy(out)
 
     def stats(self) -> Dict[str, int]:
         out = (ctypes.c_long * 6)()

@@ -495,6 +495,17 @@ long afb_hnsw_get_metadata(void* p, uint64_t id, uint8_t* out, long cap) {
   return static_cast<long>(m.size());
 }
 
+// The stored vector of `id` into out [dim] (unit-normalised for the cosine metric); 0, or -1 when the id is absent.
+int afb_hnsw_get_vector(void* p, uint64_t id, float* out) {
+  Hnsw* h = static_cast<Hnsw*>(p);
+  if (!h) return -1;
+  std::shared_lock<std::shared_mutex> lock(h->mu);
+  auto it = h->slot_of.find(id);
+  if (it == h->slot_of.end()) return -1;
+  std::memcpy(out, h->vec(it->second), sizeof(float) * static_cast<size_t>(h->dim));
+  return 0;
+}
+
 // Structural self-check: 0 when every edge points at a live node that exists on that layer, no list exceeds its
 // capacity or repeats a neighbour or names its own node, the id map agrees with the slots, and the entry point is a
 // live node of the top layer.  Otherwise a positive code naming the first violated rule.

@@ -74,6 +74,8 @@ def test_filtered_search_walks_the_graph_or_scans_directly():
     idx = HNSWIndex(x.shape[1], "l2_squared", ef_search=96, seed=2)
     idx.batch_insert(range(len(x)), x, metadata=meta)
     assert idx.metadata(3) == meta[3] and idx.metadata(10 ** 9) is None
+    torch.testing.assert_close(idx.get_vector(3), x[3])
+    assert idx.get_vector(10 ** 9) is None
     # a broad filter: graph walk, every hit carries the prefix, recall against the exact filtered answer
     keep = torch.tensor([m.startswith(b"tenant-a/") for m in meta])
     res = idx.search(q, 10, filter_prefix=b"tenant-a/")
@@ -114,7 +116,7 @@ def test_delete_repairs_the_graph_and_upsert_replaces():
     assert idx.check() == 0
     # freed slots are reused; re-inserting an id moves it
     before = idx.stats()["slots"]
-    idx.batch_insert([1, 3], torch.stack([x[5], q[0]]))
+    idx.batch_insert([1, 3, 3], torch.stack([x[5], x[6], q[0]]))       # an id repeated in a batch: the last one stays
     assert idx.stats()["slots"] == before and idx.check() == 0
     hit = idx.search(q[:1], 1)
     assert hit.ids[0, 0].item() == 3 and hit.distances[0, 0].item() < 1e-5
