@@ -15,6 +15,7 @@ o/down split by input columns).  How it is executed is B200-first:
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -448,8 +449,10 @@ class LlamaModel:
     # --------------------------------------------------------------------------------------------------
     # Skinny batches (decode, speculative verify) take the native MX path: activations are quantised to MX fp8
     # (two terms ~ bf16 accuracy) and the tensor core applies both block scales; large prefill batches keep
-    # bf16 activations and dequantise the weights in the GEMM (W8A16).
-    mx_max_tokens: int = 128
+    # bf16 activations and dequantise the weights in the GEMM (W8A16).  The MX kernel tiles any number of tokens
+    # (128 per CTA), so the boundary is a tuning knob: ANTFLY_B200_MX_MAX_TOKENS moves it (e.g. to route prefill
+    # chunks through the block-scaled tensor-core path as well).
+    mx_max_tokens: int = int(os.environ.get("ANTFLY_B200_MX_MAX_TOKENS", "128"))
     act_terms: int = 2
 
     def _use_mx(self, T: int) -> bool:
