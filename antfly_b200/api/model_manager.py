@@ -62,7 +62,8 @@ class ModelManager:
     def __init__(self, models_dir: Optional[str] = None, device: Optional[str] = None, max_loaded_models: int = 8,
                  kv_blocks: int = 4096, max_batch: int = 64, prefix_cache: bool = True, keep_alive_s: float = 0.0,
                  max_memory_mb: int = 0, strategies: Optional[Dict[str, str]] = None, clock=time.time,
-                 tensor_parallel: Optional[tuple] = None, gguf_native: Optional[bool] = None):
+                 tensor_parallel: Optional[tuple] = None, gguf_native: Optional[bool] = None,
+                 adapters: Optional[Dict[str, str]] = None):
         """``max_loaded_models`` 0 = unlimited; ``keep_alive_s`` > 0 unloads directory-backed models idle for that
         long (checked on every access and by :meth:`evict_idle`); ``max_memory_mb`` > 0 is an advisory budget on
         parameter bytes, enforced by unloading least-recently-used models; ``strategies`` maps model names to
@@ -80,6 +81,10 @@ class ModelManager:
         # tensor-parallel job (every rank serves the same requests in lockstep), the reference's
         # TERMITE_MLX_DISTRIBUTED_MODE=tensor_parallel deployment (zig/pkg/inference/docs/RERANKING.md:32-43)
         self.tensor_parallel = tensor_parallel
+        # model name -> adapter name under <model>/adapters/ (default: the adapter in the model directory itself,
+        # else adapters/retrieval; the ANTFLY_B200_ADAPTER environment variable names one for every model)
+        self.adapters = dict(adapters or {})
+        self._tls = threading.local()          # per-thread note of the adapter merged by the load in progress
         # GGUF generators: keep the projections in their block formats and expand them inside the kernels instead
         # of re-packing to block fp8 at load time (default: the ANTFLY_B200_GGUF_NATIVE environment switch)
         self.gguf_native = os.environ.get("ANTFLY_B200_GGUF_NATIVE", "0") == "1" if gguf_native is None else gguf_native
@@ -163,6 +168,11 @@ class ModelManager:
             sd, cfg_d = ST.load_model_dir(path), mf.config
         else:
             raise ModelNotFound(f"{name}: no loadable weights (found {mf.weights})")
+        # a low-rank adapter in the model directory (or the one named for this model) is folded into the weights
+        # before they are packed, so the adapted model runs at the base model's cost
+        from ..formats import lora as LORA
+
+        self._tls.adapter = LORA.apply_adapter(sd, path, self.adapters.get(name) or os.environ.get("ANTFLY_B200_ADAPTER"))
         if task == "embedder" and cfg_d.get("model_type") == "clip":
             from ..models.clip import ClipConfig, ClipModel
             from ..pipelines.multimodal import ClipEmbedder
@@ -442,7 +452,13 @@ class ModelManager:
         path = MF.resolve_model_path(name, self.models_dir, task + "s")
         if path is None:
             raise ModelNotFound(f"model {name!r} not found under {self.models_dir} ({task}s/)")
+        self._tls.adapter = None
         lm = self._load_dir(name, task, path)
+        ad = self._tls.adapter
+        if ad:
+            lm.info["adapter"] = {k: v for k, v in ad.items() if k != "path"}
+            lm.info["adapter"]["name"] = os.path.basename(ad["path"]) \
+                if os.path.basename(os.path.dirname(ad["path"])) == "adapters" else "default"
         lm.last_used = now
         lm.pinned = self.strategies.get(name) == "eager"
         lm.bytes = _param_bytes(lm.pipeline)
