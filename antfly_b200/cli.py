@@ -468,6 +468,51 @@ def cmd_list(args) -> int:
     return 0
 
 
+def cmd_finetune(args) -> int:
+    """``finetune run recipe.json [--dry-run] [--resume-from DIR]``: the recipe runner (the reference's
+    ``finetune run``, zig/pkg/inference/docs/finetuning/FINETUNING.md "Unified Recipes").  Under ``torchrun`` (RANK /
+    WORLD_SIZE set) the ranks train data-parallel: gloo on CPU, NCCL on GPUs."""
+    import os
+
+    from .finetune import recipes as R
+
+    with open(args.recipe, encoding="utf-8") as f:
+        recipe = json.load(f)
+    try:
+        if args.dry_run or args.action == "plan":
+            print(json.dumps({"recipe": R.normalize(recipe)["recipe"], "steps": R.plan(recipe)}, indent=1))
+            return 0
+        dist, device = None, args.device or "cpu"
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1:
+            import torch
+            import torch.distributed as D
+
+            if device.startswith("cuda"):
+                device = f"cuda:{os.environ.get('LOCAL_RANK', '0')}"
+                torch.cuda.set_device(device)
+            D.init_process_group("nccl" if device.startswith("cuda") else "gloo")
+            dist = (D.get_rank(), world)
+        lead = dist is None or dist[0] == 0
+
+        def log(rec):
+            if lead:
+                print("step {step} loss {loss:.4f} lr {lr:.2e} grad_norm {grad_norm:.3f}".format(**rec), file=sys.stderr)
+
+        rep = R.run_recipe(recipe, dist, device, args.resume_from, log)
+        if lead:
+            print(json.dumps({k: rep.get(k) for k in ("status", "train", "eval", "packing") if k in rep}))
+        if dist is not None:
+            import torch.distributed as D
+
+            D.barrier()
+            D.destroy_process_group()
+    except R.RecipeError as e:
+        print(f"recipe error: {e}", file=sys.stderr)
+        return 2
+    return 0
+
+
 def cmd_pull(args) -> int:
     """Fetch a model (``[hf:]owner/name[:variant]``) into the models directory from a hub or a mirror directory
     (the reference's ``pull``, zig/pkg/inference/src/registry/registry.zig:225-251)."""
@@ -607,6 +652,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
     p.set_defaults(fn=cmd_quantize)
     p = sub.add_parser("list"); common(p); p.set_defaults(fn=cmd_list)
+    p = sub.add_parser("finetune", help="run a fine-tuning recipe (LoRA / QLoRA SFT, DPO, GRPO, reranker, embedder)")
+    p.add_argument("action", choices=["run", "plan"]); p.add_argument("recipe", help="recipe JSON file")
+    p.add_argument("--dry-run", action="store_true", help="print the plan and stop")
+    p.add_argument("--resume-from", help="checkpoint directory of an earlier run of the same recipe")
+    p.add_argument("--device"); p.set_defaults(fn=cmd_finetune)
     p = sub.add_parser("pull", help="fetch models into the models directory")
     p.add_argument("refs", nargs="+", help="[hf:]owner/name[:variant] (auto, gguf, gguf:Q4_K_M, safetensors, mmproj)")
     p.add_argument("--models-dir"); p.add_argument("--token")
