@@ -476,6 +476,16 @@ def cmd_finetune(args) -> int:
 
     from .finetune import recipes as R
 
+    if args.action == "smoke-fast":
+        import tempfile
+
+        root = args.recipe or os.path.join(tempfile.gettempdir(), "antfly-b200-finetune-smoke-fast")
+        summary = R.smoke_fast(root)
+        print(json.dumps(summary))
+        return 0 if summary["ok"] else 1
+    if not args.recipe:
+        print("finetune run / plan need a recipe file", file=sys.stderr)
+        return 2
     with open(args.recipe, encoding="utf-8") as f:
         recipe = json.load(f)
     try:
@@ -653,7 +663,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.set_defaults(fn=cmd_quantize)
     p = sub.add_parser("list"); common(p); p.set_defaults(fn=cmd_list)
     p = sub.add_parser("finetune", help="run a fine-tuning recipe (LoRA / QLoRA SFT, DPO, GRPO, reranker, embedder)")
-    p.add_argument("action", choices=["run", "plan"]); p.add_argument("recipe", help="recipe JSON file")
+    p.add_argument("action", choices=["run", "plan", "smoke-fast"])
+    p.add_argument("recipe", nargs="?", help="recipe JSON file (smoke-fast: output directory, optional)")
     p.add_argument("--dry-run", action="store_true", help="print the plan and stop")
     p.add_argument("--resume-from", help="checkpoint directory of an earlier run of the same recipe")
     p.add_argument("--device"); p.set_defaults(fn=cmd_finetune)

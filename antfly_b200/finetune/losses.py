@@ -61,7 +61,8 @@ def dpo_loss(policy_chosen, policy_rejected, ref_chosen, ref_rejected, beta: flo
     """-log sigmoid(beta * ((pi_c - pi_r) - (ref_c - ref_r))); also returns the mean reward margin and accuracy."""
     margin = (policy_chosen - policy_rejected) - (ref_chosen - ref_rejected)
     loss = -F.logsigmoid(beta * margin).mean()
-    return loss, {"reward_margin": float((beta * margin).mean()), "accuracy": float((margin > 0).float().mean())}
+    m = margin.detach()
+    return loss, {"reward_margin": float((beta * m).mean()), "accuracy": float((m > 0).float().mean())}
 
 
 def grpo_advantages(rewards: torch.Tensor, group_size: int, normalize: bool = True) -> torch.Tensor:

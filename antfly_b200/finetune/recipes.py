@@ -477,3 +477,88 @@ class _Run:
 def run_recipe(recipe: dict, dist: Optional[Tuple[int, int]] = None, device: str = "cpu",
                resume_from: Optional[str] = None, log=None) -> dict:
     return _Run(recipe, dist, device, resume_from, log).run()
+
+
+# ----------------------------------------------------------------------------------------------------------
+# self-check without any downloaded model
+# ----------------------------------------------------------------------------------------------------------
+def _synthetic_decoder(path: str, seed: int = 0) -> None:
+    g = torch.Generator().manual_seed(seed)
+    H, F, V, L_, nh, nkv = 32, 64, 300, 1, 4, 2
+    D_ = H // nh
+    rnd = lambda *s, std=0.05: torch.randn(*s, generator=g) * std
+    sd = {"model.embed_tokens.weight": rnd(V, H, std=0.5), "model.norm.weight": torch.ones(H),
+          "lm_head.weight": rnd(V, H, std=0.3)}
+    for l in range(L_):
+        p = f"model.layers.{l}."
+        sd.update({p + "self_attn.q_proj.weight": rnd(nh * D_, H), p + "self_attn.k_proj.weight": rnd(nkv * D_, H),
+                   p + "self_attn.v_proj.weight": rnd(nkv * D_, H), p + "self_attn.o_proj.weight": rnd(H, nh * D_),
+                   p + "mlp.gate_proj.weight": rnd(F, H), p + "mlp.up_proj.weight": rnd(F, H),
+                   p + "mlp.down_proj.weight": rnd(H, F), p + "input_layernorm.weight": torch.ones(H),
+                   p + "post_attention_layernorm.weight": torch.ones(H)})
+    os.makedirs(path, exist_ok=True)
+    ST.save_file(sd, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as f:
+        json.dump({"model_type": "llama", "hidden_size": H, "intermediate_size": F, "num_hidden_layers": L_,
+                   "num_attention_heads": nh, "num_key_value_heads": nkv, "vocab_size": V, "rope_theta": 10000.0,
+                   "rms_norm_eps": 1e-5, "max_position_embeddings": 256, "tie_word_embeddings": False}, f)
+
+
+def _synthetic_encoder(path: str, num_labels: int, seed: int = 0) -> None:
+    from ..models.bert import BertModel
+
+    cfg = BertConfig(hidden_size=32, num_hidden_layers=1, num_attention_heads=4, intermediate_size=64, vocab_size=300,
+                     num_labels=num_labels)
+    m = BertModel.random_init(cfg, device="cpu", seed=seed)
+    os.makedirs(path, exist_ok=True)
+    ST.save_file(m.state_dict_hf(), os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as f:
+        json.dump({"model_type": "bert", "hidden_size": 32, "num_hidden_layers": 1, "num_attention_heads": 4,
+                   "intermediate_size": 64, "vocab_size": 300, "max_position_embeddings": 512,
+                   "num_labels": num_labels}, f)
+
+
+def smoke_fast(root: str) -> dict:
+    """Every recipe once on synthetic checkpoints and a handful of rows (no model or dataset needed): the plan of
+    each, a short run of each, and the check that its manifest ends ``succeeded``.  The summary is also written to
+    ``<root>/fast_smoke_summary.json`` (the reference's ``finetune smoke-fast``)."""
+    os.makedirs(root, exist_ok=True)
+    dec, enc, rr = os.path.join(root, "decoder"), os.path.join(root, "encoder"), os.path.join(root, "reranker")
+    _synthetic_decoder(dec)
+    _synthetic_encoder(enc, 0)
+    _synthetic_encoder(rr, 1)
+
+    def write(name, rows):
+        p = os.path.join(root, name)
+        with open(p, "w", encoding="utf-8") as f:
+            for r in rows:
+                f.write(json.dumps(r) + "\n")
+        return p
+
+    sft = write("sft.jsonl", [{"prompt": "ab", "completion": "xy"}, {"text": "plain row"}] * 2)
+    pref = write("pref.jsonl", [{"prompt": "pick", "chosen": "good", "rejected": "bad"}] * 2)
+    grpo = write("grpo.jsonl", [{"prompt": "say a", "target": "a"}] * 2)
+    pairs = write("pairs.jsonl", [{"query": "q", "document": "yes", "label": 1}, {"query": "q", "document": "no", "label": 0}])
+    trip = write("trip.jsonl", [{"query": "q1", "positive": "p1"}, {"query": "q2", "positive": "p2"}])
+    cases = {"lora-sft": (dec, sft), "qlora-sft": (dec, sft), "sft": (dec, sft), "dpo": (dec, pref), "grpo": (dec, grpo),
+             "reranker": (rr, pairs), "embedder": (enc, trip)}
+    summary = {"cases": {}, "ok": True}
+    for name, (model, data) in cases.items():
+        recipe = {"recipe": name, "model": {"path": model}, "dataset": {"path": data, "max_seq_len": 48},
+                  "adapter": {"rank": 2, "alpha": 4}, "grpo": {"group_size": 2, "max_completion_tokens": 2},
+                  "optimizer": {"epochs": 1, "batch_size": 2, "learning_rate": 1e-3},
+                  "artifacts": {"root": os.path.join(root, "run-" + name)}}
+        rec = {"plan": [s["name"] for s in plan(recipe)]}
+        try:
+            rep = run_recipe(recipe)
+            with open(os.path.join(root, "run-" + name, "recipe_run_manifest.json"), encoding="utf-8") as f:
+                rec["manifest_status"] = json.load(f)["status"]
+            rec["final_loss"] = rep["train"]["final_loss"]
+            rec["ok"] = rec["manifest_status"] == "succeeded" and rep["train"]["final_loss"] == rep["train"]["final_loss"]
+        except Exception as e:                                  # the suite reports, the caller decides
+            rec["ok"], rec["error"] = False, f"{type(e).__name__}: {e}"
+        summary["cases"][name] = rec
+        summary["ok"] = summary["ok"] and rec["ok"]
+    with open(os.path.join(root, "fast_smoke_summary.json"), "w", encoding="utf-8") as f:
+        json.dump(summary, f, indent=1)
+    return summary

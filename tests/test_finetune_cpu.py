@@ -322,3 +322,13 @@ def test_cli_plan_and_two_rank_data_parallel_equals_one_rank_with_the_global_bat
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps({"recipe": "rlhf"}))
     assert main(["finetune", "run", str(bad)]) == 2
+
+
+def test_smoke_fast_runs_every_recipe_on_synthetic_checkpoints(tmp_path, capsys):
+    from antfly_b200.cli import main
+
+    assert main(["finetune", "smoke-fast", str(tmp_path / "smoke")]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary["ok"] and set(summary["cases"]) == set(R.RECIPES)
+    assert all(c["manifest_status"] == "succeeded" for c in summary["cases"].values())
+    assert os.path.exists(tmp_path / "smoke" / "fast_smoke_summary.json")
