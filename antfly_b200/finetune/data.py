@@ -166,9 +166,10 @@ def encoder_pairs(tokenizer, rows: Sequence[dict], max_seq_len: int):
 
 
 def encoder_triples(tokenizer, rows: Sequence[dict], max_seq_len: int, query_prefix: str = "", doc_prefix: str = ""):
-    out = []
+    out, docs = [], {}
     for r in rows:
         enc = lambda t, p: tokenizer.encode_for_model(p + str(t), max_seq_len)
         out.append({"query": enc(r["query"], query_prefix), "positive": enc(r["positive"], doc_prefix),
-                    "negatives": [enc(n, doc_prefix) for n in r.get("negatives", [])]})
+                    "negatives": [enc(n, doc_prefix) for n in r.get("negatives", [])],
+                    "doc": docs.setdefault(str(r["positive"]), len(docs))})      # same text, same document id
     return out

@@ -93,14 +93,21 @@ def grpo_loss(new_logps, old_logps, ref_logps, advantages, token_mask, clip_epsi
 
 
 def info_nce(query: torch.Tensor, positive: torch.Tensor, negatives: Optional[torch.Tensor] = None,
-             temperature: float = 0.05, bank: Optional[torch.Tensor] = None):
+             temperature: float = 0.05, bank: Optional[torch.Tensor] = None,
+             bank_exclude: Optional[torch.Tensor] = None):
     """Contrastive loss with in-batch negatives: row i's positive is positive[i]; every other positive, the optional
-    hard negatives [B, N, D] and a bank of earlier embeddings [M, D] (a cross-batch memory) are negatives.  Inputs
-    are L2-normalised vectors."""
+    hard negatives [B, N, D] and a bank of earlier embeddings [M, D] (a cross-batch memory) are negatives, except
+    the bank entries marked in ``bank_exclude`` [B, M] (an earlier embedding of the row's own positive must not
+    count against it).  Inputs are L2-normalised vectors."""
     cands = positive
+    n_bank = 0
     if bank is not None and bank.numel():
         cands = torch.cat([cands, bank.to(cands.dtype)], 0)
+        n_bank = bank.shape[0]
     logits = query @ cands.t() / temperature
+    if n_bank and bank_exclude is not None:
+        pad = torch.zeros(query.shape[0], positive.shape[0], dtype=torch.bool, device=query.device)
+        logits = logits.masked_fill(torch.cat([pad, bank_exclude], 1), float("-inf"))
     if negatives is not None:
         hard = torch.einsum("bd,bnd->bn", query, negatives) / temperature
         logits = torch.cat([logits, hard], 1)

@@ -139,6 +139,7 @@ class DecoderNet(nn.Module):
             raise NotImplementedError("checkpoints with fused projections (Phi-3) are not trainable here")
         sd = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in sd.items()}
         self.cfg, self.checkpointing = cfg, checkpointing
+        self.neftune_alpha = 0.0          # > 0: uniform noise of magnitude alpha / sqrt(S * H) on the embeddings while training
         self.model = _DecoderBody(cfg, sd, dtype)
         head = sd.get("lm_head.weight")
         self.lm_head = _linear(head if head is not None and not cfg.tie_word_embeddings
@@ -172,6 +173,8 @@ class DecoderNet(nn.Module):
             positions = idx[None].expand(B, S)
         mask = mask | torch.eye(S, dtype=torch.bool, device=ids.device)[None]        # no empty rows (padding queries)
         x = self.model.embed_tokens(ids) * c.embed_scale
+        if self.training and self.neftune_alpha > 0:
+            x = x + (torch.rand_like(x) * 2 - 1) * (self.neftune_alpha / (S * x.shape[-1]) ** 0.5)
         for layer in self.model.layers:
             if self.checkpointing and self.training:
                 x = checkpoint(layer, x, positions, mask[:, None], self.inv_freq, use_reentrant=False)

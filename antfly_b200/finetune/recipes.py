@@ -165,6 +165,7 @@ class _Run:
             self.cfg = LlamaConfig.from_hf(mf.config)
             dtype = {"bf16": torch.bfloat16, "fp32": torch.float32}[r["model"].get("dtype", "fp32")]
             self.net = DecoderNet(self.cfg, sd, dtype=dtype, checkpointing=ckpt)
+            self.net.neftune_alpha = float(r["optimizer"].get("neftune_alpha", 0.0))
         else:
             self.cfg = BertConfig.from_hf(mf.config)
             if name == "reranker" and not self.cfg.num_labels:
@@ -334,17 +335,44 @@ class _Run:
         return LS.reranker_loss(scores, labels, groups, self.r["optimizer"].get("reranker_loss", "bce")), {}
 
     def _embedder_step(self, batch):
+        """InfoNCE over (query, positive) with in-batch negatives, optional hard negatives, an optional cross-batch
+        memory of earlier positives (``optimizer.xbm_capacity``) and Matryoshka prefixes (``optimizer.mrl_dims``: the
+        loss is averaged over the embedding truncated to each size and re-normalised), as in the reference's
+        contrastive trainer (zig/pkg/inference/docs/finetuning/FINETUNING.md "Cross-Batch Memory", "Matryoshka")."""
+        op = self.r["optimizer"]
+
         def emb(seqs):
             st, att = self._encode(seqs)
-            return self.net.pool(st, att)
+            return self.net.pool(st, att, normalize=False)
 
         q, p = emb([b["query"] for b in batch]), emb([b["positive"] for b in batch])
         n_neg = min((len(b["negatives"]) for b in batch), default=0)
         neg = None
         if n_neg:
-            flat = emb([n for b in batch for n in b["negatives"][:n_neg]])
-            neg = flat.view(len(batch), n_neg, -1)
-        return LS.info_nce(q, p, neg, float(self.r["optimizer"].get("temperature", 0.05)))
+            neg = emb([n for b in batch for n in b["negatives"][:n_neg]]).view(len(batch), n_neg, -1)
+        dims = [int(d) for d in op.get("mrl_dims") or [q.shape[-1]]]
+        bank, bank_ids = getattr(self, "_xbm", None), getattr(self, "_xbm_ids", None)
+        self._emb_steps = getattr(self, "_emb_steps", 0) + (1 if self.net.training else 0)
+        # the memory assumes embeddings that drift slowly: it is switched on after optimizer.xbm_warmup_steps
+        # micro-steps, once the encoder has left its starting point
+        warm = self._emb_steps > int(op.get("xbm_warmup_steps", 0))
+        use_bank = bank is not None and self.net.training and warm
+        ids = torch.tensor([b.get("doc", -1) for b in batch], device=self.device)
+        exclude = ids[:, None] == bank_ids[None, :] if use_bank else None
+        temp = float(op.get("temperature", 0.05))
+        norm = lambda t, d: torch.nn.functional.normalize(t[..., :d], dim=-1)
+        total, metrics = 0.0, {}
+        for d in dims:
+            loss, m = LS.info_nce(norm(q, d), norm(p, d), norm(neg, d) if neg is not None else None, temp,
+                                  norm(bank, d) if use_bank else None, exclude)
+            total = total + loss / len(dims)
+            metrics = m if d == dims[0] else metrics
+        cap = int(op.get("xbm_capacity", 0))
+        if cap and self.net.training and warm:
+            new = p.detach()
+            self._xbm = new if bank is None else torch.cat([bank, new], 0)[-cap:]
+            self._xbm_ids = ids if bank_ids is None else torch.cat([bank_ids, ids], 0)[-cap:]
+        return total, metrics
 
     def _train(self):
         r, name = self.r, self.r["recipe"]

@@ -273,10 +273,12 @@ def test_reranker_and_embedder_recipes(tmp_path):
            "dataset": {"path": _jsonl(tmp_path / "e.jsonl", triples), "eval_path": _jsonl(tmp_path / "ee.jsonl", triples),
                        "max_seq_len": 32},
            "adapter": {"rank": 4, "alpha": 8, "target_preset": "attention-only"},
-           "optimizer": {"learning_rate": 2e-2, "epochs": 40, "batch_size": 3, "warmup_ratio": 0.0, "temperature": 0.1},
+           "optimizer": {"learning_rate": 2e-2, "epochs": 40, "batch_size": 3, "warmup_ratio": 0.0, "temperature": 0.1,
+                         "mrl_dims": [64, 16], "xbm_capacity": 6, "xbm_warmup_steps": 25},
            "artifacts": {"root": str(tmp_path / "emb-run")}}
     rep = R.run_recipe(rec)
-    assert rep["train"]["final_loss"] < 0.6 * rep["train"]["first_loss"] and rep["eval"]["accuracy"] >= 0.66
+    # (the training loss is not comparable across the run: the memory adds candidates once it is switched on)
+    assert rep["eval"]["loss"] < 0.6 * rep["train"]["first_loss"] and rep["eval"]["accuracy"] >= 0.66
     cfg = json.load(open(tmp_path / "emb-run" / "adapter-trained" / "adapter_config.json"))
     assert cfg["target_modules"] == ["dense", "key", "query", "value"]
     # a failing run leaves a failed manifest behind
