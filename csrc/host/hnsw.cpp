@@ -74,12 +74,14 @@ struct Hnsw {
   float dist(const float* a, const float* b) const {
     float acc = 0.0f;
     if (metric == 0) {
+#pragma omp simd reduction(+ : acc)
       for (int i = 0; i < dim; ++i) {
         const float t = a[i] - b[i];
         acc += t * t;
       }
       return acc;
     }
+#pragma omp simd reduction(+ : acc)
     for (int i = 0; i < dim; ++i) acc += a[i] * b[i];
     return metric == 1 ? -acc : 1.0f - acc;
   }
