@@ -109,8 +109,17 @@ def _err(status: int, code: str, message: str) -> JSONResponse:
 def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
                max_concurrent_requests: int = 64, max_queue_size: int = 256,
                request_timeout_s: float = 0.0, result_cache_ttl_s: float = 120.0,
-               api_key: Optional[str] = None) -> FastAPI:
+               api_key: Optional[str] = None, content_security=None) -> FastAPI:
+    """``content_security``: an :class:`antfly_b200.api.content.ContentSecurity` (or its dictionary form) governing
+    media links in requests; by default only ``data:`` URLs are accepted."""
     app = FastAPI(title="antfly-b200 inference", version="0.1")
+    from .content import ContentFetcher, ContentSecurity
+
+    if isinstance(content_security, dict):
+        content_security = ContentSecurity.from_dict(content_security, bool(content_security.get("allow_downloads")))
+    fetcher = ContentFetcher(content_security)
+    app.state.fetcher = fetcher
+    decode_data_url = fetcher.image             # every image reference of a request goes through the policy
     if api_key:
         # shared deployments: every call except the liveness / readiness probes must carry the key
         import hmac
@@ -203,8 +212,6 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     if isinstance(url, dict):
                         url = url.get("url")
                     try:
-                        from ..pipelines.multimodal import decode_data_url
-
                         images[i] = decode_data_url(url or "")
                     except Exception as e:
                         return _err(400, "invalid_request", f"content part {i}: {e}")
@@ -345,8 +352,6 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             return bad
         if not req.documents:
             return _err(400, "invalid_request", "documents must not be empty")
-        from ..pipelines.multimodal import decode_data_url
-
         docs = []          # per document: (texts, images)
         for i, d in enumerate(req.documents):
             texts, imgs = [], []
@@ -683,8 +688,10 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             from ..pipelines.chunking import chunk_binary
 
             try:
+                vad = aopt.get("vad")          # present (even empty): voice-activity segmentation with its defaults
                 ch = chunk_binary(binary[0], binary[1], int(aopt.get("window_duration_ms") or 30000),
-                                  int(aopt.get("overlap_duration_ms") or 0), max_chunks)
+                                  int(aopt.get("overlap_duration_ms") or 0), max_chunks,
+                                  dict(vad) if isinstance(vad, dict) else None)
             except Exception as e:
                 return _err(400, "invalid_request", str(e))
             metrics.requests.labels("chunk", "200").inc()
@@ -792,8 +799,6 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             return bad
         if not req.images:
             return _err(400, "invalid_request", "images must not be empty")
-        from ..pipelines.multimodal import decode_data_url
-
         imgs = []
         for i, im in enumerate(req.images):
             url = im.get("url") if isinstance(im, dict) else im
@@ -846,8 +851,6 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         if not req.pages:
             return _err(400, "invalid_request", "pages must not be empty")
         from ..pipelines.layout import group_entities, normalize_box
-        from ..pipelines.multimodal import decode_data_url
-
         pages = []
         for i, pg in enumerate(req.pages):
             if len(pg.words) != len(pg.boxes) or any(len(b) != 4 for b in pg.boxes):
@@ -910,8 +913,6 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             if any(pictures):
                 # image inputs: a reader turns every image into text first, extraction then runs on that text
                 # (zig/pkg/inference/src/server/server.zig extractImages: read document text -> run extraction)
-                from ..pipelines.multimodal import decode_data_url
-
                 ropt = opts.get("reader") or {}
                 rname = ropt.get("model") if isinstance(ropt, dict) else None
                 if not rname:
@@ -1063,8 +1064,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     [[mk(e) for e in rec.get("entities", [])] for rec in data],
                     [[_NS(head=mk(r["source"]), tail=mk(r["target"]), label=r.get("type", ""),
                           score=float(r.get("score", 1.0))) for r in rec.get("relations", [])] for rec in data],
-                    ResolverConfig(similarity_threshold=float(opts.get("similarity_threshold", 0.85)),
-                                   type_must_match=bool(opts.get("type_must_match", True))))
+                    ResolverConfig(**{k: type(getattr(ResolverConfig, k))(v) for k, v in
+                                      {**opts, **(opts.get("resolver") if isinstance(opts.get("resolver"), dict) else {})
+                                       }.items() if k in ResolverConfig.__dataclass_fields__}))
                 out["knowledge_graph"] = {
                     "entities": [{"id": e.id, "name": e.canonical_name, "label": e.label, "score": e.score,
                                   "mentions": e.mentions, "inputs": e.text_indices} for e in kg.entities],
@@ -1186,7 +1188,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
         per_task = mgr.list_models()
         data = [{"id": n, "object": "model", "owned_by": "antfly-b200", "task": t[:-1]}
                 for t in ("generators", "embedders", "rerankers") for n in per_task.get(t, {})]
-        body = {"object": "list", "data": data, "allow_downloads": False,
+        body = {"object": "list", "data": data, "allow_downloads": bool(fetcher.policy.allow_downloads),
                 "backends": {"default": "b200", "available": ["b200" if torch.cuda.is_available() else "cpu-oracle"]}}
         body.update(per_task)
         return body

@@ -63,6 +63,7 @@ class Config:
     max_memory_mb: int = 0
     model_strategies: Dict[str, str] = field(default_factory=dict)
     allow_downloads: bool = False
+    content_security: Dict[str, object] = field(default_factory=dict)
     log: LogConfig = field(default_factory=LogConfig)
 
     # -- derived -------------------------------------------------------------------------------------------
@@ -115,8 +116,9 @@ class Config:
             raise ValueError("pool_size must be >= 1")
         for m in self.model_strategies:
             self.strategy(m)
-        if self.allow_downloads:
-            raise ValueError("allow_downloads is not supported: this build has no registry client (offline)")
+        from .api.content import ContentSecurity
+
+        ContentSecurity.from_dict(self.content_security, self.allow_downloads)      # raises on bad values
         return self
 
     def to_dict(self) -> dict:

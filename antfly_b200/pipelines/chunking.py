@@ -3,7 +3,7 @@ preference; zig/pkg/inference/src/pipelines/chunking.zig)."""
 from __future__ import annotations
 
 import re
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 
 _TOKEN = re.compile(r"\w+|[^\w\s]", re.UNICODE)
@@ -165,9 +165,112 @@ def chunk_gif(data: bytes, max_chunks: int = 0) -> List[dict]:
     return out
 
 
+VAD_FRAME = 512                     # samples per frame at 16 kHz (32 ms), the frame of the reference's detector
+VAD_DEFAULTS = {"threshold": 0.5, "min_silence_duration_ms": 300, "min_speech_duration_ms": 250, "speech_pad_ms": 30,
+                "max_segment_duration_ms": 30000}
+
+
+def vad_frame_probs(x16k) -> "np.ndarray":
+    """Speech probability per 512-sample frame of 16 kHz mono audio, without a model: frame log-energy against a
+    running noise floor (a low percentile of the recording's frame energies), squashed to (0, 1).  The reference
+    runs a neural detector here (Silero, go/pkg/termite/lib/chunking/vad_audio_chunker.go:217-266); everything
+    downstream of the probabilities follows its rules."""
+    import numpy as np
+
+    n = len(x16k) // VAD_FRAME
+    if n == 0:
+        return np.zeros(0, dtype=np.float32)
+    frames = np.asarray(x16k[: n * VAD_FRAME], dtype=np.float32).reshape(n, VAD_FRAME)
+    frames = frames - frames.mean(1, keepdims=True)
+    db = 10.0 * np.log10((frames ** 2).mean(1) + 1e-10)
+    k = max(3, n // 20)
+    floor = max(float(np.sort(db)[:k].mean()), -80.0)            # the quietest twentieth of the recording
+    # 0.5 at 9 dB above the floor, about 0.9 at 15 dB; the mid-point is kept between -50 and -35 dBFS, so a
+    # recording that is quiet throughout has no speech and one that is loud throughout (no pauses to take a floor
+    # from) is all speech
+    mid = min(max(floor + 9.0, -50.0), -35.0)
+    return (1.0 / (1.0 + np.exp(-(db - mid) / 2.7))).astype(np.float32)
+
+
+def merge_vad_frames(probs, frame_samples: int, sample_rate: int, threshold: float = 0.5,
+                     min_silence_duration_ms: int = 300, min_speech_duration_ms: int = 250, speech_pad_ms: int = 30,
+                     max_segment_duration_ms: int = 30000) -> List[tuple]:
+    """Per-frame speech probabilities -> [(start_sample, end_sample)]: threshold, runs of speech frames, runs shorter
+    than the minimum speech length dropped, neighbours closer than the minimum silence merged, padding on both sides
+    (clipped to the recording), segments longer than the maximum cut into pieces of the maximum length
+    (go/pkg/termite/lib/chunking/vad_audio_chunker.go:272-375)."""
+    raw, start = [], None
+    for i, p in enumerate(probs):
+        if p >= threshold and start is None:
+            start = i
+        elif p < threshold and start is not None:
+            raw.append((start * frame_samples, i * frame_samples))
+            start = None
+    if start is not None:
+        raw.append((start * frame_samples, len(probs) * frame_samples))
+    min_speech = min_speech_duration_ms * sample_rate // 1000
+    kept = [s for s in raw if s[1] - s[0] >= min_speech]
+    if not kept:
+        return []
+    min_sil = min_silence_duration_ms * sample_rate // 1000
+    merged = [list(kept[0])]
+    for a, b in kept[1:]:
+        if a - merged[-1][1] < min_sil:
+            merged[-1][1] = b
+        else:
+            merged.append([a, b])
+    pad, total = speech_pad_ms * sample_rate // 1000, len(probs) * frame_samples
+    merged = [(max(a - pad, 0), min(b + pad, total)) for a, b in merged]
+    if max_segment_duration_ms <= 0:
+        return merged
+    cap = max_segment_duration_ms * sample_rate // 1000
+    out = []
+    for a, b in merged:
+        for s0 in range(a, b, cap):
+            out.append((s0, min(s0 + cap, b)))
+    return out
+
+
+def chunk_wav_vad(data: bytes, vad: Optional[dict] = None, max_chunks: int = 0) -> List[dict]:
+    """Speech segments of a WAV file as chunks (mono 16-bit WAV each, with their time span): voice-activity
+    segmentation instead of fixed windows.  ``vad`` carries the request's overrides of :data:`VAD_DEFAULTS`."""
+    import io
+    import wave
+
+    import numpy as np
+
+    from ..ops.audio_ops import read_wav, resample
+
+    cfg = dict(VAD_DEFAULTS)
+    cfg.update({k: v for k, v in (vad or {}).items() if k in cfg and v})
+    wave_t, rate = read_wav(data)
+    x = wave_t.numpy()
+    x16 = x if rate == 16000 else resample(wave_t, rate, 16000).numpy()
+    segs = merge_vad_frames(vad_frame_probs(x16), VAD_FRAME, 16000, float(cfg["threshold"]),
+                            int(cfg["min_silence_duration_ms"]), int(cfg["min_speech_duration_ms"]),
+                            int(cfg["speech_pad_ms"]), int(cfg["max_segment_duration_ms"]))
+    out = []
+    for a, b in segs:
+        lo, hi = a * rate // 16000, min(b * rate // 16000, len(x))
+        buf = io.BytesIO()
+        with wave.open(buf, "wb") as w:
+            w.setnchannels(1)
+            w.setsampwidth(2)
+            w.setframerate(rate)
+            w.writeframes((np.clip(x[lo:hi], -1.0, 1.0) * 32767.0).round().astype("<i2").tobytes())
+        out.append({"id": len(out), "mime_type": "audio/wav", "data": buf.getvalue(),
+                    "start_time_ms": a * 1000.0 / 16000, "end_time_ms": b * 1000.0 / 16000})
+        if max_chunks and len(out) >= max_chunks:
+            break
+    return out
+
+
 def chunk_binary(mime_type: str, data: bytes, window_ms: int = 30000, overlap_ms: int = 0,
-                 max_chunks: int = 0) -> List[dict]:
-    """WAV audio in windows, GIF animations in frames, anything else as one chunk."""
+                 max_chunks: int = 0, vad: Optional[dict] = None) -> List[dict]:
+    """WAV audio in windows (or in speech segments when voice-activity options are given), GIF animations in frames,
+    anything else as one chunk."""
+    if mime_type == "audio/wav" and vad is not None:
+        return chunk_wav_vad(data, vad, max_chunks)
     if mime_type == "audio/wav":
         return chunk_wav(data, window_ms, overlap_ms, max_chunks)
     if mime_type == "image/gif":

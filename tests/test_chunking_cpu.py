@@ -102,3 +102,74 @@ def test_chunk_endpoint_contract():
     assert c.post("/ai/v1/chunk", json={"config": {}}).status_code == 400
     assert c.post("/ai/v1/chunk", json={"input": text, "config": {"text": {"target_tokens": 3, "overlap_tokens": 3}}}
                   ).status_code == 400
+
+
+def _tone_wav(rate, spans, total_s, amp=0.3, noise=0.002, seed=0):
+    import io
+    import wave
+
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    n = int(rate * total_s)
+    x = rng.normal(0, noise, n).astype(np.float32)
+    t = np.arange(n) / rate
+    for a, b in spans:
+        m = (t >= a) & (t < b)
+        x[m] += amp * np.sin(2 * np.pi * 220 * t[m]) * (0.6 + 0.4 * np.sin(2 * np.pi * 3 * t[m]))
+    buf = io.BytesIO()
+    with wave.open(buf, "wb") as w:
+        w.setnchannels(1); w.setsampwidth(2); w.setframerate(rate)
+        w.writeframes((np.clip(x, -1, 1) * 32767).astype("<i2").tobytes())
+    return buf.getvalue()
+
+
+def test_vad_frame_merging_rules():
+    from antfly_b200.pipelines.chunking import merge_vad_frames
+
+    F, R = 512, 16000
+    # frames: 10 speech, 3 silence, 10 speech, 30 silence, 2 speech (too short), 30 silence, 100 speech
+    probs = [0.9] * 10 + [0.1] * 3 + [0.9] * 10 + [0.1] * 30 + [0.9] * 2 + [0.1] * 30 + [0.9] * 100
+    segs = merge_vad_frames(probs, F, R, 0.5, 300, 250, 30, 0)
+    # 3 silent frames = 96 ms < 300 ms: merged; the 64 ms blip is dropped; 30 ms of padding on each side
+    pad = 30 * R // 1000
+    assert segs == [(0, 23 * F + pad), (85 * F - pad, 185 * F)]
+    assert merge_vad_frames(probs, F, R, 0.5, 50, 250, 0, 0)[:2] == [(0, 10 * F), (13 * F, 23 * F)]
+    assert merge_vad_frames(probs, F, R, 0.5, 300, 30, 0, 0)[1] == (53 * F, 55 * F)          # the blip kept
+    cut = merge_vad_frames(probs, F, R, 0.5, 300, 250, 0, 1000)
+    assert cut[-4:] == [(85 * F, 85 * F + 16000), (85 * F + 16000, 85 * F + 32000), (85 * F + 32000, 85 * F + 48000),
+                        (85 * F + 48000, 185 * F)]
+    assert merge_vad_frames([0.1] * 20, F, R) == [] and merge_vad_frames([], F, R) == []
+
+
+def test_vad_chunking_finds_the_speech_spans_and_the_endpoint_uses_it():
+    import base64
+
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+    from antfly_b200.pipelines.chunking import chunk_wav_vad
+
+    spans = [(0.5, 1.5), (3.0, 4.2)]
+    for rate in (16000, 22050):
+        data = _tone_wav(rate, spans, 5.0)
+        chunks = chunk_wav_vad(data)
+        assert len(chunks) == 2
+        for ch, (a, b) in zip(chunks, spans):
+            assert abs(ch["start_time_ms"] - a * 1000) < 80 and abs(ch["end_time_ms"] - b * 1000) < 80
+            assert ch["data"][:4] == b"RIFF"
+    assert chunk_wav_vad(_tone_wav(16000, [], 2.0)) == []                      # silence: nothing to transcribe
+    assert len(chunk_wav_vad(_tone_wav(16000, [(0.2, 3.8)], 4.0), {"max_segment_duration_ms": 1000})) == 4
+    client = TestClient(create_app(ModelManager(models_dir="/nonexistent", device="cpu")))
+    body = {"input": {"type": "media", "mime_type": "audio/wav",
+                      "data": base64.b64encode(_tone_wav(16000, spans, 5.0)).decode()},
+            "config": {"audio": {"vad": {"min_silence_duration_ms": 200}}}}
+    r = client.post("/ai/v1/chunk", json=body)
+    assert r.status_code == 200, r.text
+    got = r.json()["data"][0]["chunks"] if "data" in r.json() and "chunks" in r.json()["data"][0] else r.json()["data"]
+    assert len(got) == 2 and got[0]["mime_type"] == "audio/wav"
+    body["config"]["audio"] = {"window_duration_ms": 2000}
+    r = client.post("/ai/v1/chunk", json=body)
+    fixed = r.json()["data"][0]["chunks"] if "chunks" in r.json()["data"][0] else r.json()["data"]
+    assert len(fixed) == 3                                                     # fixed windows without the vad section

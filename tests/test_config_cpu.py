@@ -56,7 +56,7 @@ def test_bad_configuration_is_rejected(tmp_path):
     p.write_text("api_url: http://localhost:1\nno_such_key: 1\n")
     with pytest.raises(ValueError, match="unknown configuration key"):
         load_config(str(p), env={})
-    for kw in ({"keep_alive": "soon"}, {"pool_size": 0}, {"max_queue_size": -1}, {"allow_downloads": True},
+    for kw in ({"keep_alive": "soon"}, {"pool_size": 0}, {"max_queue_size": -1}, {"content_security": {"download_timeout_seconds": 0}},
                {"model_strategies": {"m": "sometimes"}}):
         with pytest.raises(ValueError):
             load_config(None, env={}, **kw)

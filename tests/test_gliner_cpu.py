@@ -230,3 +230,39 @@ def test_extract_resolve_option_builds_a_graph():
     assert [e["name"] for e in kg["entities"]] == ["Ada Lovelace", "London"] and kg["entities"][0]["inputs"] == [0, 1]
     assert kg["relations"] == [{"source": "entity-0", "target": "entity-1", "type": "lives in", "score": 0.6,
                                 "inputs": [0]}]
+
+
+def test_extract_resolver_options_filter_and_shape_the_graph():
+    """min_entity_confidence / min_relation_confidence drop weak mentions and relations, track_provenance switches
+    the mention lists off, options may sit under options.resolver."""
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+
+    class Fake:
+        def recognize(self, texts, labels, threshold=None):
+            E = G.GlinerEntity
+            return [[E("Ada Lovelace", "person", 0, 12, 0.9), E("London", "city", 20, 26, 0.4)]][: len(texts)]
+
+        def extract_relations(self, texts, ents, rels):
+            e = self.recognize(texts, ents)
+            return e, [[G.GlinerRelation(e[0][0], e[0][1], "lives in", 0.3)]][: len(texts)]
+
+        def classify(self, *a, **k):
+            return []
+
+    mgr = ModelManager(models_dir="/nonexistent", device="cpu")
+    mgr.register("fake", "recognizer", Fake(), None)
+    c = TestClient(create_app(mgr))
+    body = {"model": "fake", "inputs": [{"content": "Ada Lovelace lived in London"}],
+            "schema": {"entities": ["person", "city"], "relations": [{"type": "lives in"}]}}
+    kg = c.post("/ai/v1/extract", json={**body, "options": {"resolve": True, "track_provenance": False}}
+                ).json()["knowledge_graph"]
+    assert len(kg["entities"]) == 2 and kg["entities"][0]["mentions"] is None and len(kg["relations"]) == 1
+    kg = c.post("/ai/v1/extract", json={**body, "options": {"resolve": True, "resolver": {"min_entity_confidence": 0.5}}}
+                ).json()["knowledge_graph"]
+    assert [e["name"] for e in kg["entities"]] == ["Ada Lovelace"] and kg["relations"] == []   # London fell out
+    kg = c.post("/ai/v1/extract", json={**body, "options": {"resolve": True, "min_relation_confidence": 0.5}}
+                ).json()["knowledge_graph"]
+    assert len(kg["entities"]) == 2 and kg["relations"] == []
