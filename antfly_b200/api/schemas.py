@@ -206,6 +206,25 @@ class TableQueryRequest(BaseModel):
     fields: Optional[List[str]] = None
 
 
+class ClassifyRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    texts: List[str]
+    labels: List[str] = Field(default_factory=list)
+    hypothesis_template: Optional[str] = None
+    multi_label: bool = False
+
+
+class RecognizeRequest(BaseModel):
+    model_config = ConfigDict(extra="allow")
+    model: str
+    texts: List[str]
+    labels: List[str] = Field(default_factory=list)
+    relation_labels: List[str] = Field(default_factory=list)
+    threshold: Optional[float] = None
+    resolver: Optional[Dict[str, Any]] = None
+
+
 class RewriteRequest(BaseModel):
     model_config = ConfigDict(extra="allow")
     model: str

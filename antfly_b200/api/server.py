@@ -752,6 +752,113 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "search", 1, work)
 
+    # ---- classify / recognize: the per-task forms of what /extract answers by schema ---------------------------
+    async def classify(request: Request):
+        """``ClassifyRequest`` -> ``ClassifyResponse`` (specs/openapi/inference/api.yaml ClassifyRequest: texts, candidate
+        labels for zero-shot models, hypothesis_template, multi_label; the handler the reference keeps as
+        ``classifyText``, zig/pkg/inference/src/server/server.zig:3502)."""
+        req, bad = await parse(request, S.ClassifyRequest)
+        if bad:
+            return bad
+        if not req.texts:
+            return _err(400, "invalid_request", "texts must not be empty")
+
+        def work():
+            lm = mgr.get(req.model, "classifier")
+            pipe = lm.pipeline
+            if hasattr(pipe, "template"):                          # NLI cross-encoder: labels come from the request
+                if not req.labels:
+                    raise ValueError("this model classifies against candidate labels: labels must not be empty")
+                if req.hypothesis_template is not None and "{}" not in req.hypothesis_template:
+                    raise ValueError("hypothesis_template needs a {} placeholder")
+                keep, pipe.template = pipe.template, req.hypothesis_template or pipe.template
+                try:
+                    ranked = pipe.classify(req.texts, req.labels, multi_label=req.multi_label)
+                finally:
+                    pipe.template = keep
+            elif hasattr(pipe, "recognize"):                       # zero-shot span model used as a classifier
+                if not req.labels:
+                    raise ValueError("this model classifies against candidate labels: labels must not be empty")
+                ranked = [[{"label": l, "score": float(sc)} for l, sc in
+                           pipe.classify(t, req.labels, threshold=0.0, multi_label=req.multi_label)] for t in req.texts]
+            else:                                                  # trained head: its own label set
+                ranked = pipe.classify(req.texts, top_k=max(len(getattr(pipe, "id2label", {})), 1))
+                if req.labels:
+                    want = {l.lower() for l in req.labels}
+                    ranked = [[r for r in row if r["label"].lower() in want] for row in ranked]
+            n_tok = sum(len(t.split()) for t in req.texts)
+            return {"object": "list", "model": req.model,
+                    "data": [{"object": "classification", "index": i, "classifications": row}
+                             for i, row in enumerate(ranked)],
+                    "usage": {"prompt_tokens": n_tok, "completion_tokens": 0, "total_tokens": n_tok}}
+
+        return await asyncio.to_thread(run_guarded, "classify", max(1, len(req.texts)), work)
+
+    async def recognize(request: Request):
+        """``RecognizeRequest`` -> ``RecognizeResponse``: entities per text (character offsets), relations when
+        ``relation_labels`` are given and the model extracts them, and one resolved graph over all texts when a
+        ``resolver`` section is present (specs/openapi/inference/api.yaml RecognizeRequest / ResolverConfig; the
+        reference's ``recognizeEntities``, zig/pkg/inference/src/server/server.zig:3220)."""
+        req, bad = await parse(request, S.RecognizeRequest)
+        if bad:
+            return bad
+        if not req.texts:
+            return _err(400, "invalid_request", "texts must not be empty")
+
+        def work():
+            lm = mgr.get(req.model, "recognizer")
+            pipe = lm.pipeline
+
+            def span(e, text):
+                if hasattr(e, "start") and not hasattr(e, "start_token"):      # byte offsets -> character offsets
+                    raw = text.encode("utf-8")
+                    a = len(raw[: e.start].decode("utf-8", "replace"))
+                    return {"text": e.text, "label": e.label, "start": a, "end": a + len(e.text), "score": float(e.score)}
+                t = e.text or ""
+                at = text.find(t) if t else -1
+                if at < 0 and t:
+                    at = text.lower().find(t.lower())
+                return {"text": t, "label": e.label, "start": max(at, 0), "end": max(at, 0) + len(t),
+                        "score": float(e.score)}
+
+            rels = None
+            if hasattr(pipe, "recognize"):
+                if req.relation_labels and hasattr(pipe, "extract_relations"):
+                    ents, rels = pipe.extract_relations(req.texts, req.labels or None, req.relation_labels)
+                else:
+                    ents = pipe.recognize(req.texts, req.labels or None, threshold=req.threshold)
+            elif hasattr(pipe, "entities"):
+                ents = pipe.entities(req.texts)
+                if req.labels:
+                    want = {l.lower() for l in req.labels}
+                    ents = [[e for e in row if e.label.lower() in want] for row in ents]
+            else:
+                raise ValueError(f"model {req.model!r} does not recognise entities")
+            data = []
+            for i, (text, row) in enumerate(zip(req.texts, ents)):
+                rec = {"object": "recognition", "index": i, "entities": [span(e, text) for e in row]}
+                if rels is not None:
+                    rec["relations"] = [{"head": span(r.head, text), "tail": span(r.tail, text), "label": r.label,
+                                         "score": float(r.score)} for r in rels[i]]
+                data.append(rec)
+            n_tok = sum(len(t.split()) for t in req.texts)
+            out = {"object": "list", "model": req.model, "data": data,
+                   "usage": {"prompt_tokens": n_tok, "completion_tokens": 0, "total_tokens": n_tok}}
+            if req.resolver is not None:
+                from ..pipelines.resolver import ResolverConfig, build_knowledge_graph
+
+                cfg = ResolverConfig(**{k: type(getattr(ResolverConfig, k))(v) for k, v in req.resolver.items()
+                                        if k in ResolverConfig.__dataclass_fields__})
+                kg = build_knowledge_graph(ents, rels, cfg)
+                out["knowledge_graph"] = {
+                    "entities": [{"id": e.id, "name": e.canonical_name, "label": e.label, "score": e.score,
+                                  "mentions": e.mentions, "inputs": e.text_indices} for e in kg.entities],
+                    "relations": [{"source": r.head_id, "target": r.tail_id, "type": r.label, "score": r.score,
+                                   "inputs": r.text_indices} for r in kg.relations]}
+            return out
+
+        return await asyncio.to_thread(run_guarded, "recognize", max(1, len(req.texts)), work)
+
     # ---- rewrite (encoder-decoder text-to-text) and schema-driven extraction -------------------------------------
     async def rewrite(request: Request):
         req, bad = await parse(request, S.RewriteRequest)
@@ -1223,6 +1330,8 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/anthropic/v1/messages", anthropic_messages, methods=["POST"])
     app.add_api_route("/ai/v1/chunk", chunk_ep, methods=["POST"])
     app.add_api_route("/ai/v1/rewrite", rewrite, methods=["POST"])
+    app.add_api_route("/ai/v1/classify", classify, methods=["POST"])
+    app.add_api_route("/ai/v1/recognize", recognize, methods=["POST"])
     app.add_api_route("/ai/v1/extract", extract, methods=["POST"])
     app.add_api_route("/ai/v1/transcribe", transcribe, methods=["POST"])
     app.add_api_route("/ai/v1/read", read, methods=["POST"])

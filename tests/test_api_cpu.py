@@ -589,3 +589,59 @@ def test_generate_with_draft_model_and_cache_dtype_per_request():
     assert c.post("/ai/v1/chat/completions", json=dict(base, draft_model="nope")).status_code == 404
     assert c.post("/ai/v1/chat/completions", json=dict(base, draft_model="target")).status_code == 400
     assert c.post("/ai/v1/chat/completions", json=dict(base, cache_dtype="int3")).status_code in (400, 422)
+
+
+def test_classify_and_recognize_endpoints(tmp_path):
+    """/ai/v1/classify over a trained head (its own labels, optionally restricted) and /ai/v1/recognize over a token
+    classifier and over a zero-shot span model with relations and a resolver section."""
+    from antfly_b200.pipelines import gliner as G
+
+    _write_bert(tmp_path / "classifiers" / "clf", 3, ["negative", "neutral", "positive"], 2)
+    _write_bert(tmp_path / "recognizers" / "ner", 3, ["O", "B-PER", "I-PER"], 1)
+    mgr = ModelManager(models_dir=str(tmp_path), device="cpu")
+
+    class Fake:
+        def recognize(self, texts, labels, threshold=None):
+            E = G.GlinerEntity
+            return [[E("Zoë", "person", 0, 4, 0.9), E("Paris", "city", 14, 19, 0.8)], [E("zoë", "person", 0, 4, 0.7)]][: len(texts)]
+
+        def extract_relations(self, texts, ents, rels):
+            e = self.recognize(texts, ents)
+            return e, [[G.GlinerRelation(e[0][0], e[0][1], rels[0], 0.6)], []][: len(texts)]
+
+        def classify(self, text, labels, threshold=0.0, multi_label=False):
+            return [(labels[0], 0.75)] + [(l, 0.1) for l in labels[1:]]
+
+    mgr.register("span", "recognizer", Fake(), None)
+    mgr.register("span", "classifier", Fake(), None)
+    c = TestClient(create_app(mgr))
+    r = c.post("/ai/v1/classify", json={"model": "clf", "texts": ["good", "bad"]})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["object"] == "list" and [d["index"] for d in body["data"]] == [0, 1]
+    row = body["data"][0]["classifications"]
+    assert body["data"][0]["object"] == "classification" and {x["label"] for x in row} == {"negative", "neutral", "positive"}
+    assert abs(sum(x["score"] for x in row) - 1.0) < 1e-3 and row[0]["score"] >= row[1]["score"]
+    r = c.post("/ai/v1/classify", json={"model": "clf", "texts": ["good"], "labels": ["positive"]})
+    assert [x["label"] for x in r.json()["data"][0]["classifications"]] == ["positive"]
+    r = c.post("/ai/v1/classify", json={"model": "span", "texts": ["good"], "labels": ["a", "b"]})
+    assert r.json()["data"][0]["classifications"][0] == {"label": "a", "score": 0.75}
+    assert c.post("/ai/v1/classify", json={"model": "span", "texts": ["good"]}).status_code == 400
+    assert c.post("/ai/v1/classify", json={"model": "clf", "texts": []}).status_code == 400
+    r = c.post("/ai/v1/recognize", json={"model": "ner", "texts": ["alice went home"]})
+    assert r.status_code == 200 and r.json()["data"][0]["object"] == "recognition" and "entities" in r.json()["data"][0]
+    r = c.post("/ai/v1/recognize", json={"model": "span", "texts": ["Zoë lives in Paris", "zoë again"],
+                                         "labels": ["person", "city"], "relation_labels": ["lives_in"],
+                                         "resolver": {"similarity_threshold": 0.8}})
+    assert r.status_code == 200, r.text
+    out = r.json()
+    e0 = out["data"][0]["entities"]
+    assert e0[0] == {"text": "Zoë", "label": "person", "start": 0, "end": 3, "score": 0.9}       # characters, not bytes
+    assert e0[1]["start"] == 13 and e0[1]["end"] == 18
+    rel = out["data"][0]["relations"][0]
+    assert rel["label"] == "lives_in" and rel["head"]["text"] == "Zoë" and rel["tail"]["text"] == "Paris"
+    assert out["data"][1]["relations"] == []
+    kg = out["knowledge_graph"]
+    assert [e["name"] for e in kg["entities"]] == ["Zoë", "Paris"] and kg["entities"][0]["inputs"] == [0, 1]
+    assert kg["relations"][0]["type"] == "lives_in"
+    assert "knowledge_graph" not in c.post("/ai/v1/recognize", json={"model": "span", "texts": ["x"]}).json()
