@@ -889,7 +889,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         def work():
             lm = mgr.get(req.model, "transcriber")
-            out = lm.pipeline.transcribe(audio, language=req.language, task=req.task, max_new_tokens=req.max_tokens)
+            vad = (req.model_extra or {}).get("vad")           # {"vad": {...}}: decode the speech segments only
+            out = lm.pipeline.transcribe(audio, language=req.language, task=req.task, max_new_tokens=req.max_tokens,
+                                         **({"vad": dict(vad)} if isinstance(vad, dict) else {}))
             metrics.tokens.labels("transcribe", "completion").inc(out.completion_tokens)
             return {"object": "list", "model": req.model,
                     "data": [{"object": "transcription", "index": 0, "text": out.text,

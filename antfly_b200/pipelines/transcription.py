@@ -68,7 +68,10 @@ class Transcriber:
 
     def transcribe(self, audio: Union[bytes, str, torch.Tensor], sample_rate: Optional[int] = None,
                    language: Optional[str] = None, task: str = "transcribe",
-                   max_new_tokens: int = 224) -> Transcription:
+                   max_new_tokens: int = 224, vad: Optional[dict] = None) -> Transcription:
+        """``vad`` (voice-activity options, possibly empty): only the speech segments are decoded -- silence costs
+        nothing and cannot be hallucinated over -- each as a window of its own (segments are cut at the model's
+        30 s window by the segmenter)."""
         t0 = time.perf_counter()
         if isinstance(audio, torch.Tensor):
             wav, rate = audio.float().flatten(), sample_rate or AO.SAMPLE_RATE
@@ -83,14 +86,25 @@ class Transcriber:
         prompt = self.prompt(language, task)
         suppress = [int(t) for t in (self.gen.get("suppress_tokens") or []) if 0 <= int(t) < self.model.cfg.vocab_size]
         segments, n_prompt, n_out = [], 0, 0
-        for i in range(0, max(wav.numel(), 1), self.chunk):
-            piece = wav[i:i + self.chunk]
+        if vad is not None:
+            from .chunking import VAD_DEFAULTS, VAD_FRAME, merge_vad_frames, vad_frame_probs
+
+            cfg = dict(VAD_DEFAULTS)
+            cfg.update({k: v for k, v in vad.items() if k in cfg and v})
+            cfg["max_segment_duration_ms"] = min(int(cfg["max_segment_duration_ms"]), self.chunk * 1000 // AO.SAMPLE_RATE)
+            spans = merge_vad_frames(vad_frame_probs(wav.cpu().numpy()), VAD_FRAME, AO.SAMPLE_RATE,
+                                     float(cfg["threshold"]), int(cfg["min_silence_duration_ms"]),
+                                     int(cfg["min_speech_duration_ms"]), int(cfg["speech_pad_ms"]),
+                                     int(cfg["max_segment_duration_ms"]))
+        else:
+            spans = [(i, min(i + self.chunk, wav.numel())) for i in range(0, max(wav.numel(), 1), self.chunk)]
+        for i, j in spans:
+            piece = wav[i:j]
             mel = AO.log_mel(piece.to(self.model.device), self.model.cfg.num_mel_bins,
                              n_samples=self.frames * 160)
             ids = self.model.transcribe_ids(mel, prompt, max_new_tokens, suppress)
             text = self.tokenizer.decode(ids).strip() if self.tokenizer is not None else ""
-            segments.append({"start": i / AO.SAMPLE_RATE, "end": min(i + self.chunk, wav.numel()) / AO.SAMPLE_RATE,
-                             "text": text, "tokens": ids})
+            segments.append({"start": i / AO.SAMPLE_RATE, "end": j / AO.SAMPLE_RATE, "text": text, "tokens": ids})
             n_prompt += len(prompt)
             n_out += len(ids)
         t2 = time.perf_counter()

@@ -126,3 +126,33 @@ def test_transcription_pipeline_and_endpoint(tmp_path):
     r = c.post("/ai/v1/transcribe", json={"model": "tiny-whisper", "max_tokens": 4,
                                           "audio": base64.b64encode(_wav_bytes(x, 8000)).decode()})
     assert r.json()["data"][0]["language"] == want
+
+
+def test_transcription_with_voice_activity_segments(tmp_path):
+    """With vad options only the speech spans are decoded: two bursts separated by silence give two segments at the
+    bursts' times; a silent recording gives none; the endpoint takes the same section."""
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+
+    _write_whisper(tmp_path / "transcribers" / "tiny-whisper")
+    mgr = ModelManager(models_dir=str(tmp_path), device="cpu")
+    pipe = mgr.get("tiny-whisper", "transcriber").pipeline
+    rate = 16000
+    t = torch.arange(rate * 4) / rate
+    x = 0.002 * torch.randn(rate * 4, generator=torch.Generator().manual_seed(0))
+    for a, b in ((0.5, 1.2), (2.5, 3.3)):
+        m = (t >= a) & (t < b)
+        x[m] += 0.4 * torch.sin(2 * math.pi * 220 * t[m])
+    out = pipe.transcribe(_wav_bytes(x, rate), language="en", max_new_tokens=4, vad={})
+    assert len(out.segments) == 2
+    assert abs(out.segments[0]["start"] - 0.5) < 0.1 and abs(out.segments[0]["end"] - 1.2) < 0.1
+    assert abs(out.segments[1]["start"] - 2.5) < 0.1 and abs(out.segments[1]["end"] - 3.3) < 0.1
+    plain = pipe.transcribe(_wav_bytes(x, rate), language="en", max_new_tokens=4)
+    assert len(plain.segments) == 1 and plain.segments[0]["end"] == 4.0   # without it: one window over everything
+    quiet = pipe.transcribe(_wav_bytes(0.001 * torch.randn(rate * 2), rate), language="en", vad={})
+    assert quiet.segments == [] and quiet.text == "" and quiet.completion_tokens == 0
+    c = TestClient(create_app(mgr))
+    r = c.post("/ai/v1/transcribe", json={"model": "tiny-whisper", "language": "en", "max_tokens": 4,
+                                          "audio": base64.b64encode(_wav_bytes(x, rate)).decode(),
+                                          "vad": {"min_silence_duration_ms": 200}})
+    assert r.status_code == 200 and len(r.json()["data"][0]["segments"]) == 2
