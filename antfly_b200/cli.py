@@ -350,7 +350,8 @@ def cmd_quantize(args) -> int:
 
 
 def cmd_export(args) -> int:
-    """Export a Llama-family safetensors checkpoint directory as one GGUF file (f32 / f16 / q8_0 / q4_0)."""
+    """Export a Llama-family safetensors checkpoint directory as one GGUF file (f32 / f16, the 32-value block types
+    q4_0 .. q8_1 and the K-quants q2_k .. q6_k, q8_k; rows that are not a whole number of blocks stay f16)."""
     import os
 
     from .formats import gguf as GG
@@ -358,8 +359,12 @@ def cmd_export(args) -> int:
     from .formats import safetensors_io as ST
 
     mf = MF.read_manifest(args.inp)
-    counts = GG.export_llama_gguf(args.out, ST.load_model_dir(args.inp), mf.config, args.quant)
-    print(json.dumps({"out": args.out, "bytes": os.path.getsize(args.out), "tensor_types": counts}))
+    split = lambda v: [p.strip() for p in (v or "").split(",") if p.strip()] or None
+    counts = GG.export_llama_gguf(args.out, ST.load_model_dir(args.inp), mf.config, args.quant,
+                                  include=split(args.quantize_include), exclude=split(args.quantize_exclude),
+                                  dry_run=args.dry_run)
+    print(json.dumps({"out": args.out, "bytes": None if args.dry_run else os.path.getsize(args.out),
+                      "tensor_types": counts, "dry_run": args.dry_run}))
     return 0
 
 
@@ -577,7 +582,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--max-queue-size", type=int); p.set_defaults(fn=cmd_run)
     p = sub.add_parser("export", help="safetensors checkpoint directory -> GGUF")
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out", required=True)
-    p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "q8_0", "q4_0", "i2_s"]); p.set_defaults(fn=cmd_export)
+    p.add_argument("--quant", default="q8_0", choices=["f32", "f16", "i2_s", "q4_0", "q4_1", "q5_0", "q5_1", "q8_0",
+                                                        "q8_1", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "q8_k"])
+    p.add_argument("--quantize-include", help="comma-separated tensor-name prefixes: quantise only these")
+    p.add_argument("--quantize-exclude", help="comma-separated tensor-name prefixes: leave these in f16")
+    p.add_argument("--dry-run", action="store_true", help="report the tensor types without writing the file")
+    p.set_defaults(fn=cmd_export)
     p = sub.add_parser("compile-artifact", help="pack a checkpoint into the kernels' layout for fast loading")
     p.add_argument("--in", dest="inp", required=True); p.add_argument("--out"); p.add_argument("--device")
     p.set_defaults(fn=cmd_compile_artifact)

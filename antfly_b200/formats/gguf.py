@@ -289,13 +289,17 @@ def split_expert_tensors(sd: Dict[str, torch.Tensor], n_experts: int) -> Dict[st
 
 
 def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quant: str = "q8_0",
-                      tokens: Optional[List[str]] = None, extra_metadata: Optional[Dict[str, Any]] = None
-                      ) -> Dict[str, int]:
+                      tokens: Optional[List[str]] = None, extra_metadata: Optional[Dict[str, Any]] = None,
+                      include: Optional[List[str]] = None, exclude: Optional[List[str]] = None,
+                      dry_run: bool = False) -> Dict[str, int]:
     """Write a Llama-family Hugging Face state dict as a GGUF v3 file: 2-D projection weights in ``quant`` (f32,
     f16, q8_0, q4_0), norms and embeddings in f32 / f16; metadata keys are the ones :func:`llama_config_from_gguf`
-    reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  Returns
-    {tensor type id: count}."""
-    ty = {"f32": 0, "f16": 1, "q4_0": 2, "q8_0": 8, "i2_s": 36}[quant.lower()]   # i2_s: BitNet ternary projections
+    reads back; Q / K rows of the :data:`PAIRED_ROPE_ARCHS` in the stored order of those files.  ``include`` /
+    ``exclude`` are prefixes of (Hugging Face) tensor names that restrict which eligible tensors are quantised (the
+    others stay f16); ``dry_run`` plans without writing (the reference's --quantize-include / --quantize-exclude /
+    --dry-run, zig/pkg/inference/src/native_export_gguf.zig:4814).  Returns {tensor type id: count}."""
+    ty = {"f32": 0, "f16": 1, "i2_s": 36, **QUANT_NAMES}[quant.lower()]           # i2_s: BitNet ternary projections
+    block = 256 if ty in (10, 11, 12, 13, 14, 15) else 32
     arch = {"mixtral": "llama", "qwen2_moe": "qwen2moe", "qwen3_moe": "qwen3moe", "gemma3_text": "gemma3"}.get(
         config.get("model_type", "llama"), config.get("model_type", "llama"))
     n_exp = int(config.get("num_local_experts") or config.get("num_experts") or 0)
@@ -374,14 +378,19 @@ def export_llama_gguf(path: str, sd: Dict[str, torch.Tensor], config: dict, quan
                 t = pair_rope_rows(t, nkv)
         if arch in GEMMA_ARCHS and name.endswith("norm.weight"):
             t = t.float() + 1.0      # converted Gemma files hold 1 + gamma (the loader takes the 1 off again)
-        quantisable = t.dim() in (2, 3) and t.shape[-1] % 32 == 0 and "embed_tokens" not in name and \
+        quantisable = t.dim() in (2, 3) and t.shape[-1] % block == 0 and "embed_tokens" not in name and \
             "norm" not in name and "ffn_gate_inp" not in name
         if ty == 36:      # ternary only where the model is ternary (the projections), whole 128-value blocks
             quantisable = quantisable and name.endswith("_proj.weight") and t.numel() % 128 == 0
+        if include and not any(name.startswith(pre) for pre in include):
+            quantisable = False
+        if exclude and any(name.startswith(pre) for pre in exclude):
+            quantisable = False
         tt = ty if quantisable else (1 if t.dim() == 2 and ty != 0 and "ffn_gate_inp" not in name else 0)
         tensors[gguf_name(name, arch)] = (tt, t.float())
         counts[tt] = counts.get(tt, 0) + 1
-    write_gguf(path, md, tensors)
+    if not dry_run:
+        write_gguf(path, md, tensors)
     return counts
 
 
@@ -464,6 +473,32 @@ def pack_i2s(values: np.ndarray) -> bytes:
     return packed.astype(np.uint8).tobytes() + struct.pack("<f", scale) + b"\0" * 28
 
 
+# tensor types the export tool can write besides F32 / F16 (ggml numbering): Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q8_1 and the
+# K-quants Q2_K .. Q6_K, Q8_K
+QUANTIZABLE = (2, 3, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15)
+QUANT_NAMES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q8_1": 9, "q2_k": 10, "q3_k": 11, "q4_k": 12,
+               "q5_k": 13, "q6_k": 14, "q8_k": 15}
+
+
+def quantize(values: np.ndarray, type_id: int) -> np.ndarray:
+    """fp32 values (a whole number of blocks of the type) -> the type's block bytes (csrc/host/gguf_quantize.cpp)."""
+    lib = N.host()
+    lib.afb_gguf_block_bytes.restype = ctypes.c_long
+    lib.afb_gguf_block_values.restype = ctypes.c_long
+    a = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+    bv, bb = int(lib.afb_gguf_block_values(type_id)), int(lib.afb_gguf_block_bytes(type_id))
+    if type_id not in QUANTIZABLE or bv <= 0:
+        raise NotImplementedError(f"no quantiser for GGUF tensor type {type_id}")
+    if a.size % bv:
+        raise ValueError(f"{a.size} values are not a whole number of {bv}-value blocks")
+    out = np.empty(a.size // bv * bb, dtype=np.uint8)
+    rc = lib.afb_gguf_quantize(ctypes.c_int(type_id), a.ctypes.data_as(ctypes.c_void_p),
+                               out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(a.size))
+    if rc != 0:
+        raise RuntimeError(f"GGUF quantiser failed for type {type_id} (code {rc})")
+    return out
+
+
 def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[int, torch.Tensor]]) -> None:
     """tensors: name -> (type id, fp32 tensor); quantises with the C++ codecs (F32, F16, Q8_0, Q4_0)."""
     lib = N.host()
@@ -494,12 +529,8 @@ def write_gguf(path: str, metadata: Dict[str, Any], tensors: Dict[str, Tuple[int
             raw = a.tobytes()
         elif ty == 1:
             raw = a.astype(np.float16).tobytes()
-        elif ty in (8, 2):
-            bb = 34 if ty == 8 else 18
-            out = np.empty(a.size // 32 * bb, dtype=np.uint8)
-            fn = lib.afb_gguf_quantize_q8_0 if ty == 8 else lib.afb_gguf_quantize_q4_0
-            fn(a.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(a.size))
-            raw = out.tobytes()
+        elif ty in QUANTIZABLE:
+            raw = quantize(a, ty).tobytes()
         elif ty == 36:
             raw = pack_i2s(a)
         else:

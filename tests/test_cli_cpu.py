@@ -63,6 +63,13 @@ def test_cli_export_gguf_roundtrip_and_task_commands(capsys, tmp_path):
         tol = 0.02 * float(t.abs().max()) if t.dim() == 2 else 0.0
         assert float((back[n] - t).abs().max()) <= tol + 1e-3, n
 
+    # planning only, with filters: attention projections quantised, everything else left in f16
+    plan = tmp_path / "plan.gguf"
+    assert main(["export", "--in", str(src), "--out", str(plan), "--quant", "q5_1", "--dry-run", "--quantize-include",
+                 "model.layers.", "--quantize-exclude", "model.layers.0.mlp.,model.layers.1.mlp."]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["dry_run"] and rep["bytes"] is None and not plan.exists()
+    assert rep["tensor_types"] == {"7": 4 * L, "1": 3 * L + 2, "0": 5}
     _write_bert(tmp_path / "classifiers" / "clf", 3, ["negative", "neutral", "positive"], 2)
     _write_bert(tmp_path / "recognizers" / "ner", 3, ["O", "B-PER", "I-PER"], 1)
     _write_bert(tmp_path / "embedders" / "emb", 0, [], 3)

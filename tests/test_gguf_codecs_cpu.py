@@ -545,3 +545,82 @@ def test_mixture_of_experts_gguf_round_trip(tmp_path, kind):
     got = model.forward(b, kc, torch.zeros_like(kc)).float()
     cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
     assert float(cos.min()) > 0.98, (kind, cos)
+
+
+_QUANT_BOUNDS = {"q4_0": 0.12, "q4_1": 0.09, "q5_0": 0.06, "q5_1": 0.045, "q8_0": 0.008, "q8_1": 0.008, "q2_k": 0.40,
+                 "q3_k": 0.20, "q4_k": 0.09, "q5_k": 0.045, "q6_k": 0.025, "q8_k": 0.012}
+
+
+@pytest.mark.parametrize("name", sorted(_QUANT_BOUNDS))
+def test_block_quantisers_round_trip_within_their_precision(name):
+    """Every exported block type: the bytes decode identically through this package's decoder and the gguf
+    package's (where it has one), the error against the source is within the type's precision, a block of zeros
+    and a block of one repeated value survive, and a second quantisation of the decoded values is a fixed point for
+    the symmetric 8-bit types."""
+    import ctypes
+
+    from antfly_b200 import _native as N
+    from antfly_b200.formats import gguf as GG
+
+    ty = GG.QUANT_NAMES[name]
+    rng = np.random.default_rng(ty)
+    x = (rng.standard_normal(256 * 24) * 0.7).astype(np.float32)
+    x[:256] = 0.0
+    x[256:512] = 0.375
+    raw = GG.quantize(x, ty)
+    lib = N.host()
+    lib.afb_gguf_block_bytes.restype = ctypes.c_long
+    assert raw.size == x.size // int(lib.afb_gguf_block_values(ty)) * int(lib.afb_gguf_block_bytes(ty))
+    back = np.empty_like(x)
+    assert lib.afb_gguf_dequantize(ctypes.c_int(ty), raw.ctypes.data_as(ctypes.c_void_p),
+                                   back.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(x.size)) == 0
+    tname = name.upper()
+    if tname not in ("Q8_1", "Q8_K"):
+        ref = gguf.quants.dequantize(raw, getattr(gguf.GGMLQuantizationType, tname)).reshape(-1)
+        np.testing.assert_array_equal(ref, back)
+    body = slice(512, None)
+    err = np.sqrt(((back[body] - x[body]) ** 2).mean()) / np.sqrt((x[body] ** 2).mean())
+    assert err < _QUANT_BOUNDS[name], (name, err)
+    assert np.all(back[:256] == 0.0)
+    assert np.abs(back[256:512] - 0.375).max() < (0.2 if name in ("q2_k", "q3_k") else 0.02)
+    with pytest.raises(ValueError):
+        GG.quantize(x[:100], ty)
+    with pytest.raises(NotImplementedError):
+        GG.quantize(x, 16)
+
+
+def test_k_quant_export_is_served_from_its_blocks(tmp_path):
+    """export --quant q6_k / q4_k on a checkpoint whose rows are whole super-blocks; the native GGUF path serves the
+    file from those bytes and agrees with transformers."""
+    import torch
+
+    transformers = pytest.importorskip("transformers")
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.formats import gguf as GG
+    from antfly_b200.models.llama import StepBatch
+    from antfly_b200.ops.gguf_ops import GgufWeight
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.LlamaConfig(vocab_size=320, hidden_size=256, intermediate_size=512, num_hidden_layers=1,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                      tie_word_embeddings=False)
+    hf = transformers.LlamaForCausalLM(hf_cfg).eval().float()
+    ids = torch.randint(0, 320, (10,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    for quant, ty, floor in (("q6_k", 14, 0.995), ("q4_k", 12, 0.97)):
+        d = tmp_path / "generators" / quant
+        d.mkdir(parents=True)
+        counts = GG.export_llama_gguf(str(d / "model.gguf"), hf.state_dict(), hf_cfg.to_dict(), quant=quant)
+        assert counts[ty] == 8                                  # seven projections and the output matrix
+        lm = ModelManager(models_dir=str(tmp_path), device="cpu", gguf_native=True).get(quant, "generator")
+        model = lm.pipeline.engine.model
+        assert isinstance(model.w["l0.qkv"], GgufWeight) and model.w["l0.qkv"].segments[0][1] == ty
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32)
+        pos = torch.arange(10, dtype=torch.int32)
+        kc = torch.zeros((1, 2, 16, 2, 64), dtype=torch.bfloat16)
+        b = StepBatch(ids.int(), pos, pos.clone(), i32([0]), i32([10]), i32([10]), torch.arange(2, dtype=torch.int32)[None],
+                      pos.clone(), 10, 1)
+        got = model.forward(b, kc, torch.zeros_like(kc)).float()
+        cos = torch.nn.functional.cosine_similarity(got, want, dim=-1)
+        assert float(cos.min()) > floor, (quant, cos)
