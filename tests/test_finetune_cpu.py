@@ -334,3 +334,11 @@ def test_smoke_fast_runs_every_recipe_on_synthetic_checkpoints(tmp_path, capsys)
     assert summary["ok"] and set(summary["cases"]) == set(R.RECIPES)
     assert all(c["manifest_status"] == "succeeded" for c in summary["cases"].values())
     assert os.path.exists(tmp_path / "smoke" / "fast_smoke_summary.json")
+
+
+def test_bf16_base_weights_with_activation_checkpointing(tmp_path):
+    _tiny_llama(str(tmp_path / "m"))
+    rec = _sft_recipe(tmp_path, "qlora-sft", model={"dtype": "bf16"},
+                      optimizer={"epochs": 5, "gradient_checkpointing": True, "neftune_alpha": 1.0})
+    rep = R.run_recipe(rec)
+    assert rep["status"] == "succeeded" and rep["train"]["final_loss"] < 0.7 * rep["train"]["first_loss"]
