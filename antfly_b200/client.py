@@ -1,6 +1,6 @@
 """Minimal HTTP client for the inference API (what the reference ships as its Python SDK's inference part,
-py/packages/sdk): embeddings, rerank, generate / chat with optional streaming, rewrite, extract, transcribe, and
-the hybrid table calls.  Depends only on ``requests``."""
+py/packages/sdk): embeddings, rerank, generate / chat with optional streaming, rewrite, extract, classify,
+recognize, chunk, read, transcribe, and the hybrid table calls.  Depends only on ``requests``."""
 from __future__ import annotations
 
 import base64
@@ -105,6 +105,36 @@ class Client:
         if language:
             body["language"] = language
         return self._post("/ai/v1/transcribe", body)["data"][0]["text"]
+
+    def chunk(self, text_or_bytes: Union[str, bytes], mime_type: Optional[str] = None,
+              config: Optional[Dict[str, Any]] = None) -> List[Dict[str, Any]]:
+        """Chunks of a text, or of a media payload (WAV audio in windows or voice-activity segments, GIF frames)."""
+        part: Any = text_or_bytes
+        if isinstance(text_or_bytes, (bytes, bytearray)):
+            part = {"type": "media", "mime_type": mime_type or "application/octet-stream",
+                    "data": base64.b64encode(bytes(text_or_bytes)).decode()}
+        body: Dict[str, Any] = {"input": part}
+        if config:
+            body["config"] = config
+        data = self._post("/ai/v1/chunk", body)["data"]
+        return data[0]["chunks"] if data and isinstance(data[0], dict) and "chunks" in data[0] else data
+
+    def classify(self, model: str, texts: Sequence[str], labels: Sequence[str] = (), **options) -> List[List[Dict[str, Any]]]:
+        body = {"model": model, "texts": list(texts), "labels": list(labels), **options}
+        data = self._post("/ai/v1/classify", body)["data"]
+        return [d["classifications"] for d in sorted(data, key=lambda d: d["index"])]
+
+    def recognize(self, model: str, texts: Sequence[str], labels: Sequence[str] = (),
+                  relation_labels: Sequence[str] = (), resolver: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+        body: Dict[str, Any] = {"model": model, "texts": list(texts), "labels": list(labels),
+                                "relation_labels": list(relation_labels)}
+        if resolver is not None:
+            body["resolver"] = resolver
+        return self._post("/ai/v1/recognize", body)
+
+    def read(self, model: str, images: Sequence[bytes], mime_type: str = "image/png", **options) -> Dict[str, Any]:
+        urls = [{"url": f"data:{mime_type};base64," + base64.b64encode(b).decode()} for b in images]
+        return self._post("/ai/v1/read", {"model": model, "images": urls, **options})
 
     # -- tables --------------------------------------------------------------------------------------------
     def create_table(self, name: str, **spec) -> Dict[str, Any]:

@@ -82,6 +82,22 @@ def test_embed_rerank_generate_over_http(server):
     assert json.loads(lines[0][6:])["object"].startswith("chat.completion")
 
 
+def test_client_library_against_the_running_server(server):
+    from antfly_b200.client import ApiError, Client
+
+    c = Client(server)
+    c.wait_ready(10)
+    assert len(c.embed("random:tiny", ["a", "b"], dimensions=8)[1]) == 8
+    assert len(c.rerank("random:tiny", "q", ["x", "yy"])) == 2
+    assert isinstance(c.generate("random:tiny", "hi", max_tokens=3), str)
+    assert "".join(c.stream("random:tiny", [{"role": "user", "content": "hi"}], max_tokens=3)) is not None
+    chunks = c.chunk("One sentence here. " * 40, config={"text": {"target_tokens": 20, "overlap_tokens": 2}})
+    assert len(chunks) > 1 and chunks[0]["mime_type"] == "text/plain"
+    with pytest.raises(ApiError) as e:
+        c.classify("nobody", ["x"], ["a"])
+    assert e.value.status == 404
+
+
 def test_models_metrics_and_errors_over_http(server):
     with urllib.request.urlopen(server + "/ai/v1/models", timeout=10) as r:
         models = json.loads(r.read())
