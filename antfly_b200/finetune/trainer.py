@@ -16,7 +16,7 @@ import os
 import time
 from contextlib import contextmanager
 from dataclasses import asdict, dataclass
-from typing import Callable, Dict, Iterable, List, Optional, Tuple
+from typing import Callable, Iterable, List, Optional, Tuple
 
 import torch
 import torch.nn as nn

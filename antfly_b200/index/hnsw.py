@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import numpy as np
 import torch
@@ -21,7 +21,6 @@ from .. import _native as N
 from .distance import METRICS
 from .flat import SearchResult
 
-_u64p = ctypes.POINTER(ctypes.c_uint64)
 
 
 def _lib():
