@@ -204,6 +204,13 @@ class TableQueryRequest(BaseModel):
     pruner: Optional[Dict[str, Any]] = None
     reranker: Optional[Dict[str, Any]] = None
     fields: Optional[List[str]] = None
+    filter_prefix: Optional[str] = None
+    filter_query: Union[str, Dict[str, Any], None] = None
+    exclusion_query: Union[str, Dict[str, Any], None] = None
+    order_by: Optional[List[Dict[str, Any]]] = None
+    search_after: Optional[List[str]] = None
+    count: bool = False
+    profile: bool = False
 
 
 class ClassifyRequest(BaseModel):

@@ -1271,21 +1271,38 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             rq = None
             if req.reranker is not None:
                 rq = req.reranker.get("query") or req.semantic_search or (ft if isinstance(ft, str) else None)
+            if req.search_after is not None and (req.offset or not req.order_by):
+                raise ValueError("search_after needs order_by and excludes offset")
+            if req.order_by and (emb is not None or req.semantic_search):
+                raise ValueError("order_by applies to full-text queries; semantic results are ordered by similarity")
+            prof = {} if req.profile else None
             q = TableQuery(embedding=emb, semantic_search=req.semantic_search, full_text_search=ft or None,
-                           limit=req.limit + req.offset, search_effort=req.search_effort,
+                           limit=len(tbl) + 1 if req.count else req.limit + req.offset,
+                           search_effort=req.search_effort,
                            distance_under=req.distance_under, distance_over=req.distance_over, merge=merge,
                            pruner=pr, rerank_query=rq,
-                           rerank_field=(req.reranker or {}).get("field", tbl.text_field))
-            hits = tbl.query(q)[req.offset:]
+                           rerank_field=(req.reranker or {}).get("field", tbl.text_field),
+                           filter_prefix=req.filter_prefix, filter_query=req.filter_query,
+                           exclusion_query=req.exclusion_query, order_by=req.order_by,
+                           search_after=req.search_after, profile=prof)
+            hits = tbl.query(q)
+            total = len(hits)
+            hits = [] if req.count else hits[req.offset:]
             out = []
             for h in hits:
                 src = h.document or {}
                 if req.fields is not None:
                     src = {k: v for k, v in src.items() if k in req.fields}
-                out.append({"_id": h.id, "_score": h.score, "_index_scores": h.index_scores, "_source": src})
-            return {"responses": [{"hits": {"total": len(out), "hits": out,
-                                            "max_score": max((x["_score"] for x in out), default=0.0)},
-                                   "took": int((time.perf_counter() - t0) * 1e3), "status": 200, "table": table}]}
+                rec = {"_id": h.id, "_score": h.score, "_index_scores": h.index_scores, "_source": src}
+                if h.sort is not None:
+                    rec["_sort"] = h.sort
+                out.append(rec)
+            body = {"hits": {"total": total if req.count else len(out), "hits": out,
+                             "max_score": max((x["_score"] for x in out), default=0.0)},
+                    "took": int((time.perf_counter() - t0) * 1e3), "status": 200, "table": table}
+            if prof is not None:
+                body["profile"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in prof.items()}
+            return {"responses": [body]}
 
         return await asyncio.to_thread(run_guarded, "table_query", 1, work)
 

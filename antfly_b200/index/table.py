@@ -34,6 +34,16 @@ class TableQuery:
     rerank_query: Optional[str] = None                # set to re-score the fused hits with the cross-encoder
     rerank_field: str = "text"
     candidates: int = 0                               # per-index candidates before fusion (0: 4 x limit)
+    # restrictions applied before scoring (specs/openapi/antfly/metadata.yaml QueryRequest): documents whose key
+    # starts with filter_prefix, that match filter_query and do not match exclusion_query (index/docfilter.py)
+    filter_prefix: Optional[str] = None
+    filter_query: object = None
+    exclusion_query: object = None
+    # full-text-only queries: sort by document fields ([{"field", "desc"}]; "score" / "_score" is the match score,
+    # "_id" the key) and page with a cursor of the previous page's last sort values
+    order_by: Optional[List[dict]] = None
+    search_after: Optional[List[str]] = None
+    profile: Optional[dict] = None                    # a dictionary to fill with per-phase milliseconds
 
 
 @dataclass
@@ -42,6 +52,7 @@ class TableHit:
     score: float
     index_scores: Dict[str, float]
     document: Optional[dict] = None
+    sort: Optional[List[str]] = None                  # sort values under order_by (the cursor for search_after)
 
 
 class Table:
@@ -91,8 +102,43 @@ class Table:
             self.sparse.delete(key)
         return found                                   # dense entries are filtered at query time
 
+    def allowed_keys(self, q: TableQuery) -> Optional[set]:
+        """The keys a query may return, or None when it has no restriction."""
+        if not (q.filter_prefix or q.filter_query or q.exclusion_query):
+            return None
+        from .docfilter import compile_filter
+
+        keep = compile_filter(q.filter_query)
+        drop = compile_filter(q.exclusion_query) if q.exclusion_query else None
+        out = set()
+        for k, d in self.docs.items():
+            if q.filter_prefix and not str(k).startswith(q.filter_prefix):
+                continue
+            if keep(d) and not (drop is not None and drop(d)):
+                out.add(k)
+        return out
+
     def query(self, q: TableQuery) -> List[TableHit]:
+        import time as _time
+
+        t_start = _time.perf_counter()
+        prof = q.profile if q.profile is not None else {}
+
+        def lap(name, t0):
+            prof[name] = prof.get(name, 0.0) + (_time.perf_counter() - t0) * 1e3
+
         n_cand = q.candidates or 4 * q.limit
+        t0 = _time.perf_counter()
+        allowed = self.allowed_keys(q)
+        lap("filter_ms", t0)
+        if allowed is not None:
+            prof["filter_matches"] = len(allowed)
+            if not allowed:
+                prof["total_ms"] = (_time.perf_counter() - t_start) * 1e3
+                return []
+            # the indexes do not know the restriction: ask for more candidates in proportion to how selective it is
+            n_cand = min(max(len(self.docs), 1), int(n_cand * max(len(self.docs), 1) / len(allowed)) + 1)
+        ok = (lambda k: True) if allowed is None else allowed.__contains__
         per_index: Dict[str, List] = {}
         emb = q.embedding
         if emb is None and q.semantic_search is not None and self.dense is not None:
@@ -100,29 +146,39 @@ class Table:
                 raise ValueError("semantic_search needs an embedder")
             emb = self.embed([q.semantic_search])[0]
         if emb is not None and self.dense is not None:
+            t0 = _time.perf_counter()
             try:
                 res = self.dense.search(emb.float()[None], n_cand, effort=q.search_effort)
             except TypeError:
                 res = self.dense.search(emb.float()[None], n_cand)
             hits = []
             for dist, i in zip(res.distances[0].tolist(), res.ids[0].tolist()):
-                if i < 0 or i >= len(self._key_of) or self._key_of[i] not in self.docs:
+                if i < 0 or i >= len(self._key_of) or self._key_of[i] not in self.docs or not ok(self._key_of[i]):
                     continue
                 if (q.distance_under is not None and dist >= q.distance_under) or \
                         (q.distance_over is not None and dist <= q.distance_over):
                     continue
                 hits.append((self._key_of[i], -float(dist)))       # fusion wants higher-is-better
             per_index["dense"] = hits
+            lap("dense_ms", t0)
         sp = q.sparse_embedding
         if sp is None and q.semantic_search is not None and self.sparse is not None and self.sparse_encode is not None:
             row = self.sparse_encode([q.semantic_search])[0]
             nz = (row > 0).nonzero().flatten()
             sp = dict(zip(nz.tolist(), row[nz].tolist()))
         if sp is not None and self.sparse is not None:
-            per_index["sparse"] = self.sparse.search(sp, n_cand)
+            t0 = _time.perf_counter()
+            per_index["sparse"] = [h for h in self.sparse.search(sp, n_cand) if ok(h[0])]
+            lap("sparse_ms", t0)
         if q.full_text_search:
-            per_index["full_text"] = self.fulltext.search(q.full_text_search, n_cand)
+            t0 = _time.perf_counter()
+            per_index["full_text"] = [h for h in self.fulltext.search(q.full_text_search, n_cand) if ok(h[0])]
+            lap("full_text_ms", t0)
+        if not per_index and allowed is not None:                 # a pure filter query: everything that passes
+            per_index["filter"] = [(k, 1.0) for k in sorted(allowed, key=str)]
+        t0 = _time.perf_counter()
         fused: List[FusedHit] = fuse(per_index, q.merge)
+        lap("merge_ms", t0)
         if q.pruner is not None:
             fused = prune(fused, q.pruner)
         if q.rerank_query is not None and fused:
@@ -134,4 +190,47 @@ class Table:
                 h.index_scores["reranker"] = float(s)
                 h.score = float(s)
             fused = sorted(head, key=lambda h: (-h.score, str(h.doc_id)))
-        return [TableHit(h.doc_id, h.score, h.index_scores, self.docs.get(h.doc_id)) for h in fused[: q.limit]]
+        if q.order_by:
+            fused = self._ordered(fused, q.order_by, q.search_after)
+        prof["total_ms"] = (_time.perf_counter() - t_start) * 1e3
+        return [TableHit(h.doc_id, h.score, h.index_scores, self.docs.get(h.doc_id), getattr(h, "sort", None))
+                for h in fused[: q.limit]]
+
+    def _ordered(self, fused: List[FusedHit], order_by: List[dict], search_after: Optional[List[str]]):
+        """Sort by document fields; each hit gets its sort values (strings, as they travel in a cursor); with
+        ``search_after`` only hits strictly after that cursor remain."""
+        def value(h, field):
+            if field in ("score", "_score"):
+                return h.score
+            if field == "_id":
+                return str(h.doc_id)
+            return (self.docs.get(h.doc_id) or {}).get(field)
+
+        def key_part(v, desc):
+            # missing values last in either direction; numbers before strings; descending by negation / inversion
+            if v is None:
+                return (2, 0, "")
+            if isinstance(v, (int, float)) and not isinstance(v, bool):
+                return (0, -float(v) if desc else float(v), "")
+            s = str(v)
+            return (1, 0, "".join(chr(0x10FFFF - ord(c)) for c in s) if desc else s)
+
+        specs = [(str(o.get("field", "_score")), bool(o.get("desc", False))) for o in order_by] + [("_id", False)]
+        for h in fused:
+            h.sort = [("" if value(h, f) is None else str(value(h, f))) for f, _ in specs]
+            h._key = tuple(key_part(value(h, f), d) for f, d in specs)
+        fused = sorted(fused, key=lambda h: h._key)
+        if search_after:
+            cur = list(search_after) + [""] * (len(specs) - len(search_after))
+
+            def coerce(text, f):
+                if text == "":
+                    return None
+                if f in ("score", "_score"):
+                    return float(text)
+                sample = next((value(h, f) for h in fused if value(h, f) is not None), None)
+                return float(text) if isinstance(sample, (int, float)) and not isinstance(sample, bool) else text
+
+            after = tuple(key_part(coerce(t, f), d) for t, (f, d) in zip(cur, specs))
+            fused = [h for h in fused if h._key > after]
+        return fused
