@@ -211,6 +211,7 @@ class TableQueryRequest(BaseModel):
     search_after: Optional[List[str]] = None
     count: bool = False
     profile: bool = False
+    aggregations: Optional[Dict[str, Dict[str, Any]]] = None
 
 
 class ClassifyRequest(BaseModel):

@@ -1276,8 +1276,9 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             if req.order_by and (emb is not None or req.semantic_search):
                 raise ValueError("order_by applies to full-text queries; semantic results are ordered by similarity")
             prof = {} if req.profile else None
+            want_all = req.count or bool(req.aggregations)      # counting and aggregating look at every match
             q = TableQuery(embedding=emb, semantic_search=req.semantic_search, full_text_search=ft or None,
-                           limit=len(tbl) + 1 if req.count else req.limit + req.offset,
+                           limit=len(tbl) + 1 if want_all else req.limit + req.offset,
                            search_effort=req.search_effort,
                            distance_under=req.distance_under, distance_over=req.distance_over, merge=merge,
                            pruner=pr, rerank_query=rq,
@@ -1287,7 +1288,12 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                            search_after=req.search_after, profile=prof)
             hits = tbl.query(q)
             total = len(hits)
-            hits = [] if req.count else hits[req.offset:]
+            aggs = None
+            if req.aggregations:
+                from ..index.aggregations import aggregate
+
+                aggs = aggregate([h.document or {} for h in hits], req.aggregations)
+            hits = [] if req.count else hits[req.offset: req.offset + req.limit]
             out = []
             for h in hits:
                 src = h.document or {}
@@ -1297,9 +1303,11 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                 if h.sort is not None:
                     rec["_sort"] = h.sort
                 out.append(rec)
-            body = {"hits": {"total": total if req.count else len(out), "hits": out,
+            body = {"hits": {"total": total if want_all else len(out), "hits": out,
                              "max_score": max((x["_score"] for x in out), default=0.0)},
                     "took": int((time.perf_counter() - t0) * 1e3), "status": 200, "table": table}
+            if aggs is not None:
+                body["aggregations"] = aggs
             if prof is not None:
                 body["profile"] = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in prof.items()}
             return {"responses": [body]}

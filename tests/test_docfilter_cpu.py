@@ -117,3 +117,49 @@ def test_order_by_cursor_and_the_endpoint_fields():
                 {"embeddings": emb["note:1"].tolist(), "order_by": [{"field": "year"}]},
                 {"full_text_search": "x", "filter_query": {"fuzzy": 1}}):
         assert c.post("/db/v1/tables/t/query", json=bad).status_code == 400, bad
+
+
+def test_aggregations_over_the_matched_documents():
+    from fastapi.testclient import TestClient
+
+    from antfly_b200.api.model_manager import ModelManager
+    from antfly_b200.api.server import create_app
+    from antfly_b200.index.aggregations import aggregate
+
+    docs = list(DOCS.values())
+    out = aggregate(docs, {"y": {"type": "stats", "field": "year"}, "n": {"type": "count"},
+                           "langs": {"type": "cardinality", "field": "meta.lang"},
+                           "total": {"type": "sum", "field": "year"}, "top": {"type": "max", "field": "year"}})
+    assert out["y"]["count"] == 4 and out["y"]["min"] == 2019 and out["y"]["max"] == 2024 and out["y"]["avg"] == 2021.0
+    assert abs(out["y"]["std_deviation"] - (sum((v - 2021) ** 2 for v in (2021, 2019, 2024, 2020)) / 4) ** 0.5) < 1e-9
+    assert out["n"]["value"] == 4 and out["langs"]["value"] == 2 and out["total"]["value"] == 8084 and out["top"]["value"] == 2024
+    out = aggregate(docs, {"by_status": {"type": "terms", "field": "status", "size": 2,
+                                         "sub_aggregations": {"avg_year": {"type": "avg", "field": "year"}}},
+                           "by_tag": {"type": "terms", "field": "tags"}})
+    assert out["by_status"]["buckets"][0] == {"key": "published", "doc_count": 2,
+                                              "sub_aggregations": {"avg_year": {"value": 2022.5}}}
+    assert len(out["by_status"]["buckets"]) == 2
+    assert out["by_tag"]["buckets"][0] == {"key": "food", "doc_count": 2}
+    out = aggregate(docs, {"eras": {"type": "range", "field": "year", "ranges": [
+        {"name": "old", "to": 2021}, {"name": "new", "from": 2021}]},
+        "per_2y": {"type": "histogram", "field": "year", "interval": 2, "min_doc_count": 1},
+        "by_year": {"type": "date_histogram", "field": "created_at", "calendar_interval": "year"},
+        "recent": {"type": "date_range", "field": "created_at", "date_ranges": [{"name": "since-2023", "from": "2023-01-01"}]}})
+    assert [(b["key"], b["doc_count"]) for b in out["eras"]["buckets"]] == [("old", 2), ("new", 2)]
+    assert [(b["key"], b["doc_count"]) for b in out["per_2y"]["buckets"]] == [(2018.0, 1), (2020.0, 2), (2024.0, 1)]
+    assert [(b["key"], b["doc_count"]) for b in out["by_year"]["buckets"]] == [("2020", 1), ("2022", 1), ("2023", 1), ("2024", 1)]
+    assert out["recent"]["buckets"][0]["doc_count"] == 2
+    for bad in ({"g": {"type": "geohash_grid", "field": "loc"}}, {"s": {"type": "sum"}},
+                {"h": {"type": "histogram", "field": "year"}}):
+        with pytest.raises(ValueError):
+            aggregate(docs, bad)
+    t, _ = _table()
+    app = create_app(ModelManager(models_dir="/nonexistent", device="cpu"))
+    app.state.tables["t"] = t
+    r = TestClient(app).post("/db/v1/tables/t/query", json={
+        "full_text_search": "apple apples", "limit": 1, "filter_prefix": "article:",
+        "aggregations": {"by_status": {"type": "terms", "field": "status"}}})
+    body = r.json()["responses"][0]
+    assert r.status_code == 200 and len(body["hits"]["hits"]) == 1 and body["hits"]["total"] == 2
+    assert sorted((b["key"], b["doc_count"]) for b in body["aggregations"]["by_status"]["buckets"]) == [
+        ("draft", 1), ("published", 1)]
