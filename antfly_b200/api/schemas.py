@@ -177,7 +177,7 @@ class TableCreateRequest(BaseModel):
     dimension: Optional[int] = None
     metric: str = "cosine"
     embedder: Optional[str] = None
-    index_type: str = "flat"            # flat | hbc
+    index_type: str = "flat"            # flat | hbc | hnsw (neighbors, ef_construction, ef_search as extra fields)
     reranker: Optional[str] = None
     text_field: str = "text"
 

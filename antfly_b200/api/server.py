@@ -1214,6 +1214,13 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
                     dense = _HbcAdapter(dim, req.metric)
                 elif req.index_type == "flat":
                     dense = GrowableFlatIndex(dim, req.metric, device=str(mgr.device))
+                elif req.index_type == "hnsw":
+                    from ..index.hnsw import HNSWIndex
+
+                    extra = req.model_extra or {}
+                    dense = HNSWIndex(dim, req.metric, neighbors=int(extra.get("neighbors", 16)),
+                                      ef_construction=int(extra.get("ef_construction", 200)),
+                                      ef_search=int(extra.get("ef_search", 64)))
                 else:
                     raise ValueError(f"unknown index_type {req.index_type!r}")
             app.state.tables[table] = Table(table, dense_index=dense, embed=embed, rerank=rerank,

@@ -210,7 +210,7 @@ def test_request_queue_backpressure():
     q.acquire(1)
 
 
-@pytest.mark.parametrize("index_type", ["flat", "hbc"])
+@pytest.mark.parametrize("index_type", ["flat", "hbc", "hnsw"])
 def test_table_create_batch_and_hybrid_query(client, index_type):
     t = f"docs_{index_type}"
     r = client.post(f"/db/v1/tables/{t}", json={"embedder": "tiny-embed", "reranker": "tiny-rerank",
