@@ -45,7 +45,27 @@ class GGUFFile:
         mm = self._mm
         if mm[:4] != GGUF_MAGIC:
             raise ValueError(f"{path}: not a GGUF file")
+        try:
+            self._parse(mm)
+        except (struct.error, OverflowError, IndexError, MemoryError, RecursionError) as e:
+            raise ValueError(f"{path}: truncated or corrupt GGUF header ({type(e).__name__}: {e})") from e
+        # every tensor must lie inside the file: a directory that points past the end is refused here, not when a
+        # kernel reads the bytes
+        lib = N.host()
+        lib.afb_gguf_block_bytes.restype = ctypes.c_long
+        lib.afb_gguf_block_values.restype = ctypes.c_long
+        for info in self.tensors.values():
+            n = 1
+            for d in info.shape:
+                n *= int(d)
+            bv, bb = int(lib.afb_gguf_block_values(info.type)), int(lib.afb_gguf_block_bytes(info.type))
+            if bv > 0 and bb > 0 and (n < 0 or self.data_start + info.offset + (n // bv) * bb > len(mm)):
+                raise ValueError(f"{path}: tensor {info.name!r} extends past the end of the file")
+
+    def _parse(self, mm) -> None:
         self.version, n_tensors, n_kv = struct.unpack_from("<IQQ", mm, 4)
+        if n_tensors > len(mm) or n_kv > len(mm):             # each entry takes at least a few bytes
+            raise ValueError("GGUF header counts exceed the file size")
         self._pos = 24
         self.metadata: Dict[str, Any] = {}
         for _ in range(n_kv):
@@ -58,16 +78,22 @@ class GGUFFile:
             name = self._string()
             (nd,) = struct.unpack_from("<I", mm, self._pos)
             self._pos += 4
+            if nd > 8:
+                raise ValueError(f"tensor {name!r} declares {nd} dimensions")
             dims = struct.unpack_from(f"<{nd}Q", mm, self._pos)
             self._pos += 8 * nd
             ty, off = struct.unpack_from("<IQ", mm, self._pos)
             self._pos += 12
             self.tensors[name] = GGUFTensorInfo(name, tuple(reversed(dims)), ty, off)
-        align = int(self.metadata.get("general.alignment", 32))
+        align = self.metadata.get("general.alignment", 32)
+        if not isinstance(align, int) or align <= 0 or align > (1 << 20):
+            raise ValueError(f"bad general.alignment {align!r}")
         self.data_start = (self._pos + align - 1) // align * align
 
     def _string(self) -> str:
         (n,) = struct.unpack_from("<Q", self._mm, self._pos)
+        if self._pos + 8 + n > len(self._mm):
+            raise ValueError("string runs past the end of the file")
         s = self._mm[self._pos + 8:self._pos + 8 + n].decode("utf-8", errors="replace")
         self._pos += 8 + n
         return s
@@ -83,6 +109,8 @@ class GGUFFile:
         if vt == 9:
             et, n = struct.unpack_from("<IQ", self._mm, self._pos)
             self._pos += 12
+            if n > len(self._mm) - self._pos:                  # every element takes at least one byte
+                raise ValueError("array runs past the end of the file")
             return [self._value(et) for _ in range(n)]
         raise ValueError(f"unknown GGUF metadata value type {vt}")
 

@@ -136,3 +136,36 @@ def test_graph_index_survives_random_inserts_and_deletes(seed):
             # an exact hit on a stored vector is found
             k = next(iter(live))
             assert idx.search(torch.from_numpy(live[k])[None], 1, ef=64).ids.item() == k
+
+
+@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(0, 2), st.integers(0, 2 ** 31 - 1))
+def test_corrupt_gguf_files_are_refused_with_value_errors(tmp_path_factory, kind, seed):
+    """Truncations, flipped header bytes and overwritten counts: the reader raises ValueError or reads a file whose
+    tensors all lie inside it; nothing else escapes."""
+    d = tmp_path_factory.mktemp("gguf")
+    good = str(d / "good.gguf")
+    GG.write_gguf(good, {"general.architecture": "llama", "llama.block_count": 1, "tokenizer.ggml.tokens": ["a", "b"]},
+                  {"token_embd.weight": (8, torch.ones(4, 32)), "n.weight": (0, torch.ones(4))})
+    raw = bytearray(open(good, "rb").read())
+    rng = np.random.default_rng(seed)
+    if kind == 0:
+        raw = raw[: int(rng.integers(0, len(raw)))]
+    elif kind == 1:
+        for _ in range(3):
+            raw[int(rng.integers(0, min(len(raw), 220)))] = int(rng.integers(0, 256))
+    else:
+        raw[int(rng.integers(4, 40))] = int(rng.integers(0, 256))
+    bad = str(d / "bad.gguf")
+    with open(bad, "wb") as f:
+        f.write(bytes(raw))
+    try:
+        f = GG.GGUFFile(bad)
+    except ValueError:
+        return
+    for name, info in f.tensors.items():
+        try:
+            t = f.tensor(name)
+        except (ValueError, NotImplementedError):
+            continue
+        assert t.numel() == int(np.prod(info.shape)) if info.shape else True
