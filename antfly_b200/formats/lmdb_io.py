@@ -23,6 +23,8 @@ Keys compare as byte strings (no custom comparators, no duplicate-sorted databas
 """
 from __future__ import annotations
 
+import functools
+import inspect
 import mmap
 import os
 import struct
@@ -43,9 +45,33 @@ class LmdbError(ValueError):
     pass
 
 
+_BROKEN = (struct.error, IndexError, OverflowError, UnicodeDecodeError)
+
+
+def _refuses(fn):
+    """Reads that run off a damaged file surface as :class:`LmdbError`, whatever the low-level failure was."""
+    if inspect.isgeneratorfunction(fn):
+        @functools.wraps(fn)
+        def gen(*a, **k):
+            try:
+                yield from fn(*a, **k)
+            except _BROKEN as e:
+                raise LmdbError(f"damaged LMDB file: {e}") from e
+        return gen
+
+    @functools.wraps(fn)
+    def call(*a, **k):
+        try:
+            return fn(*a, **k)
+        except _BROKEN as e:
+            raise LmdbError(f"damaged LMDB file: {e}") from e
+    return call
+
+
 class LmdbReader:
     """Read-only view of an LMDB environment (a directory holding ``data.mdb``, or the file itself)."""
 
+    @_refuses
     def __init__(self, path: str):
         if os.path.isdir(path):
             path = os.path.join(path, "data.mdb")
@@ -122,6 +148,8 @@ class LmdbReader:
             if off + HDR + size > len(self._mm):
                 raise LmdbError("overflow value runs past the file")
             return bytes(self._mm[off + HDR: off + HDR + size])
+        if data + size > len(self._mm):
+            raise LmdbError("value runs past the file")
         return bytes(self._mm[data: data + size])
 
     def _walk(self, root: int, depth: int = 0) -> Iterator[Tuple[bytes, bytes, int]]:
@@ -163,25 +191,34 @@ class LmdbReader:
         raise LmdbError("tree deeper than 64 levels (a page cycle)")
 
     # -- databases -------------------------------------------------------------------------------------------
+    @_refuses
     def databases(self) -> List[str]:
         return [k.decode("utf-8", "replace") for k, _, nf in self._walk(self._main[7]) if nf & F_SUBDATA]
+
+    @staticmethod
+    def _sub(v: bytes):
+        if len(v) < _DB.size:
+            raise LmdbError("named database record is shorter than 48 bytes")
+        return _DB.unpack(v[:48])
 
     def _db_root(self, name: Optional[str]) -> int:
         if name is None:
             return self._main[7]
         for k, v, nf in self._walk(self._main[7]):
             if k == name.encode() and nf & F_SUBDATA:
-                return _DB.unpack(v[:48])[7]
+                return self._sub(v)[7]
         raise KeyError(f"no database named {name!r}")
 
+    @_refuses
     def entries(self, name: Optional[str] = None) -> int:
         if name is None:
             return self._main[6]
         for k, v, nf in self._walk(self._main[7]):
             if k == name.encode() and nf & F_SUBDATA:
-                return _DB.unpack(v[:48])[6]
+                return self._sub(v)[6]
         raise KeyError(f"no database named {name!r}")
 
+    @_refuses
     def items(self, name: Optional[str] = None) -> Iterator[Tuple[bytes, bytes]]:
         """Key / value pairs of a database in key order (``name`` None: the unnamed main database)."""
         for k, v, nf in self._walk(self._db_root(name)):
@@ -189,6 +226,7 @@ class LmdbReader:
                 continue
             yield k, v
 
+    @_refuses
     def get(self, name: Optional[str], key: bytes) -> Optional[bytes]:
         return self._seek(self._db_root(name), key)
 

@@ -169,3 +169,36 @@ def test_corrupt_gguf_files_are_refused_with_value_errors(tmp_path_factory, kind
         except (ValueError, NotImplementedError):
             continue
         assert t.numel() == int(np.prod(info.shape)) if info.shape else True
+
+
+@settings(max_examples=120, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(0, 2), st.integers(0, 2 ** 31 - 1))
+def test_damaged_lmdb_files_are_refused_with_lmdb_errors(tmp_path_factory, kind, seed):
+    """A stock LMDB data file cut short or with bytes overwritten: every read either works or raises LmdbError (a
+    database name that no longer decodes may also be reported missing)."""
+    import gzip
+    import os
+
+    from antfly_b200.formats.lmdb_io import LmdbError, LmdbReader
+
+    raw = bytearray(gzip.open(os.path.join(os.path.dirname(__file__), "data", "lmdb_stock_env.mdb.gz")).read())
+    rng = np.random.default_rng(seed)
+    if kind == 0:
+        raw = raw[: int(rng.integers(1, len(raw)))]
+    elif kind == 1:
+        for _ in range(int(rng.integers(1, 20))):
+            raw[int(rng.integers(0, len(raw)))] = int(rng.integers(0, 256))
+    else:
+        o = int(rng.integers(0, len(raw) - 64))
+        raw[o:o + 64] = bytes(rng.integers(0, 256, 64, dtype=np.uint8))
+    bad = str(tmp_path_factory.mktemp("lmdb") / "data.mdb")
+    with open(bad, "wb") as f:
+        f.write(bytes(raw))
+    try:
+        with LmdbReader(bad) as r:
+            for name in [None] + r.databases():
+                for _ in r.items(name):
+                    pass
+                r.entries(name)
+    except (LmdbError, KeyError):
+        pass
