@@ -232,6 +232,11 @@ def _namespaces(directory: str) -> Dict[str, Dict[bytes, bytes]]:
         with LmdbReader(directory) as r:
             have = set(r.databases())
             return {ns: dict(r.items(name)) if name in have else {} for ns, name in LMDB_NAMES.items()}
+    if os.path.exists(os.path.join(directory, "MANIFEST")):
+        from .lsm_store import LsmStore
+
+        with LsmStore(directory, read_only=True) as store, store.begin_read() as r:
+            return {ns: dict(r.items(ns)) for ns in LMDB_NAMES}
     out = {}
     for ns in LMDB_NAMES:
         path = os.path.join(directory, ns + ".kv")
@@ -240,8 +245,9 @@ def _namespaces(directory: str) -> Dict[str, Dict[bytes, bytes]]:
 
 
 def save_hbc(index: HBCIndex, directory: str, container: str = "files") -> None:
-    """``container``: "files" (one sorted file per namespace) or "lmdb" (one LMDB environment)."""
-    if container not in ("files", "lmdb"):
+    """``container``: "files" (one sorted file per namespace), "lmdb" (one LMDB environment) or "lsm" (a
+    log-structured merge store directory, loaded as one sorted table file)."""
+    if container not in ("files", "lmdb", "lsm"):
         raise ValueError(f"unknown index container {container!r}")
     os.makedirs(directory, exist_ok=True)
     nodes = {node_key(nd.id, "p"): pack_node(nd) for nd in index.nodes.values()}
@@ -259,6 +265,21 @@ def save_hbc(index: HBCIndex, directory: str, container: str = "files") -> None:
         from ..formats.lmdb_io import write_lmdb
 
         write_lmdb(directory, {LMDB_NAMES[ns]: kv for ns, kv in spaces.items()})
+        return
+    if container == "lsm":
+        from .lsm_store import LsmStore
+
+        with LsmStore(directory, background=False) as store:
+            with store.begin_write() as w:                       # rows of an earlier index in this directory go
+                for ns in spaces:
+                    for k, _ in list(w.open_cursor(ns)):
+                        if k not in spaces[ns]:
+                            w.delete(ns, k)
+            with store.begin_batch("bulk_ingest") as b:
+                for ns, kv in spaces.items():
+                    for k, v in kv.items():
+                        b.put(ns, k, v)
+            store.compact(full=True)
         return
     for ns, kv in spaces.items():
         _write_ns(os.path.join(directory, ns + ".kv"), kv)
