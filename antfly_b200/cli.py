@@ -563,6 +563,16 @@ def cmd_smoke(args) -> int:
     return 0
 
 
+def cmd_store_bench(args) -> int:
+    import tempfile
+
+    from .index.lsm_store import bench
+
+    with tempfile.TemporaryDirectory(dir=args.dir) as d:
+        print(json.dumps(bench(d, args.rows, args.value_bytes, args.batch, args.sync)))
+    return 0
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="antfly_b200", description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -685,6 +695,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--tasks", help="comma-separated tasks for the manifest (embed, rerank, generate, ...)")
     p.add_argument("--capabilities", help="comma-separated capabilities for the manifest")
     p.set_defaults(fn=cmd_pull)
+    p = sub.add_parser("store-bench", help="write / read throughput of the log-structured merge store")
+    p.add_argument("--dir", default=None); p.add_argument("--rows", type=int, default=200_000)
+    p.add_argument("--value-bytes", type=int, default=256); p.add_argument("--batch", type=int, default=500)
+    p.add_argument("--sync", action="store_true"); p.set_defaults(fn=cmd_store_bench)
     p = sub.add_parser("smoke"); p.set_defaults(fn=cmd_smoke)
     raw = list(sys.argv[1:] if argv is None else argv)
     if raw and raw[0] == "bench":              # everything after the command belongs to bench.py, options included

@@ -468,3 +468,51 @@ class LsmStore:
 
     def __exit__(self, *a):
         self.close()
+
+
+def bench(directory: str, rows: int = 200_000, value_bytes: int = 256, batch: int = 500, sync: bool = False,
+          seed: int = 0) -> Dict[str, float]:
+    """Write / read throughput of a store in ``directory`` (the counterpart of the reference's write bench,
+    zig/pkg/antfly/src/lsm_write_bench_root.zig): commits of ``batch`` random-key rows through the log, the same
+    rows again as one bulk-ingest batch into a second store, point reads of present and absent keys, a full scan."""
+    import os
+    import random
+    import time
+
+    rng = random.Random(seed)
+    keys = [b"%016x" % rng.getrandbits(64) for _ in range(rows)]
+    value = bytes(rng.getrandbits(8) for _ in range(value_bytes))
+    out: Dict[str, float] = {"rows": rows, "value_bytes": value_bytes, "batch": batch}
+    with LsmStore(os.path.join(directory, "logged"), sync=sync) as s:
+        t0 = time.perf_counter()
+        for i in range(0, rows, batch):
+            with s.begin_write() as w:
+                for k in keys[i:i + batch]:
+                    w.put("vecs", k, value)
+        out["logged_rows_per_s"] = rows / (time.perf_counter() - t0)
+        s.flush()
+        s.compact()
+        st = s.stats()
+        out["write_amplification"] = (st["compaction_bytes_written"] + sum(st[f"level{i}_bytes"] for i in range(6))) / \
+            max(rows * (value_bytes + 17), 1)
+        probe = rng.sample(keys, min(20_000, rows))
+        with s.begin_read() as r:
+            t0 = time.perf_counter()
+            for k in probe:
+                r.get("vecs", k)
+            out["get_hit_per_s"] = len(probe) / (time.perf_counter() - t0)
+            t0 = time.perf_counter()
+            for k in probe:
+                r.get("vecs", k + b"?")
+            out["get_miss_per_s"] = len(probe) / (time.perf_counter() - t0)
+            t0 = time.perf_counter()
+            n = sum(1 for _ in r.items("vecs"))
+            out["scan_rows_per_s"] = n / (time.perf_counter() - t0)
+        out.update({k: v for k, v in st.items() if k in ("flushes", "compactions", "stalls", "stall_ms")})
+    with LsmStore(os.path.join(directory, "bulk"), sync=sync) as s:
+        t0 = time.perf_counter()
+        with s.begin_batch("bulk_ingest") as b:
+            for k in keys:
+                b.append_put("vecs", k, value)
+        out["bulk_rows_per_s"] = rows / (time.perf_counter() - t0)
+    return out

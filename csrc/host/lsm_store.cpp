@@ -50,18 +50,29 @@ constexpr int kLevels = 6;
 constexpr uint8_t kPut = 1, kDel = 2;
 
 // ---- small helpers ------------------------------------------------------------------------------------------
-uint32_t crc32(const uint8_t* p, size_t n) {
-  static uint32_t table[256];
+uint32_t crc32(const uint8_t* p, size_t n) {                        // slicing-by-8
+  static uint32_t table[8][256];
   static std::once_flag once;
   std::call_once(once, [] {
     for (uint32_t i = 0; i < 256; ++i) {
       uint32_t c = i;
       for (int k = 0; k < 8; ++k) c = (c & 1) ? 0xEDB88320u ^ (c >> 1) : c >> 1;
-      table[i] = c;
+      table[0][i] = c;
     }
+    for (uint32_t i = 0; i < 256; ++i)
+      for (int t = 1; t < 8; ++t) table[t][i] = table[0][table[t - 1][i] & 0xFF] ^ (table[t - 1][i] >> 8);
   });
   uint32_t c = 0xFFFFFFFFu;
-  for (size_t i = 0; i < n; ++i) c = table[(c ^ p[i]) & 0xFF] ^ (c >> 8);
+  while (n >= 8) {
+    uint32_t a, b;
+    std::memcpy(&a, p, 4);
+    std::memcpy(&b, p + 4, 4);
+    a ^= c;
+    c = table[7][a & 0xFF] ^ table[6][(a >> 8) & 0xFF] ^ table[5][(a >> 16) & 0xFF] ^ table[4][a >> 24] ^
+        table[3][b & 0xFF] ^ table[2][(b >> 8) & 0xFF] ^ table[1][(b >> 16) & 0xFF] ^ table[0][b >> 24];
+    p += 8; n -= 8;
+  }
+  for (size_t i = 0; i < n; ++i) c = table[0][(c ^ p[i]) & 0xFF] ^ (c >> 8);
   return c ^ 0xFFFFFFFFu;
 }
 
@@ -118,6 +129,11 @@ Bytes unhex(const std::string& s) {
   auto v = [](char c) { return c <= '9' ? c - '0' : c - 'a' + 10; };
   for (size_t i = 0; i + 1 < s.size(); i += 2) b.push_back(char(v(s[i]) << 4 | v(s[i + 1])));
   return b;
+}
+
+int compare(const uint8_t* a, size_t an, const Bytes& b) {
+  int c = std::memcmp(a, b.data(), std::min(an, b.size()));
+  return c ? c : (an < b.size() ? -1 : an > b.size() ? 1 : 0);
 }
 
 // ---- table files --------------------------------------------------------------------------------------------
@@ -212,6 +228,7 @@ struct Table {
   const uint8_t* bloom = nullptr;
   uint64_t bloom_bits = 0;
   std::atomic<bool> obsolete{false};
+  mutable std::unique_ptr<std::atomic<uint8_t>[]> verified;            // per data block: checksum already checked
   mutable std::atomic<uint64_t> bloom_skips{0};
 
   ~Table() {
@@ -255,6 +272,8 @@ struct Table {
       index.push_back(std::move(h));
     }
     if (index.size() != nblocks) return p + ": block count does not match the index";
+    verified.reset(new std::atomic<uint8_t>[index.size() + 1]);
+    for (size_t i = 0; i <= index.size(); ++i) verified[i].store(0);
     bloom = map + boff;
     bloom_bits = blen * 8;
     if (!index.empty()) {
@@ -278,11 +297,43 @@ struct Table {
     return true;
   }
 
+  // The checksum of a block is computed on its first use; the mapping is read-only, so once is enough.
+  bool check_block(size_t b) const {
+    if (verified[b].load(std::memory_order_acquire)) return true;
+    const BlockHandle& h = index[b];
+    if (crc32(map + h.offset, h.bytes) != get_fixed<uint32_t>(map + h.offset + h.bytes)) return false;
+    verified[b].store(1, std::memory_order_release);
+    return true;
+  }
+
+  // Point lookup: 1 put, 2 delete, 0 absent, -1 damaged.  Walks the one block that can hold the key.
+  int find(const Bytes& key, Bytes* out, std::string* err) const {
+    size_t b = block_for(key);
+    if (b >= index.size()) return 0;
+    if (!check_block(b)) { *err = path + ": data block checksum"; return -1; }
+    const uint8_t *p = map + index[b].offset, *end = p + index[b].bytes;
+    while (p < end) {
+      uint8_t kind = *p;
+      uint64_t kl, vl;
+      const uint8_t* q = get_varint(p + 1, end, &kl);
+      if (q) q = get_varint(q, end, &vl);
+      if (!q || kl > uint64_t(end - q) || vl > uint64_t(end - q) - kl) { *err = path + ": entry runs off its block"; return -1; }
+      int c = compare(q, kl, key);
+      if (c == 0) {
+        if (kind == kPut && out) out->assign(reinterpret_cast<const char*>(q + kl), vl);
+        return kind == kPut ? 1 : 2;
+      }
+      if (c > 0) return 0;
+      p = q + kl + vl;
+    }
+    return 0;
+  }
+
   // Offsets of the entries of block b (relative to the block); verifies the block's checksum and framing.
   std::string parse_block(size_t b, std::vector<uint32_t>* offs) const {
     const BlockHandle& h = index[b];
     const uint8_t *base = map + h.offset, *p = base, *end = base + h.bytes;
-    if (crc32(base, h.bytes) != get_fixed<uint32_t>(end)) return path + ": data block checksum";
+    if (!check_block(b)) return path + ": data block checksum";
     offs->clear();
     while (p < end) {
       offs->push_back(uint32_t(p - base));
@@ -317,10 +368,6 @@ struct Table {
   }
 };
 
-int compare(const uint8_t* a, size_t an, const Bytes& b) {
-  int c = std::memcmp(a, b.data(), std::min(an, b.size()));
-  return c ? c : (an < b.size() ? -1 : an > b.size() ? 1 : 0);
-}
 
 // ---- memory tables ------------------------------------------------------------------------------------------
 struct MemVersion { uint64_t seq; uint8_t kind; Bytes value; };
@@ -605,12 +652,7 @@ struct Version {
     for (auto& m : imm) if ((r = m->get(key, seq, out))) return r == kPut;
     auto in_table = [&](const std::shared_ptr<Table>& t) -> int {      // 1 put, 2 delete, 0 absent, -1 damaged
       if (key < t->smallest || key > t->largest || !t->may_contain(key)) return 0;
-      TableSource s(t);
-      s.seek_ge(key);
-      if (!s.error.empty()) { *err = s.error; return -1; }
-      if (!s.valid || s.key != key) return 0;
-      if (s.kind == kPut && out) out->assign(reinterpret_cast<const char*>(s.val), s.vlen);
-      return s.kind;
+      return t->find(key, out, err);
     };
     for (auto& t : levels[0]) if ((r = in_table(t))) return r < 0 ? -1 : r == kPut;
     for (int l = 1; l < kLevels; ++l) {
