@@ -244,23 +244,41 @@ def _namespaces(directory: str) -> Dict[str, Dict[bytes, bytes]]:
     return out
 
 
+def hbc_rows(index: HBCIndex, known_vectors=()) -> Dict[str, Dict[bytes, bytes]]:
+    """Every row of an index, by namespace.  Leaves list their members by vector id (stable under deletes and any
+    id order); vectors no leaf holds any more are left out.  ``known_vectors``: ids whose ``v:`` row the caller
+    already has (their bytes are not produced again)."""
+    import copy
+
+    ids = index.ids.tolist()
+    nodes: Dict[bytes, bytes] = {}
+    for nd in index.nodes.values():
+        if nd.is_leaf:
+            nd = copy.copy(nd)
+            nd.children = [ids[m] for m in nd.children]
+        nodes[node_key(nd.id, "p")] = pack_node(nd)
+    live = sorted(index.leaf_of)
+    meta = {META_KEY: pack_metadata(index.cfg, index.root, len(live), len(index.nodes))}
+    vecs: Dict[bytes, bytes] = {}
+    x = index.vectors.detach().float().cpu()
+    known = set(known_vectors)
+    for i in live:
+        vid = int(ids[i])
+        if vid not in known:
+            vecs[b"v:" + struct.pack(">Q", vid)] = x[i].numpy().astype("<f4").tobytes()
+        vecs[b"l:" + struct.pack(">Q", vid)] = struct.pack("<Q", index.leaf_of[i])
+    quant = {b"q:" + struct.pack(">Q", nd.id): encode_rabitq_set(nd.quant) for nd in index.nodes.values()
+             if getattr(nd, "quant", None) is not None}
+    return {"nodes": nodes, "meta": meta, "vecs": vecs, "quant": quant}
+
+
 def save_hbc(index: HBCIndex, directory: str, container: str = "files") -> None:
     """``container``: "files" (one sorted file per namespace), "lmdb" (one LMDB environment) or "lsm" (a
     log-structured merge store directory, loaded as one sorted table file)."""
     if container not in ("files", "lmdb", "lsm"):
         raise ValueError(f"unknown index container {container!r}")
     os.makedirs(directory, exist_ok=True)
-    nodes = {node_key(nd.id, "p"): pack_node(nd) for nd in index.nodes.values()}
-    meta = {META_KEY: pack_metadata(index.cfg, index.root, int(index.vectors.shape[0]), len(index.nodes))}
-    vecs: Dict[bytes, bytes] = {}
-    x = index.vectors.detach().float().cpu()
-    for i in range(x.shape[0]):
-        vid = int(index.ids[i])
-        vecs[b"v:" + struct.pack(">Q", vid)] = x[i].numpy().astype("<f4").tobytes()
-        vecs[b"l:" + struct.pack(">Q", vid)] = struct.pack("<Q", index.leaf_of.get(i, 0))
-    quant = {b"q:" + struct.pack(">Q", nd.id): encode_rabitq_set(nd.quant) for nd in index.nodes.values()
-             if getattr(nd, "quant", None) is not None}
-    spaces = {"nodes": nodes, "meta": meta, "vecs": vecs, "quant": quant}
+    spaces = hbc_rows(index)
     if container == "lmdb":
         from ..formats.lmdb_io import write_lmdb
 
@@ -288,7 +306,14 @@ def save_hbc(index: HBCIndex, directory: str, container: str = "files") -> None:
 def load_hbc(directory: str) -> HBCIndex:
     spaces = _namespaces(directory)
     if META_KEY not in spaces["meta"]:
-        raise FileNotFoundError(f"{directory}: no HBC index metadata (neither *.kv files nor an LMDB environment)")
+        raise FileNotFoundError(f"{directory}: no HBC index metadata (no *.kv files, LMDB environment or merge store)")
+    return load_hbc_from(spaces)
+
+
+def load_hbc_from(spaces: Dict[str, Dict[bytes, bytes]]) -> HBCIndex:
+    """The index from its rows ({namespace: {key: value}})."""
+    if META_KEY not in spaces["meta"]:
+        raise FileNotFoundError("no HBC index metadata among the rows")
     md = unpack_metadata(spaces["meta"][META_KEY])
     cfg = HBCConfig(md["dims"], md["metric"], md["branching_factor"], md["leaf_size"],
                     use_quantization=md["use_quantization"], quantizer_seed=md["quantizer_seed"])
@@ -305,11 +330,15 @@ def load_hbc(directory: str) -> HBCIndex:
     idx.vectors = torch.stack(rows) if rows else torch.zeros(0, cfg.dims)
     idx.ids = torch.tensor(vids)
     pos = {v: i for i, v in enumerate(vids)}
-    for nd in idx.nodes.values():
-        if nd.is_leaf:
-            # leaf members are stored as positions at build time; ids == positions for bulk builds without ids
-            for m in nd.children:
-                idx.leaf_of[m] = nd.id
+    leaves = [nd for nd in idx.nodes.values() if nd.is_leaf]
+    # leaves list vector ids; files written before that listed row positions (the same thing whenever the ids
+    # were 0..n-1), which shows as a member that is no stored id
+    by_id = all(m in pos for nd in leaves for m in nd.children)
+    for nd in leaves:
+        if by_id:
+            nd.children = [pos[m] for m in nd.children]
+        for m in nd.children:
+            idx.leaf_of[m] = nd.id
     if cfg.use_quantization:
         stored = spaces["quant"]
         for nd in idx.nodes.values():

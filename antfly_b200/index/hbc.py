@@ -451,4 +451,4 @@ class HBCIndex:
     def stats(self) -> dict:
         leaves = sum(1 for n in self.nodes.values() if n.is_leaf)
         return {"nodes": len(self.nodes), "leaves": leaves, "levels": self.nodes[self.root].level + 1,
-                "vectors": 0 if self.vectors is None else int(self.vectors.shape[0])}
+                "vectors": len(self.leaf_of)}          # vectors some leaf holds (deleted rows are not counted)

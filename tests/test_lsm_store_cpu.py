@@ -407,3 +407,50 @@ def test_hbc_index_through_the_lsm_container_and_a_rebuild_in_the_same_directory
     artifact.save_hbc(small, d, container="lsm")
     b = artifact.load_hbc(d)
     assert b.stats() == small.stats() and b.search(x[0], 5)[0] == small.search(x[0], 5)[0]
+
+
+def test_an_hbc_index_kept_in_the_store_commits_each_batch_and_reopens_to_the_same_tree(tmp_path):
+    import torch
+
+    from antfly_b200.index.hbc import HBCConfig, HBCIndex
+    from antfly_b200.index.hbc_store import PersistentHBC
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1500, 16, generator=g)
+    cfg = HBCConfig(16, "l2_squared", branching_factor=6, leaf_size=24, search_width=16, use_quantization=True)
+    d = str(tmp_path / "idx")
+    twin = HBCIndex.bulk_build(x[:800], cfg)                     # the same operations on a plain in-memory index
+    p = PersistentHBC.create(d, x[:800], cfg, background=False, sync=False)
+    total_rows = sum(len(list(r)) for r in [p._sig]) + len(p._vectors)
+    commits = p.store.stats()["wal_records"]
+    new_ids = torch.arange(5000, 5300).flip(0)                   # ids in descending order, far from the positions
+    twin.insert(x[800:1100], new_ids)
+    wrote = p.insert(x[800:1100], new_ids)
+    assert p.store.stats()["wal_records"] == commits + 1         # one commit for the whole batch
+    small = p.insert(x[1100:1103], torch.tensor([9001, 9002, 9003]))
+    twin.insert(x[1100:1103], torch.tensor([9001, 9002, 9003]))
+    assert 3 <= small < total_rows // 4 and small < wrote        # a small batch rewrites a small part of the rows
+    gone = list(range(0, 400, 3)) + [5000, 5299, 9002]
+    assert p.delete(gone) == twin.delete(gone) == len(gone)
+    for q in x[1200:1210]:
+        assert p.search(q, 10)[0] == twin.search(q, 10)[0]
+    want = [twin.search(q, 10) for q in x[1200:1230]]
+    stats = twin.stats()
+    p.close()
+    with PersistentHBC(d, background=False, sync=False) as again:
+        assert again.index.stats() == stats
+        for q, (ids, dist) in zip(x[1200:1230], want):
+            got = again.search(q, 10)
+            assert got[0] == ids and got[1] == pytest.approx(dist, rel=1e-5, abs=1e-5)
+        assert not set(gone) & set(again.index.ids.tolist())    # deleted vectors left the store too
+        with again.store.begin_read() as r:
+            assert r.get("vecs", b"v:" + (5000).to_bytes(8, "big")) is None
+            assert r.get("vecs", b"v:" + (5001).to_bytes(8, "big")) is not None
+        again.insert(x[1300:1310], torch.arange(20000, 20010))
+        after = [again.search(q, 5)[0] for q in x[1300:1310]]
+        twin.insert(x[1300:1310], torch.arange(20000, 20010))
+        assert after == [twin.search(q, 5)[0] for q in x[1300:1310]]     # the reloaded tree behaves as the original
+    with PersistentHBC(d, background=False, sync=False) as third:
+        assert 20005 in third.index.ids.tolist() and [third.search(q, 5)[0] for q in x[1300:1310]] == after
+    with pytest.raises(FileNotFoundError):
+        PersistentHBC(str(tmp_path / "nothing"))
