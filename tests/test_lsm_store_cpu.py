@@ -454,3 +454,61 @@ def test_an_hbc_index_kept_in_the_store_commits_each_batch_and_reopens_to_the_sa
         assert 20005 in third.index.ids.tolist() and [third.search(q, 5)[0] for q in x[1300:1310]] == after
     with pytest.raises(FileNotFoundError):
         PersistentHBC(str(tmp_path / "nothing"))
+
+
+def test_random_damage_to_any_file_of_a_store_gives_an_error_or_a_working_store(tmp_path):
+    import shutil
+
+    good = str(tmp_path / "good")
+    opts = dict(SMALL, background=False)
+    with LsmStore(good, **opts) as s:
+        for rep in range(5):
+            with s.begin_write() as w:
+                for i in range(300):
+                    w.put("vecs", b"k%05d" % ((i * 7 + rep * 13) % 1500), bytes([rep]) * 40)
+                for i in range(0, 300, 9):
+                    w.delete("vecs", b"k%05d" % i)
+            if rep in (1, 3):
+                s.flush()
+        s.compact()
+        with s.begin_write() as w:
+            w.put("meta", b"tail", b"in the log only")
+    files = [f for f in sorted(os.listdir(good)) if f != "LOCK"]
+    assert any(f.endswith(".tbl") for f in files) and any(f.startswith("wal-") for f in files)
+    rng = random.Random(11)
+    outcomes = set()
+    for case in range(45):
+        d = str(tmp_path / "bad")
+        shutil.rmtree(d, ignore_errors=True)
+        shutil.copytree(good, d)
+        name = files[case % len(files)]
+        raw = bytearray(open(os.path.join(d, name), "rb").read())
+        if not raw:
+            continue
+        mode = case // len(files) % 3
+        if mode == 0:
+            raw = raw[: rng.randrange(0, len(raw))]
+        elif mode == 1:
+            for _ in range(rng.randrange(1, 6)):
+                raw[rng.randrange(len(raw))] ^= 1 + rng.randrange(255)
+        else:
+            o = rng.randrange(len(raw))
+            raw[o:o + 32] = bytes(rng.randrange(256) for _ in range(min(32, len(raw) - o)))
+        open(os.path.join(d, name), "wb").write(bytes(raw))
+        try:
+            with LsmStore(d, read_only=case % 2 == 0, **opts) as s:
+                with s.begin_read() as r:
+                    keys = [k for k, _ in r.items("vecs")]
+                    assert keys == sorted(keys)
+                    c = r.open_cursor("vecs")
+                    e = c.last()
+                    while e is not None:
+                        e = c.prev()
+                if case % 2:
+                    with s.begin_write() as w:
+                        w.put("vecs", b"new", b"1")
+                    s.compact(full=True)
+            outcomes.add(("ok", name.split(".")[-1]))
+        except LsmError:
+            outcomes.add(("refused", name.split(".")[-1]))
+    assert ("refused", "tbl") in outcomes and ("refused", "MANIFEST") in outcomes and ("ok", "log") in outcomes
