@@ -13,6 +13,9 @@ import asyncio
 import base64
 import json
 import logging
+import os
+import re
+import shutil
 import struct
 import threading
 import time
@@ -109,8 +112,12 @@ def _err(status: int, code: str, message: str) -> JSONResponse:
 def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[str, object]] = None,
                max_concurrent_requests: int = 64, max_queue_size: int = 256,
                request_timeout_s: float = 0.0, result_cache_ttl_s: float = 120.0,
-               api_key: Optional[str] = None, content_security=None) -> FastAPI:
-    """``content_security``: an :class:`antfly_b200.api.content.ContentSecurity` (or its dictionary form) governing
+               api_key: Optional[str] = None, content_security=None, data_dir: Optional[str] = None) -> FastAPI:
+    """``data_dir``: tables are kept under ``<data_dir>/tables/<name>/`` (their definition in ``table.json``, their
+    documents and embeddings in a log-structured merge store) and come back when the server starts again; without
+    it tables live in memory only.
+
+    ``content_security``: an :class:`antfly_b200.api.content.ContentSecurity` (or its dictionary form) governing
     media links in requests; by default only ``data:`` URLs are accepted."""
     app = FastAPI(title="antfly-b200 inference", version="0.1")
     from .content import ContentFetcher, ContentSecurity
@@ -1188,6 +1195,60 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     # ---- tables: documents + dense / sparse / full-text indexes, hybrid query ---------------------------------
     app.state.tables = {}
 
+    def table_dir(name: str) -> str:
+        if not re.fullmatch(r"[A-Za-z0-9_.-]{1,128}", name) or name in (".", ".."):
+            raise ValueError("a durable table's name is 1 to 128 letters, digits, '_', '-' or '.'")
+        d = os.path.join(data_dir, "tables", name)
+        os.makedirs(d, exist_ok=True)
+        return d
+
+    def build_table(table: str, spec: dict) -> dict:
+        from ..index.flat import GrowableFlatIndex
+        from ..index.table import Table
+
+        embed = rerank = None
+        dim = spec.get("dimension")
+        embedder, reranker = spec.get("embedder"), spec.get("reranker")
+        metric, index_type = spec.get("metric", "cosine"), spec.get("index_type", "flat")
+        if embedder:
+            if not dim:
+                dim = mgr.get(embedder, "embedder").pipeline.dim
+            embed = lambda texts: mgr.get(embedder, "embedder").pipeline.embed(list(texts))[0]
+        if reranker:
+            rerank = lambda q, docs: mgr.get(reranker, "reranker").pipeline.rerank(q, list(docs))[0]
+        dense = None
+        if dim:
+            if index_type == "hbc":
+                dense = _HbcAdapter(dim, metric)
+            elif index_type == "flat":
+                dense = GrowableFlatIndex(dim, metric, device=str(mgr.device))
+            elif index_type == "hnsw":
+                from ..index.hnsw import HNSWIndex
+
+                dense = HNSWIndex(dim, metric, neighbors=int(spec.get("neighbors", 16)),
+                                  ef_construction=int(spec.get("ef_construction", 200)),
+                                  ef_search=int(spec.get("ef_search", 64)))
+            else:
+                raise ValueError(f"unknown index_type {index_type!r}")
+        store = None
+        if data_dir:
+            from ..index.lsm_store import LsmStore
+
+            store = LsmStore(os.path.join(table_dir(table), "store"))
+        tbl = Table(table, dense_index=dense, embed=embed, rerank=rerank, text_field=spec.get("text_field", "text"),
+                    store=store)
+        restored = tbl.recover()
+        app.state.tables[table] = tbl
+        return {"table": table, "dimension": dim, "metric": metric, "index_type": index_type,
+                "durable": bool(data_dir), "restored": restored}
+
+    if data_dir and os.path.isdir(os.path.join(data_dir, "tables")):
+        for name in sorted(os.listdir(os.path.join(data_dir, "tables"))):
+            spec_path = os.path.join(data_dir, "tables", name, "table.json")
+            if os.path.exists(spec_path):
+                with open(spec_path, encoding="utf-8") as f:
+                    build_table(name, json.load(f))
+
     async def table_create(table: str, request: Request):
         req, bad = await parse(request, S.TableCreateRequest)
         if bad:
@@ -1196,36 +1257,12 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
             return _err(409, "table_exists", f"table {table!r} already exists")
 
         def work():
-            from ..index.flat import GrowableFlatIndex
-            from ..index.table import Table
-
-            embed = rerank = None
-            dim = req.dimension
-            if req.embedder:
-                pipe = mgr.get(req.embedder, "embedder").pipeline
-                embed = lambda texts: pipe.embed(list(texts))[0]
-                dim = dim or pipe.dim
-            if req.reranker:
-                rpipe = mgr.get(req.reranker, "reranker").pipeline
-                rerank = lambda q, docs: rpipe.rerank(q, list(docs))[0]
-            dense = None
-            if dim:
-                if req.index_type == "hbc":
-                    dense = _HbcAdapter(dim, req.metric)
-                elif req.index_type == "flat":
-                    dense = GrowableFlatIndex(dim, req.metric, device=str(mgr.device))
-                elif req.index_type == "hnsw":
-                    from ..index.hnsw import HNSWIndex
-
-                    extra = req.model_extra or {}
-                    dense = HNSWIndex(dim, req.metric, neighbors=int(extra.get("neighbors", 16)),
-                                      ef_construction=int(extra.get("ef_construction", 200)),
-                                      ef_search=int(extra.get("ef_search", 64)))
-                else:
-                    raise ValueError(f"unknown index_type {req.index_type!r}")
-            app.state.tables[table] = Table(table, dense_index=dense, embed=embed, rerank=rerank,
-                                            text_field=req.text_field)
-            return {"table": table, "dimension": dim, "metric": req.metric, "index_type": req.index_type}
+            spec = req.model_dump()
+            info = build_table(table, spec)
+            if data_dir:
+                with open(os.path.join(table_dir(table), "table.json"), "w", encoding="utf-8") as f:
+                    json.dump({**spec, "dimension": info["dimension"]}, f)
+            return info
 
         return await asyncio.to_thread(run_guarded, "table_create", 1, work)
 
@@ -1321,6 +1358,19 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
 
         return await asyncio.to_thread(run_guarded, "table_query", 1, work)
 
+    async def table_drop(table: str):
+        tbl = app.state.tables.pop(table, None)
+        if tbl is None:
+            return _err(404, "table_not_found", f"table {table!r} does not exist")
+
+        def work():
+            if tbl.store is not None:
+                tbl.store.close()
+                shutil.rmtree(table_dir(table), ignore_errors=True)
+            return {"table": table, "dropped": True}
+
+        return await asyncio.to_thread(run_guarded, "table_drop", 1, work)
+
     async def table_list():
         return {"tables": [{"name": n, "count": len(t)} for n, t in app.state.tables.items()]}
 
@@ -1373,6 +1423,7 @@ def create_app(manager: Optional[ModelManager] = None, indexes: Optional[Dict[st
     app.add_api_route("/ai/v1/search", search, methods=["POST"])
     app.add_api_route("/db/v1/tables", table_list, methods=["GET"])
     app.add_api_route("/db/v1/tables/{table}", table_create, methods=["POST", "PUT"])
+    app.add_api_route("/db/v1/tables/{table}", table_drop, methods=["DELETE"])
     app.add_api_route("/db/v1/tables/{table}/batch", table_batch, methods=["POST"])
     app.add_api_route("/db/v1/tables/{table}/query", table_query, methods=["POST"])
     app.add_api_route("/ai/v1/models", models, methods=["GET"])

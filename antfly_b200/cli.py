@@ -80,7 +80,8 @@ def cmd_run(args) -> int:
             _get(mgr, name, t)
     serve(host, port, manager=mgr, max_concurrent_requests=cfg.max_concurrent_requests or 64,
           max_queue_size=cfg.max_queue_size or 256, request_timeout_s=cfg.request_timeout_s,
-          api_key=cfg.api_key, content_security=dict(cfg.content_security, allow_downloads=cfg.allow_downloads))
+          api_key=cfg.api_key, content_security=dict(cfg.content_security, allow_downloads=cfg.allow_downloads),
+          data_dir=cfg.data_dir)
     return 0
 
 

@@ -140,6 +140,13 @@ class Client:
     def create_table(self, name: str, **spec) -> Dict[str, Any]:
         return self._post(f"/db/v1/tables/{name}", spec)
 
+    def drop_table(self, name: str) -> Dict[str, Any]:
+        r = self.s.delete(self.base + f"/db/v1/tables/{name}", timeout=self.timeout)
+        if r.status_code >= 400:
+            e = r.json()
+            raise ApiError(r.status_code, str(e.get("error")), str(e.get("message")))
+        return r.json()
+
     def upsert(self, table: str, docs: Dict[str, Dict[str, Any]], deletes: Sequence[str] = ()) -> Dict[str, Any]:
         return self._post(f"/db/v1/tables/{table}/batch", {"inserts": docs, "deletes": list(deletes)})
 

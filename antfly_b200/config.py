@@ -64,6 +64,7 @@ class Config:
     model_strategies: Dict[str, str] = field(default_factory=dict)
     allow_downloads: bool = False
     content_security: Dict[str, object] = field(default_factory=dict)
+    data_dir: Optional[str] = None      # tables are kept here across restarts (none: in memory only)
     log: LogConfig = field(default_factory=LogConfig)
 
     # -- derived -------------------------------------------------------------------------------------------

@@ -11,7 +11,7 @@ reranking/mod.zig:26 rerank stage; request fields from specs/openapi/antfly/meta
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, Hashable, List, Mapping, Optional, Sequence
+from typing import Callable, Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -59,10 +59,17 @@ class Table:
     def __init__(self, name: str, dense_index=None, embed: Optional[Callable[[Sequence[str]], torch.Tensor]] = None,
                  sparse_terms: int = 0, sparse_encode: Optional[Callable[[Sequence[str]], torch.Tensor]] = None,
                  rerank: Optional[Callable[[str, Sequence[str]], Sequence[float]]] = None, text_field: str = "text",
-                 device="cpu"):
+                 device="cpu", store=None):
         """``dense_index``: any index with ``add(vectors, ids)`` / ``search(q, k[, effort])`` returning distances
         and integer ids (flat, IVF, HBC, sharded).  ``embed`` / ``sparse_encode`` / ``rerank`` are the model
-        pipelines (callables so that the table does not depend on how they are served)."""
+        pipelines (callables so that the table does not depend on how they are served).
+
+        ``store``: an :class:`antfly_b200.index.lsm_store.LsmStore`.  With one, every upsert / delete batch is one
+        write transaction (documents as JSON under namespace 4, their embeddings as little-endian fp32 under
+        namespace 5, sparse rows under 6), and :meth:`recover` rebuilds the in-memory indexes from it without
+        running any model -- the document store / index split of the reference's shard database
+        (zig/pkg/antfly/src/storage/docstore.zig over its LSM backend)."""
+        self.store = store
         self.name, self.dense, self.embed, self.rerank = name, dense_index, embed, rerank
         self.sparse = SparseIndex(sparse_terms, device) if sparse_terms else None
         self.sparse_encode, self.text_field = sparse_encode, text_field
@@ -74,17 +81,89 @@ class Table:
     def __len__(self) -> int:
         return len(self.docs)
 
+    # -- durability ----------------------------------------------------------------------------------------
+    NS_DOCS, NS_EMBEDDINGS, NS_SPARSE = 4, 5, 6
+
+    @staticmethod
+    def _store_key(key: Hashable) -> bytes:
+        if isinstance(key, str):
+            return b"s" + key.encode("utf-8")
+        if isinstance(key, int) and not isinstance(key, bool) and 0 <= key < 1 << 64:
+            return b"i" + key.to_bytes(8, "big")
+        raise TypeError("a durable table takes string or non-negative integer keys")
+
+    @staticmethod
+    def _from_store_key(raw: bytes) -> Hashable:
+        return raw[1:].decode("utf-8") if raw[:1] == b"s" else int.from_bytes(raw[1:], "big")
+
+    def recover(self, batch: int = 1024) -> int:
+        """Re-applies what the store holds to the in-memory indexes.  -> documents restored."""
+        import json
+
+        if self.store is None:
+            return 0
+        store, self.store = self.store, None                  # the replay must not write back
+        try:
+            n = 0
+            with store.begin_read() as r:
+                rows: List[Tuple[Hashable, dict, Optional[bytes], Optional[bytes]]] = []
+
+                def apply():
+                    if not rows:
+                        return
+                    docs = {k: d for k, d, _, _ in rows}
+                    have = [e is not None for _, _, e, _ in rows]
+                    emb = None
+                    if self.dense is not None:
+                        if not all(have):
+                            raise ValueError(f"table {self.name!r}: stored documents without stored embeddings")
+                        emb = torch.stack([torch.frombuffer(bytearray(e), dtype=torch.float32) for _, _, e, _ in rows])
+                    sp = None
+                    if self.sparse is not None and all(s is not None for _, _, _, s in rows):
+                        sp = torch.stack([torch.frombuffer(bytearray(s), dtype=torch.float32) for _, _, _, s in rows])
+                    self._apply(docs, emb, sp)
+                    rows.clear()
+
+                for raw, body in r.items(self.NS_DOCS):
+                    rows.append((self._from_store_key(raw), json.loads(body), r.get(self.NS_EMBEDDINGS, raw),
+                                 r.get(self.NS_SPARSE, raw)))
+                    n += 1
+                    if len(rows) >= batch:
+                        apply()
+                apply()
+            return n
+        finally:
+            self.store = store
+
     def upsert(self, docs: Mapping[Hashable, dict], embeddings: Optional[torch.Tensor] = None) -> None:
+        keys = list(docs)
+        texts = [str(docs[k].get(self.text_field, "")) for k in keys]
+        if self.dense is not None and embeddings is None:
+            if self.embed is None:
+                raise ValueError("table has a dense index but neither embeddings nor an embedder were given")
+            embeddings = self.embed(texts)
+        sparse_rows = self.sparse_encode(texts) if self.sparse is not None and self.sparse_encode is not None else None
+        if self.store is not None:                            # durable first: a crash after this point replays it
+            import json
+
+            with self.store.begin_write() as w:
+                for i, k in enumerate(keys):
+                    raw = self._store_key(k)
+                    w.put(self.NS_DOCS, raw, json.dumps(docs[k], separators=(",", ":")).encode("utf-8"))
+                    if self.dense is not None:
+                        w.put(self.NS_EMBEDDINGS, raw, embeddings[i].detach().float().cpu().numpy().astype("<f4").tobytes())
+                    if sparse_rows is not None:
+                        w.put(self.NS_SPARSE, raw, sparse_rows[i].detach().float().cpu().numpy().astype("<f4").tobytes())
+        self._apply(docs, embeddings, sparse_rows)
+
+    def _apply(self, docs: Mapping[Hashable, dict], embeddings: Optional[torch.Tensor],
+               sparse_rows: Optional[torch.Tensor]) -> None:
         keys = list(docs)
         texts = [str(docs[k].get(self.text_field, "")) for k in keys]
         for k, t in zip(keys, texts):
             self.docs[k] = docs[k]
             self.fulltext.add(k, t)
         if self.dense is not None:
-            if embeddings is None:
-                if self.embed is None:
-                    raise ValueError("table has a dense index but neither embeddings nor an embedder were given")
-                embeddings = self.embed(texts)
             ints = []
             for k in keys:
                 if k not in self._int_of:
@@ -92,11 +171,16 @@ class Table:
                     self._key_of.append(k)
                 ints.append(self._int_of[k])
             self.dense.add(embeddings.float(), torch.tensor(ints, dtype=torch.int64))
-        if self.sparse is not None and self.sparse_encode is not None:
-            self.sparse.add_dense_rows(keys, self.sparse_encode(texts))
+        if self.sparse is not None and sparse_rows is not None:
+            self.sparse.add_dense_rows(keys, sparse_rows)
 
     def delete(self, key: Hashable) -> bool:
         found = self.docs.pop(key, None) is not None
+        if found and self.store is not None:
+            raw = self._store_key(key)
+            with self.store.begin_write() as w:
+                for ns in (self.NS_DOCS, self.NS_EMBEDDINGS, self.NS_SPARSE):
+                    w.delete(ns, raw)
         self.fulltext.delete(key)
         if self.sparse is not None:
             self.sparse.delete(key)
